@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the quantised GEMV hot path: Q4_K x Q8_K dequant-dot GEMV GB/s on B200.
+
+One step = one pass over the quant-format GEMV sweep for Q4_K - out x in of 4096x4096, 14336x4096,
+4096x14336 and 151936x896 (K padded to 1024), batch 1 - where every launch reads a different
+resident copy of its weight matrix; the copies of a shape total more than 4x the L2 size, so no
+launch is served from L2.  `value` = algorithmic bytes of the step (weights + Q8_K activations +
+fp32 outputs) / device time, inputs already in HBM.  `e2e` = the same sweep through the
+reference-named host-pointer entry point gemv_q4_k_q8_k(y, W, x_q8, M, K): weights registered
+(resident, as after model load), activations copied in from pinned host memory and outputs copied
+back inside the timed region.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--detail]
+
+Under torchrun every rank runs the sweep on its own GPU over its own shard of rows (no collective
+in the data path; weak scaling); the time is the max over ranks.
+--impl reference times the reference's own CPU thread-pool path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as graft  # noqa: E402
+
+pkg = graft.load_package()
+synth = pkg.synth
+
+METRIC = "q4_k_gemv_hbm_gbs"
+UNIT = "GB/s"
+L2_BYTES_X4 = 4 * 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+
+def sweep(fmt: str):
+    return [(m, synth.k_for(fmt, k), k) for (m, k) in synth.SWEEP_SHAPES]
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in text.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------- reference arm
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    loader = graft.oracle_loader()
+    threads = loader.host_threads()
+    os.environ["CK_NUM_THREADS"] = str(threads)
+    ref = loader.load_reference()
+    kind = "reference"
+    if ref is None:
+        ref, kind = loader.load_oracle(), "port"
+        threads = 1
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+
+    shapes = sweep("q4_k")
+    prefix = "" if kind == "reference" else "oracle_"
+    work = []
+    for m, k, k_raw in shapes:
+        w = synth.make_weights("q4_k", m, k, seed=0)
+        x = synth.make_x(k, seed=0, k_valid=k_raw if k_raw != k else None)
+        xq = cases.quantize_q8_k(ref, prefix, x)
+        y = np.zeros(m, dtype=np.float32)
+        work.append((m, k, w, xq, y))
+    if kind == "reference":
+        ref.ck_parallel_decode_init()
+        fn = ref.gemv_q4_k_q8_k_parallel_dispatch       # the reference's own thread-pool path
+    else:
+        fn = ref.oracle_gemv_q4_k_q8_k
+    fn.restype = None
+    bytes_per_step = sum(synth.gemv_bytes("q4_k", m, k) for m, k, *_ in work)
+
+    def step():
+        for m, k, w, xq, y in work:
+            fn(cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(m), C.c_int(k))
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = bytes_per_step * args.steps / dt / 1e9
+    sample = "one GEMV per sweep shape per step (no weight rotation; the largest matrix alone exceeds the host caches)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "quant-format GEMV sweep, Q4_K, batch 1", "shapes": [[m, k] for m, k, _ in shapes],
+                   "path": "gemv_q4_k_q8_k_parallel_dispatch on the reference thread pool" if kind == "reference" else "scalar port"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_sample(budget_s: float = 12.0):
+    """Rank 0, N=1: the reference's thread-pool GEMV on a bounded sample of the same sweep."""
+    loader = graft.oracle_loader()
+    threads = loader.host_threads()
+    os.environ["CK_NUM_THREADS"] = str(threads)
+    ref = loader.load_reference()
+    kind = "reference" if ref is not None else "port"
+    if ref is None:
+        ref, threads = loader.load_oracle(), 1
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+
+    prefix = "" if kind == "reference" else "oracle_"
+    if kind == "reference":
+        ref.ck_parallel_decode_init()
+        fn = ref.gemv_q4_k_q8_k_parallel_dispatch
+    else:
+        fn = ref.oracle_gemv_q4_k_q8_k
+    fn.restype = None
+    total_b, total_t, used = 0, 0.0, []
+    for m, k, k_raw in sweep("q4_k"):
+        w = synth.make_weights("q4_k", m, k, seed=0)
+        xq = cases.quantize_q8_k(ref, prefix, synth.make_x(k, seed=0, k_valid=k_raw if k_raw != k else None))
+        y = np.zeros(m, dtype=np.float32)
+        args = (cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(m), C.c_int(k))
+        fn(*args)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            fn(*args)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > budget_s / 4 or reps >= 50:
+                break
+        total_b += reps * synth.gemv_bytes("q4_k", m, k)
+        total_t += dt
+        used.append(f"{m}x{k}:{reps}")
+    return {"value": total_b / total_t / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": "Q4_K sweep shapes, repetitions " + " ".join(used) + " (up to 3 s or 50 runs each, after one warm-up)"}
+
+
+# ------------------------------------------------------------------------------------- CUDA arm
+
+def run_cuda(args, rank: int, world: int, local_rank: int):
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = pkg.load_lib()
+    if lib.ckb200_init(local_rank) != 0:
+        raise RuntimeError(lib.ckb200_last_error_message().decode())
+    lib.ckb200_launch_count.restype = C.c_longlong
+    lib.ckb200_stream.restype = C.c_void_p
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+
+    dev = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+
+    fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])
+    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}
+    quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0}
+
+    results = {}
+    host_w = {}
+    for fmt in fmts:
+        plan = []
+        for m, k, k_raw in sweep(fmt):
+            w_host = synth.make_weights(fmt, m, k, seed=rank)          # every rank holds its own shard of rows
+            nbytes = w_host.nbytes
+            copies = max(2, -(-L2_BYTES_X4 // nbytes))
+            slot = (nbytes + 255) & ~255
+            wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
+            src = torch.from_numpy(w_host).to(dev)
+            for c in range(copies):
+                wbuf[c * slot:c * slot + nbytes].copy_(src)
+            x = torch.from_numpy(synth.make_x(k, seed=rank, k_valid=k_raw if k_raw != k else None)).to(dev)
+            xq = torch.empty(synth.row_bytes("q8_0" if fmt == "q8_0" else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
+            y = torch.empty(copies, m, dtype=torch.float32, device=dev)
+            rc = quant_dev[fmt](C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, sp)
+            assert rc == 0
+            plan.append(dict(m=m, k=k, copies=copies, slot=slot, wbuf=wbuf, xq=xq, y=y, bytes=synth.gemv_bytes(fmt, m, k)))
+            if fmt == "q4_k":
+                host_w[(m, k)] = w_host
+        torch.cuda.synchronize()
+
+        def step(plan=plan, fmt=fmt):
+            for p in plan:
+                base = p["wbuf"].data_ptr()
+                for c in range(p["copies"]):
+                    rc = gemv_dev[fmt](C.c_void_p(p["y"][c].data_ptr()), C.c_void_p(base + c * p["slot"]),
+                                       C.c_void_p(p["xq"].data_ptr()), p["m"], p["k"], sp)
+                    if rc != 0:
+                        raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+        launches_before = lib.ckb200_launch_count()
+        step()                                             # un-captured: sets kernel attributes, warms caches
+        launches_per_step = lib.ckb200_launch_count() - launches_before
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(args.warmup):
+            graph.replay()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        sampler = ClockSampler(local_rank) if fmt == "q4_k" else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler else None
+        ms = e0.elapsed_time(e1)
+        if dist:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        step_bytes = sum(p["bytes"] * p["copies"] for p in plan)
+        per_shape = {}
+        if args.detail:
+            for p in plan:                                 # per-shape timing, graph of one rotation of that shape
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    step(plan=[p], fmt=fmt)
+                g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(max(3, args.steps // 2)):
+                    g.replay()
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms = a.elapsed_time(b) / max(3, args.steps // 2)
+                per_shape[f"{p['m']}x{p['k']}"] = {"gbs": p["bytes"] * p["copies"] / t_ms / 1e6, "us_per_launch": t_ms * 1e3 / p["copies"]}
+        rc = lib.ckb200_synchronize()
+        if rc != 0:
+            raise RuntimeError(lib.ckb200_last_error_message().decode())
+        results[fmt] = dict(ms=ms, step_bytes=step_bytes, launches=launches_per_step, clocks=clocks, per_shape=per_shape, plan=plan)
+
+    # ---- end to end through the reference-named host-pointer entry point (Q4_K)
+    e2e = None
+    plan = results["q4_k"]["plan"]
+    fn = lib.gemv_q4_k_q8_k
+    fn.restype = None
+    pinned = []
+    lib.ckb200_host_alloc.restype = C.c_void_p
+    for p in plan:
+        w_host = host_w[(p["m"], p["k"])]
+        assert lib.ckb200_register_weights(cases.vptr(w_host), C.c_size_t(w_host.nbytes)) == 0
+        xq_bytes = synth.row_bytes("q8_k", p["k"])
+        hx = lib.ckb200_host_alloc(C.c_size_t(xq_bytes))
+        hy = lib.ckb200_host_alloc(C.c_size_t(4 * p["m"]))
+        xq_host = p["xq"][:xq_bytes].cpu().numpy()
+        C.memmove(hx, xq_host.ctypes.data, xq_bytes)
+        pinned.append((p, w_host, hx, hy, xq_bytes))
+
+    def e2e_step():
+        for p, w_host, hx, hy, _ in pinned:
+            fn(C.c_void_p(hy), cases.vptr(w_host), C.c_void_p(hx), p["m"], p["k"])
+
+    for _ in range(max(3, args.warmup)):
+        e2e_step()
+    if dist:
+        dist.barrier()
+    lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(args.steps, 20)
+    e0.record(lstream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(lstream)
+    lstream.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_bytes = sum(p["bytes"] for p in plan)
+    e2e = {"value": world * e2e_bytes * e2e_steps / e2e_ms / 1e6, "unit": UNIT,
+           "h2d_bytes_per_step": sum(x[4] for x in pinned), "d2h_bytes_per_step": sum(4 * x[0]["m"] for x in pinned),
+           "call": "gemv_q4_k_q8_k(y_host, W_host_registered, x_q8_host, M, K), one call per sweep shape per step",
+           "ms_per_step": e2e_ms / e2e_steps}
+    for p, w_host, hx, hy, _ in pinned:
+        lib.ckb200_unregister_weights(cases.vptr(w_host))
+        lib.ckb200_host_free(C.c_void_p(hx))
+        lib.ckb200_host_free(C.c_void_p(hy))
+    pkg.check(lib)
+
+    if rank == 0:
+        r = results["q4_k"]
+        peak, peak_kind = measured_peak()
+        gbs_one = r["step_bytes"] * args.steps / r["ms"] / 1e6
+        value = gbs_one * world
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": r["ms"] / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 dot (dp4a), fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "quant-format GEMV sweep, Q4_K x Q8_K, batch 1",
+                       "shapes": [[p["m"], p["k"]] for p in r["plan"]],
+                       "l2": "every launch reads a different weight copy; copies per shape total > 4x L2 (rotation "
+                             + "/".join(str(p["copies"]) for p in r["plan"]) + ")",
+                       "sharding": "each rank streams its own shard of rows; no collective in the data path",
+                       "timing": "CUDA graph of one step replayed; CUDA events on the launching stream; max over ranks"},
+            "clocks": {k: r["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if r["clocks"] else None,
+            "e2e": e2e,
+            "gpu_launches": int(r["launches"] * args.steps),
+            "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "Q4_K GEMV (all sweep shapes)",
+                         "bytes_per_step": r["step_bytes"]},
+        }
+        if args.detail:
+            line["detail"] = {f: {"gbs": results[f]["step_bytes"] * args.steps / results[f]["ms"] / 1e6, "per_shape": results[f]["per_shape"]}
+                              for f in results}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_cuda(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,363 @@
+// Decode attention over the head-major fp32 KV cache with GQA and split-K over the context.
+//
+// Replaces attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406),
+// which calls attention_flash_decode per Q head (src/kernels/attention_flash_true.c:142-230, :696-722):
+// one query token, kv_head = h * Hkv / H, scores (q.k) / sqrt(head_dim), online softmax, out = P.V.
+//
+// Layout (the reference's memory plan): q [H][ad], K and V cache [Hkv][capacity][ad] fp32,
+// out [H][ad]; ad = aligned_head_dim.  Batched form: `batch` independent sequences with their own
+// q/out rows and cache slabs (strides given in floats).
+//
+// Fast path (ad = 64 or 128, group = H/Hkv <= 8): one CTA per (context split, kv head, sequence).
+// A warp takes 4 keys per step, 8 lanes per key; each lane owns ad/8 dimensions as float4 pieces so
+// that the 8 lanes read 128 contiguous bytes.  K and V rows are read ONCE for all `group` Q heads
+// that share the kv head.  The group partial dots are reduced with a transposing butterfly (7
+// shuffles for 8 heads); each lane keeps running (max, sum) for every head and `group` output
+// accumulators for its dimensions.  Splits write (max, sum, unnormalised out) to a scratch buffer
+// and a merge kernel combines them with the exact log-sum-exp rule.
+#include "device_common.cuh"
+#include "launch.h"
+#include "runtime.h"
+
+#include <math.h>
+
+namespace ckb {
+
+struct AttnParams {
+    const float *q;        // [batch][H][ad]
+    const float *k;        // [batch][Hkv][cap][ad] (batch stride kv_batch_stride floats)
+    const float *v;
+    float *out;            // [batch][H][ad]
+    float *part;           // scratch [batch][H][splits][ad + 2] (only when splits > 1)
+    const int *pos_ptr;    // when not NULL the context length is *pos_ptr + 1 (read on the device, graph-replayable)
+    long long kv_batch_stride;
+    int H, Hkv, kv_tokens, cap, ad, splits;
+    float scale;
+};
+
+__device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(*p.pos_ptr + 1, p.cap) : p.kv_tokens; }
+
+constexpr int ATTN_G = 8;        // max Q heads per kv head in the fast path
+constexpr int ATTN_NW = 4;       // warps per CTA
+
+template <int AD>
+__global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
+{
+    constexpr int C = AD / 32;                 // float4 pieces per lane
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane >> 3, li = lane & 7;
+    const int group = p.H / p.Hkv, h0 = kvh * group;   // heads h0 .. h0+group-1 map to kvh (H % Hkv == 0)
+
+    __shared__ __align__(16) float q_s[ATTN_G][AD];
+    __shared__ float merge_s[ATTN_NW][ATTN_G][AD + 2];
+
+    for (int i = threadIdx.x; i < ATTN_G * AD; i += blockDim.x) {
+        const int h = i / AD, c = i - h * AD;
+        q_s[h][c] = h < group ? p.q[((size_t)seq * p.H + h0 + h) * AD + c] * p.scale : 0.0f;
+    }
+    __syncthreads();
+
+    const float *kbase = p.k + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD;
+    const float *vbase = p.v + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD;
+    const int kv_tokens = attn_kv_tokens(p);
+    const int tokens_per_split = (((kv_tokens + p.splits - 1) / p.splits) + 3) & ~3;
+    const int t_begin = split * tokens_per_split;
+    const int t_end = min(kv_tokens, t_begin + tokens_per_split);
+
+    float m[ATTN_G], l[ATTN_G];
+    float4 acc[ATTN_G][C];
+#pragma unroll
+    for (int h = 0; h < ATTN_G; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) acc[h][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += ATTN_NW * 4) {
+        const int t = t0 + sub;
+        const bool valid = t < t_end;
+        const int tc = valid ? t : t_end - 1;
+        float4 kr[C], vr[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            kr[c] = __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)tc * AD) + c * 8 + li);
+            vr[c] = __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)tc * AD) + c * 8 + li);
+        }
+        // partial dots of this lane's dimensions with every head's (pre-scaled) query
+        float s[ATTN_G];
+#pragma unroll
+        for (int h = 0; h < ATTN_G; ++h) {
+            float a = 0.0f;
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[h][(c * 8 + li) * 4]);
+                a = fmaf(qv.x, kr[c].x, a);
+                a = fmaf(qv.y, kr[c].y, a);
+                a = fmaf(qv.z, kr[c].z, a);
+                a = fmaf(qv.w, kr[c].w, a);
+            }
+            s[h] = a;
+        }
+        // transposing butterfly over the 8 lanes of a key: afterwards lane li holds the full dot of head li
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float mine = (li & 4) ? s[j + 4] : s[j], theirs = (li & 4) ? s[j] : s[j + 4];
+            s[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, 4);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float mine = (li & 2) ? s[j + 2] : s[j], theirs = (li & 2) ? s[j] : s[j + 2];
+            s[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, 2);
+        }
+        {
+            const float mine = (li & 1) ? s[1] : s[0], theirs = (li & 1) ? s[0] : s[1];
+            s[0] = mine + __shfl_xor_sync(0xffffffffu, theirs, 1);
+        }
+        const float score = valid ? s[0] : -INFINITY;     // head li, key t
+        // broadcast each head's score inside the key's 8 lanes, update the running softmax
+#pragma unroll
+        for (int h = 0; h < ATTN_G; ++h) {
+            const float sh = __shfl_sync(0xffffffffu, score, (sub << 3) | h);
+            if (h < group && sh > -INFINITY) {
+                float pw;
+                if (sh > m[h]) {
+                    const float corr = expf(m[h] - sh);   // exp(-inf) = 0 on the first key
+                    l[h] *= corr;
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        acc[h][c].x *= corr; acc[h][c].y *= corr; acc[h][c].z *= corr; acc[h][c].w *= corr;
+                    }
+                    m[h] = sh;
+                    pw = 1.0f;
+                } else {
+                    pw = expf(sh - m[h]);
+                }
+                l[h] += pw;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    acc[h][c].x = fmaf(pw, vr[c].x, acc[h][c].x);
+                    acc[h][c].y = fmaf(pw, vr[c].y, acc[h][c].y);
+                    acc[h][c].z = fmaf(pw, vr[c].z, acc[h][c].z);
+                    acc[h][c].w = fmaf(pw, vr[c].w, acc[h][c].w);
+                }
+            }
+        }
+    }
+
+    // merge the 4 key streams of the warp (lanes with the same li: xor 8, xor 16)
+#pragma unroll
+    for (int h = 0; h < ATTN_G; ++h) {
+#pragma unroll
+        for (int o = 8; o <= 16; o <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o), lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+            const float mn = fmaxf(m[h], mo);
+            const float ca = m[h] == -INFINITY ? 0.0f : expf(m[h] - mn), cb = mo == -INFINITY ? 0.0f : expf(mo - mn);
+            l[h] = l[h] * ca + lo * cb;
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                acc[h][c].x = acc[h][c].x * ca + __shfl_xor_sync(0xffffffffu, acc[h][c].x, o) * cb;
+                acc[h][c].y = acc[h][c].y * ca + __shfl_xor_sync(0xffffffffu, acc[h][c].y, o) * cb;
+                acc[h][c].z = acc[h][c].z * ca + __shfl_xor_sync(0xffffffffu, acc[h][c].z, o) * cb;
+                acc[h][c].w = acc[h][c].w * ca + __shfl_xor_sync(0xffffffffu, acc[h][c].w, o) * cb;
+            }
+            m[h] = mn;
+        }
+    }
+    if (sub == 0) {
+#pragma unroll
+        for (int h = 0; h < ATTN_G; ++h) {
+#pragma unroll
+            for (int c = 0; c < C; ++c) *reinterpret_cast<float4 *>(&merge_s[warp][h][(c * 8 + li) * 4]) = acc[h][c];
+            if (li == 0) { merge_s[warp][h][AD] = m[h]; merge_s[warp][h][AD + 1] = l[h]; }
+        }
+    }
+    __syncthreads();
+
+    // merge the warps; thread -> (head, dimension)
+    for (int i = threadIdx.x; i < group * AD; i += blockDim.x) {
+        const int h = i / AD, c = i - h * AD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATTN_NW; ++w) mm = fmaxf(mm, merge_s[w][h][AD]);
+        float ll = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATTN_NW; ++w) {
+            const float mw = merge_s[w][h][AD];
+            const float f = mw == -INFINITY ? 0.0f : expf(mw - mm);
+            ll += merge_s[w][h][AD + 1] * f;
+            a += merge_s[w][h][c] * f;
+        }
+        const size_t head = (size_t)seq * p.H + h0 + h;
+        if (p.splits == 1) {
+            p.out[head * AD + c] = ll > 0.0f ? a / ll : 0.0f;
+        } else {
+            float *dst = p.part + (head * p.splits + split) * (AD + 2);
+            dst[c] = a;
+            if (c == 0) { dst[AD] = mm; dst[AD + 1] = ll; }
+        }
+    }
+}
+
+// out[head][c] = sum_s part[s][c] * exp(m_s - M) / sum_s l_s * exp(m_s - M)
+__global__ void attn_merge_kernel(const float *__restrict__ part, float *__restrict__ out, int splits, int ad)
+{
+    const size_t head = blockIdx.x;
+    const float *src = part + head * splits * (ad + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * (ad + 2) + ad]);
+    for (int c = threadIdx.x; c < ad; c += blockDim.x) {
+        float ll = 0.0f, a = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = src[s * (ad + 2) + ad];
+            const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
+            ll += src[s * (ad + 2) + ad + 1] * f;
+            a += src[s * (ad + 2) + c] * f;
+        }
+        out[head * ad + c] = ll > 0.0f ? a / ll : 0.0f;
+    }
+}
+
+// Any head size / group size: one CTA per Q head, warps stride the keys, lanes stride the dimensions.
+constexpr int ATTN_GEN_MAXD = 512;
+__global__ void __launch_bounds__(128) attn_decode_generic_kernel(AttnParams p)
+{
+    const int h = blockIdx.x, seq = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int ad = p.ad, kvh = (int)((long long)h * p.Hkv / p.H);
+    const float *q = p.q + ((size_t)seq * p.H + h) * ad;
+    const float *kbase = p.k + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * ad;
+    const float *vbase = p.v + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * ad;
+    constexpr int PER = ATTN_GEN_MAXD / 32;
+    float qr[PER], acc[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int c = lane + 32 * j;
+        qr[j] = c < ad ? q[c] * p.scale : 0.0f;
+        acc[j] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    const int kv_tokens = attn_kv_tokens(p);
+    for (int t = warp; t < kv_tokens; t += nw) {
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int c = lane + 32 * j;
+            if (c < ad) s = fmaf(qr[j], kbase[(size_t)t * ad + c], s);
+        }
+        s = group_sum<32>(s);
+        const float mn = fmaxf(m, s);
+        const float corr = m == -INFINITY ? 0.0f : expf(m - mn), pw = expf(s - mn);
+        l = l * corr + pw;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int c = lane + 32 * j;
+            if (c < ad) acc[j] = acc[j] * corr + pw * vbase[(size_t)t * ad + c];
+        }
+        m = mn;
+    }
+    __shared__ float ms[4], ls[4];
+    __shared__ float acc_s[4][ATTN_GEN_MAXD];
+    if (lane == 0) { ms[warp] = m; ls[warp] = l; }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int c = lane + 32 * j;
+        if (c < ad) acc_s[warp][c] = acc[j];
+    }
+    __syncthreads();
+    float mm = -INFINITY;
+    for (int w = 0; w < nw; ++w) mm = fmaxf(mm, ms[w]);
+    for (int c = threadIdx.x; c < ad; c += blockDim.x) {
+        float ll = 0.0f, a = 0.0f;
+        for (int w = 0; w < nw; ++w) {
+            const float f = ms[w] == -INFINITY ? 0.0f : expf(ms[w] - mm);
+            ll += ls[w] * f;
+            a += acc_s[w][c] * f;
+        }
+        p.out[((size_t)seq * p.H + h) * ad + c] = ll > 0.0f ? a / ll : 0.0f;
+    }
+}
+
+}  // namespace ckb
+
+using namespace ckb;
+
+extern "C" size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits)
+{
+    if (splits <= 1) return 0;
+    return (size_t)batch * num_heads * splits * (aligned_head_dim + 2) * sizeof(float);
+}
+
+// Number of context splits the launcher would use (1 = no scratch needed).
+extern "C" int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens)
+{
+    const int forced = ckb_tune_get("attn_splits", 0);
+    if (forced > 0) return forced;
+    const int sms = ckb_sm_count();
+    const long long ctas_wanted = 2LL * sms;
+    const long long base = (long long)batch * num_kv_heads;
+    int splits = (int)((ctas_wanted + base - 1) / base);
+    const int max_by_tokens = (kv_tokens + 63) / 64;        // at least 64 keys per split
+    if (splits > max_by_tokens) splits = max_by_tokens;
+    if (splits > 256) splits = 256;
+    if (splits < 1) splits = 1;
+    return splits;
+}
+
+// Core launcher: scratch may be NULL when splits == 1.  With pos_dev the context length is read on the
+// device as *pos_dev + 1 (kv_tokens then only has to be positive), so a captured graph can be replayed.
+extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cache, const float *v_cache, float *out,
+                                              int batch, long long kv_batch_stride, int num_heads, int num_kv_heads,
+                                              int kv_tokens, int cache_capacity, int head_dim, int aligned_head_dim,
+                                              int splits, float *scratch, const int *pos_dev, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !out) return 0;
+    if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return 0;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    AttnParams p;
+    p.q = q; p.k = k_cache; p.v = v_cache; p.out = out; p.part = scratch; p.pos_ptr = pos_dev;
+    p.kv_batch_stride = kv_batch_stride;
+    p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
+    p.scale = 1.0f / sqrtf((float)head_dim);
+    cudaStream_t st = ckb_stream(stream);
+    const int group = num_heads / num_kv_heads;
+    const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 &&
+                      group <= ATTN_G && (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 &&
+                      (kv_batch_stride % 4) == 0 && ckb_tune_get("attn_generic", 0) == 0;
+    if (!fast) {
+        if (aligned_head_dim > ATTN_GEN_MAXD) return ckb_fail(CKB_ERR_LIMIT, "attention decode: aligned_head_dim %d > %d", aligned_head_dim, ATTN_GEN_MAXD);
+        p.splits = 1;
+        attn_decode_generic_kernel<<<dim3(num_heads, batch), 128, 0, st>>>(p);
+        return ckb_check_launch("attn_decode_generic");
+    }
+    if (splits < 1) splits = 1;
+    if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
+    p.splits = splits;
+    const dim3 grid(splits, num_kv_heads, batch);
+    if (aligned_head_dim == 64) attn_decode_kernel<64><<<grid, ATTN_NW * 32, 0, st>>>(p);
+    else attn_decode_kernel<128><<<grid, ATTN_NW * 32, 0, st>>>(p);
+    if (ckb_check_launch("attn_decode")) return CKB_ERR_CUDA;
+    if (splits > 1) {
+        attn_merge_kernel<<<batch * num_heads, aligned_head_dim < 128 ? 64 : 128, 0, st>>>(scratch, out, splits, aligned_head_dim);
+        return ckb_check_launch("attn_merge");
+    }
+    return 0;
+}
+
+// Convenience form: picks the split count and takes the scratch from the library's own pool.
+extern "C" int ckb200_dev_attention_decode(const float *q, const float *k_cache, const float *v_cache, float *out,
+                                           int batch, long long kv_batch_stride, int num_heads, int num_kv_heads,
+                                           int kv_tokens, int cache_capacity, int head_dim, int aligned_head_dim, void *stream)
+{
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const int splits = ckb200_attention_decode_splits(batch, num_kv_heads, kv_tokens);
+    float *scratch = NULL;
+    if (splits > 1) {
+        scratch = (float *)ckb_scratch(CKB_SLOT_T, ckb200_attention_decode_scratch_bytes(batch, num_heads, aligned_head_dim, splits));
+        if (!scratch) return CKB_ERR_CUDA;
+    }
+    return ckb200_dev_attention_decode_ws(q, k_cache, v_cache, out, batch, kv_batch_stride, num_heads, num_kv_heads, kv_tokens,
+                                          cache_capacity, head_dim, aligned_head_dim, splits, scratch, NULL, stream);
+}

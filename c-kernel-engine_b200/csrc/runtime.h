@@ -1,0 +1,33 @@
+/* Internal host-side interface between runtime.c, the launchers (.cu) and the host-pointer shims. */
+#ifndef CKB200_RUNTIME_H
+#define CKB200_RUNTIME_H
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { CKB_SLOT_W = 0, CKB_SLOT_X = 1, CKB_SLOT_Y = 2, CKB_SLOT_A = 3, CKB_SLOT_B = 4, CKB_SLOT_C = 5, CKB_SLOT_T = 6, CKB_NSLOTS = 8 };
+
+int ckb_ensure_init(void);                 /* 0 or CKB_ERR_NO_DEVICE; initialises on first use */
+int ckb_sm_count(void);
+int *ckb_device_error_word(void);
+cudaStream_t ckb_stream(void *user);       /* user stream, or the library stream when NULL */
+int ckb_tune_get(const char *key, int dflt);
+
+/* Device scratch that grows on demand (never shrinks); one buffer per slot. */
+void *ckb_scratch(int slot, size_t bytes);
+/* Input staging: resident copy if registered (try_registry), the pointer itself if it is device
+ * memory, else an async H2D copy into the slot.  NULL on failure. */
+const void *ckb_stage_in(const void *host, size_t bytes, int slot, int try_registry);
+/* Output staging: the pointer itself if device memory, else the slot (copied back by ckb_finish_out). */
+void *ckb_stage_out(void *host, size_t bytes, int slot, int *needs_copy_back);
+/* D2H copy when needed, then synchronise the library stream. */
+int ckb_finish_out(void *host, const void *dev, size_t bytes, int needs_copy_back);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

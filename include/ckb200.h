@@ -1,0 +1,139 @@
+/*
+ * ckb200.h - C ABI of libckb200.so, the B200 (sm_100a) implementation of C-Kernel-Engine's
+ * quantised decode/prefill hot path.
+ *
+ * Two layers, both plain C (pointers and sizes only):
+ *
+ *  1. Device-pointer entry points, `ckb200_dev_*`: every pointer is DEVICE memory, the call
+ *     enqueues kernels on `stream` (a cudaStream_t passed as void*, NULL = the library's own
+ *     stream) and returns without synchronising.  This is the path the whole-step executor
+ *     uses and the one whose throughput is measured against the HBM / tensor roofline.
+ *
+ *  2. Reference-named entry points (include/ckb200_kernels.h): the reference's own symbols
+ *     with the reference's own signatures and HOST pointers, for generated libmodel.so code,
+ *     the reference's ctypes unit tests and the *_parallel_dispatch seam.  They copy
+ *     activations in and results out around the same kernels.  Weights registered with
+ *     ckb200_register_weights() stay resident in HBM and are found by host address range.
+ *
+ * Every int-returning function returns 0 on success or a CKB_ERR_* code (also kept for
+ * ckb200_last_error()).  Nothing aborts; there is no CPU fallback: without a CUDA device
+ * every compute call fails with CKB_ERR_NO_DEVICE.
+ *
+ * Citations are file:line inside the reference project (C-Kernel-Engine).
+ */
+#ifndef CKB200_H
+#define CKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ runtime + error channel
+ * The reference's kernels are void and return silently on bad arguments
+ * (src/kernels/gemm_kernels_q4k_q8k.c:188-190); GPU-only failures are reported here instead. */
+int ckb200_init(int device);                 /* select device, create the stream; idempotent */
+void ckb200_shutdown(void);                  /* free scratch, registry and stream */
+int ckb200_last_error(void);
+const char *ckb200_last_error_message(void);
+void ckb200_clear_error(void);
+int ckb200_synchronize(void);                /* sync the library stream; folds in the device error word */
+void *ckb200_stream(void);                   /* cudaStream_t of the library */
+long long ckb200_launch_count(void);         /* kernels launched by this library since load */
+int ckb200_tune_set(const char *key, int value);   /* kernel-variant switches for tuning runs */
+int ckb200_tune_get(const char *key, int dflt);
+
+/* Weights are immutable after load (generated code reads them from one bump arena at fixed
+ * offsets, version/v7/scripts/codegen_v7.py:1211-1232).  Registering the arena (or any
+ * weight buffer) uploads it once; later calls that pass a host pointer inside
+ * [host_ptr, host_ptr+bytes) use the device copy. */
+int ckb200_register_weights(const void *host_ptr, size_t bytes);
+int ckb200_unregister_weights(const void *host_ptr);
+void ckb200_unregister_all(void);
+const void *ckb200_device_ptr(const void *host_ptr);   /* NULL if not inside a registered range */
+
+/* Pinned host memory for callers that want the host<->device copies to run at full PCIe rate. */
+void *ckb200_host_alloc(size_t bytes);
+void ckb200_host_free(void *p);
+
+/* ------------------------------------------------------------------ device-pointer kernels */
+
+/* quantize_row_q8_k / quantize_batch_q8_k (src/kernels/gemm_kernels_q4k_q8k.c:53-119,
+ * src/kernels/gemm_kernels_q8_0.c:221-239): x fp32 [rows, k] -> block_q8_K [rows, k/256]; bit-exact. */
+int ckb200_dev_quantize_q8_k(const float *x, void *y, int rows, int k, void *stream);
+/* quantize_row_q8_0 / quantize_batch_q8_0 (src/kernels/gemm_kernels_q8_0.c:70-209); bit-exact. */
+int ckb200_dev_quantize_q8_0(const float *x, void *y, int rows, int k, void *stream);
+
+/* gemv_q4_k_q8_k (src/kernels/gemm_kernels_q4k_q8k.c:183-263): y[M] = W[M, K/256 x 144 B] . x_q8. */
+int ckb200_dev_gemv_q4_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+/* gemv_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1060-1088): 210-byte superblocks. */
+int ckb200_dev_gemv_q6_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+/* gemv_q8_0_q8_0 (src/kernels/gemm_kernels_q8_0.c:1237-1251): 34-byte blocks, Q8_0 activations. */
+int ckb200_dev_gemv_q8_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+
+/* gemv_q4_k / gemv_q6_k / gemv_q8_0 with fp32 activations (src/kernels/gemm_kernels_q4k.c:285-297,
+ * src/kernels/gemm_kernels_q6k.c:169-193, src/kernels/gemm_kernels_q8_0.c:632-649): the reference's debug path. */
+int ckb200_dev_gemv_q4_k(float *y, const void *W, const float *x, int M, int K, void *stream);
+int ckb200_dev_gemv_q6_k(float *y, const void *W, const float *x, int M, int K, void *stream);
+int ckb200_dev_gemv_q8_0(float *y, const void *W, const float *x, int M, int K, void *stream);
+
+/* dequant_q4_k_row / dequant_q6_k_row / dequant_q8_0_row (src/kernels/dequant_kernels.c:372-380, :422-430, :288-296). */
+int ckb200_dev_dequant_q4_k_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_dequant_q6_k_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n_elements, void *stream);
+
+/* gemm_nt_q4_k_q8_k (src/kernels/gemm_kernels_q4k_q8k.c:301-326), gemm_nt_q6_k_q8_k
+ * (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268), gemm_nt_q8_0_q8_0 (src/kernels/gemm_batch_int8.c:87-120):
+ * C[M,N] = A_q8[M,K] . B[N,K]^T + bias[N] (bias may be NULL). */
+int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
+int ckb200_dev_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
+int ckb200_dev_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
+/* the bias loop of those functions on its own: c[r][j] += bias[j] */
+int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void *stream);
+
+/* attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406) for `batch`
+ * independent sequences: q/out [batch][H][ad], caches [batch][Hkv][capacity][ad] with kv_batch_stride floats
+ * between sequences.  Split-K over the context; partial results go through a scratch buffer.
+ *   ckb200_dev_attention_decode     picks the split count, scratch comes from the library's pool
+ *   ckb200_dev_attention_decode_ws  caller gives split count and scratch (ckb200_attention_decode_scratch_bytes);
+ *                                   with pos_dev != NULL the context length is *pos_dev + 1, read on the device */
+int ckb200_dev_attention_decode(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
+                                long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
+                                int cache_capacity, int head_dim, int aligned_head_dim, void *stream);
+int ckb200_dev_attention_decode_ws(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
+                                   long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
+                                   int cache_capacity, int head_dim, int aligned_head_dim, int splits, float *scratch,
+                                   const int *pos_dev, void *stream);
+int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
+size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
+
+/* kv_cache_store (src/kernels/kv_cache_kernels.c:111-129): k, v [Hkv][head_dim] -> cache[Hkv][max_seq][head_dim] at pos
+ * (or at *pos_dev when given). */
+int ckb200_dev_kv_cache_store(float *kv_cache_k, float *kv_cache_v, const float *k, const float *v, int pos,
+                              const int *pos_dev, int num_kv_heads, int head_dim, int max_seq_len, void *stream);
+/* rmsnorm_forward (src/kernels/rmsnorm_kernels.c:126-250). */
+int ckb200_dev_rmsnorm_forward(const float *input, const float *gamma, float *output, float *rstd_cache, int tokens,
+                               int d_model, int aligned_embed_dim, float eps, void *stream);
+/* rope_precompute_cache_split (src/kernels/rope_kernels.c:221-243) and rope_forward_qk (:806-819), rotate-half. */
+int ckb200_dev_rope_precompute_cache_split(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base, void *stream);
+int ckb200_dev_rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                               int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                               const int *pos_dev, void *stream);
+/* swiglu_forward (src/kernels/swiglu_kernels.c:140-216): input [T][2D] gate then up, output [T][D]. */
+int ckb200_dev_swiglu_forward(const float *input, float *output, int tokens, int dim, void *stream);
+/* ck_residual_add_token_major (src/ckernel_orchestration.c:139-149). */
+int ckb200_dev_residual_add(const float *a, const float *b, float *out, int tokens, int aligned_embed_dim, void *stream);
+/* embedding_forward_q4_k / _q6_k / _q8_0 (src/kernels/embedding_kernels.c:76-239); ids are device int32. */
+int ckb200_dev_embedding_forward_q4_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
+                                      float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
+int ckb200_dev_embedding_forward_q6_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
+                                      float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
+int ckb200_dev_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
+                                      float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CKB200_H */

@@ -1,0 +1,123 @@
+/*
+ * ckb200_kernels.h - the reference's own kernel symbols, exported by libckb200.so with the
+ * reference's signatures and HOST pointers.  A generated libmodel.so, the *_parallel_dispatch
+ * seam or a ctypes test that links this library instead of libckernel_engine.so needs no source
+ * change.  Each declaration cites the reference prototype or definition it replaces
+ * (file:line inside C-Kernel-Engine).
+ *
+ * Behaviour kept from the reference: functions are void and return silently on NULL pointers or
+ * non-positive sizes; nothing is retained between calls; the caller owns every buffer.
+ * Added by the GPU: errors that cannot be expressed that way are readable through
+ * ckb200_last_error() (ckb200.h).
+ */
+#ifndef CKB200_KERNELS_H
+#define CKB200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- activation quantisers: include/ckernel_engine.h:269-293 (quantize_row_q8_0, quantize_batch_q8_0,
+ *      quantize_row_q8_k, quantize_batch_q8_k); definitions src/kernels/gemm_kernels_q4k_q8k.c:53-119,
+ *      src/kernels/gemm_kernels_q8_0.c:70-239 */
+void quantize_row_q8_k(const float *x, void *y, int k);
+void quantize_row_q8_k_ref(const float *x, void *y, int k);
+void quantize_batch_q8_k(const float *x, void *y, int num_rows, int k);
+void quantize_row_q8_0(const float *x, void *y, int k);
+void quantize_batch_q8_0(const float *x, void *y, int num_rows, int k);
+
+/* ---- Q4_K x Q8_K: include/ckernel_engine.h:295-337; src/kernels/gemm_kernels_q4k_q8k.c:183-326,
+ *      ISA variants src/kernels/gemm_kernels_q4k_avx.c:38-245, gemm_kernels_q4k_sse.c:33,
+ *      gemm_kernels_q4k_q8k_avx2.c:89-99, gemm_kernels_q4k_q8k_vnni.c:95-105 */
+void gemv_q4_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_ref(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_avx(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_avx2(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_vnni(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_sse(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q4_k_q8_k_parallel(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemv_q4_k_q8_k_parallel_simd(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemm_q4_k_q8_k(float *Y, const void *W, const void *X_q8, int M, int N, int K);
+void gemm_q4_k_q8_k_ref(float *Y, const void *W, const void *X_q8, int M, int N, int K);
+void gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+
+/* ---- Q6_K x Q8_K: include/ckernel_engine.h:335-358; src/kernels/gemm_kernels_q6k_q8k.c:197-214, :1032-1268 */
+void vec_dot_q6_k_q8_k(int n, float *s, const void *vx, const void *vy);
+void gemv_q6_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q6_k_q8_k_ref(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q6_k_q8_k_parallel(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemv_q6_k_q8_k_parallel_simd(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemm_q6_k_q8_k(float *Y, const void *W, const void *X_q8, int M, int N, int K);
+void gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+
+/* ---- Q8_0: include/ckernel_engine.h:246-284, include/ckernel_quant.h:409; src/kernels/gemm_kernels_q8_0.c:254-277,
+ *      :632-649, :1204-1343; src/kernels/gemm_batch_int8.c:87-120 */
+void vec_dot_q8_0_q8_0(int n, float *s, const void *vx, const void *vy);
+void gemv_q8_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q8_0_q8_0_parallel(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemv_q8_0_q8_0_parallel_simd(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemv_q8_0(float *y, const void *W, const float *x, int M, int K);
+void gemv_q8_0_ref(float *y, const void *W, const float *x, int M, int K);
+
+/* ---- fp32-activation debug path: include/ckernel_engine.h:192-225 */
+void gemv_q4_k(float *y, const void *W, const float *x, int M, int K);
+void gemv_q6_k(float *y, const void *W, const float *x, int M, int K);
+
+/* ---- row dequantisers: include/ckernel_engine.h:208, :255, :262; src/kernels/dequant_kernels.c:288-430 */
+void dequant_q4_k_row(const void *src, float *dst, size_t n_elements);
+void dequant_q6_k_row(const void *src, float *dst, size_t n_elements);
+void dequant_q8_0_row(const void *src, float *dst, size_t n_elements);
+
+/* ---- thread-pool dispatch seam: version/v7/src/ck_parallel_decode.h:33-73, version/v7/src/ck_parallel_prefill.h:36-58.
+ *      Generated code reaches these through the `#define gemv_q4_k_q8_k(...) gemv_q4_k_q8_k_parallel_dispatch(...)`
+ *      overrides (ck_parallel_decode.h:112-123). */
+void ck_parallel_decode_init(void);
+void ck_parallel_decode_shutdown(void);
+void ck_parallel_prefill_init(void);
+void ck_parallel_prefill_shutdown(void);
+void gemv_q4_k_q8_k_parallel_dispatch(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q6_k_q8_k_parallel_dispatch(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q8_0_q8_0_parallel_dispatch(float *y, const void *W, const void *x_q8, int M, int K);
+void gemm_nt_q6_k_q8_k_parallel_dispatch(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+
+/* ---- decode attention + KV cache: include/ckernel_engine.h:1635-1697; src/kernels/attention_kernels.c:3365-3406,
+ *      src/kernels/attention_flash_true.c:696-722, src/kernels/kv_cache_kernels.c:70-129 */
+void attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache, const float *v_cache,
+                                                   float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
+                                                   int cache_capacity, int head_dim, int aligned_head_dim);
+void attention_flash_decode(float *out, const float *q, const float *k, const float *v, int T_q, int T_k, int H, int D_h,
+                            float scale);
+void kv_cache_write_head_major(const float *k_token, const float *v_token, float *k_cache, float *v_cache, int num_kv_heads,
+                               int token_index, int cache_capacity, int head_dim, int aligned_head_dim);
+void kv_cache_store(float *kv_cache_k, float *kv_cache_v, const float *k, const float *v, int layer, int pos,
+                    int num_kv_heads, int head_dim, int max_seq_len);
+
+/* ---- the fp32 ops between the matmuls: src/kernels/rmsnorm_kernels.c:126-250, src/kernels/rope_kernels.c:221-243 and
+ *      :806-819, src/kernels/swiglu_kernels.c:140-216, src/ckernel_orchestration.c:139-149,
+ *      src/kernels/embedding_kernels.c:76-239 */
+void rmsnorm_forward(const float *input, const float *gamma, float *output, float *rstd_cache, int tokens, int d_model,
+                     int aligned_embed_dim, float eps);
+void rope_precompute_cache_split(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base);
+void rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads, int num_kv_heads,
+                     int num_tokens, int head_dim, int aligned_head_dim, int pos_offset);
+void swiglu_forward(const float *input, float *output, int tokens, int dim);
+void ck_residual_add_token_major(const float *a, const float *b, float *out, int tokens, int aligned_embed_dim);
+void embedding_forward_q4_k(const int32_t *token_ids, int token_count, int vocab_size, const void *token_embeddings,
+                            const float *pos_embeddings, float *output, int embed_dim, int aligned_embed_dim,
+                            int context_window, int add_pos);
+void embedding_forward_q6_k(const int32_t *token_ids, int token_count, int vocab_size, const void *token_embeddings,
+                            const float *pos_embeddings, float *output, int embed_dim, int aligned_embed_dim,
+                            int context_window, int add_pos);
+void embedding_forward_q8_0(const int32_t *token_ids, int token_count, int vocab_size, const void *token_embeddings,
+                            const float *pos_embeddings, float *output, int embed_dim, int aligned_embed_dim,
+                            int context_window, int add_pos);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CKB200_KERNELS_H */

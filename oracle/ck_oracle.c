@@ -1,0 +1,610 @@
+/*
+ * ck_oracle.c - CPU restatement of the C-Kernel-Engine quantised decode/prefill hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA kernels: the
+ * parity tests, the smoke check and the bench's cpu_baseline leg load it; the
+ * product library never links, loads or calls it.
+ *
+ * Every function restates the arithmetic of one reference function (cited as
+ * file:line inside the reference project) in plain scalar C, keeping the
+ * reference's fp32 evaluation order so that a build with -ffp-contract=off is
+ * bit-identical to the reference's scalar (_ref) functions.  Parity is pinned:
+ * tests/golden/ holds outputs of the reference itself (built unmodified into
+ * oracle/_ref/libck_ref.so) and tests/test_oracle.py checks this file against
+ * them byte for byte.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+
+#define ORC_QK_K 256
+#define ORC_QK8_0 32
+
+/* Block layouts: include/ckernel_quant.h:104-107, :124-129, :139-144, :153-157 */
+#pragma pack(push, 1)
+typedef struct { uint16_t d; int8_t qs[32]; } orc_q8_0;                              /* 34 B  */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } orc_q4_K;   /* 144 B */
+typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; } orc_q6_K; /* 210 B */
+typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } orc_q8_K;              /* 292 B */
+#pragma pack(pop)
+
+_Static_assert(sizeof(orc_q8_0) == 34, "q8_0");
+_Static_assert(sizeof(orc_q4_K) == 144, "q4_K");
+_Static_assert(sizeof(orc_q6_K) == 210, "q6_K");
+_Static_assert(sizeof(orc_q8_K) == 292, "q8_K");
+
+/* ---- fp16 <-> fp32 (include/ckernel_quant.h:265-294, :311-336; IEEE, RNE) ---- */
+
+float oracle_fp16_to_fp32(uint16_t h)
+{
+    const uint32_t sgn = (uint32_t)(h >> 15) << 31;
+    int e = (h >> 10) & 31;
+    uint32_t f = h & 1023u;
+    uint32_t bits;
+    if (e == 31) {
+        bits = sgn | 0x7F800000u | (f << 13);
+    } else if (e != 0) {
+        bits = sgn | ((uint32_t)(e + 112) << 23) | (f << 13);
+    } else if (f == 0) {
+        bits = sgn;
+    } else {
+        e = 113;
+        do { f <<= 1; --e; } while (!(f & 1024u));
+        bits = sgn | ((uint32_t)e << 23) | ((f & 1023u) << 13);
+    }
+    float out;
+    memcpy(&out, &bits, 4);
+    return out;
+}
+
+uint16_t oracle_fp32_to_fp16(float v)
+{
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    const uint16_t sgn = (uint16_t)((u >> 16) & 0x8000u);
+    const uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sgn | 0x7E00u);          /* NaN */
+    if (a >= 0x477FF000u) return (uint16_t)(sgn | 0x7C00u);         /* >= 65520 rounds to infinity */
+    if (a < 0x33000001u) return sgn;                                /* <= 2^-25: to zero (tie goes to even = 0) */
+    int e = (int)(a >> 23) - 127;
+    uint32_t m = (a & 0x7FFFFFu) | 0x800000u;
+    int shift;
+    uint32_t base;
+    if (e < -14) { shift = 13 + (-14 - e); base = 0; }               /* subnormal half */
+    else { shift = 13; base = (uint32_t)(e + 15) << 10; m &= 0x7FFFFFu; }
+    uint32_t q = m >> shift;
+    const uint32_t rem = m & ((1u << shift) - 1u);
+    const uint32_t half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) ++q;
+    return (uint16_t)(sgn | (base + q));
+}
+
+/* ---- Q4_K 6-bit scale/min unpack (include/ckernel_quant.h:227-251) ---- */
+
+void oracle_unpack_q4_k_scales(const uint8_t *s, uint8_t *sc, uint8_t *mn)
+{
+    for (int j = 0; j < 4; ++j) {
+        sc[j] = s[j] & 63;
+        mn[j] = s[j + 4] & 63;
+        sc[j + 4] = (uint8_t)((s[j + 8] & 15) | ((s[j] >> 6) << 4));
+        mn[j + 4] = (uint8_t)((s[j + 8] >> 4) | ((s[j + 4] >> 6) << 4));
+    }
+}
+
+/* ---- Q8_K activation quantiser (src/kernels/gemm_kernels_q4k_q8k.c:45-103;
+ *      same contract as src/kernels/quantize_row_q8_k_sse.c:22-82) ----
+ * Signed value of the first element with the strictly largest |x| picks the
+ * scale; iscale = -127/max; q = RNE(iscale*x) with the product rounded to fp32
+ * first; bsums over 16 elements; d = 1/iscale. */
+
+static int orc_rne(float v)
+{
+    /* |v| <= 128 here, so nearbyintf under the default rounding mode is the
+     * same integer as the reference's add-magic-constant trick. */
+    return (int)nearbyintf(v);
+}
+
+void oracle_quantize_row_q8_k(const float *x, void *vy, int k)
+{
+    if (!x || !vy || k <= 0) return;
+    orc_q8_K *y = (orc_q8_K *)vy;
+    const int nb = k / ORC_QK_K;
+    for (int b = 0; b < nb; ++b, x += ORC_QK_K) {
+        float best = 0.0f, pick = 0.0f;
+        for (int j = 0; j < ORC_QK_K; ++j) {
+            const float a = fabsf(x[j]);
+            if (a > best) { best = a; pick = x[j]; }
+        }
+        if (best == 0.0f) {
+            memset(&y[b], 0, sizeof(orc_q8_K));
+            continue;
+        }
+        const float iscale = -127.0f / pick;
+        for (int j = 0; j < ORC_QK_K; ++j) {
+            const float p = iscale * x[j];
+            int q = orc_rne(p);
+            q = q > 127 ? 127 : (q < -128 ? -128 : q);
+            y[b].qs[j] = (int8_t)q;
+        }
+        for (int g = 0; g < 16; ++g) {
+            int s = 0;
+            for (int j = 0; j < 16; ++j) s += y[b].qs[16 * g + j];
+            y[b].bsums[g] = (int16_t)s;
+        }
+        y[b].d = 1.0f / iscale;
+    }
+}
+
+/* quantize_batch_q8_k: src/kernels/gemm_kernels_q8_0.c:221-239 (rows are independent) */
+void oracle_quantize_batch_q8_k(const float *x, void *vy, int rows, int k)
+{
+    uint8_t *out = (uint8_t *)vy;
+    for (int r = 0; r < rows; ++r)
+        oracle_quantize_row_q8_k(x + (size_t)r * k, out + (size_t)r * (k / ORC_QK_K) * sizeof(orc_q8_K), k);
+}
+
+/* ---- Q8_0 activation quantiser (src/kernels/gemm_kernels_q8_0.c:70-175) ----
+ * amax over 32; d = amax/127 stored as fp16; id = 127/amax from the fp32 amax;
+ * q = RNE(x*id).  The vector path of the reference does not clamp (|q| <= 127
+ * by construction); neither does this. */
+void oracle_quantize_row_q8_0(const float *x, void *vy, int k)
+{
+    orc_q8_0 *y = (orc_q8_0 *)vy;
+    const int nb = k / ORC_QK8_0;
+    for (int b = 0; b < nb; ++b, x += ORC_QK8_0) {
+        float amax = 0.0f;
+        for (int j = 0; j < ORC_QK8_0; ++j) {
+            const float a = fabsf(x[j]);
+            if (a > amax) amax = a;
+        }
+        const float d = amax / 127.0f;
+        const float id = amax != 0.0f ? 127.0f / amax : 0.0f;
+        y[b].d = oracle_fp32_to_fp16(d);
+        for (int j = 0; j < ORC_QK8_0; ++j) {
+            const float p = x[j] * id;
+            y[b].qs[j] = (int8_t)orc_rne(p);
+        }
+    }
+}
+
+void oracle_quantize_batch_q8_0(const float *x, void *vy, int rows, int k)
+{
+    uint8_t *out = (uint8_t *)vy;
+    for (int r = 0; r < rows; ++r)
+        oracle_quantize_row_q8_0(x + (size_t)r * k, out + (size_t)r * (k / ORC_QK8_0) * sizeof(orc_q8_0), k);
+}
+
+/* ---- Q4_K x Q8_K (src/kernels/gemm_kernels_q4k_q8k.c:121-200) ---- */
+
+/* Integer stage: the eight 32-element sums of nibble*q8 of one superblock. */
+static void orc_q4k_isums(const orc_q4_K *w, const orc_q8_K *x, int32_t out[8])
+{
+    for (int g = 0; g < 4; ++g) {
+        int32_t lo = 0, hi = 0;
+        for (int l = 0; l < 32; ++l) {
+            const uint8_t byte = w->qs[32 * g + l];
+            lo += (int32_t)(byte & 15) * x->qs[64 * g + l];
+            hi += (int32_t)(byte >> 4) * x->qs[64 * g + 32 + l];
+        }
+        out[2 * g] = lo;
+        out[2 * g + 1] = hi;
+    }
+}
+
+void oracle_q4_k_q8_k_subblock_sums(const void *w_row, const void *x_q8, int K, int32_t *out)
+{
+    const orc_q4_K *w = (const orc_q4_K *)w_row;
+    const orc_q8_K *x = (const orc_q8_K *)x_q8;
+    for (int b = 0; b < K / ORC_QK_K; ++b) orc_q4k_isums(&w[b], &x[b], out + 8 * b);
+}
+
+static float orc_dot_q4k_q8k(const orc_q4_K *w, const orc_q8_K *x, int nb)
+{
+    float acc = 0.0f;
+    for (int b = 0; b < nb; ++b) {
+        uint8_t sc[8], mn[8];
+        int32_t is[8];
+        oracle_unpack_q4_k_scales(w[b].scales, sc, mn);
+        orc_q4k_isums(&w[b], &x[b], is);
+        const float d = oracle_fp16_to_fp32(w[b].d) * x[b].d;
+        const float dm = oracle_fp16_to_fp32(w[b].dmin) * x[b].d;
+        for (int j = 0; j < 8; ++j) {
+            const int32_t bs = (int32_t)x[b].bsums[2 * j] + (int32_t)x[b].bsums[2 * j + 1];
+            acc += d * (float)sc[j] * (float)is[j];
+            acc -= dm * (float)mn[j] * (float)bs;
+        }
+    }
+    return acc;
+}
+
+void oracle_gemv_q4_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    if (!y || !W || !x_q8 || M <= 0 || K <= 0) return;
+    const int nb = K / ORC_QK_K;
+    const orc_q4_K *w = (const orc_q4_K *)W;
+    for (int r = 0; r < M; ++r) y[r] = orc_dot_q4k_q8k(w + (size_t)r * nb, (const orc_q8_K *)x_q8, nb);
+}
+
+/* gemm_nt_q4_k_q8_k: src/kernels/gemm_kernels_q4k_q8k.c:301-326 - C[m][n] = dot(B row n, A row m) + bias[n] */
+void oracle_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A_q8 || !B || !C || M <= 0 || N <= 0 || K <= 0) return;
+    const int nb = K / ORC_QK_K;
+    const orc_q8_K *a = (const orc_q8_K *)A_q8;
+    for (int m = 0; m < M; ++m) {
+        oracle_gemv_q4_k_q8_k(C + (size_t)m * N, B, a + (size_t)m * nb, N, K);
+        if (bias) for (int n = 0; n < N; ++n) C[(size_t)m * N + n] += bias[n];
+    }
+}
+
+/* fp32-activation Q4_K GEMV: src/kernels/gemm_kernels_q4k.c:53-101 (dequantise then multiply,
+ * weight = d*sc*q - dmin*m as in src/kernels/dequant_kernels.c:336-366) */
+void oracle_dequant_q4_k_row(const void *src, float *dst, size_t n)
+{
+    const orc_q4_K *w = (const orc_q4_K *)src;
+    for (size_t b = 0; b < n / ORC_QK_K; ++b) {
+        uint8_t sc[8], mn[8];
+        oracle_unpack_q4_k_scales(w[b].scales, sc, mn);
+        const float d = oracle_fp16_to_fp32(w[b].d), dm = oracle_fp16_to_fp32(w[b].dmin);
+        float *o = dst + b * ORC_QK_K;
+        for (int g = 0; g < 4; ++g) {
+            const float d1 = d * (float)sc[2 * g], m1 = dm * (float)mn[2 * g];
+            const float d2 = d * (float)sc[2 * g + 1], m2 = dm * (float)mn[2 * g + 1];
+            for (int l = 0; l < 32; ++l) {
+                const uint8_t byte = w[b].qs[32 * g + l];
+                o[64 * g + l] = d1 * (float)(byte & 15) - m1;
+                o[64 * g + 32 + l] = d2 * (float)(byte >> 4) - m2;
+            }
+        }
+    }
+}
+
+/* ---- Q6_K x Q8_K (src/kernels/gemm_kernels_q6k_q8k.c:70-120, :197-214) ---- */
+
+/* 6-bit value (already minus 32) of element e (0..255) of a superblock. */
+static int orc_q6_value(const orc_q6_K *w, int e)
+{
+    const int half = e >> 7, r = e & 127, quarter = r >> 5, l = r & 31;
+    const uint8_t *ql = w->ql + 64 * half;
+    const uint8_t h = w->qh[32 * half + l];
+    const uint8_t lo = ql[l + 32 * (quarter & 1)];
+    const int nib = quarter >= 2 ? (lo >> 4) : (lo & 15);
+    return (nib | (((h >> (2 * quarter)) & 3) << 4)) - 32;
+}
+
+/* Integer stage: sixteen 16-element sums of (q6-32)*q8 of one superblock; sum j
+ * covers elements 16j..16j+15 and is scaled by scales[j]. */
+static void orc_q6k_isums(const orc_q6_K *w, const orc_q8_K *x, int32_t out[16])
+{
+    for (int j = 0; j < 16; ++j) {
+        int32_t s = 0;
+        for (int i = 0; i < 16; ++i) s += orc_q6_value(w, 16 * j + i) * (int32_t)x->qs[16 * j + i];
+        out[j] = s;
+    }
+}
+
+void oracle_q6_k_q8_k_subblock_sums(const void *w_row, const void *x_q8, int K, int32_t *out)
+{
+    const orc_q6_K *w = (const orc_q6_K *)w_row;
+    const orc_q8_K *x = (const orc_q8_K *)x_q8;
+    for (int b = 0; b < K / ORC_QK_K; ++b) orc_q6k_isums(&w[b], &x[b], out + 16 * b);
+}
+
+/* The reference's scalar order: per element, fp32, l-major over four strided streams. */
+static float orc_dot_q6k_q8k(const orc_q6_K *w, const orc_q8_K *x, int nb)
+{
+    float acc = 0.0f;
+    for (int b = 0; b < nb; ++b) {
+        const float d = oracle_fp16_to_fp32(w[b].d) * x[b].d;
+        for (int half = 0; half < 2; ++half) {
+            const int8_t *sc = w[b].scales + 8 * half;
+            const int8_t *q8 = x[b].qs + 128 * half;
+            for (int l = 0; l < 32; ++l) {
+                const int is = l >> 4;
+                for (int qt = 0; qt < 4; ++qt) {
+                    const int e = 128 * half + 32 * qt + l;
+                    acc += d * (float)sc[is + 2 * qt] * (float)orc_q6_value(&w[b], e) * (float)q8[32 * qt + l];
+                }
+            }
+        }
+    }
+    return acc;
+}
+
+void oracle_gemv_q6_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    if (!y || !W || !x_q8 || M <= 0 || K <= 0) return;
+    const int nb = K / ORC_QK_K;
+    const orc_q6_K *w = (const orc_q6_K *)W;
+    for (int r = 0; r < M; ++r) y[r] = orc_dot_q6k_q8k(w + (size_t)r * nb, (const orc_q8_K *)x_q8, nb);
+}
+
+/* The reference's vector paths (src/kernels/gemm_kernels_q6k_q8k.c:601-695, :887-1002)
+ * sum scale*isum in int32 per superblock and apply d once; same value up to fp32 rounding. */
+void oracle_gemv_q6_k_q8_k_intorder(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    if (!y || !W || !x_q8 || M <= 0 || K <= 0) return;
+    const int nb = K / ORC_QK_K;
+    const orc_q6_K *w = (const orc_q6_K *)W;
+    const orc_q8_K *x = (const orc_q8_K *)x_q8;
+    for (int r = 0; r < M; ++r) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            int32_t is[16], tot = 0;
+            const orc_q6_K *wb = &w[(size_t)r * nb + b];
+            orc_q6k_isums(wb, &x[b], is);
+            for (int j = 0; j < 16; ++j) tot += (int32_t)wb->scales[j] * is[j];
+            acc += oracle_fp16_to_fp32(wb->d) * x[b].d * (float)tot;
+        }
+        y[r] = acc;
+    }
+}
+
+void oracle_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A_q8 || !B || !C || M <= 0 || N <= 0 || K <= 0) return;
+    const int nb = K / ORC_QK_K;
+    const orc_q8_K *a = (const orc_q8_K *)A_q8;
+    for (int m = 0; m < M; ++m) {
+        oracle_gemv_q6_k_q8_k(C + (size_t)m * N, B, a + (size_t)m * nb, N, K);
+        if (bias) for (int n = 0; n < N; ++n) C[(size_t)m * N + n] += bias[n];
+    }
+}
+
+/* src/kernels/dequant_kernels.c:391-430 */
+void oracle_dequant_q6_k_row(const void *src, float *dst, size_t n)
+{
+    const orc_q6_K *w = (const orc_q6_K *)src;
+    for (size_t b = 0; b < n / ORC_QK_K; ++b) {
+        const float d = oracle_fp16_to_fp32(w[b].d);
+        for (int e = 0; e < ORC_QK_K; ++e)
+            dst[b * ORC_QK_K + e] = d * (float)w[b].scales[e >> 4] * (float)orc_q6_value(&w[b], e);
+    }
+}
+
+/* ---- Q8_0 (src/kernels/gemm_kernels_q8_0.c:254-277, :968-989, :1237-1251) ---- */
+
+void oracle_gemv_q8_0(float *y, const void *W, const float *x, int M, int K)
+{
+    const orc_q8_0 *w = (const orc_q8_0 *)W;
+    const int nb = K / ORC_QK8_0;
+    for (int r = 0; r < M; ++r) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const orc_q8_0 *blk = &w[(size_t)r * nb + b];
+            const float d = oracle_fp16_to_fp32(blk->d);
+            for (int i = 0; i < ORC_QK8_0; ++i) acc += d * (float)blk->qs[i] * x[b * ORC_QK8_0 + i];
+        }
+        y[r] = acc;
+    }
+}
+
+void oracle_vec_dot_q8_0_q8_0(int n, float *s, const void *vx, const void *vy)
+{
+    const orc_q8_0 *a = (const orc_q8_0 *)vx, *b = (const orc_q8_0 *)vy;
+    float acc = 0.0f;
+    for (int ib = 0; ib < n / ORC_QK8_0; ++ib) {
+        int32_t si = 0;
+        for (int j = 0; j < ORC_QK8_0; ++j) si += (int32_t)a[ib].qs[j] * (int32_t)b[ib].qs[j];
+        acc += (float)si * (oracle_fp16_to_fp32(a[ib].d) * oracle_fp16_to_fp32(b[ib].d));
+    }
+    *s = acc;
+}
+
+void oracle_q8_0_q8_0_block_sums(const void *w_row, const void *x_q8, int K, int32_t *out)
+{
+    const orc_q8_0 *a = (const orc_q8_0 *)w_row, *b = (const orc_q8_0 *)x_q8;
+    for (int ib = 0; ib < K / ORC_QK8_0; ++ib) {
+        int32_t si = 0;
+        for (int j = 0; j < ORC_QK8_0; ++j) si += (int32_t)a[ib].qs[j] * (int32_t)b[ib].qs[j];
+        out[ib] = si;
+    }
+}
+
+void oracle_gemv_q8_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    const orc_q8_0 *w = (const orc_q8_0 *)W;
+    const int nb = K / ORC_QK8_0;
+    for (int r = 0; r < M; ++r) oracle_vec_dot_q8_0_q8_0(K, &y[r], w + (size_t)r * nb, x_q8);
+}
+
+/* gemm_nt_q8_0_q8_0: src/kernels/gemm_batch_int8.c:87-120 */
+void oracle_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    const orc_q8_0 *a = (const orc_q8_0 *)A_q8;
+    const int nb = K / ORC_QK8_0;
+    for (int m = 0; m < M; ++m) {
+        oracle_gemv_q8_0_q8_0(C + (size_t)m * N, B, a + (size_t)m * nb, N, K);
+        if (bias) for (int n = 0; n < N; ++n) C[(size_t)m * N + n] += bias[n];
+    }
+}
+
+/* src/kernels/dequant_kernels.c:276-296 */
+void oracle_dequant_q8_0_row(const void *src, float *dst, size_t n)
+{
+    const orc_q8_0 *w = (const orc_q8_0 *)src;
+    for (size_t b = 0; b < n / ORC_QK8_0; ++b) {
+        const float d = oracle_fp16_to_fp32(w[b].d);
+        for (int i = 0; i < ORC_QK8_0; ++i) dst[b * ORC_QK8_0 + i] = d * (float)w[b].qs[i];
+    }
+}
+
+/* ---- Decode attention over the head-major KV cache
+ *      (src/kernels/attention_kernels.c:3365-3406 -> src/kernels/attention_flash_true.c:142-230) ----
+ * One query token; per Q head an online softmax over key tiles of 32 (d<=64),
+ * 16 (d<=128) or 8 keys (attention_flash_true.c:88-106). */
+static int orc_tile_k(int d) { return d > 128 ? 8 : (d > 64 ? 16 : 32); }
+
+static void orc_flash_decode_head(float *out, const float *q, const float *k, const float *v, int T, int D, float scale)
+{
+    const int tile = orc_tile_k(D);
+    float run_max = -INFINITY, run_sum = 0.0f, sc[32];
+    for (int i = 0; i < D; ++i) out[i] = 0.0f;
+    for (int t0 = 0; t0 < T; t0 += tile) {
+        const int n = T - t0 < tile ? T - t0 : tile;
+        float blk_max = -INFINITY;
+        for (int j = 0; j < n; ++j) {
+            const float *kr = k + (size_t)(t0 + j) * D;
+            float dot = 0.0f;
+            for (int i = 0; i < D; ++i) dot += q[i] * kr[i];
+            sc[j] = dot * scale;
+            if (sc[j] > blk_max) blk_max = sc[j];
+        }
+        if (blk_max > run_max) {
+            const float f = run_max == -INFINITY ? 0.0f : expf(run_max - blk_max);
+            run_sum *= f;
+            for (int i = 0; i < D; ++i) out[i] *= f;
+            run_max = blk_max;
+        }
+        for (int j = 0; j < n; ++j) {
+            const float *vr = v + (size_t)(t0 + j) * D;
+            const float p = expf(sc[j] - run_max);
+            run_sum += p;
+            for (int i = 0; i < D; ++i) out[i] += p * vr[i];
+        }
+    }
+    if (run_sum > 0.0f) {
+        const float inv = 1.0f / run_sum;
+        for (int i = 0; i < D; ++i) out[i] *= inv;
+    } else {
+        for (int i = 0; i < D; ++i) out[i] = 0.0f;
+    }
+}
+
+void oracle_attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache,
+                                                          const float *v_cache, float *out_token,
+                                                          int num_heads, int num_kv_heads, int kv_tokens,
+                                                          int cache_capacity, int head_dim, int aligned_head_dim)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const size_t hs = (size_t)cache_capacity * (size_t)aligned_head_dim;
+    for (int h = 0; h < num_heads; ++h) {
+        const int kvh = (int)((long long)h * num_kv_heads / num_heads);
+        orc_flash_decode_head(out_token + (size_t)h * aligned_head_dim, q_token + (size_t)h * aligned_head_dim,
+                              k_cache + kvh * hs, v_cache + kvh * hs, kv_tokens, aligned_head_dim, scale);
+    }
+}
+
+/* ---- KV cache store (src/kernels/kv_cache_kernels.c:70-129) ---- */
+void oracle_kv_cache_store(float *kc, float *vc, const float *k, const float *v, int layer, int pos,
+                           int num_kv_heads, int head_dim, int max_seq_len)
+{
+    (void)layer;
+    if (!k || !v || !kc || !vc || num_kv_heads <= 0 || pos < 0 || pos >= max_seq_len || head_dim <= 0) return;
+    for (int h = 0; h < num_kv_heads; ++h) {
+        const size_t dst = ((size_t)h * max_seq_len + pos) * head_dim;
+        memcpy(kc + dst, k + (size_t)h * head_dim, sizeof(float) * head_dim);
+        memcpy(vc + dst, v + (size_t)h * head_dim, sizeof(float) * head_dim);
+    }
+}
+
+/* ---- RoPE (src/kernels/rope_kernels.c:221-243 cache, :320-417 rotate-half, :806-819 q+k) ---- */
+void oracle_rope_precompute_cache_split(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base)
+{
+    const int half = head_dim / 2;
+    const long double lb = logl((long double)base);
+    for (int p = 0; p < max_seq_len; ++p)
+        for (int i = 0; i < half; ++i) {
+            const float freq = (float)expl(-((long double)(2 * i) / (long double)head_dim) * lb);
+            const float ang = (float)p * freq;
+            cos_cache[(size_t)p * half + i] = cosf(ang);
+            sin_cache[(size_t)p * half + i] = sinf(ang);
+        }
+}
+
+static void orc_rope_heads(float *x, const float *cc, const float *ss, int heads, int tokens, int hd, int ahd, int pos0)
+{
+    const int half = hd / 2;
+    for (int h = 0; h < heads; ++h)
+        for (int t = 0; t < tokens; ++t) {
+            float *r = x + ((size_t)h * tokens + t) * ahd;
+            const float *c = cc + (size_t)(pos0 + t) * half, *s = ss + (size_t)(pos0 + t) * half;
+            for (int i = 0; i < half; ++i) {
+                const float a = r[i], b = r[i + half];
+                r[i] = a * c[i] - b * s[i];
+                r[i + half] = a * s[i] + b * c[i];
+            }
+        }
+}
+
+void oracle_rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                            int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset)
+{
+    orc_rope_heads(q, cos_cache, sin_cache, num_heads, num_tokens, head_dim, aligned_head_dim, pos_offset);
+    orc_rope_heads(k, cos_cache, sin_cache, num_kv_heads, num_tokens, head_dim, aligned_head_dim, pos_offset);
+}
+
+/* ---- RMSNorm (src/kernels/rmsnorm_kernels.c:38-71 scalar form; :245-248 zero pad) ---- */
+void oracle_rmsnorm_forward(const float *in, const float *gamma, float *out, float *rstd_cache, int tokens,
+                            int d_model, int aligned, float eps)
+{
+    for (int t = 0; t < tokens; ++t) {
+        const float *x = in + (size_t)t * aligned;
+        float *y = out + (size_t)t * aligned;
+        float ss = 0.0f;
+        for (int i = 0; i < d_model; ++i) ss += x[i] * x[i];
+        const float rstd = 1.0f / sqrtf(ss * (1.0f / (float)d_model) + eps);
+        if (rstd_cache) rstd_cache[t] = rstd;
+        for (int i = 0; i < d_model; ++i) y[i] = x[i] * rstd * gamma[i];
+        for (int i = d_model; i < aligned; ++i) y[i] = 0.0f;
+    }
+}
+
+/* ---- SwiGLU (src/kernels/swiglu_kernels.c:358-379 exact form; sigmoid_kernels.c:26-29) ---- */
+void oracle_swiglu_forward(const float *in, float *out, int tokens, int dim)
+{
+    for (int t = 0; t < tokens; ++t)
+        for (int i = 0; i < dim; ++i) {
+            const float g = in[(size_t)t * 2 * dim + i], u = in[(size_t)t * 2 * dim + dim + i];
+            const float sg = 1.0f / (1.0f + expf(-g));
+            out[(size_t)t * dim + i] = g * sg * u;
+        }
+}
+
+/* ---- residual add (src/ckernel_orchestration.c:139-149) ---- */
+void oracle_residual_add_token_major(const float *a, const float *b, float *out, int tokens, int aligned)
+{
+    const size_t n = (size_t)tokens * aligned;
+    for (size_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
+}
+
+/* ---- embedding lookup (src/kernels/embedding_kernels.c:76-129 q4_k, :131-184 q8_0, :186-239 q6_k) ---- */
+static void orc_embed(const int32_t *ids, int count, int vocab, const void *table, const float *pos, float *out,
+                      int embed, int aligned, int ctx, int add_pos, size_t row_bytes,
+                      void (*deq)(const void *, float *, size_t))
+{
+    if (!ids || !table || !out) return;
+    int n = count < 0 ? 0 : (count > ctx ? ctx : count);
+    for (int t = 0; t < n; ++t) {
+        int id = ids[t];
+        if (id < 0 || id >= vocab) id = 0;
+        float *o = out + (size_t)t * aligned;
+        deq((const uint8_t *)table + (size_t)id * row_bytes, o, (size_t)aligned);
+        if (add_pos && pos) for (int i = 0; i < embed; ++i) o[i] += pos[(size_t)t * aligned + i];
+        for (int i = embed; i < aligned; ++i) o[i] = 0.0f;
+    }
+    for (int t = n; t < ctx; ++t) memset(out + (size_t)t * aligned, 0, sizeof(float) * aligned);
+}
+
+void oracle_embedding_forward_q4_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos,
+                                   float *out, int embed, int aligned, int ctx, int add_pos)
+{
+    orc_embed(ids, count, vocab, table, pos, out, embed, aligned, ctx, add_pos, (size_t)(aligned / 256) * 144,
+              oracle_dequant_q4_k_row);
+}
+void oracle_embedding_forward_q6_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos,
+                                   float *out, int embed, int aligned, int ctx, int add_pos)
+{
+    orc_embed(ids, count, vocab, table, pos, out, embed, aligned, ctx, add_pos, (size_t)(aligned / 256) * 210,
+              oracle_dequant_q6_k_row);
+}
+void oracle_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, const void *table, const float *pos,
+                                   float *out, int embed, int aligned, int ctx, int add_pos)
+{
+    orc_embed(ids, count, vocab, table, pos, out, embed, aligned, ctx, add_pos, (size_t)(aligned / 32) * 34,
+              oracle_dequant_q8_0_row);
+}

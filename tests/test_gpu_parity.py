@@ -1,0 +1,261 @@
+"""Parity of the CUDA path with the reference, through the C ABI, on a B200.
+
+Bars (the contract of this path): Q8_K / Q8_0 activation quantisation and all integer stages
+bit-exact; fp32 outputs within 1e-3 max relative error of the same-path CPU result (checked
+much tighter against the output scale); decode attention within 1e-4 absolute.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+synth = cases.synth
+
+REL_TOL = 1e-3          # max elementwise relative error, fp32 outputs (north-star tolerance)
+SCALE_TOL = 1e-5        # max abs error relative to the largest output (what fp32 reordering costs)
+ATTN_ABS_TOL = 1e-4
+
+
+def assert_fp32_close(got, want, what=""):
+    got64, want64 = got.astype(np.float64), want.astype(np.float64)
+    err = np.abs(got64 - want64)
+    scale = float(np.max(np.abs(want64))) or 1.0
+    assert float(err.max()) <= SCALE_TOL * scale, f"{what}: max abs err {err.max():.3e} vs scale {scale:.3e}"
+    rel = err / np.maximum(np.abs(want64), 1e-2 * scale)     # elementwise, guarded where |y| is tiny
+    assert float(rel.max()) <= REL_TOL, f"{what}: max rel err {rel.max():.3e}"
+
+
+# ---------------------------------------------------------------- golden vectors (reference outputs)
+
+def test_golden_cases_through_host_abi(ck, golden):
+    out = cases.golden_outputs(ck, "")
+    for name in golden.files:
+        if name.startswith("gemv_dispatch_"):
+            continue
+        assert name in out, name
+        g, o = golden[name], out[name]
+        if name.startswith(("q8k_", "q80_", "dequant_", "kv_store", "embed_")):
+            assert np.array_equal(g, o), f"{name}: not bit-exact"
+        elif name.startswith("attn_"):
+            assert float(np.max(np.abs(g - o))) <= ATTN_ABS_TOL, name
+        elif name in ("rope_cos", "rope_sin", "rope_q", "rope_k", "rmsnorm"):
+            assert float(np.max(np.abs(g - o))) <= 2e-6 * max(1.0, float(np.max(np.abs(g)))), name
+        elif name == "swiglu":
+            assert float(np.max(np.abs(g - o))) <= 2e-4 * float(np.max(np.abs(g))), name   # reference uses a fast exp
+        else:
+            assert_fp32_close(o, g, name)
+
+
+# ---------------------------------------------------------------- quantisers, bit-exact
+
+@pytest.mark.parametrize("rows,k", [(1, 256), (1, 4096), (3, 4864), (32, 8192), (512, 4096)])
+def test_quantize_q8_k_bit_exact(ck, orc, rows, k):
+    x = synth.make_x(k, seed=rows + k, rows=rows) * np.float32(2.5)
+    if rows > 2:
+        x[1, 256:512] = 0.0                                   # an all-zero block inside a batch
+    assert np.array_equal(cases.quantize_q8_k(ck, "", x, rows), cases.quantize_q8_k(orc, "oracle_", x, rows))
+
+
+def test_quantize_q8_k_edge_cases_bit_exact(ck, orc):
+    x = cases.q8k_edge_input()
+    assert np.array_equal(cases.quantize_q8_k(ck, "", x), cases.quantize_q8_k(orc, "oracle_", x))
+
+
+@pytest.mark.parametrize("rows,k", [(1, 32), (1, 896), (7, 4864), (64, 4096)])
+def test_quantize_q8_0_bit_exact(ck, orc, rows, k):
+    x = synth.make_x(k, seed=rows * 3 + k, rows=rows) * np.float32(0.3)
+    assert np.array_equal(cases.quantize_q8_0(ck, "", x, rows), cases.quantize_q8_0(orc, "oracle_", x, rows))
+
+
+# ---------------------------------------------------------------- GEMV: every kernel variant, ragged shapes
+
+VARIANTS = {"q4_k": [1, 2, 10, 11, 12, 13, 14, 15, 16, 17], "q6_k": [1, 2], "q8_0": [1, 2]}
+RAGGED = {
+    "q4_k": [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (257, 2048)],
+    "q6_k": [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (2, 28672)],
+    "q8_0": [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (2, 28672)],
+}
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q8_0"])
+def test_gemv_all_variants_ragged_shapes(ck, orc, fmt):
+    key = ("gemv_" + fmt).encode()
+    try:
+        for m, k in RAGGED[fmt]:
+            w = synth.make_weights(fmt, m, k, seed=m + k)
+            xq = cases.quantize_act(orc, "oracle_", fmt, synth.make_x(k, seed=m + k))
+            want = cases.gemv(orc, "oracle_", fmt, w, xq, m, k)
+            for v in VARIANTS[fmt]:
+                ck.ckb200_tune_set(key, v)
+                got = cases.gemv(ck, "", fmt, w, xq, m, k)
+                assert ck.ckb200_synchronize() == 0
+                assert_fp32_close(got, want, f"{fmt} variant {v} {m}x{k}")
+    finally:
+        ck.ckb200_tune_set(key, 0)
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q8_0"])
+def test_gemv_ring_with_small_stages_splits_rows_into_chunks(ck, orc, fmt):
+    """A tiny stage forces long rows through several bulk copies (partial sums carried across chunks)."""
+    key = ("gemv_" + fmt).encode()
+    try:
+        ck.ckb200_tune_set(key, 1)
+        ck.ckb200_tune_set(b"ring_stage_bytes", 1024)
+        for m, k in [(9, 4096), (4, 14336), (300, 1024 if fmt != "q8_0" else 896)]:
+            w = synth.make_weights(fmt, m, k, seed=k)
+            xq = cases.quantize_act(orc, "oracle_", fmt, synth.make_x(k, seed=k))
+            got = cases.gemv(ck, "", fmt, w, xq, m, k)
+            assert ck.ckb200_synchronize() == 0
+            assert_fp32_close(got, cases.gemv(orc, "oracle_", fmt, w, xq, m, k), f"{fmt} {m}x{k}")
+    finally:
+        ck.ckb200_tune_set(key, 0)
+        ck.ckb200_tune_set(b"ring_stage_bytes", 0)
+
+
+SWEEP = [(fmt, m, k) for fmt in ("q4_k", "q6_k", "q8_0") for (m, k) in synth.SWEEP_SHAPES]
+
+
+@pytest.mark.parametrize("fmt,m,k_raw", SWEEP)
+def test_gemv_benchmark_sweep_full_size(ck, orc, fmt, m, k_raw):
+    """The benchmark shapes at full size, seed 0, against the CPU oracle (K=896 padded to 1024 for the K-quants)."""
+    k = synth.k_for(fmt, k_raw)
+    w = synth.make_weights(fmt, m, k, seed=0)
+    x = synth.make_x(k, seed=0, k_valid=k_raw if k != k_raw else None)
+    xq = cases.quantize_act(ck, "", fmt, x)
+    assert np.array_equal(xq, cases.quantize_act(orc, "oracle_", fmt, x))
+    got = cases.gemv(ck, "", fmt, w, xq, m, k)
+    assert ck.ckb200_synchronize() == 0
+    assert_fp32_close(got, cases.gemv(orc, "oracle_", fmt, w, xq, m, k), f"{fmt} {m}x{k}")
+
+
+def test_gemv_row_split_variants_cover_all_rows(ck, orc):
+    """gemv_*_parallel(ith, nth) computes rows [dr*ith, dr*(ith+1)); the union over ith is the whole result."""
+    m, k, nth = 101, 1024, 7
+    for fmt, name in (("q4_k", "gemv_q4_k_q8_k_parallel_simd"), ("q6_k", "gemv_q6_k_q8_k_parallel"), ("q8_0", "gemv_q8_0_q8_0_parallel_simd")):
+        kk = k if fmt != "q8_0" else 896
+        w = synth.make_weights(fmt, m, kk, seed=3)
+        xq = cases.quantize_act(orc, "oracle_", fmt, synth.make_x(kk, seed=3))
+        y = np.full(m, np.nan, dtype=np.float32)
+        f = getattr(ck, name)
+        f.restype = None
+        for ith in range(nth):
+            f(cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(m), C.c_int(kk), C.c_int(ith), C.c_int(nth))
+        assert_fp32_close(y, cases.gemv(orc, "oracle_", fmt, w, xq, m, kk), name)
+
+
+def test_registered_weights_are_used_from_hbm(ck, orc):
+    m, k = 64, 2048
+    w = synth.make_weights("q4_k", m, k, seed=8)
+    xq = cases.quantize_q8_k(orc, "oracle_", synth.make_x(k, seed=8))
+    want = cases.gemv(orc, "oracle_", "q4_k", w, xq, m, k)
+    assert ck.ckb200_register_weights(cases.vptr(w), C.c_size_t(w.nbytes)) == 0
+    try:
+        ck.ckb200_device_ptr.restype = C.c_void_p
+        assert ck.ckb200_device_ptr(cases.vptr(w)) is not None
+        inner = C.c_void_p(w.ctypes.data + 5 * (k // 256) * 144)
+        assert ck.ckb200_device_ptr(inner) is not None
+        # the device copy is what is read: scribbling on the host buffer must not change the result
+        backup = w.copy()
+        w[:] = 0
+        got = cases.gemv(ck, "", "q4_k", w, xq, m, k)
+        w[:] = backup
+        assert_fp32_close(got, want, "registered")
+    finally:
+        assert ck.ckb200_unregister_weights(cases.vptr(w)) == 0
+    assert ck.ckb200_device_ptr(cases.vptr(w)) is None
+
+
+def test_silent_return_on_null_and_shape_error_is_reported(ck):
+    y = np.full(4, np.nan, dtype=np.float32)
+    w = synth.make_weights("q4_k", 4, 256, 1)
+    ck.gemv_q4_k_q8_k(cases.fptr(y), cases.vptr(w), C.c_void_p(), C.c_int(4), C.c_int(256))     # NULL: silent, like the reference
+    assert np.isnan(y).all() and ck.ckb200_last_error() == 0
+    xq = np.zeros(292, dtype=np.uint8)
+    ck.gemv_q4_k_q8_k(cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(4), C.c_int(200))   # K % 256 != 0
+    assert ck.ckb200_last_error() == 2
+    ck.ckb200_clear_error()
+
+
+# ---------------------------------------------------------------- fp32-activation path, GEMM, dequant
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q8_0"])
+def test_fp32_activation_gemv(ck, orc, fmt):
+    m, k = 17, 1024 if fmt != "q8_0" else 896
+    w = synth.make_weights(fmt, m, k, seed=4)
+    x = synth.make_x(k, seed=4)
+    got = cases.gemv_f32(ck, "", fmt, w, x, m, k)
+    deq = np.stack([cases.dequant_row(orc, "oracle_", fmt, w.reshape(m, -1)[r].copy(), k) for r in range(m)]).astype(np.float64)
+    want = (deq @ x.astype(np.float64)).astype(np.float32)
+    assert_fp32_close(got, want, fmt)
+
+
+@pytest.mark.parametrize("fmt,m,n,k", [("q4_k", 5, 33, 1024), ("q6_k", 4, 20, 512), ("q8_0", 6, 17, 896), ("q4_k", 64, 96, 2048)])
+def test_gemm_nt_matches_loop_of_gemv(ck, orc, fmt, m, n, k):
+    w = synth.make_weights(fmt, n, k, seed=n)
+    a = synth.make_x(k, seed=n, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", fmt, a, rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32)
+    got = cases.gemm_nt(ck, "", fmt, aq, w, bias, m, n, k)
+    want = cases.gemm_nt(orc, "oracle_", fmt, aq, w, bias, m, n, k)
+    assert_fp32_close(got, want, fmt)
+
+
+# ---------------------------------------------------------------- decode attention + KV cache
+
+ATTN_CASES = [  # heads, kv_heads, d(aligned), head_dim, tokens, capacity
+    (14, 2, 64, 64, 1025, 2048),       # Qwen2-0.5B-shaped decode step
+    (64, 8, 128, 128, 4096, 4096),     # Llama-3-70B-shaped
+    (8, 4, 64, 64, 64, 64),            # the reference's own test case (unittest/test_kv_cache_attention.py:228-321)
+    (8, 4, 64, 40, 63, 80),            # padded head: head_dim 40 in 64 aligned slots
+    (4, 4, 64, 64, 1, 16),             # a single key
+    (6, 2, 128, 128, 5, 8),
+    (12, 4, 96, 96, 100, 128),         # head size outside the fast path
+    (32, 2, 64, 64, 77, 128),          # group of 16 Q heads per KV head: generic path
+]
+
+
+@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,cap", ATTN_CASES)
+def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
+    q, kc, vc = cases.attention_inputs(tokens + heads, heads, kvh, ad, tokens, cap)
+    if hd < ad:
+        q[:, hd:] = 0
+        kc[:, :, hd:] = 0
+        vc[:, :, hd:] = 0
+
+    def run(lib, prefix):
+        out = np.full((heads, ad), np.nan, dtype=np.float32)
+        cases.fn(lib, prefix, "attention_forward_decode_head_major_gqa_flash")(
+            cases.fptr(q), cases.fptr(kc), cases.fptr(vc), cases.fptr(out), C.c_int(heads), C.c_int(kvh), C.c_int(tokens),
+            C.c_int(cap), C.c_int(hd), C.c_int(ad))
+        return out
+
+    want = run(orc, "oracle_")
+    for splits in (0, 1, 3, 16):
+        ck.ckb200_tune_set(b"attn_splits", splits)
+        got = run(ck, "")
+        ck.ckb200_tune_set(b"attn_splits", 0)
+        assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+
+
+def test_kv_cache_store_then_attend_token_by_token(ck, orc):
+    """The reference's own KV-cache test pattern: write token t, attend over 0..t, for every t."""
+    heads, kvh, d, cap, steps = 8, 4, 64, 32, 12
+    rng = np.random.default_rng(5)
+    kc_g = np.zeros((kvh, cap, d), np.float32)
+    vc_g = np.zeros_like(kc_g)
+    kc_c, vc_c = kc_g.copy(), vc_g.copy()
+    for t in range(steps):
+        k = rng.standard_normal((kvh, d)).astype(np.float32)
+        v = rng.standard_normal((kvh, d)).astype(np.float32)
+        q = rng.standard_normal((heads, d)).astype(np.float32)
+        cases.kv_cache_store(ck, "", kc_g, vc_g, k, v, t)
+        cases.kv_cache_store(orc, "oracle_", kc_c, vc_c, k, v, t)
+        assert np.array_equal(kc_g, kc_c) and np.array_equal(vc_g, vc_c)
+        a = cases.attention_decode(ck, "", q, kc_g, vc_g, t + 1)
+        b = cases.attention_decode(orc, "oracle_", q, kc_c, vc_c, t + 1)
+        assert float(np.max(np.abs(a - b))) <= 1e-5

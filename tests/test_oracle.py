@@ -1,0 +1,162 @@
+"""The CPU oracle is pinned against the reference: (1) against committed golden vectors that
+tests/golden/make_golden.py produced from the reference's own kernels, (2) live against
+oracle/_ref when it has been built here, on more and larger seeded cases."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+
+synth = cases.synth
+
+
+def _close(a, b, rtol_scale):
+    return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64)))) <= rtol_scale * max(1e-30, float(np.max(np.abs(a))))
+
+
+@pytest.fixture(scope="module")
+def oracle_outputs(orc):
+    return cases.golden_outputs(orc, "oracle_")
+
+
+def test_golden_file_is_complete(golden, oracle_outputs):
+    missing = [k for k in oracle_outputs if k not in golden.files and k != "residual"]
+    assert not missing, missing
+    assert len(golden.files) >= 40
+
+
+def test_oracle_bit_exact_stages(golden, oracle_outputs):
+    """Integer / byte stages and every function whose fp32 order the oracle keeps: identical bytes."""
+    checked = 0
+    for name in golden.files:
+        if name in oracle_outputs and name.startswith(cases.BIT_EXACT):
+            assert np.array_equal(golden[name], oracle_outputs[name]), name
+            checked += 1
+    assert checked >= 25
+
+
+def test_oracle_float_stages_within_tolerance(golden, oracle_outputs):
+    """Where the reference's dispatched path is vectorised (different fp32 order, FMA, fast exp)
+    the oracle agrees to well inside the 1e-3 contract."""
+    for name in golden.files:
+        if name not in oracle_outputs or name.startswith(cases.BIT_EXACT):
+            continue
+        tol = 2e-4 if name == "swiglu" else 1e-5     # the reference's AVX-512 SwiGLU uses a polynomial exp
+        assert _close(golden[name], oracle_outputs[name], tol), name
+
+
+def test_dispatched_reference_paths_agree_with_scalar(golden):
+    """The reference's own ISA paths differ from its scalar path only by fp32 rounding."""
+    for name in golden.files:
+        if name.startswith("gemv_dispatch_"):
+            assert _close(golden[name.replace("dispatch", "ref")], golden[name], 1e-5), name
+
+
+def test_q8k_edge_cases_decoded(golden):
+    """Spot-check the meaning of the edge-case vectors, not only their bytes."""
+    blocks = golden["q8k_edge"].reshape(5, 292)
+    d = blocks[:, :4].copy().view(np.float32).reshape(5)
+    qs = blocks[:, 4:260].copy().view(np.int8)
+    bsums = blocks[:, 260:].copy().view(np.int16)
+    assert d[0] == 0 and not qs[0].any() and not bsums[0].any()          # zero block
+    assert qs[1, 10] == -127 and qs[1, 200] == 127 and d[1] < 0          # +3 first: scale sign from it
+    assert qs[2, 7] == -127 and qs[2, 8] == 127 and d[2] > 0             # -5 first
+    assert qs[3, 0] == -127 and qs[3, 1] == 0 and qs[3, 2] == -2         # -0.5 -> 0, -1.5 -> -2 (ties to even)
+    assert np.array_equal(bsums, qs.reshape(5, 16, 16).sum(axis=2).astype(np.int16))
+
+
+def test_fp16_conversions_all_values(orc):
+    """Every half value round-trips; float->half agrees with numpy's IEEE conversion on a dense sample."""
+    orc.oracle_fp16_to_fp32.restype = C.c_float
+    orc.oracle_fp32_to_fp16.restype = C.c_uint16
+    h = np.arange(65536, dtype=np.uint16)
+    f = np.array([orc.oracle_fp16_to_fp32(C.c_uint16(int(v))) for v in h[::7]], dtype=np.float32)
+    expect = h[::7].view(np.float16).astype(np.float32)
+    ok = (f == expect) | (np.isnan(f) & np.isnan(expect))
+    assert ok.all()
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([rng.standard_normal(3000).astype(np.float32) * s for s in (1e-7, 1e-4, 1.0, 3e4)])
+    xs = np.concatenate([xs, np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, 2.0 ** -25, 2.0 ** -24, 6.1e-5], np.float32)])
+    got = np.array([orc.oracle_fp32_to_fp16(C.c_float(float(v))) for v in xs], dtype=np.uint16)
+    with np.errstate(over="ignore"):
+        want = xs.astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want)
+
+
+def test_subblock_sums_recompose_gemv(orc):
+    """The exported int32 sub-block sums are the integer stage of the GEMV: recombining them with the
+    unpacked scales in float64 reproduces the oracle's fp32 output to rounding."""
+    m, k = 6, 1024
+    for fmt in ("q4_k", "q6_k"):
+        w = synth.make_weights(fmt, m, k, seed=77)
+        xq = cases.quantize_q8_k(orc, "oracle_", synth.make_x(k, seed=77))
+        y = cases.gemv(orc, "oracle_", fmt, w, xq, m, k)
+        nb = k // 256
+        xb = xq.reshape(nb, 292)
+        xd = xb[:, :4].copy().view(np.float32).reshape(nb).astype(np.float64)
+        bs = xb[:, 260:].copy().view(np.int16).reshape(nb, 16).astype(np.int64)
+        for r in range(m):
+            row = w.reshape(m, -1)[r]
+            if fmt == "q4_k":
+                sums = np.zeros(nb * 8, dtype=np.int32)
+                orc.oracle_q4_k_q8_k_subblock_sums(cases.vptr(row), cases.vptr(xq), C.c_int(k), sums.ctypes.data_as(cases.c_int32_p))
+                blk = row.reshape(nb, 144)
+                acc = 0.0
+                for b in range(nb):
+                    d = float(blk[b, 0:2].copy().view(np.float16)[0]) * xd[b]
+                    dm = float(blk[b, 2:4].copy().view(np.float16)[0]) * xd[b]
+                    sc = np.zeros(8, np.uint8)
+                    mn = np.zeros(8, np.uint8)
+                    s12 = np.ascontiguousarray(blk[b, 4:16])
+                    orc.oracle_unpack_q4_k_scales(cases.vptr(s12), cases.vptr(sc), cases.vptr(mn))
+                    for j in range(8):
+                        acc += d * sc[j] * int(sums[8 * b + j]) - dm * mn[j] * int(bs[b, 2 * j] + bs[b, 2 * j + 1])
+            else:
+                sums = np.zeros(nb * 16, dtype=np.int32)
+                orc.oracle_q6_k_q8_k_subblock_sums(cases.vptr(row), cases.vptr(xq), C.c_int(k), sums.ctypes.data_as(cases.c_int32_p))
+                blk = row.reshape(nb, 210)
+                acc = 0.0
+                for b in range(nb):
+                    d = float(blk[b, 208:210].copy().view(np.float16)[0]) * xd[b]
+                    sc = blk[b, 192:208].copy().view(np.int8).astype(np.int64)
+                    acc += d * float((sc * sums[16 * b:16 * b + 16].astype(np.int64)).sum())
+            assert abs(acc - float(y[r])) <= 2e-5 * max(1.0, abs(acc)), (fmt, r, acc, y[r])
+
+
+# ---------------------------------------------------------------- live against the reference
+
+LIVE_GEMV = [("q4_k", 37, 4096, None), ("q4_k", 64, 1024, 896), ("q6_k", 33, 4096, None), ("q6_k", 21, 4864, None),
+             ("q8_0", 50, 896, None), ("q8_0", 19, 4864, None)]
+
+
+@pytest.mark.parametrize("fmt,m,k,kv", LIVE_GEMV)
+def test_oracle_vs_reference_gemv(ref, orc, fmt, m, k, kv):
+    w = synth.make_weights(fmt, m, k, seed=m)
+    x = synth.make_x(k, seed=m, k_valid=kv)
+    xq_r = cases.quantize_act(ref, "", fmt, x)
+    xq_o = cases.quantize_act(orc, "oracle_", fmt, x)
+    assert np.array_equal(xq_r, xq_o)
+    scalar = {"q4_k": "gemv_q4_k_q8_k_ref", "q6_k": "gemv_q6_k_q8_k_ref", "q8_0": None}[fmt]
+    y_o = cases.gemv(orc, "oracle_", fmt, w, xq_o, m, k)
+    if scalar:
+        assert np.array_equal(cases.gemv(ref, "", fmt, w, xq_r, m, k, scalar), y_o)
+    y_d = cases.gemv(ref, "", fmt, w, xq_r, m, k)          # the path a user of the reference gets
+    assert _close(y_d, y_o, 1e-5)
+
+
+def test_oracle_vs_reference_quantiser_many_rows(ref, orc):
+    x = synth.make_x(4864, seed=9, rows=16) * np.float32(3.7)
+    assert np.array_equal(cases.quantize_q8_k(ref, "", x, rows=16), cases.quantize_q8_k(orc, "oracle_", x, rows=16))
+    x = synth.make_x(896, seed=10, rows=16) * np.float32(0.01)
+    assert np.array_equal(cases.quantize_q8_0(ref, "", x, rows=16), cases.quantize_q8_0(orc, "oracle_", x, rows=16))
+
+
+@pytest.mark.parametrize("heads,kvh,d,tokens,cap", [(14, 2, 64, 1025, 1100), (16, 2, 128, 333, 512), (8, 4, 64, 64, 64)])
+def test_oracle_vs_reference_attention(ref, orc, heads, kvh, d, tokens, cap):
+    q, kc, vc = cases.attention_inputs(tokens, heads, kvh, d, tokens, cap)
+    a = cases.attention_decode(ref, "", q, kc, vc, tokens)
+    b = cases.attention_decode(orc, "oracle_", q, kc, vc, tokens)
+    assert float(np.max(np.abs(a - b))) < 1e-5          # the reference's own decode-vs-full tolerance

@@ -214,7 +214,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     import cases
 
     dev = torch.device("cuda", local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream(device=dev)             # graphs cannot be captured on the default stream
+    torch.cuda.set_stream(stream)
     sp = C.c_void_p(stream.cuda_stream)
 
     fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
     const int group = p.H / p.Hkv, h0 = kvh * group;   // heads h0 .. h0+group-1 map to kvh (H % Hkv == 0)
 
     __shared__ __align__(16) float q_s[ATTN_G][AD];
-    __shared__ float merge_s[ATTN_NW][ATTN_G][AD + 2];
+    __shared__ __align__(16) float merge_s[ATTN_NW][ATTN_G][AD + 4];   // row stride stays a multiple of 16 bytes
 
     for (int i = threadIdx.x; i < ATTN_G * AD; i += blockDim.x) {
         const int h = i / AD, c = i - h * AD;

@@ -416,7 +416,10 @@ int check_common(const char *name, const void *y, const void *W, const void *xq,
 
 }  // namespace
 
-// variant: 0 auto, 1 ring, 2 direct generic, 10.. tuned direct Q4_K shapes
+extern "C" int ckb_launch_gemv_q4k_pair(float *y, const void *W, const void *xq, int M, int nb, int r, int l1alloc, void *stream);   // gemv_q4k.cu
+extern "C" int ckb_launch_gemv_q4k_xreg(float *y, const void *W, const void *xq, int M, int nb, int r, int l1alloc, void *stream);   // gemv_q4k_xreg.cu
+
+// variant: 0 auto, 1 ring, 2 direct generic, 10.. direct with G lanes per row / R rows, 20/21 pair kernel (R = 1 / 2)
 extern "C" int ckb200_dev_gemv_q4_k_q8_k(float *y, const void *W, const void *xq, int M, int K, void *stream)
 {
     const int c = check_common("gemv_q4_k_q8_k", y, W, xq, M, K, QK_K);
@@ -427,8 +430,21 @@ extern "C" int ckb200_dev_gemv_q4_k_q8_k(float *y, const void *W, const void *xq
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);
     int v = ckb_tune_get("gemv_q4_k", 0);
-    if (v == 0) v = 11;
+    if (v == 0) {
+        // measured on B200 over the benchmark and decode shapes: few rows -> activations in registers
+        // (no staging, no barrier); very long rows -> same with two rows per step; otherwise the
+        // shared-activation kernel with L1-allocating loads
+        if (M <= 2048 && nb <= 128) v = 32;
+        else if (nb >= 56 && nb <= 128 && M <= 16384) v = 33;
+        else v = nb <= 4 ? 22 : 23;
+    }
     switch (v) {
+        case 30: case 31: case 32: case 33: {
+            const int rc = ckb_launch_gemv_q4k_xreg(y, W, xq, M, nb, (v & 1) ? 2 : 1, v >= 32, st);
+            if (rc >= 0) return rc;
+            return launch_q4k_direct<32, 2>(y, W, xq, M, nb, st);      // rows longer than 8 passes
+        }
+        case 20: case 21: case 22: case 23: return ckb_launch_gemv_q4k_pair(y, W, xq, M, nb, (v & 1) ? 2 : 1, v >= 22, st);
         case 1: return launch_ring<FMT_Q4K>(y, W, xq, M, nb, st);
         case 2: return launch_direct_generic<FMT_Q4K>(y, W, xq, M, nb, st);
         case 10: return launch_q4k_direct<32, 1>(y, W, xq, M, nb, st);

@@ -74,9 +74,9 @@ def test_quantize_q8_0_bit_exact(ck, orc, rows, k):
 
 # ---------------------------------------------------------------- GEMV: every kernel variant, ragged shapes
 
-VARIANTS = {"q4_k": [1, 2, 10, 11, 12, 13, 14, 15, 16, 17], "q6_k": [1, 2], "q8_0": [1, 2]}
+VARIANTS = {"q4_k": [1, 2, 10, 11, 12, 13, 14, 15, 16, 17, 20, 21, 22, 23, 30, 31, 32, 33], "q6_k": [1, 2], "q8_0": [1, 2]}
 RAGGED = {
-    "q4_k": [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (257, 2048)],
+    "q4_k": [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (257, 2048), (3, 36864), (300, 6144)],
     "q6_k": [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (2, 28672)],
     "q8_0": [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (2, 28672)],
 }

@@ -361,3 +361,103 @@ extern "C" int ckb200_dev_attention_decode(const float *q, const float *k_cache,
     return ckb200_dev_attention_decode_ws(q, k_cache, v_cache, out, batch, kv_batch_stride, num_heads, num_kv_heads, kv_tokens,
                                           cache_capacity, head_dim, aligned_head_dim, splits, scratch, NULL, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc on the decode path: a model runtime that
+// planned every byte of device memory at load time (the reference's own rule is "no malloc in
+// kernels, memory comes from the planned arena"), a real-time loop that may not take the
+// allocator's locks, or a process that has handed all free memory to another pool.  The split-K
+// kernel above needs a scratch buffer for its per-split partial results; here that buffer is a
+// fixed array inside the library image, so the call needs nothing but its inputs and outputs.
+//
+// Limits and rules:
+//   * the scratch is CKB_ATTN_STATIC_SCRATCH_BYTES (4 MiB) per GPU that loads the library, held
+//     until the process exits; a call whose partials need more is rejected with CKB_ERR_LIMIT
+//     (fewer splits, or splits = 1, always fit);
+//   * the array's device address is looked up once per device, on the first call made with that
+//     device current; make that first call before any stream capture;
+//   * every call shares the one array and it keeps the previous call's contents; nothing has to be
+//     cleared (each split slot is fully written before the merge reads it), but two calls that
+//     overlap on the GPU (different streams without ordering) race on it;
+//   * stream = NULL means the legacy default stream here (the library's own stream is not created).
+// This entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+#define CKB_ATTN_STATIC_SCRATCH_BYTES (4u << 20)
+#define CKB_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_attn_static_scratch[CKB_ATTN_STATIC_SCRATCH_BYTES / sizeof(float)];
+static float *g_attn_static_ptr[CKB_MAX_DEVICES];     // per device: address of the array on that device
+static int g_attn_static_sms[CKB_MAX_DEVICES];
+
+extern "C" size_t ckb200_attention_decode_static_scratch_limit(void) { return CKB_ATTN_STATIC_SCRATCH_BYTES; }
+
+extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k_cache, const float *v_cache, float *out,
+                                                  int batch, long long kv_batch_stride, int num_heads, int num_kv_heads,
+                                                  int kv_tokens, int cache_capacity, int head_dim, int aligned_head_dim,
+                                                  int splits, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !out) return 0;
+    if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return 0;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return 0;
+
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= CKB_MAX_DEVICES) {
+        cudaGetLastError();
+        return ckb_fail(CKB_ERR_NO_DEVICE, "attention decode (static scratch): no current CUDA device");
+    }
+    if (!g_attn_static_ptr[dev]) {
+        // set-up, once per device, with that device current: the array's name is only a host-side
+        // stand-in in host code; the kernel needs the device address
+        float *p = NULL;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_attn_static_scratch);
+        if (e != cudaSuccess || !p) {
+            ckb_check_cuda((int)e, "cudaGetSymbolAddress(static attention scratch)");
+            return CKB_ERR_CUDA;
+        }
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); sms = 148; }
+        g_attn_static_sms[dev] = sms;
+        g_attn_static_ptr[dev] = p;
+    }
+    float *scratch = g_attn_static_ptr[dev];
+
+    const int group = num_heads / num_kv_heads;
+    const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 && group <= ATTN_G &&
+                      (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 && (kv_batch_stride % 4) == 0;
+    if (splits <= 0) {                                  // same rule as ckb200_attention_decode_splits
+        const long long base = (long long)batch * num_kv_heads;
+        splits = (int)((2LL * g_attn_static_sms[dev] + base - 1) / base);
+        const int max_by_tokens = (kv_tokens + 63) / 64;
+        if (splits > max_by_tokens) splits = max_by_tokens;
+        if (splits > 256) splits = 256;
+        if (splits < 1) splits = 1;
+    }
+    AttnParams p;
+    p.q = q; p.k = k_cache; p.v = v_cache; p.out = out; p.part = scratch; p.pos_ptr = NULL;
+    p.kv_batch_stride = kv_batch_stride;
+    p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
+    p.scale = 1.0f / sqrtf((float)head_dim);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!fast) {
+        if (aligned_head_dim > ATTN_GEN_MAXD) return ckb_fail(CKB_ERR_LIMIT, "attention decode: aligned_head_dim %d > %d", aligned_head_dim, ATTN_GEN_MAXD);
+        p.splits = 1;
+        attn_decode_generic_kernel<<<dim3(num_heads, batch), 128, 0, st>>>(p);
+        return ckb_check_launch("attn_decode_generic");
+    }
+    const size_t need = splits > 1 ? (size_t)batch * num_heads * splits * (aligned_head_dim + 2) * sizeof(float) : 0;
+    if (need > CKB_ATTN_STATIC_SCRATCH_BYTES)
+        return ckb_fail(CKB_ERR_LIMIT, "attention decode (static scratch): %zu bytes of partials for batch %d x %d heads x %d splits "
+                        "exceed the built-in %u-byte scratch; use fewer splits or the allocating entry point",
+                        need, batch, num_heads, splits, (unsigned)CKB_ATTN_STATIC_SCRATCH_BYTES);
+    p.splits = splits;
+    const dim3 grid(splits, num_kv_heads, batch);
+    if (aligned_head_dim == 64) attn_decode_kernel<64><<<grid, ATTN_NW * 32, 0, st>>>(p);
+    else attn_decode_kernel<128><<<grid, ATTN_NW * 32, 0, st>>>(p);
+    if (ckb_check_launch("attn_decode")) return CKB_ERR_CUDA;
+    if (splits > 1) {
+        attn_merge_kernel<<<batch * num_heads, aligned_head_dim < 128 ? 64 : 128, 0, st>>>(scratch, out, splits, aligned_head_dim);
+        return ckb_check_launch("attn_merge");
+    }
+    return 0;
+}

@@ -106,6 +106,17 @@ int ckb200_dev_attention_decode_ws(const float *q, const float *k_cache, const f
                                    long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
                                    int cache_capacity, int head_dim, int aligned_head_dim, int splits, float *scratch,
                                    const int *pos_dev, void *stream);
+/* No counterpart in the reference.  The same decode attention for callers that must not allocate device
+ * memory on the decode path (a runtime whose device arena was planned at load time, a real-time loop, a
+ * process that gave all free memory to another pool): the split-K partials go to a fixed 4 MiB array inside
+ * the library instead of a scratch buffer.  splits <= 0 picks the split count; a call that would need more
+ * than ckb200_attention_decode_static_scratch_limit() bytes is rejected with CKB_ERR_LIMIT.  Calls share the
+ * array: do not overlap two of them on the GPU.  The first call on each device looks the array up; make it
+ * before any stream capture.  stream NULL = the legacy default stream.  Calls no cudaMalloc / cudaFree. */
+int ckb200_dev_attention_decode_static(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
+                                       long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
+                                       int cache_capacity, int head_dim, int aligned_head_dim, int splits, void *stream);
+size_t ckb200_attention_decode_static_scratch_limit(void);
 int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
 size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
 

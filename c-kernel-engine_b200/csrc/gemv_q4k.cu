@@ -40,7 +40,7 @@ __device__ __forceinline__ Q4pX q4p_stage_x(const uint8_t *xg, int nb, uint8_t *
     const uint32_t *src = reinterpret_cast<const uint32_t *>(xg);
     for (int i = threadIdx.x; i < nb * 73; i += blockDim.x) {
         const int b = i / 73, w = i - b * 73;
-        const uint32_t v = __ldg(src + i);
+        const uint32_t v = __ldcg(src + i);     // through L2: the producer may overlap this kernel (programmatic launch)
         if (w == 0) {
             xd[b] = __uint_as_float(v);
         } else if (w <= 64) {

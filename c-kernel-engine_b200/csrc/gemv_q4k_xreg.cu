@@ -22,7 +22,9 @@ struct XrX {                 // one lane's activations: quarter p and quarter p+
     uint32_t lo4, hi4;       // sub-block sums {2p, 2p+1, 2p+4, 2p+5} split as 128*hi + lo, 4 x s8 each
 };
 
-__device__ __forceinline__ uint4 ldg4w(const uint32_t *p) { return make_uint4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3)); }
+// activations were written by the previous kernel, which may overlap this one under programmatic launch:
+// they are read through L2 (__ldcg), never through the non-coherent read-only path
+__device__ __forceinline__ uint4 ldg4w(const uint32_t *p) { return make_uint4(__ldcg(p), __ldcg(p + 1), __ldcg(p + 2), __ldcg(p + 3)); }
 
 __device__ __forceinline__ XrX xr_load_x(const uint8_t *xg, int b, int p)
 {
@@ -31,12 +33,12 @@ __device__ __forceinline__ XrX xr_load_x(const uint8_t *xg, int b, int p)
     const uint32_t *qa = blk + 1 + 16 * p, *qb = blk + 1 + 16 * (p + 2);
     x.al0 = ldg4w(qa); x.al1 = ldg4w(qa + 4); x.ah0 = ldg4w(qa + 8); x.ah1 = ldg4w(qa + 12);
     x.bl0 = ldg4w(qb); x.bl1 = ldg4w(qb + 4); x.bh0 = ldg4w(qb + 8); x.bh1 = ldg4w(qb + 12);
-    x.d = __uint_as_float(__ldg(blk));
+    x.d = __uint_as_float(__ldcg(blk));
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int j = 2 * p + (i & 1) + 4 * (i >> 1);                // sub-block of byte i
-        const uint32_t v = __ldg(blk + 65 + j);
+        const uint32_t v = __ldcg(blk + 65 + j);
         const int s = (int)(short)(v & 0xffffu) + (int)(short)(v >> 16);
         lo |= (uint32_t)(s & 127) << (8 * i);
         hi |= (uint32_t)((s >> 7) & 255) << (8 * i);

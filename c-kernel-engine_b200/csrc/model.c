@@ -1,0 +1,506 @@
+/* Device-resident decode step: the op sequence the reference's generated ck_decode() issues for a
+ * Llama/Qwen-style decoder (version/v7/scripts/codegen_v7.py:886-931; per-layer template
+ * version/v7/templates/qwen2.json:95-110), run as one CUDA graph on one stream with every activation,
+ * the KV cache and the position counter in HBM.  Weights keep the reference's block formats and
+ * row-major [out][in] layout; gate and up rows are one [2I][D] matrix, gate first
+ * (codegen_v7.py:686-714).
+ *
+ * Per layer:  x += prev; h = Q8_K(rmsnorm(x))            (add_rmsnorm_q8k)
+ *             q,k,v = Wq.h, Wk.h, Wv.h                   (dequant-dot GEMVs)
+ *             rope(q,k) ; cache[pos] = k,v               (rope_kv_store)
+ *             a = attention(q, cache[0..pos])            (split-K decode attention)
+ *             o = Wo.Q8_K(a)
+ *             x += o; h = Q8_K(rmsnorm(x))
+ *             m = Q8_K(swiglu(W1.h))                     (swiglu_q8k)
+ *             prev = W2.m
+ * Finally     x += prev; logits = Wlm.Q8_K(rmsnorm(x)); pos += 1
+ *
+ * K-quant GEMVs need K % 256 == 0: rows that feed them are kept `aligned` = roundup(K, 256) wide with
+ * a zero tail, exactly what rmsnorm_forward(..., d_model, aligned_embed_dim, ...) produces in the
+ * reference (src/kernels/rmsnorm_kernels.c:245-248).
+ *
+ * Tensor parallelism: with tp_size > 1 every rank holds tp_size-th of the heads and of the FFN rows
+ * (column-parallel Wq/Wk/Wv/W1) and a 256-aligned slice of the input columns of Wo/W2 (row-parallel);
+ * the two partial outputs per layer are summed over ranks by the all-reduce hook.
+ */
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/ckb200.h"
+#include "../../include/ckb200_model.h"
+#include "launch.h"
+#include "runtime.h"
+
+enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2 };
+
+typedef struct {
+    void *w;            /* device pointer */
+    size_t bytes;
+    int fmt;            /* block format, or -1 for fp32 */
+    int rows, cols;     /* [rows][cols] elements (cols already aligned) */
+} Tensor;
+
+typedef struct {
+    Tensor t[CKB_T_PER_LAYER];
+} Layer;
+
+struct CKB200Model {
+    CKB200ModelConfig c;
+    int D, Da;              /* embed dim and its 256-aligned width */
+    int Hl, Hkvl, d;        /* local heads */
+    int Al, Ala;            /* local attention width Hl*d and aligned */
+    int Il;                 /* local intermediate size */
+    int Vl;                 /* local vocab rows */
+    Layer *layers;
+    Tensor emb, final_gamma, lm_head;
+    uint8_t *arena;         /* all weights */
+    size_t arena_bytes;
+    float *kv;              /* [L][2][B][Hkvl][S][d] */
+    long long kv_layer_stride, kv_batch_stride;
+    float *rope_cos, *rope_sin;
+    /* activations */
+    float *x, *prev, *q, *k, *v, *att, *o, *gu, *logits, *attn_scratch;
+    uint8_t *hq, *aq, *mq;
+    int32_t *tokens_dev, *pos_dev;
+    int32_t *tokens_pinned;
+    int attn_splits;
+    cudaGraphExec_t graph;
+    int graph_ready;
+    int have_prev;
+    ckb200_allreduce_fn allreduce;
+    void *allreduce_ctx;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static int round256(int v) { return (v + 255) / 256 * 256; }
+
+static size_t fmt_row_bytes(int fmt, int cols)
+{
+    switch (fmt) {
+        case FMT_Q4K: return (size_t)(cols / 256) * 144;
+        case FMT_Q6K: return (size_t)(cols / 256) * 210;
+        case FMT_Q80: return (size_t)(cols / 32) * 34;
+        default: return (size_t)cols * 4;
+    }
+}
+
+static void tensor_plan(Tensor *t, int fmt, int rows, int cols, size_t *cursor)
+{
+    t->fmt = fmt;
+    t->rows = rows;
+    t->cols = cols;
+    t->bytes = (size_t)rows * fmt_row_bytes(fmt, cols);
+    t->w = (void *)(uintptr_t)*cursor;              /* offset for now */
+    *cursor = align_up(*cursor + t->bytes + 32, 256);
+}
+
+static int cols_for(int fmt, int k) { return fmt == FMT_Q80 ? (k + 31) / 32 * 32 : round256(k); }
+
+CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
+{
+    if (!cfg) return NULL;
+    if (ckb_ensure_init()) return NULL;
+    const int tp = cfg->tp_size > 0 ? cfg->tp_size : 1;
+    if (cfg->num_heads % cfg->num_kv_heads || cfg->num_heads % tp || cfg->intermediate_size % tp ||
+        (cfg->num_kv_heads % tp && tp % cfg->num_kv_heads) || cfg->batch <= 0 || cfg->head_dim % 2) {
+        ckb_fail(CKB_ERR_SHAPE, "model_create: heads %d / kv heads %d / ffn %d do not split over tp=%d", cfg->num_heads,
+                 cfg->num_kv_heads, cfg->intermediate_size, tp);
+        return NULL;
+    }
+    CKB200Model *m = (CKB200Model *)calloc(1, sizeof *m);
+    if (!m) return NULL;
+    m->c = *cfg;
+    m->c.tp_size = tp;
+    m->D = cfg->embed_dim;
+    m->Da = round256(m->D);
+    m->d = cfg->head_dim;
+    m->Hl = cfg->num_heads / tp;
+    m->Hkvl = cfg->num_kv_heads >= tp ? cfg->num_kv_heads / tp : 1;
+    m->Al = m->Hl * m->d;
+    m->Ala = round256(m->Al);
+    m->Il = cfg->intermediate_size / tp;
+    m->Vl = cfg->vocab_size;                           /* the LM head is kept whole on every rank */
+    if (cfg->batch > 1 && m->Al != m->Ala) {
+        ckb_fail(CKB_ERR_SHAPE, "model_create: batch > 1 needs the attention width %d to be a multiple of 256", m->Al);
+        free(m);
+        return NULL;
+    }
+    if (tp > 1 && (m->Al % 256 || m->Il % 256)) {
+        ckb_fail(CKB_ERR_SHAPE, "model_create: tp=%d needs the per-rank attention width %d and FFN width %d to be multiples of 256", tp, m->Al, m->Il);
+        free(m);
+        return NULL;
+    }
+    const int L = cfg->num_layers, B = cfg->batch, S = cfg->max_seq_len;
+    m->layers = (Layer *)calloc((size_t)L, sizeof(Layer));
+    size_t cur = 0;
+    for (int l = 0; l < L; ++l) {
+        Tensor *t = m->layers[l].t;
+        tensor_plan(&t[CKB_T_LN1], -1, 1, m->Da, &cur);
+        tensor_plan(&t[CKB_T_WQ], cfg->fmt_q, m->Hl * m->d, cols_for(cfg->fmt_q, m->D), &cur);
+        tensor_plan(&t[CKB_T_WK], cfg->fmt_k, m->Hkvl * m->d, cols_for(cfg->fmt_k, m->D), &cur);
+        tensor_plan(&t[CKB_T_WV], cfg->fmt_v, m->Hkvl * m->d, cols_for(cfg->fmt_v, m->D), &cur);
+        tensor_plan(&t[CKB_T_WO], cfg->fmt_o, m->D, cols_for(cfg->fmt_o, m->Al), &cur);
+        tensor_plan(&t[CKB_T_LN2], -1, 1, m->Da, &cur);
+        tensor_plan(&t[CKB_T_W1], cfg->fmt_gate_up, 2 * m->Il, cols_for(cfg->fmt_gate_up, m->D), &cur);
+        tensor_plan(&t[CKB_T_W2], cfg->fmt_down, m->D, cols_for(cfg->fmt_down, m->Il), &cur);
+    }
+    tensor_plan(&m->final_gamma, -1, 1, m->Da, &cur);
+    tensor_plan(&m->lm_head, cfg->fmt_lm_head, m->Vl, cols_for(cfg->fmt_lm_head, m->D), &cur);
+    if (cfg->tie_embeddings) m->emb = m->lm_head;
+    else tensor_plan(&m->emb, cfg->fmt_embedding, cfg->vocab_size, cols_for(cfg->fmt_embedding, m->D), &cur);
+    m->arena_bytes = cur + 256;
+
+    int ok = 1;
+#define DEV_ALLOC(ptr, bytes) do { if (ok && ckb_check_cuda((int)cudaMalloc((void **)&(ptr), (bytes)), "cudaMalloc(model)")) ok = 0; } while (0)
+    DEV_ALLOC(m->arena, m->arena_bytes);
+    m->kv_batch_stride = (long long)m->Hkvl * S * m->d;
+    m->kv_layer_stride = 2LL * B * m->kv_batch_stride;
+    DEV_ALLOC(m->kv, (size_t)L * m->kv_layer_stride * sizeof(float));
+    DEV_ALLOC(m->rope_cos, (size_t)S * (m->d / 2) * sizeof(float));
+    DEV_ALLOC(m->rope_sin, (size_t)S * (m->d / 2) * sizeof(float));
+    DEV_ALLOC(m->x, (size_t)B * m->Da * sizeof(float));
+    DEV_ALLOC(m->prev, (size_t)B * m->Da * sizeof(float));
+    DEV_ALLOC(m->o, (size_t)B * m->Da * sizeof(float));
+    DEV_ALLOC(m->q, (size_t)B * m->Al * sizeof(float));
+    DEV_ALLOC(m->k, (size_t)B * m->Hkvl * m->d * sizeof(float));
+    DEV_ALLOC(m->v, (size_t)B * m->Hkvl * m->d * sizeof(float));
+    DEV_ALLOC(m->att, (size_t)B * m->Ala * sizeof(float));
+    DEV_ALLOC(m->gu, (size_t)B * 2 * m->Il * sizeof(float));
+    DEV_ALLOC(m->logits, (size_t)B * m->Vl * sizeof(float));
+    DEV_ALLOC(m->hq, (size_t)B * (m->Da / 32) * 34 + (size_t)B * (m->Da / 256) * 292 + 256);
+    DEV_ALLOC(m->aq, (size_t)B * (m->Ala / 32) * 34 + (size_t)B * (m->Ala / 256) * 292 + 256);
+    DEV_ALLOC(m->mq, (size_t)B * ((m->Il + 255) / 256) * 292 * 2 + 256);
+    DEV_ALLOC(m->tokens_dev, (size_t)B * sizeof(int32_t));
+    DEV_ALLOC(m->pos_dev, 256);
+    m->attn_splits = ckb200_attention_decode_splits(B, m->Hkvl, S);
+    {
+        size_t sb = ckb200_attention_decode_scratch_bytes(B, m->Hl, m->d, m->attn_splits);
+        DEV_ALLOC(m->attn_scratch, sb ? sb : 256);
+    }
+    if (ok && ckb_check_cuda((int)cudaHostAlloc((void **)&m->tokens_pinned, (size_t)B * sizeof(int32_t), cudaHostAllocDefault), "cudaHostAlloc")) ok = 0;
+    if (!ok) { ckb200_model_free(m); return NULL; }
+#undef DEV_ALLOC
+    /* offsets -> pointers */
+    for (int l = 0; l < L; ++l)
+        for (int i = 0; i < CKB_T_PER_LAYER; ++i) m->layers[l].t[i].w = m->arena + (uintptr_t)m->layers[l].t[i].w;
+    m->final_gamma.w = m->arena + (uintptr_t)m->final_gamma.w;
+    m->lm_head.w = m->arena + (uintptr_t)m->lm_head.w;
+    m->emb.w = cfg->tie_embeddings ? m->lm_head.w : (void *)(m->arena + (uintptr_t)m->emb.w);
+
+    cudaStream_t st = ckb_stream(NULL);
+    cudaMemsetAsync(m->arena, 0, m->arena_bytes, st);
+    cudaMemsetAsync(m->kv, 0, (size_t)L * m->kv_layer_stride * sizeof(float), st);
+    cudaMemsetAsync(m->att, 0, (size_t)B * m->Ala * sizeof(float), st);       /* zero tail of the attention rows stays zero */
+    cudaMemsetAsync(m->x, 0, (size_t)B * m->Da * sizeof(float), st);
+    cudaMemsetAsync(m->prev, 0, (size_t)B * m->Da * sizeof(float), st);
+    cudaMemsetAsync(m->o, 0, (size_t)B * m->Da * sizeof(float), st);
+    cudaMemsetAsync(m->pos_dev, 0, 256, st);
+    ckb200_dev_rope_precompute_cache_split(m->rope_cos, m->rope_sin, S, m->d, cfg->rope_theta, NULL);
+    if (ckb_check_cuda((int)cudaStreamSynchronize(st), "model init")) { ckb200_model_free(m); return NULL; }
+    return m;
+}
+
+void ckb200_model_free(CKB200Model *m)
+{
+    if (!m) return;
+    cudaStreamSynchronize(ckb_stream(NULL));
+    if (m->graph_ready) cudaGraphExecDestroy(m->graph);
+    void *ptrs[] = { m->arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
+                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch };
+    for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
+    if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
+    free(m->layers);
+    free(m);
+}
+
+static Tensor *find_tensor(CKB200Model *m, int layer, int which)
+{
+    if (layer >= 0 && layer < m->c.num_layers && which >= 0 && which < CKB_T_PER_LAYER) return &m->layers[layer].t[which];
+    if (layer == -1) {
+        if (which == CKB_T_FINAL_GAMMA) return &m->final_gamma;
+        if (which == CKB_T_LM_HEAD) return &m->lm_head;
+        if (which == CKB_T_EMBEDDING) return &m->emb;
+    }
+    return NULL;
+}
+
+size_t ckb200_model_tensor_bytes(CKB200Model *m, int layer, int which)
+{
+    Tensor *t = m ? find_tensor(m, layer, which) : NULL;
+    return t ? t->bytes : 0;
+}
+void *ckb200_model_tensor_ptr(CKB200Model *m, int layer, int which)
+{
+    Tensor *t = m ? find_tensor(m, layer, which) : NULL;
+    return t ? t->w : NULL;
+}
+int ckb200_model_tensor_shape(CKB200Model *m, int layer, int which, int *rows, int *cols, int *fmt)
+{
+    Tensor *t = m ? find_tensor(m, layer, which) : NULL;
+    if (!t) return CKB_ERR_STATE;
+    if (rows) *rows = t->rows;
+    if (cols) *cols = t->cols;
+    if (fmt) *fmt = t->fmt;
+    return 0;
+}
+
+int ckb200_model_upload_tensor(CKB200Model *m, int layer, int which, const void *host, size_t bytes)
+{
+    Tensor *t = m ? find_tensor(m, layer, which) : NULL;
+    if (!t || !host) return ckb_fail(CKB_ERR_STATE, "model_upload_tensor: no such tensor (%d, %d)", layer, which);
+    if (bytes != t->bytes) return ckb_fail(CKB_ERR_SHAPE, "model_upload_tensor(%d, %d): got %zu bytes, tensor has %zu", layer, which, bytes, t->bytes);
+    m->graph_ready = m->graph_ready;   /* weights are read through fixed pointers: the captured graph stays valid */
+    return ckb_check_cuda((int)cudaMemcpy(t->w, host, bytes, cudaMemcpyHostToDevice), "upload tensor");
+}
+
+static int fill_tensor(Tensor *t, unsigned long long seed)
+{
+    if (t->fmt < 0) return ckb200_dev_fill_normal((float *)t->w, (long long)t->rows * t->cols, 1, seed, NULL);
+    const long long nblocks = (long long)t->rows * (t->cols / (t->fmt == FMT_Q80 ? 32 : 256));
+    return ckb200_dev_fill_blocks(t->w, nblocks, t->fmt, seed, NULL);
+}
+
+int ckb200_model_fill_synthetic(CKB200Model *m, unsigned long long seed)
+{
+    if (!m) return CKB_ERR_STATE;
+    unsigned long long s = seed * 1000003ull + 17;
+    for (int l = 0; l < m->c.num_layers; ++l)
+        for (int i = 0; i < CKB_T_PER_LAYER; ++i)
+            if (fill_tensor(&m->layers[l].t[i], s++)) return CKB_ERR_CUDA;
+    if (fill_tensor(&m->final_gamma, s++) || fill_tensor(&m->lm_head, s++)) return CKB_ERR_CUDA;
+    if (!m->c.tie_embeddings && fill_tensor(&m->emb, s++)) return CKB_ERR_CUDA;
+    return ckb200_synchronize();
+}
+
+int ckb200_model_fill_kv_synthetic(CKB200Model *m, int tokens, unsigned long long seed)
+{
+    if (!m || tokens < 0 || tokens > m->c.max_seq_len) return ckb_fail(CKB_ERR_STATE, "model_fill_kv_synthetic: bad token count %d", tokens);
+    const int L = m->c.num_layers, B = m->c.batch, S = m->c.max_seq_len;
+    cudaStream_t st = ckb_stream(NULL);
+    cudaMemsetAsync(m->kv, 0, (size_t)L * m->kv_layer_stride * sizeof(float), st);
+    if (tokens > 0) {
+        /* N(0,1) in the first `tokens` positions of every head: fill a compact buffer, then strided copy */
+        const size_t heads = (size_t)L * 2 * B * m->Hkvl;
+        float *tmp = NULL;
+        const size_t row = (size_t)tokens * m->d;
+        const size_t chunk_heads = heads < 4096 ? heads : 4096;
+        if (ckb_check_cuda((int)cudaMalloc((void **)&tmp, chunk_heads * row * sizeof(float)), "cudaMalloc(kv fill)")) return CKB_ERR_CUDA;
+        for (size_t h0 = 0; h0 < heads; h0 += chunk_heads) {
+            const size_t n = heads - h0 < chunk_heads ? heads - h0 : chunk_heads;
+            ckb200_dev_fill_normal(tmp, (long long)(n * row), 0, seed + h0, NULL);
+            cudaMemcpy2DAsync(m->kv + h0 * (size_t)S * m->d, (size_t)S * m->d * sizeof(float), tmp, row * sizeof(float), row * sizeof(float), n,
+                              cudaMemcpyDeviceToDevice, st);
+        }
+        cudaStreamSynchronize(st);
+        cudaFree(tmp);
+    }
+    return ckb200_model_set_pos(m, tokens);
+}
+
+int ckb200_model_set_pos(CKB200Model *m, int pos)
+{
+    if (!m || pos < 0 || pos >= m->c.max_seq_len) return ckb_fail(CKB_ERR_STATE, "model_set_pos: %d outside [0, %d)", pos, m ? m->c.max_seq_len : 0);
+    int32_t p = pos;
+    cudaStream_t st = ckb_stream(NULL);
+    if (ckb_check_cuda((int)cudaMemcpyAsync(m->pos_dev, &p, sizeof p, cudaMemcpyHostToDevice, st), "set pos")) return CKB_ERR_CUDA;
+    return ckb_check_cuda((int)cudaStreamSynchronize(st), "set pos");
+}
+
+int ckb200_model_get_pos(CKB200Model *m)
+{
+    int32_t p = -1;
+    if (!m) return -1;
+    cudaStreamSynchronize(ckb_stream(NULL));
+    cudaMemcpy(&p, m->pos_dev, sizeof p, cudaMemcpyDeviceToHost);
+    return p;
+}
+
+void ckb200_model_set_allreduce(CKB200Model *m, ckb200_allreduce_fn fn, void *ctx)
+{
+    if (!m) return;
+    m->allreduce = fn;
+    m->allreduce_ctx = ctx;
+    m->graph_ready = 0;
+}
+
+float *ckb200_model_logits_device(CKB200Model *m) { return m ? m->logits : NULL; }
+void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v)
+{
+    if (!m || layer < 0 || layer >= m->c.num_layers) return NULL;
+    return m->kv + (size_t)layer * m->kv_layer_stride + (is_v ? (size_t)m->c.batch * m->kv_batch_stride : 0);
+}
+
+/* ------------------------------------------------------------------ the step */
+
+static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
+{
+    switch (fmt) {
+        case FMT_Q4K: return ckb200_dev_gemv_q4_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
+        case FMT_Q6K: return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
+        default: return ckb200_dev_gemv_q8_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
+    }
+}
+
+/* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
+static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, int y_stride, void *st)
+{
+    const size_t xrow = w->fmt == FMT_Q80 ? (size_t)(w->cols / 32) * 34 : (size_t)(w->cols / 256) * 292;
+    for (int b = 0; b < m->c.batch; ++b) {
+        const int rc = gemv_q(w->fmt, y + (size_t)b * y_stride, w, xq + b * xrow, st);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+/* h = quantised rmsnorm(x += delta) in the format the consumer `w` wants */
+static int norm_quant(CKB200Model *m, const float *delta, const Tensor *gamma, const Tensor *consumer, void *st)
+{
+    const int B = m->c.batch;
+    if (consumer->fmt != FMT_Q80)
+        return ckb200_dev_add_rmsnorm_q8k(m->x, delta, (const float *)gamma->w, m->hq, NULL, B, m->D, m->Da, m->c.rms_eps, st);
+    /* Q8_0 consumer: unfused path through an fp32 row */
+    int rc = 0;
+    if (delta) rc = ckb200_dev_add_inplace(m->x, delta, (long long)B * m->Da, st);
+    if (!rc) rc = ckb200_dev_rmsnorm_forward(m->x, (const float *)gamma->w, m->o, NULL, B, m->D, m->Da, m->c.rms_eps, st);
+    if (!rc) {
+        /* quantise each row's first `cols` elements */
+        for (int b = 0; b < B && !rc; ++b)
+            rc = ckb200_dev_quantize_q8_0(m->o + (size_t)b * m->Da, m->hq + (size_t)b * (consumer->cols / 32) * 34, 1, consumer->cols, st);
+    }
+    return rc;
+}
+
+static int quant_rows(const Tensor *consumer, const float *x, int x_stride, uint8_t *out, int rows, void *st)
+{
+    int rc = 0;
+    if (consumer->fmt == FMT_Q80) {
+        for (int b = 0; b < rows && !rc; ++b)
+            rc = ckb200_dev_quantize_q8_0(x + (size_t)b * x_stride, out + (size_t)b * (consumer->cols / 32) * 34, 1, consumer->cols, st);
+    } else if (x_stride == consumer->cols) {
+        rc = ckb200_dev_quantize_q8_k(x, out, rows, consumer->cols, st);
+    } else {
+        for (int b = 0; b < rows && !rc; ++b)
+            rc = ckb200_dev_quantize_q8_k(x + (size_t)b * x_stride, out + (size_t)b * (consumer->cols / 256) * 292, 1, consumer->cols, st);
+    }
+    return rc;
+}
+
+static int reduce_partial(CKB200Model *m, float *buf, size_t count, void *st)
+{
+    if (m->c.tp_size <= 1) return 0;
+    if (!m->allreduce) return ckb_fail(CKB_ERR_STATE, "model step: tp_size %d but no all-reduce hook set", m->c.tp_size);
+    return m->allreduce(m->allreduce_ctx, buf, count, st);
+}
+
+static int issue_step(CKB200Model *m, void *st)
+{
+    const CKB200ModelConfig *c = &m->c;
+    const int B = c->batch, L = c->num_layers;
+    int rc;
+    /* embedding of the B current tokens -> x */
+    switch (m->emb.fmt) {
+        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
+        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
+        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
+    }
+    if (rc) return rc;
+    const float *delta = NULL;
+    for (int l = 0; l < L; ++l) {
+        Tensor *t = m->layers[l].t;
+        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + (size_t)B * m->kv_batch_stride;
+        if ((rc = norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
+        if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;
+        if (t[CKB_T_WK].fmt != t[CKB_T_WQ].fmt && (t[CKB_T_WK].fmt == FMT_Q80 || t[CKB_T_WQ].fmt == FMT_Q80))
+            return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
+        if ((rc = matvec(m, &t[CKB_T_WK], m->hq, m->k, m->Hkvl * m->d, st))) return rc;
+        if ((rc = matvec(m, &t[CKB_T_WV], m->hq, m->v, m->Hkvl * m->d, st))) return rc;
+        if ((rc = ckb200_dev_rope_kv_store(m->q, m->k, m->v, kc, vc, m->rope_cos, m->rope_sin, m->pos_dev, B, m->Hl, m->Hkvl, m->d,
+                                           c->max_seq_len, m->kv_batch_stride, st))) return rc;
+        if ((rc = ckb200_dev_attention_decode_ws(m->q, kc, vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
+                                                 m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
+        /* attention rows are contiguous [B][Al]; with B == 1 the row sits in an Ala-wide buffer whose tail stays zero */
+        if ((rc = quant_rows(&t[CKB_T_WO], m->att, m->Ala, m->aq, B, st))) return rc;
+        if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
+        if ((rc = reduce_partial(m, m->o, (size_t)B * m->Da, st))) return rc;
+        if ((rc = norm_quant(m, m->o, &t[CKB_T_LN2], &t[CKB_T_W1], st))) return rc;
+        if ((rc = matvec(m, &t[CKB_T_W1], m->hq, m->gu, 2 * m->Il, st))) return rc;
+        if (t[CKB_T_W2].fmt != FMT_Q80 && m->Il % 256 == 0) {
+            if ((rc = ckb200_dev_swiglu_q8k(m->gu, m->mq, B, m->Il, st))) return rc;
+        } else {
+            /* swiglu to fp32 (reusing the front of gu is not safe: separate rows), then quantise */
+            return ckb_fail(CKB_ERR_STATE, "model step: FFN width %d with this down-projection format is not supported", m->Il);
+        }
+        if ((rc = matvec(m, &t[CKB_T_W2], m->mq, m->prev, m->Da, st))) return rc;
+        if ((rc = reduce_partial(m, m->prev, (size_t)B * m->Da, st))) return rc;
+        delta = m->prev;
+    }
+    if ((rc = norm_quant(m, delta, &m->final_gamma, &m->lm_head, st))) return rc;
+    if ((rc = matvec(m, &m->lm_head, m->hq, m->logits, m->Vl, st))) return rc;
+    return ckb200_dev_advance_pos(m->pos_dev, st);
+}
+
+int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_host)
+{
+    if (!m || !tokens) return ckb_fail(CKB_ERR_STATE, "model_decode: NULL model or tokens");
+    cudaStream_t st = ckb_stream(NULL);
+    const int B = m->c.batch;
+    memcpy(m->tokens_pinned, tokens, (size_t)B * sizeof(int32_t));
+    if (ckb_check_cuda((int)cudaMemcpyAsync(m->tokens_dev, m->tokens_pinned, (size_t)B * sizeof(int32_t), cudaMemcpyHostToDevice, st), "tokens H2D")) return CKB_ERR_CUDA;
+    const int use_graph = ckb_tune_get("model_graph", 1);
+    if (use_graph && !m->graph_ready) {
+        /* one eager step first: it sets per-kernel attributes (not allowed while capturing) and is rolled back */
+        int32_t pos0 = 0;
+        cudaMemcpyAsync(&pos0, m->pos_dev, sizeof pos0, cudaMemcpyDeviceToHost, st);
+        cudaStreamSynchronize(st);
+        int rc = issue_step(m, st);
+        if (rc) return rc;
+        cudaMemcpyAsync(m->pos_dev, &pos0, sizeof pos0, cudaMemcpyHostToDevice, st);
+        if (ckb_check_cuda((int)cudaStreamSynchronize(st), "warm-up step")) return CKB_ERR_CUDA;
+        cudaGraph_t g = NULL;
+        if (ckb_check_cuda((int)cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "begin capture")) return CKB_ERR_CUDA;
+        rc = issue_step(m, st);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
+        if (rc || e != cudaSuccess || !g) {
+            if (g) cudaGraphDestroy(g);
+            return rc ? rc : ckb_check_cuda((int)e, "end capture");
+        }
+        const cudaError_t ei = cudaGraphInstantiate(&m->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (ckb_check_cuda((int)ei, "graph instantiate")) return CKB_ERR_CUDA;
+        m->graph_ready = 1;
+    }
+    if (use_graph) {
+        if (ckb_check_cuda((int)cudaGraphLaunch(m->graph, st), "graph launch")) return CKB_ERR_CUDA;
+    } else {
+        const int rc = issue_step(m, st);
+        if (rc) return rc;
+    }
+    if (logits_host) {
+        if (ckb_check_cuda((int)cudaMemcpyAsync(logits_host, m->logits, (size_t)B * m->Vl * sizeof(float), cudaMemcpyDeviceToHost, st), "logits D2H")) return CKB_ERR_CUDA;
+        return ckb_check_cuda((int)cudaStreamSynchronize(st), "decode sync");
+    }
+    return 0;
+}
+
+/* Enqueue `steps` decode steps that keep feeding the same token ids (benchmark loop; no host sync). */
+int ckb200_model_decode_repeat(CKB200Model *m, int steps)
+{
+    if (!m || !m->graph_ready) return ckb_fail(CKB_ERR_STATE, "model_decode_repeat: run model_decode once first");
+    cudaStream_t st = ckb_stream(NULL);
+    for (int i = 0; i < steps; ++i)
+        if (ckb_check_cuda((int)cudaGraphLaunch(m->graph, st), "graph launch")) return CKB_ERR_CUDA;
+    return 0;
+}
+
+size_t ckb200_model_weight_bytes(CKB200Model *m)
+{
+    if (!m) return 0;
+    size_t s = 0;
+    for (int l = 0; l < m->c.num_layers; ++l)
+        for (int i = 0; i < CKB_T_PER_LAYER; ++i)
+            if (m->layers[l].t[i].fmt >= 0) s += m->layers[l].t[i].bytes;
+    return s + m->lm_head.bytes;
+}

@@ -7,7 +7,8 @@
 //     (the warp reduction compares (|x|, index) so that the lowest index wins ties);
 //   * iscale = -127/max and d = 1/iscale use IEEE division; the product iscale*x is rounded
 //     to fp32 before the round-to-nearest-even integer conversion (no FMA contraction).
-#include "device_common.cuh"
+#include "q8k_block.cuh"
+#include "pdl.cuh"
 #include "launch.h"
 #include "runtime.h"
 
@@ -19,55 +20,17 @@ __global__ void __launch_bounds__(128) quantize_q8_k_kernel(const float *__restr
 {
     const int lane = threadIdx.x & 31;
     const long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     if (blk >= nblocks) return;
 
+    // written by the previous kernel, which may still have been running when this one started:
+    // read through L2 (the read-only path is not coherent across a programmatic launch)
     const float4 *src = reinterpret_cast<const float4 *>(x + blk * QK_K) + 2 * lane;
-    const float4 a = src[0], b = src[1];
+    const float4 a = __ldcg(src), b = __ldcg(src + 1);
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 
-    float best = 0.0f;
-    int best_i = 8 * lane;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float ax = fabsf(v[j]);
-        if (ax > best) { best = ax; best_i = 8 * lane + j; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
-    }
-    // signed value at the winning index
-    float cand = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) if ((best_i & 7) == j) cand = v[j];
-    const float vmax = __shfl_sync(0xffffffffu, cand, best_i >> 3);
-
-    uint8_t *out = y + blk * Q8K_BYTES;
-    if (best == 0.0f) {
-        if (lane == 0) *reinterpret_cast<float *>(out) = 0.0f;
-        reinterpret_cast<uint32_t *>(out + 4)[2 * lane] = 0u;
-        reinterpret_cast<uint32_t *>(out + 4)[2 * lane + 1] = 0u;
-        if (lane < 8) reinterpret_cast<uint32_t *>(out + 260)[lane] = 0u;
-        return;
-    }
-    const float iscale = __fdiv_rn(-127.0f, vmax);
-    int q[8], s = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        int r = __float2int_rn(__fmul_rn(iscale, v[j]));
-        r = max(-128, min(127, r));
-        q[j] = r;
-        s += r;
-    }
-    const uint32_t w0 = (q[0] & 255) | ((q[1] & 255) << 8) | ((q[2] & 255) << 16) | ((uint32_t)(q[3] & 255) << 24);
-    const uint32_t w1 = (q[4] & 255) | ((q[5] & 255) << 8) | ((q[6] & 255) << 16) | ((uint32_t)(q[7] & 255) << 24);
-    reinterpret_cast<uint32_t *>(out + 4)[2 * lane] = w0;
-    reinterpret_cast<uint32_t *>(out + 4)[2 * lane + 1] = w1;
-    s += __shfl_xor_sync(0xffffffffu, s, 1);   // 16-element sum lives in both lanes of a pair
-    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(out + 260)[lane >> 1] = (int16_t)s;
-    if (lane == 0) *reinterpret_cast<float *>(out) = __fdiv_rn(1.0f, iscale);
+    quantize_block_q8k(v, y + blk * Q8K_BYTES, lane);
 }
 
 // One warp per 32-element block; lane l owns element l.
@@ -102,8 +65,7 @@ extern "C" int ckb200_dev_quantize_q8_k(const float *x, void *y, int rows, int k
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     const long long nblocks = (long long)rows * (k / ckb::QK_K);
     const unsigned grid = (unsigned)((nblocks + 3) / 4);
-    ckb::quantize_q8_k_kernel<<<grid, 128, 0, ckb_stream(stream)>>>(x, (uint8_t *)y, nblocks);
-    return ckb_check_launch("quantize_q8_k");
+    return ckb::launch_pdl("quantize_q8_k", ckb::quantize_q8_k_kernel, dim3(grid), dim3(128), 0, ckb_stream(stream), x, (uint8_t *)y, nblocks);
 }
 
 extern "C" int ckb200_dev_quantize_q8_0(const float *x, void *y, int rows, int k, void *stream)

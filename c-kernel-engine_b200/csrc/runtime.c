@@ -205,6 +205,20 @@ const void *ckb200_device_ptr(const void *host_ptr)
     return out;
 }
 
+int ckb200_copy_to_device(void *dev, const void *host, size_t bytes)
+{
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    cudaStreamSynchronize(g.stream);
+    return ckb_check_cuda((int)cudaMemcpy(dev, host, bytes, cudaMemcpyHostToDevice), "copy_to_device");
+}
+
+int ckb200_copy_to_host(void *host, const void *dev, size_t bytes)
+{
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    cudaStreamSynchronize(g.stream);
+    return ckb_check_cuda((int)cudaMemcpy(host, dev, bytes, cudaMemcpyDeviceToHost), "copy_to_host");
+}
+
 void *ckb200_host_alloc(size_t bytes)
 {
     void *p = NULL;

@@ -54,6 +54,10 @@ int ckb200_unregister_weights(const void *host_ptr);
 void ckb200_unregister_all(void);
 const void *ckb200_device_ptr(const void *host_ptr);   /* NULL if not inside a registered range */
 
+/* Synchronous copies between host memory and device pointers handed out by this library. */
+int ckb200_copy_to_device(void *dev, const void *host, size_t bytes);
+int ckb200_copy_to_host(void *host, const void *dev, size_t bytes);
+
 /* Pinned host memory for callers that want the host<->device copies to run at full PCIe rate. */
 void *ckb200_host_alloc(size_t bytes);
 void ckb200_host_free(void *p);
@@ -143,6 +147,24 @@ int ckb200_dev_embedding_forward_q6_k(const int32_t *ids, int count, int vocab, 
                                       float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
 int ckb200_dev_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
                                       float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
+
+/* ------------------------------------------------------------------ fused glue of a device-resident step
+ * Each merges ops that the reference's generated decode function issues back to back
+ * (version/v7/scripts/codegen_v7.py:569-931). */
+/* x += delta (delta may be NULL); out_q8 = quantize_row_q8_k(rmsnorm_forward(x)); norm_out (optional) = fp32 rows */
+int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const float *gamma, void *out_q8, float *norm_out, int tokens,
+                               int d_model, int aligned_embed_dim, float eps, void *stream);
+/* out_q8 = quantize_row_q8_k(swiglu_forward(gate_up)) */
+int ckb200_dev_swiglu_q8k(const float *gate_up, void *out_q8, int tokens, int dim, void *stream);
+/* rope_forward_qk on q and k of one token per sequence, then kv_cache_store at *pos_dev */
+int ckb200_dev_rope_kv_store(float *q, const float *k, const float *v, float *k_cache, float *v_cache, const float *cos_cache,
+                             const float *sin_cache, const int *pos_dev, int batch, int num_heads, int num_kv_heads,
+                             int head_dim, int max_seq_len, long long kv_batch_stride, void *stream);
+int ckb200_dev_advance_pos(int *pos_dev, void *stream);                       /* model->pos++ on the device */
+int ckb200_dev_add_inplace(float *x, const float *delta, long long n, void *stream);
+/* synthetic data generated on the device (benchmarks of shapes too large to build on the host) */
+int ckb200_dev_fill_blocks(void *w, long long nblocks, int fmt, unsigned long long seed, void *stream);
+int ckb200_dev_fill_normal(float *x, long long n, int mode, unsigned long long seed, void *stream);
 
 #ifdef __cplusplus
 }

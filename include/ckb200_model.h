@@ -1,0 +1,69 @@
+/*
+ * ckb200_model.h - device-resident decode step executor.
+ *
+ * Runs the op list that the reference's generated ck_decode() issues (version/v7/scripts/codegen_v7.py:886-931;
+ * layer template version/v7/templates/qwen2.json:95-110) for a Llama/Qwen-style decoder, with weights, KV
+ * cache, activations and the position counter resident in HBM and the whole step captured in one CUDA
+ * graph.  It is the device-side counterpart of the reference's ck_model_decode(token, logits)
+ * (codegen_v7.py:1384-1390): one call = one token per sequence.
+ *
+ * Shapes come from a config struct instead of generated macros; tensors are uploaded one by one (or
+ * filled with synthetic data on the device for benchmarks) in the reference's own block formats.
+ */
+#ifndef CKB200_MODEL_H
+#define CKB200_MODEL_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* weight block formats (values of the fmt_* fields) */
+enum { CKB_FMT_Q4_K = 0, CKB_FMT_Q6_K = 1, CKB_FMT_Q8_0 = 2 };
+
+/* per-layer tensors; the same order as the reference's layer weight list (ln1, wq, wk, wv, wo, ln2, w1, w2) */
+enum {
+    CKB_T_LN1 = 0, CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_LN2, CKB_T_W1, CKB_T_W2, CKB_T_PER_LAYER,
+    /* model-level tensors, addressed with layer = -1 */
+    CKB_T_FINAL_GAMMA = 100, CKB_T_LM_HEAD = 101, CKB_T_EMBEDDING = 102
+};
+
+/* Mirrors CKModelConfig (include/ck_model_api.h:26-40) plus what the generated code has as macros. */
+typedef struct {
+    int embed_dim, num_heads, num_kv_heads, head_dim, intermediate_size, num_layers, vocab_size, max_seq_len;
+    float rms_eps, rope_theta;
+    int fmt_q, fmt_k, fmt_v, fmt_o, fmt_gate_up, fmt_down, fmt_lm_head, fmt_embedding;
+    int tie_embeddings;      /* token embedding table = LM head matrix */
+    int batch;               /* independent sequences advanced per step (all at the same position) */
+    int tp_rank, tp_size;    /* tensor-parallel shard held by this process (tp_size <= 1: whole model) */
+} CKB200ModelConfig;
+
+typedef struct CKB200Model CKB200Model;
+
+/* sum `count` floats in place over all tensor-parallel ranks, enqueued on `stream`; returns 0 on success */
+typedef int (*ckb200_allreduce_fn)(void *ctx, float *buf, size_t count, void *stream);
+
+CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg);          /* NULL on failure (see ckb200_last_error) */
+void ckb200_model_free(CKB200Model *m);
+size_t ckb200_model_tensor_bytes(CKB200Model *m, int layer, int which);
+void *ckb200_model_tensor_ptr(CKB200Model *m, int layer, int which);     /* device pointer */
+int ckb200_model_tensor_shape(CKB200Model *m, int layer, int which, int *rows, int *cols, int *fmt);
+int ckb200_model_upload_tensor(CKB200Model *m, int layer, int which, const void *host, size_t bytes);
+int ckb200_model_fill_synthetic(CKB200Model *m, unsigned long long seed);            /* random blocks, gamma = 1 + 0.1 N(0,1) */
+int ckb200_model_fill_kv_synthetic(CKB200Model *m, int tokens, unsigned long long seed);   /* N(0,1) cache, pos = tokens */
+int ckb200_model_set_pos(CKB200Model *m, int pos);
+int ckb200_model_get_pos(CKB200Model *m);
+void ckb200_model_set_allreduce(CKB200Model *m, ckb200_allreduce_fn fn, void *ctx);
+/* one decode step: tokens[batch] in, logits[batch][vocab] out (logits_host may be NULL: no copy, no sync) */
+int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_host);
+int ckb200_model_decode_repeat(CKB200Model *m, int steps);              /* re-launch the captured step `steps` times */
+float *ckb200_model_logits_device(CKB200Model *m);
+void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v);       /* [batch][Hkv][max_seq][head_dim] fp32 */
+size_t ckb200_model_weight_bytes(CKB200Model *m);                        /* quantised bytes one step streams */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

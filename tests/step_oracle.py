@@ -1,0 +1,140 @@
+"""CPU decode step assembled from the oracle's kernels in the order the reference's generated
+ck_decode() issues them (version/v7/scripts/codegen_v7.py:886-931); the checker for the
+device-resident step executor.  One sequence at a time; weights and caches are numpy arrays."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+import cases
+
+synth = cases.synth
+FMT = {0: "q4_k", 1: "q6_k", 2: "q8_0"}
+T = dict(LN1=0, WQ=1, WK=2, WV=3, WO=4, LN2=5, W1=6, W2=7, FINAL_GAMMA=100, LM_HEAD=101, EMBEDDING=102)
+
+
+def round256(v):
+    return (v + 255) // 256 * 256
+
+
+def cols_for(fmt, k):
+    return (k + 31) // 32 * 32 if fmt == 2 else round256(k)
+
+
+class CpuModel:
+    """Whole (unsharded) model on the host: random weights in the reference's block formats."""
+
+    def __init__(self, cfg: dict, seed: int):
+        self.cfg = cfg
+        D, H, Hkv, d, I, L, V = (cfg[k] for k in ("embed_dim", "num_heads", "num_kv_heads", "head_dim", "intermediate_size", "num_layers", "vocab_size"))
+        self.Da, self.A, self.Aa = round256(D), H * d, round256(H * d)
+        rng = np.random.default_rng(seed)
+        s = seed * 100
+        self.layers = []
+        for _ in range(L):
+            lay = {}
+            lay["LN1"] = (1.0 + 0.1 * rng.standard_normal(self.Da)).astype(np.float32)
+            lay["LN2"] = (1.0 + 0.1 * rng.standard_normal(self.Da)).astype(np.float32)
+            for name, fmt, rows, k in (("WQ", cfg["fmt_q"], H * d, D), ("WK", cfg["fmt_k"], Hkv * d, D), ("WV", cfg["fmt_v"], Hkv * d, D),
+                                       ("WO", cfg["fmt_o"], D, H * d), ("W1", cfg["fmt_gate_up"], 2 * I, D), ("W2", cfg["fmt_down"], D, I)):
+                s += 1
+                lay[name] = (fmt, rows, cols_for(fmt, k), synth.make_weights(FMT[fmt], rows, cols_for(fmt, k), seed=s))
+            self.layers.append(lay)
+        self.final_gamma = (1.0 + 0.1 * rng.standard_normal(self.Da)).astype(np.float32)
+        fmt = cfg["fmt_lm_head"]
+        self.lm_head = (fmt, V, cols_for(fmt, D), synth.make_weights(FMT[fmt], V, cols_for(fmt, D), seed=s + 1))
+        S = cfg["max_seq_len"]
+        self.kc = np.zeros((L, Hkv, S, d), np.float32)
+        self.vc = np.zeros((L, Hkv, S, d), np.float32)
+
+    def prefill_kv(self, tokens: int, seed: int):
+        rng = np.random.default_rng(seed)
+        self.kc[:, :, :tokens] = rng.standard_normal(self.kc[:, :, :tokens].shape).astype(np.float32)
+        self.vc[:, :, :tokens] = rng.standard_normal(self.vc[:, :, :tokens].shape).astype(np.float32)
+
+    def _matvec(self, lib, w, x_row):
+        fmt, rows, cols, data = w
+        x = np.zeros(cols, np.float32)
+        x[:min(cols, x_row.size)] = x_row[:cols]
+        xq = cases.quantize_act(lib, "oracle_", FMT[fmt], x)
+        return cases.gemv(lib, "oracle_", FMT[fmt], data, xq, rows, cols)
+
+    def decode(self, lib, token: int, pos: int) -> np.ndarray:
+        c = self.cfg
+        D, H, Hkv, d, I = c["embed_dim"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["intermediate_size"]
+        efmt, _, ecols, edata = self.lm_head
+        x = cases.embedding(lib, "oracle_", FMT[efmt], [token], edata, c["vocab_size"], D, self.Da)[0].copy()
+        cos, sin = cases.rope_cache(lib, "oracle_", c["max_seq_len"], d, c["rope_theta"])
+        for l, lay in enumerate(self.layers):
+            h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN1"], D, c["rms_eps"])[0]
+            q = self._matvec(lib, lay["WQ"], h).reshape(H, 1, d).copy()
+            k = self._matvec(lib, lay["WK"], h).reshape(Hkv, 1, d).copy()
+            v = self._matvec(lib, lay["WV"], h).reshape(Hkv, d).copy()
+            cases.rope_qk(lib, "oracle_", q, k, cos, sin, pos)
+            cases.kv_cache_store(lib, "oracle_", self.kc[l], self.vc[l], np.ascontiguousarray(k.reshape(Hkv, d)), v, pos)
+            att = cases.attention_decode(lib, "oracle_", np.ascontiguousarray(q.reshape(H, d)), self.kc[l], self.vc[l], pos + 1).reshape(-1)
+            o = self._matvec(lib, lay["WO"], att)
+            x[:D] += o
+            h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN2"], D, c["rms_eps"])[0]
+            gu = self._matvec(lib, lay["W1"], h)
+            mm = cases.swiglu(lib, "oracle_", gu.reshape(1, -1), I)[0]
+            x[:D] += self._matvec(lib, lay["W2"], mm)
+        h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), self.final_gamma, D, c["rms_eps"])[0]
+        return self._matvec(lib, self.lm_head, h)
+
+
+class CfgStruct(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("embed_dim", "num_heads", "num_kv_heads", "head_dim", "intermediate_size", "num_layers", "vocab_size", "max_seq_len")] + \
+               [("rms_eps", C.c_float), ("rope_theta", C.c_float)] + \
+               [(n, C.c_int) for n in ("fmt_q", "fmt_k", "fmt_v", "fmt_o", "fmt_gate_up", "fmt_down", "fmt_lm_head", "fmt_embedding", "tie_embeddings", "batch", "tp_rank", "tp_size")]
+
+
+def make_cfg(cfg: dict, batch=1, tp_rank=0, tp_size=1) -> CfgStruct:
+    s = CfgStruct()
+    for k, v in cfg.items():
+        setattr(s, k, v)
+    s.fmt_embedding = cfg["fmt_lm_head"]
+    s.tie_embeddings = 1
+    s.batch, s.tp_rank, s.tp_size = batch, tp_rank, tp_size
+    return s
+
+
+def bind_model_api(lib):
+    lib.ckb200_model_create.restype = C.c_void_p
+    lib.ckb200_model_create.argtypes = [C.POINTER(CfgStruct)]
+    lib.ckb200_model_free.argtypes = [C.c_void_p]
+    lib.ckb200_model_free.restype = None
+    lib.ckb200_model_upload_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
+    lib.ckb200_model_tensor_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    lib.ckb200_model_tensor_bytes.restype = C.c_size_t
+    lib.ckb200_model_kv_device.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    lib.ckb200_model_kv_device.restype = C.c_void_p
+    lib.ckb200_model_set_pos.argtypes = [C.c_void_p, C.c_int]
+    lib.ckb200_model_get_pos.argtypes = [C.c_void_p]
+    lib.ckb200_model_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ckb200_model_decode_repeat.argtypes = [C.c_void_p, C.c_int]
+    lib.ckb200_model_fill_synthetic.argtypes = [C.c_void_p, C.c_ulonglong]
+    lib.ckb200_model_fill_kv_synthetic.argtypes = [C.c_void_p, C.c_int, C.c_ulonglong]
+    lib.ckb200_model_weight_bytes.argtypes = [C.c_void_p]
+    lib.ckb200_model_weight_bytes.restype = C.c_size_t
+    lib.ckb200_copy_to_device.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    lib.ckb200_copy_to_host.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+
+
+def upload_whole_model(lib, handle, cpu: CpuModel, batch: int):
+    """tp_size == 1: tensors go up as they are; the KV cache of sequence 0 is replicated to every sequence."""
+    for l, lay in enumerate(cpu.layers):
+        for name in ("LN1", "LN2"):
+            assert lib.ckb200_model_upload_tensor(handle, l, T[name], cases.vptr(lay[name]), lay[name].nbytes) == 0
+        for name in ("WQ", "WK", "WV", "WO", "W1", "W2"):
+            data = lay[name][3]
+            assert lib.ckb200_model_upload_tensor(handle, l, T[name], cases.vptr(data), data.nbytes) == 0, (l, name)
+    assert lib.ckb200_model_upload_tensor(handle, -1, T["FINAL_GAMMA"], cases.vptr(cpu.final_gamma), cpu.final_gamma.nbytes) == 0
+    assert lib.ckb200_model_upload_tensor(handle, -1, T["LM_HEAD"], cases.vptr(cpu.lm_head[3]), cpu.lm_head[3].nbytes) == 0
+    for l in range(len(cpu.layers)):
+        for is_v, cache in ((0, cpu.kc), (1, cpu.vc)):
+            base = lib.ckb200_model_kv_device(handle, l, is_v)
+            slab = np.ascontiguousarray(cache[l])
+            for b in range(batch):
+                assert lib.ckb200_copy_to_device(C.c_void_p(base + b * slab.nbytes), cases.vptr(slab), slab.nbytes) == 0

@@ -1,0 +1,74 @@
+"""Full decode steps on the device-resident executor against the CPU step built from the oracle's
+kernels: logits cosine >= 0.9999 (the contract for whole steps) and a tight max-abs bound."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+import step_oracle as so
+
+pytestmark = pytest.mark.gpu
+
+MINI_QWEN = dict(embed_dim=384, num_heads=6, num_kv_heads=2, head_dim=64, intermediate_size=768, num_layers=3, vocab_size=1000,
+                 max_seq_len=96, rms_eps=1e-6, rope_theta=1.0e6, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
+MINI_LLAMA = dict(embed_dim=512, num_heads=4, num_kv_heads=2, head_dim=128, intermediate_size=1024, num_layers=2, vocab_size=777,
+                  max_seq_len=64, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+
+@pytest.mark.parametrize("cfg,batch,use_graph", [(MINI_QWEN, 1, 1), (MINI_QWEN, 1, 0), (MINI_LLAMA, 2, 1)])
+def test_decode_steps_match_cpu_step(ck, orc, cfg, batch, use_graph):
+    so.bind_model_api(ck)
+    ck.ckb200_tune_set(b"model_graph", use_graph)
+    cpu = so.CpuModel(cfg, seed=7)
+    start = 40
+    cpu.prefill_kv(start, seed=8)
+    st = so.make_cfg(cfg, batch=batch)
+    handle = ck.ckb200_model_create(C.byref(st))
+    assert handle, ck.ckb200_last_error_message()
+    try:
+        so.upload_whole_model(ck, handle, cpu, batch)
+        assert ck.ckb200_model_set_pos(handle, start) == 0
+        V = cfg["vocab_size"]
+        tokens = [5, 17, 123]
+        for step, tok in enumerate(tokens):
+            want = cpu.decode(orc, tok, start + step)
+            ids = np.full(batch, tok, dtype=np.int32)
+            logits = np.full((batch, V), np.nan, dtype=np.float32)
+            assert ck.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, ck.ckb200_last_error_message()
+            for b in range(batch):
+                cos = cosine(logits[b], want)
+                err = float(np.max(np.abs(logits[b] - want))) / float(np.max(np.abs(want)))
+                assert cos >= 0.9999, (step, b, cos)
+                assert err < 5e-3, (step, b, err)
+            assert ck.ckb200_model_get_pos(handle) == start + step + 1
+    finally:
+        ck.ckb200_model_free(handle)
+        ck.ckb200_tune_set(b"model_graph", 1)
+
+
+def test_synthetic_fill_and_repeat(ck):
+    """Device-side synthetic weights: the step runs, logits are finite, the position advances per replay."""
+    so.bind_model_api(ck)
+    st = so.make_cfg(MINI_QWEN, batch=1)
+    handle = ck.ckb200_model_create(C.byref(st))
+    assert handle
+    try:
+        assert ck.ckb200_model_fill_synthetic(handle, 3) == 0
+        assert ck.ckb200_model_fill_kv_synthetic(handle, 20, 4) == 0
+        ids = np.array([11], dtype=np.int32)
+        logits = np.zeros((1, MINI_QWEN["vocab_size"]), np.float32)
+        assert ck.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0
+        assert np.isfinite(logits).all() and float(np.abs(logits).max()) > 0
+        assert ck.ckb200_model_decode_repeat(handle, 5) == 0
+        assert ck.ckb200_synchronize() == 0
+        assert ck.ckb200_model_get_pos(handle) == 26
+    finally:
+        ck.ckb200_model_free(handle)

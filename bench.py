@@ -194,6 +194,64 @@ def cpu_baseline_sample(budget_s: float = 12.0):
             "sample": "Q4_K sweep shapes, repetitions " + " ".join(used) + " (up to 3 s or 50 runs each, after one warm-up)"}
 
 
+# ------------------------------------------------------------------------------------- decode steps
+
+QWEN2_05B = dict(embed_dim=896, num_heads=14, num_kv_heads=2, head_dim=64, intermediate_size=4864, num_layers=24, vocab_size=151936,
+                 max_seq_len=2048, rms_eps=1e-6, rope_theta=1.0e6, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
+LLAMA3_70B = dict(embed_dim=8192, num_heads=64, num_kv_heads=8, head_dim=128, intermediate_size=28672, num_layers=80, vocab_size=128256,
+                  max_seq_len=4352, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
+
+
+def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1):
+    """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+    import step_oracle as so
+
+    so.bind_model_api(lib)
+    st = so.make_cfg(cfg, batch=batch)
+    handle = lib.ckb200_model_create(C.byref(st))
+    if not handle:
+        msg = lib.ckb200_last_error_message().decode()
+        lib.ckb200_clear_error()
+        return {"error": msg}
+    try:
+        assert lib.ckb200_model_fill_synthetic(handle, 1) == 0
+        assert lib.ckb200_model_fill_kv_synthetic(handle, ctx, 2) == 0
+        ids = np.full(batch, 11, dtype=np.int32)
+        launches0 = lib.ckb200_launch_count()
+        assert lib.ckb200_model_decode(handle, cases.vptr(ids), None) == 0          # eager warm-up + capture + first replay
+        launches = (lib.ckb200_launch_count() - launches0) // 2
+        assert lib.ckb200_model_decode_repeat(handle, 3) == 0
+        assert lib.ckb200_synchronize() == 0
+        lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        assert lib.ckb200_model_set_pos(handle, ctx) == 0
+        e0.record(lstream)
+        assert lib.ckb200_model_decode_repeat(handle, steps) == 0
+        e1.record(lstream)
+        lstream.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        wbytes = lib.ckb200_model_weight_bytes(handle)
+        kv_bytes = 2 * cfg["num_layers"] * cfg["num_kv_heads"] * (ctx + steps // 2) * cfg["head_dim"] * 4 * batch
+        gbs = (wbytes + kv_bytes) / ms / 1e6
+        # end to end: token id from the host, logits back to the host, every step
+        logits = np.zeros((batch, cfg["vocab_size"]), np.float32)
+        assert lib.ckb200_model_set_pos(handle, ctx) == 0
+        t0 = time.perf_counter()
+        n_e2e = max(5, steps // 2)
+        for _ in range(n_e2e):
+            assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0
+        e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
+        return {"model_shape": name, "batch": batch, "context": ctx, "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
+                "weight_bytes": int(wbytes), "kv_bytes": int(kv_bytes), "hbm_gbs": gbs, "frac_of_measured_peak": gbs / peak,
+                "e2e_tok_s": batch * 1e3 / e2e_ms, "e2e_ms_per_token": e2e_ms}
+    finally:
+        lib.ckb200_model_free(handle)
+
+
 # ------------------------------------------------------------------------------------- CUDA arm
 
 def run_cuda(args, rank: int, world: int, local_rank: int):
@@ -375,6 +433,13 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         if args.detail:
             line["detail"] = {f: {"gbs": results[f]["step_bytes"] * args.steps / results[f]["ms"] / 1e6, "per_shape": results[f]["per_shape"]}
                               for f in results}
+        if world == 1 and not args.no_decode:
+            try:
+                line["decode"] = [decode_bench(lib, "Qwen2-0.5B shape, Q4_K_M mix", QWEN2_05B, 1024, 200, peak),
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU", LLAMA3_70B, 4096, 10, peak)]
+            except Exception as exc:                      # the headline metric above must survive a failure here
+                line["decode"] = {"error": repr(exc)}
+                lib.ckb200_clear_error()
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line), flush=True)
@@ -391,6 +456,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

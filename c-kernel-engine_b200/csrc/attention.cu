@@ -9,11 +9,11 @@
 // q/out rows and cache slabs (strides given in floats).
 //
 // Fast path (ad = 64 or 128, group = H/Hkv <= 8): one CTA per (context split, kv head, sequence).
-// A warp takes 4 keys per step, 8 lanes per key; each lane owns ad/8 dimensions as float4 pieces so
-// that the 8 lanes read 128 contiguous bytes.  K and V rows are read ONCE for all `group` Q heads
-// that share the kv head.  The group partial dots are reduced with a transposing butterfly (7
-// shuffles for 8 heads); each lane keeps running (max, sum) for every head and `group` output
-// accumulators for its dimensions.  Splits write (max, sum, unnormalised out) to a scratch buffer
+// A warp takes 2 keys per step, 16 lanes per key; each lane owns ad/16 dimensions as float4 pieces so
+// that 16 lanes read 256 contiguous bytes, and the rows of the next step are loaded before the current
+// step is computed.  K and V rows are read ONCE for all `group` Q heads that share the kv head.  The
+// group partial dots are reduced with a transposing butterfly (8 shuffles for 8 heads); each lane keeps
+// running (max, sum) for every head and `group` output accumulators for its dimensions.  Splits write (max, sum, unnormalised out) to a scratch buffer
 // and a merge kernel combines them with the exact log-sum-exp rule.
 #include "device_common.cuh"
 #include "launch.h"
@@ -43,10 +43,12 @@ constexpr int ATTN_NW = 4;       // warps per CTA
 template <int AD>
 __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
 {
-    constexpr int C = AD / 32;                 // float4 pieces per lane
+    constexpr int LPK = 16;                    // lanes per key
+    constexpr int C = AD / (4 * LPK);          // float4 pieces per lane (1 for 64, 2 for 128)
+    constexpr int KPI = 32 / LPK;              // keys per warp step
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int sub = lane >> 3, li = lane & 7;
+    const int sub = lane / LPK, li = lane % LPK;
     const int group = p.H / p.Hkv, h0 = kvh * group;   // heads h0 .. h0+group-1 map to kvh (H % Hkv == 0)
 
     __shared__ __align__(16) float q_s[ATTN_G][AD];
@@ -75,16 +77,22 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
         for (int c = 0; c < C; ++c) acc[h][c] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 
-    for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += ATTN_NW * 4) {
-        const int t = t0 + sub;
-        const bool valid = t < t_end;
-        const int tc = valid ? t : t_end - 1;
-        float4 kr[C], vr[C];
+    auto load_kv = [&](float4 (&kr)[C], float4 (&vr)[C], int t) {
+        const int tc = min(t, t_end - 1);
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            kr[c] = __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)tc * AD) + c * 8 + li);
-            vr[c] = __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)tc * AD) + c * 8 + li);
+            kr[c] = __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)tc * AD) + c * LPK + li);
+            vr[c] = __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)tc * AD) + c * LPK + li);
         }
+    };
+
+    float4 kr[C], vr[C], kn[C], vn[C];
+    int t0 = t_begin + warp * KPI;
+    if (t0 < t_end) load_kv(kr, vr, t0 + sub);
+    for (; t0 < t_end; t0 += ATTN_NW * KPI) {
+        const int t = t0 + sub;
+        const bool valid = t < t_end;
+        if (t0 + ATTN_NW * KPI < t_end) load_kv(kn, vn, t + ATTN_NW * KPI);     // next step's rows are in flight during this one
         // partial dots of this lane's dimensions with every head's (pre-scaled) query
         float s[ATTN_G];
 #pragma unroll
@@ -92,7 +100,7 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
             float a = 0.0f;
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[h][(c * 8 + li) * 4]);
+                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[h][(c * LPK + li) * 4]);
                 a = fmaf(qv.x, kr[c].x, a);
                 a = fmaf(qv.y, kr[c].y, a);
                 a = fmaf(qv.z, kr[c].z, a);
@@ -100,7 +108,7 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
             }
             s[h] = a;
         }
-        // transposing butterfly over the 8 lanes of a key: afterwards lane li holds the full dot of head li
+        // transposing butterfly over lane bits 2,1,0, then a plain add over bit 3: lane li ends with head li & 7
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float mine = (li & 4) ? s[j + 4] : s[j], theirs = (li & 4) ? s[j] : s[j + 4];
@@ -115,11 +123,12 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
             const float mine = (li & 1) ? s[1] : s[0], theirs = (li & 1) ? s[0] : s[1];
             s[0] = mine + __shfl_xor_sync(0xffffffffu, theirs, 1);
         }
-        const float score = valid ? s[0] : -INFINITY;     // head li, key t
-        // broadcast each head's score inside the key's 8 lanes, update the running softmax
+        s[0] += __shfl_xor_sync(0xffffffffu, s[0], 8);
+        const float score = valid ? s[0] : -INFINITY;     // head li & 7, key t
+        // broadcast each head's score inside the key's lanes, update the running softmax
 #pragma unroll
         for (int h = 0; h < ATTN_G; ++h) {
-            const float sh = __shfl_sync(0xffffffffu, score, (sub << 3) | h);
+            const float sh = __shfl_sync(0xffffffffu, score, sub * LPK + h);
             if (h < group && sh > -INFINITY) {
                 float pw;
                 if (sh > m[h]) {
@@ -144,13 +153,15 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
                 }
             }
         }
+#pragma unroll
+        for (int c = 0; c < C; ++c) { kr[c] = kn[c]; vr[c] = vn[c]; }
     }
 
-    // merge the 4 key streams of the warp (lanes with the same li: xor 8, xor 16)
+    // merge the key streams of the warp (lanes with the same li)
 #pragma unroll
     for (int h = 0; h < ATTN_G; ++h) {
 #pragma unroll
-        for (int o = 8; o <= 16; o <<= 1) {
+        for (int o = LPK; o < 32; o <<= 1) {
             const float mo = __shfl_xor_sync(0xffffffffu, m[h], o), lo = __shfl_xor_sync(0xffffffffu, l[h], o);
             const float mn = fmaxf(m[h], mo);
             const float ca = m[h] == -INFINITY ? 0.0f : expf(m[h] - mn), cb = mo == -INFINITY ? 0.0f : expf(mo - mn);
@@ -169,7 +180,7 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
 #pragma unroll
         for (int h = 0; h < ATTN_G; ++h) {
 #pragma unroll
-            for (int c = 0; c < C; ++c) *reinterpret_cast<float4 *>(&merge_s[warp][h][(c * 8 + li) * 4]) = acc[h][c];
+            for (int c = 0; c < C; ++c) *reinterpret_cast<float4 *>(&merge_s[warp][h][(c * LPK + li) * 4]) = acc[h][c];
             if (li == 0) { merge_s[warp][h][AD] = m[h]; merge_s[warp][h][AD + 1] = l[h]; }
         }
     }
@@ -200,22 +211,51 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
     }
 }
 
-// out[head][c] = sum_s part[s][c] * exp(m_s - M) / sum_s l_s * exp(m_s - M)
-__global__ void attn_merge_kernel(const float *__restrict__ part, float *__restrict__ out, int splits, int ad)
+// out[head][c] = sum_s part[s][c] * exp(m_s - M) / sum_s l_s * exp(m_s - M); one CTA per head.
+// The per-split factors are computed once into shared memory; the column sums then run over independent loads.
+constexpr int ATTN_MAX_SPLITS = 256;
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict__ part, float *__restrict__ out, int splits, int ad)
 {
+    __shared__ float f_s[ATTN_MAX_SPLITS];
+    __shared__ float red_m[4], red_l[4];
     const size_t head = blockIdx.x;
     const float *src = part + head * splits * (ad + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * (ad + 2) + ad]);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float mloc = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float ms = src[s * (ad + 2) + ad];
+        f_s[s] = ms;
+        mloc = fmaxf(mloc, ms);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if (lane == 0) red_m[warp] = mloc;
+    __syncthreads();
+    float mm = red_m[0];
+    for (int w = 1; w < nw; ++w) mm = fmaxf(mm, red_m[w]);
+    float lloc = 0.0f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float ms = f_s[s];
+        const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
+        f_s[s] = f;
+        lloc += src[s * (ad + 2) + ad + 1] * f;
+    }
+    lloc = group_sum<32>(lloc);
+    if (lane == 0) red_l[warp] = lloc;
+    __syncthreads();
+    float ll = 0.0f;
+    for (int w = 0; w < nw; ++w) ll += red_l[w];
+    const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
     for (int c = threadIdx.x; c < ad; c += blockDim.x) {
-        float ll = 0.0f, a = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = src[s * (ad + 2) + ad];
-            const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
-            ll += src[s * (ad + 2) + ad + 1] * f;
-            a += src[s * (ad + 2) + c] * f;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float v0 = src[(s + 0) * (ad + 2) + c], v1 = src[(s + 1) * (ad + 2) + c];
+            const float v2 = src[(s + 2) * (ad + 2) + c], v3 = src[(s + 3) * (ad + 2) + c];
+            a0 = fmaf(v0, f_s[s], a0); a1 = fmaf(v1, f_s[s + 1], a1); a2 = fmaf(v2, f_s[s + 2], a2); a3 = fmaf(v3, f_s[s + 3], a3);
         }
-        out[head * ad + c] = ll > 0.0f ? a / ll : 0.0f;
+        for (; s < splits; ++s) a0 = fmaf(src[s * (ad + 2) + c], f_s[s], a0);
+        out[head * ad + c] = ((a0 + a1) + (a2 + a3)) * inv;
     }
 }
 
@@ -333,6 +373,7 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
         return ckb_check_launch("attn_decode_generic");
     }
     if (splits < 1) splits = 1;
+    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
     if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
     p.splits = splits;
     const dim3 grid(splits, num_kv_heads, batch);
@@ -340,7 +381,7 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     else attn_decode_kernel<128><<<grid, ATTN_NW * 32, 0, st>>>(p);
     if (ckb_check_launch("attn_decode")) return CKB_ERR_CUDA;
     if (splits > 1) {
-        attn_merge_kernel<<<batch * num_heads, aligned_head_dim < 128 ? 64 : 128, 0, st>>>(scratch, out, splits, aligned_head_dim);
+        attn_merge_kernel<<<batch * num_heads, 128, 0, st>>>(scratch, out, splits, aligned_head_dim);
         return ckb_check_launch("attn_merge");
     }
     return 0;
@@ -445,6 +486,7 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
         attn_decode_generic_kernel<<<dim3(num_heads, batch), 128, 0, st>>>(p);
         return ckb_check_launch("attn_decode_generic");
     }
+    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
     const size_t need = splits > 1 ? (size_t)batch * num_heads * splits * (aligned_head_dim + 2) * sizeof(float) : 0;
     if (need > CKB_ATTN_STATIC_SCRATCH_BYTES)
         return ckb_fail(CKB_ERR_LIMIT, "attention decode (static scratch): %zu bytes of partials for batch %d x %d heads x %d splits "

@@ -432,10 +432,9 @@ extern "C" int ckb200_dev_gemv_q4_k_q8_k(float *y, const void *W, const void *xq
     int v = ckb_tune_get("gemv_q4_k", 0);
     if (v == 0) {
         // measured on B200 over the benchmark and decode shapes: few rows -> activations in registers
-        // (no staging, no barrier); very long rows -> same with two rows per step; otherwise the
-        // shared-activation kernel with L1-allocating loads
+        // (every warp bound to one pass of the row); otherwise the shared-activation pair kernel with
+        // L1-allocating loads, two rows per step unless rows are a single pass
         if (M <= 2048 && nb <= 128) v = 32;
-        else if (nb >= 56 && nb <= 128 && M <= 16384) v = 33;
         else v = nb <= 4 ? 22 : 23;
     }
     switch (v) {

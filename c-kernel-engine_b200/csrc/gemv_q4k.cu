@@ -38,19 +38,32 @@ __device__ __forceinline__ Q4pX q4p_stage_x(const uint8_t *xg, int nb, uint8_t *
     int8_t *lo = reinterpret_cast<int8_t *>(smem + nb * (Q4P_SLOTS * 16 + 4));
     int8_t *hi = lo + nb * 8;
     const uint32_t *src = reinterpret_cast<const uint32_t *>(xg);
-    for (int i = threadIdx.x; i < nb * 73; i += blockDim.x) {
-        const int b = i / 73, w = i - b * 73;
-        const uint32_t v = __ldcg(src + i);     // through L2: the producer may overlap this kernel (programmatic launch)
-        if (w == 0) {
-            xd[b] = __uint_as_float(v);
-        } else if (w <= 64) {
-            xq[b * Q4P_SLOTS * 4 + (w - 1)] = v;
-        } else {
-            const int j = w - 65;                                  // 32-element sub-block
-            const int s = (int)(short)(v & 0xffffu) + (int)(short)(v >> 16);
-            const int p = (j >> 1) & 1, byte = (j & 1) | ((j >> 2) << 1);
-            lo[(b * 2 + p) * 4 + byte] = (int8_t)(s & 127);
-            hi[(b * 2 + p) * 4 + byte] = (int8_t)(s >> 7);
+    // eight independent loads per thread are issued before the first one is used: the staging costs about
+    // one L2 round trip, which matters because it sits between the dependency wait and the first multiply
+    const int total = nb * 73;
+    for (int base = 0; base < total; base += 8 * blockDim.x) {
+        uint32_t v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * blockDim.x + threadIdx.x;
+            v[u] = i < total ? __ldcg(src + i) : 0u;       // through L2: the producer may overlap this kernel (programmatic launch)
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * blockDim.x + threadIdx.x;
+            if (i >= total) break;
+            const int b = i / 73, w = i - b * 73;
+            if (w == 0) {
+                xd[b] = __uint_as_float(v[u]);
+            } else if (w <= 64) {
+                xq[b * Q4P_SLOTS * 4 + (w - 1)] = v[u];
+            } else {
+                const int j = w - 65;                                  // 32-element sub-block
+                const int sum = (int)(short)(v[u] & 0xffffu) + (int)(short)(v[u] >> 16);
+                const int p = (j >> 1) & 1, byte = (j & 1) | ((j >> 2) << 1);
+                lo[(b * 2 + p) * 4 + byte] = (int8_t)(sum & 127);
+                hi[(b * 2 + p) * 4 + byte] = (int8_t)(sum >> 7);
+            }
         }
     }
     Q4pX r;

@@ -3,7 +3,7 @@
 // Same work split as gemv_q4k.cu (two lanes per superblock; lane p takes quarters p and p+2), but
 // every warp is bound to ONE pass over the row (a fixed set of 16 superblocks), so the 64 activation
 // bytes, the Q8_K scale and the four sub-block sums a lane needs never change: they are loaded once
-// from global memory into registers and the inner loop touches no shared memory at all.  A row
+// (through one shared-memory copy per CTA) into registers and the inner loop touches no shared memory at all.  A row
 // longer than one pass is split over `npass` warps of the CTA; their partial sums meet in a small
 // shared tile that is summed in a fixed order (deterministic) once per row tile.
 //
@@ -22,23 +22,43 @@ struct XrX {                 // one lane's activations: quarter p and quarter p+
     uint32_t lo4, hi4;       // sub-block sums {2p, 2p+1, 2p+4, 2p+5} split as 128*hi + lo, 4 x s8 each
 };
 
-// activations were written by the previous kernel, which may overlap this one under programmatic launch:
-// they are read through L2 (__ldcg), never through the non-coherent read-only path
-__device__ __forceinline__ uint4 ldg4w(const uint32_t *p) { return make_uint4(__ldcg(p), __ldcg(p + 1), __ldcg(p + 2), __ldcg(p + 3)); }
+// The activation vector was written by the previous kernel, which may overlap this one under programmatic
+// launch, so it must come through L2 (__ldcg), never the non-coherent read-only path.  Letting every lane of
+// every CTA fetch its slice from L2 hammers the few L2 lines that hold the vector, so the CTA copies the
+// raw blocks into shared memory once (one L2 read per word per CTA) and lanes pick their slice from there.
+__device__ __forceinline__ void xr_stage_raw(const uint8_t *xg, int nb, uint32_t *raw)
+{
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(xg);
+    const int total = nb * 73;
+    for (int base = 0; base < total; base += 8 * blockDim.x) {
+        uint32_t v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * blockDim.x + threadIdx.x;
+            v[u] = i < total ? __ldcg(src + i) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * blockDim.x + threadIdx.x;
+            if (i < total) raw[i] = v[u];
+        }
+    }
+}
+__device__ __forceinline__ uint4 ldg4w(const uint32_t *p) { return make_uint4(p[0], p[1], p[2], p[3]); }
 
-__device__ __forceinline__ XrX xr_load_x(const uint8_t *xg, int b, int p)
+__device__ __forceinline__ XrX xr_load_x(const uint32_t *raw, int b, int p)
 {
     XrX x;
-    const uint32_t *blk = reinterpret_cast<const uint32_t *>(xg + (size_t)b * Q8K_BYTES);   // 4-byte aligned
+    const uint32_t *blk = raw + b * 73;                              // block b of the staged vector (73 words each)
     const uint32_t *qa = blk + 1 + 16 * p, *qb = blk + 1 + 16 * (p + 2);
     x.al0 = ldg4w(qa); x.al1 = ldg4w(qa + 4); x.ah0 = ldg4w(qa + 8); x.ah1 = ldg4w(qa + 12);
     x.bl0 = ldg4w(qb); x.bl1 = ldg4w(qb + 4); x.bh0 = ldg4w(qb + 8); x.bh1 = ldg4w(qb + 12);
-    x.d = __uint_as_float(__ldcg(blk));
+    x.d = __uint_as_float(blk[0]);
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int j = 2 * p + (i & 1) + 4 * (i >> 1);                // sub-block of byte i
-        const uint32_t v = __ldcg(blk + 65 + j);
+        const uint32_t v = blk[65 + j];
         const int s = (int)(short)(v & 0xffffu) + (int)(short)(v >> 16);
         lo |= (uint32_t)(s & 127) << (8 * i);
         hi |= (uint32_t)((s >> 7) & 255) << (8 * i);
@@ -91,6 +111,7 @@ __global__ void __launch_bounds__(256) gemv_q4k_xreg_kernel(const uint8_t *__res
 {
     constexpr int SPP = G / 2, RPW = (32 / G) * R;
     __shared__ float part[8][128];                                   // [pass][row in tile], used only when npass > 1
+    extern __shared__ __align__(16) uint32_t xraw[];                 // nb * 73 words: the Q8_K vector as stored
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int li = lane % G, sub = lane / G, p = li & 1;
     const int pw = warp % npass, wr = warp / npass;
@@ -127,7 +148,9 @@ __global__ void __launch_bounds__(256) gemv_q4k_xreg_kernel(const uint8_t *__res
     if (tile < ntiles) load_item(cur, tile, 0);          // weights are immutable: prefetch before the dependency wait
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const XrX x = xr_load_x(xg, b, p);
+    xr_stage_raw(xg, nb, xraw);
+    __syncthreads();
+    const XrX x = xr_load_x(xraw, b, p);
 
     while (tile < ntiles) {
         int ntile = tile, nit = it + 1;
@@ -183,7 +206,7 @@ int launch_xreg(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     auto kernel = gemv_q4k_xreg_kernel<G, R, L1A>;
     static int occ = 0;
     if (!occ) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, 0) != cudaSuccess || occ < 1) { cudaGetLastError(); occ = 1; }
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, 16 * 1024) != cudaSuccess || occ < 1) { cudaGetLastError(); occ = 1; }
     }
     const int cap = ckb_sm_count() * occ;
     // rows per tile: at most 128 (the shared partial-sum tile), but small enough that every CTA slot gets a tile
@@ -198,7 +221,7 @@ int launch_xreg(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(nwarps * 32);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = (size_t)nb * Q8K_BYTES;                   // <= 128 * 292 B
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

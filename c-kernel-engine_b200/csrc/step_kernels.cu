@@ -16,29 +16,52 @@
 
 namespace ckb {
 
-// grid = tokens.  x[t] += delta[t] (when delta != NULL; x is updated in place), then
-// h = rmsnorm(x[t]) * gamma, zero beyond d_model, quantised to Q8_K blocks of `aligned` elements.
-// Optionally also writes the fp32 normalised row (norm_out != NULL).
-__global__ void __launch_bounds__(256) add_rmsnorm_q8k_kernel(float *__restrict__ x, const float *__restrict__ delta,
-                                                              const float *__restrict__ gamma, uint8_t *__restrict__ out_q8,
-                                                              float *__restrict__ norm_out, int d_model, int aligned, float eps)
+// grid = tokens, block = aligned / 4 threads rounded up to a warp multiple, at most 1024.
+// x[t] += delta[t] (when delta != NULL; x is updated in place), then h = rmsnorm(x[t]) * gamma, zero beyond
+// d_model, quantised to Q8_K blocks of `aligned` elements.  Optionally also writes the fp32 normalised row.
+// Every thread issues all of its 16-byte loads before it uses any of them (one L2 round trip per row).
+constexpr int ARQ_MAX_V4 = 4;      // float4 pieces per thread: rows up to 1024 * 4 * 4 = 16384 elements
+__global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict__ x, const float *__restrict__ delta,
+                                                               const float *__restrict__ gamma, uint8_t *__restrict__ out_q8,
+                                                               float *__restrict__ norm_out, int d_model, int aligned, float eps)
 {
     extern __shared__ __align__(16) float row[];
-    __shared__ float red[8];
+    __shared__ float red[32];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     float *xr = x + (size_t)t * aligned;
     const float *dr = delta ? delta + (size_t)t * aligned : nullptr;
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < aligned; i += blockDim.x) {
-        float v = 0.0f;
-        if (i < d_model) {
-            v = __ldcg(xr + i);
-            if (dr) { v += __ldcg(dr + i); xr[i] = v; }
-            ss = fmaf(v, v, ss);
+    const int nv = aligned >> 2;
+    float4 xv[ARQ_MAX_V4], dv[ARQ_MAX_V4];
+#pragma unroll
+    for (int k = 0; k < ARQ_MAX_V4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        dv[k] = xv[k];
+        if (i < nv) {
+            xv[k] = __ldcg(reinterpret_cast<const float4 *>(xr) + i);
+            if (dr) dv[k] = __ldcg(reinterpret_cast<const float4 *>(dr) + i);
         }
-        row[i] = v;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ARQ_MAX_V4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nv) {
+            float4 v = xv[k];
+            const int e = 4 * i;
+            if (dr) {
+                v.x += dv[k].x; v.y += dv[k].y; v.z += dv[k].z; v.w += dv[k].w;
+                reinterpret_cast<float4 *>(xr)[i] = v;                 // pad columns of x and delta are zero by construction
+            }
+            if (e + 0 >= d_model) v.x = 0.f;
+            if (e + 1 >= d_model) v.y = 0.f;
+            if (e + 2 >= d_model) v.z = 0.f;
+            if (e + 3 >= d_model) v.w = 0.f;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            reinterpret_cast<float4 *>(row)[i] = v;
+        }
     }
     ss = group_sum<32>(ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -195,6 +218,10 @@ extern "C" int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const fl
     if (!x || !gamma || !out_q8 || tokens <= 0 || d_model <= 0) return 0;
     if (aligned_embed_dim % QK_K || aligned_embed_dim < d_model) return ckb_fail(CKB_ERR_SHAPE, "add_rmsnorm_q8k: aligned width %d must be a multiple of 256 and >= d_model", aligned_embed_dim);
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    if (aligned_embed_dim > 1024 * 4 * ARQ_MAX_V4) return ckb_fail(CKB_ERR_LIMIT, "add_rmsnorm_q8k: rows wider than %d are not supported", 1024 * 4 * ARQ_MAX_V4);
+    if (((uintptr_t)x | (uintptr_t)delta) & 15) return ckb_fail(CKB_ERR_ALIGN, "add_rmsnorm_q8k: x and delta must be 16-byte aligned");
+    int threads = (aligned_embed_dim / 4 + 31) & ~31;          // one 16-byte piece per thread while that fits a CTA
+    if (threads > 1024) threads = 1024;
     const size_t smem = (size_t)aligned_embed_dim * sizeof(float);
     if (smem > 48 * 1024) {
         static size_t set = 0;
@@ -203,7 +230,7 @@ extern "C" int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const fl
             set = smem;
         }
     }
-    return launch_pdl("add_rmsnorm_q8k", add_rmsnorm_q8k_kernel, dim3(tokens), dim3(256), smem, ckb_stream(stream), x, delta, gamma,
+    return launch_pdl("add_rmsnorm_q8k", add_rmsnorm_q8k_kernel, dim3(tokens), dim3(threads), smem, ckb_stream(stream), x, delta, gamma,
                       (uint8_t *)out_q8, norm_out, d_model, aligned_embed_dim, eps);
 }
 

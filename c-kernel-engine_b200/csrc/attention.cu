@@ -16,8 +16,7 @@
 // running (max, sum) for every head and `group` output accumulators for its dimensions.  Splits write (max, sum, unnormalised out) to a scratch buffer
 // and a merge kernel combines them with the exact log-sum-exp rule.
 #include "device_common.cuh"
-#include "launch.h"
-#include "runtime.h"
+#include "pdl.cuh"
 
 #include <math.h>
 
@@ -35,7 +34,7 @@ struct AttnParams {
     float scale;
 };
 
-__device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(*p.pos_ptr + 1, p.cap) : p.kv_tokens; }
+__device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(__ldcg(p.pos_ptr) + 1, p.cap) : p.kv_tokens; }
 
 constexpr int ATTN_G = 8;        // max Q heads per kv head in the fast path
 constexpr int ATTN_NW = 4;       // warps per CTA
@@ -54,9 +53,13 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
     __shared__ __align__(16) float q_s[ATTN_G][AD];
     __shared__ __align__(16) float merge_s[ATTN_NW][ATTN_G][AD + 4];   // row stride stays a multiple of 16 bytes
 
+    // Launched programmatically: q and the newest cache row come from kernels that may still have been
+    // running when this one started, so everything is read through L2 (__ldcg) after the wait.
+    pdl_trigger();
+    pdl_wait();
     for (int i = threadIdx.x; i < ATTN_G * AD; i += blockDim.x) {
         const int h = i / AD, c = i - h * AD;
-        q_s[h][c] = h < group ? p.q[((size_t)seq * p.H + h0 + h) * AD + c] * p.scale : 0.0f;
+        q_s[h][c] = h < group ? __ldcg(p.q + ((size_t)seq * p.H + h0 + h) * AD + c) * p.scale : 0.0f;
     }
     __syncthreads();
 
@@ -81,8 +84,8 @@ __global__ void __launch_bounds__(ATTN_NW * 32) attn_decode_kernel(AttnParams p)
         const int tc = min(t, t_end - 1);
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            kr[c] = __ldg(reinterpret_cast<const float4 *>(kbase + (size_t)tc * AD) + c * LPK + li);
-            vr[c] = __ldg(reinterpret_cast<const float4 *>(vbase + (size_t)tc * AD) + c * LPK + li);
+            kr[c] = __ldcg(reinterpret_cast<const float4 *>(kbase + (size_t)tc * AD) + c * LPK + li);
+            vr[c] = __ldcg(reinterpret_cast<const float4 *>(vbase + (size_t)tc * AD) + c * LPK + li);
         }
     };
 
@@ -221,9 +224,11 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict
     const size_t head = blockIdx.x;
     const float *src = part + head * splits * (ad + 2);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    pdl_trigger();
+    pdl_wait();
     float mloc = -INFINITY;
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
-        const float ms = src[s * (ad + 2) + ad];
+        const float ms = __ldcg(src + s * (ad + 2) + ad);
         f_s[s] = ms;
         mloc = fmaxf(mloc, ms);
     }
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict
         const float ms = f_s[s];
         const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
         f_s[s] = f;
-        lloc += src[s * (ad + 2) + ad + 1] * f;
+        lloc += __ldcg(src + s * (ad + 2) + ad + 1) * f;
     }
     lloc = group_sum<32>(lloc);
     if (lane == 0) red_l[warp] = lloc;
@@ -250,11 +255,11 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float *__restrict
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
         int s = 0;
         for (; s + 4 <= splits; s += 4) {
-            const float v0 = src[(s + 0) * (ad + 2) + c], v1 = src[(s + 1) * (ad + 2) + c];
-            const float v2 = src[(s + 2) * (ad + 2) + c], v3 = src[(s + 3) * (ad + 2) + c];
+            const float v0 = __ldcg(src + (s + 0) * (ad + 2) + c), v1 = __ldcg(src + (s + 1) * (ad + 2) + c);
+            const float v2 = __ldcg(src + (s + 2) * (ad + 2) + c), v3 = __ldcg(src + (s + 3) * (ad + 2) + c);
             a0 = fmaf(v0, f_s[s], a0); a1 = fmaf(v1, f_s[s + 1], a1); a2 = fmaf(v2, f_s[s + 2], a2); a3 = fmaf(v3, f_s[s + 3], a3);
         }
-        for (; s < splits; ++s) a0 = fmaf(src[s * (ad + 2) + c], f_s[s], a0);
+        for (; s < splits; ++s) a0 = fmaf(__ldcg(src + s * (ad + 2) + c), f_s[s], a0);
         out[head * ad + c] = ((a0 + a1) + (a2 + a3)) * inv;
     }
 }
@@ -377,13 +382,12 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
     p.splits = splits;
     const dim3 grid(splits, num_kv_heads, batch);
-    if (aligned_head_dim == 64) attn_decode_kernel<64><<<grid, ATTN_NW * 32, 0, st>>>(p);
-    else attn_decode_kernel<128><<<grid, ATTN_NW * 32, 0, st>>>(p);
-    if (ckb_check_launch("attn_decode")) return CKB_ERR_CUDA;
-    if (splits > 1) {
-        attn_merge_kernel<<<batch * num_heads, 128, 0, st>>>(scratch, out, splits, aligned_head_dim);
-        return ckb_check_launch("attn_merge");
-    }
+    const int rc = aligned_head_dim == 64 ? launch_pdl("attn_decode", attn_decode_kernel<64>, grid, dim3(ATTN_NW * 32), 0, st, p)
+                                          : launch_pdl("attn_decode", attn_decode_kernel<128>, grid, dim3(ATTN_NW * 32), 0, st, p);
+    if (rc) return rc;
+    if (splits > 1)
+        return launch_pdl("attn_merge", attn_merge_kernel, dim3(batch * num_heads), dim3(128), 0, st, (const float *)scratch, out, splits,
+                          aligned_head_dim);
     return 0;
 }
 

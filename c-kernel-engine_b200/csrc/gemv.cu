@@ -15,8 +15,7 @@
 //   direct  lanes read 16-byte pieces of 144-byte Q4_K superblocks straight from global memory
 //           (always 16-byte aligned); Q6_K / Q8_0 use 2-byte loads.  Any shape, no shared staging.
 #include "quant_units.cuh"
-#include "launch.h"
-#include "runtime.h"
+#include "pdl.cuh"
 
 namespace ckb {
 
@@ -196,6 +195,133 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_direct_kernel(const uint8_t 
 }
 
 // =====================================================================================
+// ring family helpers: activation staging (coherent, batched) and the Q6_K unit used by the ring kernel
+// =====================================================================================
+
+// Q8_K vector for Q6_K weights: q8 data in the HP = 2 padded layout, fp32 d per block, and per
+// (block, half n, l-half h) the four 16-element sums bsums[8n + 2t + h], t = 0..3, split as 128*hi + lo
+// and packed 4 x s8, so that sum_t sc_t * bsum_t is two dp4a.
+struct RingX {
+    uint32_t q, d, lo, hi;   // shared addresses (Q8_K)   | q80: q = 48-byte slots
+};
+
+__host__ __device__ inline int ringx_smem_bytes(int fmt, int nb)
+{
+    const int raw = fmt == FMT_Q80 ? nb * 48 : (fmt == FMT_Q6K ? nb * (20 * 16 + 4 + 32) : nb * (18 * 16 + 4 + 32));
+    return (raw + 127) & ~127;
+}
+
+// Batched loads through L2 (__ldcg): the vector may have been written by a kernel that overlaps this one.
+template <int FMT>
+__device__ __forceinline__ RingX ring_stage_x(const uint8_t *xg, int nb, uint8_t *smem)
+{
+    RingX r;
+    if constexpr (FMT == FMT_Q80) {
+        const int total = nb * 17;
+        for (int base = 0; base < total; base += 8 * blockDim.x) {
+            uint32_t v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * blockDim.x + threadIdx.x;
+                v[u] = 0;
+                if (i < total) {
+                    unsigned short t;
+                    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(t) : "l"(xg + 2 * (size_t)i));
+                    v[u] = t;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * blockDim.x + threadIdx.x;
+                if (i < total) {
+                    const int b = i / 17, h = i - b * 17;
+                    if (h == 0) *reinterpret_cast<float *>(smem + b * 48 + 32) = half_bits_to_float(v[u]);
+                    else *reinterpret_cast<unsigned short *>(smem + b * 48 + 2 * (h - 1)) = (unsigned short)v[u];
+                }
+            }
+        }
+        r.q = smem_u32(smem);
+        r.d = r.lo = r.hi = 0;
+    } else {
+        constexpr int SLOTS = FMT == FMT_Q6K ? 20 : 18, HP = FMT == FMT_Q6K ? 2 : 1;
+        uint32_t *xq = reinterpret_cast<uint32_t *>(smem);
+        float *xd = reinterpret_cast<float *>(smem + nb * SLOTS * 16);
+        int8_t *lo = reinterpret_cast<int8_t *>(smem + nb * (SLOTS * 16 + 4));
+        int8_t *hi = lo + nb * 16;
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(xg);
+        const int total = nb * 73;
+        for (int base = 0; base < total; base += 8 * blockDim.x) {
+            uint32_t v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * blockDim.x + threadIdx.x;
+                v[u] = i < total ? __ldcg(src + i) : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * blockDim.x + threadIdx.x;
+                if (i >= total) break;
+                const int b = i / 73, w = i - b * 73;
+                if (w == 0) {
+                    xd[b] = __uint_as_float(v[u]);
+                } else if (w <= 64) {
+                    const int c = (w - 1) >> 2;
+                    xq[b * SLOTS * 4 + (c + HP * (c >> 3)) * 4 + ((w - 1) & 3)] = v[u];
+                } else if constexpr (FMT == FMT_Q6K) {
+                    const int j = w - 65, n = j >> 2, t = j & 3;               // bsums[2j] (h = 0), bsums[2j+1] (h = 1)
+                    const int s0 = (int)(short)(v[u] & 0xffffu), s1 = (int)(short)(v[u] >> 16);
+                    lo[(b * 4 + n * 2 + 0) * 4 + t] = (int8_t)(s0 & 127);
+                    hi[(b * 4 + n * 2 + 0) * 4 + t] = (int8_t)(s0 >> 7);
+                    lo[(b * 4 + n * 2 + 1) * 4 + t] = (int8_t)(s1 & 127);
+                    hi[(b * 4 + n * 2 + 1) * 4 + t] = (int8_t)(s1 >> 7);
+                } else {
+                    reinterpret_cast<int *>(lo)[b * 8 + (w - 65)] = (int)(short)(v[u] & 0xffffu) + (int)(short)(v[u] >> 16);
+                }
+            }
+        }
+        r.q = smem_u32(xq);
+        r.d = smem_u32(xd);
+        r.lo = smem_u32(lo);
+        r.hi = smem_u32(hi);
+    }
+    return r;
+}
+
+// Q6_K quarter (n, h) from shared memory.  sum (q6 - 32) * x is split so that no 6-bit value is ever
+// assembled: the nibble planes and the 2-bit planes are multiplied in place (masked, not shifted) and
+// the place values are applied to the int32 sums; the -32 goes through the activation block sums.
+__device__ __forceinline__ float q6k_ring_unit(uint32_t a, int b, int u, const RingX &x)
+{
+    const int n = u >> 1, h = u & 1;
+    const uint4 qa = lds_u4_align2(a + 64 * n + 16 * h);
+    const uint4 qb = lds_u4_align2(a + 64 * n + 32 + 16 * h);
+    const uint4 qh = lds_u4_align2(a + 128 + 32 * n + 16 * h);
+    const uint32_t sa = a + 192 + 8 * n + h;
+    const int s0 = lds_s8(sa), s1 = lds_s8(sa + 2), s2 = lds_s8(sa + 4), s3 = lds_s8(sa + 6);
+    const uint32_t dbits = lds_u16(a + 208);
+    const uint32_t xa = x.q + (uint32_t)(b * 80 + (10 * n + h) * 4) * 4u;
+    const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 32), x2 = lds_u4(xa + 64), x3 = lds_u4(xa + 96);
+    int A1 = 0, A2 = 0, A3 = 0, A4 = 0, B1 = 0, B2 = 0, B3 = 0, B4 = 0;
+#define CKB_Q6_STEP(QA, QB, QH, X0, X1, X2, X3)                      \
+    A1 = dp4a_us((QA) & 0x0F0F0F0Fu, X0, A1); B1 = dp4a_us((QH) & 0x03030303u, X0, B1); \
+    A2 = dp4a_us((QB) & 0x0F0F0F0Fu, X1, A2); B2 = dp4a_us((QH) & 0x0C0C0C0Cu, X1, B2); \
+    A3 = dp4a_us((QA) & 0xF0F0F0F0u, X2, A3); B3 = dp4a_us((QH) & 0x30303030u, X2, B3); \
+    A4 = dp4a_us((QB) & 0xF0F0F0F0u, X3, A4); B4 = dp4a_us((QH) & 0xC0C0C0C0u, X3, B4);
+    CKB_Q6_STEP(qa.x, qb.x, qh.x, x0.x, x1.x, x2.x, x3.x)
+    CKB_Q6_STEP(qa.y, qb.y, qh.y, x0.y, x1.y, x2.y, x3.y)
+    CKB_Q6_STEP(qa.z, qb.z, qh.z, x0.z, x1.z, x2.z, x3.z)
+    CKB_Q6_STEP(qa.w, qb.w, qh.w, x0.w, x1.w, x2.w, x3.w)
+#undef CKB_Q6_STEP
+    const int S1 = A1 + 16 * B1, S2 = A2 + 4 * B2, S3 = (A3 >> 4) + B3, S4 = (A4 >> 4) + (B4 >> 2);   // all exact
+    const uint32_t sc4 = __byte_perm(__byte_perm((uint32_t)s0, (uint32_t)s1, 0x0040), __byte_perm((uint32_t)s2, (uint32_t)s3, 0x0040), 0x5410);
+    const uint32_t lo4 = lds_u32(x.lo + 4u * (b * 4 + u)), hi4 = lds_u32(x.hi + 4u * (b * 4 + u));
+    const int center = dp4a_ss(sc4, lo4, 0) + 128 * dp4a_ss(sc4, hi4, 0);          // sum_t sc_t * bsum_t
+    const int tot = s0 * S1 + s1 * S2 + s2 * S3 + s3 * S4 - 32 * center;
+    const float xd = __uint_as_float(lds_u32(x.d + 4u * b));
+    return (half_bits_to_float(dbits) * xd) * (float)tot;
+}
+
+// =====================================================================================
 // ring family: warp-private rings of bulk-copied stages.
 // =====================================================================================
 struct RingPlan {
@@ -206,6 +332,20 @@ struct RingPlan {
     int lanes_per_row;   // power of two <= 32; 32 in mode B
 };
 
+template <int FMT>
+__device__ __forceinline__ float ring_unit(uint32_t a, int b, int u, const RingX &x)
+{
+    if constexpr (FMT == FMT_Q6K) {
+        return q6k_ring_unit(a, b, u, x);
+    } else {
+        XView v;
+        v.k.q = x.q; v.k.d = x.d; v.k.bs = x.lo; v.q80 = x.q;
+        return unit_from_shared<FMT>(a, b, u, v);
+    }
+}
+
+// Programmatic dependent launch: the first stages of every warp's ring (weights only) are requested before
+// the kernel waits for its predecessor, the activation vector is staged after the wait.
 template <int FMT, int NWC, int D>
 __global__ void __launch_bounds__(NWC * 32, 1) gemv_ring_kernel(const uint8_t *__restrict__ W, const uint8_t *__restrict__ xg,
                                                                  float *__restrict__ y, int M, int nb, RingPlan plan,
@@ -214,18 +354,12 @@ __global__ void __launch_bounds__(NWC * 32, 1) gemv_ring_kernel(const uint8_t *_
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int BS = FmtTraits<FMT>::BS, UPB = FmtTraits<FMT>::UPB;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int xbytes = x_smem_bytes(FMT, nb);
+    const int xbytes = ringx_smem_bytes(FMT, nb);
     uint8_t *ring = smem + xbytes + (size_t)warp * D * plan.stage_bytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + xbytes + (size_t)NWC * D * plan.stage_bytes) + warp * D;
     const uint32_t ring_a = smem_u32(ring), bar_a = smem_u32(bars);
 
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < D; ++s) mbar_init(bar_a + 8 * s, 1);
-        mbar_fence_init();
-    }
-    const XView x = load_x<FMT>(xg, nb, smem);
-    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;");
 
     const size_t rb = (size_t)nb * BS;
     const int RT = plan.rows_per_tile, CB = plan.blocks_per_chunk, NCH = plan.chunks, G = plan.lanes_per_row;
@@ -257,9 +391,16 @@ __global__ void __launch_bounds__(NWC * 32, 1) gemv_ring_kernel(const uint8_t *_
     };
 
     if (lane == 0) {
-        for (int i = 0; i < min(D, n_mine); ++i) issue(i);
+#pragma unroll
+        for (int s = 0; s < D; ++s) mbar_init(bar_a + 8 * s, 1);
+        mbar_fence_init();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int i = 0; i < min(D, n_mine); ++i) issue(i);          // weights: nothing ever writes them
     }
-    __syncwarp();
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const RingX x = ring_stage_x<FMT>(xg, nb, smem);
+    __syncthreads();
 
     const int li = lane & (G - 1), sub = lane / G, rows_per_pass = 32 / G;
     float acc = 0.0f;
@@ -283,7 +424,7 @@ __global__ void __launch_bounds__(NWC * 32, 1) gemv_ring_kernel(const uint8_t *_
                 const uint32_t ra = base + (uint32_t)(r * rb);
                 for (int u = li; u < units; u += G) {
                     const int b = u / UPB;
-                    acc += unit_from_shared<FMT>(ra + b * BS, blk0 + b, u - b * UPB, x);
+                    acc += ring_unit<FMT>(ra + b * BS, blk0 + b, u - b * UPB, x);
                 }
             }
             if (last_chunk) {
@@ -313,7 +454,7 @@ using namespace ckb;
 
 namespace {
 
-constexpr int RING_NWC = 8, RING_D = 4;
+constexpr int RING_NWC = 16, RING_D = 3;
 constexpr int SMEM_BUDGET = 200 * 1024;   // ring + activations; the SM has 227 KB per CTA
 
 template <typename KernelT>
@@ -352,7 +493,7 @@ int launch_q4k_direct(float *y, const void *W, const void *xq, int M, int nb, cu
 // Picks the ring geometry.  Returns false when a row chunk cannot fit (never for the supported formats).
 bool plan_ring(int fmt, int bs, int upb, int M, int nb, int grid, RingPlan &p)
 {
-    const int xb = x_smem_bytes(fmt, nb);
+    const int xb = ringx_smem_bytes(fmt, nb);
     int stage = (SMEM_BUDGET - xb) / (RING_NWC * RING_D);
     stage &= ~127;
     const int cap = ckb_tune_get("ring_stage_bytes", 0);
@@ -399,11 +540,14 @@ int launch_ring(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     const int grid = ckb_sm_count();
     RingPlan plan;
     if (!plan_ring(FMT, BS, UPB, M, nb, grid, plan)) return ckb_fail(CKB_ERR_LIMIT, "gemv (ring): K too large");
-    const int smem = x_smem_bytes(FMT, nb) + RING_NWC * RING_D * plan.stage_bytes + RING_NWC * RING_D * 8;
-    if (set_smem(gemv_ring_kernel<FMT, RING_NWC, RING_D>, smem)) return CKB_ERR_CUDA;
-    gemv_ring_kernel<FMT, RING_NWC, RING_D><<<grid, RING_NWC * 32, smem, st>>>(
-        (const uint8_t *)W, (const uint8_t *)xq, y, M, nb, plan, ckb_device_error_word());
-    return ckb_check_launch("gemv_ring");
+    const int smem = ringx_smem_bytes(FMT, nb) + RING_NWC * RING_D * plan.stage_bytes + RING_NWC * RING_D * 8;
+    static int attr_set = 0;
+    if (smem > attr_set) {
+        if (set_smem(gemv_ring_kernel<FMT, RING_NWC, RING_D>, smem)) return CKB_ERR_CUDA;
+        attr_set = smem;
+    }
+    return launch_pdl("gemv_ring", gemv_ring_kernel<FMT, RING_NWC, RING_D>, dim3(grid), dim3(RING_NWC * 32), (size_t)smem, st,
+                      (const uint8_t *)W, (const uint8_t *)xq, y, M, nb, plan, ckb_device_error_word());
 }
 
 int check_common(const char *name, const void *y, const void *W, const void *xq, int M, int K, int blk)
@@ -468,7 +612,7 @@ extern "C" int ckb200_dev_gemv_q6_k_q8_k(float *y, const void *W, const void *xq
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);
     int v = ckb_tune_get("gemv_q6_k", 0);
-    if (v == 0) v = ((uintptr_t)W & 15) ? 2 : 1;
+    if (v == 0) v = (((uintptr_t)W & 15) || (nb <= 4 && M > 32768)) ? 2 : 1;     // very many short rows: per-tile ring overhead loses
     if (v == 1) return launch_ring<FMT_Q6K>(y, W, xq, M, nb, st);
     return launch_direct_generic<FMT_Q6K>(y, W, xq, M, nb, st);
 }
@@ -483,7 +627,7 @@ extern "C" int ckb200_dev_gemv_q8_0_q8_0(float *y, const void *W, const void *xq
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);
     int v = ckb_tune_get("gemv_q8_0", 0);
-    if (v == 0) v = ((uintptr_t)W & 15) ? 2 : 1;
+    if (v == 0) v = (((uintptr_t)W & 15) || (nb <= 32 && M > 32768)) ? 2 : 1;
     if (v == 1) return launch_ring<FMT_Q80>(y, W, xq, M, nb, st);
     return launch_direct_generic<FMT_Q80>(y, W, xq, M, nb, st);
 }

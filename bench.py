@@ -202,7 +202,23 @@ LLAMA3_70B = dict(embed_dim=8192, num_heads=64, num_kv_heads=8, head_dim=128, in
                   max_seq_len=4352, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
 
 
-def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1):
+def tp_setup(lib, rank, world, dev):
+    """Create the NCCL communicator of the library: rank 0 makes the id, torch.distributed carries it."""
+    import torch
+    import torch.distributed as dist
+
+    uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        buf = (C.c_char * 128)()
+        assert lib.ckb200_tp_unique_id(buf) == 0
+        uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
+    dist.broadcast(uid, 0)
+    raw = bytes(uid.cpu().numpy().tobytes())
+    if lib.ckb200_tp_init(rank, world, raw) != 0:
+        raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+
+def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None):
     """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens."""
     import torch
 
@@ -211,14 +227,17 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1):
     import step_oracle as so
 
     so.bind_model_api(lib)
-    st = so.make_cfg(cfg, batch=batch)
+    st = so.make_cfg(cfg, batch=batch, tp_rank=tp_rank, tp_size=tp_size)
     handle = lib.ckb200_model_create(C.byref(st))
     if not handle:
         msg = lib.ckb200_last_error_message().decode()
         lib.ckb200_clear_error()
         return {"error": msg}
     try:
-        assert lib.ckb200_model_fill_synthetic(handle, 1) == 0
+        if tp_size > 1:
+            lib.ckb200_model_use_tp.argtypes = [C.c_void_p]
+            lib.ckb200_model_use_tp(handle)
+        assert lib.ckb200_model_fill_synthetic(handle, 1 + tp_rank) == 0
         assert lib.ckb200_model_fill_kv_synthetic(handle, ctx, 2) == 0
         ids = np.full(batch, 11, dtype=np.int32)
         launches0 = lib.ckb200_launch_count()
@@ -229,13 +248,19 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1):
         lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         assert lib.ckb200_model_set_pos(handle, ctx) == 0
+        if dist:
+            dist.barrier()
         e0.record(lstream)
         assert lib.ckb200_model_decode_repeat(handle, steps) == 0
         e1.record(lstream)
         lstream.synchronize()
         ms = e0.elapsed_time(e1) / steps
-        wbytes = lib.ckb200_model_weight_bytes(handle)
-        kv_bytes = 2 * cfg["num_layers"] * cfg["num_kv_heads"] * (ctx + steps // 2) * cfg["head_dim"] * 4 * batch
+        if dist:
+            t = torch.tensor([ms], device=torch.device("cuda", torch.cuda.current_device()))
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        wbytes = lib.ckb200_model_weight_bytes(handle)                    # this rank's shard
+        kv_bytes = 2 * cfg["num_layers"] * max(1, cfg["num_kv_heads"] // tp_size) * (ctx + steps // 2) * cfg["head_dim"] * 4 * batch
         gbs = (wbytes + kv_bytes) / ms / 1e6
         # end to end: token id from the host, logits back to the host, every step
         logits = np.zeros((batch, cfg["vocab_size"]), np.float32)
@@ -245,8 +270,8 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1):
         for _ in range(n_e2e):
             assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0
         e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
-        return {"model_shape": name, "batch": batch, "context": ctx, "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
-                "weight_bytes": int(wbytes), "kv_bytes": int(kv_bytes), "hbm_gbs": gbs, "frac_of_measured_peak": gbs / peak,
+        return {"model_shape": name, "batch": batch, "context": ctx, "tp": tp_size, "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
+                "weight_bytes": int(wbytes), "kv_bytes": int(kv_bytes), "hbm_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peak,
                 "e2e_tok_s": batch * 1e3 / e2e_ms, "e2e_ms_per_token": e2e_ms}
     finally:
         lib.ckb200_model_free(handle)
@@ -408,6 +433,16 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         lib.ckb200_host_free(C.c_void_p(hy))
     pkg.check(lib)
 
+    decode_tp = None
+    if world > 1 and not args.no_decode:
+        try:
+            tp_setup(lib, rank, world, dev)
+            decode_tp = [decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}", LLAMA3_70B, 4096, 20, measured_peak()[0],
+                                      batch=b, tp_rank=rank, tp_size=world, dist=dist) for b in (1,)]
+        except Exception as exc:
+            decode_tp = {"error": repr(exc)}
+            lib.ckb200_clear_error()
+
     if rank == 0:
         r = results["q4_k"]
         peak, peak_kind = measured_peak()
@@ -440,6 +475,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             except Exception as exc:                      # the headline metric above must survive a failure here
                 line["decode"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()
+        if decode_tp is not None:
+            line["decode_tp"] = decode_tp
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line), flush=True)

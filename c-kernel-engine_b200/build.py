@@ -72,6 +72,16 @@ def build(verbose: bool = False, force: bool = False) -> str:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    # the two thin model-ABI libraries (same symbol names, different signatures: they cannot share one library)
+    for name, src in (("libckb200_model_v7.so", "model_v7.c"), ("libckb200_model_api.so", "model_handle.c")):
+        out = os.path.join(PKG, name)
+        srcp = os.path.join(CSRC, "abi", src)
+        if force or _newer(srcp, out, headers + [LIB]):
+            cmd = ["gcc", *CC_FLAGS, "-shared", "-fvisibility=hidden", srcp, "-o", out, f"-L{PKG}", "-lckb200", "-Wl,-rpath,$ORIGIN"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError(f"compile failed: {src}")
     return LIB
 
 

@@ -504,3 +504,101 @@ size_t ckb200_model_weight_bytes(CKB200Model *m)
             if (m->layers[l].t[i].fmt >= 0) s += m->layers[l].t[i].bytes;
     return s + m->lm_head.bytes;
 }
+
+/* ------------------------------------------------------------------ model sources
+ *
+ * ckb200_model_open(spec, batch):
+ *   "synthetic:<shape>[:seed]"  a named model SHAPE with device-generated random weights
+ *                               (qwen2-0.5b, llama3-8b, llama3-70b, mini); for benchmarks and smoke runs
+ *   "<path>"                    a file in the container format below (what tests and converters write)
+ *
+ * File: magic "CKB2MDL1", u32 version = 1, the config (8 ints, 2 floats, 12 ints as in CKB200ModelConfig),
+ * then the tensors in canonical order - per layer ln1, wq, wk, wv, wo, ln2, w1, w2; final gamma; LM head;
+ * embedding table unless tied - each as u64 byte count followed by the bytes (block formats as in the
+ * reference, fp32 for the norm weights). */
+
+static const struct { const char *name; CKB200ModelConfig cfg; } g_presets[] = {
+    { "qwen2-0.5b", { 896, 14, 2, 64, 4864, 24, 151936, 2048, 1e-6f, 1.0e6f, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 0, 1 } },
+    { "llama3-8b", { 4096, 32, 8, 128, 14336, 32, 128256, 4352, 1e-5f, 5.0e5f, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 0, 1 } },
+    { "llama3-70b", { 8192, 64, 8, 128, 28672, 80, 128256, 4352, 1e-5f, 5.0e5f, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 0, 1 } },
+    { "mini", { 384, 6, 2, 64, 768, 3, 1000, 128, 1e-6f, 1.0e6f, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 0, 1 } },
+};
+
+static int read_exact(FILE *f, void *dst, size_t n) { return fread(dst, 1, n, f) == n ? 0 : -1; }
+
+static CKB200Model *open_file(const char *path, int batch)
+{
+    FILE *f = fopen(path, "rb");
+    if (!f) { ckb_fail(CKB_ERR_STATE, "model_open: cannot open %s", path); return NULL; }
+    char magic[8];
+    uint32_t version = 0;
+    CKB200ModelConfig cfg;
+    CKB200Model *m = NULL;
+    void *buf = NULL;
+    size_t cap = 0;
+    if (read_exact(f, magic, 8) || memcmp(magic, "CKB2MDL1", 8) || read_exact(f, &version, 4) || version != 1 || read_exact(f, &cfg, sizeof cfg)) {
+        ckb_fail(CKB_ERR_STATE, "model_open: %s is not a CKB2MDL1 file", path);
+        goto done;
+    }
+    if (batch > 0) cfg.batch = batch;
+    m = ckb200_model_create(&cfg);
+    if (!m) goto done;
+    const int L = cfg.num_layers;
+    for (int i = 0; i < L * CKB_T_PER_LAYER + 2 + (cfg.tie_embeddings ? 0 : 1); ++i) {
+        const int layer = i < L * CKB_T_PER_LAYER ? i / CKB_T_PER_LAYER : -1;
+        const int which = layer >= 0 ? i % CKB_T_PER_LAYER : CKB_T_FINAL_GAMMA + (i - L * CKB_T_PER_LAYER);
+        uint64_t n = 0;
+        if (read_exact(f, &n, 8) || n != ckb200_model_tensor_bytes(m, layer, which)) {
+            ckb_fail(CKB_ERR_SHAPE, "model_open: tensor (%d, %d) of %s has %llu bytes, expected %zu", layer, which, path,
+                     (unsigned long long)n, ckb200_model_tensor_bytes(m, layer, which));
+            ckb200_model_free(m);
+            m = NULL;
+            goto done;
+        }
+        if (n > cap) { free(buf); buf = malloc(n); cap = n; }
+        if (!buf || read_exact(f, buf, n) || ckb200_model_upload_tensor(m, layer, which, buf, n)) {
+            ckb_fail(CKB_ERR_STATE, "model_open: short read in %s", path);
+            ckb200_model_free(m);
+            m = NULL;
+            goto done;
+        }
+    }
+done:
+    free(buf);
+    fclose(f);
+    return m;
+}
+
+CKB200Model *ckb200_model_open(const char *spec, int batch)
+{
+    if (!spec) { ckb_fail(CKB_ERR_STATE, "model_open: NULL spec"); return NULL; }
+    if (strncmp(spec, "synthetic:", 10) != 0) return open_file(spec, batch);
+    char name[64];
+    unsigned long long seed = 1;
+    const char *p = spec + 10, *colon = strchr(p, ':');
+    size_t n = colon ? (size_t)(colon - p) : strlen(p);
+    if (n >= sizeof name) n = sizeof name - 1;
+    memcpy(name, p, n);
+    name[n] = 0;
+    if (colon) seed = strtoull(colon + 1, NULL, 10);
+    for (size_t i = 0; i < sizeof g_presets / sizeof g_presets[0]; ++i)
+        if (!strcmp(g_presets[i].name, name)) {
+            CKB200ModelConfig cfg = g_presets[i].cfg;
+            if (batch > 0) cfg.batch = batch;
+            CKB200Model *m = ckb200_model_create(&cfg);
+            if (m && ckb200_model_fill_synthetic(m, seed)) { ckb200_model_free(m); m = NULL; }
+            return m;
+        }
+    ckb_fail(CKB_ERR_STATE, "model_open: unknown synthetic shape '%s'", name);
+    return NULL;
+}
+
+const CKB200ModelConfig *ckb200_model_config(CKB200Model *m) { return m ? &m->c : NULL; }
+
+int ckb200_model_reset(CKB200Model *m)
+{
+    if (!m) return CKB_ERR_STATE;
+    cudaStream_t st = ckb_stream(NULL);
+    cudaMemsetAsync(m->kv, 0, (size_t)m->c.num_layers * m->kv_layer_stride * sizeof(float), st);
+    return ckb200_model_set_pos(m, 0);
+}

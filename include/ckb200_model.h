@@ -45,6 +45,10 @@ typedef struct CKB200Model CKB200Model;
 /* sum `count` floats in place over all tensor-parallel ranks, enqueued on `stream`; returns 0 on success */
 typedef int (*ckb200_allreduce_fn)(void *ctx, float *buf, size_t count, void *stream);
 
+/* "synthetic:<qwen2-0.5b|llama3-8b|llama3-70b|mini>[:seed]" or the path of a CKB2MDL1 model file; batch <= 0 keeps the default */
+CKB200Model *ckb200_model_open(const char *spec, int batch);
+const CKB200ModelConfig *ckb200_model_config(CKB200Model *m);
+int ckb200_model_reset(CKB200Model *m);                                  /* zero the KV cache, pos = 0 (ck_model_kv_cache_reset) */
 CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg);          /* NULL on failure (see ckb200_last_error) */
 void ckb200_model_free(CKB200Model *m);
 size_t ckb200_model_tensor_bytes(CKB200Model *m, int layer, int which);
@@ -62,6 +66,17 @@ int ckb200_model_decode_repeat(CKB200Model *m, int steps);              /* re-la
 float *ckb200_model_logits_device(CKB200Model *m);
 void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v);       /* [batch][Hkv][max_seq][head_dim] fp32 */
 size_t ckb200_model_weight_bytes(CKB200Model *m);                        /* quantised bytes one step streams */
+
+
+/* ---- tensor-parallel exchange (no counterpart in the reference, which has no collective): fp32 sum all-reduce over
+ * NCCL, one process per GPU.  Rank 0 makes the 128-byte id, the caller distributes it, every rank calls tp_init. */
+int ckb200_tp_unique_id(void *out128);
+int ckb200_tp_init(int rank, int world, const void *id128);
+int ckb200_tp_allreduce(void *ctx, float *buf, size_t count, void *stream);   /* a ckb200_allreduce_fn */
+int ckb200_tp_rank(void);
+int ckb200_tp_world(void);
+void ckb200_tp_shutdown(void);
+void ckb200_model_use_tp(CKB200Model *m);                                     /* set_allreduce(m, ckb200_tp_allreduce, NULL) */
 
 #ifdef __cplusplus
 }

@@ -138,3 +138,98 @@ def upload_whole_model(lib, handle, cpu: CpuModel, batch: int):
             slab = np.ascontiguousarray(cache[l])
             for b in range(batch):
                 assert lib.ckb200_copy_to_device(C.c_void_p(base + b * slab.nbytes), cases.vptr(slab), slab.nbytes) == 0
+
+
+# ----------------------------------------------------------------------------- tensor-parallel sharding
+
+BLOCK = {0: (256, 144), 1: (256, 210), 2: (32, 34)}     # fmt -> (elements, bytes) per block
+
+
+def _rows(w, r0, r1):
+    fmt, rows, cols, data = w
+    rb = data.size // rows
+    return (fmt, r1 - r0, cols, np.ascontiguousarray(data.reshape(rows, rb)[r0:r1]).reshape(-1))
+
+
+def _cols(w, c0, c1):
+    """Input columns [c0, c1) of every row; both must fall on block boundaries (256 for the K-quants)."""
+    fmt, rows, cols, data = w
+    be, bb = BLOCK[fmt]
+    assert c0 % be == 0 and c1 % be == 0
+    blocks = data.reshape(rows, cols // be, bb)[:, c0 // be:c1 // be]
+    return (fmt, rows, c1 - c0, np.ascontiguousarray(blocks).reshape(-1))
+
+
+def shard_layer(cfg, lay, rank, tp):
+    """Column-parallel q/k/v/gate/up (whole heads, matching gate/up rows), row-parallel o/down split at block boundaries."""
+    H, Hkv, d, I = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["intermediate_size"]
+    Hl, Hkvl, Il = H // tp, Hkv // tp, I // tp
+    out = {"LN1": lay["LN1"], "LN2": lay["LN2"]}
+    out["WQ"] = _rows(lay["WQ"], rank * Hl * d, (rank + 1) * Hl * d)
+    out["WK"] = _rows(lay["WK"], rank * Hkvl * d, (rank + 1) * Hkvl * d)
+    out["WV"] = _rows(lay["WV"], rank * Hkvl * d, (rank + 1) * Hkvl * d)
+    g = _rows(lay["W1"], rank * Il, (rank + 1) * Il)
+    u = _rows(lay["W1"], I + rank * Il, I + (rank + 1) * Il)
+    out["W1"] = (g[0], 2 * Il, g[2], np.concatenate([g[3], u[3]]))
+    out["WO"] = _cols(lay["WO"], rank * Hl * d, (rank + 1) * Hl * d)
+    out["W2"] = _cols(lay["W2"], rank * Il, (rank + 1) * Il)
+    return out
+
+
+class TpShard:
+    """One rank's view of a CpuModel: sharded layers, its own KV heads, the whole LM head."""
+
+    def __init__(self, cpu: CpuModel, rank: int, tp: int):
+        c = cpu.cfg
+        assert c["num_heads"] % tp == 0 and c["num_kv_heads"] % tp == 0 and c["intermediate_size"] % tp == 0
+        self.cpu, self.rank, self.tp = cpu, rank, tp
+        self.layers = [shard_layer(c, lay, rank, tp) for lay in cpu.layers]
+        Hkvl = c["num_kv_heads"] // tp
+        self.kc = np.ascontiguousarray(cpu.kc[:, rank * Hkvl:(rank + 1) * Hkvl])
+        self.vc = np.ascontiguousarray(cpu.vc[:, rank * Hkvl:(rank + 1) * Hkvl])
+
+    def decode(self, lib, token: int, pos: int, allreduce) -> np.ndarray:
+        """Same op order as CpuModel.decode on this rank's shard; `allreduce(vec)` sums a vector over ranks in place."""
+        cpu, c, tp = self.cpu, self.cpu.cfg, self.tp
+        D, d = c["embed_dim"], c["head_dim"]
+        Hl, Hkvl, Il = c["num_heads"] // tp, c["num_kv_heads"] // tp, c["intermediate_size"] // tp
+        efmt, _, _, edata = cpu.lm_head
+        x = cases.embedding(lib, "oracle_", FMT[efmt], [token], edata, c["vocab_size"], D, cpu.Da)[0].copy()
+        cos, sin = cases.rope_cache(lib, "oracle_", c["max_seq_len"], d, c["rope_theta"])
+        for l, lay in enumerate(self.layers):
+            h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN1"], D, c["rms_eps"])[0]
+            q = cpu._matvec(lib, lay["WQ"], h).reshape(Hl, 1, d).copy()
+            k = cpu._matvec(lib, lay["WK"], h).reshape(Hkvl, 1, d).copy()
+            v = cpu._matvec(lib, lay["WV"], h).reshape(Hkvl, d).copy()
+            cases.rope_qk(lib, "oracle_", q, k, cos, sin, pos)
+            cases.kv_cache_store(lib, "oracle_", self.kc[l], self.vc[l], np.ascontiguousarray(k.reshape(Hkvl, d)), v, pos)
+            att = cases.attention_decode(lib, "oracle_", np.ascontiguousarray(q.reshape(Hl, d)), self.kc[l], self.vc[l], pos + 1).reshape(-1)
+            o = cpu._matvec(lib, lay["WO"], att)
+            allreduce(o)
+            x[:D] += o
+            h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN2"], D, c["rms_eps"])[0]
+            gu = cpu._matvec(lib, lay["W1"], h)
+            mm = cases.swiglu(lib, "oracle_", gu.reshape(1, -1), Il)[0]
+            dn = cpu._matvec(lib, lay["W2"], mm)
+            allreduce(dn)
+            x[:D] += dn
+        h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), cpu.final_gamma, D, c["rms_eps"])[0]
+        return cpu._matvec(lib, cpu.lm_head, h)
+
+
+def upload_shard(lib, handle, shard: TpShard, batch: int = 1):
+    cpu = shard.cpu
+    for l, lay in enumerate(shard.layers):
+        for name in ("LN1", "LN2"):
+            assert lib.ckb200_model_upload_tensor(handle, l, T[name], cases.vptr(lay[name]), lay[name].nbytes) == 0
+        for name in ("WQ", "WK", "WV", "WO", "W1", "W2"):
+            data = lay[name][3]
+            assert lib.ckb200_model_upload_tensor(handle, l, T[name], cases.vptr(data), data.nbytes) == 0, (l, name)
+    assert lib.ckb200_model_upload_tensor(handle, -1, T["FINAL_GAMMA"], cases.vptr(cpu.final_gamma), cpu.final_gamma.nbytes) == 0
+    assert lib.ckb200_model_upload_tensor(handle, -1, T["LM_HEAD"], cases.vptr(cpu.lm_head[3]), cpu.lm_head[3].nbytes) == 0
+    for l in range(len(shard.layers)):
+        for is_v, cache in ((0, shard.kc), (1, shard.vc)):
+            base = lib.ckb200_model_kv_device(handle, l, is_v)
+            slab = np.ascontiguousarray(cache[l])
+            for b in range(batch):
+                assert lib.ckb200_copy_to_device(C.c_void_p(base + b * slab.nbytes), cases.vptr(slab), slab.nbytes) == 0

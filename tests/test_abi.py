@@ -16,9 +16,14 @@ import cases
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols() -> dict[str, str]:
+HEADER_LIB = {"ckb200_model_v7.h": "libckb200_model_v7.so", "ckb200_model_handle.h": "libckb200_model_api.so"}
+
+
+def declared_symbols(lib_name: str = "libckb200.so") -> dict[str, str]:
     out = {}
     for path in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
+        if HEADER_LIB.get(os.path.basename(path), "libckb200.so") != lib_name:
+            continue
         text = open(path).read()
         text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
         text = re.sub(r"//[^\n]*", " ", text)
@@ -38,15 +43,53 @@ def test_headers_declare_the_expected_surface():
                  "attention_forward_decode_head_major_gqa_flash", "kv_cache_store", "gemv_q4_k_q8_k_parallel_dispatch",
                  "ckb200_dev_gemv_q4_k_q8_k", "ckb200_register_weights", "ckb200_last_error"):
         assert name in syms, name
-    assert len(syms) > 80
+    assert len(syms) > 100
 
 
-def test_library_exports_every_declared_symbol(pkg):
-    path = pkg.find_lib()
+@pytest.mark.parametrize("lib_name", ["libckb200.so", "libckb200_model_v7.so", "libckb200_model_api.so"])
+def test_library_exports_every_declared_symbol(pkg, lib_name):
+    path = pkg.find_lib(lib_name)
     nm = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
     exported = {line.split()[-1] for line in nm.splitlines() if " T " in line}
-    missing = sorted(s for s in declared_symbols() if s not in exported)
-    assert not missing, f"declared in include/ but not exported by {os.path.basename(path)}: {missing}"
+    declared = declared_symbols(lib_name)
+    assert len(declared) >= 10
+    missing = sorted(s for s in declared if s not in exported)
+    assert not missing, f"declared in include/ but not exported by {lib_name}: {missing}"
+
+
+def test_registry_contract(pkg):
+    """ck_op_supported / ck_ir_validate_supported behave like src/ckernel_registry.c:26-60: seven forward ops, no backward ops."""
+    lib = pkg.load_lib()
+    assert [lib.ck_op_supported(op) for op in range(14)] == [1] * 7 + [0] * 7
+
+    class KernelId(C.Structure):
+        _fields_ = [("layer", C.c_uint16), ("node", C.c_uint16)]
+
+    class InputRef(C.Structure):
+        _fields_ = [("producer", KernelId), ("out_index", C.c_uint8)]
+
+    class Node(C.Structure):
+        _fields_ = [("id", KernelId), ("op", C.c_int), ("inputs", InputRef * 4), ("n_inputs", C.c_uint8), ("n_outputs", C.c_uint8)]
+
+    class Cfg(C.Structure):
+        _fields_ = [(n, C.c_int) for n in ("num_layers", "hidden_size", "intermediate_size", "num_heads", "num_kv_heads", "vocab_size", "context_window")] + \
+                   [("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("rotary_dim", C.c_int), ("rope_scaling_factor", C.c_float),
+                    ("rope_scaling_type", C.c_char * 16)]
+
+    class Graph(C.Structure):
+        _fields_ = [("config", Cfg), ("num_nodes", C.c_int), ("nodes", C.POINTER(Node))]
+
+    nodes = (Node * 3)()
+    for i, op in enumerate((0, 2, 6)):
+        nodes[i].op = op
+    g = Graph()
+    g.num_nodes, g.nodes = 3, nodes
+    assert lib.ck_ir_validate_supported(C.byref(g)) == 0
+    nodes[1].op = 9                                   # ATTENTION_BWD
+    assert lib.ck_ir_validate_supported(C.byref(g)) == -1
+    assert lib.ck_ir_validate_supported(None) == -1
+    lib.ckb200_op_kernels.restype = C.c_char_p
+    assert b"gemv_q4_k_q8_k" in lib.ckb200_op_kernels(1) and lib.ckb200_op_kernels(9) is None
 
 
 def test_every_header_entry_cites_the_reference():

@@ -54,6 +54,14 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -475,6 +483,11 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             except Exception as exc:                      # the headline metric above must survive a failure here
                 line["decode"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()
+            try:
+                line["prefill"] = prefill_bench(lib, 512, 20, sp, torch, measured_tensor_peak())
+            except Exception as exc:
+                line["prefill"] = {"error": repr(exc)}
+                lib.ckb200_clear_error()
         if decode_tp is not None:
             line["decode_tp"] = decode_tp
         if world == 1 and not args.no_cpu:
@@ -483,6 +496,115 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     if dist:
         dist.barrier()
         dist.destroy_process_group()
+
+
+PREFILL_SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336)]      # (N, K) of the Llama-3-8B projections
+
+
+def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
+    """Batched quantised GEMM C[M,N] = A_q8k[M,K] . W_q4k[N,K]^T at prefill size (tcgen05 kernel), per projection shape."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {"workload": f"Llama-3-8B-shaped prefill GEMM, Q4_K x Q8_K, M={m_tokens}", "shapes": {}}
+    flops_total, ms_total = 0.0, 0.0
+    for n, k in PREFILL_SHAPES:
+        w = torch.from_numpy(synth.make_weights("q4_k", n, k, seed=3)).to(dev)
+        a = torch.from_numpy(synth.make_x(k, seed=3, rows=m_tokens)).to(dev)
+        aq = torch.empty(m_tokens * synth.row_bytes("q8_k", k) + 64, dtype=torch.uint8, device=dev)
+        c = torch.empty(m_tokens, n, dtype=torch.float32, device=dev)
+        assert lib.ckb200_dev_quantize_q8_k(C.c_void_p(a.data_ptr()), C.c_void_p(aq.data_ptr()), m_tokens, k, stream_ptr) == 0
+
+        def run():
+            rc = lib.ckb200_dev_gemm_nt_q4_k_q8_k(C.c_void_p(aq.data_ptr()), C.c_void_p(w.data_ptr()), None, C.c_void_p(c.data_ptr()),
+                                                  m_tokens, n, k, stream_ptr)
+            if rc != 0:
+                raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        st = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            run()
+        e1.record(st)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        flops = 2.0 * m_tokens * n * k
+        out["shapes"][f"{n}x{k}"] = {"ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": m_tokens / ms * 1e3}
+        flops_total += flops
+        ms_total += ms
+    out["tflops"] = flops_total / ms_total / 1e9
+    out["roofline"] = {"bound": "tensor", "achieved": out["tflops"], "peak": tensor_peak, "unit": "TFLOP/s", "frac": out["tflops"] / tensor_peak,
+                       "note": "2*M*N*K of the f16 MMA; peak = measured cuBLAS bf16 burst"}
+    if lib.ckb200_synchronize() != 0:
+        raise RuntimeError(lib.ckb200_last_error_message().decode())
+    return out
+
+
+def run_prefill_only(args):
+    """Plain launches of the prefill GEMM: the command behind the tensor-core profile."""
+    import torch
+
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    print(json.dumps(prefill_bench(lib, args.prefill_only, args.launches, None, torch, measured_tensor_peak())))
+
+
+def run_single(args):
+    """A few plain (un-captured) launches of one GEMV on rotating weight copies: the small case for ncu captures."""
+    import torch
+
+    fmt, shape = args.single.split(":")
+    m, k = (int(v) for v in shape.split("x"))
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    dev = torch.device("cuda", 0)
+    gemv = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}[fmt]
+    quant = lib.ckb200_dev_quantize_q8_0 if fmt == "q8_0" else lib.ckb200_dev_quantize_q8_k
+    w_host = synth.make_weights(fmt, m, k, seed=1)
+    nbytes = w_host.nbytes
+    copies = max(2, min(8, -(-600_000_000 // nbytes)))          # > L2 in total, well under 1 GB on the device
+    slot = (nbytes + 255) & ~255
+    wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
+    src = torch.from_numpy(w_host).to(dev)
+    for c in range(copies):
+        wbuf[c * slot:c * slot + nbytes].copy_(src)
+    x = torch.from_numpy(synth.make_x(k, seed=1)).to(dev)
+    xq = torch.empty(synth.row_bytes("q8_0" if fmt == "q8_0" else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
+    y = torch.empty(copies, m, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    assert quant(C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, None) == 0
+    for i in range(args.launches):
+        c = i % copies
+        assert gemv(C.c_void_p(y[c].data_ptr()), C.c_void_p(wbuf.data_ptr() + c * slot), C.c_void_p(xq.data_ptr()), m, k, None) == 0
+    assert lib.ckb200_synchronize() == 0
+    print(json.dumps({"single": args.single, "launches": args.launches, "copies": copies, "bytes_per_launch": synth.gemv_bytes(fmt, m, k)}))
+
+
+def run_decode_only(args):
+    """Eager (un-captured) decode steps of a model shape: the command behind the decode launch lists in profiles/."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cases
+    import step_oracle as so
+
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    so.bind_model_api(lib)
+    cfg, ctx = (QWEN2_05B, 1024) if args.decode_only == "qwen2-0.5b" else (LLAMA3_70B, 4096)
+    lib.ckb200_tune_set(b"model_graph", 0)
+    st = so.make_cfg(cfg, batch=1)
+    h = lib.ckb200_model_create(C.byref(st))
+    assert h, lib.ckb200_last_error_message()
+    assert lib.ckb200_model_fill_synthetic(h, 1) == 0 and lib.ckb200_model_fill_kv_synthetic(h, ctx, 2) == 0
+    ids = np.array([11], np.int32)
+    lib.ckb200_launch_count.restype = C.c_longlong
+    n0 = lib.ckb200_launch_count()
+    for _ in range(args.steps):
+        assert lib.ckb200_model_decode(h, cases.vptr(ids), None) == 0
+    assert lib.ckb200_synchronize() == 0
+    print(json.dumps({"decode_only": args.decode_only, "steps": args.steps, "launches_per_step": (lib.ckb200_launch_count() - n0) // args.steps}))
+    lib.ckb200_model_free(h)
 
 
 def main():
@@ -494,7 +616,17 @@ def main():
     ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
+    ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
+    ap.add_argument("--launches", type=int, default=8)
+    ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
+    ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
     args = ap.parse_args()
+    if args.single:
+        return run_single(args)
+    if args.decode_only:
+        return run_decode_only(args)
+    if args.prefill_only:
+        return run_prefill_only(args)
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -13,6 +13,7 @@ extern "C" int ckb200_dev_gemv_q4_k_q8_k(float *, const void *, const void *, in
 extern "C" int ckb200_dev_gemv_q6_k_q8_k(float *, const void *, const void *, int, int, void *);
 extern "C" int ckb200_dev_gemv_q8_0_q8_0(float *, const void *, const void *, int, int, void *);
 extern "C" int ckb200_dev_add_bias_rows(float *, const float *, int, int, void *);
+extern "C" int ckb_launch_gemm_q4k_tc(const void *, const void *, const float *, float *, int, int, int, void *);
 
 typedef int (*gemv_fn)(float *, const void *, const void *, int, int, void *);
 
@@ -29,6 +30,10 @@ static int gemm_nt_by_rows(gemv_fn fn, size_t a_row_bytes, const void *A_q8, con
 
 extern "C" int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
 {
+    if (A_q8 && B && C && M > 0 && N > 0 && K > 0) {
+        const int rc = ckb_launch_gemm_q4k_tc(A_q8, B, bias, C, M, N, K, stream);
+        if (rc >= 0) return rc;
+    }
     return gemm_nt_by_rows(ckb200_dev_gemv_q4_k_q8_k, (size_t)(K / 256) * ckb::Q8K_BYTES, A_q8, B, bias, C, M, N, K, stream);
 }
 extern "C" int ckb200_dev_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)

@@ -205,6 +205,38 @@ def test_gemm_nt_matches_loop_of_gemv(ck, orc, fmt, m, n, k):
     assert_fp32_close(got, want, fmt)
 
 
+@pytest.mark.parametrize("m,n,k,with_bias", [(64, 128, 256, False), (128, 256, 1024, True), (200, 200, 512, True), (512, 384, 4096, False),
+                                               (65, 129, 768, True), (300, 1000, 2048, False)])
+def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
+    """M >= 64 takes the tcgen05 kernel: full tiles, ragged token and row edges, one and many superblocks."""
+    w = synth.make_weights("q4_k", n, k, seed=m + n)
+    a = synth.make_x(k, seed=m, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32) if with_bias else None
+    got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+    want = cases.gemm_nt(orc, "oracle_", "q4_k", aq, w, bias, m, n, k)
+    assert_fp32_close(got, want, "q4_k")
+    ck.ckb200_tune_set(b"gemm_tc", 0)
+    try:
+        by_rows = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+    finally:
+        ck.ckb200_tune_set(b"gemm_tc", 1)
+    assert_fp32_close(by_rows, want, "q4_k")
+
+
+def test_gemm_nt_q4_k_tensor_core_extreme_values(ck, orc):
+    """Largest scales, nibbles and activations: the integer sums reach the top of the fp32-exact range."""
+    m, n, k = 64, 128, 512
+    w = synth.make_weights("q4_k", n, k, seed=9).reshape(n, k // 256, 144).copy()
+    w[:, :, 4:16] = 0xFF          # every 6-bit scale and min = 63
+    w[:, :, 16:] = 0xFF           # every nibble = 15
+    a = np.where(np.arange(k) % 3 == 0, -1.0, 1.0).astype(np.float32)[None, :].repeat(m, 0) * np.linspace(0.5, 2.0, m, dtype=np.float32)[:, None]
+    aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
+    got = cases.gemm_nt(ck, "", "q4_k", aq, w.reshape(-1), None, m, n, k)
+    want = cases.gemm_nt(orc, "oracle_", "q4_k", aq, w.reshape(-1), None, m, n, k)
+    assert_fp32_close(got, want, "q4_k")
+
+
 # ---------------------------------------------------------------- decode attention + KV cache
 
 ATTN_CASES = [  # heads, kv_heads, d(aligned), head_dim, tokens, capacity

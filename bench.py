@@ -522,7 +522,11 @@ def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
         for _ in range(3):
             run()
         torch.cuda.synchronize()
-        st = torch.cuda.current_stream()
+        if stream_ptr is None:                             # launches go to the library's own stream: time on that one
+            lib.ckb200_stream.restype = C.c_void_p
+            st = torch.cuda.ExternalStream(lib.ckb200_stream())
+        else:
+            st = torch.cuda.current_stream()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(st)
         for _ in range(iters):
@@ -548,6 +552,7 @@ def run_prefill_only(args):
 
     lib = pkg.load_lib()
     assert lib.ckb200_init(0) == 0
+    lib.ckb200_tune_set(b"gemm_tc_nh", args.token_tiles)
     print(json.dumps(prefill_bench(lib, args.prefill_only, args.launches, None, torch, measured_tensor_peak())))
 
 
@@ -619,6 +624,7 @@ def main():
     ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
+    ap.add_argument("--token-tiles", type=int, default=0, choices=[0, 1, 2], help="with --prefill-only: 128-token tiles per CTA (0 = automatic)")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
     args = ap.parse_args()
     if args.single:

@@ -213,14 +213,17 @@ def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
     a = synth.make_x(k, seed=m, rows=m)
     aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
     bias = np.random.default_rng(n).standard_normal(n).astype(np.float32) if with_bias else None
-    got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
     want = cases.gemm_nt(orc, "oracle_", "q4_k", aq, w, bias, m, n, k)
-    assert_fp32_close(got, want, "q4_k")
-    ck.ckb200_tune_set(b"gemm_tc", 0)
     try:
+        for token_tiles_per_cta in (0, 1, 2):         # 0 = the launcher's own choice
+            ck.ckb200_tune_set(b"gemm_tc_nh", token_tiles_per_cta)
+            got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+            assert_fp32_close(got, want, f"q4_k tiles/cta={token_tiles_per_cta}")
+        ck.ckb200_tune_set(b"gemm_tc", 0)
         by_rows = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
     finally:
         ck.ckb200_tune_set(b"gemm_tc", 1)
+        ck.ckb200_tune_set(b"gemm_tc_nh", 0)
     assert_fp32_close(by_rows, want, "q4_k")
 
 

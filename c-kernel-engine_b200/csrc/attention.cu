@@ -17,24 +17,11 @@
 // and a merge kernel combines them with the exact log-sum-exp rule.
 #include "device_common.cuh"
 #include "pdl.cuh"
+#include "attention_params.cuh"
 
 #include <math.h>
 
 namespace ckb {
-
-struct AttnParams {
-    const float *q;        // [batch][H][ad]
-    const float *k;        // [batch][Hkv][cap][ad] (batch stride kv_batch_stride floats)
-    const float *v;
-    float *out;            // [batch][H][ad]
-    float *part;           // scratch [batch][H][splits][ad + 2] (only when splits > 1)
-    const int *pos_ptr;    // when not NULL the context length is *pos_ptr + 1 (read on the device, graph-replayable)
-    long long kv_batch_stride;
-    int H, Hkv, kv_tokens, cap, ad, splits;
-    float scale;
-};
-
-__device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(__ldcg(p.pos_ptr) + 1, p.cap) : p.kv_tokens; }
 
 constexpr int ATTN_G = 8;        // max Q heads per kv head in the fast path
 constexpr int ATTN_NW = 4;       // warps per CTA
@@ -328,6 +315,8 @@ __global__ void __launch_bounds__(128) attn_decode_generic_kernel(AttnParams p)
 
 using namespace ckb;
 
+extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream);     // attention_tile.cu
+
 extern "C" size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits)
 {
     if (splits <= 1) return 0;
@@ -340,13 +329,15 @@ extern "C" int ckb200_attention_decode_splits(int batch, int num_kv_heads, int k
     const int forced = ckb_tune_get("attn_splits", 0);
     if (forced > 0) return forced;
     const int sms = ckb_sm_count();
-    const long long ctas_wanted = 2LL * sms;
+    const long long ctas_wanted = ckb_tune_get("attn_tile", 1) ? sms : 2LL * sms;   // the tile kernel fills an SM with one CTA
     const long long base = (long long)batch * num_kv_heads;
     int splits = (int)((ctas_wanted + base - 1) / base);
-    const int max_by_tokens = (kv_tokens + 63) / 64;        // at least 64 keys per split
-    if (splits > max_by_tokens) splits = max_by_tokens;
+    const int tiles = (kv_tokens + 63) / 64;                 // at least one 64-key tile per split
+    if (splits > tiles) splits = tiles;
     if (splits > 256) splits = 256;
     if (splits < 1) splits = 1;
+    const int tiles_per_split = (tiles + splits - 1) / splits;
+    splits = (tiles + tiles_per_split - 1) / tiles_per_split;   // no split without work
     return splits;
 }
 
@@ -382,8 +373,12 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
     p.splits = splits;
     const dim3 grid(splits, num_kv_heads, batch);
-    const int rc = aligned_head_dim == 64 ? launch_pdl("attn_decode", attn_decode_kernel<64>, grid, dim3(ATTN_NW * 32), 0, st, p)
-                                          : launch_pdl("attn_decode", attn_decode_kernel<128>, grid, dim3(ATTN_NW * 32), 0, st, p);
+    int rc;
+    if (ckb_tune_get("attn_tile", 1))
+        rc = ckb_launch_attn_tile(&p, batch, st);
+    else
+        rc = aligned_head_dim == 64 ? launch_pdl("attn_decode", attn_decode_kernel<64>, grid, dim3(ATTN_NW * 32), 0, st, p)
+                                    : launch_pdl("attn_decode", attn_decode_kernel<128>, grid, dim3(ATTN_NW * 32), 0, st, p);
     if (rc) return rc;
     if (splits > 1)
         return launch_pdl("attn_merge", attn_merge_kernel, dim3(batch * num_heads), dim3(128), 0, st, (const float *)scratch, out, splits,

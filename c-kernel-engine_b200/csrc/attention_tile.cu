@@ -1,0 +1,275 @@
+// Decode attention, bandwidth form: K/V tiles of 64 keys are brought into shared memory with 1-D bulk copies
+// (three stages per CTA, so two tiles are always in flight) and every warp works on 8 keys of the tile.
+//
+// Same mathematics as attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406;
+// per head attention_flash_decode, src/kernels/attention_flash_true.c:142-230): scores (q.k)/sqrt(head_dim),
+// softmax, out = P.V, kv_head = h * Hkv / H.  In the head-major cache the rows t .. t+63 of one kv head are one
+// contiguous range of 64 * ad * 4 bytes, so a tile is two bulk copies (K and V), each completing on the
+// stage's mbarrier.
+//
+// A warp takes 2 keys per step with 16 lanes per key (each lane owns ad/16 dimensions, read as float4 so that
+// 16 lanes read 256 contiguous bytes of shared memory); the query of all <= 8 Q heads of the group lives in
+// registers.  The 8 partial dots of a step are reduced with a transposing butterfly, which leaves lane li with
+// the score of head li & 7.  The softmax is updated once per 8 keys (tile maximum, one rescale of the
+// accumulators) instead of once per key.  Splits write (max, sum, unnormalised out) partials that
+// attn_merge_kernel combines with the exact log-sum-exp rule.
+//
+// All mbarrier waits are bounded; on a timeout the CTA records the device error word and leaves.
+#include "attention_params.cuh"
+#include "launch.h"
+#include "pdl.cuh"
+#include "runtime.h"
+
+#include <math.h>
+
+namespace ckb {
+
+constexpr int AT_NW = 8;            // warps per CTA
+constexpr int AT_KT = 64;           // keys per tile
+constexpr int AT_STAGES = 3;
+constexpr int AT_LPK = 16;          // lanes per key
+
+template <int AD> constexpr int at_stage_bytes() { return 2 * AT_KT * AD * 4; }
+template <int AD> constexpr int at_smem_bytes() { return AT_STAGES * at_stage_bytes<AD>() + 2 * AT_STAGES * 8 + 16; }
+
+template <int AD>
+__global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, int *__restrict__ dev_err)
+{
+    constexpr int C = AD / (4 * AT_LPK);           // float4 pieces per lane (1 for 64, 2 for 128)
+    constexpr int G = ATTN_MAX_GROUP;
+    constexpr int KPW = AT_KT / AT_NW;             // keys per warp per tile
+    constexpr int STEPS = KPW / 2;
+    constexpr int ROW = AD * 4;                    // bytes per cache row
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t s_bar = s_base + AT_STAGES * at_stage_bytes<AD>();
+#define AT_FULL(i) (s_bar + 8u * (uint32_t)(i))
+#define AT_EMPTY(i) (s_bar + 8u * (uint32_t)(AT_STAGES + (i)))
+
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / AT_LPK, li = lane % AT_LPK;
+    const int group = p.H / p.Hkv, h0 = kvh * group;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < AT_STAGES; ++i) { mbar_init(AT_FULL(i), 1); mbar_init(AT_EMPTY(i), AT_NW); }
+        mbar_fence_init();
+    }
+    pdl_trigger();
+    __syncthreads();
+    pdl_wait();           // q, the newest cache row and the position come from kernels that may still have been running
+
+    const int kv_tokens = attn_kv_tokens(p);
+    const int ntiles_all = (kv_tokens + AT_KT - 1) / AT_KT;
+    const int tiles_per_split = (ntiles_all + p.splits - 1) / p.splits;
+    const int tile0 = split * tiles_per_split;
+    const int ntiles = max(0, min(ntiles_all, tile0 + tiles_per_split) - tile0);
+    const uint8_t *kbase = reinterpret_cast<const uint8_t *>(p.k + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD);
+    const uint8_t *vbase = reinterpret_cast<const uint8_t *>(p.v + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD);
+
+    auto issue_tile = [&](int i) {                 // one thread: both copies of tile i of this split
+        const int st = i % AT_STAGES, t_begin = (tile0 + i) * AT_KT;
+        const uint32_t bytes = (uint32_t)min(AT_KT, kv_tokens - t_begin) * ROW;
+        const uint32_t dst = s_base + st * at_stage_bytes<AD>();
+        mbar_arrive_expect_tx(AT_FULL(st), 2 * bytes);
+        bulk_g2s(dst, kbase + (size_t)t_begin * ROW, bytes, AT_FULL(st));
+        bulk_g2s(dst + AT_KT * ROW, vbase + (size_t)t_begin * ROW, bytes, AT_FULL(st));
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < min(ntiles, AT_STAGES - 1); ++i) issue_tile(i);
+
+    // query of the group's heads, pre-scaled, this lane's dimensions
+    float4 q[G][C];
+#pragma unroll
+    for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (h < group) v = __ldcg(reinterpret_cast<const float4 *>(p.q + ((size_t)seq * p.H + h0 + h) * AD) + c * AT_LPK + li);
+            q[h][c] = make_float4(v.x * p.scale, v.y * p.scale, v.z * p.scale, v.w * p.scale);
+        }
+
+    float m_run = -INFINITY, l_run = 0.0f;         // of head li & 7 (the same value on the lanes that share it)
+    float4 acc[G][C];
+#pragma unroll
+    for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int c = 0; c < C; ++c) acc[h][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    bool ok = true;
+    for (int i = 0; i < ntiles; ++i) {
+        const int st = i % AT_STAGES;
+        if (threadIdx.x == 0 && i + AT_STAGES - 1 < ntiles) {
+            // the stage of tile i + STAGES - 1 was last used by tile i - 1: wait until all warps have released it
+            const int j = i + AT_STAGES - 1;
+            if (i >= 1 && !mbar_wait_spin(AT_EMPTY(j % AT_STAGES), (uint32_t)(((j / AT_STAGES) - 1) & 1))) ok = false;
+            if (ok) issue_tile(j);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;      // warp 0 follows its lane 0
+        if (!ok || !mbar_wait_spin(AT_FULL(st), (uint32_t)((i / AT_STAGES) & 1))) { ok = false; break; }
+
+        const int t_tile = (tile0 + i) * AT_KT;
+        const int nvalid = min(AT_KT, kv_tokens - t_tile);
+        const uint32_t ks = s_base + st * at_stage_bytes<AD>() + (uint32_t)(warp * KPW) * ROW, vs = ks + AT_KT * ROW;
+
+        // ---- scores of this warp's 8 keys: sc[step] = score(head li & 7, key 2 * step + sub)
+        float sc[STEPS];
+#pragma unroll
+        for (int step = 0; step < STEPS; ++step) {
+            const int key = 2 * step + sub;
+            float4 kr[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) kr[c] = lds_f4(ks + (uint32_t)key * ROW + (uint32_t)(c * AT_LPK + li) * 16u);
+            float s[G];
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                float a = 0.0f;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    a = fmaf(q[h][c].x, kr[c].x, a);
+                    a = fmaf(q[h][c].y, kr[c].y, a);
+                    a = fmaf(q[h][c].z, kr[c].z, a);
+                    a = fmaf(q[h][c].w, kr[c].w, a);
+                }
+                s[h] = a;
+            }
+            // transposing butterfly over lane bits 2, 1, 0, then a plain add over bit 3
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float mine = (li & 4) ? s[j + 4] : s[j], theirs = (li & 4) ? s[j] : s[j + 4];
+                s[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, 4);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float mine = (li & 2) ? s[j + 2] : s[j], theirs = (li & 2) ? s[j] : s[j + 2];
+                s[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, 2);
+            }
+            {
+                const float mine = (li & 1) ? s[1] : s[0], theirs = (li & 1) ? s[0] : s[1];
+                s[0] = mine + __shfl_xor_sync(0xffffffffu, theirs, 1);
+            }
+            s[0] += __shfl_xor_sync(0xffffffffu, s[0], 8);
+            sc[step] = (warp * KPW + key < nvalid) ? s[0] : -INFINITY;
+        }
+
+        // ---- softmax update for these 8 keys (per head; identical on the lanes that share the head)
+        float tmax = sc[0];
+#pragma unroll
+        for (int step = 1; step < STEPS; ++step) tmax = fmaxf(tmax, sc[step]);
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+        const float m_new = fmaxf(m_run, tmax);
+        const float corr = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
+        float pw[STEPS], psum = 0.0f;
+#pragma unroll
+        for (int step = 0; step < STEPS; ++step) {
+            pw[step] = sc[step] == -INFINITY ? 0.0f : expf(sc[step] - m_new);
+            psum += pw[step];
+        }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+        l_run = l_run * corr + psum;
+        m_run = m_new;
+
+        // ---- rescale once, then accumulate P.V
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            const float ch = __shfl_sync(0xffffffffu, corr, h);
+#pragma unroll
+            for (int c = 0; c < C; ++c) { acc[h][c].x *= ch; acc[h][c].y *= ch; acc[h][c].z *= ch; acc[h][c].w *= ch; }
+        }
+#pragma unroll
+        for (int step = 0; step < STEPS; ++step) {
+            const int key = 2 * step + sub;
+            const bool valid = warp * KPW + key < nvalid;      // rows past the end of the context were never copied
+            float4 vr[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                vr[c] = lds_f4(vs + (uint32_t)key * ROW + (uint32_t)(c * AT_LPK + li) * 16u);
+                if (!valid) vr[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float ph = __shfl_sync(0xffffffffu, pw[step], sub * AT_LPK + h);
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    acc[h][c].x = fmaf(ph, vr[c].x, acc[h][c].x);
+                    acc[h][c].y = fmaf(ph, vr[c].y, acc[h][c].y);
+                    acc[h][c].z = fmaf(ph, vr[c].z, acc[h][c].z);
+                    acc[h][c].w = fmaf(ph, vr[c].w, acc[h][c].w);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(AT_EMPTY(st));
+    }
+    if (!ok && lane == 0) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;       // every issued copy has landed and been consumed when all warps got here
+    if (!ok) return;
+
+    // ---- the two key streams of the warp share (m, l): add their accumulators; then merge the warps through shared memory
+    float *merge_s = reinterpret_cast<float *>(smem);              // [AT_NW][G][AD + 4], over the (now idle) stages
+#pragma unroll
+    for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            acc[h][c].x += __shfl_xor_sync(0xffffffffu, acc[h][c].x, 16);
+            acc[h][c].y += __shfl_xor_sync(0xffffffffu, acc[h][c].y, 16);
+            acc[h][c].z += __shfl_xor_sync(0xffffffffu, acc[h][c].z, 16);
+            acc[h][c].w += __shfl_xor_sync(0xffffffffu, acc[h][c].w, 16);
+        }
+    if (sub == 0) {
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int c = 0; c < C; ++c) *reinterpret_cast<float4 *>(&merge_s[((warp * G + h) * (AD + 4)) + (c * AT_LPK + li) * 4]) = acc[h][c];
+        if (li < G) {
+            merge_s[(warp * G + li) * (AD + 4) + AD] = m_run;
+            merge_s[(warp * G + li) * (AD + 4) + AD + 1] = l_run;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * AD; i += blockDim.x) {
+        const int h = i / AD, c = i - h * AD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AT_NW; ++w) mm = fmaxf(mm, merge_s[(w * G + h) * (AD + 4) + AD]);
+        float ll = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < AT_NW; ++w) {
+            const float mw = merge_s[(w * G + h) * (AD + 4) + AD];
+            const float f = mw == -INFINITY ? 0.0f : expf(mw - mm);
+            ll += merge_s[(w * G + h) * (AD + 4) + AD + 1] * f;
+            a += merge_s[(w * G + h) * (AD + 4) + c] * f;
+        }
+        const size_t head = (size_t)seq * p.H + h0 + h;
+        if (p.splits == 1) {
+            p.out[head * AD + c] = ll > 0.0f ? a / ll : 0.0f;
+        } else {
+            float *dst = p.part + (head * p.splits + split) * (AD + 2);
+            dst[c] = a;
+            if (c == 0) { dst[AD] = mm; dst[AD + 1] = ll; }
+        }
+    }
+#undef AT_FULL
+#undef AT_EMPTY
+}
+
+}  // namespace ckb
+
+using namespace ckb;
+
+// Launches the tile kernel for aligned_head_dim 64 or 128; the caller has checked group size and alignment.
+extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream)
+{
+    const int ad = p->ad;
+    const int smem = ad == 64 ? at_smem_bytes<64>() : at_smem_bytes<128>();
+    static int attr_set[2] = {0, 0};
+    if (!attr_set[ad == 128]) {
+        const cudaError_t e = ad == 64 ? cudaFuncSetAttribute(attn_tile_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                                       : cudaFuncSetAttribute(attn_tile_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (ckb_check_cuda((int)e, "attention smem attr")) return CKB_ERR_CUDA;
+        attr_set[ad == 128] = 1;
+    }
+    const dim3 grid(p->splits, p->Hkv, batch);
+    return ad == 64 ? launch_pdl("attn_tile", attn_tile_kernel<64>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word())
+                    : launch_pdl("attn_tile", attn_tile_kernel<128>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word());
+}

@@ -59,6 +59,11 @@ __device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
     unsigned short v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -120,6 +125,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
         if (i > 64) __nanosleep(64);
     }
     return false;
+}
+// Same contract, for pipelines whose barriers are usually complete already: polls without sleeping and gives up
+// after about a second of SM clock cycles.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 31)) return false;
+    }
 }
 // src and dst 16-byte aligned, bytes a multiple of 16.  No multicast: one CTA, its own shared memory.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {

@@ -186,20 +186,6 @@ struct Q4Stage {
     uint4 qa, qb;
 };
 
-// Bounded wait on an mbarrier phase: polls without sleeping (the common case is a barrier that is complete or about
-// to be) and gives up after about a second of SM clock cycles.
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > (1ll << 31)) return false;
-    }
-}
-
 // In-kernel cycle counters of CTA (0,0), written over the first output row: a tuning aid, compiled out by default.
 #ifdef CKB_TC_PROFILE
 __device__ float g_tc_prof[64];
@@ -258,7 +244,7 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
     constexpr int REGS_CTL = TcRegs<NH, EW>::CTL, REGS_EXP = TcRegs<NH, EW>::EXP, REGS_DRAIN = TcRegs<NH, EW>::DRAIN;
 #define TC_SETMAXNREG(op, n) asm volatile("setmaxnreg." op ".sync.aligned.u32 %0;" ::"n"(n))
 #define TC_WAIT(bar, parity, code)                                        \
-    if (!tc_wait(bar, parity)) { atomicExch(dev_err, code); break; }
+    if (!mbar_wait_spin(bar, parity)) { atomicExch(dev_err, code); break; }
 
     if (warp < 4) {
         TC_SETMAXNREG("dec", REGS_CTL);
@@ -298,7 +284,7 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
                 }
             }
             if (!go) {                                 // copies still in flight must land before the CTA's shared memory goes away
-                for (uint32_t c = cb > 4 ? cb - 4 : 0; c < cb; ++c) tc_wait(BAR(BAR_B_FULL + (c & 3u)), (c >> 2) & 1u);
+                for (uint32_t c = cb > 4 ? cb - 4 : 0; c < cb; ++c) mbar_wait_spin(BAR(BAR_B_FULL + (c & 3u)), (c >> 2) & 1u);
             }
             if (lane == 0) TC_PROF_OUT(0);
         } else if (warp == 1) {

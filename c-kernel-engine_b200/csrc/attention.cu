@@ -357,6 +357,7 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0;
     cudaStream_t st = ckb_stream(stream);
     const int group = num_heads / num_kv_heads;
     const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 &&
@@ -384,6 +385,52 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
         return launch_pdl("attn_merge", attn_merge_kernel, dim3(batch * num_heads), dim3(128), 0, st, (const float *)scratch, out, splits,
                           aligned_head_dim);
     return 0;
+}
+
+extern "C" int ckb200_dev_quantize_q8_k(const float *, void *, int, int, void *);
+
+extern "C" size_t ckb200_attention_decode_counter_bytes(int batch, int num_kv_heads) { return (size_t)batch * (num_kv_heads + 1) * sizeof(int); }
+
+// One launch for attention + split merge + Q8_K quantisation of the finished rows (what the o-projection GEMV
+// consumes).  out rows are out_stride floats apart and the q8_cols - H*ad floats after each row must be zero;
+// `counters` is ckb200_attention_decode_counter_bytes() of device memory that was zero before the first call
+// (every call leaves it zero).  Shapes outside the tile kernel's fast path run as separate launches.
+extern "C" int ckb200_dev_attention_decode_fused(const float *q, const float *k_cache, const float *v_cache, float *out, int out_stride,
+                                                 int batch, long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
+                                                 int cache_capacity, int head_dim, int aligned_head_dim, int splits, float *scratch,
+                                                 int *counters, const int *pos_dev, void *q8_out, int q8_cols, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !out || !counters) return 0;
+    if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return 0;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const int group = num_heads / num_kv_heads;
+    const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 && group <= ATTN_G &&
+                      (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) == 0 && (kv_batch_stride % 4) == 0 &&
+                      out_stride % 4 == 0 && ckb_tune_get("attn_generic", 0) == 0 && ckb_tune_get("attn_tile", 1) && ckb_tune_get("attn_fused", 1) &&
+                      (!q8_out || (q8_cols % 256 == 0 && q8_cols <= out_stride && q8_cols >= num_heads * aligned_head_dim));
+    if (!fast) {
+        if (out_stride != num_heads * aligned_head_dim && batch > 1)
+            return ckb_fail(CKB_ERR_SHAPE, "attention decode (fused): this shape needs densely packed output rows");
+        int rc = ckb200_dev_attention_decode_ws(q, k_cache, v_cache, out, batch, kv_batch_stride, num_heads, num_kv_heads, kv_tokens, cache_capacity,
+                                                head_dim, aligned_head_dim, splits, scratch, pos_dev, stream);
+        if (!rc && q8_out) {
+            for (int b = 0; b < batch && !rc; ++b)
+                rc = ckb200_dev_quantize_q8_k(out + (size_t)b * out_stride, (uint8_t *)q8_out + (size_t)b * (q8_cols / 256) * Q8K_BYTES, 1, q8_cols, stream);
+        }
+        return rc;
+    }
+    if (splits < 1) splits = 1;
+    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
+    if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
+    AttnParams p;
+    p.q = q; p.k = k_cache; p.v = v_cache; p.out = out; p.part = scratch; p.pos_ptr = pos_dev;
+    p.kv_batch_stride = kv_batch_stride;
+    p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
+    p.scale = 1.0f / sqrtf((float)head_dim);
+    p.splits = splits;
+    p.counters = counters; p.q8_out = (uint8_t *)q8_out; p.out_stride = out_stride; p.q8_cols = q8_cols;
+    return ckb_launch_attn_tile(&p, batch, ckb_stream(stream));
 }
 
 // Convenience form: picks the split count and takes the scratch from the library's own pool.
@@ -478,6 +525,7 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (!fast) {
         if (aligned_head_dim > ATTN_GEN_MAXD) return ckb_fail(CKB_ERR_LIMIT, "attention decode: aligned_head_dim %d > %d", aligned_head_dim, ATTN_GEN_MAXD);

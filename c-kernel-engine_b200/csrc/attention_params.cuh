@@ -14,6 +14,13 @@ struct AttnParams {
     long long kv_batch_stride;
     int H, Hkv, kv_tokens, cap, ad, splits;
     float scale;
+    // Fused tail of the tile kernel (all optional).  `counters` (zero on entry, left zero on exit) holds one arrival
+    // count per (sequence, kv head) followed by one per sequence: the last split CTA of a kv head merges its heads'
+    // partials, and the last kv head of a sequence quantises the finished row to Q8_K blocks for the consumer GEMV.
+    int *counters;
+    uint8_t *q8_out;       // [batch][q8_cols / 256] Q8_K blocks, or NULL
+    int out_stride;        // floats between the out rows of consecutive sequences (>= H * ad)
+    int q8_cols;           // elements quantised per row (multiple of 256, <= out_stride; the row's tail must be zero)
 };
 
 __device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(__ldcg(p.pos_ptr) + 1, p.cap) : p.kv_tokens; }

@@ -18,6 +18,7 @@
 #include "attention_params.cuh"
 #include "launch.h"
 #include "pdl.cuh"
+#include "q8k_block.cuh"
 #include "runtime.h"
 
 #include <math.h>
@@ -227,6 +228,7 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         }
     }
     __syncthreads();
+    const bool fused = p.counters != nullptr;
     for (int i = threadIdx.x; i < group * AD; i += blockDim.x) {
         const int h = i / AD, c = i - h * AD;
         float mm = -INFINITY;
@@ -242,12 +244,86 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         }
         const size_t head = (size_t)seq * p.H + h0 + h;
         if (p.splits == 1) {
-            p.out[head * AD + c] = ll > 0.0f ? a / ll : 0.0f;
+            p.out[(size_t)seq * p.out_stride + (size_t)(h0 + h) * AD + c] = ll > 0.0f ? a / ll : 0.0f;
         } else {
             float *dst = p.part + (head * p.splits + split) * (AD + 2);
             dst[c] = a;
             if (c == 0) { dst[AD] = mm; dst[AD + 1] = ll; }
         }
+    }
+    if (!fused) return;
+
+    // ---- fused tail 1: the last split CTA of this (sequence, kv head) merges the partials of its heads
+    __shared__ int s_last;
+    float *f_s = merge_s + AT_NW * G * (AD + 4);       // [G][splits] factors, then [G] inverse sums
+    if (p.splits > 1) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int *cnt = p.counters + seq * p.Hkv + kvh;
+            const int prev = atomicAdd(cnt, 1);
+            s_last = prev == p.splits - 1;
+            if (s_last) *cnt = 0;                      // ready for the next launch
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const int S = p.splits;
+        const float *part0 = p.part + ((size_t)seq * p.H + h0) * S * (AD + 2);
+        for (int i = threadIdx.x; i < group * S; i += blockDim.x) f_s[i] = __ldcg(part0 + (size_t)i * (AD + 2) + AD);
+        __syncthreads();
+        if (warp < group) {
+            float mm = -INFINITY;
+            for (int s2 = lane; s2 < S; s2 += 32) mm = fmaxf(mm, f_s[warp * S + s2]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+            float ll = 0.0f;
+            for (int s2 = lane; s2 < S; s2 += 32) {
+                const float ms = f_s[warp * S + s2];
+                const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
+                f_s[warp * S + s2] = f;
+                ll += __ldcg(part0 + (size_t)(warp * S + s2) * (AD + 2) + AD + 1) * f;
+            }
+            ll = group_sum<32>(ll);
+            if (lane == 0) f_s[G * S + warp] = ll > 0.0f ? 1.0f / ll : 0.0f;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < group * AD; i += blockDim.x) {
+            const int h = i / AD, c = i - h * AD;
+            const float *src = part0 + (size_t)h * S * (AD + 2) + c;
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            int s2 = 0;
+            for (; s2 + 4 <= S; s2 += 4) {
+                const float v0 = __ldcg(src + (size_t)(s2 + 0) * (AD + 2)), v1 = __ldcg(src + (size_t)(s2 + 1) * (AD + 2));
+                const float v2 = __ldcg(src + (size_t)(s2 + 2) * (AD + 2)), v3 = __ldcg(src + (size_t)(s2 + 3) * (AD + 2));
+                a0 = fmaf(v0, f_s[h * S + s2], a0); a1 = fmaf(v1, f_s[h * S + s2 + 1], a1);
+                a2 = fmaf(v2, f_s[h * S + s2 + 2], a2); a3 = fmaf(v3, f_s[h * S + s2 + 3], a3);
+            }
+            for (; s2 < S; ++s2) a0 = fmaf(__ldcg(src + (size_t)s2 * (AD + 2)), f_s[h * S + s2], a0);
+            p.out[(size_t)seq * p.out_stride + (size_t)(h0 + h) * AD + c] = ((a0 + a1) + (a2 + a3)) * f_s[G * S + h];
+        }
+    }
+    if (!p.q8_out) return;
+
+    // ---- fused tail 2: the last kv head of this sequence quantises the finished row for the consumer GEMV
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int *cnt = p.counters + gridDim.z * p.Hkv + seq;
+        const int prev = atomicAdd(cnt, 1);
+        s_last = prev == p.Hkv - 1;
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float *row = p.out + (size_t)seq * p.out_stride;
+    uint8_t *qrow = p.q8_out + (size_t)seq * (p.q8_cols / 256) * Q8K_BYTES;
+    for (int blk = warp; blk < p.q8_cols / 256; blk += AT_NW) {
+        const float4 lo = __ldcg(reinterpret_cast<const float4 *>(row + blk * 256) + 2 * lane);
+        const float4 hi = __ldcg(reinterpret_cast<const float4 *>(row + blk * 256) + 2 * lane + 1);
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        quantize_block_q8k(v, qrow + (size_t)blk * Q8K_BYTES, lane);
     }
 #undef AT_FULL
 #undef AT_EMPTY

@@ -125,7 +125,11 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_pair_kernel(const uint8_t *_
     constexpr int RPW = (32 / G) * R;          // rows per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int li = lane % G, sub = lane / G, p = li & 1, b0 = li >> 1;
-    const int ntiles = (M + NW * RPW - 1) / (NW * RPW);
+    // Work item = the RPW rows one warp reduces.  Item j belongs to CTA j % grid, warp slot j / grid, so the items are
+    // dealt round-robin over the CTAs (and with them over the SMs) instead of in blocks of NW: no SM ends up with a
+    // whole CTA more than its neighbour.
+    const int ntiles = (M + RPW - 1) / RPW;
+    const int tile_stride = gridDim.x * NW;
     const int npass = (nb + SPP - 1) / SPP;
     const size_t rb = (size_t)nb * Q4K_BYTES;
 
@@ -136,7 +140,7 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_pair_kernel(const uint8_t *_
         else return ldg_stream_u4(q);
     };
     auto load_item = [&](Q4pW (&w)[R], int tile, int pass) {
-        const int row0 = (tile * NW + warp) * RPW + sub * R;
+        const int row0 = tile * RPW + sub * R;
         const int b = min(b0 + pass * SPP, nb - 1);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -150,7 +154,7 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_pair_kernel(const uint8_t *_
     };
 
     Q4pW cur[R], nxt[R];
-    int tile = blockIdx.x, pass = 0;
+    int tile = blockIdx.x + gridDim.x * warp, pass = 0;
     if (tile < ntiles) load_item(cur, tile, 0);     // weights are never written by a kernel: safe before the wait
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -163,7 +167,7 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_pair_kernel(const uint8_t *_
 
     while (tile < ntiles) {
         int ntile = tile, npass_i = pass + 1;
-        if (npass_i == npass) { npass_i = 0; ntile = tile + gridDim.x; }
+        if (npass_i == npass) { npass_i = 0; ntile = tile + tile_stride; }
         if (ntile < ntiles) load_item(nxt, ntile, npass_i);
         const int b = b0 + pass * SPP;
         if (b < nb) {
@@ -171,7 +175,7 @@ __global__ void __launch_bounds__(NW * 32) gemv_q4k_pair_kernel(const uint8_t *_
             for (int r = 0; r < R; ++r) acc[r] += q4p_unit(cur[r], x, b, p);
         }
         if (npass_i == 0) {                          // row finished
-            const int row0 = (tile * NW + warp) * RPW + sub * R;
+            const int row0 = tile * RPW + sub * R;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const float s = group_sum<G>(acc[r]);
@@ -214,9 +218,13 @@ int launch_pair(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     }
     if (occ_cache_smem != smem) { occ_cache = occupancy_of(kernel, NW * 32, smem); occ_cache_smem = smem; }
     constexpr int rows_per_cta = NW * (32 / G) * R;
-    const int ntiles = (M + rows_per_cta - 1) / rows_per_cta;
+    const int ntiles = (M + rows_per_cta - 1) / rows_per_cta;    // CTAs needed if every warp took exactly one item
     const int cap = ckb_sm_count() * occ_cache;
-    const int grid = ntiles < cap ? ntiles : cap;
+    int grid = ntiles < cap ? ntiles : cap;
+    if (ntiles > ckb_sm_count() && grid % ckb_sm_count()) {       // a whole number of CTAs per SM, so that the round-robin deal is even
+        grid = (grid / ckb_sm_count() + 1) * ckb_sm_count();
+        if (grid > cap) grid = cap;
+    }
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);

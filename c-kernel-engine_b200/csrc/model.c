@@ -69,6 +69,10 @@ struct CKB200Model {
     int attn_splits;
     cudaGraphExec_t graph;
     int graph_ready;
+    /* q, k and v projections read the same quantised row and are independent: they run on three streams (forked and
+     * joined with events, which a stream capture turns into parallel branches of the step's graph) */
+    cudaStream_t side[2];
+    cudaEvent_t ev_fork, ev_join[2];
     int have_prev;
     ckb200_allreduce_fn allreduce;
     void *allreduce_ctx;
@@ -181,6 +185,11 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
         DEV_ALLOC(m->attn_scratch, sb ? sb : 256);
     }
     if (ok && ckb_check_cuda((int)cudaHostAlloc((void **)&m->tokens_pinned, (size_t)B * sizeof(int32_t), cudaHostAllocDefault), "cudaHostAlloc")) ok = 0;
+    for (int i = 0; ok && i < 2; ++i) {
+        if (ckb_check_cuda((int)cudaStreamCreateWithFlags(&m->side[i], cudaStreamNonBlocking), "side stream")) ok = 0;
+        if (ok && ckb_check_cuda((int)cudaEventCreateWithFlags(&m->ev_join[i], cudaEventDisableTiming), "join event")) ok = 0;
+    }
+    if (ok && ckb_check_cuda((int)cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming), "fork event")) ok = 0;
     if (!ok) { ckb200_model_free(m); return NULL; }
 #undef DEV_ALLOC
     /* offsets -> pointers */
@@ -212,6 +221,11 @@ void ckb200_model_free(CKB200Model *m)
                      m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch };
     for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
+    for (int i = 0; i < 2; ++i) {
+        if (m->side[i]) cudaStreamDestroy(m->side[i]);
+        if (m->ev_join[i]) cudaEventDestroy(m->ev_join[i]);
+    }
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
     free(m->layers);
     free(m);
 }
@@ -412,16 +426,31 @@ static int issue_step(CKB200Model *m, void *st)
         Tensor *t = m->layers[l].t;
         float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + (size_t)B * m->kv_batch_stride;
         if ((rc = norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
-        if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;
         if (t[CKB_T_WK].fmt != t[CKB_T_WQ].fmt && (t[CKB_T_WK].fmt == FMT_Q80 || t[CKB_T_WQ].fmt == FMT_Q80))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
-        if ((rc = matvec(m, &t[CKB_T_WK], m->hq, m->k, m->Hkvl * m->d, st))) return rc;
-        if ((rc = matvec(m, &t[CKB_T_WV], m->hq, m->v, m->Hkvl * m->d, st))) return rc;
+        if (ckb_tune_get("model_qkv_streams", 1)) {
+            cudaStream_t main_st = (cudaStream_t)st;
+            if (ckb_check_cuda((int)cudaEventRecord(m->ev_fork, main_st), "fork")) return CKB_ERR_CUDA;
+            if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;
+            for (int i = 0; i < 2; ++i) {
+                if (ckb_check_cuda((int)cudaStreamWaitEvent(m->side[i], m->ev_fork, 0), "fork wait")) return CKB_ERR_CUDA;
+                if ((rc = matvec(m, &t[i ? CKB_T_WV : CKB_T_WK], m->hq, i ? m->v : m->k, m->Hkvl * m->d, m->side[i]))) return rc;
+                if (ckb_check_cuda((int)cudaEventRecord(m->ev_join[i], m->side[i]), "join")) return CKB_ERR_CUDA;
+                if (ckb_check_cuda((int)cudaStreamWaitEvent(main_st, m->ev_join[i], 0), "join wait")) return CKB_ERR_CUDA;
+            }
+        } else {
+            if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;
+            if ((rc = matvec(m, &t[CKB_T_WK], m->hq, m->k, m->Hkvl * m->d, st))) return rc;
+            if ((rc = matvec(m, &t[CKB_T_WV], m->hq, m->v, m->Hkvl * m->d, st))) return rc;
+        }
         if ((rc = ckb200_dev_rope_kv_store(m->q, m->k, m->v, kc, vc, m->rope_cos, m->rope_sin, m->pos_dev, B, m->Hl, m->Hkvl, m->d,
                                            c->max_seq_len, m->kv_batch_stride, st))) return rc;
+        /* attention rows are contiguous [B][Al]; with B == 1 the row sits in an Ala-wide buffer whose tail stays zero.
+         * Attention, split merge and quantisation stay three launches: chained with programmatic dependent launch inside
+         * the step's graph they measured faster than the single-launch form (ckb200_dev_attention_decode_fused), whose
+         * merge and quantise tails run serially in the last CTAs. */
         if ((rc = ckb200_dev_attention_decode_ws(m->q, kc, vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
                                                  m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
-        /* attention rows are contiguous [B][Al]; with B == 1 the row sits in an Ala-wide buffer whose tail stays zero */
         if ((rc = quant_rows(&t[CKB_T_WO], m->att, m->Ala, m->aq, B, st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
         if ((rc = reduce_partial(m, m->o, (size_t)B * m->Da, st))) return rc;

@@ -121,6 +121,16 @@ int ckb200_dev_attention_decode_static(const float *q, const float *k_cache, con
                                        long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
                                        int cache_capacity, int head_dim, int aligned_head_dim, int splits, void *stream);
 size_t ckb200_attention_decode_static_scratch_limit(void);
+/* The step executor's form: the same attention, the merge of the context splits and quantize_row_q8_k of the
+ * finished rows (src/kernels/gemm_kernels_q4k_q8k.c:53-103; what the o-projection consumes) in ONE launch.
+ * out rows are out_stride floats apart; the q8_cols - H*ad floats after each row must be zero; q8_out may be NULL.
+ * `counters`: ckb200_attention_decode_counter_bytes() of device memory, zero before the first call (each call
+ * leaves it zero).  Shapes outside the tile kernel's fast path run as separate launches with the same result. */
+int ckb200_dev_attention_decode_fused(const float *q, const float *k_cache, const float *v_cache, float *out, int out_stride,
+                                      int batch, long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens,
+                                      int cache_capacity, int head_dim, int aligned_head_dim, int splits, float *scratch,
+                                      int *counters, const int *pos_dev, void *q8_out, int q8_cols, void *stream);
+size_t ckb200_attention_decode_counter_bytes(int batch, int num_kv_heads);
 int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
 size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
 

@@ -294,3 +294,48 @@ def test_kv_cache_store_then_attend_token_by_token(ck, orc):
         a = cases.attention_decode(ck, "", q, kc_g, vc_g, t + 1)
         b = cases.attention_decode(orc, "oracle_", q, kc_c, vc_c, t + 1)
         assert float(np.max(np.abs(a - b))) <= 1e-5
+
+
+@pytest.mark.parametrize("batch,heads,kvh,d,tokens,cap,splits", [(1, 14, 2, 64, 1025, 2048, 0), (1, 64, 8, 128, 4096, 4096, 0), (2, 8, 4, 64, 130, 256, 3),
+                                                              (1, 8, 8, 128, 70, 128, 1), (3, 16, 2, 128, 333, 512, 5)])
+def test_attention_decode_fused_merge_and_quantise(ck, orc, batch, heads, kvh, d, tokens, cap, splits):
+    """Attention + split merge + Q8_K quantisation in one launch: the rows match the oracle's attention, and the
+    Q8_K blocks are bit-exact with the oracle's quantiser applied to those rows.  Called twice: the arrival
+    counters must be back at zero after every call."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    width = heads * d
+    cols = -(-width // 256) * 256                       # the row sits in a zero-padded buffer, as in the step executor
+    if batch > 1:
+        assert cols == width
+    rng = np.random.default_rng(tokens)
+    q = rng.standard_normal((batch, heads, d)).astype(np.float32)
+    kc = rng.standard_normal((batch, kvh, cap, d)).astype(np.float32)
+    vc = rng.standard_normal((batch, kvh, cap, d)).astype(np.float32)
+    want = np.stack([cases.attention_decode(orc, "oracle_", q[b], kc[b], vc[b], tokens) for b in range(batch)]).reshape(batch, width)
+
+    ck.ckb200_attention_decode_scratch_bytes.restype = C.c_size_t
+    ck.ckb200_attention_decode_counter_bytes.restype = C.c_size_t
+    ck.ckb200_stream.restype = C.c_void_p
+    nsplit = splits or ck.ckb200_attention_decode_splits(batch, kvh, tokens)
+    tq, tk, tv = (torch.from_numpy(a).to(dev) for a in (q, kc, vc))
+    out = torch.zeros(batch, cols, device=dev)
+    scratch = torch.empty(max(256, ck.ckb200_attention_decode_scratch_bytes(batch, heads, d, nsplit)) // 4, device=dev)
+    counters = torch.zeros(ck.ckb200_attention_decode_counter_bytes(batch, kvh) // 4 + 4, dtype=torch.int32, device=dev)
+    q8 = torch.zeros(batch * (cols // 256) * 292, dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        out[:, :width] = float("nan")
+        q8.zero_()
+        torch.cuda.synchronize()
+        rc = ck.ckb200_dev_attention_decode_fused(
+            C.c_void_p(tq.data_ptr()), C.c_void_p(tk.data_ptr()), C.c_void_p(tv.data_ptr()), C.c_void_p(out.data_ptr()), cols, batch,
+            C.c_longlong(kvh * cap * d), heads, kvh, tokens, cap, d, d, nsplit, C.c_void_p(scratch.data_ptr()), C.c_void_p(counters.data_ptr()),
+            None, C.c_void_p(q8.data_ptr()), cols, None)
+        assert rc == 0 and ck.ckb200_synchronize() == 0
+        got = out.cpu().numpy()
+        assert float(np.max(np.abs(got[:, :width] - want))) <= ATTN_ABS_TOL
+        assert not counters.cpu().numpy().any()
+        for b in range(batch):
+            assert np.array_equal(q8.cpu().numpy().reshape(batch, -1)[b], cases.quantize_q8_k(orc, "oracle_", got[b]))

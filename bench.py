@@ -308,6 +308,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     stream = torch.cuda.Stream(device=dev)             # graphs cannot be captured on the default stream
     torch.cuda.set_stream(stream)
     sp = C.c_void_p(stream.cuda_stream)
+    side_streams = [torch.cuda.Stream(device=dev) for _ in range(max(0, args.streams - 1))]
 
     fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])
     gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}
@@ -336,14 +337,23 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                 host_w[(m, k)] = w_host
         torch.cuda.synchronize()
 
-        def step(plan=plan, fmt=fmt):
+        def step(plan=plan, fmt=fmt, nstreams=1):
+            """One pass over the sweep.  The launches are independent GEMVs (own weights, own output); with nstreams > 1
+            they are dealt round-robin to that many streams, which a graph capture turns into parallel branches."""
+            lanes = [stream] + side_streams[:nstreams - 1]
+            for s2 in lanes[1:]:
+                s2.wait_stream(stream)
+            i = 0
             for p in plan:
                 base = p["wbuf"].data_ptr()
                 for c in range(p["copies"]):
                     rc = gemv_dev[fmt](C.c_void_p(p["y"][c].data_ptr()), C.c_void_p(base + c * p["slot"]),
-                                       C.c_void_p(p["xq"].data_ptr()), p["m"], p["k"], sp)
+                                       C.c_void_p(p["xq"].data_ptr()), p["m"], p["k"], C.c_void_p(lanes[i % len(lanes)].cuda_stream))
+                    i += 1
                     if rc != 0:
                         raise RuntimeError(lib.ckb200_last_error_message().decode())
+            for s2 in lanes[1:]:
+                stream.wait_stream(s2)
 
         launches_before = lib.ckb200_launch_count()
         step()                                             # un-captured: sets kernel attributes, warms caches
@@ -351,7 +361,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            step()
+            step(nstreams=args.streams)
         for _ in range(args.warmup):
             graph.replay()
         torch.cuda.synchronize()
@@ -371,12 +381,26 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         step_bytes = sum(p["bytes"] * p["copies"] for p in plan)
+        serial_gbs = None
+        if args.streams > 1 and fmt == "q4_k":             # the same step as one dependent chain on one stream, for the record
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1, stream=stream):
+                step(nstreams=1)
+            g1.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(max(3, args.steps // 2)):
+                g1.replay()
+            b.record(stream)
+            torch.cuda.synchronize()
+            serial_gbs = step_bytes * max(3, args.steps // 2) / a.elapsed_time(b) / 1e6
         per_shape = {}
         if args.detail:
             for p in plan:                                 # per-shape timing, graph of one rotation of that shape
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=stream):
-                    step(plan=[p], fmt=fmt)
+                    step(plan=[p], fmt=fmt, nstreams=args.streams)
                 g.replay()
                 torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -390,7 +414,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         rc = lib.ckb200_synchronize()
         if rc != 0:
             raise RuntimeError(lib.ckb200_last_error_message().decode())
-        results[fmt] = dict(ms=ms, step_bytes=step_bytes, launches=launches_per_step, clocks=clocks, per_shape=per_shape, plan=plan)
+        results[fmt] = dict(ms=ms, step_bytes=step_bytes, launches=launches_per_step, clocks=clocks, per_shape=per_shape, plan=plan, serial_gbs=serial_gbs)
 
     # ---- end to end through the reference-named host-pointer entry point (Q4_K)
     e2e = None
@@ -465,7 +489,11 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                        "l2": "every launch reads a different weight copy; copies per shape total > 4x L2 (rotation "
                              + "/".join(str(p["copies"]) for p in r["plan"]) + ")",
                        "sharding": "each rank streams its own shard of rows; no collective in the data path",
-                       "timing": "CUDA graph of one step replayed; CUDA events on the launching stream; max over ranks"},
+                       "timing": "CUDA graph of one step replayed; CUDA events on the launching stream; max over ranks",
+                       "schedule": f"the launches of a step are independent GEMVs and are dealt round-robin to {args.streams} stream(s) "
+                                   "(parallel branches of the graph), as the step executor does with q/k/v; serial_chain_gbs is the "
+                                   "same step as one dependent chain on one stream"},
+            "serial_chain_gbs": (r["serial_gbs"] * world) if r["serial_gbs"] else None,
             "clocks": {k: r["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if r["clocks"] else None,
             "e2e": e2e,
             "gpu_launches": int(r["launches"] * args.steps),
@@ -621,6 +649,7 @@ def main():
     ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
+    ap.add_argument("--streams", type=int, default=2, help="streams the independent GEMV launches of a sweep step are dealt to")
     ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")

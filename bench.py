@@ -311,7 +311,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(max(0, args.streams - 1))]
 
     fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])
-    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}
+    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}
+    lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
     quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0}
 
     results = {}
@@ -323,8 +324,14 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             nbytes = w_host.nbytes
             copies = max(2, -(-L2_BYTES_X4 // nbytes))
             slot = (nbytes + 255) & ~255
-            wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
             src = torch.from_numpy(w_host).to(dev)
+            if fmt == "q6_k":                              # resident Q6_K weights live in the library's row-planar layout (same bits)
+                nbytes = lib.ckb200_q6_k_planar_bytes(m, k)
+                slot = (nbytes + 255) & ~255
+                planar = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                assert lib.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(src.data_ptr()), m, k, sp) == 0
+                src = planar
+            wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
             for c in range(copies):
                 wbuf[c * slot:c * slot + nbytes].copy_(src)
             x = torch.from_numpy(synth.make_x(k, seed=rank, k_valid=k_raw if k_raw != k else None)).to(dev)

@@ -97,6 +97,15 @@ int ckb200_dev_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *b
 /* the bias loop of those functions on its own: c[r][j] += bias[j] */
 int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void *stream);
 
+/* Q6_K weights that stay resident on the device can be kept in a row-planar layout (per row: all ql, all qh, all
+ * scales, all d; same bits, 210 bytes per superblock plus at most 14 bytes of row padding) in which every piece is
+ * naturally aligned for 16-byte loads; the block_q6_K stream itself (include/ckernel_quant.h:135-146) is only
+ * 2-byte aligned.  ckb200_dev_gemv_q6_k_planar_q8_k gives the same result as ckb200_dev_gemv_q6_k_q8_k
+ * (gemv_q6_k_q8_k, src/kernels/gemm_kernels_q6k_q8k.c:197-214) on the original rows. */
+size_t ckb200_q6_k_planar_bytes(int rows, int cols);
+int ckb200_dev_q6_k_to_planar(void *dst_planar, const void *src_q6k_rows, int rows, int cols, void *stream);
+int ckb200_dev_gemv_q6_k_planar_q8_k(float *y, const void *W_planar, const void *x_q8, int M, int K, void *stream);
+
 /* attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406) for `batch`
  * independent sequences: q/out [batch][H][ad], caches [batch][Hkv][capacity][ad] with kv_batch_stride floats
  * between sequences.  Split-K over the context; partial results go through a scratch buffer.

@@ -339,3 +339,31 @@ def test_attention_decode_fused_merge_and_quantise(ck, orc, batch, heads, kvh, d
         assert not counters.cpu().numpy().any()
         for b in range(batch):
             assert np.array_equal(q8.cpu().numpy().reshape(batch, -1)[b], cases.quantize_q8_k(orc, "oracle_", got[b]))
+
+
+@pytest.mark.parametrize("m,k", [(1, 256), (3, 512), (7, 1024), (33, 4096), (130, 4864), (5, 14336), (2, 28672), (300, 6144), (4100, 1024)])
+def test_gemv_q6_k_planar_layout(ck, orc, m, k):
+    """Weights re-laid row-planar on the device give the oracle's result; both row counts per lane group."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    w = synth.make_weights("q6_k", m, k, seed=m + k)
+    xq = cases.quantize_act(orc, "oracle_", "q6_k", synth.make_x(k, seed=m + k))
+    want = cases.gemv(orc, "oracle_", "q6_k", w, xq, m, k)
+    ck.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+    raw = torch.from_numpy(w).to(dev)
+    planar = torch.full((ck.ckb200_q6_k_planar_bytes(m, k),), 0xAA, dtype=torch.uint8, device=dev)
+    txq = torch.from_numpy(xq).to(dev)
+    y = torch.full((m,), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    assert ck.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), m, k, None) == 0
+    try:
+        for rows_per_group in (0, 1, 2):
+            ck.ckb200_tune_set(b"gemv_q6p_rows", rows_per_group)
+            y.fill_(float("nan"))
+            torch.cuda.synchronize()
+            assert ck.ckb200_dev_gemv_q6_k_planar_q8_k(C.c_void_p(y.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(txq.data_ptr()), m, k, None) == 0
+            assert ck.ckb200_synchronize() == 0
+            assert_fp32_close(y.cpu().numpy(), want, f"q6_k planar {m}x{k} rows/group={rows_per_group}")
+    finally:
+        ck.ckb200_tune_set(b"gemv_q6p_rows", 0)

@@ -41,6 +41,7 @@ typedef struct {
     size_t bytes;
     int fmt;            /* block format, or -1 for fp32 */
     int rows, cols;     /* [rows][cols] elements (cols already aligned) */
+    void *planar;       /* Q6_K matrices that feed a GEMV: second copy in the row-planar layout (aligned 16-byte loads), or NULL */
 } Tensor;
 
 typedef struct {
@@ -58,6 +59,9 @@ struct CKB200Model {
     Tensor emb, final_gamma, lm_head;
     uint8_t *arena;         /* all weights */
     size_t arena_bytes;
+    uint8_t *planar_arena;  /* row-planar copies of the Q6_K projection matrices, rebuilt from `arena` when weights change */
+    size_t planar_bytes;
+    int planar_ready;
     float *kv;              /* [L][2][B][Hkvl][S][d] */
     long long kv_layer_stride, kv_batch_stride;
     float *rope_cos, *rope_sin;
@@ -156,10 +160,30 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     if (cfg->tie_embeddings) m->emb = m->lm_head;
     else tensor_plan(&m->emb, cfg->fmt_embedding, cfg->vocab_size, cols_for(cfg->fmt_embedding, m->D), &cur);
     m->arena_bytes = cur + 256;
+    {
+        size_t pc = 0;
+        for (int l = 0; l <= L; ++l) {
+            Tensor *list[7];
+            int n = 0;
+            if (l < L) {
+                static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
+                for (int i = 0; i < 6; ++i) list[n++] = &m->layers[l].t[which[i]];
+            } else {
+                list[n++] = &m->lm_head;
+            }
+            for (int i = 0; i < n; ++i) {
+                if (list[i]->fmt != FMT_Q6K) continue;
+                list[i]->planar = (void *)(uintptr_t)(pc + 1);      /* offset + 1 for now (0 = none) */
+                pc = align_up(pc + ckb200_q6_k_planar_bytes(list[i]->rows, list[i]->cols), 256);
+            }
+        }
+        m->planar_bytes = pc;
+    }
 
     int ok = 1;
 #define DEV_ALLOC(ptr, bytes) do { if (ok && ckb_check_cuda((int)cudaMalloc((void **)&(ptr), (bytes)), "cudaMalloc(model)")) ok = 0; } while (0)
     DEV_ALLOC(m->arena, m->arena_bytes);
+    if (m->planar_bytes) DEV_ALLOC(m->planar_arena, m->planar_bytes);
     m->kv_batch_stride = (long long)m->Hkvl * S * m->d;
     m->kv_layer_stride = 2LL * B * m->kv_batch_stride;
     DEV_ALLOC(m->kv, (size_t)L * m->kv_layer_stride * sizeof(float));
@@ -198,6 +222,11 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     m->final_gamma.w = m->arena + (uintptr_t)m->final_gamma.w;
     m->lm_head.w = m->arena + (uintptr_t)m->lm_head.w;
     m->emb.w = cfg->tie_embeddings ? m->lm_head.w : (void *)(m->arena + (uintptr_t)m->emb.w);
+    for (int l = 0; l < L; ++l)
+        for (int i = 0; i < CKB_T_PER_LAYER; ++i)
+            if (m->layers[l].t[i].planar) m->layers[l].t[i].planar = m->planar_arena + ((uintptr_t)m->layers[l].t[i].planar - 1);
+    if (m->lm_head.planar) m->lm_head.planar = m->planar_arena + ((uintptr_t)m->lm_head.planar - 1);
+    if (cfg->tie_embeddings) m->emb.planar = NULL;             /* the embedding lookup reads the original rows */
 
     cudaStream_t st = ckb_stream(NULL);
     cudaMemsetAsync(m->arena, 0, m->arena_bytes, st);
@@ -217,7 +246,7 @@ void ckb200_model_free(CKB200Model *m)
     if (!m) return;
     cudaStreamSynchronize(ckb_stream(NULL));
     if (m->graph_ready) cudaGraphExecDestroy(m->graph);
-    void *ptrs[] = { m->arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
+    void *ptrs[] = { m->arena, m->planar_arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
                      m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch };
     for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
@@ -266,7 +295,7 @@ int ckb200_model_upload_tensor(CKB200Model *m, int layer, int which, const void 
     Tensor *t = m ? find_tensor(m, layer, which) : NULL;
     if (!t || !host) return ckb_fail(CKB_ERR_STATE, "model_upload_tensor: no such tensor (%d, %d)", layer, which);
     if (bytes != t->bytes) return ckb_fail(CKB_ERR_SHAPE, "model_upload_tensor(%d, %d): got %zu bytes, tensor has %zu", layer, which, bytes, t->bytes);
-    m->graph_ready = m->graph_ready;   /* weights are read through fixed pointers: the captured graph stays valid */
+    m->planar_ready = 0;               /* weights are read through fixed pointers: the captured graph stays valid */
     return ckb_check_cuda((int)cudaMemcpy(t->w, host, bytes, cudaMemcpyHostToDevice), "upload tensor");
 }
 
@@ -280,6 +309,7 @@ static int fill_tensor(Tensor *t, unsigned long long seed)
 int ckb200_model_fill_synthetic(CKB200Model *m, unsigned long long seed)
 {
     if (!m) return CKB_ERR_STATE;
+    m->planar_ready = 0;
     unsigned long long s = seed * 1000003ull + 17;
     for (int l = 0; l < m->c.num_layers; ++l)
         for (int i = 0; i < CKB_T_PER_LAYER; ++i)
@@ -353,7 +383,9 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
 {
     switch (fmt) {
         case FMT_Q4K: return ckb200_dev_gemv_q4_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
-        case FMT_Q6K: return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
+        case FMT_Q6K:
+            if (w->planar) return ckb200_dev_gemv_q6_k_planar_q8_k(y, w->planar, xq, w->rows, w->cols, st);
+            return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
         default: return ckb200_dev_gemv_q8_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
     }
 }
@@ -407,6 +439,23 @@ static int reduce_partial(CKB200Model *m, float *buf, size_t count, void *st)
     if (m->c.tp_size <= 1) return 0;
     if (!m->allreduce) return ckb_fail(CKB_ERR_STATE, "model step: tp_size %d but no all-reduce hook set", m->c.tp_size);
     return m->allreduce(m->allreduce_ctx, buf, count, st);
+}
+
+/* (Re)builds the row-planar copies of the Q6_K projection matrices from the uploaded rows; outside any capture. */
+static int ensure_planar(CKB200Model *m, void *st)
+{
+    if (m->planar_ready || !m->planar_bytes) return 0;
+    int rc = 0;
+    for (int l = 0; l < m->c.num_layers && !rc; ++l)
+        for (int i = 0; i < CKB_T_PER_LAYER && !rc; ++i) {
+            const Tensor *t = &m->layers[l].t[i];
+            if (t->planar) rc = ckb200_dev_q6_k_to_planar(t->planar, t->w, t->rows, t->cols, st);
+        }
+    if (!rc && m->lm_head.planar) rc = ckb200_dev_q6_k_to_planar(m->lm_head.planar, m->lm_head.w, m->lm_head.rows, m->lm_head.cols, st);
+    if (rc) return rc;
+    if (ckb_check_cuda((int)cudaStreamSynchronize((cudaStream_t)st), "planar weights")) return CKB_ERR_CUDA;
+    m->planar_ready = 1;
+    return 0;
 }
 
 static int issue_step(CKB200Model *m, void *st)
@@ -478,6 +527,7 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
     const int B = m->c.batch;
     memcpy(m->tokens_pinned, tokens, (size_t)B * sizeof(int32_t));
     if (ckb_check_cuda((int)cudaMemcpyAsync(m->tokens_dev, m->tokens_pinned, (size_t)B * sizeof(int32_t), cudaMemcpyHostToDevice, st), "tokens H2D")) return CKB_ERR_CUDA;
+    { const int rc = ensure_planar(m, st); if (rc) return rc; }
     const int use_graph = ckb_tune_get("model_graph", 1);
     if (use_graph && !m->graph_ready) {
         /* one eager step first: it sets per-kernel attributes (not allowed while capturing) and is rolled back */

@@ -384,7 +384,8 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
     switch (fmt) {
         case FMT_Q4K: return ckb200_dev_gemv_q4_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
         case FMT_Q6K:
-            if (w->planar) return ckb200_dev_gemv_q6_k_planar_q8_k(y, w->planar, xq, w->rows, w->cols, st);
+            /* few long rows: the ring kernel, which splits a row over warps, measured faster than the planar one */
+            if (w->planar && !(w->rows <= 2048 && w->cols >= 4096)) return ckb200_dev_gemv_q6_k_planar_q8_k(y, w->planar, xq, w->rows, w->cols, st);
             return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
         default: return ckb200_dev_gemv_q8_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
     }

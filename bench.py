@@ -514,7 +514,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         if world == 1 and not args.no_decode:
             try:
                 line["decode"] = [decode_bench(lib, "Qwen2-0.5B shape, Q4_K_M mix", QWEN2_05B, 1024, 200, peak),
-                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU", LLAMA3_70B, 4096, 10, peak)]
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU", LLAMA3_70B, 4096, 10, peak),
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32", LLAMA3_70B, 4096, 4, peak, batch=32)]
             except Exception as exc:                      # the headline metric above must survive a failure here
                 line["decode"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()

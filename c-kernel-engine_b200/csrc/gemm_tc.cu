@@ -199,15 +199,23 @@ __device__ float g_tc_prof[64];
 #endif
 
 // Register counts per role after setmaxnreg; 128 * (CTL + EW * EXP + 2 * DRAIN) must not exceed threads x launch registers.
+enum { TC_W_Q4K = 0, TC_W_Q6K_PLANAR = 1 };       // weight operand formats
+
 template <int NH, int EW> struct TcRegs;
 template <> struct TcRegs<1, 2> { static constexpr int CTL = 32, EXP = 72, DRAIN = 152, LAUNCH = 96; };    // 640 threads x 96
 template <> struct TcRegs<2, 1> { static constexpr int CTL = 40, EXP = 72, DRAIN = 200, LAUNCH = 128; };   // 512 threads x 128
 
-// NH 128-token tiles per CTA, EW warpgroups of weight expanders (they take alternate k-stages).
-template <int NH, int EW>
+// WF weight format, NH 128-token tiles per CTA, EW warpgroups of weight expanders.
+//
+// Q6_K weights (row-planar layout, see gemv_q6k_planar.cu) use the same pipeline with A = (q6 - 32) * sc as fp16: the
+// offset is inside the operand, so there is no second accumulator, and each 64-deep k-stage is one (half n, nibble
+// half) of a superblock (include/ckernel_quant.h:135-146, src/kernels/gemm_kernels_q6k_q8k.c:86-116).  The product is
+// an exact fp16 integer whenever |q6 - 32| * |sc| <= 2048 (always for |sc| <= 64); above that it is rounded to the
+// nearest even integer, a relative error of at most 2^-12 on that element.
+template <int WF, int NH, int EW>
 __global__ void __launch_bounds__(128 * (3 + EW), 1)
-gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B, const float *__restrict__ bias, float *__restrict__ C, int M, int N,
-                   int nb, int *__restrict__ dev_err)
+gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B, const float *__restrict__ bias, float *__restrict__ C, int ldc, int M,
+                  int N, int nb, int *__restrict__ dev_err)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t s_base = smem_u32(smem);
@@ -324,14 +332,21 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
                             TC_PROF(5);
                         }
                         if (s < 4) break;
-                        const uint32_t x2 = (uint32_t)b & 1u;
-                        TC_WAIT(BAR(BAR_A2_FULL + x2), ((uint32_t)b >> 1) & 1u, DEV_ERR_FULL_WAIT);
-                        TC_WAIT(BAR(BAR_B2_FULL + buf), (u >> 1) & 1u, DEV_ERR_FULL_WAIT);
-                        if (tc_elect_one()) {
-                            tc_mma(tacc + 128u, dA2 + (uint64_t)(x2 * (TC_AUX >> 4)), dB2 + (uint64_t)(buf * (TC_AUXX >> 4)), 0u);
-                            tc_commit(BAR(BAR_B2_EMPTY + buf));
-                            if (last_use) tc_commit(BAR(BAR_A2_EMPTY + x2));
-                            tc_commit(BAR(BAR_T_FULL + buf));
+                        if constexpr (WF == TC_W_Q4K) {
+                            const uint32_t x2 = (uint32_t)b & 1u;
+                            TC_WAIT(BAR(BAR_A2_FULL + x2), ((uint32_t)b >> 1) & 1u, DEV_ERR_FULL_WAIT);
+                            TC_WAIT(BAR(BAR_B2_FULL + buf), (u >> 1) & 1u, DEV_ERR_FULL_WAIT);
+                            if (tc_elect_one()) {
+                                tc_mma(tacc + 128u, dA2 + (uint64_t)(x2 * (TC_AUX >> 4)), dB2 + (uint64_t)(buf * (TC_AUXX >> 4)), 0u);
+                                tc_commit(BAR(BAR_B2_EMPTY + buf));
+                                if (last_use) tc_commit(BAR(BAR_A2_EMPTY + x2));
+                                tc_commit(BAR(BAR_T_FULL + buf));
+                            }
+                        } else {
+                            if (tc_elect_one()) {
+                                tc_commit(BAR(BAR_B2_EMPTY + buf));      // nothing reads the bsum tile; the drain warps still release the block scales
+                                tc_commit(BAR(BAR_T_FULL + buf));
+                            }
                         }
                         __syncwarp();
                         TC_PROF(6);
@@ -345,63 +360,118 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
         // ------------------------------------------------------------ weight expanders: thread = row, stage = quarter of a superblock
         TC_SETMAXNREG("dec", REGS_EXP);
         const int set = (warp - 4) >> 2, row = tid & 127;
-        const uint8_t *wrow = B + (size_t)min(n0 + row, N - 1) * nb * Q4K_BYTES;
-        const uint32_t stages = (uint32_t)nb * 4u;
-        Q4Stage cur;
-        uint4 hdr;
-        {
-            const uint8_t *p0 = wrow + 16 + 32 * set;
-            cur.qa = __ldg(reinterpret_cast<const uint4 *>(p0));
-            cur.qb = __ldg(reinterpret_cast<const uint4 *>(p0 + 16));
-            hdr = __ldg(reinterpret_cast<const uint4 *>(wrow));
-        }
-        TC_PROF_DECL();
-        for (uint32_t it = (uint32_t)set; it < stages; it += EW) {
-            const uint32_t b = it >> 2, s = it & 3u, ia = it & 7u, x2 = b & 1u;
-            TC_PROF(0);
-            Q4Stage nxt = cur;
-            uint4 hdr_next = hdr;
-            if (it + EW < stages) {                   // this thread's next quarter, possibly of the next superblock
-                const uint8_t *pn = wrow + (size_t)((it + EW) >> 2) * Q4K_BYTES;
-                nxt.qa = __ldg(reinterpret_cast<const uint4 *>(pn + 16 + 32 * ((it + EW) & 3u)));
-                nxt.qb = __ldg(reinterpret_cast<const uint4 *>(pn + 32 + 32 * ((it + EW) & 3u)));
-                if (((it + EW) >> 2) != b) hdr_next = __ldg(reinterpret_cast<const uint4 *>(pn));
-            }
-            uint32_t sc2, m2;
-            q4k_scales(hdr.y, hdr.z, hdr.w, (int)s, sc2, m2);
-            const float sclo = (float)(sc2 & 255u), schi = (float)(sc2 >> 8);
-            const __half2 s_lo = __floats2half2_rn(sclo, sclo), s_hi = __floats2half2_rn(schi, schi);
-            const __half2 b_lo = __floats2half2_rn(-1024.0f * sclo, -1024.0f * sclo), b_hi = __floats2half2_rn(-1024.0f * schi, -1024.0f * schi);
-            const float mlo = (float)(m2 & 255u), mhi = (float)(m2 >> 8);
-            const __half2 mm_lo = __floats2half2_rn(mlo, mlo), mm_hi = __floats2half2_rn(mhi, mhi);
-            TC_PROF(1);
-            TC_WAIT(BAR(BAR_A_EMPTY + ia), ((it >> 3) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT);
-            TC_PROF(2);
-            if (s < (uint32_t)EW) { TC_WAIT(BAR(BAR_A2_EMPTY + x2), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }   // this set's first write of the superblock
-            TC_PROF(3);
-            const uint32_t ml = 0x0F0F0F0Fu;
-            const uint32_t w[8] = {cur.qa.x, cur.qa.y, cur.qa.z, cur.qa.w, cur.qb.x, cur.qb.y, cur.qb.z, cur.qb.w};
-            uint8_t *dst = smem + TC_OFF_A + ia * TC_STAGE;
+        if constexpr (WF == TC_W_Q6K_PLANAR) {
+            // set e takes half n = e (EW = 2) or both halves in turn (EW = 1): the 64 ql bytes and 32 qh bytes of a half feed two stages
+            const size_t rb = ((size_t)nb * Q6K_BYTES + 15) & ~(size_t)15;
+            const uint8_t *wrow = B + (size_t)min(n0 + row, N - 1) * rb;
+            const size_t off_qh = (size_t)nb * 128, off_sc = (size_t)nb * 192;
+            const __half2 c66 = __floats2half2_rn(66.0f, 66.0f);
+            const uint32_t halves_total = (uint32_t)nb * 2u;
+            for (uint32_t hf = (uint32_t)set; hf < halves_total; hf += EW) {
+                const uint32_t b = hf >> 1, n = hf & 1u;
+                uint4 ql[4], qh[2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {     // low nibbles = sub-block 2s: k-chunks 0-3 of the stage; high nibbles = sub-block 2s+1: k-chunks 4-7
-                *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, c)) = q4_chunk_to_half(w[2 * c] & ml, w[2 * c + 1] & ml, s_lo, b_lo);
-                *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, 4 + c)) = q4_chunk_to_half((w[2 * c] >> 4) & ml, (w[2 * c + 1] >> 4) & ml, s_hi, b_hi);
+                for (int j = 0; j < 4; ++j) ql[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)b * 128 + 64 * n + 16 * j));
+#pragma unroll
+                for (int j = 0; j < 2; ++j) qh[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + off_qh + (size_t)b * 64 + 32 * n + 16 * j));
+                const uint2 sc8 = __ldg(reinterpret_cast<const uint2 *>(wrow + off_sc + (size_t)b * 16 + 8 * n));
+                const uint32_t qlw[16] = {ql[0].x, ql[0].y, ql[0].z, ql[0].w, ql[1].x, ql[1].y, ql[1].z, ql[1].w,
+                                          ql[2].x, ql[2].y, ql[2].z, ql[2].w, ql[3].x, ql[3].y, ql[3].z, ql[3].w};
+                const uint32_t qhw[8] = {qh[0].x, qh[0].y, qh[0].z, qh[0].w, qh[1].x, qh[1].y, qh[1].z, qh[1].w};
+                bool ok_stage = true;
+#pragma unroll 1
+                for (uint32_t hi = 0; hi < 2 && ok_stage; ++hi) {
+                    const uint32_t it = 4u * b + 2u * n + hi, ia = it & 7u;
+                    const uint32_t scw = hi ? sc8.y : sc8.x;       // scale groups 8n + 4hi + {0, 1, 2, 3}
+                    if (!mbar_wait_spin(BAR(BAR_A_EMPTY + ia), ((it >> 3) & 1u) ^ 1u)) { atomicExch(dev_err, DEV_ERR_EMPTY_WAIT); ok_stage = false; break; }
+                    uint8_t *dst = smem + TC_OFF_A + ia * TC_STAGE;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {                  // chunk c: weights (c < 4 ? ql[l] : ql[32 + l]) with l = 8 (c & 3) .. + 7
+                        const int sb = 2 * (c >> 2) + ((c & 3) >> 1);
+                        const float scf = 16.0f * (float)(int)(int8_t)((scw >> (8 * sb)) & 255u);
+                        const __half2 sc2 = __floats2half2_rn(scf, scf);
+                        uint32_t o[4];
+#pragma unroll
+                        for (int w2 = 0; w2 < 2; ++w2) {
+                            const uint32_t lw = qlw[8 * (c >> 2) + 2 * (c & 3) + w2], hw = qhw[2 * (c & 3) + w2];
+                            const uint32_t nib = (lw >> (4u * hi)) & 0x0F0F0F0Fu;
+                            const uint32_t two = ((hw >> (4u * hi + 2u * (uint32_t)(c >> 2))) << 4) & 0x30303030u;
+                            uint32_t h01, h23;
+                            // 0x5400 | q is the fp16 bit pattern of 64 + q / 16
+                            h01 = __byte_perm(nib | two, 0x54545454u, 0x5140);
+                            h23 = __byte_perm(nib | two, 0x54545454u, 0x7362);
+                            const __half2 r0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h01), c66), sc2);   // (q - 32) / 16 * 16 sc
+                            const __half2 r1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h23), c66), sc2);
+                            o[2 * w2] = *reinterpret_cast<const uint32_t *>(&r0);
+                            o[2 * w2 + 1] = *reinterpret_cast<const uint32_t *>(&r1);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(BAR_A_FULL + ia));
+                }
+                if (!ok_stage) break;
             }
-            // the two mins of this quarter, each doubled (bsums come per 16 elements): positions 4s .. 4s+3 of the 16-deep tile
-            uint32_t *d2 = reinterpret_cast<uint32_t *>(smem + TC_OFF_A2 + x2 * TC_AUX + tc_tile_offset(row, (int)(s >> 1))) + 2 * (s & 1u);
-            d2[0] = *reinterpret_cast<const uint32_t *>(&mm_lo);
-            d2[1] = *reinterpret_cast<const uint32_t *>(&mm_hi);
-            TC_PROF(4);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-            TC_PROF(5);
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(BAR(BAR_A_FULL + ia));
-                if (s >= 4u - (uint32_t)EW) mbar_arrive(BAR(BAR_A2_FULL + x2));   // this set's last quarter of the superblock
+        } else {
+            const uint8_t *wrow = B + (size_t)min(n0 + row, N - 1) * nb * Q4K_BYTES;
+            const uint32_t stages = (uint32_t)nb * 4u;
+            Q4Stage cur;
+            uint4 hdr;
+            {
+                const uint8_t *p0 = wrow + 16 + 32 * set;
+                cur.qa = __ldg(reinterpret_cast<const uint4 *>(p0));
+                cur.qb = __ldg(reinterpret_cast<const uint4 *>(p0 + 16));
+                hdr = __ldg(reinterpret_cast<const uint4 *>(wrow));
             }
-            cur = nxt;
-            hdr = hdr_next;
-            TC_PROF(6);
+            TC_PROF_DECL();
+            for (uint32_t it = (uint32_t)set; it < stages; it += EW) {
+                const uint32_t b = it >> 2, s = it & 3u, ia = it & 7u, x2 = b & 1u;
+                TC_PROF(0);
+                Q4Stage nxt = cur;
+                uint4 hdr_next = hdr;
+                if (it + EW < stages) {                   // this thread's next quarter, possibly of the next superblock
+                    const uint8_t *pn = wrow + (size_t)((it + EW) >> 2) * Q4K_BYTES;
+                    nxt.qa = __ldg(reinterpret_cast<const uint4 *>(pn + 16 + 32 * ((it + EW) & 3u)));
+                    nxt.qb = __ldg(reinterpret_cast<const uint4 *>(pn + 32 + 32 * ((it + EW) & 3u)));
+                    if (((it + EW) >> 2) != b) hdr_next = __ldg(reinterpret_cast<const uint4 *>(pn));
+                }
+                uint32_t sc2, m2;
+                q4k_scales(hdr.y, hdr.z, hdr.w, (int)s, sc2, m2);
+                const float sclo = (float)(sc2 & 255u), schi = (float)(sc2 >> 8);
+                const __half2 s_lo = __floats2half2_rn(sclo, sclo), s_hi = __floats2half2_rn(schi, schi);
+                const __half2 b_lo = __floats2half2_rn(-1024.0f * sclo, -1024.0f * sclo), b_hi = __floats2half2_rn(-1024.0f * schi, -1024.0f * schi);
+                const float mlo = (float)(m2 & 255u), mhi = (float)(m2 >> 8);
+                const __half2 mm_lo = __floats2half2_rn(mlo, mlo), mm_hi = __floats2half2_rn(mhi, mhi);
+                TC_PROF(1);
+                TC_WAIT(BAR(BAR_A_EMPTY + ia), ((it >> 3) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT);
+                TC_PROF(2);
+                if (s < (uint32_t)EW) { TC_WAIT(BAR(BAR_A2_EMPTY + x2), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }   // this set's first write of the superblock
+                TC_PROF(3);
+                const uint32_t ml = 0x0F0F0F0Fu;
+                const uint32_t w[8] = {cur.qa.x, cur.qa.y, cur.qa.z, cur.qa.w, cur.qb.x, cur.qb.y, cur.qb.z, cur.qb.w};
+                uint8_t *dst = smem + TC_OFF_A + ia * TC_STAGE;
+    #pragma unroll
+                for (int c = 0; c < 4; ++c) {     // low nibbles = sub-block 2s: k-chunks 0-3 of the stage; high nibbles = sub-block 2s+1: k-chunks 4-7
+                    *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, c)) = q4_chunk_to_half(w[2 * c] & ml, w[2 * c + 1] & ml, s_lo, b_lo);
+                    *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, 4 + c)) = q4_chunk_to_half((w[2 * c] >> 4) & ml, (w[2 * c + 1] >> 4) & ml, s_hi, b_hi);
+                }
+                // the two mins of this quarter, each doubled (bsums come per 16 elements): positions 4s .. 4s+3 of the 16-deep tile
+                uint32_t *d2 = reinterpret_cast<uint32_t *>(smem + TC_OFF_A2 + x2 * TC_AUX + tc_tile_offset(row, (int)(s >> 1))) + 2 * (s & 1u);
+                d2[0] = *reinterpret_cast<const uint32_t *>(&mm_lo);
+                d2[1] = *reinterpret_cast<const uint32_t *>(&mm_hi);
+                TC_PROF(4);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+                TC_PROF(5);
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(BAR(BAR_A_FULL + ia));
+                    if (s >= 4u - (uint32_t)EW) mbar_arrive(BAR(BAR_A2_FULL + x2));   // this set's last quarter of the superblock
+                }
+                cur = nxt;
+                hdr = hdr_next;
+                TC_PROF(6);
+            }
         }
         if (lane == 0 && (warp & 3) == 0) TC_PROF_OUT(2 + set);
     } else {
@@ -411,7 +481,9 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
         const int dw = warp - (4 + 4 * EW);
         const int q = dw & 3, ch = dw >> 2;           // (4 + 4 * EW) % 4 == 0: warp % 4 is the TMEM lane quarter this warp may read
         const int row = 32 * q + lane, n = n0 + row;
-        const uint8_t *wrow = B + (size_t)min(n, N - 1) * nb * Q4K_BYTES;
+        constexpr size_t DSTRIDE = WF == TC_W_Q4K ? Q4K_BYTES : 2;        // bytes between the block scales of consecutive superblocks
+        const uint8_t *wrow = WF == TC_W_Q4K ? B + (size_t)min(n, N - 1) * nb * Q4K_BYTES
+                                             : B + (size_t)min(n, N - 1) * (((size_t)nb * Q6K_BYTES + 15) & ~(size_t)15) + (size_t)nb * 208;
         float acc[NH][64];
 #pragma unroll
         for (int h = 0; h < NH; ++h)
@@ -419,10 +491,14 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
             for (int i = 0; i < 64; ++i) acc[h][i] = 0.0f;
         bool go = true;
         TC_PROF_DECL();
-        uint32_t dd_next = __ldg(reinterpret_cast<const uint32_t *>(wrow));
+        auto load_dd = [&](int b) -> uint32_t {       // Q4_K: fp16 d | dmin of the superblock; Q6_K: fp16 d
+            if constexpr (WF == TC_W_Q4K) return __ldg(reinterpret_cast<const uint32_t *>(wrow + (size_t)b * DSTRIDE));
+            else return ldg_nc_u16(wrow + (size_t)b * DSTRIDE);
+        };
+        uint32_t dd_next = load_dd(0);
         for (int b = 0; b < nb && go; ++b) {
             const uint32_t dd_bits = dd_next;
-            if (b + 1 < nb) dd_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (size_t)(b + 1) * Q4K_BYTES));
+            if (b + 1 < nb) dd_next = load_dd(b + 1);
             const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&dd_bits));
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
@@ -444,7 +520,7 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
 #pragma unroll
                             for (int j = 0; j < RC / 16; ++j) {
                                 tc_ld16(taddr + (uint32_t)(RC * c + 16 * j), t1[j]);
-                                tc_ld16(taddr + 128u + (uint32_t)(RC * c + 16 * j), t2[j]);
+                                if constexpr (WF == TC_W_Q4K) tc_ld16(taddr + 128u + (uint32_t)(RC * c + 16 * j), t2[j]);
                             }
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                             TC_PROF(3);
@@ -455,9 +531,13 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
                                     const float4 dx = dxp[(RC * c + 16 * j) / 4 + i4];
                                     const float dxf[4] = {dx.x, dx.y, dx.z, dx.w};
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i)
-                                        acc[h][RC * c + 16 * j + 4 * i4 + i] +=
-                                            dxf[i] * (dd.x * __uint_as_float(t1[j][4 * i4 + i]) - dd.y * __uint_as_float(t2[j][4 * i4 + i]));
+                                    for (int i = 0; i < 4; ++i) {
+                                        if constexpr (WF == TC_W_Q4K)
+                                            acc[h][RC * c + 16 * j + 4 * i4 + i] +=
+                                                dxf[i] * (dd.x * __uint_as_float(t1[j][4 * i4 + i]) - dd.y * __uint_as_float(t2[j][4 * i4 + i]));
+                                        else
+                                            acc[h][RC * c + 16 * j + 4 * i4 + i] += (dxf[i] * dd.x) * __uint_as_float(t1[j][4 * i4 + i]);
+                                    }
                                 }
                         }
                         TC_PROF(4);
@@ -481,7 +561,7 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int m = m0 + h * TC_ROWS + 64 * ch + i;
-                    if (h < halves && m < M) C[(size_t)m * N + n] = acc[h][i] + bv;
+                    if (h < halves && m < M) C[(size_t)m * ldc + n] = acc[h][i] + bv;
                 }
         }
     }
@@ -498,8 +578,8 @@ gemm_q4k_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B
 
 using namespace ckb;
 
-template <int NH, int EW>
-static int launch_tc(const uint8_t *xt, const void *B, const float *bias, float *C, int M, int N, int nb, int mtiles, cudaStream_t st)
+template <int WF, int NH, int EW>
+static int launch_tc(const uint8_t *xt, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, int mtiles, cudaStream_t st)
 {
     static int attr_set = 0;
     if (!attr_set) {
@@ -507,25 +587,28 @@ static int launch_tc(const uint8_t *xt, const void *B, const float *bias, float 
         static_assert(128 * (R::CTL + EW * R::EXP + 2 * R::DRAIN) <= 128 * (3 + EW) * R::LAUNCH, "setmaxnreg targets exceed the CTA's register pool");
         static_assert(128 * (3 + EW) * R::LAUNCH <= 65536 && R::CTL <= R::LAUNCH && R::EXP <= R::LAUNCH && R::DRAIN >= R::LAUNCH, "register plan");
         cudaFuncAttributes fa;
-        if (ckb_check_cuda((int)cudaFuncGetAttributes(&fa, gemm_q4k_tc_kernel<NH, EW>), "func attributes")) return CKB_ERR_CUDA;
+        if (ckb_check_cuda((int)cudaFuncGetAttributes(&fa, gemm_kq_tc_kernel<WF, NH, EW>), "func attributes")) return CKB_ERR_CUDA;
         if (fa.numRegs != R::LAUNCH)          // a different allocation at launch would make setmaxnreg.inc wait for registers that never come
-            return ckb_fail(CKB_ERR_LIMIT, "gemm_q4k_tc: kernel compiled with an unexpected register count");
-        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_q4k_tc_kernel<NH, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM), "smem attr")) return CKB_ERR_CUDA;
+            return ckb_fail(CKB_ERR_LIMIT, "gemm_kq_tc: kernel compiled with an unexpected register count");
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_kq_tc_kernel<WF, NH, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM), "smem attr")) return CKB_ERR_CUDA;
         attr_set = 1;
     }
     const dim3 grid((N + TC_ROWS - 1) / TC_ROWS, (mtiles + NH - 1) / NH);
-    gemm_q4k_tc_kernel<NH, EW><<<grid, 128 * (3 + EW), TC_SMEM, st>>>(xt, (const uint8_t *)B, bias, C, M, N, nb, ckb_device_error_word());
-    return ckb_check_launch("gemm_q4k_tc");
+    gemm_kq_tc_kernel<WF, NH, EW><<<grid, 128 * (3 + EW), TC_SMEM, st>>>(xt, (const uint8_t *)B, bias, C, ldc, M, N, nb, ckb_device_error_word());
+    return ckb_check_launch("gemm_kq_tc");
 }
 
 #ifdef CKB_TC_PROFILE
 extern "C" int ckb200_tc_profile(float *out64) { return (int)cudaMemcpyFromSymbol(out64, g_tc_prof, sizeof(float) * 64); }
 #endif
 
-// Returns -1 when the shape is not handled here (caller falls back to the per-token path).
-extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
+// C[m * ldc + n] = A_q8[m] . W[n] (+ bias[n]).  wf: TC_W_Q4K (the reference's block_q4_K rows) or TC_W_Q6K_PLANAR.
+// Returns -1 when the shape is not handled here (caller falls back to the per-token path).  min_tokens: smallest M
+// worth the tensor-core path (the token tile is 128 wide; fewer tokens are padded with zeros).
+extern "C" int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens,
+                                  void *stream)
 {
-    if (M < 64 || K % QK_K || ((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3) || ckb_tune_get("gemm_tc", 1) == 0) return -1;
+    if (M < min_tokens || K % QK_K || ((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3) || ckb_tune_get("gemm_tc", 1) == 0) return -1;
     const int nb = K / QK_K, mtiles = (M + TC_ROWS - 1) / TC_ROWS;
     uint8_t *xt = (uint8_t *)ckb_scratch(CKB_SLOT_G, (size_t)mtiles * nb * TC_XBLOB);
     if (!xt) return CKB_ERR_CUDA;
@@ -535,5 +618,29 @@ extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const flo
     // One token tile per CTA with two expander warpgroups measured faster at every prefill size tried (the issuer is
     // bound by shared-memory operand traffic, not by the expansion); the two-tile variant stays selectable for tuning.
     const int nh = ckb_tune_get("gemm_tc_nh", 0) == 2 && mtiles >= 2 ? 2 : 1;
-    return nh == 2 ? launch_tc<2, 1>(xt, B, bias, C, M, N, nb, mtiles, st) : launch_tc<1, 2>(xt, B, bias, C, M, N, nb, mtiles, st);
+    if (wf == TC_W_Q6K_PLANAR)
+        return nh == 2 ? launch_tc<TC_W_Q6K_PLANAR, 2, 1>(xt, B, bias, C, ldc, M, N, nb, mtiles, st)
+                       : launch_tc<TC_W_Q6K_PLANAR, 1, 2>(xt, B, bias, C, ldc, M, N, nb, mtiles, st);
+    return nh == 2 ? launch_tc<TC_W_Q4K, 2, 1>(xt, B, bias, C, ldc, M, N, nb, mtiles, st) : launch_tc<TC_W_Q4K, 1, 2>(xt, B, bias, C, ldc, M, N, nb, mtiles, st);
+}
+
+extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
+{
+    return ckb_launch_gemm_tc(TC_W_Q4K, A_q8, B, bias, C, N, M, N, K, ckb_tune_get("gemm_tc_min_tokens", 16), stream);
+}
+
+// gemm_nt_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268) over weights in the row-planar layout
+extern "C" int ckb200_dev_gemv_q6_k_planar_q8_k(float *, const void *, const void *, int, int, void *);
+extern "C" int ckb200_dev_add_bias_rows(float *, const float *, int, int, void *);
+extern "C" int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream)
+{
+    if (!A_q8 || !B_planar || !C || M <= 0 || N <= 0 || K <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const int rc = ckb_launch_gemm_tc(TC_W_Q6K_PLANAR, A_q8, B_planar, bias, C, N, M, N, K, ckb_tune_get("gemm_tc_min_tokens", 16), stream);
+    if (rc >= 0) return rc;
+    for (int m = 0; m < M; ++m) {
+        const int r2 = ckb200_dev_gemv_q6_k_planar_q8_k(C + (size_t)m * N, B_planar, (const uint8_t *)A_q8 + (size_t)m * (K / QK_K) * Q8K_BYTES, N, K, stream);
+        if (r2) return r2;
+    }
+    return bias ? ckb200_dev_add_bias_rows(C, bias, M, N, stream) : 0;
 }

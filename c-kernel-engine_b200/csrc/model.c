@@ -391,9 +391,19 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
     }
 }
 
+/* tensor-core GEMM of gemm_tc.cu: wf 0 = Q4_K rows, 1 = Q6_K row-planar; -1 when the shape is not handled */
+int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *stream);
+#define MODEL_GEMM_MIN_BATCH 16
+
 /* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
 static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, int y_stride, void *st)
 {
+    if (m->c.batch >= MODEL_GEMM_MIN_BATCH && (w->fmt == FMT_Q4K || (w->fmt == FMT_Q6K && w->planar))) {
+        /* batched decode: the weights are streamed once for all sequences */
+        const int rc = ckb_launch_gemm_tc(w->fmt == FMT_Q6K, xq, w->fmt == FMT_Q6K ? w->planar : w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols,
+                                          MODEL_GEMM_MIN_BATCH, st);
+        if (rc >= 0) return rc;
+    }
     const size_t xrow = w->fmt == FMT_Q80 ? (size_t)(w->cols / 32) * 34 : (size_t)(w->cols / 256) * 292;
     for (int b = 0; b < m->c.batch; ++b) {
         const int rc = gemv_q(w->fmt, y + (size_t)b * y_stride, w, xq + b * xrow, st);
@@ -478,7 +488,7 @@ static int issue_step(CKB200Model *m, void *st)
         if ((rc = norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
         if (t[CKB_T_WK].fmt != t[CKB_T_WQ].fmt && (t[CKB_T_WK].fmt == FMT_Q80 || t[CKB_T_WQ].fmt == FMT_Q80))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
-        if (ckb_tune_get("model_qkv_streams", 1)) {
+        if (ckb_tune_get("model_qkv_streams", 1) && B < MODEL_GEMM_MIN_BATCH) {     /* the batched GEMMs share one workspace: keep them in order */
             cudaStream_t main_st = (cudaStream_t)st;
             if (ckb_check_cuda((int)cudaEventRecord(m->ev_fork, main_st), "fork")) return CKB_ERR_CUDA;
             if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;

@@ -105,6 +105,8 @@ int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void 
 size_t ckb200_q6_k_planar_bytes(int rows, int cols);
 int ckb200_dev_q6_k_to_planar(void *dst_planar, const void *src_q6k_rows, int rows, int cols, void *stream);
 int ckb200_dev_gemv_q6_k_planar_q8_k(float *y, const void *W_planar, const void *x_q8, int M, int K, void *stream);
+/* gemm_nt_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268) over planar weights: tensor-core kernel from 16 tokens up */
+int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);
 
 /* attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406) for `batch`
  * independent sequences: q/out [batch][H][ad], caches [batch][Hkv][capacity][ad] with kv_batch_stride floats

@@ -367,3 +367,42 @@ def test_gemv_q6_k_planar_layout(ck, orc, m, k):
             assert_fp32_close(y.cpu().numpy(), want, f"q6_k planar {m}x{k} rows/group={rows_per_group}")
     finally:
         ck.ckb200_tune_set(b"gemv_q6p_rows", 0)
+
+
+@pytest.mark.parametrize("m,n,k,big_scales", [(16, 128, 256, False), (32, 256, 1024, False), (64, 200, 512, True), (130, 384, 2048, False), (512, 256, 4096, True)])
+def test_gemm_nt_q6_k_planar_tensor_core(ck, orc, m, n, k, big_scales):
+    """Q6_K prefill / batched-decode GEMM on tcgen05 over planar weights; with |scale| up to 127 some products
+    leave the exactly representable fp16 range and are rounded (<= 2^-12 relative on that element)."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    w = synth.make_weights("q6_k", n, k, seed=m + n).reshape(n, k // 256, 210).copy()
+    if big_scales:
+        w[:, :, 192:208] = np.random.default_rng(3).integers(-128, 128, size=(n, k // 256, 16)).astype(np.int8).view(np.uint8)
+    w = w.reshape(-1)
+    a = synth.make_x(k, seed=m, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", "q6_k", a, rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32)
+    want = cases.gemm_nt(orc, "oracle_", "q6_k", aq, w, bias, m, n, k)
+    ck.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+    raw, taq, tb = torch.from_numpy(w).to(dev), torch.from_numpy(aq).to(dev), torch.from_numpy(bias).to(dev)
+    planar = torch.empty(ck.ckb200_q6_k_planar_bytes(n, k), dtype=torch.uint8, device=dev)
+    c = torch.full((m, n), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    assert ck.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), n, k, None) == 0
+    try:
+        for tiles in (1, 2):
+            ck.ckb200_tune_set(b"gemm_tc_nh", tiles)
+            c.fill_(float("nan"))
+            torch.cuda.synchronize()
+            assert ck.ckb200_dev_gemm_nt_q6_k_planar_q8_k(C.c_void_p(taq.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(tb.data_ptr()),
+                                                          C.c_void_p(c.data_ptr()), m, n, k, None) == 0
+            assert ck.ckb200_synchronize() == 0
+            got = c.cpu().numpy()
+            if big_scales:
+                err = np.abs(got.astype(np.float64) - want) / float(np.max(np.abs(want)))
+                assert float(err.max()) <= 2e-4, float(err.max())
+            else:
+                assert_fp32_close(got, want, f"q6_k planar gemm tiles/cta={tiles}")
+    finally:
+        ck.ckb200_tune_set(b"gemm_tc_nh", 0)

@@ -311,8 +311,9 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(max(0, args.streams - 1))]
 
     fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])
-    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}
+    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_planar_q8_0}
     lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+    lib.ckb200_q8_0_planar_bytes.restype = C.c_size_t
     quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0}
 
     results = {}
@@ -325,11 +326,13 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             copies = max(2, -(-L2_BYTES_X4 // nbytes))
             slot = (nbytes + 255) & ~255
             src = torch.from_numpy(w_host).to(dev)
-            if fmt == "q6_k":                              # resident Q6_K weights live in the library's row-planar layout (same bits)
-                nbytes = lib.ckb200_q6_k_planar_bytes(m, k)
+            if fmt in ("q6_k", "q8_0"):                    # resident Q6_K / Q8_0 weights live in the library's row-planar layout (same bits)
+                size_fn, conv_fn = ((lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar) if fmt == "q6_k" else
+                                    (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar))
+                nbytes = size_fn(m, k)
                 slot = (nbytes + 255) & ~255
                 planar = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-                assert lib.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(src.data_ptr()), m, k, sp) == 0
+                assert conv_fn(C.c_void_p(planar.data_ptr()), C.c_void_p(src.data_ptr()), m, k, sp) == 0
                 src = planar
             wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
             for c in range(copies):
@@ -588,7 +591,6 @@ def run_prefill_only(args):
 
     lib = pkg.load_lib()
     assert lib.ckb200_init(0) == 0
-    lib.ckb200_tune_set(b"gemm_tc_nh", args.token_tiles)
     print(json.dumps(prefill_bench(lib, args.prefill_only, args.launches, None, torch, measured_tensor_peak())))
 
 
@@ -661,7 +663,6 @@ def main():
     ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
-    ap.add_argument("--token-tiles", type=int, default=0, choices=[0, 1, 2], help="with --prefill-only: 128-token tiles per CTA (0 = automatic)")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
     args = ap.parse_args()
     if args.single:

@@ -105,6 +105,11 @@ int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void 
 size_t ckb200_q6_k_planar_bytes(int rows, int cols);
 int ckb200_dev_q6_k_to_planar(void *dst_planar, const void *src_q6k_rows, int rows, int cols, void *stream);
 int ckb200_dev_gemv_q6_k_planar_q8_k(float *y, const void *W_planar, const void *x_q8, int M, int K, void *stream);
+/* The same for Q8_0 weights (block_q8_0, include/ckernel_quant.h:104-110, 34 bytes, 2-byte aligned): per row all
+ * quants, then all d.  Same result as ckb200_dev_gemv_q8_0_q8_0 (gemv_q8_0_q8_0, src/kernels/gemm_kernels_q8_0.c:1237-1251). */
+size_t ckb200_q8_0_planar_bytes(int rows, int cols);
+int ckb200_dev_q8_0_to_planar(void *dst_planar, const void *src_q8_0_rows, int rows, int cols, void *stream);
+int ckb200_dev_gemv_q8_0_planar_q8_0(float *y, const void *W_planar, const void *x_q8_0, int M, int K, void *stream);
 /* gemm_nt_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268) over planar weights: tensor-core kernel from 16 tokens up */
 int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);
 

@@ -214,17 +214,14 @@ def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
     aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
     bias = np.random.default_rng(n).standard_normal(n).astype(np.float32) if with_bias else None
     want = cases.gemm_nt(orc, "oracle_", "q4_k", aq, w, bias, m, n, k)
+    got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+    assert_fp32_close(got, want, "q4_k tensor-core path")
     try:
-        for token_tiles_per_cta in (0, 1, 2):         # 0 = the launcher's own choice
-            ck.ckb200_tune_set(b"gemm_tc_nh", token_tiles_per_cta)
-            got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
-            assert_fp32_close(got, want, f"q4_k tiles/cta={token_tiles_per_cta}")
         ck.ckb200_tune_set(b"gemm_tc", 0)
         by_rows = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
     finally:
         ck.ckb200_tune_set(b"gemm_tc", 1)
-        ck.ckb200_tune_set(b"gemm_tc_nh", 0)
-    assert_fp32_close(by_rows, want, "q4_k")
+    assert_fp32_close(by_rows, want, "q4_k per-token path")
 
 
 def test_gemm_nt_q4_k_tensor_core_extreme_values(ck, orc):
@@ -390,19 +387,31 @@ def test_gemm_nt_q6_k_planar_tensor_core(ck, orc, m, n, k, big_scales):
     c = torch.full((m, n), float("nan"), device=dev)
     torch.cuda.synchronize()
     assert ck.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), n, k, None) == 0
-    try:
-        for tiles in (1, 2):
-            ck.ckb200_tune_set(b"gemm_tc_nh", tiles)
-            c.fill_(float("nan"))
-            torch.cuda.synchronize()
-            assert ck.ckb200_dev_gemm_nt_q6_k_planar_q8_k(C.c_void_p(taq.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(tb.data_ptr()),
-                                                          C.c_void_p(c.data_ptr()), m, n, k, None) == 0
-            assert ck.ckb200_synchronize() == 0
-            got = c.cpu().numpy()
-            if big_scales:
-                err = np.abs(got.astype(np.float64) - want) / float(np.max(np.abs(want)))
-                assert float(err.max()) <= 2e-4, float(err.max())
-            else:
-                assert_fp32_close(got, want, f"q6_k planar gemm tiles/cta={tiles}")
-    finally:
-        ck.ckb200_tune_set(b"gemm_tc_nh", 0)
+    assert ck.ckb200_dev_gemm_nt_q6_k_planar_q8_k(C.c_void_p(taq.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(tb.data_ptr()),
+                                                  C.c_void_p(c.data_ptr()), m, n, k, None) == 0
+    assert ck.ckb200_synchronize() == 0
+    got = c.cpu().numpy()
+    if big_scales:
+        err = np.abs(got.astype(np.float64) - want) / float(np.max(np.abs(want)))
+        assert float(err.max()) <= 2e-4, float(err.max())
+    else:
+        assert_fp32_close(got, want, "q6_k planar gemm")
+
+
+@pytest.mark.parametrize("m,k", [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (2, 28672), (4100, 896)])
+def test_gemv_q8_0_planar_layout(ck, orc, m, k):
+    import torch
+
+    dev = torch.device("cuda", 0)
+    w = synth.make_weights("q8_0", m, k, seed=m + k)
+    xq = cases.quantize_act(orc, "oracle_", "q8_0", synth.make_x(k, seed=m + k))
+    want = cases.gemv(orc, "oracle_", "q8_0", w, xq, m, k)
+    ck.ckb200_q8_0_planar_bytes.restype = C.c_size_t
+    raw, txq = torch.from_numpy(w).to(dev), torch.from_numpy(xq).to(dev)
+    planar = torch.full((ck.ckb200_q8_0_planar_bytes(m, k),), 0xAA, dtype=torch.uint8, device=dev)
+    y = torch.full((m,), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    assert ck.ckb200_dev_q8_0_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), m, k, None) == 0
+    assert ck.ckb200_dev_gemv_q8_0_planar_q8_0(C.c_void_p(y.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(txq.data_ptr()), m, k, None) == 0
+    assert ck.ckb200_synchronize() == 0
+    assert_fp32_close(y.cpu().numpy(), want, f"q8_0 planar {m}x{k}")

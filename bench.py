@@ -369,9 +369,14 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         step()                                             # un-captured: sets kernel attributes, warms caches
         launches_per_step = lib.ckb200_launch_count() - launches_before
         torch.cuda.synchronize()
+        # Independent launches on several streams run best when each takes one CTA per SM (kernels of different launches are then
+        # resident together and one launch's ramp-up and tail hide behind the others' streaming); a dependent chain wants the full
+        # occupancy.  The grid size is fixed when the launch is captured.
+        lib.ckb200_tune_set(b"gemv_occ_cap", 1 if args.streams > 1 else 0)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             step(nstreams=args.streams)
+        lib.ckb200_tune_set(b"gemv_occ_cap", 0)
         for _ in range(args.warmup):
             graph.replay()
         torch.cuda.synchronize()
@@ -409,8 +414,10 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         if args.detail:
             for p in plan:                                 # per-shape timing, graph of one rotation of that shape
                 g = torch.cuda.CUDAGraph()
+                lib.ckb200_tune_set(b"gemv_occ_cap", 1 if args.streams > 1 else 0)
                 with torch.cuda.graph(g, stream=stream):
                     step(plan=[p], fmt=fmt, nstreams=args.streams)
+                lib.ckb200_tune_set(b"gemv_occ_cap", 0)
                 g.replay()
                 torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -501,8 +508,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                        "sharding": "each rank streams its own shard of rows; no collective in the data path",
                        "timing": "CUDA graph of one step replayed; CUDA events on the launching stream; max over ranks",
                        "schedule": f"the launches of a step are independent GEMVs and are dealt round-robin to {args.streams} stream(s) "
-                                   "(parallel branches of the graph), as the step executor does with q/k/v; serial_chain_gbs is the "
-                                   "same step as one dependent chain on one stream"},
+                                   "(parallel branches of the graph, one CTA per SM per launch), as the step executor does with q/k/v; "
+                                   "serial_chain_gbs is the same step as one dependent chain on one stream at full occupancy"},
             "serial_chain_gbs": (r["serial_gbs"] * world) if r["serial_gbs"] else None,
             "clocks": {k: r["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if r["clocks"] else None,
             "e2e": e2e,
@@ -659,7 +666,7 @@ def main():
     ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
-    ap.add_argument("--streams", type=int, default=2, help="streams the independent GEMV launches of a sweep step are dealt to")
+    ap.add_argument("--streams", type=int, default=8, help="streams the independent GEMV launches of a sweep step are dealt to")
     ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")

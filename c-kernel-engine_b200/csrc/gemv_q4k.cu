@@ -219,7 +219,8 @@ int launch_pair(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     if (occ_cache_smem != smem) { occ_cache = occupancy_of(kernel, NW * 32, smem); occ_cache_smem = smem; }
     constexpr int rows_per_cta = NW * (32 / G) * R;
     const int ntiles = (M + rows_per_cta - 1) / rows_per_cta;    // CTAs needed if every warp took exactly one item
-    const int cap = ckb_sm_count() * occ_cache;
+    const int occ_cap = ckb_tune_get("gemv_occ_cap", 0);          // fewer resident CTAs per SM leave room for concurrent launches
+    const int cap = ckb_sm_count() * (occ_cap > 0 && occ_cap < occ_cache ? occ_cap : occ_cache);
     int grid = ntiles < cap ? ntiles : cap;
     if (ntiles > ckb_sm_count() && grid % ckb_sm_count()) {       // a whole number of CTAs per SM, so that the round-robin deal is even
         grid = (grid / ckb_sm_count() + 1) * ckb_sm_count();

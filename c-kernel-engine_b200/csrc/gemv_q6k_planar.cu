@@ -177,7 +177,8 @@ int launch_q6p(float *y, const void *W, const void *xq, int M, int nb, cudaStrea
     if (occ_cache_smem != smem) { occ_cache = occupancy_of(kernel, NW * 32, smem); occ_cache_smem = smem; }
     constexpr int rows_per_cta = NW * (32 / G) * R;
     const int ctas_full = (M + rows_per_cta - 1) / rows_per_cta;
-    const int sms = ckb_sm_count(), cap = sms * occ_cache;
+    const int occ_cap = ckb_tune_get("gemv_occ_cap", 0);          // fewer resident CTAs per SM leave room for concurrent launches
+    const int sms = ckb_sm_count(), cap = sms * (occ_cap > 0 && occ_cap < occ_cache ? occ_cap : occ_cache);
     int grid = ctas_full < cap ? ctas_full : cap;
     if (ctas_full > sms && grid % sms) {             // a whole number of CTAs per SM, so that the round-robin deal is even
         grid = (grid / sms + 1) * sms;

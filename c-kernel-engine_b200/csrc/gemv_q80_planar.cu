@@ -135,7 +135,8 @@ int launch_q80p(float *y, const void *W, const void *xq, int M, int nb, cudaStre
     }
     constexpr int rows_per_cta = NW * (32 / G) * R;
     const int ctas_full = (M + rows_per_cta - 1) / rows_per_cta;
-    const int sms = ckb_sm_count(), cap = sms * occ_cache;
+    const int occ_cap = ckb_tune_get("gemv_occ_cap", 0);          // fewer resident CTAs per SM leave room for concurrent launches
+    const int sms = ckb_sm_count(), cap = sms * (occ_cap > 0 && occ_cap < occ_cache ? occ_cap : occ_cache);
     int grid = ctas_full < cap ? ctas_full : cap;
     if (ctas_full > sms && grid % sms) {
         grid = (grid / sms + 1) * sms;

@@ -602,22 +602,35 @@ def run_prefill_only(args):
 
 
 def run_single(args):
-    """A few plain (un-captured) launches of one GEMV on rotating weight copies: the small case for ncu captures."""
+    """A few plain (un-captured) launches of one GEMV on rotating weight copies: the small case for ncu captures.
+    FMT: q4_k, q6_k (ring kernel on the reference's rows), q6_k_planar, q8_0, q8_0_planar."""
     import torch
 
-    fmt, shape = args.single.split(":")
+    name, shape = args.single.split(":")
+    planar = name.endswith("_planar")
+    fmt = name[:-7] if planar else name
     m, k = (int(v) for v in shape.split("x"))
     lib = pkg.load_lib()
     assert lib.ckb200_init(0) == 0
     dev = torch.device("cuda", 0)
-    gemv = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0}[fmt]
+    gemv = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0,
+            "q6_k_planar": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0_planar": lib.ckb200_dev_gemv_q8_0_planar_q8_0}[name]
     quant = lib.ckb200_dev_quantize_q8_0 if fmt == "q8_0" else lib.ckb200_dev_quantize_q8_k
     w_host = synth.make_weights(fmt, m, k, seed=1)
+    src = torch.from_numpy(w_host).to(dev)
     nbytes = w_host.nbytes
+    if planar:
+        size_fn, conv_fn = ((lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar) if fmt == "q6_k" else
+                            (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar))
+        size_fn.restype = C.c_size_t
+        nbytes = size_fn(m, k)
+        dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        assert conv_fn(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), m, k, None) == 0
+        assert lib.ckb200_synchronize() == 0
+        src = dst
     copies = max(2, min(8, -(-600_000_000 // nbytes)))          # > L2 in total, well under 1 GB on the device
     slot = (nbytes + 255) & ~255
     wbuf = torch.empty(copies * slot + 256, dtype=torch.uint8, device=dev)
-    src = torch.from_numpy(w_host).to(dev)
     for c in range(copies):
         wbuf[c * slot:c * slot + nbytes].copy_(src)
     x = torch.from_numpy(synth.make_x(k, seed=1)).to(dev)
@@ -630,6 +643,30 @@ def run_single(args):
         assert gemv(C.c_void_p(y[c].data_ptr()), C.c_void_p(wbuf.data_ptr() + c * slot), C.c_void_p(xq.data_ptr()), m, k, None) == 0
     assert lib.ckb200_synchronize() == 0
     print(json.dumps({"single": args.single, "launches": args.launches, "copies": copies, "bytes_per_launch": synth.gemv_bytes(fmt, m, k)}))
+
+
+def run_attention_only(args):
+    """Plain launches of decode attention on the 70B shape (64 Q / 8 KV heads, d 128) over rotating KV caches."""
+    import torch
+
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    lib.ckb200_attention_decode_scratch_bytes.restype = C.c_size_t
+    dev = torch.device("cuda", 0)
+    H, Hkv, d, T, cap, nl = 64, 8, 128, args.attention_only, args.attention_only + 256, 8
+    q = torch.randn(1, H, d, device=dev)
+    out = torch.empty_like(q)
+    kc = torch.randn(nl, Hkv, cap, d, device=dev)
+    vc = torch.randn(nl, Hkv, cap, d, device=dev)
+    splits = lib.ckb200_attention_decode_splits(1, Hkv, T)
+    scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(1, H, d, splits)) // 4, device=dev)
+    torch.cuda.synchronize()
+    for i in range(args.launches):
+        l = i % nl
+        assert lib.ckb200_dev_attention_decode_ws(C.c_void_p(q.data_ptr()), C.c_void_p(kc[l].data_ptr()), C.c_void_p(vc[l].data_ptr()), C.c_void_p(out.data_ptr()),
+                                                  1, C.c_longlong(Hkv * cap * d), H, Hkv, T, cap, d, d, splits, C.c_void_p(scratch.data_ptr()), None, None) == 0
+    assert lib.ckb200_synchronize() == 0
+    print(json.dumps({"attention_only": T, "launches": args.launches, "splits": splits, "kv_bytes_per_launch": 2 * Hkv * T * d * 4}))
 
 
 def run_decode_only(args):
@@ -667,15 +704,18 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
     ap.add_argument("--streams", type=int, default=8, help="streams the independent GEMV launches of a sweep step are dealt to")
-    ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096")
+    ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096, q6_k_planar:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
+    ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
     args = ap.parse_args()
     if args.single:
         return run_single(args)
     if args.decode_only:
         return run_decode_only(args)
+    if args.attention_only:
+        return run_attention_only(args)
     if args.prefill_only:
         return run_prefill_only(args)
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup

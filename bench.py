@@ -210,22 +210,6 @@ LLAMA3_70B = dict(embed_dim=8192, num_heads=64, num_kv_heads=8, head_dim=128, in
                   max_seq_len=4352, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
 
 
-def tp_setup(lib, rank, world, dev):
-    """Create the NCCL communicator of the library: rank 0 makes the id, torch.distributed carries it."""
-    import torch
-    import torch.distributed as dist
-
-    uid = torch.zeros(128, dtype=torch.uint8, device=dev)
-    if rank == 0:
-        buf = (C.c_char * 128)()
-        assert lib.ckb200_tp_unique_id(buf) == 0
-        uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).to(dev)
-    dist.broadcast(uid, 0)
-    raw = bytes(uid.cpu().numpy().tobytes())
-    if lib.ckb200_tp_init(rank, world, raw) != 0:
-        raise RuntimeError(lib.ckb200_last_error_message().decode())
-
-
 def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None):
     """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens."""
     import torch
@@ -485,9 +469,15 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     decode_tp = None
     if world > 1 and not args.no_decode:
         try:
-            tp_setup(lib, rank, world, dev)
-            decode_tp = [decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}", LLAMA3_70B, 4096, 20, measured_peak()[0],
-                                      batch=b, tp_rank=rank, tp_size=world, dist=dist) for b in (1,)]
+            pkg.tp.setup(lib, rank, world, dev, p2p_floats=32 * LLAMA3_70B["embed_dim"])
+            decode_tp = []
+            for p2p, how in ((1, "one-shot push all-reduce over peer memory"), (0, "NCCL all-reduce")):
+                lib.ckb200_tune_set(b"tp_p2p", p2p)
+                d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}", LLAMA3_70B, 4096, 20, measured_peak()[0],
+                                 batch=1, tp_rank=rank, tp_size=world, dist=dist)
+                d["exchange"] = how
+                decode_tp.append(d)
+            lib.ckb200_tune_set(b"tp_p2p", 1)
         except Exception as exc:
             decode_tp = {"error": repr(exc)}
             lib.ckb200_clear_error()

@@ -10,6 +10,7 @@
 #include <cuda_runtime_api.h>
 #include <dlfcn.h>
 #include <stddef.h>
+#include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -83,10 +84,17 @@ int ckb200_tp_init(int rank, int world, const void *id128)
     return 0;
 }
 
-/* ckb200_allreduce_fn: in-place fp32 sum over all ranks, enqueued on `stream` (capturable in a CUDA graph) */
+int ckb_tp_p2p_allreduce(float *buf, size_t count, void *stream);   /* tp_p2p.cu */
+
+/* ckb200_allreduce_fn: in-place fp32 sum over all ranks, enqueued on `stream` (capturable in a CUDA graph).
+ * Vectors that fit the peer-memory exchange buffer (when the ranks have connected one) take the one-shot push
+ * kernel; everything else goes through NCCL.  Every rank takes the same branch: the choice depends only on the
+ * count and on state that all ranks set up together. */
 int ckb200_tp_allreduce(void *ctx, float *buf, size_t count, void *stream)
 {
     (void)ctx;
+    if (ckb200_tp_p2p_ready() && count <= ckb200_tp_p2p_max_floats() && !((uintptr_t)buf & 15) && ckb_tune_get("tp_p2p", 1))
+        return ckb_tp_p2p_allreduce(buf, count, stream);
     if (!g_tp.comm) return ckb_fail(CKB_ERR_STATE, "tp_allreduce: ckb200_tp_init has not been called");
     return tp_check(g_tp.AllReduce(buf, buf, count, NCCL_FLOAT, NCCL_SUM, g_tp.comm, ckb_stream(stream)), "ncclAllReduce");
 }
@@ -96,6 +104,7 @@ int ckb200_tp_world(void) { return g_tp.comm ? g_tp.world : 1; }
 
 void ckb200_tp_shutdown(void)
 {
+    ckb200_tp_p2p_shutdown();
     if (g_tp.comm) {
         cudaStreamSynchronize(ckb_stream(NULL));
         g_tp.CommDestroy(g_tp.comm);

@@ -1,0 +1,184 @@
+// Tensor-parallel exchange over peer memory: a one-shot fp32 sum all-reduce for the small [batch, hidden] vectors that
+// follow the row-parallel o_proj and down_proj GEMVs of a sharded decode step.  The reference has no collective of any
+// kind (one process, one thread pool: include/ck_threadpool.h:1-30); NCCL (tp_nccl.c) is the general path, this kernel is
+// the latency path: there are two exchanges per layer and each carries only 32 KB per rank at batch 1.
+//
+// One process per GPU.  Every rank owns one buffer (cudaMalloc, exported with cudaIpcGetMemHandle, opened by its peers):
+//     lines [2 parities][world sources][max_floats / 2] x 16 bytes   { value 2i, call number, value 2i+1, call number }
+// Data and flag travel in the same 16-byte store (each 8-byte half is written atomically and carries its own copy of the
+// call number), so a receiver that reads both call numbers equal to the current one holds both values: no fence, no
+// separate flag, one NVLink crossing of latency.  A call (number e, parity e & 1) on rank r: every thread stores its
+// lines into slot (e & 1, r) of every PEER, then polls the same lines of slots (e & 1, s) in its OWN buffer for the
+// other sources s, and sums the world values in rank order (deterministic; its own value comes from registers).  Only
+// local memory is ever polled or read.  Two parities are enough: a rank cannot finish call e + 1 before every peer has
+// stored for e + 1, which a peer does only after it has finished reading call e.  The call number lives in device memory
+// and is advanced by the last CTA of a call, so a captured CUDA graph can be replayed.
+//
+// The poll is bounded (about ten seconds of SM clock: ranks reach their first step at different times); a timeout sets
+// the device error word and leaves the vector unreduced.  No multicast, no peer loads: remote stores only.
+#include "device_common.cuh"
+#include "launch.h"
+#include "pdl.cuh"
+#include "runtime.h"
+
+#include <string.h>
+
+namespace ckb {
+
+constexpr int P2P_MAX_CTAS = 32, P2P_THREADS = 256, P2P_MAX_WORLD = 8;
+
+struct P2PView {
+    uint4 *lines[P2P_MAX_WORLD];         // line area of every rank's buffer (this rank's own included)
+    unsigned *epoch;                     // this rank's call number, and behind it the count of CTAs that finished the call
+    size_t max_lines;
+    int rank, world;
+};
+
+__device__ __forceinline__ void st_line(uint4 *p, const uint4 &v)
+{
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line(const uint4 *p)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *__restrict__ buf, size_t count, P2PView v, int *__restrict__ dev_err)
+{
+    pdl_trigger();
+    pdl_wait();
+    const int W = v.world, me = v.rank;
+    const unsigned e = *reinterpret_cast<volatile unsigned *>(v.epoch) + 1u, par = e & 1u;
+    const size_t nl = (count + 1) / 2, stride = (size_t)gridDim.x * P2P_THREADS, first = (size_t)blockIdx.x * P2P_THREADS + threadIdx.x;
+    const size_t my_slot = ((size_t)par * W + me) * v.max_lines;
+
+    for (size_t i = first; i < nl; i += stride) {
+        const float x0 = __ldcg(buf + 2 * i), x1 = 2 * i + 1 < count ? __ldcg(buf + 2 * i + 1) : 0.0f;
+        const uint4 line = make_uint4(__float_as_uint(x0), e, __float_as_uint(x1), e);
+        for (int r = 0; r < W; ++r)
+            if (r != me) st_line(v.lines[r] + my_slot + i, line);
+    }
+    const long long t0 = clock64();
+    bool ok = true;
+    for (size_t i = first; i < nl && ok; i += stride) {
+        float s0 = 0.0f, s1 = 0.0f;
+        for (int src = 0; src < W; ++src) {
+            float a, b;
+            if (src == me) {
+                a = __ldcg(buf + 2 * i);
+                b = 2 * i + 1 < count ? __ldcg(buf + 2 * i + 1) : 0.0f;
+            } else {
+                const uint4 *p = v.lines[me] + ((size_t)par * W + src) * v.max_lines + i;
+                uint4 l = ld_line(p);
+                while (l.y != e || l.w != e) {
+                    if (clock64() - t0 > (1ll << 34)) { ok = false; break; }
+                    l = ld_line(p);
+                }
+                if (!ok) break;
+                a = __uint_as_float(l.x);
+                b = __uint_as_float(l.z);
+            }
+            s0 = src ? s0 + a : a;
+            s1 = src ? s1 + b : b;
+        }
+        if (ok) {
+            buf[2 * i] = s0;
+            if (2 * i + 1 < count) buf[2 * i + 1] = s1;
+        }
+    }
+    if (!ok) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(v.epoch + 1, 1u) == gridDim.x - 1) {      // last CTA of this call: every CTA has read the call number
+            v.epoch[1] = 0;
+            *reinterpret_cast<volatile unsigned *>(v.epoch) = e;
+        }
+    }
+}
+
+}  // namespace ckb
+
+using namespace ckb;
+
+static struct {
+    uint8_t *local;                      // this rank's buffer
+    void *peer_base[P2P_MAX_WORLD];      // opened peer buffers (NULL for self)
+    P2PView view;
+    size_t bytes;
+    int ready;
+} g_p2p;
+
+static size_t p2p_line_bytes(int world, size_t max_floats) { return 2 * (size_t)world * (max_floats / 2) * sizeof(uint4); }
+static size_t p2p_total_bytes(int world, size_t max_floats) { return p2p_line_bytes(world, max_floats) + 256; }
+
+// Allocates this rank's exchange buffer for vectors of up to max_floats (a multiple of 4) and writes its 64-byte IPC handle.
+extern "C" int ckb200_tp_p2p_create(int rank, int world, size_t max_floats, void *handle_out64)
+{
+    if (!handle_out64 || world < 2 || world > P2P_MAX_WORLD || rank < 0 || rank >= world || max_floats == 0 || max_floats % 4)
+        return ckb_fail(CKB_ERR_STATE, "tp_p2p_create: bad rank %d / world %d / size %zu", rank, world, max_floats);
+    if (g_p2p.local) return ckb_fail(CKB_ERR_STATE, "tp_p2p_create: already created");
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    g_p2p.bytes = p2p_total_bytes(world, max_floats);
+    if (ckb_check_cuda((int)cudaMalloc((void **)&g_p2p.local, g_p2p.bytes), "cudaMalloc(tp exchange buffer)")) return CKB_ERR_CUDA;
+    if (ckb_check_cuda((int)cudaMemset(g_p2p.local, 0, g_p2p.bytes), "cudaMemset(tp exchange buffer)")) return CKB_ERR_CUDA;
+    cudaIpcMemHandle_t h;
+    if (ckb_check_cuda((int)cudaIpcGetMemHandle(&h, g_p2p.local), "cudaIpcGetMemHandle")) return CKB_ERR_CUDA;
+    memcpy(handle_out64, &h, 64);
+    memset(&g_p2p.view, 0, sizeof g_p2p.view);
+    g_p2p.view.rank = rank;
+    g_p2p.view.world = world;
+    g_p2p.view.max_lines = max_floats / 2;
+    return 0;
+}
+
+// all_handles: the 64-byte handles of ranks 0 .. world-1 in rank order (gathered by the host program)
+extern "C" int ckb200_tp_p2p_connect(const void *all_handles)
+{
+    if (!all_handles || !g_p2p.local) return ckb_fail(CKB_ERR_STATE, "tp_p2p_connect: ckb200_tp_p2p_create has not been called");
+    const int W = g_p2p.view.world, me = g_p2p.view.rank;
+    for (int r = 0; r < W; ++r) {
+        uint8_t *base = g_p2p.local;
+        if (r != me) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const uint8_t *)all_handles + 64 * (size_t)r, 64);
+            void *p = NULL;
+            if (ckb_check_cuda((int)cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return CKB_ERR_CUDA;
+            g_p2p.peer_base[r] = p;
+            base = (uint8_t *)p;
+        }
+        g_p2p.view.lines[r] = (uint4 *)base;
+    }
+    g_p2p.view.epoch = (unsigned *)(g_p2p.local + p2p_line_bytes(W, 2 * g_p2p.view.max_lines));
+    g_p2p.ready = 1;
+    return 0;
+}
+
+extern "C" int ckb200_tp_p2p_ready(void) { return g_p2p.ready; }
+extern "C" size_t ckb200_tp_p2p_max_floats(void) { return g_p2p.ready ? 2 * g_p2p.view.max_lines : 0; }
+
+// In-place sum over all ranks of buf[0 .. count) (count <= max_floats, buf 16-byte aligned); capturable.
+extern "C" int ckb_tp_p2p_allreduce(float *buf, size_t count, void *stream)
+{
+    if (!g_p2p.ready) return ckb_fail(CKB_ERR_STATE, "tp_p2p_allreduce: not connected");
+    if (count > 2 * g_p2p.view.max_lines) return ckb_fail(CKB_ERR_LIMIT, "tp_p2p_allreduce: %zu floats exceed the exchange buffer", count);
+    if (count == 0) return 0;
+    const size_t nl = (count + 1) / 2;
+    size_t ctas = (nl + P2P_THREADS - 1) / P2P_THREADS;
+    if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
+    return launch_pdl("tp_allreduce_push", tp_allreduce_push_kernel, dim3((unsigned)ctas), dim3(P2P_THREADS), 0, ckb_stream(stream), buf, count, g_p2p.view,
+                      ckb_device_error_word());
+}
+
+extern "C" void ckb200_tp_p2p_shutdown(void)
+{
+    if (!g_p2p.local) return;
+    cudaStreamSynchronize(ckb_stream(NULL));
+    for (int r = 0; r < P2P_MAX_WORLD; ++r)
+        if (g_p2p.peer_base[r]) { cudaIpcCloseMemHandle(g_p2p.peer_base[r]); g_p2p.peer_base[r] = NULL; }
+    cudaFree(g_p2p.local);
+    memset(&g_p2p, 0, sizeof g_p2p);
+}

@@ -76,6 +76,15 @@ int ckb200_tp_allreduce(void *ctx, float *buf, size_t count, void *stream);   /*
 int ckb200_tp_rank(void);
 int ckb200_tp_world(void);
 void ckb200_tp_shutdown(void);
+/* Optional latency path for small vectors: a one-shot push all-reduce over peer memory (CUDA IPC, NVLink stores).
+ * Every rank calls create (max_floats a multiple of 4; writes its 64-byte handle), the caller gathers the handles
+ * of ranks 0 .. world-1 in rank order, every rank calls connect.  ckb200_tp_allreduce then uses it for counts
+ * <= max_floats (tune "tp_p2p" 0 switches it off); waits are bounded and report through the device error word. */
+int ckb200_tp_p2p_create(int rank, int world, size_t max_floats, void *handle_out64);
+int ckb200_tp_p2p_connect(const void *all_handles);
+int ckb200_tp_p2p_ready(void);
+size_t ckb200_tp_p2p_max_floats(void);
+void ckb200_tp_p2p_shutdown(void);
 void ckb200_model_use_tp(CKB200Model *m);                                     /* set_allreduce(m, ckb200_tp_allreduce, NULL) */
 
 #ifdef __cplusplus

@@ -1,4 +1,5 @@
-"""Tensor-parallel decode on 2 GPUs: one process per GPU, the NCCL all-reduce after o_proj and down_proj,
+"""Tensor-parallel decode on 2 GPUs: one process per GPU, the all-reduce after o_proj and down_proj (peer-memory
+push kernel checked against NCCL, then used by the step),
 logits of every rank against the unsharded CPU step.  Skipped on a box with a single GPU."""
 from __future__ import annotations
 
@@ -40,14 +41,24 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     lib = graft.load_package().load_lib()
     assert lib.ckb200_init(rank) == 0
     so.bind_model_api(lib)
-    uid = torch.zeros(128, dtype=torch.uint8)
-    if rank == 0:
-        buf = (C.c_char * 128)()
-        assert lib.ckb200_tp_unique_id(buf) == 0
-        uid = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
-    dist.broadcast(uid, 0)
-    raw = bytes(uid.numpy().tobytes())
-    assert lib.ckb200_tp_init(rank, world, raw) == 0, lib.ckb200_last_error_message()
+    pkg = graft.load_package()
+    pkg.tp.setup(lib, rank, world, None, p2p_floats=4096)
+    assert lib.ckb200_tp_p2p_ready() == 1
+
+    # the exchange step alone: the peer-memory kernel against NCCL on the same vectors (both sum in fp32; two
+    # ranks: one addition, so bit-exact), several calls in a row to cross both buffer parities, ragged counts
+    lib.ckb200_tp_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    for call, count in enumerate((4096, 1000, 4, 4096, 2052, 1)):
+        x = torch.from_numpy(np.random.default_rng(100 * call + rank).standard_normal(count).astype(np.float32)).cuda()
+        got, want = x.clone(), x.clone()
+        torch.cuda.synchronize()
+        lib.ckb200_tune_set(b"tp_p2p", 1)
+        assert lib.ckb200_tp_allreduce(None, got.data_ptr(), count, None) == 0, lib.ckb200_last_error_message()
+        lib.ckb200_tune_set(b"tp_p2p", 0)
+        assert lib.ckb200_tp_allreduce(None, want.data_ptr(), count, None) == 0, lib.ckb200_last_error_message()
+        assert lib.ckb200_synchronize() == 0, lib.ckb200_last_error_message()
+        assert torch.equal(got, want), (rank, call, count)
+    lib.ckb200_tune_set(b"tp_p2p", 1)
 
     cpu = so.CpuModel(TP_CFG, seed=5)
     cpu.prefill_kv(20, seed=6)

@@ -40,44 +40,62 @@ constexpr int TC_ROWS = 128;                          // rows of either operand 
 constexpr int TC_CHUNK = TC_ROWS * 16;                // one 8-element k-chunk of 128 rows: 2048 B
 constexpr int TC_STAGE = 8 * TC_CHUNK;                // 64-deep k-stage of 128 rows: 16 KB
 constexpr int TC_AUX = 2 * TC_CHUNK;                  // 16-deep tile (mins / bsums): 4 KB
-constexpr int TC_STAGES = 6;                          // ring depth (a stage = weight tile + activation tile)
-// activation blob of one (token tile, superblock): 4 k-stages, the bsum tile, 128 block scales
-constexpr int TC_XBLOB_B2 = 4 * TC_STAGE;
-constexpr int TC_XBLOB_DX = TC_XBLOB_B2 + TC_AUX;
-constexpr int TC_XBLOB = TC_XBLOB_DX + TC_ROWS * 4;   // 70144 B, a multiple of 16
 
-constexpr int TC_OFF_A = 0;                                           // weight tiles   [TC_STAGES][16 KB]
-constexpr int TC_OFF_B = TC_OFF_A + TC_STAGES * TC_STAGE;             // activation tiles
-constexpr int TC_OFF_A2 = TC_OFF_B + TC_STAGES * TC_STAGE;            // mins tiles     [2][4 KB]
-constexpr int TC_OFF_B2 = TC_OFF_A2 + 2 * TC_AUX;                     // bsum tiles     [2][4 KB]
-constexpr int TC_OFF_DX = TC_OFF_B2 + 2 * TC_AUX;                     // block scales   [2][128] fp32
-constexpr int TC_OFF_BAR = TC_OFF_DX + 2 * TC_ROWS * 4;
-enum { BAR_FULL = 0, BAR_EMPTY = TC_STAGES, BAR_A2_EMPTY = 2 * TC_STAGES, BAR_B2_EMPTY = BAR_A2_EMPTY + 2, BAR_DX_FULL = BAR_B2_EMPTY + 2,
-       BAR_T_FULL = BAR_DX_FULL + 2, BAR_T_EMPTY = BAR_T_FULL + 2, BAR_COUNT = BAR_T_EMPTY + 2 };
-constexpr int TC_SMEM = TC_OFF_BAR + BAR_COUNT * 8 + 16;
+// Everything that depends on the width NT of the token tile (the N operand of the MMA).  NT = 128 is the prefill
+// shape: one CTA of 640 threads per SM.  NT = 32 is the batched-decode shape (up to 64 tokens): the activation tiles,
+// the drain and the accumulators shrink so far that two CTAs of 512 threads share an SM, and every latency of the
+// per-stage chain (weight loads, barrier waits, MMA issue, commit) is overlapped by the neighbour.
+template <int NT>
+struct TcCfg {
+    static constexpr int STAGES = NT == 128 ? 6 : 5;          // ring depth (a stage = weight tile + activation tile)
+    static constexpr int B_CHUNK = NT * 16;                   // one 8-element k-chunk of NT tokens
+    static constexpr int B_STAGE = 8 * B_CHUNK;               // 64-deep k-stage of NT tokens
+    static constexpr int B_AUX = 2 * B_CHUNK;                 // 16-deep bsum tile
+    // activation blob of one (token tile, superblock): 4 k-stages, the bsum tile, NT block scales
+    static constexpr int XBLOB_B2 = 4 * B_STAGE, XBLOB_DX = XBLOB_B2 + B_AUX, XBLOB = XBLOB_DX + NT * 4;   // a multiple of 16
+    static constexpr int OFF_A = 0;                                      // weight tiles   [STAGES][16 KB]
+    static constexpr int OFF_B = OFF_A + STAGES * TC_STAGE;              // activation tiles
+    static constexpr int OFF_A2 = OFF_B + STAGES * B_STAGE;              // mins tiles     [2][4 KB]
+    static constexpr int OFF_B2 = OFF_A2 + 2 * TC_AUX;                   // bsum tiles     [2]
+    static constexpr int OFF_DX = OFF_B2 + 2 * B_AUX;                    // block scales   [2][NT] fp32
+    static constexpr int OFF_BAR = OFF_DX + 2 * NT * 4;
+    static constexpr int BAR_FULL = 0, BAR_EMPTY = STAGES, BAR_A2_EMPTY = 2 * STAGES, BAR_B2_EMPTY = BAR_A2_EMPTY + 2, BAR_DX_FULL = BAR_B2_EMPTY + 2,
+                         BAR_T_FULL = BAR_DX_FULL + 2, BAR_T_EMPTY = BAR_T_FULL + 2, BAR_COUNT = BAR_T_EMPTY + 2;
+    static constexpr int SMEM = OFF_BAR + BAR_COUNT * 8 + 16;
+    static constexpr int DRAIN_WARPS = NT == 128 ? 8 : 4;     // 4 TMEM lane quarters x column halves
+    static constexpr int DRAIN_COLS = NT / (DRAIN_WARPS / 4); // token columns per drain thread
+    static constexpr int THREADS = (12 + DRAIN_WARPS) * 32, CTAS_PER_SM = NT == 128 ? 1 : 2;
+    // Register counts per role after setmaxnreg.  setmaxnreg.inc blocks until the CTA's own pool (threads x registers
+    // at launch) can supply the registers, so 128 * CTL + 256 * EXP + 32 * DRAIN_WARPS * DRAIN must not exceed
+    // THREADS * LAUNCH; the launcher checks the compiled register count against LAUNCH before the first launch.
+    static constexpr int REGS_LAUNCH = NT == 128 ? 96 : 64, REGS_CTL = 32, REGS_EXP = 72, REGS_DRAIN = NT == 128 ? 152 : 80;
+    static_assert(128 * REGS_CTL + 256 * REGS_EXP + 32 * DRAIN_WARPS * REGS_DRAIN <= THREADS * REGS_LAUNCH, "setmaxnreg targets exceed the CTA's register pool");
+    static_assert(THREADS * REGS_LAUNCH * CTAS_PER_SM <= 65536, "register plan");
+    static constexpr uint32_t TMEM_COLS = NT == 128 ? 512 : 128, T_BUF = TMEM_COLS / 2, T2_OFF = NT;   // buffer u & 1 at column T_BUF * (u & 1): T at +0, T2 at +NT
+    // instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = NT
+    static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+    static_assert(CTAS_PER_SM * (SMEM + 1024) <= 228 * 1024 && SMEM <= 227 * 1024, "shared memory plan");
+};
 
 // shared-memory matrix descriptor: K-major, no swizzle; LBO = distance between the two 8-element k-chunks of
-// one MMA (2048 B), SBO = distance between 8-row groups (128 B); version 1 (Blackwell)
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr)
+// one MMA (rows x 16 B), SBO = distance between 8-row groups (128 B); version 1 (Blackwell)
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t chunk_bytes)
 {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(TC_CHUNK >> 4) << 16;
+    d |= (uint64_t)(chunk_bytes >> 4) << 16;
     d |= (uint64_t)(128 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     return d;
 }
 
-// instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128
-constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_ROWS >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
-
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate)
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(TC_IDESC), "r"(accumulate), "r"(0u));
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u));
 }
 __device__ __forceinline__ void tc_commit(uint32_t bar)
 {
@@ -149,27 +167,31 @@ __device__ __forceinline__ uint4 s8_chunk_to_half(uint32_t w0, uint32_t w1)
 }
 
 __device__ __forceinline__ uint32_t tc_tile_offset(int row, int kchunk) { return (uint32_t)(kchunk * TC_CHUNK + (row >> 3) * 128 + (row & 7) * 16); }
+template <int NT>
+__device__ __forceinline__ uint32_t tc_xtile_offset(int tok, int kchunk) { return (uint32_t)(kchunk * TcCfg<NT>::B_CHUNK + (tok >> 3) * 128 + (tok & 7) * 16); }
 
 // ---------------------------------------------------------------- activation tiles
 
 // grid (superblocks, token tiles); consecutive threads take consecutive tokens of one k-chunk, so every warp
 // writes 512 contiguous bytes of the blob
+template <int NT>
 __global__ void __launch_bounds__(256) gemm_x_tiles_kernel(const uint8_t *__restrict__ A_q8, uint8_t *__restrict__ xt, int M, int nb)
 {
+    using Cfg = TcCfg<NT>;
     const int b = blockIdx.x, mt = blockIdx.y;
-    uint8_t *blob = xt + ((size_t)mt * nb + b) * TC_XBLOB;
-    for (int it = threadIdx.x; it < TC_ROWS * 32; it += 256) {
-        const int t = it & (TC_ROWS - 1), kc = it >> 7, m = mt * TC_ROWS + t;
+    uint8_t *blob = xt + ((size_t)mt * nb + b) * Cfg::XBLOB;
+    for (int it = threadIdx.x; it < NT * 32; it += 256) {
+        const int t = it % NT, kc = it / NT, m = mt * NT + t;
         uint32_t w0 = 0, w1 = 0;
         if (m < M) {
             const uint32_t *blk = reinterpret_cast<const uint32_t *>(A_q8 + ((size_t)m * nb + b) * Q8K_BYTES);
             w0 = __ldcg(blk + 1 + 2 * kc);
             w1 = __ldcg(blk + 2 + 2 * kc);
         }
-        *reinterpret_cast<uint4 *>(blob + (kc >> 3) * TC_STAGE + tc_tile_offset(t, kc & 7)) = s8_chunk_to_half(w0, w1);
+        *reinterpret_cast<uint4 *>(blob + (kc >> 3) * Cfg::B_STAGE + tc_xtile_offset<NT>(t, kc & 7)) = s8_chunk_to_half(w0, w1);
     }
-    {
-        const int t = threadIdx.x & (TC_ROWS - 1), g = threadIdx.x >> 7, m = mt * TC_ROWS + t;    // bsums[8g .. 8g+7], |bsum| <= 2048: exact
+    if (threadIdx.x < 2 * NT) {
+        const int t = threadIdx.x % NT, g = threadIdx.x / NT, m = mt * NT + t;    // bsums[8g .. 8g+7], |bsum| <= 2048: exact
         uint32_t o[4] = {0u, 0u, 0u, 0u};
         float d = 0.0f;
         if (m < M) {
@@ -182,8 +204,8 @@ __global__ void __launch_bounds__(256) gemm_x_tiles_kernel(const uint8_t *__rest
             }
             d = __uint_as_float(__ldcg(blk));
         }
-        *reinterpret_cast<uint4 *>(blob + TC_XBLOB_B2 + tc_tile_offset(t, g)) = make_uint4(o[0], o[1], o[2], o[3]);
-        if (g == 0) reinterpret_cast<float *>(blob + TC_XBLOB_DX)[t] = d;
+        *reinterpret_cast<uint4 *>(blob + Cfg::XBLOB_B2 + tc_xtile_offset<NT>(t, g)) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (g == 0) reinterpret_cast<float *>(blob + Cfg::XBLOB_DX)[t] = d;
     }
 }
 
@@ -199,73 +221,73 @@ __device__ long long g_tc_trace[4][1024];
 
 enum { TC_W_Q4K = 0, TC_W_Q6K_PLANAR = 1 };       // weight operand formats
 
-// Register counts per role after setmaxnreg.  setmaxnreg.inc blocks until the CTA's own pool (threads x registers at
-// launch) can supply the registers, so 128 * (CTL + 2 * EXP + 2 * DRAIN) must not exceed 640 * LAUNCH; the launcher
-// checks the compiled register count against LAUNCH before the first launch.
-constexpr int TC_THREADS = 640, TC_REGS_LAUNCH = 96, TC_REGS_CTL = 32, TC_REGS_EXP = 72, TC_REGS_DRAIN = 152;
-static_assert(128 * (TC_REGS_CTL + 2 * TC_REGS_EXP + 2 * TC_REGS_DRAIN) <= TC_THREADS * TC_REGS_LAUNCH, "setmaxnreg targets exceed the CTA's register pool");
-static_assert(TC_THREADS * TC_REGS_LAUNCH <= 65536, "register plan");
-
-template <int WF>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B, const float *__restrict__ bias, float *__restrict__ C, int ldc, int M,
-                  int N, int nb, int *__restrict__ dev_err)
+// Split K: blockIdx.z takes the superblocks [z * nbz, z * nbz + nbz) and writes its partial sums to C + z * cz
+// (the launcher adds the slices up in a fixed order); a single slice writes C itself, bias included.
+template <int WF, int NT>
+__global__ void __launch_bounds__(TcCfg<NT>::THREADS, TcCfg<NT>::CTAS_PER_SM)
+gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B, const float *__restrict__ bias, float *__restrict__ C, int ldc, size_t cz,
+                  int M, int N, int nb_row, int nbz, int *__restrict__ dev_err)
 {
+    using Cfg = TcCfg<NT>;
+    constexpr int TC_STAGES = Cfg::STAGES, BAR_FULL = Cfg::BAR_FULL, BAR_EMPTY = Cfg::BAR_EMPTY, BAR_A2_EMPTY = Cfg::BAR_A2_EMPTY, BAR_B2_EMPTY = Cfg::BAR_B2_EMPTY,
+                  BAR_DX_FULL = Cfg::BAR_DX_FULL, BAR_T_FULL = Cfg::BAR_T_FULL, BAR_T_EMPTY = Cfg::BAR_T_EMPTY;
+    constexpr int TC_OFF_A = Cfg::OFF_A, TC_OFF_A2 = Cfg::OFF_A2, TC_OFF_DX = Cfg::OFF_DX;
+    const int kb0 = blockIdx.z * nbz, nb = min(nbz, nb_row - kb0);         // this slice: superblocks kb0 .. kb0 + nb of rows that hold nb_row
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t s_base = smem_u32(smem);
-    const uint32_t sA = s_base + TC_OFF_A, sB = s_base + TC_OFF_B, sA2 = s_base + TC_OFF_A2, sB2 = s_base + TC_OFF_B2, sDX = s_base + TC_OFF_DX;
-    const uint32_t sBar = s_base + TC_OFF_BAR;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + TC_OFF_BAR + BAR_COUNT * 8);
+    const uint32_t sA = s_base + Cfg::OFF_A, sB = s_base + Cfg::OFF_B, sA2 = s_base + Cfg::OFF_A2, sB2 = s_base + Cfg::OFF_B2, sDX = s_base + Cfg::OFF_DX;
+    const uint32_t sBar = s_base + Cfg::OFF_BAR;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + Cfg::OFF_BAR + Cfg::BAR_COUNT * 8);
 #define BAR(i) (sBar + 8u * (uint32_t)(i))
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n0 = blockIdx.x * TC_ROWS, mt = blockIdx.y, m0 = mt * TC_ROWS;
+    const int n0 = blockIdx.x * TC_ROWS, mt = blockIdx.y, m0 = mt * NT;
     const uint32_t stages = (uint32_t)nb * 4u;
 
     if (tid == 0) {
         for (int i = 0; i < TC_STAGES; ++i) { mbar_init(BAR(BAR_FULL + i), 5); mbar_init(BAR(BAR_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(BAR_A2_EMPTY + i), 1);
-            mbar_init(BAR(BAR_B2_EMPTY + i), 9);          // the T2 MMA (or, for Q6_K, the unit's last commit) and the 8 drain warps
+            mbar_init(BAR(BAR_B2_EMPTY + i), 1 + Cfg::DRAIN_WARPS);   // the T2 MMA (or, for Q6_K, the unit's last commit) and the drain warps
             mbar_init(BAR(BAR_DX_FULL + i), 1);
             mbar_init(BAR(BAR_T_FULL + i), 1);
-            mbar_init(BAR(BAR_T_EMPTY + i), 8);
+            mbar_init(BAR(BAR_T_EMPTY + i), Cfg::DRAIN_WARPS);
         }
         mbar_fence_init();
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;                 // buffer u & 1 at column 256 * (u & 1): T at +0, T2 at +128
+    const uint32_t tmem = *tmem_slot;
 
 #define TC_SETMAXNREG(op, n) asm volatile("setmaxnreg." op ".sync.aligned.u32 %0;" ::"n"(n))
 #define TC_WAIT(bar, parity, code)                                        \
     if (!mbar_wait_spin(bar, parity)) { atomicExch(dev_err, code); break; }
 
     if (warp < 4) {
-        TC_SETMAXNREG("dec", TC_REGS_CTL);
+        TC_SETMAXNREG("dec", Cfg::REGS_CTL);
         if (warp == 0) {
             // ------------------------------------------------------------ loader
             uint32_t issued = 0;
             for (uint32_t it = 0; it < stages; ++it) {
                 const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, x = b & 1u;
-                const uint8_t *blob = xt + ((size_t)mt * nb + b) * TC_XBLOB;
+                const uint8_t *blob = xt + ((size_t)mt * nb_row + kb0 + b) * Cfg::XBLOB;
                 TC_WAIT(BAR(BAR_EMPTY + i), ((it / TC_STAGES) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT);
                 if (s == 3) { TC_WAIT(BAR(BAR_B2_EMPTY + x), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }
                 if (tc_elect_one()) {
                     // the bsum tile of the superblock rides on the barrier of its last k-stage (the issuer needs it for the T2 MMA
                     // right after that stage); the block scales have their own barrier, for the drain warps
                     const bool with_bsums = s == 3 && WF == TC_W_Q4K;
-                    mbar_arrive_expect_tx(BAR(BAR_FULL + i), TC_STAGE + (with_bsums ? TC_AUX : 0));
-                    bulk_g2s(sB + i * TC_STAGE, blob + s * TC_STAGE, TC_STAGE, BAR(BAR_FULL + i));
-                    if (with_bsums) bulk_g2s(sB2 + x * TC_AUX, blob + TC_XBLOB_B2, TC_AUX, BAR(BAR_FULL + i));
+                    mbar_arrive_expect_tx(BAR(BAR_FULL + i), Cfg::B_STAGE + (with_bsums ? Cfg::B_AUX : 0));
+                    bulk_g2s(sB + i * Cfg::B_STAGE, blob + s * Cfg::B_STAGE, Cfg::B_STAGE, BAR(BAR_FULL + i));
+                    if (with_bsums) bulk_g2s(sB2 + x * Cfg::B_AUX, blob + Cfg::XBLOB_B2, Cfg::B_AUX, BAR(BAR_FULL + i));
                     if (s == 3) {
-                        mbar_arrive_expect_tx(BAR(BAR_DX_FULL + x), TC_ROWS * 4);
-                        bulk_g2s(sDX + x * TC_ROWS * 4, blob + TC_XBLOB_DX, TC_ROWS * 4, BAR(BAR_DX_FULL + x));
+                        mbar_arrive_expect_tx(BAR(BAR_DX_FULL + x), NT * 4);
+                        bulk_g2s(sDX + x * NT * 4, blob + Cfg::XBLOB_DX, NT * 4, BAR(BAR_DX_FULL + x));
                     }
                 }
                 issued = it + 1;
@@ -277,9 +299,9 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
         } else if (warp == 1) {
             // ------------------------------------------------------------ issuer: the warp runs the loop and the waits uniformly
             // (descriptors and addresses stay in uniform registers), one elected lane issues
-            const uint64_t dA = tc_smem_desc(sA), dB = tc_smem_desc(sB), dA2 = tc_smem_desc(sA2), dB2 = tc_smem_desc(sB2);
+            const uint64_t dA = tc_smem_desc(sA, TC_CHUNK), dB = tc_smem_desc(sB, Cfg::B_CHUNK), dA2 = tc_smem_desc(sA2, TC_CHUNK), dB2 = tc_smem_desc(sB2, Cfg::B_CHUNK);
             for (uint32_t it = 0; it < stages; ++it) {
-                const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, buf = b & 1u, tacc = tmem + 256u * buf;
+                const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, buf = b & 1u, tacc = tmem + Cfg::T_BUF * buf;
                 if (s == 0) {
                     TC_WAIT(BAR(BAR_T_EMPTY + buf), ((b >> 1) & 1u) ^ 1u, DEV_ERR_MMA_WAIT);
                     tc_fence_after();                  // orders the drain's tcgen05.ld of this buffer before the MMAs that overwrite it
@@ -287,15 +309,15 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                 if (lane == 0) TC_TRACE(0, 3 * it + 0);
                 TC_WAIT(BAR(BAR_FULL + i), (it / TC_STAGES) & 1u, DEV_ERR_FULL_WAIT);
                 if (lane == 0) TC_TRACE(0, 3 * it + 1);
-                const uint64_t da = dA + (uint64_t)(i * (TC_STAGE >> 4)), db = dB + (uint64_t)(i * (TC_STAGE >> 4));
+                const uint64_t da = dA + (uint64_t)(i * (TC_STAGE >> 4)), db = dB + (uint64_t)(i * (Cfg::B_STAGE >> 4));
                 if (tc_elect_one()) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tc_mma(tacc, da + (uint64_t)(k * (2 * TC_CHUNK >> 4)), db + (uint64_t)(k * (2 * TC_CHUNK >> 4)), (s | (uint32_t)k) ? 1u : 0u);
+                        tc_mma(tacc, da + (uint64_t)(k * (2 * TC_CHUNK >> 4)), db + (uint64_t)(k * (2 * Cfg::B_CHUNK >> 4)), Cfg::IDESC, (s | (uint32_t)k) ? 1u : 0u);
                     tc_commit(BAR(BAR_EMPTY + i));
                     if (s == 3) {
                         if constexpr (WF == TC_W_Q4K) {
-                            tc_mma(tacc + 128u, dA2 + (uint64_t)(buf * (TC_AUX >> 4)), dB2 + (uint64_t)(buf * (TC_AUX >> 4)), 0u);
+                            tc_mma(tacc + Cfg::T2_OFF, dA2 + (uint64_t)(buf * (TC_AUX >> 4)), dB2 + (uint64_t)(buf * (Cfg::B_AUX >> 4)), Cfg::IDESC, 0u);
                             tc_commit(BAR(BAR_A2_EMPTY + buf));
                         }
                         tc_commit(BAR(BAR_B2_EMPTY + buf));
@@ -307,23 +329,24 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------ weight expanders: thread = row
-        TC_SETMAXNREG("dec", TC_REGS_EXP);
+        if constexpr (Cfg::REGS_EXP < Cfg::REGS_LAUNCH) TC_SETMAXNREG("dec", Cfg::REGS_EXP);
+        else TC_SETMAXNREG("inc", Cfg::REGS_EXP);
         const int set = (warp - 4) >> 2, row = tid & 127;
         if constexpr (WF == TC_W_Q6K_PLANAR) {
             // set e takes half n = e of every superblock: its 64 ql bytes and 32 qh bytes feed two k-stages
-            const size_t rb = ((size_t)nb * Q6K_BYTES + 15) & ~(size_t)15;
+            const size_t rb = ((size_t)nb_row * Q6K_BYTES + 15) & ~(size_t)15;
             const uint8_t *wrow = B + (size_t)min(n0 + row, N - 1) * rb;
-            const size_t off_qh = (size_t)nb * 128, off_sc = (size_t)nb * 192;
+            const size_t off_qh = (size_t)nb_row * 128, off_sc = (size_t)nb_row * 192;
             const __half2 c66 = __floats2half2_rn(66.0f, 66.0f);
             bool go = true;
             for (uint32_t b = 0; b < (uint32_t)nb && go; ++b) {
                 const uint32_t n = (uint32_t)set;
                 uint4 ql[4], qh[2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) ql[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)b * 128 + 64 * n + 16 * j));
+                for (int j = 0; j < 4; ++j) ql[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)(kb0 + b) * 128 + 64 * n + 16 * j));
 #pragma unroll
-                for (int j = 0; j < 2; ++j) qh[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + off_qh + (size_t)b * 64 + 32 * n + 16 * j));
-                const uint2 sc8 = __ldg(reinterpret_cast<const uint2 *>(wrow + off_sc + (size_t)b * 16 + 8 * n));
+                for (int j = 0; j < 2; ++j) qh[j] = __ldg(reinterpret_cast<const uint4 *>(wrow + off_qh + (size_t)(kb0 + b) * 64 + 32 * n + 16 * j));
+                const uint2 sc8 = __ldg(reinterpret_cast<const uint2 *>(wrow + off_sc + (size_t)(kb0 + b) * 16 + 8 * n));
                 const uint32_t qlw[16] = {ql[0].x, ql[0].y, ql[0].z, ql[0].w, ql[1].x, ql[1].y, ql[1].z, ql[1].w,
                                           ql[2].x, ql[2].y, ql[2].z, ql[2].w, ql[3].x, ql[3].y, ql[3].z, ql[3].w};
                 const uint32_t qhw[8] = {qh[0].x, qh[0].y, qh[0].z, qh[0].w, qh[1].x, qh[1].y, qh[1].z, qh[1].w};
@@ -360,7 +383,7 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             }
         } else {
             // set e takes the k-stages (quarters of a superblock) it = e, e + 2, ...
-            const uint8_t *wrow = B + (size_t)min(n0 + row, N - 1) * nb * Q4K_BYTES;
+            const uint8_t *wrow = B + ((size_t)min(n0 + row, N - 1) * nb_row + kb0) * Q4K_BYTES;
             uint4 cur_a, cur_b, hdr;
             {
                 const uint8_t *p0 = wrow + 16 + 32 * set;
@@ -412,16 +435,17 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
         }
     } else {
         // ------------------------------------------------------------ accumulator drain: thread = TMEM lane (weight row), 64 token columns
-        TC_SETMAXNREG("inc", TC_REGS_DRAIN);
+        TC_SETMAXNREG("inc", Cfg::REGS_DRAIN);
+        constexpr int COLS = Cfg::DRAIN_COLS;         // token columns of this thread
         const int dw = warp - 12;
         const int q = dw & 3, ch = dw >> 2;           // warp % 4 is the TMEM lane quarter this warp may read (12 % 4 == 0)
         const int row = 32 * q + lane, n = n0 + row;
         constexpr size_t DSTRIDE = WF == TC_W_Q4K ? Q4K_BYTES : 2;        // bytes between the block scales of consecutive superblocks
-        const uint8_t *wrow = WF == TC_W_Q4K ? B + (size_t)min(n, N - 1) * nb * Q4K_BYTES
-                                             : B + (size_t)min(n, N - 1) * (((size_t)nb * Q6K_BYTES + 15) & ~(size_t)15) + (size_t)nb * 208;
-        float acc[64];
+        const uint8_t *wrow = WF == TC_W_Q4K ? B + ((size_t)min(n, N - 1) * nb_row + kb0) * Q4K_BYTES
+                                             : B + (size_t)min(n, N - 1) * (((size_t)nb_row * Q6K_BYTES + 15) & ~(size_t)15) + (size_t)nb_row * 208 + (size_t)kb0 * 2;
+        float acc[COLS];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < COLS; ++i) acc[i] = 0.0f;
         auto load_dd = [&](int b) -> uint32_t {       // Q4_K: fp16 d | dmin of the superblock; Q6_K: fp16 d
             if constexpr (WF == TC_W_Q4K) return __ldg(reinterpret_cast<const uint32_t *>(wrow + (size_t)b * DSTRIDE));
             else return ldg_nc_u16(wrow + (size_t)b * DSTRIDE);
@@ -433,35 +457,36 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             if (b + 1 < nb) dd_next = load_dd(b + 1);
             const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&dd_bits));
             const uint32_t buf = (uint32_t)b & 1u;
-            const float4 *dxp = reinterpret_cast<const float4 *>(smem + TC_OFF_DX + buf * TC_ROWS * 4) + ch * 16;
+            const float4 *dxp = reinterpret_cast<const float4 *>(smem + TC_OFF_DX + buf * NT * 4) + ch * (COLS / 4);
             if (lane == 0 && dw == 0) TC_TRACE(2, 3 * b + 0);
             TC_WAIT(BAR(BAR_DX_FULL + buf), ((uint32_t)b >> 1) & 1u, DEV_ERR_FULL_WAIT);
             TC_WAIT(BAR(BAR_T_FULL + buf), ((uint32_t)b >> 1) & 1u, DEV_ERR_MMA_WAIT);
             if (lane == 0 && dw == 0) TC_TRACE(2, 3 * b + 1);
             tc_fence_after();
-            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + 256u * buf + 64u * (uint32_t)ch;
+            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + Cfg::T_BUF * buf + (uint32_t)(COLS * ch);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {             // two rounds of 32 columns
-                uint32_t t1[2][16], t2[2][16];
+            constexpr int RJ = NT == 128 ? 2 : 1;     // 16-column loads in flight per round (registers: 16 or 32 per accumulator)
+            for (int c = 0; c < COLS / (16 * RJ); ++c) {
+                uint32_t t1[RJ][16], t2[RJ][16];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    tc_ld16(taddr + (uint32_t)(32 * c + 16 * j), t1[j]);
-                    if constexpr (WF == TC_W_Q4K) tc_ld16(taddr + 128u + (uint32_t)(32 * c + 16 * j), t2[j]);
+                for (int j = 0; j < RJ; ++j) {
+                    tc_ld16(taddr + (uint32_t)(16 * (RJ * c + j)), t1[j]);
+                    if constexpr (WF == TC_W_Q4K) tc_ld16(taddr + Cfg::T2_OFF + (uint32_t)(16 * (RJ * c + j)), t2[j]);
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < RJ; ++j)
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4) {
-                        const float4 dx = dxp[(32 * c + 16 * j) / 4 + i4];
+                        const float4 dx = dxp[4 * (RJ * c + j) + i4];
                         const float dxf[4] = {dx.x, dx.y, dx.z, dx.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             if constexpr (WF == TC_W_Q4K)
-                                acc[32 * c + 16 * j + 4 * i4 + i] +=
+                                acc[16 * (RJ * c + j) + 4 * i4 + i] +=
                                     dxf[i] * (dd.x * __uint_as_float(t1[j][4 * i4 + i]) - dd.y * __uint_as_float(t2[j][4 * i4 + i]));
                             else
-                                acc[32 * c + 16 * j + 4 * i4 + i] += (dxf[i] * dd.x) * __uint_as_float(t1[j][4 * i4 + i]);
+                                acc[16 * (RJ * c + j) + 4 * i4 + i] += (dxf[i] * dd.x) * __uint_as_float(t1[j][4 * i4 + i]);
                         }
                     }
             }
@@ -474,11 +499,12 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             if (lane == 0 && dw == 0) TC_TRACE(2, 3 * b + 2);
         }
         if (b == nb && n < N) {
-            const float bv = bias ? bias[n] : 0.0f;
+            const float bv = bias && gridDim.z == 1 ? bias[n] : 0.0f;
+            float *Cz = C + (size_t)blockIdx.z * cz;
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const int m = m0 + 64 * ch + i;
-                if (m < M) C[(size_t)m * ldc + n] = acc[i] + bv;
+            for (int i = 0; i < COLS; ++i) {
+                const int m = m0 + COLS * ch + i;
+                if (m < M) Cz[(size_t)m * ldc + n] = acc[i] + bv;
             }
         }
     }
@@ -488,28 +514,77 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
     __syncwarp();
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS));
+}
+
+// sum of the split-K slices in slice order, plus bias: C[m * ldc + n] = sum_z part[z][m][n] + bias[n]
+__global__ void __launch_bounds__(256) gemm_splitk_sum_kernel(const float *__restrict__ part, int Z, const float *__restrict__ bias, float *__restrict__ C, int ldc,
+                                                              int M, int N)
+{
+    const size_t mn = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < mn; i += (size_t)gridDim.x * 256) {
+        const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
+        float s = __ldcg(part + i);
+        for (int z = 1; z < Z; ++z) s += __ldcg(part + (size_t)z * mn + i);
+        C[(size_t)m * ldc + n] = s + (bias ? bias[n] : 0.0f);
+    }
 }
 
 }  // namespace ckb
 
 using namespace ckb;
 
-template <int WF>
-static int launch_tc(const uint8_t *xt, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, int mtiles, cudaStream_t st)
+// How many K slices: enough CTAs to fill the resident slots (SMs x CTAs per SM) in whole waves.  Few tokens only (the
+// partial sums cost Z * M * N * 4 bytes of traffic), slices of at least 4 superblocks, at most 16.
+static int tc_pick_slices(int tiles, int nb, int slots)
 {
+    int best = 1;
+    double best_eff = 0.0;
+    for (int z = 1; z <= 16 && nb / z >= 4; ++z) {
+        const long ctas = (long)tiles * z, waves = (ctas + slots - 1) / slots;
+        const double eff = (double)ctas / (double)(waves * slots);
+        if (eff > best_eff * 1.08) { best_eff = eff; best = z; }      // a larger Z must pay for its partial sums
+    }
+    return best;
+}
+
+template <int WF, int NT>
+static int launch_tc(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
+{
+    using Cfg = TcCfg<NT>;
+    auto kernel = gemm_kq_tc_kernel<WF, NT>;
     static int attr_set = 0;
     if (!attr_set) {
         cudaFuncAttributes fa;
-        if (ckb_check_cuda((int)cudaFuncGetAttributes(&fa, gemm_kq_tc_kernel<WF>), "func attributes")) return CKB_ERR_CUDA;
-        if (fa.numRegs != TC_REGS_LAUNCH)     // a different allocation at launch would make setmaxnreg.inc wait for registers that never come
+        if (ckb_check_cuda((int)cudaFuncGetAttributes(&fa, kernel), "func attributes")) return CKB_ERR_CUDA;
+        if (fa.numRegs != Cfg::REGS_LAUNCH)     // a different allocation at launch would make setmaxnreg.inc wait for registers that never come
             return ckb_fail(CKB_ERR_LIMIT, "gemm_kq_tc: kernel compiled with an unexpected register count");
-        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_kq_tc_kernel<WF>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM), "smem attr")) return CKB_ERR_CUDA;
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM), "smem attr")) return CKB_ERR_CUDA;
         attr_set = 1;
     }
-    const dim3 grid((N + TC_ROWS - 1) / TC_ROWS, mtiles);
-    gemm_kq_tc_kernel<WF><<<grid, TC_THREADS, TC_SMEM, st>>>(xt, (const uint8_t *)B, bias, C, ldc, M, N, nb, ckb_device_error_word());
-    return ckb_check_launch("gemm_kq_tc");
+    const int mtiles = (M + NT - 1) / NT, ntiles = (N + TC_ROWS - 1) / TC_ROWS;
+    int Z = M <= 128 && ckb_tune_get("gemm_tc_splitk", 1) ? tc_pick_slices(ntiles * mtiles, nb, ckb_sm_count() * Cfg::CTAS_PER_SM) : 1;
+    const int forced = ckb_tune_get("gemm_tc_slices", 0);
+    if (forced > 0 && forced <= nb) Z = forced;
+    const int nbz = (nb + Z - 1) / Z;
+    Z = (nb + nbz - 1) / nbz;                          // no empty slice
+    const size_t xt_bytes = ((size_t)mtiles * nb * Cfg::XBLOB + 255) & ~(size_t)255, part_bytes = Z > 1 ? (size_t)Z * M * N * sizeof(float) : 0;
+    uint8_t *xt = (uint8_t *)ckb_scratch(CKB_SLOT_G, xt_bytes + part_bytes);
+    if (!xt) return CKB_ERR_CUDA;
+    float *part = reinterpret_cast<float *>(xt + xt_bytes);
+    gemm_x_tiles_kernel<NT><<<dim3(nb, mtiles), 256, 0, st>>>((const uint8_t *)A_q8, xt, M, nb);
+    if (int rc = ckb_check_launch("gemm_x_tiles")) return rc;
+    const dim3 grid(ntiles, mtiles, Z);
+    if (Z == 1) {
+        kernel<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B, bias, C, ldc, (size_t)0, M, N, nb, nbz, ckb_device_error_word());
+        return ckb_check_launch("gemm_kq_tc");
+    }
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B, nullptr, part, N, (size_t)M * N, M, N, nb, nbz, ckb_device_error_word());
+    if (int rc = ckb_check_launch("gemm_kq_tc")) return rc;
+    const size_t mn = (size_t)M * N;
+    const unsigned blocks = (unsigned)((mn + 1023) / 1024 < 1184 ? (mn + 1023) / 1024 : 1184);
+    gemm_splitk_sum_kernel<<<blocks, 256, 0, st>>>(part, Z, bias, C, ldc, M, N);
+    return ckb_check_launch("gemm_splitk_sum");
 }
 
 #ifdef CKB_TC_TRACE
@@ -523,14 +598,11 @@ extern "C" int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const
                                   void *stream)
 {
     if (M < min_tokens || K % QK_K || ((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3) || ckb_tune_get("gemm_tc", 1) == 0) return -1;
-    const int nb = K / QK_K, mtiles = (M + TC_ROWS - 1) / TC_ROWS;
-    uint8_t *xt = (uint8_t *)ckb_scratch(CKB_SLOT_G, (size_t)mtiles * nb * TC_XBLOB);
-    if (!xt) return CKB_ERR_CUDA;
+    const int nb = K / QK_K;
     cudaStream_t st = ckb_stream(stream);
-    gemm_x_tiles_kernel<<<dim3(nb, mtiles), 256, 0, st>>>((const uint8_t *)A_q8, xt, M, nb);
-    if (int rc = ckb_check_launch("gemm_x_tiles")) return rc;
-    return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR>(xt, B, bias, C, ldc, M, N, nb, mtiles, st)
-                                 : launch_tc<TC_W_Q4K>(xt, B, bias, C, ldc, M, N, nb, mtiles, st);
+    if (M <= ckb_tune_get("gemm_tc_small_max", 64))     // batched decode: 32-token tiles, two CTAs per SM
+        return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 32>(A_q8, B, bias, C, ldc, M, N, nb, st) : launch_tc<TC_W_Q4K, 32>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 128>(A_q8, B, bias, C, ldc, M, N, nb, st) : launch_tc<TC_W_Q4K, 128>(A_q8, B, bias, C, ldc, M, N, nb, st);
 }
 
 extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)

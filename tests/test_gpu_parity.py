@@ -206,9 +206,11 @@ def test_gemm_nt_matches_loop_of_gemv(ck, orc, fmt, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k,with_bias", [(64, 128, 256, False), (128, 256, 1024, True), (200, 200, 512, True), (512, 384, 4096, False),
-                                               (65, 129, 768, True), (300, 1000, 2048, False)])
+                                               (65, 129, 768, True), (300, 1000, 2048, False),
+                                               (16, 128, 256, False), (32, 300, 4096, True), (40, 256, 2048, True), (33, 520, 8192, True)])
 def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
-    """M >= 64 takes the tcgen05 kernel: full tiles, ragged token and row edges, one and many superblocks."""
+    """M >= 16 takes the tcgen05 kernel (32-token tiles up to 64 tokens, 128-token tiles above): full tiles, ragged token
+    and row edges, one and many superblocks, K split over several CTAs where the grid would not fill the SMs."""
     w = synth.make_weights("q4_k", n, k, seed=m + n)
     a = synth.make_x(k, seed=m, rows=m)
     aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
@@ -224,9 +226,50 @@ def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
     assert_fp32_close(by_rows, want, "q4_k per-token path")
 
 
-def test_gemm_nt_q4_k_tensor_core_extreme_values(ck, orc):
-    """Largest scales, nibbles and activations: the integer sums reach the top of the fp32-exact range."""
-    m, n, k = 64, 128, 512
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("m,small_max,slices", [(24, 64, 3), (24, 0, 3), (70, 64, 4), (64, 64, 1), (64, 64, 10)])
+def test_gemm_tensor_core_split_k(ck, orc, fmt, m, small_max, slices):
+    """Both tile widths with a forced number of K slices (uneven last slice: 10 superblocks in 3 or 4 slices; one
+    superblock per slice), against the oracle; the slices are summed in a fixed order, so two runs agree bit for bit."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    n, k = 260, 2560
+    w = synth.make_weights(fmt, n, k, seed=m)
+    a = synth.make_x(k, seed=m + 1, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", fmt, a, rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32)
+    want = cases.gemm_nt(orc, "oracle_", fmt, aq, w, bias, m, n, k)
+    raw, taq, tb = torch.from_numpy(w).to(dev), torch.from_numpy(aq).to(dev), torch.from_numpy(bias).to(dev)
+    if fmt == "q6_k":
+        ck.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+        wdev = torch.empty(ck.ckb200_q6_k_planar_bytes(n, k), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+        assert ck.ckb200_dev_q6_k_to_planar(C.c_void_p(wdev.data_ptr()), C.c_void_p(raw.data_ptr()), n, k, None) == 0
+        fn = ck.ckb200_dev_gemm_nt_q6_k_planar_q8_k
+    else:
+        wdev, fn = raw, ck.ckb200_dev_gemm_nt_q4_k_q8_k
+    outs = []
+    try:
+        ck.ckb200_tune_set(b"gemm_tc_small_max", small_max)
+        ck.ckb200_tune_set(b"gemm_tc_slices", slices)
+        for _ in range(2):
+            c = torch.full((m, n), float("nan"), device=dev)
+            torch.cuda.synchronize()
+            assert fn(C.c_void_p(taq.data_ptr()), C.c_void_p(wdev.data_ptr()), C.c_void_p(tb.data_ptr()), C.c_void_p(c.data_ptr()), m, n, k, None) == 0
+            assert ck.ckb200_synchronize() == 0
+            outs.append(c.cpu().numpy())
+    finally:
+        ck.ckb200_tune_set(b"gemm_tc_small_max", 64)
+        ck.ckb200_tune_set(b"gemm_tc_slices", 0)
+    assert_fp32_close(outs[0], want, f"{fmt} split-K gemm")
+    assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("m", [64, 128])
+def test_gemm_nt_q4_k_tensor_core_extreme_values(ck, orc, m):
+    """Largest scales, nibbles and activations: the integer sums reach the top of the fp32-exact range (both tile widths)."""
+    n, k = 128, 512
     w = synth.make_weights("q4_k", n, k, seed=9).reshape(n, k // 256, 144).copy()
     w[:, :, 4:16] = 0xFF          # every 6-bit scale and min = 63
     w[:, :, 16:] = 0xFF           # every nibble = 15
@@ -366,7 +409,8 @@ def test_gemv_q6_k_planar_layout(ck, orc, m, k):
         ck.ckb200_tune_set(b"gemv_q6p_rows", 0)
 
 
-@pytest.mark.parametrize("m,n,k,big_scales", [(16, 128, 256, False), (32, 256, 1024, False), (64, 200, 512, True), (130, 384, 2048, False), (512, 256, 4096, True)])
+@pytest.mark.parametrize("m,n,k,big_scales", [(16, 128, 256, False), (32, 256, 1024, False), (64, 200, 512, True), (130, 384, 2048, False), (512, 256, 4096, True),
+                                                 (48, 300, 8192, False)])
 def test_gemm_nt_q6_k_planar_tensor_core(ck, orc, m, n, k, big_scales):
     """Q6_K prefill / batched-decode GEMM on tcgen05 over planar weights; with |scale| up to 127 some products
     leave the exactly representable fp16 range and are rounded (<= 2^-12 relative on that element)."""

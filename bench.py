@@ -471,13 +471,16 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         try:
             pkg.tp.setup(lib, rank, world, dev, p2p_floats=32 * LLAMA3_70B["embed_dim"])
             decode_tp = []
-            for p2p, how in ((1, "one-shot push all-reduce over peer memory"), (0, "NCCL all-reduce")):
+            for p2p, fused, how in ((1, 1, "peer-memory exchange fused into the residual-add + RMSNorm + quantise kernel"),
+                                    (1, 0, "one-shot push all-reduce kernel over peer memory"), (0, 0, "NCCL all-reduce")):
                 lib.ckb200_tune_set(b"tp_p2p", p2p)
+                lib.ckb200_tune_set(b"tp_fused_norm", fused)
                 d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}", LLAMA3_70B, 4096, 20, measured_peak()[0],
                                  batch=1, tp_rank=rank, tp_size=world, dist=dist)
                 d["exchange"] = how
                 decode_tp.append(d)
             lib.ckb200_tune_set(b"tp_p2p", 1)
+            lib.ckb200_tune_set(b"tp_fused_norm", 1)
         except Exception as exc:
             decode_tp = {"error": repr(exc)}
             lib.ckb200_clear_error()
@@ -670,17 +673,17 @@ def run_decode_only(args):
     so.bind_model_api(lib)
     cfg, ctx = (QWEN2_05B, 1024) if args.decode_only == "qwen2-0.5b" else (LLAMA3_70B, 4096)
     lib.ckb200_tune_set(b"model_graph", 0)
-    st = so.make_cfg(cfg, batch=1)
+    st = so.make_cfg(cfg, batch=args.batch)
     h = lib.ckb200_model_create(C.byref(st))
     assert h, lib.ckb200_last_error_message()
     assert lib.ckb200_model_fill_synthetic(h, 1) == 0 and lib.ckb200_model_fill_kv_synthetic(h, ctx, 2) == 0
-    ids = np.array([11], np.int32)
+    ids = np.full(args.batch, 11, np.int32)
     lib.ckb200_launch_count.restype = C.c_longlong
     n0 = lib.ckb200_launch_count()
     for _ in range(args.steps):
         assert lib.ckb200_model_decode(h, cases.vptr(ids), None) == 0
     assert lib.ckb200_synchronize() == 0
-    print(json.dumps({"decode_only": args.decode_only, "steps": args.steps, "launches_per_step": (lib.ckb200_launch_count() - n0) // args.steps}))
+    print(json.dumps({"decode_only": args.decode_only, "batch": args.batch, "steps": args.steps, "launches_per_step": (lib.ckb200_launch_count() - n0) // args.steps}))
     lib.ckb200_model_free(h)
 
 
@@ -698,6 +701,7 @@ def main():
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
     ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per step of --decode-only")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
     args = ap.parse_args()
     if args.single:

@@ -80,6 +80,8 @@ struct CKB200Model {
     int have_prev;
     ckb200_allreduce_fn allreduce;
     void *allreduce_ctx;
+    ckb200_tp_norm_fn tp_norm;
+    void *tp_norm_ctx;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -362,6 +364,14 @@ int ckb200_model_get_pos(CKB200Model *m)
     return p;
 }
 
+void ckb200_model_set_tp_norm(CKB200Model *m, ckb200_tp_norm_fn fn, void *ctx)
+{
+    if (!m) return;
+    m->tp_norm = fn;
+    m->tp_norm_ctx = ctx;
+    m->graph_ready = 0;
+}
+
 void ckb200_model_set_allreduce(CKB200Model *m, ckb200_allreduce_fn fn, void *ctx)
 {
     if (!m) return;
@@ -452,6 +462,21 @@ static int reduce_partial(CKB200Model *m, float *buf, size_t count, void *st)
     return m->allreduce(m->allreduce_ctx, buf, count, st);
 }
 
+/* norm_quant of a delta that is still a per-rank partial sum (row-parallel o_proj / down_proj): the fused exchange when
+ * the hook takes it, else all-reduce in place and the plain kernel */
+static int reduce_norm_quant(CKB200Model *m, float *delta, const Tensor *gamma, const Tensor *consumer, void *st)
+{
+    if (delta && m->c.tp_size > 1) {
+        if (m->tp_norm && consumer->fmt != FMT_Q80) {
+            const int rc = m->tp_norm(m->tp_norm_ctx, m->x, delta, (const float *)gamma->w, m->hq, m->c.batch, m->D, m->Da, m->c.rms_eps, st);
+            if (rc != -1) return rc;
+        }
+        const int rc = reduce_partial(m, delta, (size_t)m->c.batch * m->Da, st);
+        if (rc) return rc;
+    }
+    return norm_quant(m, delta, gamma, consumer, st);
+}
+
 /* (Re)builds the row-planar copies of the Q6_K projection matrices from the uploaded rows; outside any capture. */
 static int ensure_planar(CKB200Model *m, void *st)
 {
@@ -481,11 +506,11 @@ static int issue_step(CKB200Model *m, void *st)
         default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
     }
     if (rc) return rc;
-    const float *delta = NULL;
+    float *delta = NULL;
     for (int l = 0; l < L; ++l) {
         Tensor *t = m->layers[l].t;
         float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + (size_t)B * m->kv_batch_stride;
-        if ((rc = norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
+        if ((rc = reduce_norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
         if (t[CKB_T_WK].fmt != t[CKB_T_WQ].fmt && (t[CKB_T_WK].fmt == FMT_Q80 || t[CKB_T_WQ].fmt == FMT_Q80))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
         if (ckb_tune_get("model_qkv_streams", 1) && B < MODEL_GEMM_MIN_BATCH) {     /* the batched GEMMs share one workspace: keep them in order */
@@ -513,8 +538,7 @@ static int issue_step(CKB200Model *m, void *st)
                                                  m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
         if ((rc = quant_rows(&t[CKB_T_WO], m->att, m->Ala, m->aq, B, st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
-        if ((rc = reduce_partial(m, m->o, (size_t)B * m->Da, st))) return rc;
-        if ((rc = norm_quant(m, m->o, &t[CKB_T_LN2], &t[CKB_T_W1], st))) return rc;
+        if ((rc = reduce_norm_quant(m, m->o, &t[CKB_T_LN2], &t[CKB_T_W1], st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_W1], m->hq, m->gu, 2 * m->Il, st))) return rc;
         if (t[CKB_T_W2].fmt != FMT_Q80 && m->Il % 256 == 0) {
             if ((rc = ckb200_dev_swiglu_q8k(m->gu, m->mq, B, m->Il, st))) return rc;
@@ -523,10 +547,9 @@ static int issue_step(CKB200Model *m, void *st)
             return ckb_fail(CKB_ERR_STATE, "model step: FFN width %d with this down-projection format is not supported", m->Il);
         }
         if ((rc = matvec(m, &t[CKB_T_W2], m->mq, m->prev, m->Da, st))) return rc;
-        if ((rc = reduce_partial(m, m->prev, (size_t)B * m->Da, st))) return rc;
-        delta = m->prev;
+        delta = m->prev;                         /* a per-rank partial sum when tp_size > 1: reduced where it is consumed */
     }
-    if ((rc = norm_quant(m, delta, &m->final_gamma, &m->lm_head, st))) return rc;
+    if ((rc = reduce_norm_quant(m, delta, &m->final_gamma, &m->lm_head, st))) return rc;
     if ((rc = matvec(m, &m->lm_head, m->hq, m->logits, m->Vl, st))) return rc;
     return ckb200_dev_advance_pos(m->pos_dev, st);
 }

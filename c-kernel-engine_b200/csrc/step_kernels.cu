@@ -11,6 +11,7 @@
 // producer is still running, so everything a previous kernel wrote is read with __ldcg (through L2);
 // the read-only / L1 paths are not coherent across a programmatic launch.  Weights (gamma, cos/sin)
 // are never written by a kernel and may use any path.
+#include "add_rmsnorm_q8k.cuh"
 #include "pdl.cuh"
 #include "q8k_block.cuh"
 
@@ -20,7 +21,6 @@ namespace ckb {
 // x[t] += delta[t] (when delta != NULL; x is updated in place), then h = rmsnorm(x[t]) * gamma, zero beyond
 // d_model, quantised to Q8_K blocks of `aligned` elements.  Optionally also writes the fp32 normalised row.
 // Every thread issues all of its 16-byte loads before it uses any of them (one L2 round trip per row).
-constexpr int ARQ_MAX_V4 = 4;      // float4 pieces per thread: rows up to 1024 * 4 * 4 = 16384 elements
 __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict__ x, const float *__restrict__ delta,
                                                                const float *__restrict__ gamma, uint8_t *__restrict__ out_q8,
                                                                float *__restrict__ norm_out, int d_model, int aligned, float eps)
@@ -50,38 +50,14 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict
         const int i = threadIdx.x + k * blockDim.x;
         if (i < nv) {
             float4 v = xv[k];
-            const int e = 4 * i;
             if (dr) {
                 v.x += dv[k].x; v.y += dv[k].y; v.z += dv[k].z; v.w += dv[k].w;
                 reinterpret_cast<float4 *>(xr)[i] = v;                 // pad columns of x and delta are zero by construction
             }
-            if (e + 0 >= d_model) v.x = 0.f;
-            if (e + 1 >= d_model) v.y = 0.f;
-            if (e + 2 >= d_model) v.z = 0.f;
-            if (e + 3 >= d_model) v.w = 0.f;
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            reinterpret_cast<float4 *>(row)[i] = v;
+            arq_keep_piece(v, i, d_model, row, ss);
         }
     }
-    ss = group_sum<32>(ss);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-    for (int w = 0; w < nw; ++w) tot += red[w];
-    const float mean = __fmul_rn(tot, __fdiv_rn(1.0f, (float)d_model));
-    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    const int nb = aligned / QK_K;
-    for (int b = warp; b < nb; b += nw) {
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int i = b * QK_K + 8 * lane + j;
-            v[j] = i < d_model ? __fmul_rn(__fmul_rn(row[i], rstd), gamma[i]) : 0.0f;
-            if (norm_out) norm_out[(size_t)t * aligned + i] = v[j];
-        }
-        quantize_block_q8k(v, out_q8 + ((size_t)t * nb + b) * Q8K_BYTES, lane);
-    }
+    arq_norm_quant(ss, row, red, gamma, out_q8, norm_out, t, d_model, aligned, eps);
 }
 
 // one warp per 256-element block of the output: out = silu(gate) * up, quantised to Q8_K

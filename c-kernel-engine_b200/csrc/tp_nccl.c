@@ -112,5 +112,9 @@ void ckb200_tp_shutdown(void)
     }
 }
 
-/* convenience: bind the NCCL all-reduce to a tensor-parallel model */
-void ckb200_model_use_tp(CKB200Model *m) { ckb200_model_set_allreduce(m, ckb200_tp_allreduce, NULL); }
+/* convenience: bind the all-reduce and the fused exchange + norm to a tensor-parallel model */
+void ckb200_model_use_tp(CKB200Model *m)
+{
+    ckb200_model_set_allreduce(m, ckb200_tp_allreduce, NULL);
+    ckb200_model_set_tp_norm(m, ckb200_tp_add_rmsnorm_q8k, NULL);
+}

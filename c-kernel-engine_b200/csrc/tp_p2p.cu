@@ -15,7 +15,9 @@
 // and is advanced by the last CTA of a call, so a captured CUDA graph can be replayed.
 //
 // The poll is bounded (about ten seconds of SM clock: ranks reach their first step at different times); a timeout sets
-// the device error word and leaves the vector unreduced.  No multicast, no peer loads: remote stores only.
+// the device error word and leaves the vector unreduced, and while that word is set no later call polls at all, so a
+// lost peer costs one timeout, not one per call.  No multicast, no peer loads: remote stores only.
+#include "add_rmsnorm_q8k.cuh"
 #include "device_common.cuh"
 #include "launch.h"
 #include "pdl.cuh"
@@ -61,7 +63,7 @@ __global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *_
             if (r != me) st_line(v.lines[r] + my_slot + i, line);
     }
     const long long t0 = clock64();
-    bool ok = true;
+    bool ok = *reinterpret_cast<volatile int *>(dev_err) == 0;      // after a failure nothing waits again until the host has cleared the error
     for (size_t i = first; i < nl && ok; i += stride) {
         float s0 = 0.0f, s1 = 0.0f;
         for (int src = 0; src < W; ++src) {
@@ -93,6 +95,85 @@ __global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *_
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(v.epoch + 1, 1u) == gridDim.x - 1) {      // last CTA of this call: every CTA has read the call number
+            v.epoch[1] = 0;
+            *reinterpret_cast<volatile unsigned *>(v.epoch) = e;
+        }
+    }
+}
+
+// The exchange fused into its consumer: x[t] += sum over ranks of delta[t], then RMSNorm and Q8_K quantisation of the row
+// (add_rmsnorm_q8k, step_kernels.cu), one CTA per token row.  Every thread stores its pieces of the local delta into the
+// peers' slots, polls its own slots for the other ranks' pieces, and adds them up in rank order, the same order and
+// arithmetic as tp_allreduce_push_kernel followed by add_rmsnorm_q8k, so both forms give the same bits.  Line index of
+// piece i of row t: t * aligned / 2 + 2 i (+1): the whole [tokens][aligned] vector is one call of the exchange.
+__global__ void __launch_bounds__(1024) tp_add_rmsnorm_q8k_kernel(float *__restrict__ x, const float *__restrict__ delta, const float *__restrict__ gamma,
+                                                                  uint8_t *__restrict__ out_q8, int d_model, int aligned, float eps, P2PView v,
+                                                                  int *__restrict__ dev_err)
+{
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, W = v.world, me = v.rank;
+    const unsigned e = *reinterpret_cast<volatile unsigned *>(v.epoch) + 1u, par = e & 1u;
+    float *xr = x + (size_t)t * aligned;
+    const float *dr = delta + (size_t)t * aligned;
+    const int nv = aligned >> 2;
+    const size_t line0 = (size_t)t * (aligned >> 1);
+    float4 xv[ARQ_MAX_V4], dv[ARQ_MAX_V4];
+#pragma unroll
+    for (int k = 0; k < ARQ_MAX_V4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        dv[k] = xv[k];
+        if (i < nv) {
+            xv[k] = __ldcg(reinterpret_cast<const float4 *>(xr) + i);
+            dv[k] = __ldcg(reinterpret_cast<const float4 *>(dr) + i);
+            const uint4 l0 = make_uint4(__float_as_uint(dv[k].x), e, __float_as_uint(dv[k].y), e);
+            const uint4 l1 = make_uint4(__float_as_uint(dv[k].z), e, __float_as_uint(dv[k].w), e);
+            for (int r = 0; r < W; ++r)
+                if (r != me) {
+                    uint4 *dst = v.lines[r] + ((size_t)par * W + me) * v.max_lines + line0 + 2 * i;
+                    st_line(dst, l0);
+                    st_line(dst + 1, l1);
+                }
+        }
+    }
+    const long long t0 = clock64();
+    bool ok = *reinterpret_cast<volatile int *>(dev_err) == 0;      // after a failure nothing waits again until the host has cleared the error
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ARQ_MAX_V4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nv) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int src = 0; src < W; ++src) {
+                float4 a = dv[k];
+                if (src != me) {
+                    const uint4 *p = v.lines[me] + ((size_t)par * W + src) * v.max_lines + line0 + 2 * i;
+                    uint4 l0 = ld_line(p), l1 = ld_line(p + 1);
+                    while (ok && (l0.y != e || l0.w != e || l1.y != e || l1.w != e)) {
+                        if (clock64() - t0 > (1ll << 34)) ok = false;
+                        l0 = ld_line(p);
+                        l1 = ld_line(p + 1);
+                    }
+                    a = make_float4(__uint_as_float(l0.x), __uint_as_float(l0.z), __uint_as_float(l1.x), __uint_as_float(l1.z));
+                }
+                if (src == 0) s = a;
+                else { s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+            }
+            float4 u = xv[k];
+            u.x += s.x; u.y += s.y; u.z += s.z; u.w += s.w;
+            reinterpret_cast<float4 *>(xr)[i] = u;                 // pad columns of x and delta are zero by construction
+            arq_keep_piece(u, i, d_model, row, ss);
+        }
+    }
+    if (!ok) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
+    arq_norm_quant(ss, row, red, gamma, out_q8, nullptr, t, d_model, aligned, eps);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(v.epoch + 1, 1u) == gridDim.x - 1) {
             v.epoch[1] = 0;
             *reinterpret_cast<volatile unsigned *>(v.epoch) = e;
         }
@@ -171,6 +252,31 @@ extern "C" int ckb_tp_p2p_allreduce(float *buf, size_t count, void *stream)
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     return launch_pdl("tp_allreduce_push", tp_allreduce_push_kernel, dim3((unsigned)ctas), dim3(P2P_THREADS), 0, ckb_stream(stream), buf, count, g_p2p.view,
                       ckb_device_error_word());
+}
+
+// ckb200_tp_norm_fn: x[t] += sum over ranks of delta[t]; out_q8[t] = Q8_K(rmsnorm(x[t]) * gamma).  Returns -1 when the
+// exchange buffer cannot take the vector (not connected, too large, switched off): the caller then reduces and normalises
+// in two steps.
+extern "C" int ckb200_tp_add_rmsnorm_q8k(void *ctx, float *x, const float *delta, const float *gamma, void *out_q8, int tokens, int d_model,
+                                         int aligned_embed_dim, float eps, void *stream)
+{
+    (void)ctx;
+    if (!g_p2p.ready || !ckb_tune_get("tp_p2p", 1) || !ckb_tune_get("tp_fused_norm", 1)) return -1;
+    if (!x || !delta || !gamma || !out_q8 || tokens <= 0 || d_model <= 0) return -1;
+    if (aligned_embed_dim % QK_K || aligned_embed_dim < d_model || aligned_embed_dim > 1024 * 4 * ARQ_MAX_V4) return -1;
+    if ((size_t)tokens * aligned_embed_dim > 2 * g_p2p.view.max_lines || (((uintptr_t)x | (uintptr_t)delta) & 15)) return -1;
+    int threads = (aligned_embed_dim / 4 + 31) & ~31;
+    if (threads > 1024) threads = 1024;
+    const size_t smem = (size_t)aligned_embed_dim * sizeof(float);
+    if (smem > 48 * 1024) {
+        static size_t set = 0;
+        if (smem > set) {
+            if (ckb_check_cuda((int)cudaFuncSetAttribute(tp_add_rmsnorm_q8k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr")) return CKB_ERR_CUDA;
+            set = smem;
+        }
+    }
+    return launch_pdl("tp_add_rmsnorm_q8k", tp_add_rmsnorm_q8k_kernel, dim3(tokens), dim3(threads), smem, ckb_stream(stream), x, delta, gamma, (uint8_t *)out_q8,
+                      d_model, aligned_embed_dim, eps, g_p2p.view, ckb_device_error_word());
 }
 
 extern "C" void ckb200_tp_p2p_shutdown(void)

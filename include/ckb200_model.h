@@ -44,6 +44,10 @@ typedef struct CKB200Model CKB200Model;
 
 /* sum `count` floats in place over all tensor-parallel ranks, enqueued on `stream`; returns 0 on success */
 typedef int (*ckb200_allreduce_fn)(void *ctx, float *buf, size_t count, void *stream);
+/* Optional fused form of "all-reduce the residual delta, add it, RMSNorm, quantise to Q8_K" (one kernel per token row that
+ * exchanges over peer memory).  Returns -1 when it does not handle the call; the step then uses the all-reduce hook. */
+typedef int (*ckb200_tp_norm_fn)(void *ctx, float *x, const float *delta, const float *gamma, void *out_q8, int tokens, int d_model,
+                                 int aligned_embed_dim, float eps, void *stream);
 
 /* "synthetic:<qwen2-0.5b|llama3-8b|llama3-70b|mini>[:seed]" or the path of a CKB2MDL1 model file; batch <= 0 keeps the default */
 CKB200Model *ckb200_model_open(const char *spec, int batch);
@@ -60,6 +64,7 @@ int ckb200_model_fill_kv_synthetic(CKB200Model *m, int tokens, unsigned long lon
 int ckb200_model_set_pos(CKB200Model *m, int pos);
 int ckb200_model_get_pos(CKB200Model *m);
 void ckb200_model_set_allreduce(CKB200Model *m, ckb200_allreduce_fn fn, void *ctx);
+void ckb200_model_set_tp_norm(CKB200Model *m, ckb200_tp_norm_fn fn, void *ctx);
 /* one decode step: tokens[batch] in, logits[batch][vocab] out (logits_host may be NULL: no copy, no sync) */
 int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_host);
 int ckb200_model_decode_repeat(CKB200Model *m, int steps);              /* re-launch the captured step `steps` times */
@@ -85,7 +90,9 @@ int ckb200_tp_p2p_connect(const void *all_handles);
 int ckb200_tp_p2p_ready(void);
 size_t ckb200_tp_p2p_max_floats(void);
 void ckb200_tp_p2p_shutdown(void);
-void ckb200_model_use_tp(CKB200Model *m);                                     /* set_allreduce(m, ckb200_tp_allreduce, NULL) */
+int ckb200_tp_add_rmsnorm_q8k(void *ctx, float *x, const float *delta, const float *gamma, void *out_q8, int tokens, int d_model,
+                              int aligned_embed_dim, float eps, void *stream);                  /* a ckb200_tp_norm_fn */
+void ckb200_model_use_tp(CKB200Model *m);       /* set_allreduce(m, ckb200_tp_allreduce, NULL) and set_tp_norm(m, ckb200_tp_add_rmsnorm_q8k, NULL) */
 
 #ifdef __cplusplus
 }

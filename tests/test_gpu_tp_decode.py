@@ -63,22 +63,37 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     cpu = so.CpuModel(TP_CFG, seed=5)
     cpu.prefill_kv(20, seed=6)
     shard = so.TpShard(cpu, rank, world)
-    st = so.make_cfg(TP_CFG, batch=1, tp_rank=rank, tp_size=world)
-    handle = lib.ckb200_model_create(C.byref(st))
-    assert handle, lib.ckb200_last_error_message()
     lib.ckb200_model_use_tp.argtypes = [C.c_void_p]
-    lib.ckb200_model_use_tp(handle)
-    so.upload_shard(lib, handle, shard)
-    assert lib.ckb200_model_set_pos(handle, 20) == 0
-    outs = []
-    for tok in (7, 123):
-        ids = np.array([tok], dtype=np.int32)
-        logits = np.zeros((1, TP_CFG["vocab_size"]), np.float32)
-        assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, lib.ckb200_last_error_message()
-        outs.append(logits[0].copy())
-    np.save(os.path.join(out_dir, f"rank{rank}.npy"), np.stack(outs))
+
+    def run(fused: int):
+        """Two decode steps of a fresh model; fused: the exchange inside the norm kernel (1) or the all-reduce kernel (0)."""
+        lib.ckb200_tune_set(b"tp_fused_norm", fused)
+        st = so.make_cfg(TP_CFG, batch=1, tp_rank=rank, tp_size=world)
+        handle = lib.ckb200_model_create(C.byref(st))
+        assert handle, lib.ckb200_last_error_message()
+        lib.ckb200_model_use_tp(handle)
+        so.upload_shard(lib, handle, shard)
+        assert lib.ckb200_model_set_pos(handle, 20) == 0
+        outs = []
+        for tok in (7, 123):
+            ids = np.array([tok], dtype=np.int32)
+            logits = np.zeros((1, TP_CFG["vocab_size"]), np.float32)
+            assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, lib.ckb200_last_error_message()
+            outs.append(logits[0].copy())
+        dist.barrier()
+        lib.ckb200_model_free(handle)
+        return np.stack(outs)
+
+    launches0 = lib.ckb200_launch_count()
+    fused = run(1)
+    launches_fused = lib.ckb200_launch_count() - launches0
+    unfused = run(0)
+    launches_unfused = lib.ckb200_launch_count() - launches0 - launches_fused
+    lib.ckb200_tune_set(b"tp_fused_norm", 1)
+    assert launches_fused < launches_unfused, (launches_fused, launches_unfused)     # the fused form really ran
+    assert np.array_equal(fused, unfused)            # same sums in the same order: the two forms agree bit for bit
+    np.save(os.path.join(out_dir, f"rank{rank}.npy"), fused)
     dist.barrier()
-    lib.ckb200_model_free(handle)
     lib.ckb200_tp_shutdown()
     dist.destroy_process_group()
 

@@ -481,6 +481,10 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                 decode_tp.append(d)
             lib.ckb200_tune_set(b"tp_p2p", 1)
             lib.ckb200_tune_set(b"tp_fused_norm", 1)
+            d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}, batch 32", LLAMA3_70B, 4096, 4, measured_peak()[0],
+                             batch=32, tp_rank=rank, tp_size=world, dist=dist)
+            d["exchange"] = "peer-memory exchange fused into the residual-add + RMSNorm + quantise kernel"
+            decode_tp.append(d)
         except Exception as exc:
             decode_tp = {"error": repr(exc)}
             lib.ckb200_clear_error()

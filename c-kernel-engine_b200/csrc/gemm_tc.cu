@@ -464,8 +464,8 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             if (lane == 0 && dw == 0) TC_TRACE(2, 3 * b + 1);
             tc_fence_after();
             const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + Cfg::T_BUF * buf + (uint32_t)(COLS * ch);
-#pragma unroll
             constexpr int RJ = NT == 128 ? 2 : 1;     // 16-column loads in flight per round (registers: 16 or 32 per accumulator)
+#pragma unroll
             for (int c = 0; c < COLS / (16 * RJ); ++c) {
                 uint32_t t1[RJ][16], t2[RJ][16];
 #pragma unroll

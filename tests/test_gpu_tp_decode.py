@@ -1,6 +1,6 @@
-"""Tensor-parallel decode on 2 GPUs: one process per GPU, the all-reduce after o_proj and down_proj (peer-memory
+"""Tensor-parallel decode on 2 and 4 GPUs: one process per GPU, the all-reduce after o_proj and down_proj (peer-memory
 push kernel checked against NCCL, then used by the step),
-logits of every rank against the unsharded CPU step.  Skipped on a box with a single GPU."""
+logits of every rank against the unsharded CPU step.  Skipped on a box with fewer GPUs."""
 from __future__ import annotations
 
 import os
@@ -23,7 +23,7 @@ def _gpu_count() -> int:
         return 0
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, out_dir: str, cfg: dict):
     import ctypes as C
 
     import torch
@@ -57,10 +57,13 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         lib.ckb200_tune_set(b"tp_p2p", 0)
         assert lib.ckb200_tp_allreduce(None, want.data_ptr(), count, None) == 0, lib.ckb200_last_error_message()
         assert lib.ckb200_synchronize() == 0, lib.ckb200_last_error_message()
-        assert torch.equal(got, want), (rank, call, count)
+        if world == 2:
+            assert torch.equal(got, want), (rank, call, count)
+        else:                                             # more than two addends: NCCL's order of additions is its own
+            assert torch.allclose(got, want, rtol=1e-5, atol=1e-5), (rank, call, count)
     lib.ckb200_tune_set(b"tp_p2p", 1)
 
-    cpu = so.CpuModel(TP_CFG, seed=5)
+    cpu = so.CpuModel(cfg, seed=5)
     cpu.prefill_kv(20, seed=6)
     shard = so.TpShard(cpu, rank, world)
     lib.ckb200_model_use_tp.argtypes = [C.c_void_p]
@@ -68,7 +71,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     def run(fused: int):
         """Two decode steps of a fresh model; fused: the exchange inside the norm kernel (1) or the all-reduce kernel (0)."""
         lib.ckb200_tune_set(b"tp_fused_norm", fused)
-        st = so.make_cfg(TP_CFG, batch=1, tp_rank=rank, tp_size=world)
+        st = so.make_cfg(cfg, batch=1, tp_rank=rank, tp_size=world)
         handle = lib.ckb200_model_create(C.byref(st))
         assert handle, lib.ckb200_last_error_message()
         lib.ckb200_model_use_tp(handle)
@@ -77,7 +80,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         outs = []
         for tok in (7, 123):
             ids = np.array([tok], dtype=np.int32)
-            logits = np.zeros((1, TP_CFG["vocab_size"]), np.float32)
+            logits = np.zeros((1, cfg["vocab_size"]), np.float32)
             assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, lib.ckb200_last_error_message()
             outs.append(logits[0].copy())
         dist.barrier()
@@ -98,20 +101,23 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(_gpu_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_tensor_parallel_decode(tmp_path, orc):
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_decode(tmp_path, orc, world):
     import torch.multiprocessing as mp
 
     import step_oracle as so
 
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cfg = TP_CFG if world == 2 else dict(TP_CFG, num_kv_heads=4)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    cpu = so.CpuModel(TP_CFG, seed=5)
+    mp.spawn(_worker, args=(world, port, str(tmp_path), cfg), nprocs=world, join=True)
+    cpu = so.CpuModel(cfg, seed=5)
     cpu.prefill_kv(20, seed=6)
     want = np.stack([cpu.decode(orc, tok, 20 + i) for i, tok in enumerate((7, 123))])
-    for rank in range(2):
+    for rank in range(world):
         got = np.load(tmp_path / f"rank{rank}.npy")
         for a, b in zip(got, want):
             cos = float(a.astype(np.float64) @ b.astype(np.float64) / (np.linalg.norm(a) * np.linalg.norm(b)))

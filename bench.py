@@ -581,6 +581,35 @@ def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
         out["shapes"][f"{n}x{k}"] = {"ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": m_tokens / ms * 1e3}
         flops_total += flops
         ms_total += ms
+    # causal attention of the same prefill (Llama-3-8B heads), fp32 head-major tensors resident on the device
+    H, Hkv, d = 32, 8, 128
+    gen = torch.Generator(device=dev).manual_seed(5)
+    q = torch.randn(H, m_tokens, d, device=dev, generator=gen)
+    kk = torch.randn(Hkv, m_tokens, d, device=dev, generator=gen)
+    vv = torch.randn(Hkv, m_tokens, d, device=dev, generator=gen)
+    oo = torch.empty_like(q)
+    lib.ckb200_stream.restype = C.c_void_p
+    st = torch.cuda.ExternalStream(lib.ckb200_stream()) if stream_ptr is None else torch.cuda.current_stream()
+
+    def attn():
+        rc = lib.ckb200_dev_attention_prefill(C.c_void_p(q.data_ptr()), C.c_void_p(kk.data_ptr()), C.c_void_p(vv.data_ptr()), C.c_void_p(oo.data_ptr()),
+                                              H, Hkv, m_tokens, d, d, m_tokens, 1, stream_ptr)
+        if rc != 0:
+            raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+    torch.cuda.synchronize()
+    for _ in range(3):
+        attn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for _ in range(iters):
+        attn()
+    e1.record(st)
+    torch.cuda.synchronize()
+    attn_ms = e0.elapsed_time(e1) / iters
+    attn_flops = 4.0 * (m_tokens * (m_tokens + 1) / 2) * d * H
+    out["causal_attention"] = {"shape": f"H={H} Hkv={Hkv} d={d} T={m_tokens}", "ms": attn_ms, "tflops_fp32": attn_flops / attn_ms / 1e9,
+                               "note": "exact fp32 FMA on the CUDA cores (the parity tolerance leaves no room for fp16/tf32 scores)"}
     out["tflops"] = flops_total / ms_total / 1e9
     out["roofline"] = {"bound": "tensor", "achieved": out["tflops"], "peak": tensor_peak, "unit": "TFLOP/s", "frac": out["tflops"] / tensor_peak,
                        "note": "2*M*N*K of the f16 MMA; peak = measured cuBLAS bf16 burst"}

@@ -150,6 +150,14 @@ size_t ckb200_attention_decode_counter_bytes(int batch, int num_kv_heads);
 int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
 size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
 
+/* Prefill attention over head-major fp32 tensors: attention_forward_causal_head_major_gqa_flash[_strided] and
+ * attention_forward_full_head_major_gqa_flash[_strided] (src/kernels/attention_kernels.c:2847-3005).
+ * q, out [H][T][aligned_head_dim]; k, v [Hkv][kv_stride_tokens][aligned_head_dim]; causal != 0: query token i sees keys
+ * 0 .. i, else all T.  Shapes: H a multiple of Hkv with at most 8 query heads per kv head, aligned head size 64 or 128;
+ * others are refused with CKB_ERR_SHAPE. */
+int ckb200_dev_attention_prefill(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads,
+                                 int num_tokens, int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal, void *stream);
+
 /* kv_cache_store (src/kernels/kv_cache_kernels.c:111-129): k, v [Hkv][head_dim] -> cache[Hkv][max_seq][head_dim] at pos
  * (or at *pos_dev when given). */
 int ckb200_dev_kv_cache_store(float *kv_cache_k, float *kv_cache_v, const float *k, const float *v, int pos,

@@ -90,6 +90,17 @@ void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const 
 void attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache, const float *v_cache,
                                                    float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
                                                    int cache_capacity, int head_dim, int aligned_head_dim);
+/* prefill attention: include/ckernel_engine.h:1122-1165; src/kernels/attention_kernels.c:2924-3005 */
+void attention_forward_causal_head_major_gqa_flash(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                   int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim);
+void attention_forward_causal_head_major_gqa_flash_strided(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                           int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                           int kv_stride_tokens);
+void attention_forward_full_head_major_gqa_flash(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                 int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim);
+void attention_forward_full_head_major_gqa_flash_strided(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                         int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                         int kv_stride_tokens);
 void attention_flash_decode(float *out, const float *q, const float *k, const float *v, int T_q, int T_k, int H, int D_h,
                             float scale);
 void kv_cache_write_head_major(const float *k_token, const float *v_token, float *k_cache, float *v_cache, int num_kv_heads,

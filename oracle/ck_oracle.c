@@ -489,6 +489,66 @@ void oracle_attention_forward_decode_head_major_gqa_flash(const float *q_token, 
     }
 }
 
+/* ---- prefill attention (src/kernels/attention_kernels.c:2847-3005; per-query online softmax :1546-1602) ----
+ * q, out [H][T][ad]; k, v [Hkv][kv_stride_tokens][ad]; query token i of head h sees keys 0 .. i (causal) or all T of
+ * kv head h * Hkv / H; key by key: a new maximum rescales the running sum and output, otherwise exp(score - max). */
+static void orc_flash_query(const float *q, const float *k, const float *v, int kv_tokens, int hd, int ad, float scale, float *out)
+{
+    float m = -INFINITY, s = 0.0f;
+    for (int d = 0; d < hd; ++d) out[d] = 0.0f;
+    for (int j = 0; j < kv_tokens; ++j) {
+        const float *kr = k + (size_t)j * ad, *vr = v + (size_t)j * ad;
+        float dot = 0.0f;
+        for (int d = 0; d < hd; ++d) dot += q[d] * kr[d];
+        const float score = dot * scale;
+        if (score > m) {
+            const float f = m == -INFINITY ? 0.0f : expf(m - score);
+            s *= f;
+            for (int d = 0; d < hd; ++d) out[d] *= f;
+            s += 1.0f;
+            for (int d = 0; d < hd; ++d) out[d] += vr[d];
+            m = score;
+        } else {
+            const float e = expf(score - m);
+            s += e;
+            for (int d = 0; d < hd; ++d) out[d] += e * vr[d];
+        }
+    }
+    const float inv = 1.0f / s;
+    for (int d = 0; d < hd; ++d) out[d] *= inv;
+    for (int d = hd; d < ad; ++d) out[d] = 0.0f;
+}
+
+static void orc_attention_prefill(const float *q, const float *k, const float *v, float *output, int num_heads, int num_kv_heads, int num_tokens,
+                                  int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal)
+{
+    if (!q || !k || !v || !output) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || kv_stride_tokens < num_tokens) return;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const size_t hs = (size_t)kv_stride_tokens * (size_t)aligned_head_dim;
+    for (int h = 0; h < num_heads; ++h) {
+        const int kvh = (int)((long long)h * num_kv_heads / num_heads);
+        for (int i = 0; i < num_tokens; ++i) {
+            const size_t row = ((size_t)h * num_tokens + i) * aligned_head_dim;
+            orc_flash_query(q + row, k + kvh * hs, v + kvh * hs, causal ? i + 1 : num_tokens, head_dim, aligned_head_dim, scale, output + row);
+        }
+    }
+}
+
+void oracle_attention_forward_causal_head_major_gqa_flash_strided(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                  int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                  int kv_stride_tokens)
+{
+    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 1);
+}
+
+void oracle_attention_forward_full_head_major_gqa_flash_strided(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                int kv_stride_tokens)
+{
+    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 0);
+}
+
 /* ---- KV cache store (src/kernels/kv_cache_kernels.c:70-129) ---- */
 void oracle_kv_cache_store(float *kc, float *vc, const float *k, const float *v, int layer, int pos,
                            int num_kv_heads, int head_dim, int max_seq_len)

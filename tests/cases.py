@@ -140,6 +140,25 @@ def attention_decode(lib, prefix, q, kc, vc, tokens: int) -> np.ndarray:
     return out
 
 
+def prefill_attention_inputs(seed: int, heads: int, kv_heads: int, ad: int, hd: int, tokens: int, stride: int):
+    """q [H][T][ad], k/v [Hkv][stride][ad]; the pad columns [hd, ad) hold garbage on purpose: the kernels must ignore them."""
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((heads, tokens, ad)).astype(np.float32)
+    k = rng.standard_normal((kv_heads, stride, ad)).astype(np.float32)
+    v = rng.standard_normal((kv_heads, stride, ad)).astype(np.float32)
+    return q, k, v
+
+
+def attention_prefill(lib, prefix, q, k, v, hd: int, causal: bool = True) -> np.ndarray:
+    heads, tokens, ad = q.shape
+    kv_heads, stride, _ = k.shape
+    out = np.full((heads, tokens, ad), np.nan, dtype=np.float32)
+    name = "attention_forward_causal_head_major_gqa_flash_strided" if causal else "attention_forward_full_head_major_gqa_flash_strided"
+    fn(lib, prefix, name)(fptr(q), fptr(k), fptr(v), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(hd), C.c_int(ad),
+                          C.c_int(stride))
+    return out
+
+
 def kv_cache_store(lib, prefix, kc, vc, k, v, pos: int):
     kv_heads, cap, d = kc.shape
     fn(lib, prefix, "kv_cache_store")(fptr(kc), fptr(vc), fptr(k), fptr(v), C.c_int(0), C.c_int(pos),

@@ -317,6 +317,37 @@ def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
         assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
 
 
+PREFILL_ATTN_CASES = [  # heads, kv_heads, ad, head_dim, tokens, kv stride, causal
+    (32, 8, 128, 128, 512, 512, True),     # Llama-3-8B-shaped prefill
+    (14, 2, 64, 64, 100, 128, True),       # Qwen2-0.5B heads: 7 query heads per kv head, strided cache
+    (8, 4, 64, 40, 33, 48, True),          # padded head, odd token count (the last pair has one row)
+    (4, 4, 64, 64, 1, 1, True),            # a single token
+    (6, 2, 128, 128, 65, 65, True),        # three heads per kv head
+    (16, 2, 128, 128, 50, 64, False),      # full (non-causal) form, 8 heads per kv head
+    (3, 3, 64, 64, 130, 130, True),        # one head per kv head: 64-token blocks
+]
+
+
+@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,stride,causal", PREFILL_ATTN_CASES)
+def test_attention_prefill(ck, orc, heads, kvh, ad, hd, tokens, stride, causal):
+    """Causal / full prefill attention through the reference-named entry points against the oracle: fp32 within
+    ATTN_ABS_TOL absolute on outputs of order one; pad columns of the output are zero."""
+    q, k, v = cases.prefill_attention_inputs(tokens + heads, heads, kvh, ad, hd, tokens, stride)
+    want = cases.attention_prefill(orc, "oracle_", q, k, v, hd, causal)
+    got = cases.attention_prefill(ck, "", q, k, v, hd, causal)
+    assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, float(np.max(np.abs(got - want)))
+    assert np.all(got[:, :, hd:] == 0)
+
+
+def test_attention_prefill_refuses_unsupported_shapes(ck):
+    """Head sizes and group sizes outside the kernel are refused loudly, the output stays untouched."""
+    q, k, v = cases.prefill_attention_inputs(1, 12, 4, 96, 96, 8, 8)
+    out = cases.attention_prefill(ck, "", q, k, v, 96)
+    assert np.all(np.isnan(out))
+    assert ck.ckb200_last_error() != 0
+    ck.ckb200_clear_error()
+
+
 def test_kv_cache_store_then_attend_token_by_token(ck, orc):
     """The reference's own KV-cache test pattern: write token t, attend over 0..t, for every t."""
     heads, kvh, d, cap, steps = 8, 4, 64, 32, 12

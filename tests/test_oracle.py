@@ -160,3 +160,14 @@ def test_oracle_vs_reference_attention(ref, orc, heads, kvh, d, tokens, cap):
     a = cases.attention_decode(ref, "", q, kc, vc, tokens)
     b = cases.attention_decode(orc, "oracle_", q, kc, vc, tokens)
     assert float(np.max(np.abs(a - b))) < 1e-5          # the reference's own decode-vs-full tolerance
+
+
+@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,stride,causal", [(8, 4, 64, 64, 37, 37, True), (14, 2, 64, 64, 70, 96, True), (4, 4, 64, 40, 9, 16, True),
+                                                                (8, 2, 128, 128, 33, 40, False)])
+def test_oracle_vs_reference_prefill_attention(ref, orc, heads, kvh, ad, hd, tokens, stride, causal):
+    """The restated per-query online softmax against the reference's own build (its SIMD path sums in another order)."""
+    q, k, v = cases.prefill_attention_inputs(tokens, heads, kvh, ad, hd, tokens, stride)
+    a = cases.attention_prefill(ref, "", q, k, v, hd, causal)
+    b = cases.attention_prefill(orc, "oracle_", q, k, v, hd, causal)
+    assert float(np.max(np.abs(a - b))) < 1e-5
+    assert np.all(b[:, :, hd:] == 0)

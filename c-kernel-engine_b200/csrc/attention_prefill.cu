@@ -9,8 +9,9 @@
 // consecutive tokens): each lane keeps a quarter of both query vectors and of both output accumulators in registers,
 // reads its quarter of a key (value) once for both rows (a 64-byte broadcast per row pair), and the four partial dot
 // products meet in two shuffles.  Keys are taken four at a time (eight independent dot products, one branch-free softmax
-// update per block), because a row's keys are a serial chain and the longest CTA sets the kernel's time.  fp32 arithmetic on the CUDA cores: the reference's tolerance (1e-3 relative on
-// fp32 outputs) leaves no room for fp16/tf32 score rounding under the exponential.
+// update per block), because a row's keys are a serial chain and the longest CTA sets the kernel's time.  fp32
+// arithmetic on the CUDA cores: the reference's tolerance (1e-3 relative on fp32 outputs) leaves no room for fp16/tf32
+// score rounding under the exponential.
 #include <math.h>
 
 #include "device_common.cuh"

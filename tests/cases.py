@@ -140,6 +140,9 @@ def attention_decode(lib, prefix, q, kc, vc, tokens: int) -> np.ndarray:
     return out
 
 
+GOLDEN_PREFILL_ATTN = [(8, 4, 64, 64, 37, 40, 61), (4, 2, 64, 40, 9, 9, 62)]   # heads, kv heads, ad, head_dim, tokens, kv stride, seed
+
+
 def prefill_attention_inputs(seed: int, heads: int, kv_heads: int, ad: int, hd: int, tokens: int, stride: int):
     """q [H][T][ad], k/v [Hkv][stride][ad]; the pad columns [hd, ad) hold garbage on purpose: the kernels must ignore them."""
     rng = np.random.default_rng(seed)
@@ -265,6 +268,10 @@ def golden_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
     for heads, kvh, d, tokens, cap, seed in GOLDEN_ATTN:
         q, kc, vc = attention_inputs(seed, heads, kvh, d, tokens, cap)
         out[f"attn_{heads}_{kvh}_{d}_{tokens}"] = attention_decode(lib, prefix, q, kc, vc, tokens)
+
+    for heads, kvh, ad, hd, tokens, stride, seed in GOLDEN_PREFILL_ATTN:
+        q, k, v = prefill_attention_inputs(seed, heads, kvh, ad, hd, tokens, stride)
+        out[f"prefill_attn_{heads}_{kvh}_{ad}_{hd}_{tokens}"] = attention_prefill(lib, prefix, q, k, v, hd, True)
 
     rng = np.random.default_rng(41)
     cos, sin = rope_cache(lib, prefix, 40, 64, 1.0e6)

@@ -527,6 +527,11 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                 line["decode"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()
             try:
+                line["attention"] = attention_bench(lib, torch, peak)
+            except Exception as exc:
+                line["attention"] = {"error": repr(exc)}
+                lib.ckb200_clear_error()
+            try:
                 line["prefill"] = prefill_bench(lib, 512, 20, sp, torch, measured_tensor_peak())
             except Exception as exc:
                 line["prefill"] = {"error": repr(exc)}
@@ -669,6 +674,50 @@ def run_single(args):
         assert gemv(C.c_void_p(y[c].data_ptr()), C.c_void_p(wbuf.data_ptr() + c * slot), C.c_void_p(xq.data_ptr()), m, k, None) == 0
     assert lib.ckb200_synchronize() == 0
     print(json.dumps({"single": args.single, "launches": args.launches, "copies": copies, "bytes_per_launch": synth.gemv_bytes(fmt, m, k)}))
+
+
+def attention_bench(lib, torch, peak, iters=40):
+    """Decode attention of the 70B shape (64 Q / 8 KV heads, d 128, context 4096) over an fp32 and an IEEE fp16 KV cache, batch 1 and
+    32, each launch on another layer's cache (the caches of a case total several L2 sizes).  Times cover attention and split merge."""
+    lib.ckb200_attention_decode_scratch_bytes.restype = C.c_size_t
+    lib.ckb200_stream.restype = C.c_void_p
+    dev = torch.device("cuda", torch.cuda.current_device())
+    st = torch.cuda.ExternalStream(lib.ckb200_stream())
+    H, Hkv, d, T = 64, 8, 128, 4096
+    out = []
+    for batch, nl in ((1, 12), (32, 2)):
+        for kind, dt, eb, fn in (("fp32", torch.float32, 4, lib.ckb200_dev_attention_decode_ws), ("fp16", torch.float16, 2, lib.ckb200_dev_attention_decode_f16cache_ws)):
+            q = torch.randn(batch, H, d, device=dev)
+            o = torch.empty_like(q)
+            kc = torch.randn(nl, batch, Hkv, T, d, device=dev, dtype=dt)
+            vc = torch.randn(nl, batch, Hkv, T, d, device=dev, dtype=dt)
+            splits = lib.ckb200_attention_decode_splits(batch, Hkv, T)
+            scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(batch, H, d, splits)) // 4, device=dev)
+
+            def run(i):
+                l = i % nl
+                rc = fn(C.c_void_p(q.data_ptr()), C.c_void_p(kc[l].data_ptr()), C.c_void_p(vc[l].data_ptr()), C.c_void_p(o.data_ptr()), batch,
+                        C.c_longlong(Hkv * T * d), H, Hkv, T, T, d, d, splits, C.c_void_p(scratch.data_ptr()), None, None)
+                if rc != 0:
+                    raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+            torch.cuda.synchronize()
+            for i in range(3):
+                run(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for i in range(iters):
+                run(i)
+            e1.record(st)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            nbytes = batch * (2 * Hkv * T * d * eb + 2 * H * d * 4)
+            out.append({"kv_cache": kind, "batch": batch, "us": ms * 1e3, "kv_bytes": nbytes, "gbs": nbytes / ms / 1e6, "frac_of_measured_peak": nbytes / ms / 1e6 / peak,
+                        "splits": splits})
+            del kc, vc
+    if lib.ckb200_synchronize() != 0:
+        raise RuntimeError(lib.ckb200_last_error_message().decode())
+    return out
 
 
 def run_attention_only(args):

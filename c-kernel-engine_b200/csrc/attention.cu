@@ -357,7 +357,7 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
-    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0;
     cudaStream_t st = ckb_stream(stream);
     const int group = num_heads / num_kv_heads;
     const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 &&
@@ -429,8 +429,59 @@ extern "C" int ckb200_dev_attention_decode_fused(const float *q, const float *k_
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
     p.splits = splits;
-    p.counters = counters; p.q8_out = (uint8_t *)q8_out; p.out_stride = out_stride; p.q8_cols = q8_cols;
+    p.counters = counters; p.q8_out = (uint8_t *)q8_out; p.out_stride = out_stride; p.q8_cols = q8_cols; p.kv_f16 = 0;
     return ckb_launch_attn_tile(&p, batch, ckb_stream(stream));
+}
+
+// Decode attention over IEEE fp16 caches (attention_forward_decode_head_major_gqa_flash_f16cache,
+// src/kernels/attention_kernels.c:3450-3557): the same layout with 2-byte elements, widened to fp32 in the tile kernel;
+// the arithmetic after that is the fp32 path's.  Tile kernel shapes only (aligned head size 64 or 128, groups <= 8).
+extern "C" int ckb200_dev_attention_decode_f16cache_ws(const float *q, const uint16_t *k_cache, const uint16_t *v_cache, float *out, int batch,
+                                                       long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                                       int head_dim, int aligned_head_dim, int splits, float *scratch, const int *pos_dev, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !out) return 0;
+    if (batch <= 0 || num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return 0;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const int group = num_heads / num_kv_heads;
+    if ((aligned_head_dim != 64 && aligned_head_dim != 128) || num_heads % num_kv_heads || group > ATTN_G)
+        return ckb_fail(CKB_ERR_SHAPE, "attention decode (fp16 cache): %d heads / %d kv heads / head size %d is outside the tile kernel", num_heads,
+                        num_kv_heads, aligned_head_dim);
+    if ((((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) || (kv_batch_stride % 8))
+        return ckb_fail(CKB_ERR_ALIGN, "attention decode (fp16 cache): pointers and the sequence stride must be 16-byte aligned");
+    if (splits < 1) splits = 1;
+    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
+    if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
+    AttnParams p;
+    p.q = q; p.k = reinterpret_cast<const float *>(k_cache); p.v = reinterpret_cast<const float *>(v_cache); p.out = out; p.part = scratch;
+    p.pos_ptr = pos_dev;
+    p.kv_batch_stride = kv_batch_stride;
+    p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
+    p.scale = 1.0f / sqrtf((float)head_dim);
+    p.splits = splits;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 1;
+    cudaStream_t st = ckb_stream(stream);
+    const int rc = ckb_launch_attn_tile(&p, batch, st);
+    if (rc) return rc;
+    if (splits > 1)
+        return launch_pdl("attn_merge", attn_merge_kernel, dim3(batch * num_heads), dim3(128), 0, st, (const float *)scratch, out, splits, aligned_head_dim);
+    return 0;
+}
+
+extern "C" int ckb200_dev_attention_decode_f16cache(const float *q, const uint16_t *k_cache, const uint16_t *v_cache, float *out, int batch,
+                                                    long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                                    int head_dim, int aligned_head_dim, void *stream)
+{
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const int splits = ckb200_attention_decode_splits(batch, num_kv_heads, kv_tokens);
+    float *scratch = NULL;
+    if (splits > 1) {
+        scratch = (float *)ckb_scratch(CKB_SLOT_T, ckb200_attention_decode_scratch_bytes(batch, num_heads, aligned_head_dim, splits));
+        if (!scratch) return CKB_ERR_CUDA;
+    }
+    return ckb200_dev_attention_decode_f16cache_ws(q, k_cache, v_cache, out, batch, kv_batch_stride, num_heads, num_kv_heads, kv_tokens, cache_capacity,
+                                                   head_dim, aligned_head_dim, splits, scratch, NULL, stream);
 }
 
 // Convenience form: picks the split count and takes the scratch from the library's own pool.
@@ -525,7 +576,7 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
-    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (!fast) {
         if (aligned_head_dim > ATTN_GEN_MAXD) return ckb_fail(CKB_ERR_LIMIT, "attention decode: aligned_head_dim %d > %d", aligned_head_dim, ATTN_GEN_MAXD);

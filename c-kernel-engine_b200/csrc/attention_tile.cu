@@ -30,17 +30,34 @@ constexpr int AT_KT = 64;           // keys per tile
 constexpr int AT_STAGES = 3;
 constexpr int AT_LPK = 16;          // lanes per key
 
+// EB: bytes per cache element, 4 (fp32 cache) or 2 (IEEE fp16 cache, attention_forward_decode_head_major_gqa_flash_f16cache,
+// src/kernels/attention_kernels.c:3450-3557: the halves are widened to fp32 and the arithmetic is the same).  The merge
+// scratch of the epilogue needs the fp32-sized stages either way.
 template <int AD> constexpr int at_stage_bytes() { return 2 * AT_KT * AD * 4; }
 template <int AD> constexpr int at_smem_bytes() { return AT_STAGES * at_stage_bytes<AD>() + 2 * AT_STAGES * 8 + 16; }
 
-template <int AD>
+// this lane's four dimensions of piece `idx` of a cache row in shared memory
+template <int EB>
+__device__ __forceinline__ float4 at_row_piece(uint32_t row_addr, int idx)
+{
+    if constexpr (EB == 4) {
+        return lds_f4(row_addr + (uint32_t)idx * 16u);
+    } else {
+        uint32_t lo, hi;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(row_addr + (uint32_t)idx * 8u));
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&lo)), b = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+}
+
+template <int AD, int EB>
 __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, int *__restrict__ dev_err)
 {
     constexpr int C = AD / (4 * AT_LPK);           // float4 pieces per lane (1 for 64, 2 for 128)
     constexpr int G = ATTN_MAX_GROUP;
     constexpr int KPW = AT_KT / AT_NW;             // keys per warp per tile
     constexpr int STEPS = KPW / 2;
-    constexpr int ROW = AD * 4;                    // bytes per cache row
+    constexpr int ROW = AD * EB;                   // bytes per cache row
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t s_base = smem_u32(smem);
     const uint32_t s_bar = s_base + AT_STAGES * at_stage_bytes<AD>();
@@ -65,8 +82,8 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
     const int tiles_per_split = (ntiles_all + p.splits - 1) / p.splits;
     const int tile0 = split * tiles_per_split;
     const int ntiles = max(0, min(ntiles_all, tile0 + tiles_per_split) - tile0);
-    const uint8_t *kbase = reinterpret_cast<const uint8_t *>(p.k + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD);
-    const uint8_t *vbase = reinterpret_cast<const uint8_t *>(p.v + (size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD);
+    const uint8_t *kbase = reinterpret_cast<const uint8_t *>(p.k) + ((size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD) * EB;
+    const uint8_t *vbase = reinterpret_cast<const uint8_t *>(p.v) + ((size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD) * EB;
 
     auto issue_tile = [&](int i) {                 // one thread: both copies of tile i of this split
         const int st = i % AT_STAGES, t_begin = (tile0 + i) * AT_KT;
@@ -120,7 +137,7 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
             const int key = 2 * step + sub;
             float4 kr[C];
 #pragma unroll
-            for (int c = 0; c < C; ++c) kr[c] = lds_f4(ks + (uint32_t)key * ROW + (uint32_t)(c * AT_LPK + li) * 16u);
+            for (int c = 0; c < C; ++c) kr[c] = at_row_piece<EB>(ks + (uint32_t)key * ROW, c * AT_LPK + li);
             float s[G];
 #pragma unroll
             for (int h = 0; h < G; ++h) {
@@ -184,7 +201,7 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
             float4 vr[C];
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                vr[c] = lds_f4(vs + (uint32_t)key * ROW + (uint32_t)(c * AT_LPK + li) * 16u);
+                vr[c] = at_row_piece<EB>(vs + (uint32_t)key * ROW, c * AT_LPK + li);
                 if (!valid) vr[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
@@ -334,18 +351,21 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
 using namespace ckb;
 
 // Launches the tile kernel for aligned_head_dim 64 or 128; the caller has checked group size and alignment.
-extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream)
+template <int AD, int EB>
+static int launch_attn_tile(const AttnParams *p, int batch, void *stream)
 {
-    const int ad = p->ad;
-    const int smem = ad == 64 ? at_smem_bytes<64>() : at_smem_bytes<128>();
-    static int attr_set[2] = {0, 0};
-    if (!attr_set[ad == 128]) {
-        const cudaError_t e = ad == 64 ? cudaFuncSetAttribute(attn_tile_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                                       : cudaFuncSetAttribute(attn_tile_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (ckb_check_cuda((int)e, "attention smem attr")) return CKB_ERR_CUDA;
-        attr_set[ad == 128] = 1;
+    const int smem = at_smem_bytes<AD>();
+    static int attr_set = 0;
+    if (!attr_set) {
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_tile_kernel<AD, EB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention smem attr")) return CKB_ERR_CUDA;
+        attr_set = 1;
     }
     const dim3 grid(p->splits, p->Hkv, batch);
-    return ad == 64 ? launch_pdl("attn_tile", attn_tile_kernel<64>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word())
-                    : launch_pdl("attn_tile", attn_tile_kernel<128>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word());
+    return launch_pdl("attn_tile", attn_tile_kernel<AD, EB>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word());
+}
+
+extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream)
+{
+    if (p->kv_f16) return p->ad == 64 ? launch_attn_tile<64, 2>(p, batch, stream) : launch_attn_tile<128, 2>(p, batch, stream);
+    return p->ad == 64 ? launch_attn_tile<64, 4>(p, batch, stream) : launch_attn_tile<128, 4>(p, batch, stream);
 }

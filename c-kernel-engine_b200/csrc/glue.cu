@@ -115,6 +115,22 @@ __global__ void kv_store_kernel(float *__restrict__ kc, float *__restrict__ vc, 
     }
 }
 
+// the same store into IEEE fp16 caches (kv_cache_store_f16, src/kernels/kv_cache_kernels.c:131-163): round to nearest even
+__global__ void kv_store_f16_kernel(unsigned short *__restrict__ kc, unsigned short *__restrict__ vc, const float *__restrict__ k,
+                                    const float *__restrict__ v, int pos, const int *__restrict__ pos_dev, int num_kv_heads,
+                                    int head_dim, int max_seq)
+{
+    const int p = pos_dev ? *pos_dev : pos;
+    if (p < 0 || p >= max_seq) return;
+    const int n = num_kv_heads * head_dim;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        const size_t dst = ((size_t)h * max_seq + p) * head_dim + d;
+        kc[dst] = __half_as_ushort(__float2half_rn(k[i]));
+        vc[dst] = __half_as_ushort(__float2half_rn(v[i]));
+    }
+}
+
 // one CTA per token: dequantise the table row of its id (out-of-range ids read row 0), zero the padding
 template <int FMT>
 __global__ void embedding_kernel(const int32_t *__restrict__ ids, int count, int vocab, const uint8_t *__restrict__ table,
@@ -204,6 +220,17 @@ extern "C" int ckb200_dev_kv_cache_store(float *kv_cache_k, float *kv_cache_v, c
     kv_store_kernel<<<grid_for((long long)num_kv_heads * head_dim, 256, 64), 256, 0, ckb_stream(stream)>>>(
         kv_cache_k, kv_cache_v, k, v, pos, pos_dev, num_kv_heads, head_dim, max_seq_len);
     return ckb_check_launch("kv_cache_store");
+}
+
+extern "C" int ckb200_dev_kv_cache_store_f16(uint16_t *kv_cache_k, uint16_t *kv_cache_v, const float *k, const float *v, int pos,
+                                             const int *pos_dev, int num_kv_heads, int head_dim, int max_seq_len, void *stream)
+{
+    if (!kv_cache_k || !kv_cache_v || !k || !v || num_kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return 0;
+    if (!pos_dev && (pos < 0 || pos >= max_seq_len)) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    kv_store_f16_kernel<<<grid_for((long long)num_kv_heads * head_dim, 256, 64), 256, 0, ckb_stream(stream)>>>(
+        kv_cache_k, kv_cache_v, k, v, pos, pos_dev, num_kv_heads, head_dim, max_seq_len);
+    return ckb_check_launch("kv_cache_store_f16");
 }
 
 template <int FMT>

@@ -343,6 +343,50 @@ void kv_cache_store(float *kv_cache_k, float *kv_cache_v, const float *k, const 
     kv_cache_write_head_major(k, v, kv_cache_k, kv_cache_v, num_kv_heads, pos, max_seq_len, head_dim, head_dim);
 }
 
+/* fp16 KV cache (src/kernels/kv_cache_kernels.c:131-163, src/kernels/attention_kernels.c:3450-3557): k, v [Hkv][head_dim]
+ * fp32 -> cache[Hkv][max_seq_len][head_dim] IEEE half at pos; only the touched rows travel. */
+void kv_cache_store_f16(uint16_t *kv_cache_k, uint16_t *kv_cache_v, const float *k, const float *v, int layer, int pos, int num_kv_heads,
+                        int head_dim, int max_seq_len)
+{
+    (void)layer;
+    if (!kv_cache_k || !kv_cache_v || !k || !v) return;
+    if (num_kv_heads <= 0 || pos < 0 || head_dim <= 0 || max_seq_len <= 0 || pos >= max_seq_len) return;
+    if (ckb_ensure_init()) return;
+    const size_t tok_b = (size_t)num_kv_heads * head_dim * sizeof(float);
+    const float *dk = (const float *)ckb_stage_in(k, tok_b, CKB_SLOT_X, 0);
+    const float *dv = (const float *)ckb_stage_in(v, tok_b, CKB_SLOT_A, 0);
+    uint16_t *stage = (uint16_t *)ckb_scratch(CKB_SLOT_T, tok_b);            /* two one-token fp16 caches [Hkv][1][d] */
+    if (!dk || !dv || !stage) return;
+    uint16_t *dkc = stage, *dvc = stage + (size_t)num_kv_heads * head_dim;
+    if (ckb200_dev_kv_cache_store_f16(dkc, dvc, dk, dv, 0, NULL, num_kv_heads, head_dim, 1, NULL) != 0) return;
+    cudaStream_t st = ckb_stream(NULL);
+    const size_t row = (size_t)head_dim * sizeof(uint16_t), pitch = (size_t)max_seq_len * row;
+    if (ckb_check_cuda((int)cudaMemcpy2DAsync(kv_cache_k + (size_t)pos * head_dim, pitch, dkc, row, row, num_kv_heads, cudaMemcpyDefault, st), "fp16 k rows")) return;
+    if (ckb_check_cuda((int)cudaMemcpy2DAsync(kv_cache_v + (size_t)pos * head_dim, pitch, dvc, row, row, num_kv_heads, cudaMemcpyDefault, st), "fp16 v rows")) return;
+    ckb_check_cuda((int)cudaStreamSynchronize(st), "sync");
+}
+
+void attention_forward_decode_head_major_gqa_flash_f16cache(const float *q_token, const uint16_t *k_cache, const uint16_t *v_cache,
+                                                            float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
+                                                            int cache_capacity, int head_dim, int aligned_head_dim)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    if (ckb_ensure_init()) return;
+    const size_t q_b = (size_t)num_heads * aligned_head_dim * sizeof(float);
+    const size_t kv_b = (size_t)num_kv_heads * cache_capacity * aligned_head_dim * sizeof(uint16_t);
+    const float *dq = (const float *)ckb_stage_in(q_token, q_b, CKB_SLOT_X, 0);
+    const uint16_t *dk = (const uint16_t *)ckb_stage_in(k_cache, kv_b, CKB_SLOT_A, 0);
+    const uint16_t *dv = (const uint16_t *)ckb_stage_in(v_cache, kv_b, CKB_SLOT_B, 0);
+    int back;
+    float *dout = (float *)ckb_stage_out(out_token, q_b, CKB_SLOT_Y, &back);
+    if (!dq || !dk || !dv || !dout) return;
+    if (ckb200_dev_attention_decode_f16cache(dq, dk, dv, dout, 1, 0, num_heads, num_kv_heads, kv_tokens, cache_capacity, head_dim,
+                                             aligned_head_dim, NULL) != 0) return;
+    ckb_finish_out(out_token, dout, q_b, back);
+}
+
 /* ------------------------------------------------------------------ glue ops */
 
 void rmsnorm_forward(const float *input, const float *gamma, float *output, float *rstd_cache, int tokens, int d_model,

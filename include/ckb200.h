@@ -150,6 +150,20 @@ size_t ckb200_attention_decode_counter_bytes(int batch, int num_kv_heads);
 int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
 size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
 
+/* fp16 KV cache: kv_cache_store_f16 (src/kernels/kv_cache_kernels.c:131-163; round to nearest even, bit-exact) and
+ * attention_forward_decode_head_major_gqa_flash_f16cache (src/kernels/attention_kernels.c:3450-3557): the layouts of the
+ * fp32 entry points with 2-byte elements (kv_batch_stride counted in elements, a multiple of 8).  Half the KV bytes per
+ * token; the halves are widened to fp32 in shared memory, the arithmetic is the fp32 path's.  Aligned head size 64 or
+ * 128 and at most 8 query heads per kv head; other shapes are refused with CKB_ERR_SHAPE. */
+int ckb200_dev_kv_cache_store_f16(uint16_t *kv_cache_k, uint16_t *kv_cache_v, const float *k, const float *v, int pos,
+                                  const int *pos_dev, int num_kv_heads, int head_dim, int max_seq_len, void *stream);
+int ckb200_dev_attention_decode_f16cache(const float *q, const uint16_t *k_cache, const uint16_t *v_cache, float *out, int batch,
+                                         long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                         int head_dim, int aligned_head_dim, void *stream);
+int ckb200_dev_attention_decode_f16cache_ws(const float *q, const uint16_t *k_cache, const uint16_t *v_cache, float *out, int batch,
+                                            long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                            int head_dim, int aligned_head_dim, int splits, float *scratch, const int *pos_dev, void *stream);
+
 /* Prefill attention over head-major fp32 tensors: attention_forward_causal_head_major_gqa_flash[_strided] and
  * attention_forward_full_head_major_gqa_flash[_strided] (src/kernels/attention_kernels.c:2847-3005).
  * q, out [H][T][aligned_head_dim]; k, v [Hkv][kv_stride_tokens][aligned_head_dim]; causal != 0: query token i sees keys

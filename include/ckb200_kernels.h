@@ -90,6 +90,12 @@ void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const 
 void attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache, const float *v_cache,
                                                    float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
                                                    int cache_capacity, int head_dim, int aligned_head_dim);
+/* fp16 KV cache: include/ckernel_engine.h:1232-1241, :1682-1690 */
+void attention_forward_decode_head_major_gqa_flash_f16cache(const float *q_token, const uint16_t *k_cache, const uint16_t *v_cache,
+                                                            float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
+                                                            int cache_capacity, int head_dim, int aligned_head_dim);
+void kv_cache_store_f16(uint16_t *kv_cache_k, uint16_t *kv_cache_v, const float *k, const float *v, int layer, int pos,
+                        int num_kv_heads, int head_dim, int max_seq_len);
 /* prefill attention: include/ckernel_engine.h:1122-1165; src/kernels/attention_kernels.c:2924-3005 */
 void attention_forward_causal_head_major_gqa_flash(const float *q, const float *k, const float *v, float *output, int num_heads,
                                                    int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim);

@@ -16,6 +16,7 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #define ORC_QK_K 256
@@ -560,6 +561,47 @@ void oracle_kv_cache_store(float *kc, float *vc, const float *k, const float *v,
         memcpy(kc + dst, k + (size_t)h * head_dim, sizeof(float) * head_dim);
         memcpy(vc + dst, v + (size_t)h * head_dim, sizeof(float) * head_dim);
     }
+}
+
+/* ---- fp16 KV cache (src/kernels/kv_cache_kernels.c:131-163 store; src/kernels/attention_kernels.c:3450-3557 decode:
+ * every kv head's rows are widened to fp32 and attended exactly like the fp32 cache) ---- */
+void oracle_kv_cache_store_f16(uint16_t *kc, uint16_t *vc, const float *k, const float *v, int layer, int pos,
+                               int num_kv_heads, int head_dim, int max_seq_len)
+{
+    (void)layer;
+    if (!k || !v || !kc || !vc || num_kv_heads <= 0 || pos < 0 || pos >= max_seq_len || head_dim <= 0) return;
+    for (int h = 0; h < num_kv_heads; ++h) {
+        const size_t dst = ((size_t)h * max_seq_len + pos) * head_dim;
+        for (int d = 0; d < head_dim; ++d) {
+            kc[dst + d] = oracle_fp32_to_fp16(k[(size_t)h * head_dim + d]);
+            vc[dst + d] = oracle_fp32_to_fp16(v[(size_t)h * head_dim + d]);
+        }
+    }
+}
+
+void oracle_attention_forward_decode_head_major_gqa_flash_f16cache(const float *q_token, const uint16_t *k_cache, const uint16_t *v_cache,
+                                                                   float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
+                                                                   int cache_capacity, int head_dim, int aligned_head_dim)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const size_t hs = (size_t)cache_capacity * (size_t)aligned_head_dim, n = (size_t)kv_tokens * aligned_head_dim;
+    float *kf = (float *)malloc(n * sizeof(float)), *vf = (float *)malloc(n * sizeof(float));
+    if (!kf || !vf) { free(kf); free(vf); return; }
+    for (int kvh = 0; kvh < num_kv_heads; ++kvh) {
+        for (size_t i = 0; i < n; ++i) {
+            kf[i] = oracle_fp16_to_fp32(k_cache[kvh * hs + i]);
+            vf[i] = oracle_fp16_to_fp32(v_cache[kvh * hs + i]);
+        }
+        const int h0 = (int)((long long)kvh * num_heads / num_kv_heads), h1 = (int)((long long)(kvh + 1) * num_heads / num_kv_heads);
+        for (int h = h0; h < h1; ++h)
+            orc_flash_decode_head(out_token + (size_t)h * aligned_head_dim, q_token + (size_t)h * aligned_head_dim, kf, vf, kv_tokens,
+                                  aligned_head_dim, scale);
+    }
+    free(kf);
+    free(vf);
 }
 
 /* ---- RoPE (src/kernels/rope_kernels.c:221-243 cache, :320-417 rotate-half, :806-819 q+k) ---- */

@@ -162,6 +162,23 @@ def attention_prefill(lib, prefix, q, k, v, hd: int, causal: bool = True) -> np.
     return out
 
 
+def attention_decode_f16cache(lib, prefix, q, kc16, vc16, tokens: int, hd: int | None = None) -> np.ndarray:
+    """kc16, vc16: uint16 arrays [Hkv][cap][ad] holding IEEE halves."""
+    heads, d = q.shape
+    kv_heads, cap, _ = kc16.shape
+    out = np.full((heads, d), np.nan, dtype=np.float32)
+    fn(lib, prefix, "attention_forward_decode_head_major_gqa_flash_f16cache")(
+        fptr(q), vptr(kc16), vptr(vc16), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(cap),
+        C.c_int(hd or d), C.c_int(d))
+    return out
+
+
+def kv_cache_store_f16(lib, prefix, kc16, vc16, k, v, pos: int):
+    kv_heads, cap, d = kc16.shape
+    fn(lib, prefix, "kv_cache_store_f16")(vptr(kc16), vptr(vc16), fptr(k), fptr(v), C.c_int(0), C.c_int(pos), C.c_int(kv_heads),
+                                          C.c_int(d), C.c_int(cap))
+
+
 def kv_cache_store(lib, prefix, kc, vc, k, v, pos: int):
     kv_heads, cap, d = kc.shape
     fn(lib, prefix, "kv_cache_store")(fptr(kc), fptr(vc), fptr(k), fptr(v), C.c_int(0), C.c_int(pos),
@@ -268,6 +285,15 @@ def golden_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
     for heads, kvh, d, tokens, cap, seed in GOLDEN_ATTN:
         q, kc, vc = attention_inputs(seed, heads, kvh, d, tokens, cap)
         out[f"attn_{heads}_{kvh}_{d}_{tokens}"] = attention_decode(lib, prefix, q, kc, vc, tokens)
+
+    heads, kvh, d, tokens, cap, seed = GOLDEN_ATTN[0]
+    q, kc, vc = attention_inputs(seed, heads, kvh, d, tokens, cap)
+    out[f"attn_f16cache_{heads}_{kvh}_{d}_{tokens}"] = attention_decode_f16cache(lib, prefix, q, kc.astype(np.float16).view(np.uint16),
+                                                                                  vc.astype(np.float16).view(np.uint16), tokens)
+    kc16, vc16 = np.zeros((2, 16, 64), np.uint16), np.zeros((2, 16, 64), np.uint16)
+    r16 = np.random.default_rng(43)
+    kv_cache_store_f16(lib, prefix, kc16, vc16, (r16.standard_normal((2, 64)) * 100).astype(np.float32), r16.standard_normal((2, 64)).astype(np.float32), pos=9)
+    out["kv_store_f16_k"], out["kv_store_f16_v"] = kc16, vc16
 
     for heads, kvh, ad, hd, tokens, stride, seed in GOLDEN_PREFILL_ATTN:
         q, k, v = prefill_attention_inputs(seed, heads, kvh, ad, hd, tokens, stride)

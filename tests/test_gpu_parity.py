@@ -317,6 +317,41 @@ def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
         assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
 
 
+@pytest.mark.parametrize("heads,kvh,d,tokens,cap", [(14, 2, 64, 1025, 2048), (64, 8, 128, 4096, 4096), (8, 4, 64, 64, 64), (4, 4, 64, 1, 16),
+                                                    (6, 2, 128, 5, 8), (16, 2, 128, 333, 512)])
+def test_attention_decode_f16_cache(ck, orc, heads, kvh, d, tokens, cap):
+    """Decode attention over an IEEE fp16 KV cache (half the bytes), every split count, against the oracle."""
+    q, kc, vc = cases.attention_inputs(tokens + heads, heads, kvh, d, tokens, cap)
+    kc16, vc16 = kc.astype(np.float16).view(np.uint16), vc.astype(np.float16).view(np.uint16)
+    want = cases.attention_decode_f16cache(orc, "oracle_", q, kc16, vc16, tokens)
+    for splits in (0, 1, 3, 16):
+        ck.ckb200_tune_set(b"attn_splits", splits)
+        got = cases.attention_decode_f16cache(ck, "", q, kc16, vc16, tokens)
+        ck.ckb200_tune_set(b"attn_splits", 0)
+        assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+
+
+def test_kv_cache_store_f16_bit_exact_then_attend(ck, orc):
+    """fp32 -> fp16 store is bit-exact with the oracle (ties, subnormals, large values), token by token, and attention over the
+    cache built that way matches."""
+    heads, kvh, d, cap, steps = 8, 4, 64, 32, 10
+    rng = np.random.default_rng(7)
+    kc_g = np.zeros((kvh, cap, d), np.uint16); vc_g = np.zeros_like(kc_g)
+    kc_c, vc_c = kc_g.copy(), vc_g.copy()
+    for t in range(steps):
+        k = (rng.standard_normal((kvh, d)) * rng.choice([1e-7, 1e-3, 1.0, 2049.0], size=(kvh, d))).astype(np.float32)
+        v = rng.standard_normal((kvh, d)).astype(np.float32)
+        k[0, :4] = [1.0009765625, 1.00048828125, 65519.9, 6.0e-8]          # halfway cases, the overflow edge, a subnormal
+        q = rng.standard_normal((heads, d)).astype(np.float32)
+        cases.kv_cache_store_f16(ck, "", kc_g, vc_g, k, v, t)
+        cases.kv_cache_store_f16(orc, "oracle_", kc_c, vc_c, k, v, t)
+        assert np.array_equal(kc_g, kc_c) and np.array_equal(vc_g, vc_c)
+    ks = np.clip(kc_g.view(np.float16).astype(np.float32), -8, 8).astype(np.float16).view(np.uint16)   # keep the scores in range
+    a = cases.attention_decode_f16cache(ck, "", q, ks, vc_g, steps)
+    b = cases.attention_decode_f16cache(orc, "oracle_", q, ks, vc_c, steps)
+    assert float(np.max(np.abs(a - b))) <= ATTN_ABS_TOL
+
+
 PREFILL_ATTN_CASES = [  # heads, kv_heads, ad, head_dim, tokens, kv stride, causal
     (32, 8, 128, 128, 512, 512, True),     # Llama-3-8B-shaped prefill
     (14, 2, 64, 64, 100, 128, True),       # Qwen2-0.5B heads: 7 query heads per kv head, strided cache

@@ -171,3 +171,23 @@ def test_oracle_vs_reference_prefill_attention(ref, orc, heads, kvh, ad, hd, tok
     b = cases.attention_prefill(orc, "oracle_", q, k, v, hd, causal)
     assert float(np.max(np.abs(a - b))) < 1e-5
     assert np.all(b[:, :, hd:] == 0)
+
+
+@pytest.mark.parametrize("heads,kvh,d,tokens,cap", [(14, 2, 64, 300, 320), (16, 2, 128, 333, 512), (8, 4, 64, 5000, 5000)])
+def test_oracle_vs_reference_f16_kv_cache(ref, orc, heads, kvh, d, tokens, cap):
+    """fp16 cache: the store is bit-exact (round to nearest even), decode attention agrees within the reference's own
+    tolerance between its paths (the last case is large enough for the reference's two-pass branch)."""
+    rng = np.random.default_rng(tokens)
+    kc_r = np.zeros((kvh, cap, d), np.uint16); vc_r = np.zeros_like(kc_r)
+    kc_o = np.zeros_like(kc_r); vc_o = np.zeros_like(kc_r)
+    for pos in (0, 1, cap - 1):
+        k = (rng.standard_normal((kvh, d)) * rng.choice([1e-6, 1.0, 300.0], size=(kvh, d))).astype(np.float32)
+        v = rng.standard_normal((kvh, d)).astype(np.float32)
+        cases.kv_cache_store_f16(ref, "", kc_r, vc_r, k, v, pos)
+        cases.kv_cache_store_f16(orc, "oracle_", kc_o, vc_o, k, v, pos)
+    assert np.array_equal(kc_r, kc_o) and np.array_equal(vc_r, vc_o)
+    q, kc, vc = cases.attention_inputs(tokens, heads, kvh, d, tokens, cap)
+    kc16, vc16 = kc.astype(np.float16).view(np.uint16), vc.astype(np.float16).view(np.uint16)
+    a = cases.attention_decode_f16cache(ref, "", q, kc16, vc16, tokens)
+    b = cases.attention_decode_f16cache(orc, "oracle_", q, kc16, vc16, tokens)
+    assert float(np.max(np.abs(a - b))) < 1e-5

@@ -433,6 +433,22 @@ extern "C" int ckb200_dev_attention_decode_fused(const float *q, const float *k_
     return ckb_launch_attn_tile(&p, batch, ckb_stream(stream));
 }
 
+// attention_forward_decode_head_major_gqa_flash_sliding (src/kernels/attention_kernels_sliding.c:528-600): the query attends
+// the last min(kv_tokens, sliding_window) cache rows, which in the head-major cache is the same attention on row pointers
+// moved forward by kv_tokens - that many rows (the head stride stays cache_capacity rows).
+extern "C" int ckb200_dev_attention_decode(const float *, const float *, const float *, float *, int, long long, int, int, int, int, int, int, void *);
+extern "C" int ckb200_dev_attention_decode_sliding(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
+                                                   long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                                   int head_dim, int aligned_head_dim, int sliding_window, void *stream)
+{
+    if (!q || !k_cache || !v_cache || !out) return 0;
+    if (kv_tokens <= 0 || kv_tokens > cache_capacity || aligned_head_dim <= 0) return 0;
+    const int eff = sliding_window > 0 && sliding_window < kv_tokens ? sliding_window : kv_tokens;
+    const size_t skip = (size_t)(kv_tokens - eff) * aligned_head_dim;
+    return ckb200_dev_attention_decode(q, k_cache + skip, v_cache + skip, out, batch, kv_batch_stride, num_heads, num_kv_heads, eff, cache_capacity,
+                                       head_dim, aligned_head_dim, stream);
+}
+
 // Decode attention over IEEE fp16 caches (attention_forward_decode_head_major_gqa_flash_f16cache,
 // src/kernels/attention_kernels.c:3450-3557): the same layout with 2-byte elements, widened to fp32 in the tile kernel;
 // the arithmetic after that is the fp32 path's.  Tile kernel shapes only (aligned head size 64 or 128, groups <= 8).

@@ -26,7 +26,7 @@ constexpr int AP_MAX_GROUP = 8;      // query heads per kv head on this path
 template <int AD>
 __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                            float *__restrict__ out, int H, int Hkv, int T, int head_dim, int kv_stride, int BT, float scale,
-                                                           int causal)
+                                                           int causal, int window)
 {
     extern __shared__ __align__(16) float4 ap_smem[];
     constexpr int P = AD / 4;        // float4 pieces per row
@@ -59,9 +59,12 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
     const int last_tok = min(T, t0 + BT) - 1;
     const int kend = causal ? last_tok + 1 : T;                       // keys 0 .. kend-1 are needed by some row of this CTA
     const int limA = causal ? tokA : T - 1, limB = causal ? tokB : T - 1;
+    // sliding window (attention_kernels_sliding.c:391-402): token i sees keys max(0, i - window + 1) .. i
+    const int loA = window > 0 ? max(0, tokA - window + 1) : 0, loB = window > 0 ? max(0, tokB - window + 1) : 0;
+    const int kbegin = window > 0 ? (max(0, t0 - window + 1) / AP_BK) * AP_BK : 0;      // first tile any row of this CTA needs
     const float *kbase = k + (size_t)kvh * kv_stride * AD, *vbase = v + (size_t)kvh * kv_stride * AD;
 
-    for (int k0 = 0; k0 < kend; k0 += AP_BK) {
+    for (int k0 = kbegin; k0 < kend; k0 += AP_BK) {
         const int nk = min(AP_BK, kend - k0), nk4 = (nk + 3) & ~3;
         __syncthreads();                                              // the previous tile has been consumed
         for (int e = threadIdx.x; e < nk4 * P; e += blockDim.x) {     // keys past the end of the block's range read as zero
@@ -88,16 +91,20 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
                 dA[c] += __shfl_xor_sync(0xffffffffu, dA[c], 1); dB[c] += __shfl_xor_sync(0xffffffffu, dB[c], 1);
                 dA[c] += __shfl_xor_sync(0xffffffffu, dA[c], 2); dB[c] += __shfl_xor_sync(0xffffffffu, dB[c], 2);
                 const int j = k0 + jj + c;
-                dA[c] = j <= limA ? dA[c] * scale : -INFINITY;        // key 0 is visible to every row, so the maxima are finite from the first block on
-                dB[c] = j <= limB ? dB[c] * scale : -INFINITY;
+                dA[c] = (j <= limA && j >= loA) ? dA[c] * scale : -INFINITY;
+                dB[c] = (j <= limB && j >= loB) ? dB[c] * scale : -INFINITY;
                 nmA = fmaxf(nmA, dA[c]);
                 nmB = fmaxf(nmB, dB[c]);
             }
-            const float cA = __expf(mA - nmA), cB = __expf(mB - nmB);
+            // a row may have seen no key yet (its window starts later, or it lies past T): its maximum is still -inf
+            const float cA = mA == -INFINITY ? 0.f : __expf(mA - nmA), cB = mB == -INFINITY ? 0.f : __expf(mB - nmB);
             mA = nmA; mB = nmB;
             float pA[4], pB[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) { pA[c] = __expf(dA[c] - nmA); pB[c] = __expf(dB[c] - nmB); }
+            for (int c = 0; c < 4; ++c) {
+                pA[c] = dA[c] == -INFINITY ? 0.f : __expf(dA[c] - nmA);
+                pB[c] = dB[c] == -INFINITY ? 0.f : __expf(dB[c] - nmB);
+            }
             sA = sA * cA + ((pA[0] + pA[1]) + (pA[2] + pA[3]));
             sB = sB * cB + ((pB[0] + pB[1]) + (pB[2] + pB[3]));
 #pragma unroll
@@ -136,9 +143,11 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 using namespace ckb;
 
 // q, out [H][T][ad]; k, v [Hkv][kv_stride_tokens][ad]; causal != 0: token i sees keys 0 .. i, else all T keys.
-extern "C" int ckb200_dev_attention_prefill(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int num_tokens,
-                                            int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal, void *stream)
+extern "C" int ckb200_dev_attention_prefill_window(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads,
+                                                   int num_tokens, int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal,
+                                                   int sliding_window, void *stream)
 {
+    const int window = causal && sliding_window > 0 ? sliding_window : 0;
     if (!q || !k || !v || !out) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || kv_stride_tokens < num_tokens) return 0;      // the reference returns silently
     if (head_dim <= 0 || aligned_head_dim < head_dim) return 0;
@@ -155,8 +164,17 @@ extern "C" int ckb200_dev_attention_prefill(const float *q, const float *k, cons
     const float scale = 1.0f / sqrtf((float)head_dim);
     cudaStream_t st = ckb_stream(stream);
     if (aligned_head_dim == 64)
-        attn_prefill_kernel<64><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal);
+        attn_prefill_kernel<64><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal,
+                                                             window);
     else
-        attn_prefill_kernel<128><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal);
+        attn_prefill_kernel<128><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal,
+                                                              window);
     return ckb_check_launch("attn_prefill");
+}
+
+extern "C" int ckb200_dev_attention_prefill(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int num_tokens,
+                                            int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal, void *stream)
+{
+    return ckb200_dev_attention_prefill_window(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, causal, 0,
+                                               stream);
 }

@@ -171,6 +171,14 @@ int ckb200_dev_attention_decode_f16cache_ws(const float *q, const uint16_t *k_ca
  * others are refused with CKB_ERR_SHAPE. */
 int ckb200_dev_attention_prefill(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads,
                                  int num_tokens, int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal, void *stream);
+/* The same with a sliding window (src/kernels/attention_kernels_sliding.c:450-600): with causal != 0 and sliding_window > 0
+ * token i sees keys max(0, i - sliding_window + 1) .. i; decode: the query sees the last min(kv_tokens, sliding_window) rows. */
+int ckb200_dev_attention_prefill_window(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads,
+                                        int num_tokens, int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal,
+                                        int sliding_window, void *stream);
+int ckb200_dev_attention_decode_sliding(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
+                                        long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
+                                        int head_dim, int aligned_head_dim, int sliding_window, void *stream);
 
 /* kv_cache_store (src/kernels/kv_cache_kernels.c:111-129): k, v [Hkv][head_dim] -> cache[Hkv][max_seq][head_dim] at pos
  * (or at *pos_dev when given). */

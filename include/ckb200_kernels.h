@@ -90,6 +90,13 @@ void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const 
 void attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache, const float *v_cache,
                                                    float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
                                                    int cache_capacity, int head_dim, int aligned_head_dim);
+/* sliding-window attention: include/ckernel_engine.h:1259-1273, :1611-1623; src/kernels/attention_kernels_sliding.c:450-600 */
+void attention_forward_causal_head_major_gqa_flash_strided_sliding(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                   int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                   int kv_stride_tokens, int sliding_window);
+void attention_forward_decode_head_major_gqa_flash_sliding(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
+                                                           int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
+                                                           int aligned_head_dim, int sliding_window);
 /* fp16 KV cache: include/ckernel_engine.h:1232-1241, :1682-1690 */
 void attention_forward_decode_head_major_gqa_flash_f16cache(const float *q_token, const uint16_t *k_cache, const uint16_t *v_cache,
                                                             float *out_token, int num_heads, int num_kv_heads, int kv_tokens,

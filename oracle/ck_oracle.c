@@ -521,7 +521,7 @@ static void orc_flash_query(const float *q, const float *k, const float *v, int 
 }
 
 static void orc_attention_prefill(const float *q, const float *k, const float *v, float *output, int num_heads, int num_kv_heads, int num_tokens,
-                                  int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal)
+                                  int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal, int window)
 {
     if (!q || !k || !v || !output) return;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || kv_stride_tokens < num_tokens) return;
@@ -531,7 +531,11 @@ static void orc_attention_prefill(const float *q, const float *k, const float *v
         const int kvh = (int)((long long)h * num_kv_heads / num_heads);
         for (int i = 0; i < num_tokens; ++i) {
             const size_t row = ((size_t)h * num_tokens + i) * aligned_head_dim;
-            orc_flash_query(q + row, k + kvh * hs, v + kvh * hs, causal ? i + 1 : num_tokens, head_dim, aligned_head_dim, scale, output + row);
+            /* sliding window (src/kernels/attention_kernels_sliding.c:391-402): keys max(0, i - window + 1) .. i */
+            const int start = causal && window > 0 && i - window + 1 > 0 ? i - window + 1 : 0;
+            const size_t skip = (size_t)start * aligned_head_dim;
+            orc_flash_query(q + row, k + kvh * hs + skip, v + kvh * hs + skip, (causal ? i + 1 : num_tokens) - start, head_dim, aligned_head_dim, scale,
+                            output + row);
         }
     }
 }
@@ -540,14 +544,39 @@ void oracle_attention_forward_causal_head_major_gqa_flash_strided(const float *q
                                                                   int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
                                                                   int kv_stride_tokens)
 {
-    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 1);
+    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 1, 0);
 }
 
 void oracle_attention_forward_full_head_major_gqa_flash_strided(const float *q, const float *k, const float *v, float *output, int num_heads,
                                                                 int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
                                                                 int kv_stride_tokens)
 {
-    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 0);
+    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 0, 0);
+}
+
+void oracle_attention_forward_causal_head_major_gqa_flash_strided_sliding(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                          int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                          int kv_stride_tokens, int sliding_window)
+{
+    orc_attention_prefill(q, k, v, output, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, 1, sliding_window);
+}
+
+/* decode with a window (src/kernels/attention_kernels_sliding.c:528-600): the last min(kv_tokens, window) rows of every kv head */
+void oracle_attention_forward_decode_head_major_gqa_flash_sliding(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
+                                                                  int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
+                                                                  int aligned_head_dim, int sliding_window)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens <= 0 || kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    const int eff = sliding_window > 0 && sliding_window < kv_tokens ? sliding_window : kv_tokens;
+    const size_t hs = (size_t)cache_capacity * aligned_head_dim, skip = (size_t)(kv_tokens - eff) * aligned_head_dim;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    for (int h = 0; h < num_heads; ++h) {
+        const int kvh = (int)((long long)h * num_kv_heads / num_heads);
+        orc_flash_query(q_token + (size_t)h * aligned_head_dim, k_cache + kvh * hs + skip, v_cache + kvh * hs + skip, eff, head_dim, aligned_head_dim,
+                        scale, out_token + (size_t)h * aligned_head_dim);
+    }
 }
 
 /* ---- KV cache store (src/kernels/kv_cache_kernels.c:70-129) ---- */

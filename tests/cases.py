@@ -162,6 +162,26 @@ def attention_prefill(lib, prefix, q, k, v, hd: int, causal: bool = True) -> np.
     return out
 
 
+def attention_prefill_sliding(lib, prefix, q, k, v, hd: int, window: int) -> np.ndarray:
+    heads, tokens, ad = q.shape
+    kv_heads, stride, _ = k.shape
+    out = np.full((heads, tokens, ad), np.nan, dtype=np.float32)
+    fn(lib, prefix, "attention_forward_causal_head_major_gqa_flash_strided_sliding")(
+        fptr(q), fptr(k), fptr(v), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(hd), C.c_int(ad), C.c_int(stride),
+        C.c_int(window))
+    return out
+
+
+def attention_decode_sliding(lib, prefix, q, kc, vc, tokens: int, window: int) -> np.ndarray:
+    heads, d = q.shape
+    kv_heads, cap, _ = kc.shape
+    out = np.full((heads, d), np.nan, dtype=np.float32)
+    fn(lib, prefix, "attention_forward_decode_head_major_gqa_flash_sliding")(
+        fptr(q), fptr(kc), fptr(vc), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(cap), C.c_int(d), C.c_int(d),
+        C.c_int(window))
+    return out
+
+
 def attention_decode_f16cache(lib, prefix, q, kc16, vc16, tokens: int, hd: int | None = None) -> np.ndarray:
     """kc16, vc16: uint16 arrays [Hkv][cap][ad] holding IEEE halves."""
     heads, d = q.shape

@@ -374,6 +374,25 @@ def test_attention_prefill(ck, orc, heads, kvh, ad, hd, tokens, stride, causal):
     assert np.all(got[:, :, hd:] == 0)
 
 
+@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,stride,window", [(32, 8, 128, 128, 300, 300, 64), (14, 2, 64, 64, 100, 128, 1), (8, 4, 64, 40, 70, 70, 33),
+                                                                   (8, 2, 128, 128, 90, 96, 17), (4, 4, 64, 64, 50, 50, 0), (6, 2, 64, 64, 40, 40, 1000)])
+def test_attention_prefill_sliding_window(ck, orc, heads, kvh, ad, hd, tokens, stride, window):
+    """Sliding-window prefill: windows of one key, windows that end inside a key tile, windows wider than the prompt, and no window."""
+    q, k, v = cases.prefill_attention_inputs(tokens + window, heads, kvh, ad, hd, tokens, stride)
+    want = cases.attention_prefill_sliding(orc, "oracle_", q, k, v, hd, window)
+    got = cases.attention_prefill_sliding(ck, "", q, k, v, hd, window)
+    assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, float(np.max(np.abs(got - want)))
+
+
+@pytest.mark.parametrize("heads,kvh,d,tokens,cap,window", [(14, 2, 64, 1025, 2048, 512), (64, 8, 128, 4096, 4096, 1000), (8, 4, 64, 64, 64, 1),
+                                                           (8, 4, 64, 20, 32, 0), (6, 2, 128, 77, 80, 500)])
+def test_attention_decode_sliding_window(ck, orc, heads, kvh, d, tokens, cap, window):
+    q, kc, vc = cases.attention_inputs(tokens + window, heads, kvh, d, tokens, cap)
+    want = cases.attention_decode_sliding(orc, "oracle_", q, kc, vc, tokens, window)
+    got = cases.attention_decode_sliding(ck, "", q, kc, vc, tokens, window)
+    assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, float(np.max(np.abs(got - want)))
+
+
 def test_attention_prefill_refuses_unsupported_shapes(ck):
     """Head sizes and group sizes outside the kernel are refused loudly, the output stays untouched."""
     q, k, v = cases.prefill_attention_inputs(1, 12, 4, 96, 96, 8, 8)

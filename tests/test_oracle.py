@@ -191,3 +191,16 @@ def test_oracle_vs_reference_f16_kv_cache(ref, orc, heads, kvh, d, tokens, cap):
     a = cases.attention_decode_f16cache(ref, "", q, kc16, vc16, tokens)
     b = cases.attention_decode_f16cache(orc, "oracle_", q, kc16, vc16, tokens)
     assert float(np.max(np.abs(a - b))) < 1e-5
+
+
+@pytest.mark.parametrize("window", [0, 1, 7, 32, 1000])
+def test_oracle_vs_reference_sliding_window(ref, orc, window):
+    """Sliding-window prefill and decode attention against the reference build (a window of 0 means no limit)."""
+    q, k, v = cases.prefill_attention_inputs(window + 3, 8, 4, 64, 64, 70, 80)
+    a = cases.attention_prefill_sliding(ref, "", q, k, v, 64, window)
+    b = cases.attention_prefill_sliding(orc, "oracle_", q, k, v, 64, window)
+    assert float(np.max(np.abs(a - b))) < 1e-5
+    qd, kc, vc = cases.attention_inputs(window + 5, 14, 2, 64, 333, 400)
+    a = cases.attention_decode_sliding(ref, "", qd, kc, vc, 333, window)
+    b = cases.attention_decode_sliding(orc, "oracle_", qd, kc, vc, 333, window)
+    assert float(np.max(np.abs(a - b))) < 1e-5

@@ -294,11 +294,13 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     sp = C.c_void_p(stream.cuda_stream)
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(max(0, args.streams - 1))]
 
-    fmts = ["q4_k"] + (["q6_k", "q8_0"] if args.detail else [])
-    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_planar_q8_0}
+    fmts = ["q4_k"] + (["q6_k", "q8_0", "q5_0"] if args.detail else [])
+    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_planar_q8_0,
+                "q5_0": lib.ckb200_dev_gemv_q5_0_q8_0}
     lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
     lib.ckb200_q8_0_planar_bytes.restype = C.c_size_t
-    quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0}
+    quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0,
+                 "q5_0": lib.ckb200_dev_quantize_q8_0}
 
     results = {}
     host_w = {}
@@ -322,7 +324,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             for c in range(copies):
                 wbuf[c * slot:c * slot + nbytes].copy_(src)
             x = torch.from_numpy(synth.make_x(k, seed=rank, k_valid=k_raw if k_raw != k else None)).to(dev)
-            xq = torch.empty(synth.row_bytes("q8_0" if fmt == "q8_0" else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
+            xq = torch.empty(synth.row_bytes("q8_0" if fmt in ("q8_0", "q5_0") else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
             y = torch.empty(copies, m, dtype=torch.float32, device=dev)
             rc = quant_dev[fmt](C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, sp)
             assert rc == 0

@@ -15,6 +15,7 @@ constexpr int QK8_0 = 32;
 constexpr int Q4K_BYTES = 144;   // fp16 d, fp16 dmin, 12 packed scale bytes, 128 nibble bytes
 constexpr int Q6K_BYTES = 210;   // 128 ql, 64 qh, 16 int8 scales, fp16 d
 constexpr int Q80_BYTES = 34;    // fp16 d, 32 int8
+constexpr int Q50_BYTES = 22;    // fp16 d, 4 bytes of fifth bits, 16 nibble bytes (block_q5_0)
 constexpr int Q8K_BYTES = 292;   // fp32 d, 256 int8, 16 int16 bsums
 
 // Device-side error word (one per library).  A kernel that gives up on a bounded wait

@@ -44,3 +44,10 @@ extern "C" int ckb200_dev_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, con
 {
     return gemm_nt_by_rows(ckb200_dev_gemv_q8_0_q8_0, (size_t)(K / 32) * ckb::Q80_BYTES, A_q8, B, bias, C, M, N, K, stream);
 }
+
+// gemm_nt_q5_0_q8_0 (src/kernels/gemm_kernels_q5_0.c:1725-1752): one GEMV per token, as the reference
+extern "C" int ckb200_dev_gemv_q5_0_q8_0(float *, const void *, const void *, int, int, void *);
+extern "C" int ckb200_dev_gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
+{
+    return gemm_nt_by_rows(ckb200_dev_gemv_q5_0_q8_0, (size_t)(K / 32) * ckb::Q80_BYTES, A_q8, B, bias, C, M, N, K, stream);
+}

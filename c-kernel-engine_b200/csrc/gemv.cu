@@ -25,6 +25,7 @@ template <int FMT> struct FmtTraits;
 template <> struct FmtTraits<FMT_Q4K> { static constexpr int BS = Q4K_BYTES, UPB = 4, HP = 1; };
 template <> struct FmtTraits<FMT_Q6K> { static constexpr int BS = Q6K_BYTES, UPB = 4, HP = 2; };
 template <> struct FmtTraits<FMT_Q80> { static constexpr int BS = Q80_BYTES, UPB = 1, HP = 0; };
+template <> struct FmtTraits<FMT_Q50> { static constexpr int BS = Q50_BYTES, UPB = 1, HP = 0; };
 
 struct XView {           // repacked activations in shared memory (either layout)
     XQ8K k;              // Q8_K view (Q4_K / Q6_K weights)
@@ -35,7 +36,7 @@ template <int FMT>
 __device__ __forceinline__ XView load_x(const uint8_t *xg, int nb, uint8_t *smem)
 {
     XView v;
-    if constexpr (FMT == FMT_Q80) {
+    if constexpr (FMT == FMT_Q80 || FMT == FMT_Q50) {
         v.q80 = load_x_q80(xg, nb, smem);
         v.k.q = v.k.d = v.k.bs = 0;
     } else {
@@ -47,8 +48,31 @@ __device__ __forceinline__ XView load_x(const uint8_t *xg, int nb, uint8_t *smem
 
 __host__ __device__ inline int x_smem_bytes(int fmt, int nb)
 {
-    const int raw = fmt == FMT_Q80 ? xq80_smem_bytes(nb) : xq8k_smem_bytes(nb, fmt == FMT_Q4K ? 1 : 2);
+    const int raw = (fmt == FMT_Q80 || fmt == FMT_Q50) ? xq80_smem_bytes(nb) : xq8k_smem_bytes(nb, fmt == FMT_Q4K ? 1 : 2);
     return (raw + 127) & ~127;
+}
+
+// One block_q5_0 against one Q8_0 activation block (vec_dot_q5_0_q8_0_ref, src/kernels/gemm_kernels_q5_0.c:901-939): element j
+// (j < 16) is the low nibble of qs[j] with bit j of qh as its fifth bit, element j + 16 the high nibble with bit j + 16, both
+// minus 16; int32 dot with the activation bytes, times d_w * d_x.  Four bits of qh are spread to bit 4 of four bytes with
+// one multiply (t * 0x00204081 puts bit i of t at bit 8 i), and v - 16 becomes a signed byte without borrows between bytes.
+__device__ __forceinline__ uint32_t q50_s8x4(uint32_t nibbles, uint32_t qh_bits4)
+{
+    const uint32_t v = nibbles | ((((qh_bits4 & 15u) * 0x00204081u) & 0x01010101u) << 4);      // 0 .. 31 per byte
+    return ((v | 0x80808080u) - 0x10101010u) ^ 0x80808080u;                                    // v - 16 as int8
+}
+__device__ __forceinline__ float q50_unit(uint32_t dbits, uint32_t qh, const uint4 &qs, uint32_t xa)
+{
+    const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 16);
+    const float xd = __uint_as_float(lds_u32(xa + 32));
+    const uint32_t w[4] = {qs.x, qs.y, qs.z, qs.w}, xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s = dp4a_ss(q50_s8x4(w[i] & 0x0F0F0F0Fu, qh >> (4 * i)), xl[i], s);
+        s = dp4a_ss(q50_s8x4((w[i] >> 4) & 0x0F0F0F0Fu, qh >> (16 + 4 * i)), xh[i], s);
+    }
+    return (float)s * (half_bits_to_float(dbits) * xd);
 }
 
 // ---- one unit from GLOBAL memory: block pointer p (Q4_K: 16-byte aligned; others 2-byte), unit u of block b
@@ -71,6 +95,9 @@ __device__ __forceinline__ float unit_from_global(const uint8_t *p, int b, int u
         const uint32_t d = ldg_nc_u16(p + 208);
         const Q6kX xr = q6k_load_x(x.k, b, n, h);
         return q6k_unit(ql_a, ql_b, qh, s0, s1, s2, s3, d, xr);
+    } else if constexpr (FMT == FMT_Q50) {
+        const uint32_t d = ldg_nc_u16(p), qh = ldg_nc_u16(p + 2) | (ldg_nc_u16(p + 4) << 16);
+        return q50_unit(d, qh, ldg_u4_align2(p + 6), x.q80 + 48u * b);
     } else {
         const uint32_t d = ldg_nc_u16(p);
         const uint4 w0 = ldg_u4_align2(p + 2), w1 = ldg_u4_align2(p + 18);
@@ -104,6 +131,9 @@ __device__ __forceinline__ float unit_from_shared(uint32_t a, int b, int u, cons
         const uint32_t d = lds_u16(a + 208);
         const Q6kX xr = q6k_load_x(x.k, b, n, h);
         return q6k_unit(ql_a, ql_b, qh, s0, s1, s2, s3, d, xr);
+    } else if constexpr (FMT == FMT_Q50) {
+        const uint32_t d = lds_u16(a), qh = lds_u16(a + 2) | (lds_u16(a + 4) << 16);
+        return q50_unit(d, qh, lds_u4_align2(a + 6), x.q80 + 48u * b);
     } else {
         const uint32_t d = lds_u16(a);
         const uint4 w0 = lds_u4_align2(a + 2), w1 = lds_u4_align2(a + 18);
@@ -541,4 +571,20 @@ extern "C" int ckb200_dev_gemv_q8_0_q8_0(float *y, const void *W, const void *xq
     if (v == 0) v = (((uintptr_t)W & 15) || (nb <= 32 && M > 32768)) ? 2 : 1;
     if (v == 1) return launch_ring<FMT_Q80>(y, W, xq, M, nb, st);
     return launch_direct_generic<FMT_Q80>(y, W, xq, M, nb, st);
+}
+
+// gemv_q5_0_q8_0 (src/kernels/gemm_kernels_q5_0.c:1637-1651): Q5_0 weights (22-byte blocks), Q8_0 activations
+extern "C" int ckb200_dev_gemv_q5_0_q8_0(float *y, const void *W, const void *xq, int M, int K, void *stream)
+{
+    const int c = check_common("gemv_q5_0_q8_0", y, W, xq, M, K, QK8_0);
+    if (c) return c == 1 ? 0 : CKB_ERR_SHAPE;
+    if (((uintptr_t)W & 1) || ((uintptr_t)xq & 1))
+        return ckb_fail(CKB_ERR_ALIGN, "gemv_q5_0_q8_0: W and x_q8 must be 2-byte aligned");
+    const int nb = K / QK8_0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    cudaStream_t st = ckb_stream(stream);
+    int v = ckb_tune_get("gemv_q5_0", 0);
+    if (v == 0) v = (((uintptr_t)W & 15) || (nb <= 32 && M > 32768)) ? 2 : 1;
+    if (v == 1) return launch_ring<FMT_Q50>(y, W, xq, M, nb, st);
+    return launch_direct_generic<FMT_Q50>(y, W, xq, M, nb, st);
 }

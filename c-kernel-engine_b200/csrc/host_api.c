@@ -23,17 +23,18 @@
 #define Q80_B 34
 #define Q8K_B 292
 
-enum { F_Q4K = 0, F_Q6K = 1, F_Q80 = 2 };
+enum { F_Q4K = 0, F_Q6K = 1, F_Q80 = 2, F_Q50 = 3 };     /* F_Q50: Q5_0 weights (22-byte blocks) with Q8_0 activations */
 
 static size_t w_row_bytes(int fmt, int K)
 {
     switch (fmt) {
         case F_Q4K: return (size_t)(K / 256) * Q4K_B;
         case F_Q6K: return (size_t)(K / 256) * Q6K_B;
+        case F_Q50: return (size_t)(K / 32) * 22;
         default: return (size_t)(K / 32) * Q80_B;
     }
 }
-static size_t xq_bytes(int fmt, int K) { return fmt == F_Q80 ? (size_t)(K / 32) * Q80_B : (size_t)(K / 256) * Q8K_B; }
+static size_t xq_bytes(int fmt, int K) { return (fmt == F_Q80 || fmt == F_Q50) ? (size_t)(K / 32) * Q80_B : (size_t)(K / 256) * Q8K_B; }
 
 /* ------------------------------------------------------------------ quantisers */
 
@@ -64,6 +65,7 @@ static int dev_gemv(int fmt, float *y, const void *W, const void *xq, int M, int
     switch (fmt) {
         case F_Q4K: return ckb200_dev_gemv_q4_k_q8_k(y, W, xq, M, K, NULL);
         case F_Q6K: return ckb200_dev_gemv_q6_k_q8_k(y, W, xq, M, K, NULL);
+        case F_Q50: return ckb200_dev_gemv_q5_0_q8_0(y, W, xq, M, K, NULL);
         default: return ckb200_dev_gemv_q8_0_q8_0(y, W, xq, M, K, NULL);
     }
 }
@@ -126,6 +128,18 @@ void vec_dot_q6_k_q8_k(int n, float *s, const void *vx, const void *vy)
     if (!s || !vx || !vy || n <= 0) return;
     host_gemv(F_Q6K, s, vx, vy, 1, n);
 }
+/* Q5_0 x Q8_0 (src/kernels/gemm_kernels_q5_0.c:901-939, :1602-1720): the reference has no plain _parallel form for this pair */
+void gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K) { host_gemv(F_Q50, y, W, x_q8, M, K); }
+void gemv_q5_0_q8_0_parallel_simd(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth)
+{ host_gemv_part(F_Q50, y, W, x_q8, M, K, ith, nth); }
+void gemv_q5_0_q8_0_parallel_dispatch(float *y, const void *W, const void *x_q8, int M, int K) { host_gemv(F_Q50, y, W, x_q8, M, K); }
+void vec_dot_q5_0_q8_0(int n, float *s, const void *vx, const void *vy)
+{
+    if (!s || !vx || !vy || n <= 0) return;
+    host_gemv(F_Q50, s, vx, vy, 1, n);
+}
+void vec_dot_q5_0_q8_0_ref(int n, float *s, const void *vx, const void *vy) { vec_dot_q5_0_q8_0(n, s, vx, vy); }
+
 void vec_dot_q8_0_q8_0(int n, float *s, const void *vx, const void *vy)
 {
     if (!s || !vx || !vy || n <= 0) return;
@@ -156,6 +170,7 @@ static void host_gemm_nt(int fmt, const void *A_q8, const void *B, const float *
     switch (fmt) {
         case F_Q4K: rc = ckb200_dev_gemm_nt_q4_k_q8_k(dA, dB, dbias, dC, M, N, K, NULL); break;
         case F_Q6K: rc = ckb200_dev_gemm_nt_q6_k_q8_k(dA, dB, dbias, dC, M, N, K, NULL); break;
+        case F_Q50: rc = ckb200_dev_gemm_nt_q5_0_q8_0(dA, dB, dbias, dC, M, N, K, NULL); break;
         default: rc = ckb200_dev_gemm_nt_q8_0_q8_0(dA, dB, dbias, dC, M, N, K, NULL); break;
     }
     if (rc != 0) return;
@@ -165,6 +180,7 @@ static void host_gemm_nt(int fmt, const void *A_q8, const void *B, const float *
 void gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q4K, A_q8, B, bias, C, M, N, K); }
 void gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q6K, A_q8, B, bias, C, M, N, K); }
 void gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q80, A_q8, B, bias, C, M, N, K); }
+void gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q50, A_q8, B, bias, C, M, N, K); }
 void gemm_nt_q6_k_q8_k_parallel_dispatch(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q6K, A_q8, B, bias, C, M, N, K); }
 void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K) { host_gemm_nt(F_Q80, A_q8, B, bias, C, M, N, K); }
 void gemm_q4_k_q8_k(float *Y, const void *W, const void *X_q8, int M, int N, int K) { host_gemm_nt(F_Q4K, X_q8, W, NULL, Y, N, M, K); }

@@ -5,7 +5,7 @@
 
 namespace ckb {
 
-enum Fmt : int { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2 };
+enum Fmt : int { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2, FMT_Q50 = 3 };   // Q5_0 weights take Q8_0 activations, like Q8_0
 
 // Q8_K vector for Q6_K weights: q8 data in the HP = 2 padded layout, fp32 d per block, and per
 // (block, half n, l-half h) the four 16-element sums bsums[8n + 2t + h], t = 0..3, split as 128*hi + lo
@@ -16,7 +16,7 @@ struct RingX {
 
 __host__ __device__ inline int ringx_smem_bytes(int fmt, int nb)
 {
-    const int raw = fmt == FMT_Q80 ? nb * 48 : (fmt == FMT_Q6K ? nb * (20 * 16 + 4 + 32) : nb * (18 * 16 + 4 + 32));
+    const int raw = (fmt == FMT_Q80 || fmt == FMT_Q50) ? nb * 48 : (fmt == FMT_Q6K ? nb * (20 * 16 + 4 + 32) : nb * (18 * 16 + 4 + 32));
     return (raw + 127) & ~127;
 }
 
@@ -25,7 +25,7 @@ template <int FMT>
 __device__ __forceinline__ RingX ring_stage_x(const uint8_t *xg, int nb, uint8_t *smem)
 {
     RingX r;
-    if constexpr (FMT == FMT_Q80) {
+    if constexpr (FMT == FMT_Q80 || FMT == FMT_Q50) {
         const int total = nb * 17;
         for (int base = 0; base < total; base += 8 * blockDim.x) {
             uint32_t v[8];

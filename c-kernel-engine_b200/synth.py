@@ -18,8 +18,8 @@ import numpy as np
 
 QK_K = 256
 QK8_0 = 32
-BLOCK_BYTES = {"q4_k": 144, "q6_k": 210, "q8_0": 34, "q8_k": 292}
-BLOCK_ELEMS = {"q4_k": 256, "q6_k": 256, "q8_0": 32, "q8_k": 256}
+BLOCK_BYTES = {"q4_k": 144, "q6_k": 210, "q8_0": 34, "q8_k": 292, "q5_0": 22}
+BLOCK_ELEMS = {"q4_k": 256, "q6_k": 256, "q8_0": 32, "q8_k": 256, "q5_0": 32}
 
 
 def row_bytes(fmt: str, k: int) -> int:
@@ -32,7 +32,7 @@ def gemv_bytes(fmt: str, m: int, k: int, act: str = "q8") -> int:
     """Algorithmic bytes of one GEMV: weights + activation vector + fp32 outputs."""
     if act == "f32":
         xb = 4 * k
-    elif fmt == "q8_0":
+    elif fmt in ("q8_0", "q5_0"):
         xb = row_bytes("q8_0", k)
     else:
         xb = row_bytes("q8_k", k)
@@ -67,7 +67,16 @@ def make_q8_0(rng: np.random.Generator, rows: int, k: int) -> np.ndarray:
     return out.reshape(-1)
 
 
-MAKERS = {"q4_k": make_q4_k, "q6_k": make_q6_k, "q8_0": make_q8_0}
+def make_q5_0(rng: np.random.Generator, rows: int, k: int) -> np.ndarray:
+    """block_q5_0: fp16 d ~ U(0, 0.02), 4 bytes of fifth bits, 16 nibble bytes, all uniform random."""
+    nb = rows * (k // QK8_0)
+    out = np.empty((nb, 22), dtype=np.uint8)
+    out[:, 0:2] = rng.uniform(0.0, 0.02, nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    out[:, 2:22] = rng.integers(0, 256, (nb, 20), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+MAKERS = {"q4_k": make_q4_k, "q6_k": make_q6_k, "q8_0": make_q8_0, "q5_0": make_q5_0}
 
 
 def make_weights(fmt: str, rows: int, k: int, seed: int = 0) -> np.ndarray:
@@ -90,6 +99,6 @@ SWEEP_SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336), (151936, 896)]
 
 
 def k_for(fmt: str, k: int) -> int:
-    if fmt == "q8_0":
+    if fmt in ("q8_0", "q5_0"):
         return k
     return ((k + QK_K - 1) // QK_K) * QK_K

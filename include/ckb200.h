@@ -91,6 +91,11 @@ int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n_elements, 
 /* gemm_nt_q4_k_q8_k (src/kernels/gemm_kernels_q4k_q8k.c:301-326), gemm_nt_q6_k_q8_k
  * (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268), gemm_nt_q8_0_q8_0 (src/kernels/gemm_batch_int8.c:87-120):
  * C[M,N] = A_q8[M,K] . B[N,K]^T + bias[N] (bias may be NULL). */
+/* Q5_0 weights (block_q5_0, include/ckernel_quant.h:70-74: fp16 d, 4 bytes of fifth bits, 16 nibble bytes = 22 B per 32) with
+ * Q8_0 activations: gemv_q5_0_q8_0 / gemm_nt_q5_0_q8_0 (src/kernels/gemm_kernels_q5_0.c:1637-1651, :1725-1752); the int32 block
+ * sums are exact, fp32 accumulation in block order. */
+int ckb200_dev_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+int ckb200_dev_gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
 int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
 int ckb200_dev_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
 int ckb200_dev_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);

@@ -90,6 +90,14 @@ void gemm_nt_q8_0_q8_0_parallel_dispatch(const void *A_q8, const void *B, const 
 void attention_forward_decode_head_major_gqa_flash(const float *q_token, const float *k_cache, const float *v_cache,
                                                    float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
                                                    int cache_capacity, int head_dim, int aligned_head_dim);
+/* Q5_0 x Q8_0: src/kernels/gemm_kernels_q5_0.c:901-939 (vec_dot), :1637-1720 (gemv), :1725-1752 (gemm_nt);
+ *      version/v7/src/ck_parallel_decode.h (the _parallel_dispatch seam) */
+void gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q5_0_q8_0_parallel_simd(float *y, const void *W, const void *x_q8, int M, int K, int ith, int nth);
+void gemv_q5_0_q8_0_parallel_dispatch(float *y, const void *W, const void *x_q8, int M, int K);
+void vec_dot_q5_0_q8_0(int n, float *s, const void *vx, const void *vy);
+void vec_dot_q5_0_q8_0_ref(int n, float *s, const void *vx, const void *vy);
+void gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
 /* sliding-window attention: include/ckernel_engine.h:1259-1273, :1611-1623; src/kernels/attention_kernels_sliding.c:450-600 */
 void attention_forward_causal_head_major_gqa_flash_strided_sliding(const float *q, const float *k, const float *v, float *output, int num_heads,
                                                                    int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,

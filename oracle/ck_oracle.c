@@ -490,6 +490,52 @@ void oracle_attention_forward_decode_head_major_gqa_flash(const float *q_token, 
     }
 }
 
+/* ---- Q5_0 x Q8_0 (src/kernels/gemm_kernels_q5_0.c:901-939 vec_dot, :1637-1651 gemv, :1725-1752 gemm_nt) ----
+ * block_q5_0 = { fp16 d; u8 qh[4]; u8 qs[16] } (include/ckernel_quant.h:70-74): element j < 16 is the low nibble of qs[j]
+ * with bit j of qh as bit 4, element j + 16 the high nibble with bit j + 16, both minus 16. */
+typedef struct { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; } orc_q5_0;
+typedef struct { uint16_t d; int8_t qs[32]; } orc_q8_0_blk;
+
+void oracle_vec_dot_q5_0_q8_0(int n, float *s, const void *vx, const void *vy)
+{
+    const orc_q5_0 *x = (const orc_q5_0 *)vx;
+    const orc_q8_0_blk *y = (const orc_q8_0_blk *)vy;
+    float sumf = 0.0f;
+    for (int ib = 0; ib < n / 32; ++ib) {
+        uint32_t qh;
+        memcpy(&qh, x[ib].qh, 4);
+        int sumi0 = 0, sumi1 = 0;
+        for (int j = 0; j < 16; ++j) {
+            const int x0 = (int)((x[ib].qs[j] & 15) | (((qh >> j) & 1u) << 4)) - 16;
+            const int x1 = (int)((x[ib].qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) - 16;
+            sumi0 += x0 * y[ib].qs[j];
+            sumi1 += x1 * y[ib].qs[j + 16];
+        }
+        sumf += (oracle_fp16_to_fp32(x[ib].d) * oracle_fp16_to_fp32(y[ib].d)) * (float)(sumi0 + sumi1);
+    }
+    *s = sumf;
+}
+
+void oracle_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    if (!y || !W || !x_q8 || M <= 0 || K <= 0) return;
+    const orc_q5_0 *w = (const orc_q5_0 *)W;
+    for (int r = 0; r < M; ++r) oracle_vec_dot_q5_0_q8_0(K, &y[r], w + (size_t)r * (K / 32), x_q8);
+}
+
+void oracle_gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A_q8 || !B || !C || M <= 0 || N <= 0 || K <= 0) return;
+    const orc_q5_0 *w = (const orc_q5_0 *)B;
+    const orc_q8_0_blk *a = (const orc_q8_0_blk *)A_q8;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float *out = &C[(size_t)m * N + n];
+            oracle_vec_dot_q5_0_q8_0(K, out, w + (size_t)n * (K / 32), a + (size_t)m * (K / 32));
+            if (bias) *out += bias[n];
+        }
+}
+
 /* ---- prefill attention (src/kernels/attention_kernels.c:2847-3005; per-query online softmax :1546-1602) ----
  * q, out [H][T][ad]; k, v [Hkv][kv_stride_tokens][ad]; query token i of head h sees keys 0 .. i (causal) or all T of
  * kv head h * Hkv / H; key by key: a new maximum rescales the running sum and output, otherwise exp(score - max). */

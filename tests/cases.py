@@ -84,12 +84,12 @@ def quantize_q8_0(lib, prefix, x: np.ndarray, rows: int = 1) -> np.ndarray:
 
 # ----------------------------------------------------------------------------- GEMV / GEMM
 
-GEMV_SYMBOL = {"q4_k": "gemv_q4_k_q8_k", "q6_k": "gemv_q6_k_q8_k", "q8_0": "gemv_q8_0_q8_0"}
-GEMM_NT_SYMBOL = {"q4_k": "gemm_nt_q4_k_q8_k", "q6_k": "gemm_nt_q6_k_q8_k", "q8_0": "gemm_nt_q8_0_q8_0"}
+GEMV_SYMBOL = {"q4_k": "gemv_q4_k_q8_k", "q6_k": "gemv_q6_k_q8_k", "q8_0": "gemv_q8_0_q8_0", "q5_0": "gemv_q5_0_q8_0"}
+GEMM_NT_SYMBOL = {"q4_k": "gemm_nt_q4_k_q8_k", "q6_k": "gemm_nt_q6_k_q8_k", "q8_0": "gemm_nt_q8_0_q8_0", "q5_0": "gemm_nt_q5_0_q8_0"}
 
 
 def quantize_act(lib, prefix, fmt: str, x: np.ndarray, rows: int = 1) -> np.ndarray:
-    return quantize_q8_0(lib, prefix, x, rows) if fmt == "q8_0" else quantize_q8_k(lib, prefix, x, rows)
+    return quantize_q8_0(lib, prefix, x, rows) if fmt in ("q8_0", "q5_0") else quantize_q8_k(lib, prefix, x, rows)
 
 
 def gemv(lib, prefix, fmt: str, w: np.ndarray, xq: np.ndarray, m: int, k: int, symbol: str | None = None) -> np.ndarray:

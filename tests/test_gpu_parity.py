@@ -352,6 +352,32 @@ def test_kv_cache_store_f16_bit_exact_then_attend(ck, orc):
     assert float(np.max(np.abs(a - b))) <= ATTN_ABS_TOL
 
 
+@pytest.mark.parametrize("m,k", [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (4100, 896), (151936, 896)])
+def test_gemv_q5_0_q8_0(ck, orc, m, k):
+    """Q5_0 weights (22-byte blocks, what GGUF Q4_K_M mixes use for K = 896 tensors) x Q8_0 activations, ring and direct kernels."""
+    w = synth.make_weights("q5_0", m, k, seed=m % 97)
+    xq = cases.quantize_q8_0(orc, "oracle_", synth.make_x(k, seed=k))
+    want = cases.gemv(orc, "oracle_", "q5_0", w, xq, m, k)
+    for variant in (0, 1, 2):
+        ck.ckb200_tune_set(b"gemv_q5_0", variant)
+        got = cases.gemv(ck, "", "q5_0", w, xq, m, k)
+        ck.ckb200_tune_set(b"gemv_q5_0", 0)
+        assert_fp32_close(got, want, f"q5_0 variant {variant}")
+
+
+def test_gemm_nt_and_vec_dot_q5_0(ck, orc):
+    m, n, k = 5, 17, 896
+    w = synth.make_weights("q5_0", n, k, seed=3)
+    a = synth.make_x(k, seed=4, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", "q5_0", a, rows=m)
+    bias = np.random.default_rng(5).standard_normal(n).astype(np.float32)
+    assert_fp32_close(cases.gemm_nt(ck, "", "q5_0", aq, w, bias, m, n, k), cases.gemm_nt(orc, "oracle_", "q5_0", aq, w, bias, m, n, k), "gemm_nt_q5_0")
+    s_g, s_o = np.zeros(1, np.float32), np.zeros(1, np.float32)
+    ck.vec_dot_q5_0_q8_0(C.c_int(k), cases.fptr(s_g), cases.vptr(w), cases.vptr(aq))
+    orc.oracle_vec_dot_q5_0_q8_0(C.c_int(k), cases.fptr(s_o), cases.vptr(w), cases.vptr(aq))
+    assert abs(float(s_g[0]) - float(s_o[0])) <= 1e-3 * max(1e-3, abs(float(s_o[0])))
+
+
 PREFILL_ATTN_CASES = [  # heads, kv_heads, ad, head_dim, tokens, kv stride, causal
     (32, 8, 128, 128, 512, 512, True),     # Llama-3-8B-shaped prefill
     (14, 2, 64, 64, 100, 128, True),       # Qwen2-0.5B heads: 7 query heads per kv head, strided cache

@@ -204,3 +204,18 @@ def test_oracle_vs_reference_sliding_window(ref, orc, window):
     a = cases.attention_decode_sliding(ref, "", qd, kc, vc, 333, window)
     b = cases.attention_decode_sliding(orc, "oracle_", qd, kc, vc, 333, window)
     assert float(np.max(np.abs(a - b))) < 1e-5
+
+
+@pytest.mark.parametrize("m,k", [(3, 32), (5, 896), (7, 4096), (64, 4864)])
+def test_oracle_vs_reference_q5_0(ref, orc, m, k):
+    """Q5_0 x Q8_0: the scalar restatement against the reference's dispatched GEMV (SIMD paths sum the same exact int32
+    block sums; fp32 order may differ) and bit for bit against its scalar vec_dot."""
+    w = synth.make_weights("q5_0", m, k, seed=m)
+    xq = cases.quantize_q8_0(ref, "", synth.make_x(k, seed=m))
+    a = cases.gemv(ref, "", "q5_0", w, xq, m, k)
+    b = cases.gemv(orc, "oracle_", "q5_0", w, xq, m, k)
+    assert _close(a, b, 1e-5)
+    s_ref, s_orc = np.zeros(1, np.float32), np.zeros(1, np.float32)
+    ref.vec_dot_q5_0_q8_0_ref(C.c_int(k), cases.fptr(s_ref), cases.vptr(w), cases.vptr(xq))
+    orc.oracle_vec_dot_q5_0_q8_0(C.c_int(k), cases.fptr(s_orc), cases.vptr(w), cases.vptr(xq))
+    assert s_ref[0] == s_orc[0]

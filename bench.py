@@ -296,9 +296,10 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
 
     fmts = ["q4_k"] + (["q6_k", "q8_0", "q5_0"] if args.detail else [])
     gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_planar_q8_0,
-                "q5_0": lib.ckb200_dev_gemv_q5_0_q8_0}
+                "q5_0": lib.ckb200_dev_gemv_q5_0_planar_q8_0}
     lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
     lib.ckb200_q8_0_planar_bytes.restype = C.c_size_t
+    lib.ckb200_q5_0_planar_bytes.restype = C.c_size_t
     quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0,
                  "q5_0": lib.ckb200_dev_quantize_q8_0}
 
@@ -312,9 +313,10 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             copies = max(2, -(-L2_BYTES_X4 // nbytes))
             slot = (nbytes + 255) & ~255
             src = torch.from_numpy(w_host).to(dev)
-            if fmt in ("q6_k", "q8_0"):                    # resident Q6_K / Q8_0 weights live in the library's row-planar layout (same bits)
-                size_fn, conv_fn = ((lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar) if fmt == "q6_k" else
-                                    (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar))
+            if fmt in ("q6_k", "q8_0", "q5_0"):            # resident Q6_K / Q8_0 / Q5_0 weights live in the library's row-planar layout (same bits)
+                size_fn, conv_fn = {"q6_k": (lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar),
+                                    "q8_0": (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar),
+                                    "q5_0": (lib.ckb200_q5_0_planar_bytes, lib.ckb200_dev_q5_0_to_planar)}[fmt]
                 nbytes = size_fn(m, k)
                 slot = (nbytes + 255) & ~255
                 planar = torch.empty(nbytes, dtype=torch.uint8, device=dev)

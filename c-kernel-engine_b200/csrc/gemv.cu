@@ -52,29 +52,6 @@ __host__ __device__ inline int x_smem_bytes(int fmt, int nb)
     return (raw + 127) & ~127;
 }
 
-// One block_q5_0 against one Q8_0 activation block (vec_dot_q5_0_q8_0_ref, src/kernels/gemm_kernels_q5_0.c:901-939): element j
-// (j < 16) is the low nibble of qs[j] with bit j of qh as its fifth bit, element j + 16 the high nibble with bit j + 16, both
-// minus 16; int32 dot with the activation bytes, times d_w * d_x.  Four bits of qh are spread to bit 4 of four bytes with
-// one multiply (t * 0x00204081 puts bit i of t at bit 8 i), and v - 16 becomes a signed byte without borrows between bytes.
-__device__ __forceinline__ uint32_t q50_s8x4(uint32_t nibbles, uint32_t qh_bits4)
-{
-    const uint32_t v = nibbles | ((((qh_bits4 & 15u) * 0x00204081u) & 0x01010101u) << 4);      // 0 .. 31 per byte
-    return ((v | 0x80808080u) - 0x10101010u) ^ 0x80808080u;                                    // v - 16 as int8
-}
-__device__ __forceinline__ float q50_unit(uint32_t dbits, uint32_t qh, const uint4 &qs, uint32_t xa)
-{
-    const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 16);
-    const float xd = __uint_as_float(lds_u32(xa + 32));
-    const uint32_t w[4] = {qs.x, qs.y, qs.z, qs.w}, xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
-    int s = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        s = dp4a_ss(q50_s8x4(w[i] & 0x0F0F0F0Fu, qh >> (4 * i)), xl[i], s);
-        s = dp4a_ss(q50_s8x4((w[i] >> 4) & 0x0F0F0F0Fu, qh >> (16 + 4 * i)), xh[i], s);
-    }
-    return (float)s * (half_bits_to_float(dbits) * xd);
-}
-
 // ---- one unit from GLOBAL memory: block pointer p (Q4_K: 16-byte aligned; others 2-byte), unit u of block b
 template <int FMT>
 __device__ __forceinline__ float unit_from_global(const uint8_t *p, int b, int u, const XView &x)

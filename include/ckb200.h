@@ -95,6 +95,11 @@ int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n_elements, 
  * Q8_0 activations: gemv_q5_0_q8_0 / gemm_nt_q5_0_q8_0 (src/kernels/gemm_kernels_q5_0.c:1637-1651, :1725-1752); the int32 block
  * sums are exact, fp32 accumulation in block order. */
 int ckb200_dev_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+/* Resident Q5_0 weights in a row-planar layout (all nibble bytes | all fifth-bit words | all d, rows padded to 16 B; the same
+ * bits, aligned loads): size, conversion from the reference's rows, and the GEMV over it. */
+size_t ckb200_q5_0_planar_bytes(int rows, int cols);
+int ckb200_dev_q5_0_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+int ckb200_dev_gemv_q5_0_planar_q8_0(float *y, const void *W_planar, const void *x_q8, int M, int K, void *stream);
 int ckb200_dev_gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
 int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
 int ckb200_dev_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);

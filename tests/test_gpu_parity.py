@@ -570,3 +570,22 @@ def test_gemv_q8_0_planar_layout(ck, orc, m, k):
     assert ck.ckb200_dev_gemv_q8_0_planar_q8_0(C.c_void_p(y.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(txq.data_ptr()), m, k, None) == 0
     assert ck.ckb200_synchronize() == 0
     assert_fp32_close(y.cpu().numpy(), want, f"q8_0 planar {m}x{k}")
+
+
+@pytest.mark.parametrize("m,k", [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (2, 28672), (4100, 896)])
+def test_gemv_q5_0_planar_layout(ck, orc, m, k):
+    import torch
+
+    dev = torch.device("cuda", 0)
+    w = synth.make_weights("q5_0", m, k, seed=m + k)
+    xq = cases.quantize_act(orc, "oracle_", "q5_0", synth.make_x(k, seed=m + k))
+    want = cases.gemv(orc, "oracle_", "q5_0", w, xq, m, k)
+    ck.ckb200_q5_0_planar_bytes.restype = C.c_size_t
+    raw, txq = torch.from_numpy(w).to(dev), torch.from_numpy(xq).to(dev)
+    planar = torch.full((ck.ckb200_q5_0_planar_bytes(m, k),), 0xAA, dtype=torch.uint8, device=dev)
+    y = torch.full((m,), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    assert ck.ckb200_dev_q5_0_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), m, k, None) == 0
+    assert ck.ckb200_dev_gemv_q5_0_planar_q8_0(C.c_void_p(y.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(txq.data_ptr()), m, k, None) == 0
+    assert ck.ckb200_synchronize() == 0
+    assert_fp32_close(y.cpu().numpy(), want, f"q5_0 planar {m}x{k}")

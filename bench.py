@@ -638,7 +638,7 @@ def run_prefill_only(args):
 
 def run_single(args):
     """A few plain (un-captured) launches of one GEMV on rotating weight copies: the small case for ncu captures.
-    FMT: q4_k, q6_k (ring kernel on the reference's rows), q6_k_planar, q8_0, q8_0_planar."""
+    FMT: q4_k, q6_k (ring kernel on the reference's rows), q6_k_planar, q8_0, q8_0_planar, q5_0, q5_0_planar."""
     import torch
 
     name, shape = args.single.split(":")
@@ -649,14 +649,16 @@ def run_single(args):
     assert lib.ckb200_init(0) == 0
     dev = torch.device("cuda", 0)
     gemv = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_q8_0,
-            "q6_k_planar": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0_planar": lib.ckb200_dev_gemv_q8_0_planar_q8_0}[name]
-    quant = lib.ckb200_dev_quantize_q8_0 if fmt == "q8_0" else lib.ckb200_dev_quantize_q8_k
+            "q6_k_planar": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0_planar": lib.ckb200_dev_gemv_q8_0_planar_q8_0,
+            "q5_0": lib.ckb200_dev_gemv_q5_0_q8_0, "q5_0_planar": lib.ckb200_dev_gemv_q5_0_planar_q8_0}[name]
+    quant = lib.ckb200_dev_quantize_q8_0 if fmt in ("q8_0", "q5_0") else lib.ckb200_dev_quantize_q8_k
     w_host = synth.make_weights(fmt, m, k, seed=1)
     src = torch.from_numpy(w_host).to(dev)
     nbytes = w_host.nbytes
     if planar:
-        size_fn, conv_fn = ((lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar) if fmt == "q6_k" else
-                            (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar))
+        size_fn, conv_fn = {"q6_k": (lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar),
+                            "q8_0": (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar),
+                            "q5_0": (lib.ckb200_q5_0_planar_bytes, lib.ckb200_dev_q5_0_to_planar)}[fmt]
         size_fn.restype = C.c_size_t
         nbytes = size_fn(m, k)
         dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -669,7 +671,7 @@ def run_single(args):
     for c in range(copies):
         wbuf[c * slot:c * slot + nbytes].copy_(src)
     x = torch.from_numpy(synth.make_x(k, seed=1)).to(dev)
-    xq = torch.empty(synth.row_bytes("q8_0" if fmt == "q8_0" else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
+    xq = torch.empty(synth.row_bytes("q8_0" if fmt in ("q8_0", "q5_0") else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
     y = torch.empty(copies, m, dtype=torch.float32, device=dev)
     torch.cuda.synchronize()
     assert quant(C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, None) == 0

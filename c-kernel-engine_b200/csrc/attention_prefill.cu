@@ -26,7 +26,7 @@ constexpr int AP_MAX_GROUP = 8;      // query heads per kv head on this path
 template <int AD>
 __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                            float *__restrict__ out, int H, int Hkv, int T, int head_dim, int kv_stride, int BT, float scale,
-                                                           int causal, int window)
+                                                           int causal, int window, int nsets)
 {
     extern __shared__ __align__(16) float4 ap_smem[];
     constexpr int P = AD / 4;        // float4 pieces per row
@@ -34,7 +34,11 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
     float4 *Ks = ap_smem, *Vs = ap_smem + AP_BK * P;
     // token blocks are dealt from the last (most keys under the causal mask) to the first: the long CTAs start first
     const int G = H / Hkv, kvh = blockIdx.y, t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BT;
-    const int l4 = threadIdx.x & 3, grp = threadIdx.x >> 2, npairs = BT >> 1;
+    // two key sets: the second half of the CTA's threads holds the same rows and takes every other block of four keys, which
+    // halves the serial chain of the longest (last) token block; the sets' partial results meet in shared memory at the end
+    // (nsets == 2; group sizes whose two sets would not fit 256 threads run one set)
+    const int rows_threads = (int)blockDim.x / nsets, ks = (int)threadIdx.x >= rows_threads ? 1 : 0, ltid = (int)threadIdx.x - ks * rows_threads;
+    const int l4 = ltid & 3, grp = ltid >> 2, npairs = BT >> 1;
     const int g = grp / npairs, a = grp - g * npairs;
     const int tokA = t0 + 2 * a, tokB = tokA + 1, h = kvh * G + g;
     const bool rowA = g < G && tokA < T, rowB = g < G && tokB < T;
@@ -74,7 +78,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
         }
         __syncthreads();
         // four keys at a time: eight independent dot products, one block-wise softmax update without branches
-        for (int jj = 0; jj < nk4; jj += 4) {
+        for (int jj = 4 * ks; jj < nk4; jj += 4 * nsets) {
             float dA[4] = {0.f, 0.f, 0.f, 0.f}, dB[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
@@ -123,6 +127,32 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
         }
     }
 
+    // merge the two key sets: set 1 parks (max, sum, accumulators) in shared memory, set 0 combines them with its own
+    if (nsets == 2) {
+    __syncthreads();
+    float4 *ms = ap_smem;                                              // [2 * NV + 1][rows_threads] float4
+    if (ks == 1) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) { ms[i * rows_threads + ltid] = oA[i]; ms[(NV + i) * rows_threads + ltid] = oB[i]; }
+        ms[2 * NV * rows_threads + ltid] = make_float4(mA, sA, mB, sB);
+    }
+    __syncthreads();
+    if (ks == 1) return;
+    {
+        const float4 o = ms[2 * NV * rows_threads + ltid];
+        const float nA = fmaxf(mA, o.x), nB = fmaxf(mB, o.z);
+        const float fA0 = mA == -INFINITY ? 0.f : __expf(mA - nA), fA1 = o.x == -INFINITY ? 0.f : __expf(o.x - nA);
+        const float fB0 = mB == -INFINITY ? 0.f : __expf(mB - nB), fB1 = o.z == -INFINITY ? 0.f : __expf(o.z - nB);
+        sA = sA * fA0 + o.y * fA1;
+        sB = sB * fB0 + o.w * fB1;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const float4 a = ms[i * rows_threads + ltid], b = ms[(NV + i) * rows_threads + ltid];
+            oA[i] = make_float4(oA[i].x * fA0 + a.x * fA1, oA[i].y * fA0 + a.y * fA1, oA[i].z * fA0 + a.z * fA1, oA[i].w * fA0 + a.w * fA1);
+            oB[i] = make_float4(oB[i].x * fB0 + b.x * fB1, oB[i].y * fB0 + b.y * fB1, oB[i].z * fB0 + b.z * fB1, oB[i].w * fB0 + b.w * fB1);
+        }
+    }
+    }
     const float iA = sA > 0.f ? 1.0f / sA : 0.f, iB = sB > 0.f ? 1.0f / sB : 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -157,18 +187,21 @@ extern "C" int ckb200_dev_attention_prefill_window(const float *q, const float *
         return ckb_fail(CKB_ERR_SHAPE, "attention prefill: %d heads / %d kv heads / head size %d is outside this kernel (groups <= %d, aligned head size 64 or 128)",
                         num_heads, num_kv_heads, aligned_head_dim, AP_MAX_GROUP);
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return ckb_fail(CKB_ERR_ALIGN, "attention prefill: pointers must be 16-byte aligned");
-    const int BT = G >= 4 ? 16 : (G >= 2 ? 32 : 64);                 // 2 * BT * G threads, a multiple of 32, at most 256
-    const int threads = 2 * BT * G;
+    // 2 * BT * G threads per key set (a multiple of 32); two key sets when both fit 256 threads
+    const int BT = G == 1 ? 64 : (G == 2 ? 32 : ((G == 6 || G == 8) ? 8 : 16));
+    const int nsets = 2 * (2 * BT * G) <= 256 ? 2 : 1;
+    const int threads = nsets * 2 * BT * G;
     const dim3 grid((num_tokens + BT - 1) / BT, num_kv_heads);
-    const size_t smem = 2 * (size_t)AP_BK * aligned_head_dim * sizeof(float);
+    const size_t tile_b = 2 * (size_t)AP_BK * aligned_head_dim * sizeof(float), merge_b = (size_t)(2 * (aligned_head_dim / 16) + 1) * (2 * BT * G) * 16;
+    const size_t smem = tile_b > merge_b ? tile_b : merge_b;
     const float scale = 1.0f / sqrtf((float)head_dim);
     cudaStream_t st = ckb_stream(stream);
     if (aligned_head_dim == 64)
         attn_prefill_kernel<64><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal,
-                                                             window);
+                                                             window, nsets);
     else
         attn_prefill_kernel<128><<<grid, threads, smem, st>>>(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, kv_stride_tokens, BT, scale, causal,
-                                                              window);
+                                                              window, nsets);
     return ckb_check_launch("attn_prefill");
 }
 

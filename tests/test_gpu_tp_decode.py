@@ -109,6 +109,8 @@ def test_tensor_parallel_decode(tmp_path, orc, world):
 
     if _gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    if world > 2 and os.environ.get("CKB200_TEST_TP4") != "1":
+        pytest.skip("the 4-rank case has not been run on hardware yet (no 4-GPU machine was available): set CKB200_TEST_TP4=1 to run it")
     cfg = TP_CFG if world == 2 else dict(TP_CFG, num_kv_heads=4)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

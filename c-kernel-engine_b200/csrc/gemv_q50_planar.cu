@@ -23,7 +23,7 @@ struct Q50pW { uint4 qs; uint32_t qh, d; };
 
 __device__ __forceinline__ float q50p_unit(const Q50pW &w, int b, const RingX &x)
 {
-    return q50_unit(w.d, w.qh, w.qs, x.q + 48u * b);
+    return q50_unit_presum(w.d, w.qh, w.qs, x.q + 48u * b);
 }
 
 template <int G, int R, int NW>
@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(NW * 32) gemv_q50p_kernel(const uint8_t *__res
 
     pdl_wait();
     const RingX x = ring_stage_x<FMT_Q80>(xg, nb, smem);
+    __syncthreads();
+    q50_store_xsums(x.q, nb);
     __syncthreads();
 
     float acc[R];

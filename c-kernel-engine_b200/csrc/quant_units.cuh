@@ -246,4 +246,37 @@ __device__ __forceinline__ float q50_unit(uint32_t dbits, uint32_t qh, const uin
     return (float)s * (half_bits_to_float(dbits) * xd);
 }
 
+// The same block with the -16 taken out of the bytes: sum (v - 16) x = sum nibble x + 16 sum fifth-bit x - 16 sum x, where
+// sum x of the activation block was stored once per CTA at byte 36 of the block's 48-byte slot (q50_store_xsums).  Nibbles
+// and spread fifth bits go into unsigned x signed dp4a as they are: about 6 integer instructions per 4 weights instead of 10.
+__device__ __forceinline__ float q50_unit_presum(uint32_t dbits, uint32_t qh, const uint4 &qs, uint32_t xa)
+{
+    const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 16);
+    const float xd = __uint_as_float(lds_u32(xa + 32));
+    const int xsum = (int)lds_u32(xa + 36);
+    const uint32_t w[4] = {qs.x, qs.y, qs.z, qs.w}, xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
+    int s = 0, hb = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s = dp4a_us(w[i] & 0x0F0F0F0Fu, xl[i], s);
+        s = dp4a_us((w[i] >> 4) & 0x0F0F0F0Fu, xh[i], s);
+        hb = dp4a_us((((qh >> (4 * i)) & 15u) * 0x00204081u) & 0x01010101u, xl[i], hb);
+        hb = dp4a_us((((qh >> (16 + 4 * i)) & 15u) * 0x00204081u) & 0x01010101u, xh[i], hb);
+    }
+    return (float)(s + 16 * (hb - xsum)) * (half_bits_to_float(dbits) * xd);
+}
+
+// one thread per activation block: the sum of its 32 bytes into the spare word of the slot (call between two __syncthreads)
+__device__ __forceinline__ void q50_store_xsums(uint32_t xq, int nb)
+{
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        const uint32_t xa = xq + 48u * b;
+        const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 16);
+        int t = 0;
+        t = dp4a_ss(0x01010101u, x0.x, t); t = dp4a_ss(0x01010101u, x0.y, t); t = dp4a_ss(0x01010101u, x0.z, t); t = dp4a_ss(0x01010101u, x0.w, t);
+        t = dp4a_ss(0x01010101u, x1.x, t); t = dp4a_ss(0x01010101u, x1.y, t); t = dp4a_ss(0x01010101u, x1.z, t); t = dp4a_ss(0x01010101u, x1.w, t);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(xa + 36), "r"(t) : "memory");
+    }
+}
+
 }  // namespace ckb

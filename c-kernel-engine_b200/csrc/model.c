@@ -34,7 +34,9 @@
 #include "launch.h"
 #include "runtime.h"
 
-enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2 };
+enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2, FMT_Q50 = 3 };
+/* formats with 32-element blocks take Q8_0 activations, the K-quants take Q8_K */
+static int fmt_block32(int fmt) { return fmt == FMT_Q80 || fmt == FMT_Q50; }
 
 typedef struct {
     void *w;            /* device pointer */
@@ -93,6 +95,7 @@ static size_t fmt_row_bytes(int fmt, int cols)
         case FMT_Q4K: return (size_t)(cols / 256) * 144;
         case FMT_Q6K: return (size_t)(cols / 256) * 210;
         case FMT_Q80: return (size_t)(cols / 32) * 34;
+        case FMT_Q50: return (size_t)(cols / 32) * 22;
         default: return (size_t)cols * 4;
     }
 }
@@ -107,7 +110,7 @@ static void tensor_plan(Tensor *t, int fmt, int rows, int cols, size_t *cursor)
     *cursor = align_up(*cursor + t->bytes + 32, 256);
 }
 
-static int cols_for(int fmt, int k) { return fmt == FMT_Q80 ? (k + 31) / 32 * 32 : round256(k); }
+static int cols_for(int fmt, int k) { return fmt_block32(fmt) ? (k + 31) / 32 * 32 : round256(k); }
 
 CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
 {
@@ -161,6 +164,18 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     tensor_plan(&m->lm_head, cfg->fmt_lm_head, m->Vl, cols_for(cfg->fmt_lm_head, m->D), &cur);
     if (cfg->tie_embeddings) m->emb = m->lm_head;
     else tensor_plan(&m->emb, cfg->fmt_embedding, cfg->vocab_size, cols_for(cfg->fmt_embedding, m->D), &cur);
+    {
+        /* every fmt_* field names a known block format; token embeddings have no Q5_0 row kernel */
+        const int fmts[] = { cfg->fmt_q, cfg->fmt_k, cfg->fmt_v, cfg->fmt_o, cfg->fmt_gate_up, cfg->fmt_down, cfg->fmt_lm_head, m->emb.fmt };
+        int bad = m->emb.fmt == FMT_Q50;
+        for (unsigned i = 0; i < sizeof fmts / sizeof fmts[0]; ++i) bad |= fmts[i] < FMT_Q4K || fmts[i] > FMT_Q50;
+        if (bad) {
+            ckb_fail(CKB_ERR_SHAPE, "model_create: unknown weight format, or Q5_0 for the token embedding");
+            free(m->layers);
+            free(m);
+            return NULL;
+        }
+    }
     m->arena_bytes = cur + 256;
     {
         size_t pc = 0;
@@ -304,7 +319,7 @@ int ckb200_model_upload_tensor(CKB200Model *m, int layer, int which, const void 
 static int fill_tensor(Tensor *t, unsigned long long seed)
 {
     if (t->fmt < 0) return ckb200_dev_fill_normal((float *)t->w, (long long)t->rows * t->cols, 1, seed, NULL);
-    const long long nblocks = (long long)t->rows * (t->cols / (t->fmt == FMT_Q80 ? 32 : 256));
+    const long long nblocks = (long long)t->rows * (t->cols / (fmt_block32(t->fmt) ? 32 : 256));
     return ckb200_dev_fill_blocks(t->w, nblocks, t->fmt, seed, NULL);
 }
 
@@ -397,6 +412,7 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
             /* few long rows: the ring kernel, which splits a row over warps, measured faster than the planar one */
             if (w->planar && !(w->rows <= 2048 && w->cols >= 4096)) return ckb200_dev_gemv_q6_k_planar_q8_k(y, w->planar, xq, w->rows, w->cols, st);
             return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
+        case FMT_Q50: return ckb200_dev_gemv_q5_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
         default: return ckb200_dev_gemv_q8_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
     }
 }
@@ -414,7 +430,7 @@ static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, 
                                           MODEL_GEMM_MIN_BATCH, st);
         if (rc >= 0) return rc;
     }
-    const size_t xrow = w->fmt == FMT_Q80 ? (size_t)(w->cols / 32) * 34 : (size_t)(w->cols / 256) * 292;
+    const size_t xrow = fmt_block32(w->fmt) ? (size_t)(w->cols / 32) * 34 : (size_t)(w->cols / 256) * 292;
     for (int b = 0; b < m->c.batch; ++b) {
         const int rc = gemv_q(w->fmt, y + (size_t)b * y_stride, w, xq + b * xrow, st);
         if (rc) return rc;
@@ -426,7 +442,7 @@ static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, 
 static int norm_quant(CKB200Model *m, const float *delta, const Tensor *gamma, const Tensor *consumer, void *st)
 {
     const int B = m->c.batch;
-    if (consumer->fmt != FMT_Q80)
+    if (!fmt_block32(consumer->fmt))
         return ckb200_dev_add_rmsnorm_q8k(m->x, delta, (const float *)gamma->w, m->hq, NULL, B, m->D, m->Da, m->c.rms_eps, st);
     /* Q8_0 consumer: unfused path through an fp32 row */
     int rc = 0;
@@ -443,7 +459,7 @@ static int norm_quant(CKB200Model *m, const float *delta, const Tensor *gamma, c
 static int quant_rows(const Tensor *consumer, const float *x, int x_stride, uint8_t *out, int rows, void *st)
 {
     int rc = 0;
-    if (consumer->fmt == FMT_Q80) {
+    if (fmt_block32(consumer->fmt)) {
         for (int b = 0; b < rows && !rc; ++b)
             rc = ckb200_dev_quantize_q8_0(x + (size_t)b * x_stride, out + (size_t)b * (consumer->cols / 32) * 34, 1, consumer->cols, st);
     } else if (x_stride == consumer->cols) {
@@ -467,7 +483,7 @@ static int reduce_partial(CKB200Model *m, float *buf, size_t count, void *st)
 static int reduce_norm_quant(CKB200Model *m, float *delta, const Tensor *gamma, const Tensor *consumer, void *st)
 {
     if (delta && m->c.tp_size > 1) {
-        if (m->tp_norm && consumer->fmt != FMT_Q80) {
+        if (m->tp_norm && !fmt_block32(consumer->fmt)) {
             const int rc = m->tp_norm(m->tp_norm_ctx, m->x, delta, (const float *)gamma->w, m->hq, m->c.batch, m->D, m->Da, m->c.rms_eps, st);
             if (rc != -1) return rc;
         }
@@ -511,7 +527,7 @@ static int issue_step(CKB200Model *m, void *st)
         Tensor *t = m->layers[l].t;
         float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + (size_t)B * m->kv_batch_stride;
         if ((rc = reduce_norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
-        if (t[CKB_T_WK].fmt != t[CKB_T_WQ].fmt && (t[CKB_T_WK].fmt == FMT_Q80 || t[CKB_T_WQ].fmt == FMT_Q80))
+        if (fmt_block32(t[CKB_T_WK].fmt) != fmt_block32(t[CKB_T_WQ].fmt) || fmt_block32(t[CKB_T_WV].fmt) != fmt_block32(t[CKB_T_WQ].fmt))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
         if (ckb_tune_get("model_qkv_streams", 1) && B < MODEL_GEMM_MIN_BATCH) {     /* the batched GEMMs share one workspace: keep them in order */
             cudaStream_t main_st = (cudaStream_t)st;
@@ -540,7 +556,7 @@ static int issue_step(CKB200Model *m, void *st)
         if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
         if ((rc = reduce_norm_quant(m, m->o, &t[CKB_T_LN2], &t[CKB_T_W1], st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_W1], m->hq, m->gu, 2 * m->Il, st))) return rc;
-        if (t[CKB_T_W2].fmt != FMT_Q80 && m->Il % 256 == 0) {
+        if (!fmt_block32(t[CKB_T_W2].fmt) && m->Il % 256 == 0) {
             if ((rc = ckb200_dev_swiglu_q8k(m->gu, m->mq, B, m->Il, st))) return rc;
         } else {
             /* swiglu to fp32 (reusing the front of gu is not safe: separate rows), then quantise */

@@ -148,7 +148,7 @@ __device__ __forceinline__ uint32_t mix32(uint64_t z)
 // fmt 0: Q4_K, 1: Q6_K, 2: Q8_0
 __global__ void fill_blocks_kernel(uint8_t *__restrict__ w, long long nblocks, int fmt, uint64_t seed)
 {
-    const int bs = fmt == 0 ? Q4K_BYTES : (fmt == 1 ? Q6K_BYTES : Q80_BYTES);
+    const int bs = fmt == 0 ? Q4K_BYTES : (fmt == 1 ? Q6K_BYTES : (fmt == 3 ? Q50_BYTES : Q80_BYTES));     // 3: block_q5_0
     for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (long long)gridDim.x * blockDim.x) {
         uint8_t *p = w + b * bs;
         const uint64_t base = seed * 0x100000001B3ull + (uint64_t)b * 64;
@@ -164,6 +164,8 @@ __global__ void fill_blocks_kernel(uint8_t *__restrict__ w, long long nblocks, i
         } else if (fmt == 1) {
             for (int i = 0; i < 16; ++i) p[192 + i] = (uint8_t)(int8_t)((int)(mix32(base + 2000 + i) & 63) - 32);
             *reinterpret_cast<unsigned short *>(p + 208) = __half_as_ushort(__float2half_rn(0.02f * u0));
+        } else if (fmt == 3) {
+            *reinterpret_cast<unsigned short *>(p) = __half_as_ushort(__float2half_rn(0.02f * u0));       // the other 20 bytes stay uniform random
         } else {
             *reinterpret_cast<unsigned short *>(p) = __half_as_ushort(__float2half_rn(0.01f * u0));
             for (int i = 0; i < 32; ++i) p[2 + i] = (uint8_t)(int8_t)((int)(mix32(base + 3000 + i) % 255u) - 127);

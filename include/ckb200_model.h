@@ -21,7 +21,7 @@ extern "C" {
 #endif
 
 /* weight block formats (values of the fmt_* fields) */
-enum { CKB_FMT_Q4_K = 0, CKB_FMT_Q6_K = 1, CKB_FMT_Q8_0 = 2 };
+enum { CKB_FMT_Q4_K = 0, CKB_FMT_Q6_K = 1, CKB_FMT_Q8_0 = 2, CKB_FMT_Q5_0 = 3 };   /* Q5_0: projections only (Q8_0 activations), not the down projection or the token embedding */
 
 /* per-layer tensors; the same order as the reference's layer weight list (ln1, wq, wk, wv, wo, ln2, w1, w2) */
 enum {

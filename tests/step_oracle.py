@@ -10,7 +10,7 @@ import numpy as np
 import cases
 
 synth = cases.synth
-FMT = {0: "q4_k", 1: "q6_k", 2: "q8_0"}
+FMT = {0: "q4_k", 1: "q6_k", 2: "q8_0", 3: "q5_0"}
 T = dict(LN1=0, WQ=1, WK=2, WV=3, WO=4, LN2=5, W1=6, W2=7, FINAL_GAMMA=100, LM_HEAD=101, EMBEDDING=102)
 
 
@@ -19,7 +19,7 @@ def round256(v):
 
 
 def cols_for(fmt, k):
-    return (k + 31) // 32 * 32 if fmt == 2 else round256(k)
+    return (k + 31) // 32 * 32 if fmt in (2, 3) else round256(k)
 
 
 class CpuModel:
@@ -142,7 +142,7 @@ def upload_whole_model(lib, handle, cpu: CpuModel, batch: int):
 
 # ----------------------------------------------------------------------------- tensor-parallel sharding
 
-BLOCK = {0: (256, 144), 1: (256, 210), 2: (32, 34)}     # fmt -> (elements, bytes) per block
+BLOCK = {0: (256, 144), 1: (256, 210), 2: (32, 34), 3: (32, 22)}     # fmt -> (elements, bytes) per block
 
 
 def _rows(w, r0, r1):

@@ -18,12 +18,19 @@ MINI_LLAMA = dict(embed_dim=512, num_heads=4, num_kv_heads=2, head_dim=128, inte
                   max_seq_len=64, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
 
 
+# hidden size 384 is not a multiple of 256: the projections that read it are Q5_0 (32-element blocks, Q8_0 activations), as in
+# GGUF Q4_K_M files of models like Qwen2-0.5B; the down projection (K = 768) stays a K-quant
+MINI_Q5_0 = dict(embed_dim=384, num_heads=6, num_kv_heads=2, head_dim=64, intermediate_size=768, num_layers=3, vocab_size=500,
+                 max_seq_len=96, rms_eps=1e-6, rope_theta=1.0e6, fmt_q=3, fmt_k=3, fmt_v=3, fmt_o=3, fmt_gate_up=3, fmt_down=1, fmt_lm_head=1)
+
+
 def cosine(a, b):
     a, b = a.astype(np.float64), b.astype(np.float64)
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
 
 
-@pytest.mark.parametrize("cfg,batch,use_graph", [(MINI_QWEN, 1, 1), (MINI_QWEN, 1, 0), (MINI_LLAMA, 2, 1), (MINI_LLAMA, 16, 1)])   # 16 sequences: tensor-core GEMMs
+@pytest.mark.parametrize("cfg,batch,use_graph", [(MINI_QWEN, 1, 1), (MINI_QWEN, 1, 0), (MINI_LLAMA, 2, 1), (MINI_LLAMA, 16, 1),
+                                                 (MINI_Q5_0, 1, 1), (MINI_Q5_0, 1, 0)])   # 16 sequences: tensor-core GEMMs
 def test_decode_steps_match_cpu_step(ck, orc, cfg, batch, use_graph):
     so.bind_model_api(ck)
     ck.ckb200_tune_set(b"model_graph", use_graph)

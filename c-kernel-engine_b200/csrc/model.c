@@ -43,7 +43,7 @@ typedef struct {
     size_t bytes;
     int fmt;            /* block format, or -1 for fp32 */
     int rows, cols;     /* [rows][cols] elements (cols already aligned) */
-    void *planar;       /* Q6_K matrices that feed a GEMV: second copy in the row-planar layout (aligned 16-byte loads), or NULL */
+    void *planar;       /* Q6_K / Q5_0 matrices that feed a GEMV: second copy in the row-planar layout (aligned 16-byte loads), or NULL */
 } Tensor;
 
 typedef struct {
@@ -189,9 +189,10 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
                 list[n++] = &m->lm_head;
             }
             for (int i = 0; i < n; ++i) {
-                if (list[i]->fmt != FMT_Q6K) continue;
+                if (list[i]->fmt != FMT_Q6K && list[i]->fmt != FMT_Q50) continue;
                 list[i]->planar = (void *)(uintptr_t)(pc + 1);      /* offset + 1 for now (0 = none) */
-                pc = align_up(pc + ckb200_q6_k_planar_bytes(list[i]->rows, list[i]->cols), 256);
+                pc = align_up(pc + (list[i]->fmt == FMT_Q6K ? ckb200_q6_k_planar_bytes(list[i]->rows, list[i]->cols)
+                                                            : ckb200_q5_0_planar_bytes(list[i]->rows, list[i]->cols)), 256);
             }
         }
         m->planar_bytes = pc;
@@ -412,7 +413,9 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
             /* few long rows: the ring kernel, which splits a row over warps, measured faster than the planar one */
             if (w->planar && !(w->rows <= 2048 && w->cols >= 4096)) return ckb200_dev_gemv_q6_k_planar_q8_k(y, w->planar, xq, w->rows, w->cols, st);
             return ckb200_dev_gemv_q6_k_q8_k(y, w->w, xq, w->rows, w->cols, st);
-        case FMT_Q50: return ckb200_dev_gemv_q5_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
+        case FMT_Q50:
+            if (w->planar) return ckb200_dev_gemv_q5_0_planar_q8_0(y, w->planar, xq, w->rows, w->cols, st);
+            return ckb200_dev_gemv_q5_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
         default: return ckb200_dev_gemv_q8_0_q8_0(y, w->w, xq, w->rows, w->cols, st);
     }
 }
@@ -493,17 +496,21 @@ static int reduce_norm_quant(CKB200Model *m, float *delta, const Tensor *gamma, 
     return norm_quant(m, delta, gamma, consumer, st);
 }
 
-/* (Re)builds the row-planar copies of the Q6_K projection matrices from the uploaded rows; outside any capture. */
+/* (Re)builds the row-planar copies of the Q6_K and Q5_0 projection matrices from the uploaded rows; outside any capture. */
+static int tensor_to_planar(const Tensor *t, void *st)
+{
+    if (!t->planar) return 0;
+    return t->fmt == FMT_Q6K ? ckb200_dev_q6_k_to_planar(t->planar, t->w, t->rows, t->cols, st)
+                             : ckb200_dev_q5_0_to_planar(t->planar, t->w, t->rows, t->cols, st);
+}
+
 static int ensure_planar(CKB200Model *m, void *st)
 {
     if (m->planar_ready || !m->planar_bytes) return 0;
     int rc = 0;
     for (int l = 0; l < m->c.num_layers && !rc; ++l)
-        for (int i = 0; i < CKB_T_PER_LAYER && !rc; ++i) {
-            const Tensor *t = &m->layers[l].t[i];
-            if (t->planar) rc = ckb200_dev_q6_k_to_planar(t->planar, t->w, t->rows, t->cols, st);
-        }
-    if (!rc && m->lm_head.planar) rc = ckb200_dev_q6_k_to_planar(m->lm_head.planar, m->lm_head.w, m->lm_head.rows, m->lm_head.cols, st);
+        for (int i = 0; i < CKB_T_PER_LAYER && !rc; ++i) rc = tensor_to_planar(&m->layers[l].t[i], st);
+    if (!rc) rc = tensor_to_planar(&m->lm_head, st);
     if (rc) return rc;
     if (ckb_check_cuda((int)cudaStreamSynchronize((cudaStream_t)st), "planar weights")) return CKB_ERR_CUDA;
     m->planar_ready = 1;

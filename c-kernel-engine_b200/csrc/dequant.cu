@@ -67,6 +67,7 @@ static int launch_dequant(const void *src, float *dst, size_t n, void *stream)
 extern "C" int ckb200_dev_dequant_q4_k_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q4K>(src, dst, n, stream); }
 extern "C" int ckb200_dev_dequant_q6_k_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q6K>(src, dst, n, stream); }
 extern "C" int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q80>(src, dst, n, stream); }
+extern "C" int ckb200_dev_dequant_q5_0_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q50>(src, dst, n, stream); }
 
 template <int FMT>
 static int launch_gemv_f32(float *y, const void *W, const float *x, int M, int K, void *stream)
@@ -82,6 +83,7 @@ static int launch_gemv_f32(float *y, const void *W, const float *x, int M, int K
 extern "C" int ckb200_dev_gemv_q4_k(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q4K>(y, W, x, M, K, stream); }
 extern "C" int ckb200_dev_gemv_q6_k(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q6K>(y, W, x, M, K, stream); }
 extern "C" int ckb200_dev_gemv_q8_0(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q80>(y, W, x, M, K, stream); }
+extern "C" int ckb200_dev_gemv_q5_0(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q50>(y, W, x, M, K, stream); }
 
 extern "C" int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void *stream)
 {

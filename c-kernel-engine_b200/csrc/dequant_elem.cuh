@@ -1,4 +1,4 @@
-// Element-wise dequantisation of the three weight formats (src/kernels/dequant_kernels.c:276-430):
+// Element-wise dequantisation of the weight formats (src/kernels/dequant_kernels.c:276-430):
 // the same rounding sequence as the reference (separate fp32 multiplies and subtraction, no FMA).
 #pragma once
 
@@ -6,7 +6,7 @@
 
 namespace ckb {
 
-enum { DQ_Q4K = 0, DQ_Q6K = 1, DQ_Q80 = 2 };
+enum { DQ_Q4K = 0, DQ_Q6K = 1, DQ_Q80 = 2, DQ_Q50 = 3 };
 
 __device__ __forceinline__ void q4k_scale_min(const uint8_t *s, int j, int &sc, int &mn)
 {
@@ -40,6 +40,12 @@ __device__ __forceinline__ float dequant_elem(const uint8_t *p, int e)
         const float d = half_bits_to_float(p[208] | (p[209] << 8));
         const int sc = (int)(int8_t)p[192 + (e >> 4)];
         return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+    } else if constexpr (FMT == DQ_Q50) {
+        // block_q5_0 (src/kernels/dequant_kernels.c:160-193): element j < 16: low nibble of qs[j] and bit j of qh; j + 16: high nibble, bit j + 16
+        const float d = half_bits_to_float(p[0] | (p[1] << 8));
+        const uint32_t qh = p[2] | (p[3] << 8) | (p[4] << 16) | ((uint32_t)p[5] << 24);
+        const int j = e & 15, nib = e < 16 ? (p[6 + j] & 15) : (p[6 + j] >> 4);
+        return __fmul_rn(d, (float)((nib | (int)(((qh >> e) & 1u) << 4)) - 16));
     } else {
         const float d = half_bits_to_float(p[0] | (p[1] << 8));
         return __fmul_rn(d, (float)(int8_t)p[2 + e]);
@@ -50,5 +56,6 @@ template <int FMT> struct DqTraits;
 template <> struct DqTraits<DQ_Q4K> { static constexpr int BS = Q4K_BYTES, BE = 256; };
 template <> struct DqTraits<DQ_Q6K> { static constexpr int BS = Q6K_BYTES, BE = 256; };
 template <> struct DqTraits<DQ_Q80> { static constexpr int BS = Q80_BYTES, BE = 32; };
+template <> struct DqTraits<DQ_Q50> { static constexpr int BS = Q50_BYTES, BE = 32; };
 
 }  // namespace ckb

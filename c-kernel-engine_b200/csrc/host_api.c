@@ -202,6 +202,7 @@ static void host_gemv_f32(int fmt, float *y, const void *W, const float *x, int 
     switch (fmt) {
         case F_Q4K: rc = ckb200_dev_gemv_q4_k(dY, dW, dX, M, K, NULL); break;
         case F_Q6K: rc = ckb200_dev_gemv_q6_k(dY, dW, dX, M, K, NULL); break;
+        case F_Q50: rc = ckb200_dev_gemv_q5_0(dY, dW, dX, M, K, NULL); break;
         default: rc = ckb200_dev_gemv_q8_0(dY, dW, dX, M, K, NULL); break;
     }
     if (rc != 0) return;
@@ -212,12 +213,15 @@ void gemv_q4_k(float *y, const void *W, const float *x, int M, int K) { host_gem
 void gemv_q6_k(float *y, const void *W, const float *x, int M, int K) { host_gemv_f32(F_Q6K, y, W, x, M, K); }
 void gemv_q8_0(float *y, const void *W, const float *x, int M, int K) { host_gemv_f32(F_Q80, y, W, x, M, K); }
 void gemv_q8_0_ref(float *y, const void *W, const float *x, int M, int K) { host_gemv_f32(F_Q80, y, W, x, M, K); }
+/* fp32-activation Q5_0 (src/kernels/gemm_kernels_q5_0.c:67-111, :550-567) */
+void gemv_q5_0(float *y, const void *W, const float *x, int M, int K) { host_gemv_f32(F_Q50, y, W, x, M, K); }
+void gemv_q5_0_ref(float *y, const void *W, const float *x, int M, int K) { host_gemv_f32(F_Q50, y, W, x, M, K); }
 
 static void host_dequant(int fmt, const void *src, float *dst, size_t n)
 {
     if (!src || !dst || n == 0) return;
     if (ckb_ensure_init()) return;
-    const size_t in_b = fmt == F_Q80 ? (n / 32) * Q80_B : (n / 256) * (fmt == F_Q4K ? Q4K_B : Q6K_B);
+    const size_t in_b = fmt == F_Q80 ? (n / 32) * Q80_B : (fmt == F_Q50 ? (n / 32) * 22 : (n / 256) * (fmt == F_Q4K ? Q4K_B : Q6K_B));
     const void *ds = ckb_stage_in(src, in_b, CKB_SLOT_W, 1);
     int back;
     float *dd = (float *)ckb_stage_out(dst, n * sizeof(float), CKB_SLOT_Y, &back);
@@ -226,6 +230,7 @@ static void host_dequant(int fmt, const void *src, float *dst, size_t n)
     switch (fmt) {
         case F_Q4K: rc = ckb200_dev_dequant_q4_k_row(ds, dd, n, NULL); break;
         case F_Q6K: rc = ckb200_dev_dequant_q6_k_row(ds, dd, n, NULL); break;
+        case F_Q50: rc = ckb200_dev_dequant_q5_0_row(ds, dd, n, NULL); break;
         default: rc = ckb200_dev_dequant_q8_0_row(ds, dd, n, NULL); break;
     }
     if (rc != 0) return;
@@ -235,6 +240,7 @@ static void host_dequant(int fmt, const void *src, float *dst, size_t n)
 void dequant_q4_k_row(const void *src, float *dst, size_t n_elements) { host_dequant(F_Q4K, src, dst, n_elements); }
 void dequant_q6_k_row(const void *src, float *dst, size_t n_elements) { host_dequant(F_Q6K, src, dst, n_elements); }
 void dequant_q8_0_row(const void *src, float *dst, size_t n_elements) { host_dequant(F_Q80, src, dst, n_elements); }
+void dequant_q5_0_row(const void *src, float *dst, size_t n_elements) { host_dequant(F_Q50, src, dst, n_elements); }   /* src/kernels/dequant_kernels.c:198-206 */
 
 /* ------------------------------------------------------------------ attention + KV cache */
 

@@ -95,6 +95,9 @@ int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n_elements, 
  * Q8_0 activations: gemv_q5_0_q8_0 / gemm_nt_q5_0_q8_0 (src/kernels/gemm_kernels_q5_0.c:1637-1651, :1725-1752); the int32 block
  * sums are exact, fp32 accumulation in block order. */
 int ckb200_dev_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+/* dequant_q5_0_row (src/kernels/dequant_kernels.c:198-206) and the fp32-activation gemv_q5_0 (src/kernels/gemm_kernels_q5_0.c:67-111) */
+int ckb200_dev_dequant_q5_0_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_gemv_q5_0(float *y, const void *W, const float *x, int M, int K, void *stream);
 /* Resident Q5_0 weights in a row-planar layout (all nibble bytes | all fifth-bit words | all d, rows padded to 16 B; the same
  * bits, aligned loads): size, conversion from the reference's rows, and the GEMV over it. */
 size_t ckb200_q5_0_planar_bytes(int rows, int cols);

@@ -98,6 +98,9 @@ void gemv_q5_0_q8_0_parallel_dispatch(float *y, const void *W, const void *x_q8,
 void vec_dot_q5_0_q8_0(int n, float *s, const void *vx, const void *vy);
 void vec_dot_q5_0_q8_0_ref(int n, float *s, const void *vx, const void *vy);
 void gemm_nt_q5_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemv_q5_0(float *y, const void *W, const float *x, int M, int K);          /* fp32 activations: src/kernels/gemm_kernels_q5_0.c:550-567 */
+void gemv_q5_0_ref(float *y, const void *W, const float *x, int M, int K);
+void dequant_q5_0_row(const void *src, float *dst, size_t n_elements);          /* src/kernels/dequant_kernels.c:198-206 */
 /* sliding-window attention: include/ckernel_engine.h:1259-1273, :1611-1623; src/kernels/attention_kernels_sliding.c:450-600 */
 void attention_forward_causal_head_major_gqa_flash_strided_sliding(const float *q, const float *k, const float *v, float *output, int num_heads,
                                                                    int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,

@@ -516,6 +516,42 @@ void oracle_vec_dot_q5_0_q8_0(int n, float *s, const void *vx, const void *vy)
     *s = sumf;
 }
 
+/* dequant_q5_0_row (src/kernels/dequant_kernels.c:160-206) and gemv_q5_0_ref (src/kernels/gemm_kernels_q5_0.c:67-111):
+ * weight = d * (q5 - 16); the GEMV adds d * q * x element by element in block order */
+void oracle_dequant_q5_0_row(const void *src, float *dst, size_t n)
+{
+    const orc_q5_0 *b = (const orc_q5_0 *)src;
+    for (size_t ib = 0; ib < n / 32; ++ib) {
+        const float d = oracle_fp16_to_fp32(b[ib].d);
+        uint32_t qh;
+        memcpy(&qh, b[ib].qh, 4);
+        for (int j = 0; j < 16; ++j) {
+            const int q0 = (int)((b[ib].qs[j] & 15) | (((qh >> j) & 1u) << 4)) - 16;
+            const int q1 = (int)((b[ib].qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) - 16;
+            dst[ib * 32 + j] = d * (float)q0;
+            dst[ib * 32 + j + 16] = d * (float)q1;
+        }
+    }
+}
+
+void oracle_gemv_q5_0(float *y, const void *W, const float *x, int M, int K)
+{
+    if (!y || !W || !x || M <= 0 || K <= 0) return;
+    const orc_q5_0 *w = (const orc_q5_0 *)W;
+    float tmp[32];
+    for (int r = 0; r < M; ++r) {
+        float sum = 0.0f;
+        for (int b = 0; b < K / 32; ++b) {
+            oracle_dequant_q5_0_row(&w[(size_t)r * (K / 32) + b], tmp, 32);
+            for (int j = 0; j < 16; ++j) {           /* the reference walks the packed bytes: elements j and j + 16 together */
+                sum += tmp[j] * x[b * 32 + j];
+                sum += tmp[j + 16] * x[b * 32 + j + 16];
+            }
+        }
+        y[r] = sum;
+    }
+}
+
 void oracle_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, int K)
 {
     if (!y || !W || !x_q8 || M <= 0 || K <= 0) return;

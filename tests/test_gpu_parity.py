@@ -365,6 +365,14 @@ def test_gemv_q5_0_q8_0(ck, orc, m, k):
         assert_fp32_close(got, want, f"q5_0 variant {variant}")
 
 
+def test_dequant_and_fp32_gemv_q5_0(ck, orc):
+    m, k = 37, 896
+    w = synth.make_weights("q5_0", m, k, seed=21)
+    assert np.array_equal(cases.dequant_row(ck, "", "q5_0", w, m * k), cases.dequant_row(orc, "oracle_", "q5_0", w, m * k))
+    x = synth.make_x(k, seed=22)
+    assert_fp32_close(cases.gemv_f32(ck, "", "q5_0", w, x, m, k), cases.gemv_f32(orc, "oracle_", "q5_0", w, x, m, k, "gemv_q5_0"), "gemv_q5_0 fp32")
+
+
 def test_gemm_nt_and_vec_dot_q5_0(ck, orc):
     m, n, k = 5, 17, 896
     w = synth.make_weights("q5_0", n, k, seed=3)

@@ -219,3 +219,13 @@ def test_oracle_vs_reference_q5_0(ref, orc, m, k):
     ref.vec_dot_q5_0_q8_0_ref(C.c_int(k), cases.fptr(s_ref), cases.vptr(w), cases.vptr(xq))
     orc.oracle_vec_dot_q5_0_q8_0(C.c_int(k), cases.fptr(s_orc), cases.vptr(w), cases.vptr(xq))
     assert s_ref[0] == s_orc[0]
+
+
+def test_oracle_vs_reference_q5_0_dequant_and_fp32_gemv(ref, orc):
+    m, k = 9, 896
+    w = synth.make_weights("q5_0", m, k, seed=11)
+    assert np.array_equal(cases.dequant_row(ref, "", "q5_0", w, m * k), cases.dequant_row(orc, "oracle_", "q5_0", w, m * k))
+    x = synth.make_x(k, seed=12)
+    a = cases.gemv_f32(ref, "", "q5_0", w, x, m, k, "gemv_q5_0_ref")
+    b = cases.gemv_f32(orc, "oracle_", "q5_0", w, x, m, k, "gemv_q5_0")
+    assert np.array_equal(a, b)

@@ -45,4 +45,35 @@ __device__ __forceinline__ void arq_norm_quant(float ss, const float *row, float
     }
 }
 
+// The same tail for a consumer with 32-element blocks (Q8_0 / Q5_0 weights): the first `cols` elements of the normalised row
+// (a multiple of 32) go to Q8_0 blocks with the arithmetic of quantize_row_q8_0 (src/kernels/gemm_kernels_q8_0.c:70-175;
+// quantize.cu): one warp per block, amax over the 32 lanes, d = amax / 127 as fp16, q = rint(x * (127 / amax)).
+__device__ __forceinline__ void arq_norm_quant_q80(float ss, const float *row, float *red, const float *__restrict__ gamma, uint8_t *__restrict__ out_q80,
+                                                   int t, int d_model, int cols, float eps)
+{
+    ss = group_sum<32>(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int w = 0; w < nw; ++w) tot += red[w];
+    const float mean = __fmul_rn(tot, __fdiv_rn(1.0f, (float)d_model));
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    const int nb = cols / 32;
+    for (int b = warp; b < nb; b += nw) {
+        const int i = b * 32 + lane;
+        const float v = i < d_model ? __fmul_rn(__fmul_rn(row[i], rstd), gamma[i]) : 0.0f;
+        float amax = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+        const int q = __float2int_rn(__fmul_rn(v, id));
+        const int qn = __shfl_down_sync(0xffffffffu, q, 1);
+        uint8_t *out = out_q80 + ((size_t)t * nb + b) * Q80_BYTES;
+        if (lane == 0) *reinterpret_cast<unsigned short *>(out) = __half_as_ushort(__float2half_rn(d));
+        if ((lane & 1) == 0) *reinterpret_cast<unsigned short *>(out + 2 + lane) = (unsigned short)((q & 255) | ((qn & 255) << 8));
+    }
+}
+
 }  // namespace ckb

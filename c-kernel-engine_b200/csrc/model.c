@@ -447,7 +447,9 @@ static int norm_quant(CKB200Model *m, const float *delta, const Tensor *gamma, c
     const int B = m->c.batch;
     if (!fmt_block32(consumer->fmt))
         return ckb200_dev_add_rmsnorm_q8k(m->x, delta, (const float *)gamma->w, m->hq, NULL, B, m->D, m->Da, m->c.rms_eps, st);
-    /* Q8_0 consumer: unfused path through an fp32 row */
+    if (ckb_tune_get("model_fused_norm_q80", 1))
+        return ckb200_dev_add_rmsnorm_q8_0(m->x, delta, (const float *)gamma->w, m->hq, B, m->D, m->Da, consumer->cols, m->c.rms_eps, st);
+    /* unfused path through an fp32 row (tune model_fused_norm_q80 = 0) */
     int rc = 0;
     if (delta) rc = ckb200_dev_add_inplace(m->x, delta, (long long)B * m->Da, st);
     if (!rc) rc = ckb200_dev_rmsnorm_forward(m->x, (const float *)gamma->w, m->o, NULL, B, m->D, m->Da, m->c.rms_eps, st);

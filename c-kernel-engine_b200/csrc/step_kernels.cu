@@ -60,6 +60,32 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict
     arq_norm_quant(ss, row, red, gamma, out_q8, norm_out, t, d_model, aligned, eps);
 }
 
+// add_rmsnorm_q8k for a consumer that takes Q8_0 activations (Q8_0 / Q5_0 weights): the same row kernel, Q8_0 blocks of the
+// first `cols` elements out
+__global__ void __launch_bounds__(1024) add_rmsnorm_q80_kernel(float *__restrict__ x, const float *__restrict__ delta, const float *__restrict__ gamma,
+                                                               uint8_t *__restrict__ out_q80, int d_model, int aligned, int cols, float eps)
+{
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float *xr = x + (size_t)t * aligned;
+    const float *dr = delta ? delta + (size_t)t * aligned : nullptr;
+    const int nv = aligned >> 2;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        float4 v = __ldcg(reinterpret_cast<const float4 *>(xr) + i);
+        if (dr) {
+            const float4 dv = __ldcg(reinterpret_cast<const float4 *>(dr) + i);
+            v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            reinterpret_cast<float4 *>(xr)[i] = v;
+        }
+        arq_keep_piece(v, i, d_model, row, ss);
+    }
+    arq_norm_quant_q80(ss, row, red, gamma, out_q80, t, d_model, cols, eps);
+}
+
 // one warp per 256-element block of the output: out = silu(gate) * up, quantised to Q8_K
 __global__ void __launch_bounds__(128) swiglu_q8k_kernel(const float *__restrict__ gate_up, uint8_t *__restrict__ out_q8, int tokens, int dim)
 {
@@ -210,6 +236,29 @@ extern "C" int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const fl
     }
     return launch_pdl("add_rmsnorm_q8k", add_rmsnorm_q8k_kernel, dim3(tokens), dim3(threads), smem, ckb_stream(stream), x, delta, gamma,
                       (uint8_t *)out_q8, norm_out, d_model, aligned_embed_dim, eps);
+}
+
+extern "C" int ckb200_dev_add_rmsnorm_q8_0(float *x, const float *delta, const float *gamma, void *out_q80, int tokens, int d_model,
+                                           int aligned_embed_dim, int cols, float eps, void *stream)
+{
+    if (!x || !gamma || !out_q80 || tokens <= 0 || d_model <= 0) return 0;
+    if (aligned_embed_dim % 4 || aligned_embed_dim < d_model || cols % 32 || cols > aligned_embed_dim || cols <= 0)
+        return ckb_fail(CKB_ERR_SHAPE, "add_rmsnorm_q8_0: widths %d / %d / %d", d_model, aligned_embed_dim, cols);
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    if ((((uintptr_t)x | (uintptr_t)delta) & 15) || ((uintptr_t)out_q80 & 1)) return ckb_fail(CKB_ERR_ALIGN, "add_rmsnorm_q8_0: x and delta must be 16-byte aligned");
+    int threads = (aligned_embed_dim / 4 + 31) & ~31;
+    if (threads > 1024) threads = 1024;
+    if (threads < 32) threads = 32;
+    const size_t smem = (size_t)aligned_embed_dim * sizeof(float);
+    if (smem > 48 * 1024) {
+        static size_t set = 0;
+        if (smem > set) {
+            if (ckb_check_cuda((int)cudaFuncSetAttribute(add_rmsnorm_q80_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr")) return CKB_ERR_CUDA;
+            set = smem;
+        }
+    }
+    return launch_pdl("add_rmsnorm_q80", add_rmsnorm_q80_kernel, dim3(tokens), dim3(threads), smem, ckb_stream(stream), x, delta, gamma, (uint8_t *)out_q80,
+                      d_model, aligned_embed_dim, cols, eps);
 }
 
 extern "C" int ckb200_dev_swiglu_q8k(const float *gate_up, void *out_q8, int tokens, int dim, void *stream)

@@ -220,6 +220,10 @@ int ckb200_dev_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, 
 /* ------------------------------------------------------------------ fused glue of a device-resident step
  * Each merges ops that the reference's generated decode function issues back to back
  * (version/v7/scripts/codegen_v7.py:569-931). */
+/* The same fusion for consumers with 32-element blocks (Q8_0 / Q5_0 weights): x[t] += delta[t]; Q8_0 blocks (quantize_row_q8_0,
+ * src/kernels/gemm_kernels_q8_0.c:70-175) of the first `cols` elements of rmsnorm(x[t]) * gamma, `cols` a multiple of 32. */
+int ckb200_dev_add_rmsnorm_q8_0(float *x, const float *delta, const float *gamma, void *out_q80, int tokens, int d_model,
+                                int aligned_embed_dim, int cols, float eps, void *stream);
 /* x += delta (delta may be NULL); out_q8 = quantize_row_q8_k(rmsnorm_forward(x)); norm_out (optional) = fp32 rows */
 int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const float *gamma, void *out_q8, float *norm_out, int tokens,
                                int d_model, int aligned_embed_dim, float eps, void *stream);

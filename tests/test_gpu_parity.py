@@ -597,3 +597,35 @@ def test_gemv_q5_0_planar_layout(ck, orc, m, k):
     assert ck.ckb200_dev_gemv_q5_0_planar_q8_0(C.c_void_p(y.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(txq.data_ptr()), m, k, None) == 0
     assert ck.ckb200_synchronize() == 0
     assert_fp32_close(y.cpu().numpy(), want, f"q5_0 planar {m}x{k}")
+
+
+@pytest.mark.parametrize("tokens,d_model,aligned,cols,with_delta", [(1, 896, 1024, 896, True), (3, 384, 512, 384, False), (2, 4096, 4096, 4096, True), (1, 100, 256, 128, True)])
+def test_add_rmsnorm_q8_0_matches_the_three_kernel_form(ck, tokens, d_model, aligned, cols, with_delta):
+    """Residual add + RMSNorm + Q8_0 quantisation in one kernel against add_inplace + rmsnorm_forward + quantize_q8_0 on the device:
+    the same bytes (and the same updated residual)."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(tokens + d_model)
+    x = np.zeros((tokens, aligned), np.float32); x[:, :d_model] = rng.standard_normal((tokens, d_model)).astype(np.float32)
+    dl = np.zeros_like(x); dl[:, :d_model] = rng.standard_normal((tokens, d_model)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(aligned)).astype(np.float32)
+    tg = torch.from_numpy(gamma).to(dev)
+    x1, x2, d1 = torch.from_numpy(x).to(dev), torch.from_numpy(x).to(dev), torch.from_numpy(dl).to(dev)
+    nbytes = tokens * (cols // 32) * 34
+    q1 = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    q2 = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    normed = torch.zeros(tokens, aligned, device=dev)
+    torch.cuda.synchronize()
+    dptr = C.c_void_p(d1.data_ptr()) if with_delta else None
+    assert ck.ckb200_dev_add_rmsnorm_q8_0(C.c_void_p(x1.data_ptr()), dptr, C.c_void_p(tg.data_ptr()), C.c_void_p(q1.data_ptr()), tokens, d_model, aligned, cols,
+                                          C.c_float(1e-6), None) == 0
+    if with_delta:
+        assert ck.ckb200_dev_add_inplace(C.c_void_p(x2.data_ptr()), C.c_void_p(d1.data_ptr()), C.c_longlong(tokens * aligned), None) == 0
+    assert ck.ckb200_dev_rmsnorm_forward(C.c_void_p(x2.data_ptr()), C.c_void_p(tg.data_ptr()), C.c_void_p(normed.data_ptr()), None, tokens, d_model, aligned,
+                                         C.c_float(1e-6), None) == 0
+    for t in range(tokens):
+        assert ck.ckb200_dev_quantize_q8_0(C.c_void_p(normed.data_ptr() + 4 * t * aligned), C.c_void_p(q2.data_ptr() + t * (cols // 32) * 34), 1, cols, None) == 0
+    assert ck.ckb200_synchronize() == 0
+    assert torch.equal(x1, x2)
+    assert torch.equal(q1, q2)

@@ -7,6 +7,7 @@
  * variable CKB200_MODEL (default "synthetic:mini") or from the path given to ck_model_load_weights().
  */
 #include <stdint.h>
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -90,9 +91,11 @@ CK_EXPORT void ck_model_decode(void *model, const int *token, int token_index)
 {
     Handle *h = (Handle *)model;
     if (!h || !token || token_index < 0) return;
-    if (ckb200_model_set_pos(h->m, token_index)) return;
+    /* the function is void: a failure (a position past the context, a device error) leaves NaN logits instead of the
+     * previous call's, and the reason in ckb200_last_error() */
     const int32_t t = *token;
-    ckb200_model_decode(h->m, &t, h->logits);
+    if (ckb200_model_set_pos(h->m, token_index) || ckb200_model_decode(h->m, &t, h->logits))
+        for (int i = 0; i < g_cfg.vocab_size; ++i) h->logits[i] = NAN;
 }
 
 CK_EXPORT void ck_model_forward(void *model, const int *tokens, int num_tokens)

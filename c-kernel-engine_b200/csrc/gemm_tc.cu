@@ -549,7 +549,7 @@ static int tc_pick_slices(int tiles, int nb, int slots)
 }
 
 template <int WF, int NT>
-static int launch_tc(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
+static int launch_tc(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, uint8_t *ws, size_t ws_bytes, cudaStream_t st)
 {
     using Cfg = TcCfg<NT>;
     auto kernel = gemm_kq_tc_kernel<WF, NT>;
@@ -569,7 +569,11 @@ static int launch_tc(const void *A_q8, const void *B, const float *bias, float *
     const int nbz = (nb + Z - 1) / Z;
     Z = (nb + nbz - 1) / nbz;                          // no empty slice
     const size_t xt_bytes = ((size_t)mtiles * nb * Cfg::XBLOB + 255) & ~(size_t)255, part_bytes = Z > 1 ? (size_t)Z * M * N * sizeof(float) : 0;
-    uint8_t *xt = (uint8_t *)ckb_scratch(CKB_SLOT_G, xt_bytes + part_bytes);
+    // A caller that records the launch in a CUDA graph brings its own workspace: the library's pool may be freed and
+    // regrown by any later call that needs more, which would leave a captured pointer dangling.
+    if (ws && xt_bytes + part_bytes > ws_bytes)
+        return ckb_fail(CKB_ERR_LIMIT, "gemm_kq_tc: the caller's workspace holds %zu bytes, this call needs %zu", ws_bytes, xt_bytes + part_bytes);
+    uint8_t *xt = ws ? ws : (uint8_t *)ckb_scratch(CKB_SLOT_G, xt_bytes + part_bytes);
     if (!xt) return CKB_ERR_CUDA;
     float *part = reinterpret_cast<float *>(xt + xt_bytes);
     gemm_x_tiles_kernel<NT><<<dim3(nb, mtiles), 256, 0, st>>>((const uint8_t *)A_q8, xt, M, nb);
@@ -594,15 +598,38 @@ extern "C" int ckb200_tc_trace(long long *out4096) { return (int)cudaMemcpyFromS
 // C[m * ldc + n] = A_q8[m] . W[n] (+ bias[n]).  wf: TC_W_Q4K (the reference's block_q4_K rows) or TC_W_Q6K_PLANAR.
 // Returns -1 when the shape is not handled here (caller falls back to the per-token path).  min_tokens: smallest M
 // worth the tensor-core path (the token tile is 128 wide; fewer tokens are padded with zeros).
+extern "C" int ckb_launch_gemm_tc_ws(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens,
+                                     void *ws, size_t ws_bytes, void *stream)
+{
+    if (M < min_tokens || K % QK_K || ((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3) || ((uintptr_t)ws & 255) || ckb_tune_get("gemm_tc", 1) == 0) return -1;
+    const int nb = K / QK_K;
+    cudaStream_t st = ckb_stream(stream);
+    uint8_t *w8 = (uint8_t *)ws;
+    if (M <= ckb_tune_get("gemm_tc_small_max", 64))     // batched decode: 32-token tiles, two CTAs per SM
+        return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 32>(A_q8, B, bias, C, ldc, M, N, nb, w8, ws_bytes, st)
+                                     : launch_tc<TC_W_Q4K, 32>(A_q8, B, bias, C, ldc, M, N, nb, w8, ws_bytes, st);
+    return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 128>(A_q8, B, bias, C, ldc, M, N, nb, w8, ws_bytes, st)
+                                 : launch_tc<TC_W_Q4K, 128>(A_q8, B, bias, C, ldc, M, N, nb, w8, ws_bytes, st);
+}
+
 extern "C" int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens,
                                   void *stream)
 {
-    if (M < min_tokens || K % QK_K || ((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3) || ckb_tune_get("gemm_tc", 1) == 0) return -1;
+    return ckb_launch_gemm_tc_ws(wf, A_q8, B, bias, C, ldc, M, N, K, min_tokens, NULL, 0, stream);
+}
+
+// Upper bound of the workspace one call with these sizes can need (activation tiles plus the partial sums of the largest
+// K split the launcher picks by itself), for callers that allocate it once.
+extern "C" size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || K % QK_K) return 0;
     const int nb = K / QK_K;
-    cudaStream_t st = ckb_stream(stream);
-    if (M <= ckb_tune_get("gemm_tc_small_max", 64))     // batched decode: 32-token tiles, two CTAs per SM
-        return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 32>(A_q8, B, bias, C, ldc, M, N, nb, st) : launch_tc<TC_W_Q4K, 32>(A_q8, B, bias, C, ldc, M, N, nb, st);
-    return wf == TC_W_Q6K_PLANAR ? launch_tc<TC_W_Q6K_PLANAR, 128>(A_q8, B, bias, C, ldc, M, N, nb, st) : launch_tc<TC_W_Q4K, 128>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    const size_t blob = TcCfg<32>::XBLOB > TcCfg<128>::XBLOB ? TcCfg<32>::XBLOB : TcCfg<128>::XBLOB;
+    const size_t mtiles = (size_t)(M + 31) / 32;
+    const size_t xt = (mtiles * nb * blob + 255) & ~(size_t)255;
+    int zmax = nb / 4 < 1 ? 1 : (nb / 4 > 16 ? 16 : nb / 4);
+    if (M > 128) zmax = 1;
+    return xt + (zmax > 1 ? (size_t)zmax * M * N * sizeof(float) : 0) + 256;
 }
 
 extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)

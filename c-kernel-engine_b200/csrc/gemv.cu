@@ -219,18 +219,8 @@ __device__ __forceinline__ float q6k_ring_unit(uint32_t a, int b, int u, const R
     const uint32_t dbits = lds_u16(a + 208);
     const uint32_t xa = x.q + (uint32_t)(b * 80 + (10 * n + h) * 4) * 4u;
     const uint4 x0 = lds_u4(xa), x1 = lds_u4(xa + 32), x2 = lds_u4(xa + 64), x3 = lds_u4(xa + 96);
-    int A1 = 0, A2 = 0, A3 = 0, A4 = 0, B1 = 0, B2 = 0, B3 = 0, B4 = 0;
-#define CKB_Q6_STEP(QA, QB, QH, X0, X1, X2, X3)                      \
-    A1 = dp4a_us((QA) & 0x0F0F0F0Fu, X0, A1); B1 = dp4a_us((QH) & 0x03030303u, X0, B1); \
-    A2 = dp4a_us((QB) & 0x0F0F0F0Fu, X1, A2); B2 = dp4a_us((QH) & 0x0C0C0C0Cu, X1, B2); \
-    A3 = dp4a_us((QA) & 0xF0F0F0F0u, X2, A3); B3 = dp4a_us((QH) & 0x30303030u, X2, B3); \
-    A4 = dp4a_us((QB) & 0xF0F0F0F0u, X3, A4); B4 = dp4a_us((QH) & 0xC0C0C0C0u, X3, B4);
-    CKB_Q6_STEP(qa.x, qb.x, qh.x, x0.x, x1.x, x2.x, x3.x)
-    CKB_Q6_STEP(qa.y, qb.y, qh.y, x0.y, x1.y, x2.y, x3.y)
-    CKB_Q6_STEP(qa.z, qb.z, qh.z, x0.z, x1.z, x2.z, x3.z)
-    CKB_Q6_STEP(qa.w, qb.w, qh.w, x0.w, x1.w, x2.w, x3.w)
-#undef CKB_Q6_STEP
-    const int S1 = A1 + 16 * B1, S2 = A2 + 4 * B2, S3 = (A3 >> 4) + B3, S4 = (A4 >> 4) + (B4 >> 2);   // all exact
+    int S1, S2, S3, S4;
+    q6k_plane_sums(qa, qb, qh, x0, x1, x2, x3, S1, S2, S3, S4);
     const uint32_t sc4 = __byte_perm(__byte_perm((uint32_t)s0, (uint32_t)s1, 0x0040), __byte_perm((uint32_t)s2, (uint32_t)s3, 0x0040), 0x5410);
     const uint32_t lo4 = lds_u32(x.lo + 4u * (b * 4 + u)), hi4 = lds_u32(x.hi + 4u * (b * 4 + u));
     const int center = dp4a_ss(sc4, lo4, 0) + 128 * dp4a_ss(sc4, hi4, 0);          // sum_t sc_t * bsum_t

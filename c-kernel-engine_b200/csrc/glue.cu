@@ -47,17 +47,43 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
         y[i] = i < d_model ? __fmul_rn(__fmul_rn(x[i], rstd), gamma[i]) : 0.0f;
 }
 
-__global__ void rope_cache_kernel(float *__restrict__ cos_cache, float *__restrict__ sin_cache, int max_seq, int head_dim, float base)
+// rows of rot_dim / 2 values; frequencies are spaced over rot_dim (head_dim for the split form); with lin_scale > 0 the
+// position is divided by it first (the reference's "linear" scaling, src/kernels/rope_kernels.c:270-316)
+__global__ void rope_cache_kernel(float *__restrict__ cos_cache, float *__restrict__ sin_cache, int max_seq, int rot_dim, float base, float lin_scale)
 {
-    const int half = head_dim / 2;
+    const int half = rot_dim / 2;
     const long long n = (long long)max_seq * half;
     const double lb = log((double)base);
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const int pos = (int)(i / half), j = (int)(i - (long long)pos * half);
-        const float freq = (float)exp(-((double)(2 * j) / (double)head_dim) * lb);
-        const float ang = __fmul_rn((float)pos, freq);
+        const float freq = (float)exp(-((double)(2 * j) / (double)rot_dim) * lb);
+        const float epos = lin_scale > 0.0f ? __fdiv_rn((float)pos, lin_scale) : (float)pos;
+        const float ang = __fmul_rn(epos, freq);
         cos_cache[i] = (float)cos((double)ang);
         sin_cache[i] = (float)sin((double)ang);
+    }
+}
+
+// x: [heads][tokens][ahd]; pairs (2i, 2i+1) of the first rot_dim elements are rotated with cos/sin rows of rot_dim / 2 values
+// (rope_forward_qk_pairwise_with_rotary_dim, src/kernels/rope_kernels.c:419-451, :839-866); the rest of the row is untouched
+__global__ void rope_pairwise_kernel(float *__restrict__ q, float *__restrict__ k, const float *__restrict__ cos_cache,
+                                     const float *__restrict__ sin_cache, int num_heads, int num_kv_heads, int tokens, int rot_dim, int ahd,
+                                     int pos_offset, const int *__restrict__ pos_dev)
+{
+    const int half = rot_dim / 2;
+    const int pos0 = pos_dev ? *pos_dev : pos_offset;
+    const long long n = (long long)(num_heads + num_kv_heads) * tokens * half;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % half);
+        const long long ht = i / half;
+        const int t = (int)(ht % tokens), h = (int)(ht / tokens);
+        float *row = h < num_heads ? q + ((size_t)h * tokens + t) * ahd : k + ((size_t)(h - num_heads) * tokens + t) * ahd;
+        const float c = cos_cache[(size_t)(pos0 + t) * half + j], s = sin_cache[(size_t)(pos0 + t) * half + j];
+        const float2 ab = *reinterpret_cast<const float2 *>(row + 2 * j);
+        float2 r;
+        r.x = __fsub_rn(__fmul_rn(ab.x, c), __fmul_rn(ab.y, s));
+        r.y = __fadd_rn(__fmul_rn(ab.x, s), __fmul_rn(ab.y, c));
+        *reinterpret_cast<float2 *>(row + 2 * j) = r;
     }
 }
 
@@ -178,8 +204,38 @@ extern "C" int ckb200_dev_rope_precompute_cache_split(float *cos_cache, float *s
     if (!cos_cache || !sin_cache || max_seq_len <= 0 || head_dim <= 1) return 0;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     const long long n = (long long)max_seq_len * (head_dim / 2);
-    rope_cache_kernel<<<grid_for(n, 256, 2048), 256, 0, ckb_stream(stream)>>>(cos_cache, sin_cache, max_seq_len, head_dim, base);
+    rope_cache_kernel<<<grid_for(n, 256, 2048), 256, 0, ckb_stream(stream)>>>(cos_cache, sin_cache, max_seq_len, head_dim, base, 0.0f);
     return ckb_check_launch("rope_precompute_cache_split");
+}
+
+// rope_precompute_cache (src/kernels/rope_kernels.c:270-316): rows of rotary_dim / 2 values, optional linear position scaling
+extern "C" int ckb200_dev_rope_precompute_cache(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base, int rotary_dim,
+                                                int linear_scaling, float scaling_factor, void *stream)
+{
+    if (!cos_cache || !sin_cache || max_seq_len <= 0 || head_dim <= 1) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    if (rotary_dim < 2) return 0;
+    const float lin = (linear_scaling && scaling_factor > 0.0f && scaling_factor != 1.0f) ? scaling_factor : 0.0f;
+    const long long n = (long long)max_seq_len * (rotary_dim / 2);
+    rope_cache_kernel<<<grid_for(n, 256, 2048), 256, 0, ckb_stream(stream)>>>(cos_cache, sin_cache, max_seq_len, rotary_dim, base, lin);
+    return ckb_check_launch("rope_precompute_cache");
+}
+
+// rope_forward_qk_pairwise_with_rotary_dim (src/kernels/rope_kernels.c:839-866): the interleaved (Llama) pairing
+extern "C" int ckb200_dev_rope_forward_qk_pairwise(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                                   int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                                   int rotary_dim, const int *pos_dev, void *stream)
+{
+    if (!q || !k || !cos_cache || !sin_cache || num_heads <= 0 || num_kv_heads < 0 || num_tokens <= 0 || head_dim <= 1) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    if (rotary_dim < 2) return 0;
+    if ((aligned_head_dim & 1) || (((uintptr_t)q | (uintptr_t)k) & 7)) return ckb_fail(CKB_ERR_ALIGN, "rope_forward_qk_pairwise: rows must be 8-byte aligned");
+    const long long n = (long long)(num_heads + num_kv_heads) * num_tokens * (rotary_dim / 2);
+    rope_pairwise_kernel<<<grid_for(n, 256, 2048), 256, 0, ckb_stream(stream)>>>(q, k, cos_cache, sin_cache, num_heads, num_kv_heads,
+                                                                               num_tokens, rotary_dim, aligned_head_dim, pos_offset, pos_dev);
+    return ckb_check_launch("rope_forward_qk_pairwise");
 }
 
 extern "C" int ckb200_dev_rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,

@@ -34,6 +34,13 @@
 #include "launch.h"
 #include "runtime.h"
 
+/* tensor-core GEMM of gemm_tc.cu: wf 0 = Q4_K rows, 1 = Q6_K row-planar; -1 when the shape is not handled.  The workspace
+ * (activation tiles + split-K partial sums) is the model's own: a pointer recorded in the step's graph must not come from
+ * the library's grow-on-demand pool, which any later call may free and regrow. */
+int ckb_launch_gemm_tc_ws(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *ws,
+                          size_t ws_bytes, void *stream);
+size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
+
 enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2, FMT_Q50 = 3 };
 /* formats with 32-element blocks take Q8_0 activations, the K-quants take Q8_K */
 static int fmt_block32(int fmt) { return fmt == FMT_Q80 || fmt == FMT_Q50; }
@@ -72,6 +79,9 @@ struct CKB200Model {
     uint8_t *hq, *aq, *mq;
     int32_t *tokens_dev, *pos_dev;
     int32_t *tokens_pinned;
+    int host_pos;           /* mirror of *pos_dev as of the last enqueued step (decode refuses to run past the context) */
+    uint8_t *gemm_ws;       /* workspace of the tensor-core GEMM of batched decode: the step's graph keeps this pointer */
+    size_t gemm_ws_bytes;
     int attn_splits;
     cudaGraphExec_t graph;
     int graph_ready;
@@ -221,6 +231,17 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     DEV_ALLOC(m->mq, (size_t)B * ((m->Il + 255) / 256) * 292 * 2 + 256);
     DEV_ALLOC(m->tokens_dev, (size_t)B * sizeof(int32_t));
     DEV_ALLOC(m->pos_dev, 256);
+    if (B >= 16) {
+        /* largest projection of the step (row counts and input widths as planned above) */
+        size_t need = 0;
+        const int shapes[][2] = { { m->Hl * m->d, m->Da }, { m->D, m->Ala }, { 2 * m->Il, m->Da }, { m->D, round256(m->Il) }, { m->Vl, m->Da } };
+        for (unsigned i = 0; i < sizeof shapes / sizeof shapes[0]; ++i) {
+            const size_t b = ckb_gemm_tc_workspace_bytes(B, shapes[i][0], shapes[i][1]);
+            if (b > need) need = b;
+        }
+        m->gemm_ws_bytes = need;
+        DEV_ALLOC(m->gemm_ws, need);
+    }
     m->attn_splits = ckb200_attention_decode_splits(B, m->Hkvl, S);
     {
         size_t sb = ckb200_attention_decode_scratch_bytes(B, m->Hl, m->d, m->attn_splits);
@@ -265,7 +286,7 @@ void ckb200_model_free(CKB200Model *m)
     cudaStreamSynchronize(ckb_stream(NULL));
     if (m->graph_ready) cudaGraphExecDestroy(m->graph);
     void *ptrs[] = { m->arena, m->planar_arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
-                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch };
+                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch, m->gemm_ws };
     for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     for (int i = 0; i < 2; ++i) {
@@ -314,6 +335,9 @@ int ckb200_model_upload_tensor(CKB200Model *m, int layer, int which, const void 
     if (!t || !host) return ckb_fail(CKB_ERR_STATE, "model_upload_tensor: no such tensor (%d, %d)", layer, which);
     if (bytes != t->bytes) return ckb_fail(CKB_ERR_SHAPE, "model_upload_tensor(%d, %d): got %zu bytes, tensor has %zu", layer, which, bytes, t->bytes);
     m->planar_ready = 0;               /* weights are read through fixed pointers: the captured graph stays valid */
+    /* Weights may only change while the stream is idle: queued steps still read them (the GEMVs even prefetch weights ahead
+     * of their dependency wait), and this copy runs outside the library's non-blocking stream. */
+    if (ckb_check_cuda((int)cudaStreamSynchronize(ckb_stream(NULL)), "upload tensor (drain)")) return CKB_ERR_CUDA;
     return ckb_check_cuda((int)cudaMemcpy(t->w, host, bytes, cudaMemcpyHostToDevice), "upload tensor");
 }
 
@@ -368,7 +392,9 @@ int ckb200_model_set_pos(CKB200Model *m, int pos)
     int32_t p = pos;
     cudaStream_t st = ckb_stream(NULL);
     if (ckb_check_cuda((int)cudaMemcpyAsync(m->pos_dev, &p, sizeof p, cudaMemcpyHostToDevice, st), "set pos")) return CKB_ERR_CUDA;
-    return ckb_check_cuda((int)cudaStreamSynchronize(st), "set pos");
+    if (ckb_check_cuda((int)cudaStreamSynchronize(st), "set pos")) return CKB_ERR_CUDA;
+    m->host_pos = pos;
+    return 0;
 }
 
 int ckb200_model_get_pos(CKB200Model *m)
@@ -420,8 +446,6 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
     }
 }
 
-/* tensor-core GEMM of gemm_tc.cu: wf 0 = Q4_K rows, 1 = Q6_K row-planar; -1 when the shape is not handled */
-int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *stream);
 #define MODEL_GEMM_MIN_BATCH 16
 
 /* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
@@ -429,8 +453,8 @@ static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, 
 {
     if (m->c.batch >= MODEL_GEMM_MIN_BATCH && (w->fmt == FMT_Q4K || (w->fmt == FMT_Q6K && w->planar))) {
         /* batched decode: the weights are streamed once for all sequences */
-        const int rc = ckb_launch_gemm_tc(w->fmt == FMT_Q6K, xq, w->fmt == FMT_Q6K ? w->planar : w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols,
-                                          MODEL_GEMM_MIN_BATCH, st);
+        const int rc = ckb_launch_gemm_tc_ws(w->fmt == FMT_Q6K, xq, w->fmt == FMT_Q6K ? w->planar : w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols,
+                                             MODEL_GEMM_MIN_BATCH, m->gemm_ws, m->gemm_ws_bytes, st);
         if (rc >= 0) return rc;
     }
     const size_t xrow = fmt_block32(w->fmt) ? (size_t)(w->cols / 32) * 34 : (size_t)(w->cols / 256) * 292;
@@ -582,6 +606,8 @@ static int issue_step(CKB200Model *m, void *st)
 int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_host)
 {
     if (!m || !tokens) return ckb_fail(CKB_ERR_STATE, "model_decode: NULL model or tokens");
+    if (m->host_pos >= m->c.max_seq_len)
+        return ckb_fail(CKB_ERR_LIMIT, "model_decode: position %d is past the context of %d tokens (reset or set_pos first)", m->host_pos, m->c.max_seq_len);
     cudaStream_t st = ckb_stream(NULL);
     const int B = m->c.batch;
     memcpy(m->tokens_pinned, tokens, (size_t)B * sizeof(int32_t));
@@ -616,9 +642,10 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
         const int rc = issue_step(m, st);
         if (rc) return rc;
     }
+    m->host_pos += 1;
     if (logits_host) {
         if (ckb_check_cuda((int)cudaMemcpyAsync(logits_host, m->logits, (size_t)B * m->Vl * sizeof(float), cudaMemcpyDeviceToHost, st), "logits D2H")) return CKB_ERR_CUDA;
-        return ckb_check_cuda((int)cudaStreamSynchronize(st), "decode sync");
+        return ckb_sync_check(st, "model_decode");        /* a timed-out exchange must not come back as rc 0 with stale logits */
     }
     return 0;
 }
@@ -627,9 +654,12 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
 int ckb200_model_decode_repeat(CKB200Model *m, int steps)
 {
     if (!m || !m->graph_ready) return ckb_fail(CKB_ERR_STATE, "model_decode_repeat: run model_decode once first");
+    if (steps > m->c.max_seq_len - m->host_pos)
+        return ckb_fail(CKB_ERR_LIMIT, "model_decode_repeat: %d steps from position %d run past the context of %d tokens", steps, m->host_pos, m->c.max_seq_len);
     cudaStream_t st = ckb_stream(NULL);
     for (int i = 0; i < steps; ++i)
         if (ckb_check_cuda((int)cudaGraphLaunch(m->graph, st), "graph launch")) return CKB_ERR_CUDA;
+    m->host_pos += steps;
     return 0;
 }
 

@@ -197,6 +197,28 @@ __device__ __forceinline__ float q6k_unit(const uint4 &ql_a, const uint4 &ql_b, 
     return (half_bits_to_float(d_bits) * x.d) * (float)tot;
 }
 
+// Integer stage of a Q6_K quarter (n, h) without assembling any 6-bit value: the nibble planes and the 2-bit planes are
+// multiplied in place (masked, not shifted) by the activation bytes and the place values are applied to the int32 sums.
+// S_t = sum over the 16 elements of scale group 8n + h + 2t of q6 * q8 with q6 in 0..63, t = 0..3; the reference's
+// sum of (q6 - 32) * q8 (src/kernels/gemm_kernels_q6k_q8k.c:92-111) is S_t - 32 * bsums[8n + h + 2t].
+// qa = ql[64n + 16h ..], qb = ql[64n + 32 + 16h ..], qh = qh[32n + 16h ..]; x_t = q8[128n + 32t + 16h ..].
+__device__ __forceinline__ void q6k_plane_sums(const uint4 &qa, const uint4 &qb, const uint4 &qh, const uint4 &x0, const uint4 &x1,
+                                               const uint4 &x2, const uint4 &x3, int &S1, int &S2, int &S3, int &S4)
+{
+    int A1 = 0, A2 = 0, A3 = 0, A4 = 0, B1 = 0, B2 = 0, B3 = 0, B4 = 0;
+#define CKB_Q6_STEP(QA, QB, QH, X0, X1, X2, X3)                      \
+    A1 = dp4a_us((QA) & 0x0F0F0F0Fu, X0, A1); B1 = dp4a_us((QH) & 0x03030303u, X0, B1); \
+    A2 = dp4a_us((QB) & 0x0F0F0F0Fu, X1, A2); B2 = dp4a_us((QH) & 0x0C0C0C0Cu, X1, B2); \
+    A3 = dp4a_us((QA) & 0xF0F0F0F0u, X2, A3); B3 = dp4a_us((QH) & 0x30303030u, X2, B3); \
+    A4 = dp4a_us((QB) & 0xF0F0F0F0u, X3, A4); B4 = dp4a_us((QH) & 0xC0C0C0C0u, X3, B4);
+    CKB_Q6_STEP(qa.x, qb.x, qh.x, x0.x, x1.x, x2.x, x3.x)
+    CKB_Q6_STEP(qa.y, qb.y, qh.y, x0.y, x1.y, x2.y, x3.y)
+    CKB_Q6_STEP(qa.z, qb.z, qh.z, x0.z, x1.z, x2.z, x3.z)
+    CKB_Q6_STEP(qa.w, qb.w, qh.w, x0.w, x1.w, x2.w, x3.w)
+#undef CKB_Q6_STEP
+    S1 = A1 + 16 * B1; S2 = A2 + 4 * B2; S3 = (A3 >> 4) + B3; S4 = (A4 >> 4) + (B4 >> 2);   // all exact
+}
+
 // ---------------------------------------------------------------- unaligned 16-byte reads
 
 // 16 bytes starting at a 2-byte-aligned shared address: five aligned words + funnel shifts.

@@ -26,6 +26,8 @@ static struct {
     int sm_count;
     cudaStream_t stream;
     int *dev_err;               /* device error word */
+    int *err_pinned;            /* pinned host word the device error word is copied into before a sync */
+    int clock_khz;              /* SM clock, for wait limits given in milliseconds */
     int err_code;
     char err_msg[512];
     long long launches;
@@ -122,6 +124,11 @@ int ckb200_init(int device)
     if (ckb_check_cuda((int)cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking), "cudaStreamCreate")) return CKB_ERR_CUDA;
     if (ckb_check_cuda((int)cudaMalloc((void **)&g.dev_err, 256), "cudaMalloc(error word)")) return CKB_ERR_CUDA;
     if (ckb_check_cuda((int)cudaMemset(g.dev_err, 0, 256), "cudaMemset(error word)")) return CKB_ERR_CUDA;
+    if (ckb_check_cuda((int)cudaHostAlloc((void **)&g.err_pinned, 64, cudaHostAllocDefault), "cudaHostAlloc(error word)")) return CKB_ERR_CUDA;
+    *g.err_pinned = 0;
+    g.clock_khz = 0;
+    cudaDeviceGetAttribute(&g.clock_khz, cudaDevAttrClockRate, device);
+    if (g.clock_khz <= 0) g.clock_khz = 1965000;
     g.inited = 1;
     return 0;
 }
@@ -132,17 +139,36 @@ int *ckb_device_error_word(void) { return g.dev_err; }
 void *ckb200_stream(void) { return ckb_ensure_init() ? NULL : (void *)g.stream; }
 cudaStream_t ckb_stream(void *user) { return user ? (cudaStream_t)user : g.stream; }
 
+/* Synchronises `st` and folds in the device error word: kernels that gave up on a bounded wait (a peer that never wrote,
+ * a copy that never landed) leave a code there and return, so without this check the caller would get rc 0 and a result
+ * built from stale data.  The word travels in the same stream, just before the sync (4 bytes, pinned). */
+int ckb_sync_check(cudaStream_t st, const char *what)
+{
+    if (ckb_check_cuda((int)cudaMemcpyAsync(g.err_pinned, g.dev_err, sizeof(int), cudaMemcpyDeviceToHost, st), "read error word")) return CKB_ERR_CUDA;
+    if (ckb_check_cuda((int)cudaStreamSynchronize(st), what)) return CKB_ERR_CUDA;
+    const int word = *g.err_pinned;
+    if (word != 0) {
+        cudaMemsetAsync(g.dev_err, 0, sizeof(int), st);
+        cudaStreamSynchronize(st);
+        *g.err_pinned = 0;
+        return ckb_fail(CKB_ERR_DEVICE_WAIT, "%s: a kernel gave up on a bounded wait (device code %d)", what, word);
+    }
+    return 0;
+}
+
 int ckb200_synchronize(void)
 {
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
-    if (ckb_check_cuda((int)cudaStreamSynchronize(g.stream), "cudaStreamSynchronize")) return CKB_ERR_CUDA;
-    int word = 0;
-    if (ckb_check_cuda((int)cudaMemcpy(&word, g.dev_err, sizeof word, cudaMemcpyDeviceToHost), "read error word")) return CKB_ERR_CUDA;
-    if (word != 0) {
-        cudaMemset(g.dev_err, 0, sizeof word);
-        return ckb_fail(CKB_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (device code %d)", word);
-    }
-    return 0;
+    return ckb_sync_check(g.stream, "ckb200_synchronize");
+}
+
+/* Limit of the waits on another GPU, in SM clock cycles: tune key wait_limit_ms (default 10 s: ranks reach their first
+ * step at different times). */
+long long ckb_wait_limit_cycles(void)
+{
+    int ms = ckb200_tune_get("wait_limit_ms", 10000);
+    if (ms < 1) ms = 1;
+    return (long long)ms * (long long)(g.clock_khz > 0 ? g.clock_khz : 1965000);
 }
 
 /* ------------------------------------------------------------------ resident weights */
@@ -247,7 +273,7 @@ void *ckb_scratch(int slot, size_t bytes)
     return g_slot[slot].p;
 }
 
-static int is_device_ptr(const void *p)
+int ckb_is_device_ptr(const void *p)
 {
     struct cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return 0; }
@@ -260,7 +286,7 @@ const void *ckb_stage_in(const void *host, size_t bytes, int slot, int try_regis
         const void *d = ckb200_device_ptr(host);
         if (d) return d;
     }
-    if (is_device_ptr(host)) return host;
+    if (ckb_is_device_ptr(host)) return host;
     void *d = ckb_scratch(slot, bytes);
     if (!d) return NULL;
     if (ckb_check_cuda((int)cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, g.stream), "H2D")) return NULL;
@@ -269,7 +295,7 @@ const void *ckb_stage_in(const void *host, size_t bytes, int slot, int try_regis
 
 void *ckb_stage_out(void *host, size_t bytes, int slot, int *needs_copy_back)
 {
-    if (is_device_ptr(host)) { *needs_copy_back = 0; return host; }
+    if (ckb_is_device_ptr(host)) { *needs_copy_back = 0; return host; }
     *needs_copy_back = 1;
     return ckb_scratch(slot, bytes);
 }
@@ -278,7 +304,7 @@ int ckb_finish_out(void *host, const void *dev, size_t bytes, int needs_copy_bac
 {
     if (needs_copy_back &&
         ckb_check_cuda((int)cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, g.stream), "D2H")) return CKB_ERR_CUDA;
-    return ckb_check_cuda((int)cudaStreamSynchronize(g.stream), "sync");
+    return ckb_sync_check(g.stream, "sync");
 }
 
 void ckb200_shutdown(void)
@@ -292,6 +318,7 @@ void ckb200_shutdown(void)
         g_slot[i].cap = 0;
     }
     cudaFree(g.dev_err);
+    cudaFreeHost(g.err_pinned);
     cudaStreamDestroy(g.stream);
     g.inited = 0;
 }

@@ -16,6 +16,9 @@ int ckb_sm_count(void);
 int *ckb_device_error_word(void);
 cudaStream_t ckb_stream(void *user);       /* user stream, or the library stream when NULL */
 int ckb_tune_get(const char *key, int dflt);
+int ckb_is_device_ptr(const void *p);      /* device or managed memory */
+int ckb_sync_check(cudaStream_t st, const char *what);   /* sync + device error word -> 0, CKB_ERR_CUDA or CKB_ERR_DEVICE_WAIT */
+long long ckb_wait_limit_cycles(void);     /* tune key wait_limit_ms in SM cycles */
 
 /* Device scratch that grows on demand (never shrinks); one buffer per slot. */
 void *ckb_scratch(int slot, size_t bytes);

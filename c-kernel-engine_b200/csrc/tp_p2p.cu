@@ -14,9 +14,12 @@
 // stored for e + 1, which a peer does only after it has finished reading call e.  The call number lives in device memory
 // and is advanced by the last CTA of a call, so a captured CUDA graph can be replayed.
 //
-// The poll is bounded (about ten seconds of SM clock: ranks reach their first step at different times); a timeout sets
-// the device error word and leaves the vector unreduced, and while that word is set no later call polls at all, so a
-// lost peer costs one timeout, not one per call.  No multicast, no peer loads: remote stores only.
+// The poll is bounded (tune key wait_limit_ms, ten seconds by default: ranks reach their first step at different times; the
+// limit is read when a call is issued, so a captured graph keeps the value it was captured with); a timeout sets the device
+// error word and leaves the vector unreduced, and while that word is set no later call polls at all, so a lost peer costs
+// one timeout, not one per call.  The host sees the word at its next synchronising call (CKB_ERR_DEVICE_WAIT).  After a
+// timeout the ranks' call numbers may differ: ckb200_tp_p2p_shutdown + create + connect on every rank starts over.
+// No multicast, no peer loads: remote stores only.
 #include "add_rmsnorm_q8k.cuh"
 #include "device_common.cuh"
 #include "launch.h"
@@ -47,7 +50,7 @@ __device__ __forceinline__ uint4 ld_line(const uint4 *p)
     return v;
 }
 
-__global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *__restrict__ buf, size_t count, P2PView v, int *__restrict__ dev_err)
+__global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *__restrict__ buf, size_t count, P2PView v, long long wait_limit, int *__restrict__ dev_err)
 {
     pdl_trigger();
     pdl_wait();
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *_
                 const uint4 *p = v.lines[me] + ((size_t)par * W + src) * v.max_lines + i;
                 uint4 l = ld_line(p);
                 while (l.y != e || l.w != e) {
-                    if (clock64() - t0 > (1ll << 34)) { ok = false; break; }
+                    if (clock64() - t0 > wait_limit) { ok = false; break; }
                     l = ld_line(p);
                 }
                 if (!ok) break;
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(P2P_THREADS) tp_allreduce_push_kernel(float *_
 // piece i of row t: t * aligned / 2 + 2 i (+1): the whole [tokens][aligned] vector is one call of the exchange.
 __global__ void __launch_bounds__(1024) tp_add_rmsnorm_q8k_kernel(float *__restrict__ x, const float *__restrict__ delta, const float *__restrict__ gamma,
                                                                   uint8_t *__restrict__ out_q8, int d_model, int aligned, float eps, P2PView v,
-                                                                  int *__restrict__ dev_err)
+                                                                  long long wait_limit, int *__restrict__ dev_err)
 {
     extern __shared__ __align__(16) float row[];
     __shared__ float red[32];
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(1024) tp_add_rmsnorm_q8k_kernel(float *__restr
                     const uint4 *p = v.lines[me] + ((size_t)par * W + src) * v.max_lines + line0 + 2 * i;
                     uint4 l0 = ld_line(p), l1 = ld_line(p + 1);
                     while (ok && (l0.y != e || l0.w != e || l1.y != e || l1.w != e)) {
-                        if (clock64() - t0 > (1ll << 34)) ok = false;
+                        if (clock64() - t0 > wait_limit) ok = false;
                         l0 = ld_line(p);
                         l1 = ld_line(p + 1);
                     }
@@ -238,6 +241,18 @@ extern "C" int ckb200_tp_p2p_connect(const void *all_handles)
     return 0;
 }
 
+// Every "peer" is this rank's own buffer: the stores land in this rank's own source slot and nothing ever fills the other
+// sources' slots, so each exchange runs into its wait limit.  For exercising the timeout path on a single GPU.
+extern "C" int ckb200_tp_p2p_connect_self(void)
+{
+    if (!g_p2p.local) return ckb_fail(CKB_ERR_STATE, "tp_p2p_connect_self: ckb200_tp_p2p_create has not been called");
+    const int W = g_p2p.view.world;
+    for (int r = 0; r < W; ++r) g_p2p.view.lines[r] = (uint4 *)g_p2p.local;
+    g_p2p.view.epoch = (unsigned *)(g_p2p.local + p2p_line_bytes(W, 2 * g_p2p.view.max_lines));
+    g_p2p.ready = 1;
+    return 0;
+}
+
 extern "C" int ckb200_tp_p2p_ready(void) { return g_p2p.ready; }
 extern "C" size_t ckb200_tp_p2p_max_floats(void) { return g_p2p.ready ? 2 * g_p2p.view.max_lines : 0; }
 
@@ -251,7 +266,7 @@ extern "C" int ckb_tp_p2p_allreduce(float *buf, size_t count, void *stream)
     size_t ctas = (nl + P2P_THREADS - 1) / P2P_THREADS;
     if (ctas > P2P_MAX_CTAS) ctas = P2P_MAX_CTAS;
     return launch_pdl("tp_allreduce_push", tp_allreduce_push_kernel, dim3((unsigned)ctas), dim3(P2P_THREADS), 0, ckb_stream(stream), buf, count, g_p2p.view,
-                      ckb_device_error_word());
+                      ckb_wait_limit_cycles(), ckb_device_error_word());
 }
 
 // ckb200_tp_norm_fn: x[t] += sum over ranks of delta[t]; out_q8[t] = Q8_K(rmsnorm(x[t]) * gamma).  Returns -1 when the
@@ -276,7 +291,7 @@ extern "C" int ckb200_tp_add_rmsnorm_q8k(void *ctx, float *x, const float *delta
         }
     }
     return launch_pdl("tp_add_rmsnorm_q8k", tp_add_rmsnorm_q8k_kernel, dim3(tokens), dim3(threads), smem, ckb_stream(stream), x, delta, gamma, (uint8_t *)out_q8,
-                      d_model, aligned_embed_dim, eps, g_p2p.view, ckb_device_error_word());
+                      d_model, aligned_embed_dim, eps, g_p2p.view, ckb_wait_limit_cycles(), ckb_device_error_word());
 }
 
 extern "C" void ckb200_tp_p2p_shutdown(void)

@@ -126,6 +126,17 @@ int ckb200_dev_gemv_q8_0_planar_q8_0(float *y, const void *W_planar, const void 
 /* gemm_nt_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268) over planar weights: tensor-core kernel from 16 tokens up */
 int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);
 
+/* The integer stage of the K-quant dot products, dumped for bit-exact checks.  The reference accumulates int32 sums of
+ * (weight code x activation byte) per sub-block before any floating point: for Q4_K the eight 32-element sums
+ * sum_q4q8_lo / sum_q4q8_hi of a superblock (dot_q4_k_q8_k_ref, src/kernels/gemm_kernels_q4k_q8k.c:144-167), for Q6_K
+ * the sixteen 16-element sums of (q6 - 32) x q8 (dot_q6_k_q8_k_ref, src/kernels/gemm_kernels_q6k_q8k.c:92-111).
+ * W: M rows in the reference's layout, x_q8: one Q8_K vector, out: int32 [M][K/256][8] (Q4_K) or [M][K/256][16] (Q6_K).
+ * The sums are produced by the device functions the GEMV kernels themselves call; `variant` picks the family:
+ * 0 = the tuned kernels' unit (Q4_K pair / register-activation kernels; Q6_K planar and ring kernels, bit-plane form),
+ * 1 = the generic direct kernels' unit. */
+int ckb200_dev_subblock_sums_q4_k_q8_k(const void *W, const void *x_q8, int M, int K, int32_t *out, int variant, void *stream);
+int ckb200_dev_subblock_sums_q6_k_q8_k(const void *W, const void *x_q8, int M, int K, int32_t *out, int variant, void *stream);
+
 /* attention_forward_decode_head_major_gqa_flash (src/kernels/attention_kernels.c:3365-3406) for `batch`
  * independent sequences: q/out [batch][H][ad], caches [batch][Hkv][capacity][ad] with kv_batch_stride floats
  * between sequences.  Split-K over the context; partial results go through a scratch buffer.
@@ -205,6 +216,14 @@ int ckb200_dev_rope_precompute_cache_split(float *cos_cache, float *sin_cache, i
 int ckb200_dev_rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
                                int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
                                const int *pos_dev, void *stream);
+/* rope_precompute_cache (src/kernels/rope_kernels.c:270-316): rows of rotary_dim / 2 values (rotary_dim <= 0 or > head_dim means
+ * head_dim), positions divided by scaling_factor when linear_scaling != 0; and rope_forward_qk_pairwise_with_rotary_dim
+ * (:839-866): pairs (2i, 2i+1) of the first rotary_dim elements of every head row are rotated. */
+int ckb200_dev_rope_precompute_cache(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base, int rotary_dim,
+                                     int linear_scaling, float scaling_factor, void *stream);
+int ckb200_dev_rope_forward_qk_pairwise(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                        int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                        int rotary_dim, const int *pos_dev, void *stream);
 /* swiglu_forward (src/kernels/swiglu_kernels.c:140-216): input [T][2D] gate then up, output [T][D]. */
 int ckb200_dev_swiglu_forward(const float *input, float *output, int tokens, int dim, void *stream);
 /* ck_residual_add_token_major (src/ckernel_orchestration.c:139-149). */

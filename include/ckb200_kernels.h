@@ -152,6 +152,62 @@ void embedding_forward_q8_0(const int32_t *token_ids, int token_count, int vocab
                             const float *pos_embeddings, float *output, int embed_dim, int aligned_embed_dim,
                             int context_window, int add_pos);
 
+/* ---- fp32-activation GEMMs (the reference's debug path): one fp32-activation GEMV per token.
+ *      gemm_nt_q4_k src/kernels/gemm_kernels_q4k.c:683-711, gemm_q4_k[_ref] :316-326, :461-469;
+ *      gemm_nt_q6_k[_ref] src/kernels/gemm_kernels_q6k.c:212-250, gemm_q6_k :195-210; gemm_nt_q6_k_sse
+ *      src/kernels/gemm_kernels_q6k_sse.c:66-97 (quantises A to Q8_K itself); gemm_nt_q8_0
+ *      src/kernels/gemm_kernels_q8_0.c:683-696, gemm_q8_0 :658-666.  gemm_nt: A [M][K], B [N][K] blocks, C [M][N];
+ *      gemm: Y [N][M], W [M][K] blocks, X [N][K]. */
+void gemm_nt_q4_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_q4_k(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_q4_k_ref(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_nt_q6_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q6_k_ref(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q6_k_sse(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_q6_k(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_nt_q8_0(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_q8_0(float *Y, const void *W, const float *X, int M, int N, int K);
+
+/* ---- fp32 in, Q8_0 quantisation inside: src/kernels/gemm_kernels_q8_0_q8_0_contract.c:377-406, :408-486
+ *      (rows of more than 1024 blocks take the fp32-activation GEMV, as there) */
+void gemv_q8_0_q8_0_contract(float *y, const void *W, const float *x, int M, int K);
+void gemm_nt_q8_0_q8_0_contract(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+
+/* ---- RoPE, general table and pairwise rotation: rope_precompute_cache src/kernels/rope_kernels.c:270-316 (rows of
+ *      rotary_dim / 2 values; scaling_type "linear" divides the position by scaling_factor, anything else is ignored as in
+ *      the reference), rope_forward_qk_pairwise_with_rotary_dim :839-866 (pairs (2i, 2i+1), the Llama form) */
+void rope_precompute_cache(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base, int rotary_dim,
+                           const char *scaling_type, float scaling_factor);
+void rope_forward_qk_pairwise_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                              int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                              int rotary_dim);
+
+/* ---- small copies: add_inplace_f32 include/ckernel_engine.h:1894 (src/kernels/add_kernels_bf16.c:304-330),
+ *      logits_copy_to_position src/kernels/kv_cache_kernels.c:178-191 */
+void add_inplace_f32(float *a, const float *b, size_t n);
+void logits_copy_to_position(const float *src, float *dst, int position, int vocab_size);
+
+/* ---- the reference's flat parity API (include/ck_parity_api.h, src/ck_parity_api.c:189-694): what its kernel-parity
+ *      scripts bind.  Each quantises the fp32 input as the reference wrapper does and runs the quantised kernel. */
+void ck_test_dequant_q4_k(const void *src, float *dst, int n);
+void ck_test_dequant_q6_k(const void *src, float *dst, int n);
+void ck_test_quantize_q8_k(const float *src, void *dst, int n);
+void ck_test_gemv_q4_k(const void *weight_q4k, const float *input_f32, float *output, int cols);
+void ck_test_gemv_q6_k(const void *weight_q6k, const float *input_f32, float *output, int cols);
+void ck_test_gemv_q5_0(const void *weight_q5_0, const float *input_f32, float *output, int rows, int cols);
+void ck_test_gemv_q8_0(const void *weight_q8_0, const float *input_f32, float *output, int rows, int cols);
+void ck_test_gemv_q5_0_q8_0(const void *weight_q5_0, const float *input_f32, float *output, int rows, int cols);
+void ck_test_gemv_q8_0_q8_0(const void *weight_q8_0, const float *input_f32, float *output, int rows, int cols);
+void ck_test_vec_dot_q5_0_q8_0(const void *weight_q5_0, const void *input_q8_0, float *output, int cols);
+void ck_test_vec_dot_q8_0_q8_0(const void *weight_q8_0, const void *input_q8_0, float *output, int cols);
+void ck_test_gemm_q4_k(const void *weight_q4k, const float *input_f32, float *output, int rows, int cols, int n_tokens);
+void ck_test_gemm_q6_k(const void *weight_q6k, const float *input_f32, float *output, int rows, int cols, int n_tokens);
+void ck_test_gemm_q8_0(const void *weight_q8_0, const float *input_f32, float *output, int rows, int cols, int n_tokens);
+void ck_test_gemm_q5_0(const void *weight_q5_0, const float *input_f32, float *output, int rows, int cols, int n_tokens);
+void ck_test_rmsnorm(const float *input, const float *weight, float *output, int n_tokens, int dim, float eps);
+void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta);
+void ck_test_swiglu(const float *gate_up, float *output, int n_tokens, int intermediate_dim);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,10 @@ void ckb200_tp_shutdown(void);
  * <= max_floats (tune "tp_p2p" 0 switches it off); waits are bounded and report through the device error word. */
 int ckb200_tp_p2p_create(int rank, int world, size_t max_floats, void *handle_out64);
 int ckb200_tp_p2p_connect(const void *all_handles);
+/* Single-GPU loopback for exercising the bounded wait: every peer pointer is this rank's own buffer, so the other ranks'
+ * slots are never filled and each exchange runs into its limit (tune key "wait_limit_ms", default 10000), after which the
+ * kernel returns, the device error word is set and the next synchronising call reports CKB_ERR_DEVICE_WAIT. */
+int ckb200_tp_p2p_connect_self(void);
 int ckb200_tp_p2p_ready(void);
 size_t ckb200_tp_p2p_max_floats(void);
 void ckb200_tp_p2p_shutdown(void);

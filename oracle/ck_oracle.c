@@ -821,3 +821,153 @@ void oracle_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, con
     orc_embed(ids, count, vocab, table, pos, out, embed, aligned, ctx, add_pos, (size_t)(aligned / 32) * 34,
               oracle_dequant_q8_0_row);
 }
+
+/* ---- fp32-activation products of the reference's debug path ----
+ * gemv_q4_k_ref: src/kernels/gemm_kernels_q4k.c:53-101 (per element (d*sc*q - dmin*m) * x, in element order);
+ * gemv_q6_k -> dot_q6_k_ref: src/kernels/gemm_kernels_q6k.c:80-118, :169-193 (l-major over the four strided streams). */
+void oracle_gemv_q4_k(float *y, const void *W, const float *x, int M, int K)
+{
+    if (!y || !W || !x || M <= 0 || K <= 0) return;
+    const orc_q4_K *w = (const orc_q4_K *)W;
+    const int nb = K / ORC_QK_K;
+    for (int r = 0; r < M; ++r) {
+        float sum = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const orc_q4_K *blk = &w[(size_t)r * nb + b];
+            const float d = oracle_fp16_to_fp32(blk->d), dmin = oracle_fp16_to_fp32(blk->dmin);
+            uint8_t sc[8], mn[8];
+            oracle_unpack_q4_k_scales(blk->scales, sc, mn);
+            for (int g = 0; g < 4; ++g) {
+                const float d1 = d * (float)sc[2 * g], m1 = dmin * (float)mn[2 * g];
+                const float d2 = d * (float)sc[2 * g + 1], m2 = dmin * (float)mn[2 * g + 1];
+                const uint8_t *qs = blk->qs + 32 * g;
+                const float *xp = x + (size_t)b * ORC_QK_K + 64 * g;
+                for (int l = 0; l < 32; ++l) sum += (d1 * (float)(qs[l] & 15) - m1) * xp[l];
+                for (int l = 0; l < 32; ++l) sum += (d2 * (float)(qs[l] >> 4) - m2) * xp[l + 32];
+            }
+        }
+        y[r] = sum;
+    }
+}
+
+void oracle_gemv_q6_k(float *y, const void *W, const float *x, int M, int K)
+{
+    if (!y || !W || !x || M <= 0 || K <= 0) return;
+    const orc_q6_K *w = (const orc_q6_K *)W;
+    const int nb = K / ORC_QK_K;
+    for (int r = 0; r < M; ++r) {
+        float sum = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const orc_q6_K *blk = &w[(size_t)r * nb + b];
+            const float d = oracle_fp16_to_fp32(blk->d);
+            for (int half = 0; half < 2; ++half)
+                for (int l = 0; l < 32; ++l)
+                    for (int qt = 0; qt < 4; ++qt) {
+                        const int e = 128 * half + 32 * qt + l;
+                        sum += d * (float)blk->scales[8 * half + (l >> 4) + 2 * qt] * (float)orc_q6_value(blk, e) * x[(size_t)b * ORC_QK_K + e];
+                    }
+        }
+        y[r] = sum;
+    }
+}
+
+/* gemm_nt_<fmt>(A fp32 [M][K], B [N][K], bias, C [M][N]): one fp32-activation GEMV per token, then the bias
+ * (src/kernels/gemm_kernels_q4k.c:683-711, src/kernels/gemm_kernels_q6k.c:212-238, src/kernels/gemm_kernels_q8_0.c:683-696);
+ * gemm_<fmt>(Y [N][M], W [M][K], X [N][K]) is the same loop (gemm_kernels_q4k.c:316-326, gemm_kernels_q6k.c:195-210,
+ * gemm_kernels_q8_0.c:658-666). */
+typedef void (*orc_gemv_f32_fn)(float *, const void *, const float *, int, int);
+static void orc_gemm_nt_f32(orc_gemv_f32_fn gemv, const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return;
+    for (int m = 0; m < M; ++m) {
+        gemv(C + (size_t)m * N, B, A + (size_t)m * K, N, K);
+        if (bias) for (int n = 0; n < N; ++n) C[(size_t)m * N + n] += bias[n];
+    }
+}
+void oracle_gemm_nt_q4_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q4_k, A, B, bias, C, M, N, K); }
+void oracle_gemm_nt_q6_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q6_k, A, B, bias, C, M, N, K); }
+void oracle_gemm_nt_q8_0(const float *A, const void *B, const float *bias, float *C, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q8_0, A, B, bias, C, M, N, K); }
+void oracle_gemm_q4_k(float *Y, const void *W, const float *X, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q4_k, X, W, NULL, Y, N, M, K); }
+void oracle_gemm_q6_k(float *Y, const void *W, const float *X, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q6_k, X, W, NULL, Y, N, M, K); }
+void oracle_gemm_q8_0(float *Y, const void *W, const float *X, int M, int N, int K) { orc_gemm_nt_f32(oracle_gemv_q8_0, X, W, NULL, Y, N, M, K); }
+
+/* gemm_nt_q6_k_sse (src/kernels/gemm_kernels_q6k_sse.c:66-97): A rows quantised to Q8_K, then Q6_K x Q8_K dots */
+void oracle_gemm_nt_q6_k_sse(const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0 || K % ORC_QK_K) return;
+    orc_q8_K *aq = (orc_q8_K *)malloc((size_t)M * (K / ORC_QK_K) * sizeof(orc_q8_K));
+    if (!aq) return;
+    oracle_quantize_batch_q8_k(A, aq, M, K);
+    oracle_gemm_nt_q6_k_q8_k(aq, B, bias, C, M, N, K);
+    free(aq);
+}
+
+/* gemv_q8_0_q8_0_contract / gemm_nt_q8_0_q8_0_contract (src/kernels/gemm_kernels_q8_0_q8_0_contract.c:377-406, :408-486, the
+ * non-strict path): x quantised to Q8_0 when a row has at most 1024 blocks, else the fp32-activation GEMV */
+void oracle_gemv_q8_0_q8_0_contract(float *y, const void *W, const float *x, int M, int K)
+{
+    if (!y || !W || !x || M <= 0 || K <= 0) return;
+    if (K % ORC_QK8_0 || K / ORC_QK8_0 > 1024) { oracle_gemv_q8_0(y, W, x, M, K); return; }
+    orc_q8_0 xq[1024];
+    oracle_quantize_row_q8_0(x, xq, K);
+    oracle_gemv_q8_0_q8_0(y, W, xq, M, K);
+}
+void oracle_gemm_nt_q8_0_q8_0_contract(const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    orc_gemm_nt_f32(oracle_gemv_q8_0_q8_0_contract, A, B, bias, C, M, N, K);
+}
+
+/* ---- RoPE, general table and pairwise rotation (src/kernels/rope_kernels.c:270-316, :419-451, :839-866) ---- */
+void oracle_rope_precompute_cache(float *cos_cache, float *sin_cache, int max_seq_len, int head_dim, float base, int rotary_dim,
+                                  const char *scaling_type, float scaling_factor)
+{
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    const int linear = scaling_type && !strcmp(scaling_type, "linear") && scaling_factor > 0.0f && scaling_factor != 1.0f;
+    const int half = rotary_dim / 2;
+    const long double lb = logl((long double)base);
+    for (int p = 0; p < max_seq_len; ++p) {
+        const float epos = linear ? (float)p / scaling_factor : (float)p;
+        for (int i = 0; i < half; ++i) {
+            const float freq = (float)expl(-((long double)(2 * i) / (long double)rotary_dim) * lb);
+            const float ang = epos * freq;
+            cos_cache[(size_t)p * half + i] = cosf(ang);
+            sin_cache[(size_t)p * half + i] = sinf(ang);
+        }
+    }
+}
+
+static void orc_rope_heads_pairwise(float *x, const float *cc, const float *ss, int heads, int tokens, int rot, int ahd, int pos0)
+{
+    const int half = rot / 2;
+    for (int h = 0; h < heads; ++h)
+        for (int t = 0; t < tokens; ++t) {
+            float *r = x + ((size_t)h * tokens + t) * ahd;
+            const float *c = cc + (size_t)(pos0 + t) * half, *s = ss + (size_t)(pos0 + t) * half;
+            for (int i = 0; i < half; ++i) {
+                const float a = r[2 * i], b = r[2 * i + 1];
+                r[2 * i] = a * c[i] - b * s[i];
+                r[2 * i + 1] = a * s[i] + b * c[i];
+            }
+        }
+}
+
+void oracle_rope_forward_qk_pairwise_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                                     int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                                     int rotary_dim)
+{
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    orc_rope_heads_pairwise(q, cos_cache, sin_cache, num_heads, num_tokens, rotary_dim, aligned_head_dim, pos_offset);
+    orc_rope_heads_pairwise(k, cos_cache, sin_cache, num_kv_heads, num_tokens, rotary_dim, aligned_head_dim, pos_offset);
+}
+
+/* ---- add_inplace_f32 (src/kernels/add_kernels_bf16.c:304-335), logits_copy_to_position (src/kernels/kv_cache_kernels.c:178-191) ---- */
+void oracle_add_inplace_f32(float *a, const float *b, size_t n)
+{
+    if (!a || !b) return;
+    for (size_t i = 0; i < n; ++i) a[i] = a[i] + b[i];
+}
+void oracle_logits_copy_to_position(const float *src, float *dst, int position, int vocab_size)
+{
+    if (!src || !dst || position < 0 || vocab_size <= 0) return;
+    memmove(dst + (size_t)position * (size_t)vocab_size, src, (size_t)vocab_size * sizeof(float));
+}

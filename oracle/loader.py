@@ -2,6 +2,7 @@
 
   load_oracle()     -> oracle/libck_oracle.so, this repository's C restatement
   load_reference()  -> oracle/_ref/libck_ref*.so, the reference's own kernels (None if not built)
+  load_reference_parity() -> oracle/_ref/libck_ref_parity*.so, the reference's ck_test_* wrappers over those kernels
 
 The reference library comes in two ISA levels; the one the host can execute is chosen
 from /proc/cpuinfo so that a host without AVX-512 does not die with SIGILL.
@@ -57,6 +58,19 @@ def reference_path() -> str | None:
 def load_reference() -> ctypes.CDLL | None:
     p = reference_path()
     return ctypes.CDLL(p) if p else None
+
+
+def load_reference_parity() -> ctypes.CDLL | None:
+    """The reference's flat parity API (ck_test_*), built beside the kernels.  It wraps more kernels than this path compiles,
+    so it is loaded with lazy binding; only the hot-path wrappers may be called."""
+    p = reference_path()
+    if not p:
+        return None
+    q = p.replace("libck_ref", "libck_ref_parity")
+    if not os.path.exists(q):
+        return None
+    ctypes.CDLL(p, mode=ctypes.RTLD_GLOBAL)
+    return ctypes.CDLL(q, mode=os.RTLD_LAZY)
 
 
 def host_threads() -> int:

@@ -250,6 +250,101 @@ def embedding(lib, prefix, fmt: str, ids, table, vocab: int, embed: int, aligned
     return out
 
 
+
+# ----------------------------------------------------------------------------- fp32-activation GEMMs, contract forms, pairwise RoPE, copies
+
+def gemm_nt_f32(lib, prefix, name: str, a: np.ndarray, w: np.ndarray, bias, m: int, n: int, k: int) -> np.ndarray:
+    """gemm_nt_q4_k / gemm_nt_q6_k[_ref/_sse] / gemm_nt_q8_0 / gemm_nt_q8_0_q8_0_contract: A fp32 [m][k], B [n][k] blocks -> C [m][n]."""
+    c = np.full((m, n), np.nan, dtype=np.float32)
+    b = fptr(bias) if bias is not None else c_float_p()
+    fn(lib, prefix, name)(fptr(np.ascontiguousarray(a.reshape(-1))), vptr(w), b, fptr(c), C.c_int(m), C.c_int(n), C.c_int(k))
+    return c
+
+
+def gemm_f32(lib, prefix, name: str, w: np.ndarray, x: np.ndarray, m: int, n: int, k: int) -> np.ndarray:
+    """gemm_q4_k / gemm_q6_k / gemm_q8_0: W [m][k] blocks, X fp32 [n][k] -> Y [n][m]."""
+    y = np.full((n, m), np.nan, dtype=np.float32)
+    fn(lib, prefix, name)(fptr(y), vptr(w), fptr(np.ascontiguousarray(x.reshape(-1))), C.c_int(m), C.c_int(n), C.c_int(k))
+    return y
+
+
+def gemv_contract(lib, prefix, w: np.ndarray, x: np.ndarray, m: int, k: int) -> np.ndarray:
+    y = np.full(m, np.nan, dtype=np.float32)
+    fn(lib, prefix, "gemv_q8_0_q8_0_contract")(fptr(y), vptr(w), fptr(np.ascontiguousarray(x)), C.c_int(m), C.c_int(k))
+    return y
+
+
+def rope_cache_general(lib, prefix, max_seq: int, d: int, theta: float, rotary_dim: int, scaling: bytes | None, factor: float):
+    rot = rotary_dim if 0 < rotary_dim <= d else d
+    cos = np.zeros((max_seq, rot // 2), dtype=np.float32)
+    sin = np.zeros((max_seq, rot // 2), dtype=np.float32)
+    fn(lib, prefix, "rope_precompute_cache")(fptr(cos), fptr(sin), C.c_int(max_seq), C.c_int(d), C.c_float(theta), C.c_int(rotary_dim),
+                                             C.c_char_p(scaling), C.c_float(factor))
+    return cos, sin
+
+
+def rope_qk_pairwise(lib, prefix, q, k, cos, sin, pos: int, hd: int, rotary_dim: int):
+    """q [H, tokens, ad], k [Hkv, tokens, ad]; pairs (2i, 2i+1) of the first rotary_dim elements rotated in place."""
+    fn(lib, prefix, "rope_forward_qk_pairwise_with_rotary_dim")(
+        fptr(q), fptr(k), fptr(cos), fptr(sin), C.c_int(q.shape[0]), C.c_int(k.shape[0]), C.c_int(q.shape[1]), C.c_int(hd),
+        C.c_int(q.shape[2]), C.c_int(pos), C.c_int(rotary_dim))
+
+
+def add_inplace(lib, prefix, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    out = a.copy()
+    fn(lib, prefix, "add_inplace_f32")(fptr(out), fptr(b), C.c_size_t(out.size))
+    return out
+
+
+def logits_copy(lib, prefix, src: np.ndarray, rows: int, position: int) -> np.ndarray:
+    dst = np.zeros((rows, src.size), dtype=np.float32)
+    fn(lib, prefix, "logits_copy_to_position")(fptr(src), fptr(dst), C.c_int(position), C.c_int(src.size))
+    return dst
+
+
+def boundary_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
+    """Seeded cases for the entry points above; run through the reference (golden file), the oracle and the CUDA library."""
+    out: dict[str, np.ndarray] = {}
+    for fmt, m, n, k, seed in [("q4_k", 3, 9, 512, 71), ("q6_k", 2, 7, 512, 72), ("q8_0", 3, 6, 160, 73)]:
+        w = synth.make_weights(fmt, n, k, seed)
+        a = synth.make_x(k, seed, rows=m).reshape(m, k)
+        bias = np.random.default_rng(seed).standard_normal(n).astype(np.float32)
+        out[f"gemm_nt_f32_{fmt}"] = gemm_nt_f32(lib, prefix, f"gemm_nt_{fmt}", a, w, bias, m, n, k)
+        out[f"gemm_f32_{fmt}"] = gemm_f32(lib, prefix, f"gemm_{fmt}", w, a, n, m, k)
+    w = synth.make_weights("q6_k", 5, 768, 74)
+    a = synth.make_x(768, 74, rows=2).reshape(2, 768)
+    out["gemm_nt_q6_k_sse"] = gemm_nt_f32(lib, prefix, "gemm_nt_q6_k_sse", a, w, None, 2, 5, 768)
+    w = synth.make_weights("q8_0", 11, 896, 75)
+    x = synth.make_x(896, 75)
+    out["gemv_contract"] = gemv_contract(lib, prefix, w, x, 11, 896)
+    a = synth.make_x(896, 76, rows=3).reshape(3, 896)
+    bias = np.random.default_rng(76).standard_normal(11).astype(np.float32)
+    out["gemm_nt_contract"] = gemm_nt_f32(lib, prefix, "gemm_nt_q8_0_q8_0_contract", a, w, bias, 3, 11, 896)
+
+    rng = np.random.default_rng(77)
+    cos, sin = rope_cache_general(lib, prefix, 48, 128, 5.0e5, 0, None, 1.0)
+    out["rope_general_cos"], out["rope_general_sin"] = cos, sin
+    cos2, sin2 = rope_cache_general(lib, prefix, 33, 64, 1.0e4, 32, b"linear", 4.0)
+    out["rope_linear_cos"], out["rope_linear_sin"] = cos2, sin2
+    q = rng.standard_normal((8, 3, 128)).astype(np.float32)
+    k = rng.standard_normal((2, 3, 128)).astype(np.float32)
+    rope_qk_pairwise(lib, prefix, q, k, cos, sin, pos=41, hd=128, rotary_dim=0)
+    out["rope_pair_q"], out["rope_pair_k"] = q, k
+    q = rng.standard_normal((4, 2, 72)).astype(np.float32)          # aligned head 72 > head_dim 64 > rotary 32: the tail is untouched
+    k = rng.standard_normal((4, 2, 72)).astype(np.float32)
+    rope_qk_pairwise(lib, prefix, q, k, cos2, sin2, pos=30, hd=64, rotary_dim=32)
+    out["rope_pair_partial_q"], out["rope_pair_partial_k"] = q, k
+
+    a = rng.standard_normal(1000).astype(np.float32)
+    b = rng.standard_normal(1000).astype(np.float32)
+    out["add_inplace"] = add_inplace(lib, prefix, a, b)
+    out["logits_copy"] = logits_copy(lib, prefix, rng.standard_normal(77).astype(np.float32), 4, 2)
+    return out
+
+
+# Outputs the oracle reproduces bit for bit (the reference computes them in scalar order, or they are integer work plus one fp32 product per block)
+BOUNDARY_BIT_EXACT = ("gemm_nt_f32_q6_k", "gemm_f32_q6_k", "add_inplace", "logits_copy", "gemv_contract", "gemm_nt_contract", "rope_")
+
 # ----------------------------------------------------------------------------- the golden case list
 
 GOLDEN_GEMV = [  # fmt, M, K, K_valid, seed

@@ -64,3 +64,18 @@ def _no_stale_error(request):
         msg = lib.ckb200_last_error_message().decode()
         lib.ckb200_clear_error()
         assert code == 0, f"library recorded error {code}: {msg}"
+
+
+@pytest.fixture(scope="session")
+def golden_boundary():
+    """Reference outputs for the fp32-activation GEMMs, contract forms, pairwise RoPE and copies (tests/cases.boundary_outputs)."""
+    return np.load(os.path.join(ROOT, "tests", "golden", "reference_boundary_outputs.npz"))
+
+
+@pytest.fixture(scope="session")
+def ref_parity():
+    """The reference's ck_test_* wrappers, when oracle/_ref was built (skips otherwise)."""
+    lib = graft.oracle_loader().load_reference_parity()
+    if lib is None:
+        pytest.skip("oracle/_ref/libck_ref_parity.so not built on this machine")
+    return lib

@@ -229,3 +229,98 @@ def test_oracle_vs_reference_q5_0_dequant_and_fp32_gemv(ref, orc):
     a = cases.gemv_f32(ref, "", "q5_0", w, x, m, k, "gemv_q5_0_ref")
     b = cases.gemv_f32(orc, "oracle_", "q5_0", w, x, m, k, "gemv_q5_0")
     assert np.array_equal(a, b)
+
+
+# ---------------------------------------------------------------- later entry points: fp32-activation GEMMs, contract forms, pairwise RoPE, copies
+
+def test_boundary_oracle_against_golden(golden_boundary, orc):
+    got = cases.boundary_outputs(orc, "oracle_")
+    assert sorted(got) == sorted(golden_boundary.files)
+    for name in golden_boundary.files:
+        if name.startswith(cases.BOUNDARY_BIT_EXACT):
+            assert np.array_equal(golden_boundary[name], got[name]), name
+        else:
+            # the reference dispatches these to vector code (another fp32 order); the rope tables go through libm's long double
+            assert _close(golden_boundary[name], got[name], 2e-6 if name.startswith("rope_") else 1e-5), name
+
+
+def test_boundary_oracle_vs_reference_live(ref, orc):
+    a, b = cases.boundary_outputs(ref, ""), cases.boundary_outputs(orc, "oracle_")
+    for name in a:
+        if name.startswith(cases.BOUNDARY_BIT_EXACT):
+            assert np.array_equal(a[name], b[name]), name
+        else:
+            assert _close(a[name], b[name], 1e-5), name
+
+
+def test_contract_long_rows_take_the_fp32_path(ref, orc):
+    """More than 1024 blocks per row: the reference's contract GEMV falls back to gemv_q8_0; so does the oracle."""
+    m, k = 3, 32 * 1030
+    w = synth.make_weights("q8_0", m, k, 81)
+    x = synth.make_x(k, 81)
+    assert _close(cases.gemv_contract(ref, "", w, x, m, k), cases.gemv_contract(orc, "oracle_", w, x, m, k), 1e-5)
+
+
+def parity_api_cases(lib, quant_lib, quant_prefix):
+    """Drives the flat ck_test_* API of `lib` (the reference's wrappers or the CUDA library's)."""
+    out = {}
+    rng = np.random.default_rng(91)
+    w4, w6 = synth.make_weights("q4_k", 6, 512, 91), synth.make_weights("q6_k", 6, 512, 92)
+    w8, w5 = synth.make_weights("q8_0", 6, 256, 93), synth.make_weights("q5_0", 6, 256, 94)
+    x512, x256 = synth.make_x(512, 91), synth.make_x(256, 93)
+    for name, w in (("q4_k", w4), ("q6_k", w6)):
+        d = np.zeros(512, np.float32)
+        getattr(lib, f"ck_test_dequant_{name}")(cases.vptr(w), cases.fptr(d), 512)
+        out[f"dequant_{name}"] = d
+        y = np.zeros(1, np.float32)
+        getattr(lib, f"ck_test_gemv_{name}")(cases.vptr(w), cases.fptr(x512), cases.fptr(y), 512)
+        out[f"gemv_{name}"] = y
+        a = synth.make_x(512, 95, rows=3)
+        c = np.zeros((3, 6), np.float32)
+        getattr(lib, f"ck_test_gemm_{name}")(cases.vptr(w), cases.fptr(a), cases.fptr(c), 6, 512, 3)
+        out[f"gemm_{name}"] = c
+    q = np.zeros(2 * 292, np.uint8)
+    lib.ck_test_quantize_q8_k(cases.fptr(x512), cases.vptr(q), 512)
+    out["quantize_q8_k"] = q
+    for name, w in (("q8_0", w8), ("q5_0", w5)):
+        for sym in (f"ck_test_gemv_{name}", f"ck_test_gemv_{name}_q8_0"):
+            y = np.zeros(6, np.float32)
+            getattr(lib, sym)(cases.vptr(w), cases.fptr(x256), cases.fptr(y), 6, 256)
+            out[sym] = y
+        xq = cases.quantize_q8_0(quant_lib, quant_prefix, x256)
+        y = np.zeros(1, np.float32)
+        getattr(lib, f"ck_test_vec_dot_{name}_q8_0")(cases.vptr(w), cases.vptr(xq), cases.fptr(y), 256)
+        out[f"vec_dot_{name}"] = y
+        a = synth.make_x(256, 96, rows=2)
+        c = np.zeros((2, 6), np.float32)
+        getattr(lib, f"ck_test_gemm_{name}")(cases.vptr(w), cases.fptr(a), cases.fptr(c), 6, 256, 2)
+        out[f"gemm_{name}"] = c
+    xn = rng.standard_normal((2, 320)).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(320)).astype(np.float32)
+    yn = np.zeros_like(xn)
+    lib.ck_test_rmsnorm(cases.fptr(xn), cases.fptr(g), cases.fptr(yn), 2, 320, C.c_float(1e-5))
+    out["rmsnorm"] = yn
+    qr, kr = rng.standard_normal((3, 4 * 64)).astype(np.float32), rng.standard_normal((3, 2 * 64)).astype(np.float32)
+    lib.ck_test_rope(cases.fptr(qr), cases.fptr(kr), 3, 4, 2, 64, 5, C.c_float(1.0e4))
+    out["rope_q"], out["rope_k"] = qr, kr
+    gu = (2 * rng.standard_normal((2, 2 * 96))).astype(np.float32)
+    so = np.zeros((2, 96), np.float32)
+    lib.ck_test_swiglu(cases.fptr(gu), cases.fptr(so), 2, 96)
+    out["swiglu"] = so
+    return out
+
+
+def test_parity_api_reference_wrappers_match_oracle_compositions(ref_parity, ref, orc):
+    """The reference's ck_test_* wrappers are thin compositions (quantise, then the quantised kernel); the same compositions of
+    oracle functions give the same numbers, which is what the CUDA library's wrappers are held to on the GPU."""
+    got = parity_api_cases(ref_parity, ref, "")
+    w4, w6 = synth.make_weights("q4_k", 6, 512, 91), synth.make_weights("q6_k", 6, 512, 92)
+    x512 = synth.make_x(512, 91)
+    xq = cases.quantize_q8_k(orc, "oracle_", x512)
+    assert np.array_equal(got["quantize_q8_k"], xq)
+    assert np.array_equal(got["dequant_q4_k"], cases.dequant_row(orc, "oracle_", "q4_k", w4, 512))
+    assert _close(got["gemv_q4_k"], cases.gemv(orc, "oracle_", "q4_k", w4, xq, 1, 512), 1e-5)
+    assert _close(got["gemv_q6_k"], cases.gemv(orc, "oracle_", "q6_k", w6, xq, 1, 512), 1e-5)
+    aq = cases.quantize_q8_k(orc, "oracle_", synth.make_x(512, 95, rows=3), rows=3)
+    assert _close(got["gemm_q4_k"], cases.gemm_nt(orc, "oracle_", "q4_k", aq, w4, None, 3, 6, 512), 1e-5)
+    assert _close(got["gemm_q6_k"], cases.gemm_nt(orc, "oracle_", "q6_k", aq, w6, None, 3, 6, 512), 1e-5)

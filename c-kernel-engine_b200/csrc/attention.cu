@@ -560,9 +560,13 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
         cudaGetLastError();
         return ckb_fail(CKB_ERR_NO_DEVICE, "attention decode (static scratch): no current CUDA device");
     }
-    if (!g_attn_static_ptr[dev]) {
+    float *scratch = __atomic_load_n(&g_attn_static_ptr[dev], __ATOMIC_ACQUIRE);
+    if (!scratch) {
         // set-up, once per device, with that device current: the array's name is only a host-side
-        // stand-in in host code; the kernel needs the device address
+        // stand-in in host code; the kernel needs the device address.  Two host threads may both get here:
+        // they compute the same two values, and the address is published last (release), so a thread
+        // that sees it also sees the SM count.  The cached address belongs to this process's CUDA
+        // context: after cudaDeviceReset the library must be reloaded.
         float *p = NULL;
         const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_attn_static_scratch);
         if (e != cudaSuccess || !p) {
@@ -571,15 +575,15 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
         }
         int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); sms = 148; }
-        g_attn_static_sms[dev] = sms;
-        g_attn_static_ptr[dev] = p;
+        __atomic_store_n(&g_attn_static_sms[dev], sms, __ATOMIC_RELAXED);
+        __atomic_store_n(&g_attn_static_ptr[dev], p, __ATOMIC_RELEASE);
+        scratch = p;
     }
-    float *scratch = g_attn_static_ptr[dev];
 
     const int group = num_heads / num_kv_heads;
     const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 && group <= ATTN_G &&
                       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 && (kv_batch_stride % 4) == 0;
-    if (splits <= 0) {                                  // same rule as ckb200_attention_decode_splits
+    if (splits <= 0) {                                  // two CTAs per SM, at least 64 keys per split; the attn_splits tune key is not consulted here
         const long long base = (long long)batch * num_kv_heads;
         splits = (int)((2LL * g_attn_static_sms[dev] + base - 1) / base);
         const int max_by_tokens = (kv_tokens + 63) / 64;

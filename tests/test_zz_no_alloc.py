@@ -8,7 +8,8 @@ fixed 4 MiB array inside the library and therefore needs only inputs and outputs
 
 The test calls it through the C ABI twice in a row (different context lengths, so the second
 call runs over the first call's leftovers in the shared array) and checks each result against
-the ordinary entry point, then checks that an oversized request is refused with a clear error.
+the ordinary entry point and against the CPU oracle, checks that the calls left the amount of free
+device memory unchanged, then checks that an oversized request is refused with a clear error.
 It is collected last so that a failure here cannot hide any other test.
 """
 from __future__ import annotations
@@ -37,8 +38,15 @@ def _run(ck, torch, fn_static: bool, q, kc, vc, tokens, splits, stream):
     return rc, out.cpu().numpy()
 
 
-def test_static_scratch_attention_matches_allocating_entry_point(ck):
+def _free_device_bytes(torch):
+    free, _total = torch.cuda.mem_get_info()
+    return free
+
+
+def test_static_scratch_attention_matches_allocating_entry_point(ck, orc):
     import torch
+
+    import cases
 
     dev = torch.device("cuda", 0)
     stream = torch.cuda.Stream(device=dev)
@@ -52,12 +60,19 @@ def test_static_scratch_attention_matches_allocating_entry_point(ck):
         splits = ck.ckb200_attention_decode_splits(batch, kvh, tokens)
         assert splits > 1, "the case must exercise the scratch"
         rc_ref, want = _run(ck, torch, False, q, kc, vc, tokens, splits, stream)
-        rc, got = _run(ck, torch, True, q, kc, vc, tokens, splits, stream)
+        rc, got = _run(ck, torch, True, q, kc, vc, tokens, splits, stream)      # first call on the device: looks the array up
         assert rc_ref == 0 and rc == 0
         assert np.isfinite(got).all()
         assert float(np.max(np.abs(got - want))) <= 1e-4
+        free_before = _free_device_bytes(torch)
         rc, got_auto = _run(ck, torch, True, q, kc, vc, tokens, 0, stream)      # split count chosen by the entry point
+        rc2, got_again = _run(ck, torch, True, q, kc, vc, tokens, splits, stream)
+        assert _free_device_bytes(torch) == free_before, "the entry point must not allocate device memory"
         assert rc == 0 and float(np.max(np.abs(got_auto - want))) <= 1e-4
+        assert rc2 == 0 and np.array_equal(got_again, got)
+        for b in range(batch):                                                  # and directly against the CPU oracle
+            cpu = cases.attention_decode(orc, "oracle_", q[b].cpu().numpy(), kc[b].cpu().numpy(), vc[b].cpu().numpy(), tokens)
+            assert float(np.max(np.abs(got[b] - cpu))) <= 1e-4
 
 
 def test_static_scratch_rejects_oversized_request(ck):

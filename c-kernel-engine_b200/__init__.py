@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 
-from . import synth, tp  # noqa: F401
+from . import model_api, synth, tp  # noqa: F401
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libckb200.so"

@@ -84,42 +84,9 @@ class CpuModel:
         return self._matvec(lib, self.lm_head, h)
 
 
-class CfgStruct(C.Structure):
-    _fields_ = [(n, C.c_int) for n in ("embed_dim", "num_heads", "num_kv_heads", "head_dim", "intermediate_size", "num_layers", "vocab_size", "max_seq_len")] + \
-               [("rms_eps", C.c_float), ("rope_theta", C.c_float)] + \
-               [(n, C.c_int) for n in ("fmt_q", "fmt_k", "fmt_v", "fmt_o", "fmt_gate_up", "fmt_down", "fmt_lm_head", "fmt_embedding", "tie_embeddings", "batch", "tp_rank", "tp_size")]
-
-
-def make_cfg(cfg: dict, batch=1, tp_rank=0, tp_size=1) -> CfgStruct:
-    s = CfgStruct()
-    for k, v in cfg.items():
-        setattr(s, k, v)
-    s.fmt_embedding = cfg["fmt_lm_head"]
-    s.tie_embeddings = 1
-    s.batch, s.tp_rank, s.tp_size = batch, tp_rank, tp_size
-    return s
-
-
-def bind_model_api(lib):
-    lib.ckb200_model_create.restype = C.c_void_p
-    lib.ckb200_model_create.argtypes = [C.POINTER(CfgStruct)]
-    lib.ckb200_model_free.argtypes = [C.c_void_p]
-    lib.ckb200_model_free.restype = None
-    lib.ckb200_model_upload_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
-    lib.ckb200_model_tensor_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
-    lib.ckb200_model_tensor_bytes.restype = C.c_size_t
-    lib.ckb200_model_kv_device.argtypes = [C.c_void_p, C.c_int, C.c_int]
-    lib.ckb200_model_kv_device.restype = C.c_void_p
-    lib.ckb200_model_set_pos.argtypes = [C.c_void_p, C.c_int]
-    lib.ckb200_model_get_pos.argtypes = [C.c_void_p]
-    lib.ckb200_model_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
-    lib.ckb200_model_decode_repeat.argtypes = [C.c_void_p, C.c_int]
-    lib.ckb200_model_fill_synthetic.argtypes = [C.c_void_p, C.c_ulonglong]
-    lib.ckb200_model_fill_kv_synthetic.argtypes = [C.c_void_p, C.c_int, C.c_ulonglong]
-    lib.ckb200_model_weight_bytes.argtypes = [C.c_void_p]
-    lib.ckb200_model_weight_bytes.restype = C.c_size_t
-    lib.ckb200_copy_to_device.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
-    lib.ckb200_copy_to_host.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+# the ctypes view of the executor's C interface lives in the package (bench.py uses it too)
+_model_api = cases.load_package().model_api
+CfgStruct, make_cfg, bind_model_api = _model_api.CfgStruct, _model_api.make_cfg, _model_api.bind_model_api
 
 
 def upload_whole_model(lib, handle, cpu: CpuModel, batch: int):

@@ -46,6 +46,26 @@ def sweep(fmt: str):
     return [(m, synth.k_for(fmt, k), k) for (m, k) in synth.SWEEP_SHAPES]
 
 
+def sweep_config():
+    """The workload both arms (this library on the GPU, the reference on the host cores) are timed on."""
+    return {"workload": "quant-format GEMV sweep, Q4_K x Q8_K, batch 1",
+            "shapes": [[m, k] for m, k, _ in sweep("q4_k")],
+            "inputs": "Q4_K weights with fp16 d~U(0,0.02), dmin~U(0,0.01), uniform random scale and quant bytes; x fp32 N(0,1) quantised to Q8_K; "
+                      "K = 896 zero-padded to 1024"}
+
+
+vptr, fptr = pkg.model_api.vptr, pkg.model_api.fptr
+
+
+def cpu_quantize_q8_k(lib, prefix, x):
+    """quantize_row_q8_k of a CPU library (the reference build or the oracle port)."""
+    out = np.zeros(synth.row_bytes("q8_k", x.size), dtype=np.uint8)
+    f = getattr(lib, prefix + "quantize_row_q8_k")
+    f.restype = None
+    f(fptr(np.ascontiguousarray(x)), vptr(out), C.c_int(x.size))
+    return out
+
+
 def measured_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -117,16 +137,13 @@ def run_reference(args, rank: int):
     if ref is None:
         ref, kind = loader.load_oracle(), "port"
         threads = 1
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import cases
-
     shapes = sweep("q4_k")
     prefix = "" if kind == "reference" else "oracle_"
     work = []
     for m, k, k_raw in shapes:
         w = synth.make_weights("q4_k", m, k, seed=0)
         x = synth.make_x(k, seed=0, k_valid=k_raw if k_raw != k else None)
-        xq = cases.quantize_q8_k(ref, prefix, x)
+        xq = cpu_quantize_q8_k(ref, prefix, x)
         y = np.zeros(m, dtype=np.float32)
         work.append((m, k, w, xq, y))
     if kind == "reference":
@@ -139,7 +156,7 @@ def run_reference(args, rank: int):
 
     def step():
         for m, k, w, xq, y in work:
-            fn(cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(m), C.c_int(k))
+            fn(fptr(y), vptr(w), vptr(xq), C.c_int(m), C.c_int(k))
 
     for _ in range(args.warmup):
         step()
@@ -153,8 +170,8 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "quant-format GEMV sweep, Q4_K, batch 1", "shapes": [[m, k] for m, k, _ in shapes],
-                   "path": "gemv_q4_k_q8_k_parallel_dispatch on the reference thread pool" if kind == "reference" else "scalar port"},
+        "config": sweep_config(),
+        "path": "gemv_q4_k_q8_k_parallel_dispatch on the reference thread pool" if kind == "reference" else "scalar port",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -171,9 +188,6 @@ def cpu_baseline_sample(budget_s: float = 12.0):
     kind = "reference" if ref is not None else "port"
     if ref is None:
         ref, threads = loader.load_oracle(), 1
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import cases
-
     prefix = "" if kind == "reference" else "oracle_"
     if kind == "reference":
         ref.ck_parallel_decode_init()
@@ -184,9 +198,9 @@ def cpu_baseline_sample(budget_s: float = 12.0):
     total_b, total_t, used = 0, 0.0, []
     for m, k, k_raw in sweep("q4_k"):
         w = synth.make_weights("q4_k", m, k, seed=0)
-        xq = cases.quantize_q8_k(ref, prefix, synth.make_x(k, seed=0, k_valid=k_raw if k_raw != k else None))
+        xq = cpu_quantize_q8_k(ref, prefix, synth.make_x(k, seed=0, k_valid=k_raw if k_raw != k else None))
         y = np.zeros(m, dtype=np.float32)
-        args = (cases.fptr(y), cases.vptr(w), cases.vptr(xq), C.c_int(m), C.c_int(k))
+        args = (fptr(y), vptr(w), vptr(xq), C.c_int(m), C.c_int(k))
         fn(*args)
         reps, t0 = 0, time.perf_counter()
         while True:
@@ -210,14 +224,12 @@ LLAMA3_70B = dict(embed_dim=8192, num_heads=64, num_kv_heads=8, head_dim=128, in
                   max_seq_len=4352, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
 
 
-def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None):
-    """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens."""
+def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None, keep_logits=None):
+    """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens.
+    With keep_logits (a list) the logits of one extra step at position ctx are appended to it as a device tensor."""
     import torch
 
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import cases
-    import step_oracle as so
-
+    so = pkg.model_api
     so.bind_model_api(lib)
     st = so.make_cfg(cfg, batch=batch, tp_rank=tp_rank, tp_size=tp_size)
     handle = lib.ckb200_model_create(C.byref(st))
@@ -227,13 +239,14 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1
         return {"error": msg}
     try:
         if tp_size > 1:
-            lib.ckb200_model_use_tp.argtypes = [C.c_void_p]
             lib.ckb200_model_use_tp(handle)
-        assert lib.ckb200_model_fill_synthetic(handle, 1 + tp_rank) == 0
+        # the same seed on every rank: the replicated tensors (norm weights, LM head) must agree, and a rank's shard of the
+        # others is random data either way
+        assert lib.ckb200_model_fill_synthetic(handle, 1) == 0
         assert lib.ckb200_model_fill_kv_synthetic(handle, ctx, 2) == 0
         ids = np.full(batch, 11, dtype=np.int32)
         launches0 = lib.ckb200_launch_count()
-        assert lib.ckb200_model_decode(handle, cases.vptr(ids), None) == 0          # eager warm-up + capture + first replay
+        assert lib.ckb200_model_decode(handle, vptr(ids), None) == 0          # eager warm-up + capture + first replay
         launches = (lib.ckb200_launch_count() - launches0) // 2
         assert lib.ckb200_model_decode_repeat(handle, 3) == 0
         assert lib.ckb200_synchronize() == 0
@@ -260,8 +273,12 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1
         t0 = time.perf_counter()
         n_e2e = max(5, steps // 2)
         for _ in range(n_e2e):
-            assert lib.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0
+            assert lib.ckb200_model_decode(handle, vptr(ids), vptr(logits)) == 0
         e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
+        if keep_logits is not None:
+            assert lib.ckb200_model_set_pos(handle, ctx) == 0
+            assert lib.ckb200_model_decode(handle, vptr(ids), vptr(logits)) == 0
+            keep_logits.append(torch.from_numpy(logits[0].copy()).to(torch.device("cuda", torch.cuda.current_device())))
         return {"model_shape": name, "batch": batch, "context": ctx, "tp": tp_size, "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
                 "weight_bytes": int(wbytes), "kv_bytes": int(kv_bytes), "hbm_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peak,
                 "e2e_tok_s": batch * 1e3 / e2e_ms, "e2e_ms_per_token": e2e_ms}
@@ -270,6 +287,24 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1
 
 
 # ------------------------------------------------------------------------------------- CUDA arm
+
+# DRAM traffic of the Q4_K GEMV kernels relative to their algorithmic bytes, from the ncu capture summarised in
+# profiles/gemv_q4k_pair_14336x4096.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that
+# launch).  Traffic grows with the bytes streamed (every weight byte is read once), so a step's traffic is this ratio times its bytes.
+Q4K_DRAM_TRAFFIC_RATIO = 0.999
+
+# sweep name -> (weight format, resident layout, device entry point)
+SWEEPS = {
+    "q4_k": ("q4_k", None, "ckb200_dev_gemv_q4_k_q8_k"),
+    "q6_k_planar": ("q6_k", "planar", "ckb200_dev_gemv_q6_k_planar_q8_k"),
+    "q6_k_reference_layout": ("q6_k", None, "ckb200_dev_gemv_q6_k_q8_k"),
+    "q8_0_planar": ("q8_0", "planar", "ckb200_dev_gemv_q8_0_planar_q8_0"),
+    "q8_0_reference_layout": ("q8_0", None, "ckb200_dev_gemv_q8_0_q8_0"),
+    "q5_0_planar": ("q5_0", "planar", "ckb200_dev_gemv_q5_0_planar_q8_0"),
+    "q5_0_reference_layout": ("q5_0", None, "ckb200_dev_gemv_q5_0_q8_0"),
+}
+DEFAULT_SWEEPS = ["q4_k", "q6_k_planar", "q6_k_reference_layout", "q8_0_planar", "q8_0_reference_layout"]
+
 
 def run_cuda(args, rank: int, world: int, local_rank: int):
     import torch
@@ -285,8 +320,6 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         raise RuntimeError(lib.ckb200_last_error_message().decode())
     lib.ckb200_launch_count.restype = C.c_longlong
     lib.ckb200_stream.restype = C.c_void_p
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import cases
 
     dev = torch.device("cuda", local_rank)
     stream = torch.cuda.Stream(device=dev)             # graphs cannot be captured on the default stream
@@ -294,18 +327,20 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
     sp = C.c_void_p(stream.cuda_stream)
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(max(0, args.streams - 1))]
 
-    fmts = ["q4_k"] + (["q6_k", "q8_0", "q5_0"] if args.detail else [])
-    gemv_dev = {"q4_k": lib.ckb200_dev_gemv_q4_k_q8_k, "q6_k": lib.ckb200_dev_gemv_q6_k_planar_q8_k, "q8_0": lib.ckb200_dev_gemv_q8_0_planar_q8_0,
-                "q5_0": lib.ckb200_dev_gemv_q5_0_planar_q8_0}
-    lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
-    lib.ckb200_q8_0_planar_bytes.restype = C.c_size_t
-    lib.ckb200_q5_0_planar_bytes.restype = C.c_size_t
-    quant_dev = {"q4_k": lib.ckb200_dev_quantize_q8_k, "q6_k": lib.ckb200_dev_quantize_q8_k, "q8_0": lib.ckb200_dev_quantize_q8_0,
-                 "q5_0": lib.ckb200_dev_quantize_q8_0}
+    names = list(DEFAULT_SWEEPS) + (["q5_0_planar", "q5_0_reference_layout"] if args.detail else [])
+    if world > 1:
+        names = ["q4_k"]                                # the scaling runs time the headline sweep only
+    planar_fns = {"q6_k": (lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar),
+                  "q8_0": (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar),
+                  "q5_0": (lib.ckb200_q5_0_planar_bytes, lib.ckb200_dev_q5_0_to_planar)}
+    for size_fn, _ in planar_fns.values():
+        size_fn.restype = C.c_size_t
 
     results = {}
-    host_w = {}
-    for fmt in fmts:
+    for name in names:
+        fmt, layout, entry = SWEEPS[name]
+        gemv = getattr(lib, entry)
+        quant = lib.ckb200_dev_quantize_q8_0 if fmt in ("q8_0", "q5_0") else lib.ckb200_dev_quantize_q8_k
         plan = []
         for m, k, k_raw in sweep(fmt):
             w_host = synth.make_weights(fmt, m, k, seed=rank)          # every rank holds its own shard of rows
@@ -313,10 +348,8 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             copies = max(2, -(-L2_BYTES_X4 // nbytes))
             slot = (nbytes + 255) & ~255
             src = torch.from_numpy(w_host).to(dev)
-            if fmt in ("q6_k", "q8_0", "q5_0"):            # resident Q6_K / Q8_0 / Q5_0 weights live in the library's row-planar layout (same bits)
-                size_fn, conv_fn = {"q6_k": (lib.ckb200_q6_k_planar_bytes, lib.ckb200_dev_q6_k_to_planar),
-                                    "q8_0": (lib.ckb200_q8_0_planar_bytes, lib.ckb200_dev_q8_0_to_planar),
-                                    "q5_0": (lib.ckb200_q5_0_planar_bytes, lib.ckb200_dev_q5_0_to_planar)}[fmt]
+            if layout == "planar":                     # resident Q6_K / Q8_0 / Q5_0 weights in the library's row-planar layout (same bits)
+                size_fn, conv_fn = planar_fns[fmt]
                 nbytes = size_fn(m, k)
                 slot = (nbytes + 255) & ~255
                 planar = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -328,14 +361,12 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             x = torch.from_numpy(synth.make_x(k, seed=rank, k_valid=k_raw if k_raw != k else None)).to(dev)
             xq = torch.empty(synth.row_bytes("q8_0" if fmt in ("q8_0", "q5_0") else "q8_k", k) + 64, dtype=torch.uint8, device=dev)
             y = torch.empty(copies, m, dtype=torch.float32, device=dev)
-            rc = quant_dev[fmt](C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, sp)
-            assert rc == 0
-            plan.append(dict(m=m, k=k, copies=copies, slot=slot, wbuf=wbuf, xq=xq, y=y, bytes=synth.gemv_bytes(fmt, m, k)))
-            if fmt == "q4_k":
-                host_w[(m, k)] = w_host
+            assert quant(C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), 1, k, sp) == 0
+            plan.append(dict(m=m, k=k, copies=copies, slot=slot, wbuf=wbuf, xq=xq, y=y, bytes=synth.gemv_bytes(fmt, m, k),
+                             w_host=w_host if name == "q4_k" else None))
         torch.cuda.synchronize()
 
-        def step(plan=plan, fmt=fmt, nstreams=1):
+        def step(plan=plan, gemv=gemv, nstreams=1):
             """One pass over the sweep.  The launches are independent GEMVs (own weights, own output); with nstreams > 1
             they are dealt round-robin to that many streams, which a graph capture turns into parallel branches."""
             lanes = [stream] + side_streams[:nstreams - 1]
@@ -345,13 +376,24 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             for p in plan:
                 base = p["wbuf"].data_ptr()
                 for c in range(p["copies"]):
-                    rc = gemv_dev[fmt](C.c_void_p(p["y"][c].data_ptr()), C.c_void_p(base + c * p["slot"]),
-                                       C.c_void_p(p["xq"].data_ptr()), p["m"], p["k"], C.c_void_p(lanes[i % len(lanes)].cuda_stream))
+                    rc = gemv(C.c_void_p(p["y"][c].data_ptr()), C.c_void_p(base + c * p["slot"]),
+                              C.c_void_p(p["xq"].data_ptr()), p["m"], p["k"], C.c_void_p(lanes[i % len(lanes)].cuda_stream))
                     i += 1
                     if rc != 0:
                         raise RuntimeError(lib.ckb200_last_error_message().decode())
             for s2 in lanes[1:]:
                 stream.wait_stream(s2)
+
+        def timed_graph(g, reps):
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(reps):
+                g.replay()
+            b.record(stream)
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
 
         launches_before = lib.ckb200_launch_count()
         step()                                             # un-captured: sets kernel attributes, warms caches
@@ -370,7 +412,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
-        sampler = ClockSampler(local_rank) if fmt == "q4_k" else None
+        sampler = ClockSampler(local_rank) if name == "q4_k" else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -385,62 +427,55 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             ms = float(t.item())
         step_bytes = sum(p["bytes"] * p["copies"] for p in plan)
         serial_gbs = None
-        if args.streams > 1 and fmt == "q4_k":             # the same step as one dependent chain on one stream, for the record
+        if args.streams > 1:                               # the same step as ONE dependent chain on one stream at full occupancy
             g1 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g1, stream=stream):
                 step(nstreams=1)
-            g1.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for _ in range(max(3, args.steps // 2)):
-                g1.replay()
-            b.record(stream)
-            torch.cuda.synchronize()
-            serial_gbs = step_bytes * max(3, args.steps // 2) / a.elapsed_time(b) / 1e6
+            serial_gbs = step_bytes / timed_graph(g1, max(3, args.steps // 2)) / 1e6
         per_shape = {}
         if args.detail:
             for p in plan:                                 # per-shape timing, graph of one rotation of that shape
                 g = torch.cuda.CUDAGraph()
                 lib.ckb200_tune_set(b"gemv_occ_cap", 1 if args.streams > 1 else 0)
                 with torch.cuda.graph(g, stream=stream):
-                    step(plan=[p], fmt=fmt, nstreams=args.streams)
+                    step(plan=[p], nstreams=args.streams)
                 lib.ckb200_tune_set(b"gemv_occ_cap", 0)
-                g.replay()
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                for _ in range(max(3, args.steps // 2)):
-                    g.replay()
-                b.record(stream)
-                torch.cuda.synchronize()
-                t_ms = a.elapsed_time(b) / max(3, args.steps // 2)
+                t_ms = timed_graph(g, max(3, args.steps // 2))
                 per_shape[f"{p['m']}x{p['k']}"] = {"gbs": p["bytes"] * p["copies"] / t_ms / 1e6, "us_per_launch": t_ms * 1e3 / p["copies"]}
         rc = lib.ckb200_synchronize()
         if rc != 0:
             raise RuntimeError(lib.ckb200_last_error_message().decode())
-        results[fmt] = dict(ms=ms, step_bytes=step_bytes, launches=launches_per_step, clocks=clocks, per_shape=per_shape, plan=plan, serial_gbs=serial_gbs)
+        results[name] = dict(ms=ms, step_bytes=step_bytes, launches=launches_per_step, clocks=clocks, per_shape=per_shape, serial_gbs=serial_gbs,
+                             plan=plan if name == "q4_k" else None, rotation="/".join(str(p["copies"]) for p in plan))
+        del graph
+        if name != "q4_k":
+            del plan
+            torch.cuda.empty_cache()
 
-    # ---- end to end through the reference-named host-pointer entry point (Q4_K)
-    e2e = None
+    # ---- end to end through the reference-named host-pointer entry point (Q4_K): resident weights (registered once, as after
+    # model load) on rotating copies like the device leg, Q8_K activations in from pinned host memory, fp32 outputs back to it
     plan = results["q4_k"]["plan"]
     fn = lib.gemv_q4_k_q8_k
     fn.restype = None
-    pinned = []
     lib.ckb200_host_alloc.restype = C.c_void_p
+    pinned = []
     for p in plan:
-        w_host = host_w[(p["m"], p["k"])]
-        assert lib.ckb200_register_weights(cases.vptr(w_host), C.c_size_t(w_host.nbytes)) == 0
+        rot = max(2, min(p["copies"], 16))                          # at most 16 host copies per shape (more than L2 in total for every shape)
+        w_rot = np.ascontiguousarray(np.tile(p["w_host"], rot))
+        assert lib.ckb200_register_weights(vptr(w_rot), C.c_size_t(w_rot.nbytes)) == 0
         xq_bytes = synth.row_bytes("q8_k", p["k"])
         hx = lib.ckb200_host_alloc(C.c_size_t(xq_bytes))
         hy = lib.ckb200_host_alloc(C.c_size_t(4 * p["m"]))
         xq_host = p["xq"][:xq_bytes].cpu().numpy()
         C.memmove(hx, xq_host.ctypes.data, xq_bytes)
-        pinned.append((p, w_host, hx, hy, xq_bytes))
+        pinned.append(dict(p=p, w=w_rot, rot=rot, one=p["w_host"].nbytes, hx=hx, hy=hy, xq_bytes=xq_bytes))
+    e2e_calls = [0]
 
     def e2e_step():
-        for p, w_host, hx, hy, _ in pinned:
-            fn(C.c_void_p(hy), cases.vptr(w_host), C.c_void_p(hx), p["m"], p["k"])
+        i = e2e_calls[0]
+        for q in pinned:
+            fn(C.c_void_p(q["hy"]), C.c_void_p(q["w"].ctypes.data + (i % q["rot"]) * q["one"]), C.c_void_p(q["hx"]), q["p"]["m"], q["p"]["k"])
+        e2e_calls[0] = i + 1
 
     for _ in range(max(3, args.warmup)):
         e2e_step()
@@ -461,13 +496,15 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         e2e_ms = float(t.item())
     e2e_bytes = sum(p["bytes"] for p in plan)
     e2e = {"value": world * e2e_bytes * e2e_steps / e2e_ms / 1e6, "unit": UNIT,
-           "h2d_bytes_per_step": sum(x[4] for x in pinned), "d2h_bytes_per_step": sum(4 * x[0]["m"] for x in pinned),
-           "call": "gemv_q4_k_q8_k(y_host, W_host_registered, x_q8_host, M, K), one call per sweep shape per step",
+           "h2d_bytes_per_step": sum(q["xq_bytes"] for q in pinned), "d2h_bytes_per_step": sum(4 * q["p"]["m"] for q in pinned),
+           "call": "gemv_q4_k_q8_k(y_host, W_host_registered, x_q8_host, M, K), one call per sweep shape per step, weights rotating over "
+                   + "/".join(str(q["rot"]) for q in pinned) + " resident copies",
            "ms_per_step": e2e_ms / e2e_steps}
-    for p, w_host, hx, hy, _ in pinned:
-        lib.ckb200_unregister_weights(cases.vptr(w_host))
-        lib.ckb200_host_free(C.c_void_p(hx))
-        lib.ckb200_host_free(C.c_void_p(hy))
+    for q in pinned:
+        lib.ckb200_unregister_weights(vptr(q["w"]))
+        lib.ckb200_host_free(C.c_void_p(q["hx"]))
+        lib.ckb200_host_free(C.c_void_p(q["hy"]))
+    pinned.clear()
     pkg.check(lib)
 
     decode_tp = None
@@ -475,19 +512,32 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         try:
             pkg.tp.setup(lib, rank, world, dev, p2p_floats=32 * LLAMA3_70B["embed_dim"])
             decode_tp = []
-            for p2p, fused, how in ((1, 1, "peer-memory exchange fused into the residual-add + RMSNorm + quantise kernel"),
-                                    (1, 0, "one-shot push all-reduce kernel over peer memory"), (0, 0, "NCCL all-reduce")):
+            kept = []
+            forms = ((1, 1, "peer-memory exchange fused into the residual-add + RMSNorm + quantise kernel"),
+                     (1, 0, "one-shot push all-reduce kernel over peer memory"), (0, 0, "NCCL all-reduce"))
+            for p2p, fused, how in forms:
                 lib.ckb200_tune_set(b"tp_p2p", p2p)
                 lib.ckb200_tune_set(b"tp_fused_norm", fused)
                 d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}", LLAMA3_70B, 4096, 20, measured_peak()[0],
-                                 batch=1, tp_rank=rank, tp_size=world, dist=dist)
+                                 batch=1, tp_rank=rank, tp_size=world, dist=dist, keep_logits=kept)
                 d["exchange"] = how
+                if "error" not in d and len(kept) == len(decode_tp) + 1:
+                    # correctness carried with the number: the replicated LM head must see the same hidden state on every rank, and the
+                    # three exchange forms must agree with each other
+                    mine = kept[-1]
+                    hi, lo = mine.clone(), mine.clone()
+                    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                    first = kept[0].double()
+                    cos = float((first @ mine.double()) / (first.norm() * mine.double().norm()))
+                    d["logits_check"] = {"max_abs_spread_across_ranks": float((hi - lo).abs().max().item()), "finite": bool(torch.isfinite(mine).all().item()),
+                                         "cosine_vs_first_form_rank0": cos, "max_abs_logit": float(mine.abs().max().item())}
                 decode_tp.append(d)
             lib.ckb200_tune_set(b"tp_p2p", 1)
             lib.ckb200_tune_set(b"tp_fused_norm", 1)
             d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}, batch 32", LLAMA3_70B, 4096, 4, measured_peak()[0],
                              batch=32, tp_rank=rank, tp_size=world, dist=dist)
-            d["exchange"] = "peer-memory exchange fused into the residual-add + RMSNorm + quantise kernel"
+            d["exchange"] = "default"
             decode_tp.append(d)
         except Exception as exc:
             decode_tp = {"error": repr(exc)}
@@ -498,30 +548,35 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         peak, peak_kind = measured_peak()
         gbs_one = r["step_bytes"] * args.steps / r["ms"] / 1e6
         value = gbs_one * world
+        sweeps = {}
+        for name, rr in results.items():
+            g = rr["step_bytes"] * args.steps / rr["ms"] / 1e6
+            sweeps[name] = {"gbs": g, "frac": g / peak, "serial_chain_gbs": rr["serial_gbs"], "frac_serial_chain": rr["serial_gbs"] / peak if rr["serial_gbs"] else None,
+                            "bytes_per_step": rr["step_bytes"], "launches_per_step": int(rr["launches"]), "rotation": rr["rotation"], "entry_point": SWEEPS[name][2]}
+            if rr["per_shape"]:
+                sweeps[name]["per_shape"] = rr["per_shape"]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": r["ms"] / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 dot (dp4a), fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "quant-format GEMV sweep, Q4_K x Q8_K, batch 1",
-                       "shapes": [[p["m"], p["k"]] for p in r["plan"]],
-                       "l2": "every launch reads a different weight copy; copies per shape total > 4x L2 (rotation "
-                             + "/".join(str(p["copies"]) for p in r["plan"]) + ")",
+            "config": sweep_config(),
+            "method": {"l2": "every launch reads a different weight copy; copies per shape total > 4x L2 (rotation " + r["rotation"] + ")",
                        "sharding": "each rank streams its own shard of rows; no collective in the data path",
                        "timing": "CUDA graph of one step replayed; CUDA events on the launching stream; max over ranks",
                        "schedule": f"the launches of a step are independent GEMVs and are dealt round-robin to {args.streams} stream(s) "
                                    "(parallel branches of the graph, one CTA per SM per launch), as the step executor does with q/k/v; "
-                                   "serial_chain_gbs is the same step as one dependent chain on one stream at full occupancy"},
+                                   "frac_serial_chain is the same step as one dependent chain on one stream at full occupancy"},
             "serial_chain_gbs": (r["serial_gbs"] * world) if r["serial_gbs"] else None,
             "clocks": {k: r["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if r["clocks"] else None,
             "e2e": e2e,
-            "gpu_launches": int(r["launches"] * args.steps),
+            "gpu_launches": int(sum(rr["launches"] for rr in results.values()) * args.steps),
             "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "Q4_K GEMV (all sweep shapes)",
-                         "bytes_per_step": r["step_bytes"]},
+                         "frac_serial_chain": r["serial_gbs"] / peak if r["serial_gbs"] else None,
+                         "traffic": Q4K_DRAM_TRAFFIC_RATIO * r["step_bytes"],
+                         "traffic_note": "DRAM bytes per step = measured DRAM / algorithmic ratio of one launch (ncu, 14336x4096) x the step's algorithmic bytes",
+                         "peak_kind": peak_kind, "kernel": "Q4_K GEMV (all sweep shapes)", "bytes_per_step": r["step_bytes"]},
+            "sweeps": sweeps,
         }
-        if args.detail:
-            line["detail"] = {f: {"gbs": results[f]["step_bytes"] * args.steps / results[f]["ms"] / 1e6, "per_shape": results[f]["per_shape"]}
-                              for f in results}
         if world == 1 and not args.no_decode:
             try:
                 line["decode"] = [decode_bench(lib, "Qwen2-0.5B shape, Q4_K_M mix", QWEN2_05B, 1024, 200, peak),
@@ -752,10 +807,7 @@ def run_attention_only(args):
 
 def run_decode_only(args):
     """Eager (un-captured) decode steps of a model shape: the command behind the decode launch lists in profiles/."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import cases
-    import step_oracle as so
-
+    so = pkg.model_api
     lib = pkg.load_lib()
     assert lib.ckb200_init(0) == 0
     so.bind_model_api(lib)
@@ -769,7 +821,7 @@ def run_decode_only(args):
     lib.ckb200_launch_count.restype = C.c_longlong
     n0 = lib.ckb200_launch_count()
     for _ in range(args.steps):
-        assert lib.ckb200_model_decode(h, cases.vptr(ids), None) == 0
+        assert lib.ckb200_model_decode(h, vptr(ids), None) == 0
     assert lib.ckb200_synchronize() == 0
     print(json.dumps({"decode_only": args.decode_only, "batch": args.batch, "steps": args.steps, "launches_per_step": (lib.ckb200_launch_count() - n0) // args.steps}))
     lib.ckb200_model_free(h)
@@ -781,7 +833,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--detail", action="store_true", help="also time Q6_K / Q8_0 and every shape on its own")
+    ap.add_argument("--detail", action="store_true", help="also time the Q5_0 sweeps and every shape on its own")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step tokens/s section")
     ap.add_argument("--streams", type=int, default=8, help="streams the independent GEMV launches of a sweep step are dealt to")

@@ -1,4 +1,4 @@
-"""Tensor-parallel decode on 2 and 4 GPUs: one process per GPU, the all-reduce after o_proj and down_proj (peer-memory
+"""Tensor-parallel decode on 2, 4 and 8 GPUs: one process per GPU, the all-reduce after o_proj and down_proj (peer-memory
 push kernel checked against NCCL, then used by the step),
 logits of every rank against the unsharded CPU step.  Skipped on a box with fewer GPUs."""
 from __future__ import annotations
@@ -101,7 +101,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, cfg: dict):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_decode(tmp_path, orc, world):
     import torch.multiprocessing as mp
 
@@ -109,9 +109,8 @@ def test_tensor_parallel_decode(tmp_path, orc, world):
 
     if _gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    if world > 2 and os.environ.get("CKB200_TEST_TP4") != "1":
-        pytest.skip("the 4-rank case has not been run on hardware yet (no 4-GPU machine was available): set CKB200_TEST_TP4=1 to run it")
-    cfg = TP_CFG if world == 2 else dict(TP_CFG, num_kv_heads=4)
+    # whole KV heads per rank, and per-rank attention and FFN widths that are multiples of 256
+    cfg = TP_CFG if world == 2 else dict(TP_CFG, num_heads=4 * world, num_kv_heads=world, intermediate_size=256 * world)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]

@@ -33,6 +33,7 @@
 #include "../../include/ckb200_model.h"
 #include "launch.h"
 #include "runtime.h"
+#include "step_fused.h"
 
 /* tensor-core GEMM of gemm_tc.cu: wf 0 = Q4_K rows, 1 = Q6_K row-planar; -1 when the shape is not handled.  The workspace
  * (activation tiles + split-K partial sums) is the model's own: a pointer recorded in the step's graph must not come from
@@ -76,6 +77,9 @@ struct CKB200Model {
     float *rope_cos, *rope_sin;
     /* activations */
     float *x, *prev, *q, *k, *v, *att, *o, *gu, *logits, *attn_scratch;
+    float *x2;              /* second residual row of the fused step (each fused launch reads one and writes the other) */
+    float *mf;              /* fp32 SwiGLU output of the fused step, round256(Il) wide, tail zero */
+    int *attn_counters;     /* arrival counters of the attention kernel's in-launch split merge */
     uint8_t *hq, *aq, *mq;
     int32_t *tokens_dev, *pos_dev;
     int32_t *tokens_pinned;
@@ -229,6 +233,9 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     DEV_ALLOC(m->hq, (size_t)B * (m->Da / 32) * 34 + (size_t)B * (m->Da / 256) * 292 + 256);
     DEV_ALLOC(m->aq, (size_t)B * (m->Ala / 32) * 34 + (size_t)B * (m->Ala / 256) * 292 + 256);
     DEV_ALLOC(m->mq, (size_t)B * ((m->Il + 255) / 256) * 292 * 2 + 256);
+    DEV_ALLOC(m->x2, (size_t)B * m->Da * sizeof(float));
+    DEV_ALLOC(m->mf, (size_t)B * round256(m->Il) * sizeof(float));
+    DEV_ALLOC(m->attn_counters, ckb200_attention_decode_counter_bytes(B, m->Hkvl) + 256);
     DEV_ALLOC(m->tokens_dev, (size_t)B * sizeof(int32_t));
     DEV_ALLOC(m->pos_dev, 256);
     if (B >= 16) {
@@ -275,6 +282,9 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     cudaMemsetAsync(m->prev, 0, (size_t)B * m->Da * sizeof(float), st);
     cudaMemsetAsync(m->o, 0, (size_t)B * m->Da * sizeof(float), st);
     cudaMemsetAsync(m->pos_dev, 0, 256, st);
+    cudaMemsetAsync(m->x2, 0, (size_t)B * m->Da * sizeof(float), st);
+    cudaMemsetAsync(m->mf, 0, (size_t)B * round256(m->Il) * sizeof(float), st);
+    cudaMemsetAsync(m->attn_counters, 0, ckb200_attention_decode_counter_bytes(B, m->Hkvl) + 256, st);
     ckb200_dev_rope_precompute_cache_split(m->rope_cos, m->rope_sin, S, m->d, cfg->rope_theta, NULL);
     if (ckb_check_cuda((int)cudaStreamSynchronize(st), "model init")) { ckb200_model_free(m); return NULL; }
     return m;
@@ -286,7 +296,7 @@ void ckb200_model_free(CKB200Model *m)
     cudaStreamSynchronize(ckb_stream(NULL));
     if (m->graph_ready) cudaGraphExecDestroy(m->graph);
     void *ptrs[] = { m->arena, m->planar_arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
-                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch, m->gemm_ws };
+                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch, m->gemm_ws, m->x2, m->mf, m->attn_counters };
     for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     for (int i = 0; i < 2; ++i) {
@@ -543,8 +553,165 @@ static int ensure_planar(CKB200Model *m, void *st)
     return 0;
 }
 
+/* ------------------------------------------------------------------ the fused step (one sequence, one GPU)
+ *
+ * Five launches per layer instead of thirteen (step_fused.cu):
+ *   1. q | k | v projections  <- prologue: x += delta, RMSNorm, Q8_K;  epilogue: RoPE, KV-cache store
+ *   2. attention over the cache, the split merge done by the last CTA of each kv head
+ *   3. o projection            <- prologue: Q8_K of the attention row
+ *   4. gate | up projection    <- prologue: x += o, RMSNorm, Q8_K;     epilogue: SwiGLU
+ *   5. down projection         <- prologue: Q8_K of the SwiGLU row
+ * and the LM head with the final norm in its prologue and the position increment at its end.  The residual row ping-pongs
+ * between two buffers: every CTA of a launch reads the old row while the first CTA writes the new one. */
+
+static int fused_fmt(const Tensor *t) { return t->fmt == FMT_Q4K ? SG_FMT_Q4K : (t->fmt == FMT_Q6K && t->planar ? SG_FMT_Q6K_PLANAR : -1); }
+
+static int fused_step_ok(const CKB200Model *m)
+{
+    if (m->c.batch != 1 || m->c.tp_size != 1 || !ckb_tune_get("model_fused_step", 1)) return 0;
+    for (int l = 0; l < m->c.num_layers; ++l) {
+        static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
+        for (int i = 0; i < 6; ++i)
+            if (fused_fmt(&m->layers[l].t[which[i]]) < 0) return 0;
+    }
+    if (fused_fmt(&m->lm_head) < 0) return 0;
+    return m->d % 2 == 0 && m->Al % 2 == 0 && ckb_step_gemv_ctas_per_sm(m->Da / 256, SG_PRO_NORM) > 0 &&
+           ckb_step_gemv_ctas_per_sm(round256(m->Il) / 256, SG_PRO_QUANT) > 0 && ckb_step_gemv_ctas_per_sm(m->Ala / 256, SG_PRO_QUANT) > 0;
+}
+
+static void seg_set(StepSeg *sg, const Tensor *t, float *out, int epi)
+{
+    sg->fmt = fused_fmt(t);
+    sg->W = (const uint8_t *)(sg->fmt == SG_FMT_Q6K_PLANAR ? t->planar : t->w);
+    sg->out = out;
+    sg->M = t->rows;
+    sg->epi = epi;
+}
+
+/* CTAs of the grid dealt to the segments: one work item (the rows of one warp) per CTA while that fits the resident
+ * slots, else the slots in proportion to the segments' bytes */
+static int plan_and_launch(StepGemvParams *p, void *st)
+{
+    const int occ = ckb_step_gemv_ctas_per_sm(p->nb, p->pro);
+    if (occ <= 0) return ckb_fail(CKB_ERR_LIMIT, "fused step: rows of %d superblocks do not fit the kernel's shared memory", p->nb);
+    const int cap = ckb_sm_count() * occ;
+    int g4 = 2;
+    while (g4 < 32 && g4 < 2 * p->nb) g4 <<= 1;
+    const int g6 = g4 * 2 > 32 ? 32 : g4 * 2;
+    long items[3], total_items = 0;
+    double bytes[3], total_bytes = 0;
+    for (int i = 0; i < p->nseg; ++i) {
+        const int q6 = p->seg[i].fmt == SG_FMT_Q6K_PLANAR;
+        const int rpw = (32 / (q6 ? g6 : g4)) * 2;
+        items[i] = (p->seg[i].M + rpw - 1) / rpw;
+        bytes[i] = (double)p->seg[i].M * p->nb * (q6 ? 210 : 144);
+        total_items += items[i];
+        total_bytes += bytes[i];
+    }
+    int grid = 0;
+    for (int i = 0; i < p->nseg; ++i) {
+        long n = items[i];
+        if (total_items > cap) {
+            n = (long)((double)cap * bytes[i] / total_bytes);
+            if (n < 1) n = 1;
+            if (n > items[i]) n = items[i];
+        }
+        p->seg[i].cta0 = grid;
+        p->seg[i].ncta = (int)n;
+        grid += (int)n;
+    }
+    const int rc = ckb_launch_step_gemv(p, grid, st);
+    return rc == -1 ? ckb_fail(CKB_ERR_SHAPE, "fused step: shape not handled") : rc;
+}
+
+static int issue_step_fused(CKB200Model *m, void *st)
+{
+    const CKB200ModelConfig *c = &m->c;
+    const int L = c->num_layers;
+    int rc;
+    switch (m->emb.fmt) {
+        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
+        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
+        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
+    }
+    if (rc) return rc;
+    float *cur = m->x, *nxt = m->x2;
+    const float *delta = NULL;
+    StepGemvParams base;
+    memset(&base, 0, sizeof base);
+    base.cos_cache = m->rope_cos;
+    base.sin_cache = m->rope_sin;
+    base.pos = m->pos_dev;
+    base.head_dim = m->d;
+    base.max_seq = c->max_seq_len;
+    base.d_model = m->D;
+    base.eps = c->rms_eps;
+    for (int l = 0; l < L; ++l) {
+        Tensor *t = m->layers[l].t;
+        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + m->kv_batch_stride;
+        StepGemvParams p = base;
+        /* 1: q | k | v */
+        p.nseg = 3;
+        p.nb = m->Da / 256;
+        p.pro = SG_PRO_NORM;
+        p.x_in = cur;
+        p.delta = delta;
+        p.gamma = (const float *)t[CKB_T_LN1].w;
+        p.x_out = delta ? nxt : NULL;
+        seg_set(&p.seg[0], &t[CKB_T_WQ], m->q, SG_EPI_ROPE_Q);
+        seg_set(&p.seg[1], &t[CKB_T_WK], kc, SG_EPI_ROPE_K);
+        seg_set(&p.seg[2], &t[CKB_T_WV], vc, SG_EPI_STORE_V);
+        if ((rc = plan_and_launch(&p, st))) return rc;
+        if (delta) { float *tmp = cur; cur = nxt; nxt = tmp; }
+        /* 2: attention, merge inside */
+        if ((rc = ckb200_dev_attention_decode_fused(m->q, kc, vc, m->att, m->Ala, 1, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
+                                                    m->attn_splits, m->attn_scratch, m->attn_counters, m->pos_dev, NULL, 0, st))) return rc;
+        /* 3: o projection */
+        p = base;
+        p.nseg = 1;
+        p.nb = m->Ala / 256;
+        p.pro = SG_PRO_QUANT;
+        p.src = m->att;
+        seg_set(&p.seg[0], &t[CKB_T_WO], m->o, SG_EPI_STORE);
+        if ((rc = plan_and_launch(&p, st))) return rc;
+        /* 4: gate | up with SwiGLU */
+        p = base;
+        p.nseg = 1;
+        p.nb = m->Da / 256;
+        p.pro = SG_PRO_NORM;
+        p.x_in = cur;
+        p.delta = m->o;
+        p.gamma = (const float *)t[CKB_T_LN2].w;
+        p.x_out = nxt;
+        seg_set(&p.seg[0], &t[CKB_T_W1], m->mf, SG_EPI_SWIGLU);
+        if ((rc = plan_and_launch(&p, st))) return rc;
+        { float *tmp = cur; cur = nxt; nxt = tmp; }
+        /* 5: down projection */
+        p = base;
+        p.nseg = 1;
+        p.nb = round256(m->Il) / 256;
+        p.pro = SG_PRO_QUANT;
+        p.src = m->mf;
+        seg_set(&p.seg[0], &t[CKB_T_W2], m->prev, SG_EPI_STORE);
+        if ((rc = plan_and_launch(&p, st))) return rc;
+        delta = m->prev;
+    }
+    StepGemvParams p = base;
+    p.nseg = 1;
+    p.nb = m->Da / 256;
+    p.pro = SG_PRO_NORM;
+    p.x_in = cur;
+    p.delta = delta;
+    p.gamma = (const float *)m->final_gamma.w;
+    p.x_out = NULL;
+    p.pos_advance = m->pos_dev;
+    seg_set(&p.seg[0], &m->lm_head, m->logits, SG_EPI_STORE);
+    return plan_and_launch(&p, st);
+}
+
 static int issue_step(CKB200Model *m, void *st)
 {
+    if (fused_step_ok(m)) return issue_step_fused(m, st);
     const CKB200ModelConfig *c = &m->c;
     const int B = c->batch, L = c->num_layers;
     int rc;

@@ -20,6 +20,9 @@ __host__ __device__ inline int q4p_smem_bytes(int nb) { return ((nb * (Q4P_SLOTS
 
 struct Q4pX { uint32_t q, d, lo, hi; };
 
+// LOCAL_SRC: the Q8_K vector was just built by this CTA in shared memory (a fused quantising prologue) and is read with plain
+// loads; otherwise it is global memory written by an earlier kernel and comes through L2.
+template <bool LOCAL_SRC = false>
 __device__ __forceinline__ Q4pX q4p_stage_x(const uint8_t *xg, int nb, uint8_t *smem)
 {
     uint32_t *xq = reinterpret_cast<uint32_t *>(smem);
@@ -35,7 +38,8 @@ __device__ __forceinline__ Q4pX q4p_stage_x(const uint8_t *xg, int nb, uint8_t *
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int i = base + u * blockDim.x + threadIdx.x;
-            v[u] = i < total ? __ldcg(src + i) : 0u;       // through L2: the producer may overlap this kernel (programmatic launch)
+            if constexpr (LOCAL_SRC) v[u] = i < total ? src[i] : 0u;
+            else v[u] = i < total ? __ldcg(src + i) : 0u;  // through L2: the producer may overlap this kernel (programmatic launch)
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {

@@ -21,7 +21,8 @@ __host__ __device__ inline int ringx_smem_bytes(int fmt, int nb)
 }
 
 // Batched loads through L2 (__ldcg): the vector may have been written by a kernel that overlaps this one.
-template <int FMT>
+// LOCAL_SRC (Q8_K only): the vector was just built by this CTA in shared memory and is read with plain loads.
+template <int FMT, bool LOCAL_SRC = false>
 __device__ __forceinline__ RingX ring_stage_x(const uint8_t *xg, int nb, uint8_t *smem)
 {
     RingX r;
@@ -64,7 +65,8 @@ __device__ __forceinline__ RingX ring_stage_x(const uint8_t *xg, int nb, uint8_t
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int i = base + u * blockDim.x + threadIdx.x;
-                v[u] = i < total ? __ldcg(src + i) : 0u;
+                if constexpr (LOCAL_SRC) v[u] = i < total ? src[i] : 0u;
+                else v[u] = i < total ? __ldcg(src + i) : 0u;
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {

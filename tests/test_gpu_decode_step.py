@@ -79,3 +79,56 @@ def test_synthetic_fill_and_repeat(ck):
         assert ck.ckb200_model_get_pos(handle) == 26
     finally:
         ck.ckb200_model_free(handle)
+
+
+@pytest.mark.parametrize("cfg", [MINI_QWEN, MINI_LLAMA], ids=["mini-qwen", "mini-llama"])
+@pytest.mark.parametrize("pdl", [1, 0])
+def test_fused_step_matches_the_launch_per_op_step(ck, orc, cfg, pdl):
+    """One sequence on one GPU runs as five fused launches per layer (prologue: residual add + RMSNorm + Q8_K or plain Q8_K;
+    epilogue: RoPE + cache store or SwiGLU); the launch-per-op step (tune model_fused_step 0) is the same arithmetic, so the two
+    agree far inside the contract, and both match the CPU step.  With and without programmatic dependent launch."""
+    so.bind_model_api(ck)
+    cpu = so.CpuModel(cfg, seed=11)
+    start = 33
+    cpu.prefill_kv(start, seed=12)
+    V = cfg["vocab_size"]
+    tokens = [3, 250, 77, 8]
+    want = [cpu.decode(orc, tok, start + i) for i, tok in enumerate(tokens)]
+    got = {}
+    launches = {}
+    ck.ckb200_launch_count.restype = C.c_longlong
+    try:
+        ck.ckb200_tune_set(b"pdl", pdl)
+        for fused in (1, 0):
+            ck.ckb200_tune_set(b"model_fused_step", fused)
+            cpu2 = so.CpuModel(cfg, seed=11)
+            cpu2.prefill_kv(start, seed=12)
+            handle = ck.ckb200_model_create(C.byref(so.make_cfg(cfg, batch=1)))
+            assert handle, ck.ckb200_last_error_message()
+            try:
+                so.upload_whole_model(ck, handle, cpu2, 1)
+                assert ck.ckb200_model_set_pos(handle, start) == 0
+                outs = []
+                for i, tok in enumerate(tokens):
+                    ids = np.array([tok], dtype=np.int32)
+                    logits = np.full((1, V), np.nan, dtype=np.float32)
+                    n0 = ck.ckb200_launch_count()
+                    assert ck.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, ck.ckb200_last_error_message()
+                    if i == 0:
+                        launches[fused] = (ck.ckb200_launch_count() - n0) // 2      # the first call issues the step twice (warm-up, capture)
+                    outs.append(logits[0].copy())
+                    assert ck.ckb200_model_get_pos(handle) == start + i + 1
+                got[fused] = outs
+            finally:
+                ck.ckb200_model_free(handle)
+    finally:
+        ck.ckb200_tune_set(b"model_fused_step", 1)
+        ck.ckb200_tune_set(b"pdl", 1)
+    L = cfg["num_layers"]
+    assert launches[1] <= 5 * L + 2 < launches[0], launches
+    for i in range(len(tokens)):
+        for fused in (1, 0):
+            assert cosine(got[fused][i], want[i]) >= 0.9999, (fused, i)
+        scale = float(np.max(np.abs(want[i])))
+        assert float(np.max(np.abs(got[1][i] - got[0][i]))) <= 2e-3 * scale, i
+        assert cosine(got[1][i], got[0][i]) >= 0.99999, i

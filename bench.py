@@ -843,7 +843,13 @@ def main():
     ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
     ap.add_argument("--batch", type=int, default=1, help="sequences per step of --decode-only")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="set a kernel-variant switch of the library (ckb200_tune_set) before running")
     args = ap.parse_args()
+    if args.tune:
+        lib = pkg.load_lib()
+        for kv in args.tune:
+            key, _, val = kv.partition("=")
+            lib.ckb200_tune_set(key.encode(), int(val))
     if args.single:
         return run_single(args)
     if args.decode_only:

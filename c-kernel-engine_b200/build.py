@@ -21,7 +21,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
 ]
-NVCC_FLAGS += os.environ.get("CKB_NVCC_EXTRA", "").split()       # e.g. -DCKB_TC_PROFILE for the in-kernel cycle counters
+NVCC_FLAGS += os.environ.get("CKB_NVCC_EXTRA", "").split()       # e.g. -DCKB_TC_TRACE or -DCKB_STEP_TRACE for the in-kernel timeline recorders
 CC_FLAGS = ["-O2", "-fPIC", "-std=c11", "-Wall", "-Wextra", "-Wno-unused-parameter", f"-I{CUDA_HOME}/include"]
 
 

@@ -20,9 +20,26 @@ __device__ __forceinline__ void arq_keep_piece(float4 v, int i, int d_model, flo
     reinterpret_cast<float4 *>(row)[i] = v;
 }
 
+// gamma of the first block a warp will quantise (block `warp`), fetched before the dependency wait: the norm weights are
+// constants, and a load issued after the row statistics are known would put an L2 round trip on the critical path
+struct ArqGamma { float4 g0, g1; bool valid; };
+__device__ __forceinline__ ArqGamma arq_prefetch_gamma(const float *__restrict__ gamma, int d_model)
+{
+    ArqGamma g;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    g.g0 = g.g1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    g.valid = warp * QK_K + 8 * lane + 8 <= d_model && (reinterpret_cast<uintptr_t>(gamma) & 15) == 0;      // gamma holds d_model values
+    if (g.valid) {
+        const float4 *p = reinterpret_cast<const float4 *>(gamma + (size_t)warp * QK_K) + 2 * lane;
+        g.g0 = __ldg(p);
+        g.g1 = __ldg(p + 1);
+    }
+    return g;
+}
+
 // block-wide sum of squares -> rstd; one warp per 256-element block scales by gamma and quantises (row t of the output)
 __device__ __forceinline__ void arq_norm_quant(float ss, const float *row, float *red, const float *__restrict__ gamma, uint8_t *__restrict__ out_q8,
-                                               float *__restrict__ norm_out, int t, int d_model, int aligned, float eps)
+                                               float *__restrict__ norm_out, int t, int d_model, int aligned, float eps, const ArqGamma *pre = nullptr)
 {
     ss = group_sum<32>(ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -33,12 +50,21 @@ __device__ __forceinline__ void arq_norm_quant(float ss, const float *row, float
     const float mean = __fmul_rn(tot, __fdiv_rn(1.0f, (float)d_model));
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
     const int nb = aligned / QK_K;
+    const bool have_pre = pre != nullptr && pre->valid;
     for (int b = warp; b < nb; b += nw) {
+        float gv[8];
+        if (have_pre && b == warp) {
+            gv[0] = pre->g0.x; gv[1] = pre->g0.y; gv[2] = pre->g0.z; gv[3] = pre->g0.w;
+            gv[4] = pre->g1.x; gv[5] = pre->g1.y; gv[6] = pre->g1.z; gv[7] = pre->g1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gv[j] = b * QK_K + 8 * lane + j < d_model ? gamma[b * QK_K + 8 * lane + j] : 0.0f;
+        }
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int i = b * QK_K + 8 * lane + j;
-            v[j] = i < d_model ? __fmul_rn(__fmul_rn(row[i], rstd), gamma[i]) : 0.0f;
+            v[j] = i < d_model ? __fmul_rn(__fmul_rn(row[i], rstd), gv[j]) : 0.0f;
             if (norm_out) norm_out[(size_t)t * aligned + i] = v[j];
         }
         quantize_block_q8k(v, out_q8 + ((size_t)t * nb + b) * Q8K_BYTES, lane);

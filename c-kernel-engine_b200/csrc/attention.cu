@@ -315,7 +315,13 @@ __global__ void __launch_bounds__(128) attn_decode_generic_kernel(AttnParams p)
 
 using namespace ckb;
 
-extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream);     // attention_tile.cu
+// Set by the step executor around its attention call: within a decode step only the newest cache row is written and the device
+// position is stable, so the tile kernel may read both before its dependency wait (see attention_tile.cu).
+static int g_attn_early_rows = 0;
+extern "C" void ckb_attn_hint_early_rows(int on) { g_attn_early_rows = on; }
+
+extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream);
+extern "C" int ckb_launch_attn_cluster(const AttnParams *p, int batch, int ranks, void *stream);     // attention_tile.cu
 
 extern "C" size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits)
 {
@@ -357,7 +363,7 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
-    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0; p.early_rows = pos_dev != NULL && g_attn_early_rows;
     cudaStream_t st = ckb_stream(stream);
     const int group = num_heads / num_kv_heads;
     const bool fast = (aligned_head_dim == 64 || aligned_head_dim == 128) && num_heads % num_kv_heads == 0 &&
@@ -429,7 +435,16 @@ extern "C" int ckb200_dev_attention_decode_fused(const float *q, const float *k_
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
     p.splits = splits;
-    p.counters = counters; p.q8_out = (uint8_t *)q8_out; p.out_stride = out_stride; p.q8_cols = q8_cols; p.kv_f16 = 0;
+    p.counters = counters; p.q8_out = (uint8_t *)q8_out; p.out_stride = out_stride; p.q8_cols = q8_cols; p.kv_f16 = 0; p.early_rows = pos_dev != NULL && g_attn_early_rows;
+    if (!q8_out && ckb_tune_get("attn_cluster", 1)) {
+        // the CTAs of a kv head as one thread-block cluster: the split merge happens in distributed shared memory
+        static int unavailable = 0;
+        if (!unavailable) {
+            const int rc = ckb_launch_attn_cluster(&p, batch, ckb_tune_get("attn_cluster_ranks", 8), ckb_stream(stream));
+            if (rc >= 0) return rc;
+            unavailable = 1;
+        }
+    }
     return ckb_launch_attn_tile(&p, batch, ckb_stream(stream));
 }
 
@@ -476,7 +491,7 @@ extern "C" int ckb200_dev_attention_decode_f16cache_ws(const float *q, const uin
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
     p.splits = splits;
-    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 1;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 1; p.early_rows = 0;
     cudaStream_t st = ckb_stream(stream);
     const int rc = ckb_launch_attn_tile(&p, batch, st);
     if (rc) return rc;
@@ -596,7 +611,7 @@ extern "C" int ckb200_dev_attention_decode_static(const float *q, const float *k
     p.kv_batch_stride = kv_batch_stride;
     p.H = num_heads; p.Hkv = num_kv_heads; p.kv_tokens = kv_tokens; p.cap = cache_capacity; p.ad = aligned_head_dim;
     p.scale = 1.0f / sqrtf((float)head_dim);
-    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0;
+    p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 0; p.early_rows = 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (!fast) {
         if (aligned_head_dim > ATTN_GEN_MAXD) return ckb_fail(CKB_ERR_LIMIT, "attention decode: aligned_head_dim %d > %d", aligned_head_dim, ATTN_GEN_MAXD);

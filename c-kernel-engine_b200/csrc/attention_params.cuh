@@ -22,6 +22,7 @@ struct AttnParams {
     int out_stride;        // floats between the out rows of consecutive sequences (>= H * ad)
     int q8_cols;           // elements quantised per row (multiple of 256, <= out_stride; the row's tail must be zero)
     int kv_f16;            // the caches hold IEEE fp16 (k and v then point at uint16 data, strides counted in elements)
+    int early_rows;        // tile kernel: cache rows before the newest one and *pos_ptr may be read before the dependency wait
 };
 
 __device__ __forceinline__ int attn_kv_tokens(const AttnParams &p) { return p.pos_ptr ? min(__ldcg(p.pos_ptr) + 1, p.cap) : p.kv_tokens; }

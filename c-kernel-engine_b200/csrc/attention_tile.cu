@@ -25,6 +25,16 @@
 
 namespace ckb {
 
+#ifdef CKB_STEP_TRACE
+// Tuning aid (build with -DCKB_STEP_TRACE): global-timer stamps of the first CTA and of the CTA that merges the first kv head.
+static __device__ unsigned long long at_trace[8 * 4096];
+static __device__ unsigned at_trace_n;
+__device__ __forceinline__ unsigned long long at_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define AT_TRACE(slot, k) do { if ((slot) < 4096u) at_trace[8 * (slot) + (k)] = at_now(); } while (0)
+#else
+#define AT_TRACE(slot, k) do { } while (0)
+#endif
+
 constexpr int AT_NW = 8;            // warps per CTA
 constexpr int AT_KT = 64;           // keys per tile
 constexpr int AT_STAGES = 3;
@@ -50,7 +60,28 @@ __device__ __forceinline__ float4 at_row_piece(uint32_t row_addr, int idx)
     }
 }
 
-template <int AD, int EB>
+// CLUSTER: the CTAs that share a kv head form one thread-block cluster.  Tiles are dealt round-robin to the ranks, and the
+// partial results (running max, sum, unnormalised output per head) never leave the chip: each CTA leaves them in its shared
+// memory, the cluster synchronises, and every rank combines one slice of the output by reading its peers' shared memory
+// (distributed shared memory).  No scratch buffer, no arrival counter, no second pass through L2.
+__device__ __forceinline__ uint32_t at_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t at_cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void at_cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a float at byte offset `off` of the shared window of cluster rank `rank`
+__device__ __forceinline__ float at_ld_peer(uint32_t local_addr, uint32_t rank)
+{
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int AD, int EB, bool CLUSTER>
 __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, int *__restrict__ dev_err)
 {
     constexpr int C = AD / (4 * AT_LPK);           // float4 pieces per lane (1 for 64, 2 for 128)
@@ -69,32 +100,56 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
     const int sub = lane / AT_LPK, li = lane % AT_LPK;
     const int group = p.H / p.Hkv, h0 = kvh * group;
 
+    unsigned tr = 0xffffffffu;
+#ifdef CKB_STEP_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) tr = atomicAdd(&at_trace_n, 1u);
+    AT_TRACE(tr, 0);
+#endif
     if (threadIdx.x == 0) {
         for (int i = 0; i < AT_STAGES; ++i) { mbar_init(AT_FULL(i), 1); mbar_init(AT_EMPTY(i), AT_NW); }
         mbar_fence_init();
     }
     pdl_trigger();
     __syncthreads();
-    pdl_wait();           // q, the newest cache row and the position come from kernels that may still have been running
-
+    // early_rows (set by the step executor): within a decode step only the newest cache row is written, and the position changes
+    // only at the end of a step, after which the next step starts with a fully ordered launch.  The position is then read and the
+    // tiles that end before the newest row are requested BEFORE the dependency wait: their HBM latency overlaps the predecessor.
+    if (!p.early_rows) {
+        pdl_wait();       // q, the newest cache row and the position come from kernels that may still have been running
+        AT_TRACE(tr, 1);
+    }
     const int kv_tokens = attn_kv_tokens(p);
     const int ntiles_all = (kv_tokens + AT_KT - 1) / AT_KT;
-    const int tiles_per_split = (ntiles_all + p.splits - 1) / p.splits;
-    const int tile0 = split * tiles_per_split;
-    const int ntiles = max(0, min(ntiles_all, tile0 + tiles_per_split) - tile0);
+    // plain: split s owns a contiguous run of tiles; cluster: rank r owns tiles r, r + size, r + 2 size, ...
+    const int tiles_per_split = CLUSTER ? 0 : (ntiles_all + p.splits - 1) / p.splits;
+    const int tile_stride = CLUSTER ? (int)gridDim.x : 1;
+    const int tile0 = CLUSTER ? split : split * tiles_per_split;
+    const int ntiles = CLUSTER ? (ntiles_all > split ? (ntiles_all - split + tile_stride - 1) / tile_stride : 0)
+                               : max(0, min(ntiles_all, tile0 + tiles_per_split) - tile0);
     const uint8_t *kbase = reinterpret_cast<const uint8_t *>(p.k) + ((size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD) * EB;
     const uint8_t *vbase = reinterpret_cast<const uint8_t *>(p.v) + ((size_t)seq * p.kv_batch_stride + (size_t)kvh * p.cap * AD) * EB;
 
     auto issue_tile = [&](int i) {                 // one thread: both copies of tile i of this split
-        const int st = i % AT_STAGES, t_begin = (tile0 + i) * AT_KT;
+        const int st = i % AT_STAGES, t_begin = (tile0 + i * tile_stride) * AT_KT;
         const uint32_t bytes = (uint32_t)min(AT_KT, kv_tokens - t_begin) * ROW;
         const uint32_t dst = s_base + st * at_stage_bytes<AD>();
         mbar_arrive_expect_tx(AT_FULL(st), 2 * bytes);
         bulk_g2s(dst, kbase + (size_t)t_begin * ROW, bytes, AT_FULL(st));
         bulk_g2s(dst + AT_KT * ROW, vbase + (size_t)t_begin * ROW, bytes, AT_FULL(st));
     };
-    if (threadIdx.x == 0)
-        for (int i = 0; i < min(ntiles, AT_STAGES - 1); ++i) issue_tile(i);
+    {
+        const int first = min(ntiles, AT_STAGES - 1);
+        int early = 0;                             // leading tiles that do not reach the newest row
+        if (p.early_rows) {
+            while (early < first && (tile0 + early * tile_stride) * AT_KT + AT_KT <= kv_tokens - 1) ++early;
+            if (threadIdx.x == 0)
+                for (int i = 0; i < early; ++i) issue_tile(i);
+            pdl_wait();
+            AT_TRACE(tr, 1);
+        }
+        if (threadIdx.x == 0)
+            for (int i = early; i < first; ++i) issue_tile(i);
+    }
 
     // query of the group's heads, pre-scaled, this lane's dimensions
     float4 q[G][C];
@@ -126,7 +181,7 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;      // warp 0 follows its lane 0
         if (!ok || !mbar_wait_spin(AT_FULL(st), (uint32_t)((i / AT_STAGES) & 1))) { ok = false; break; }
 
-        const int t_tile = (tile0 + i) * AT_KT;
+        const int t_tile = (tile0 + i * tile_stride) * AT_KT;
         const int nvalid = min(AT_KT, kv_tokens - t_tile);
         const uint32_t ks = s_base + st * at_stage_bytes<AD>() + (uint32_t)(warp * KPW) * ROW, vs = ks + AT_KT * ROW;
 
@@ -219,9 +274,19 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         __syncwarp();
         if (lane == 0) mbar_arrive(AT_EMPTY(st));
     }
+    AT_TRACE(tr, 2);
     if (!ok && lane == 0) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
     ok = __syncthreads_and(ok ? 1 : 0) != 0;       // every issued copy has landed and been consumed when all warps got here
-    if (!ok) return;
+    if constexpr (!CLUSTER) {
+        if (!ok) return;
+    } else if (!ok) {                              // a cluster member may not leave before the cluster barriers: contribute nothing
+        m_run = -INFINITY;
+        l_run = 0.0f;
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int c = 0; c < C; ++c) acc[h][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 
     // ---- the two key streams of the warp share (m, l): add their accumulators; then merge the warps through shared memory
     float *merge_s = reinterpret_cast<float *>(smem);              // [AT_NW][G][AD + 4], over the (now idle) stages
@@ -245,6 +310,44 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         }
     }
     __syncthreads();
+    if constexpr (CLUSTER) {
+        // this CTA's result per head -> cta_s[h][0 .. AD) unnormalised output, [AD] max, [AD + 1] sum (behind the warps' area)
+        float *cta_s = merge_s + AT_NW * G * (AD + 4);
+        for (int i = threadIdx.x; i < group * (AD + 2); i += blockDim.x) {
+            const int h = i / (AD + 2), c = i - h * (AD + 2);       // c < AD: an output column, AD: the max, AD + 1: the sum
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < AT_NW; ++w) mm = fmaxf(mm, merge_s[(w * G + h) * (AD + 4) + AD]);
+            float val = mm;
+            if (c != AD) {
+                val = 0.0f;
+#pragma unroll
+                for (int w = 0; w < AT_NW; ++w) {
+                    const float mw = merge_s[(w * G + h) * (AD + 4) + AD];
+                    val += merge_s[(w * G + h) * (AD + 4) + c] * (mw == -INFINITY ? 0.0f : expf(mw - mm));
+                }
+            }
+            cta_s[h * (AD + 4) + c] = val;
+        }
+        at_cluster_sync();                          // every rank's cta_s is complete and visible
+        const uint32_t nrank = at_cluster_size(), me = at_cluster_rank();
+        const uint32_t cta_a = smem_u32(cta_s);
+        for (int i = (int)me * blockDim.x + threadIdx.x; i < group * AD; i += (int)nrank * blockDim.x) {
+            const int h = i / AD, c = i - h * AD;
+            float mm = -INFINITY;
+            for (uint32_t r = 0; r < nrank; ++r) mm = fmaxf(mm, at_ld_peer(cta_a + 4u * (uint32_t)(h * (AD + 4) + AD), r));
+            float ll = 0.0f, a = 0.0f;
+            for (uint32_t r = 0; r < nrank; ++r) {
+                const float mr = at_ld_peer(cta_a + 4u * (uint32_t)(h * (AD + 4) + AD), r);
+                const float f = mr == -INFINITY ? 0.0f : expf(mr - mm);
+                ll += at_ld_peer(cta_a + 4u * (uint32_t)(h * (AD + 4) + AD + 1), r) * f;
+                a += at_ld_peer(cta_a + 4u * (uint32_t)(h * (AD + 4) + c), r) * f;
+            }
+            p.out[(size_t)seq * p.out_stride + (size_t)(h0 + h) * AD + c] = ll > 0.0f ? a / ll : 0.0f;
+        }
+        at_cluster_sync();                          // nobody's shared memory goes away while a peer may still read it
+        return;
+    }
     const bool fused = p.counters != nullptr;
     for (int i = threadIdx.x; i < group * AD; i += blockDim.x) {
         const int h = i / AD, c = i - h * AD;
@@ -268,6 +371,7 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
             if (c == 0) { dst[AD] = mm; dst[AD + 1] = ll; }
         }
     }
+    AT_TRACE(tr, 3);
     if (!fused) return;
 
     // ---- fused tail 1: the last split CTA of this (sequence, kv head) merges the partials of its heads
@@ -284,6 +388,9 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
         }
         __syncthreads();
         if (!s_last) return;
+#ifdef CKB_STEP_TRACE
+        if (kvh == 0 && seq == 0 && threadIdx.x == 0 && at_trace_n > 0) { tr = at_trace_n - 1; AT_TRACE(tr, 4); }
+#endif
         __threadfence();
         const int S = p.splits;
         const float *part0 = p.part + ((size_t)seq * p.H + h0) * S * (AD + 2);
@@ -320,6 +427,9 @@ __global__ void __launch_bounds__(AT_NW * 32, 1) attn_tile_kernel(AttnParams p, 
             p.out[(size_t)seq * p.out_stride + (size_t)(h0 + h) * AD + c] = ((a0 + a1) + (a2 + a3)) * f_s[G * S + h];
         }
     }
+#ifdef CKB_STEP_TRACE
+    if (kvh == 0 && seq == 0 && threadIdx.x == 0) AT_TRACE(tr, 5);
+#endif
     if (!p.q8_out) return;
 
     // ---- fused tail 2: the last kv head of this sequence quantises the finished row for the consumer GEMV
@@ -357,15 +467,61 @@ static int launch_attn_tile(const AttnParams *p, int batch, void *stream)
     const int smem = at_smem_bytes<AD>();
     static int attr_set = 0;
     if (!attr_set) {
-        if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_tile_kernel<AD, EB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention smem attr")) return CKB_ERR_CUDA;
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_tile_kernel<AD, EB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention smem attr")) return CKB_ERR_CUDA;
         attr_set = 1;
     }
     const dim3 grid(p->splits, p->Hkv, batch);
-    return launch_pdl("attn_tile", attn_tile_kernel<AD, EB>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word());
+    return launch_pdl("attn_tile", attn_tile_kernel<AD, EB, false>, grid, dim3(AT_NW * 32), (size_t)smem, (cudaStream_t)stream, *p, ckb_device_error_word());
 }
 
 extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream)
 {
     if (p->kv_f16) return p->ad == 64 ? launch_attn_tile<64, 2>(p, batch, stream) : launch_attn_tile<128, 2>(p, batch, stream);
     return p->ad == 64 ? launch_attn_tile<64, 4>(p, batch, stream) : launch_attn_tile<128, 4>(p, batch, stream);
+}
+
+// The cluster form: grid (ranks, Hkv, batch) with the `ranks` CTAs of a kv head in one cluster (8: the portable maximum; 16 needs the
+// opt-in attribute and is used when the device can place such a cluster).  Returns -1 when the launch is not possible here.
+template <int AD, int EB>
+static int launch_attn_cluster(const AttnParams *p, int batch, int ranks, void *stream)
+{
+    const int smem = at_smem_bytes<AD>();
+    auto kernel = attn_tile_kernel<AD, EB, true>;
+    static int attr_set = 0, max16 = -1;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) { cudaGetLastError(); return -1; }
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { cudaGetLastError(); max16 = 0; }
+        attr_set = 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ranks, p->Hkv, batch);
+    cfg.blockDim = dim3(AT_NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ckb_tune_get("pdl", 1) ? 2 : 1;
+    if (ranks > 8) {
+        if (max16 < 0) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+            max16 = n;
+        }
+        if (max16 <= 0) return -1;
+    }
+    if (cudaLaunchKernelEx(&cfg, kernel, *p, ckb_device_error_word()) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return ckb_check_launch("attn_cluster");
+}
+
+// ranks: CTAs per kv head (8 or 16).  -1: not available (the caller uses the split form).
+extern "C" int ckb_launch_attn_cluster(const AttnParams *p, int batch, int ranks, void *stream)
+{
+    if (p->kv_f16) return p->ad == 64 ? launch_attn_cluster<64, 2>(p, batch, ranks, stream) : launch_attn_cluster<128, 2>(p, batch, ranks, stream);
+    return p->ad == 64 ? launch_attn_cluster<64, 4>(p, batch, ranks, stream) : launch_attn_cluster<128, 4>(p, batch, ranks, stream);
 }

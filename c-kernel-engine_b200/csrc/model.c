@@ -38,6 +38,7 @@
 /* tensor-core GEMM of gemm_tc.cu: wf 0 = Q4_K rows, 1 = Q6_K row-planar; -1 when the shape is not handled.  The workspace
  * (activation tiles + split-K partial sums) is the model's own: a pointer recorded in the step's graph must not come from
  * the library's grow-on-demand pool, which any later call may free and regrow. */
+void ckb_attn_hint_early_rows(int on);      /* attention.cu */
 int ckb_launch_gemm_tc_ws(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *ws,
                           size_t ws_bytes, void *stream);
 size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
@@ -568,15 +569,15 @@ static int fused_fmt(const Tensor *t) { return t->fmt == FMT_Q4K ? SG_FMT_Q4K : 
 
 static int fused_step_ok(const CKB200Model *m)
 {
-    if (m->c.batch != 1 || m->c.tp_size != 1 || !ckb_tune_get("model_fused_step", 1)) return 0;
+    if (m->c.batch != 1 || m->c.tp_size != 1 || !ckb_tune_get("model_fused_step", 0)) return 0;
     for (int l = 0; l < m->c.num_layers; ++l) {
         static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
         for (int i = 0; i < 6; ++i)
             if (fused_fmt(&m->layers[l].t[which[i]]) < 0) return 0;
     }
     if (fused_fmt(&m->lm_head) < 0) return 0;
-    return m->d % 2 == 0 && m->Al % 2 == 0 && ckb_step_gemv_ctas_per_sm(m->Da / 256, SG_PRO_NORM) > 0 &&
-           ckb_step_gemv_ctas_per_sm(round256(m->Il) / 256, SG_PRO_QUANT) > 0 && ckb_step_gemv_ctas_per_sm(m->Ala / 256, SG_PRO_QUANT) > 0;
+    return m->d % 2 == 0 && m->d / 2 <= 128 && m->Al % 2 == 0 && ckb_step_gemv_ctas_per_sm(m->Da / 256, SG_PRO_GLOBAL, 0) > 0 &&
+           ckb_step_gemv_ctas_per_sm(round256(m->Il) / 256, SG_PRO_GLOBAL, 0) > 0 && ckb_step_gemv_ctas_per_sm(m->Ala / 256, SG_PRO_GLOBAL, 0) > 0;
 }
 
 static void seg_set(StepSeg *sg, const Tensor *t, float *out, int epi)
@@ -588,33 +589,55 @@ static void seg_set(StepSeg *sg, const Tensor *t, float *out, int epi)
     sg->epi = epi;
 }
 
-/* CTAs of the grid dealt to the segments: one work item (the rows of one warp) per CTA while that fits the resident
- * slots, else the slots in proportion to the segments' bytes */
+/* Deals the CTAs of the grid to the segments and launches.  In the latency regime (few work items) a segment gets about one
+ * CTA per SM of its share of the machine, each with as few busy warps as that allows, and long rows are split over the warps
+ * of a CTA so that every warp has one load round; in the streaming regime the resident slots are shared out by bytes. */
 static int plan_and_launch(StepGemvParams *p, void *st)
 {
-    const int occ = ckb_step_gemv_ctas_per_sm(p->nb, p->pro);
+    /* matrices of a few megabytes: the launch is a chain of latencies, and the rehearsing instantiation pays */
+    double launch_bytes = 0;
+    for (int i = 0; i < p->nseg; ++i) launch_bytes += (double)p->seg[i].M * p->nb * (p->seg[i].fmt == SG_FMT_Q6K_PLANAR ? 210 : 144);
+    p->dry_run = ckb_tune_get("step_dry_run", 1) && launch_bytes <= (double)ckb_tune_get("step_dry_run_max_mb", 24) * 1048576.0;
+    int occ = ckb_step_gemv_ctas_per_sm(p->nb, p->pro, p->dry_run);
     if (occ <= 0) return ckb_fail(CKB_ERR_LIMIT, "fused step: rows of %d superblocks do not fit the kernel's shared memory", p->nb);
-    const int cap = ckb_sm_count() * occ;
+    const int occ_cap = ckb_tune_get("step_occ_cap", 0);
+    if (occ_cap > 0 && occ_cap < occ) occ = occ_cap;
+    const int sms = ckb_sm_count(), cap = sms * occ;
     int g4 = 2;
     while (g4 < 32 && g4 < 2 * p->nb) g4 <<= 1;
     const int g6 = g4 * 2 > 32 ? 32 : g4 * 2;
-    long items[3], total_items = 0;
+    long want[3], total_want = 0;
     double bytes[3], total_bytes = 0;
     for (int i = 0; i < p->nseg; ++i) {
-        const int q6 = p->seg[i].fmt == SG_FMT_Q6K_PLANAR;
-        const int rpw = (32 / (q6 ? g6 : g4)) * 2;
-        items[i] = (p->seg[i].M + rpw - 1) / rpw;
-        bytes[i] = (double)p->seg[i].M * p->nb * (q6 ? 210 : 144);
-        total_items += items[i];
+        bytes[i] = (double)p->seg[i].M * p->nb * (p->seg[i].fmt == SG_FMT_Q6K_PLANAR ? 210 : 144);
         total_bytes += bytes[i];
+    }
+    for (int i = 0; i < p->nseg; ++i) {
+        StepSeg *sg = &p->seg[i];
+        const int q6 = sg->fmt == SG_FMT_Q6K_PLANAR;
+        const int rpw = (32 / (q6 ? g6 : g4)) * 2;
+        const long items = (sg->M + rpw - 1) / rpw;
+        const int passes = ckb_step_gemv_passes(p->nb, sg->fmt);
+        long share = (long)((double)sms * bytes[i] / total_bytes + 0.5);       /* SMs of this segment at one CTA per SM */
+        if (share < 1) share = 1;
+        sg->split = passes > 1 && passes <= 8 && items * passes <= (long)cap * 8 && ckb_tune_get("step_split", 1);
+        if (sg->split) {
+            const int ipc = 8 / passes;
+            want[i] = (items + ipc - 1) / ipc;                                   /* one round per CTA */
+        } else {
+            long wpc = (items + share - 1) / share;                              /* busy warps per CTA */
+            if (wpc > 8) wpc = 8;
+            want[i] = (items + wpc - 1) / wpc;
+        }
+        total_want += want[i];
     }
     int grid = 0;
     for (int i = 0; i < p->nseg; ++i) {
-        long n = items[i];
-        if (total_items > cap) {
+        long n = want[i];
+        if (total_want > cap) {
             n = (long)((double)cap * bytes[i] / total_bytes);
             if (n < 1) n = 1;
-            if (n > items[i]) n = items[i];
+            if (n > want[i]) n = want[i];
         }
         p->seg[i].cta0 = grid;
         p->seg[i].ncta = (int)n;
@@ -622,6 +645,36 @@ static int plan_and_launch(StepGemvParams *p, void *st)
     }
     const int rc = ckb_launch_step_gemv(p, grid, st);
     return rc == -1 ? ckb_fail(CKB_ERR_SHAPE, "fused step: shape not handled") : rc;
+}
+
+/* The quantised input of a fused launch: built inside the launch when the row is short (every CTA repeats the work, which is
+ * cheaper than a launch), else by the stand-alone kernel into `xq_buf`.  kind: SG_PRO_NORM (x row `cur` += delta, in place
+ * when stand-alone, else into `nxt`) or SG_PRO_QUANT (fp32 row `src`).  Returns 1 when the residual row moved to `nxt`. */
+static int fused_input(CKB200Model *m, StepGemvParams *p, int kind, float *cur, float *nxt, const float *delta, const float *gamma, const float *src,
+                       uint8_t *xq_buf, void *st, int *rc)
+{
+    *rc = 0;
+    if (kind == SG_PRO_NORM) {
+        if (p->nb <= SG_NORM_MAX_NB && p->nb <= ckb_tune_get("step_norm_max_nb", SG_NORM_MAX_NB)) {
+            p->pro = SG_PRO_NORM;
+            p->x_in = cur;
+            p->delta = delta;
+            p->gamma = gamma;
+            p->x_out = delta ? nxt : NULL;
+            return delta != NULL;
+        }
+        *rc = ckb200_dev_add_rmsnorm_q8k(cur, delta, gamma, xq_buf, NULL, 1, m->D, m->Da, m->c.rms_eps, st);
+    } else {
+        if (p->nb <= ckb_tune_get("step_quant_max_nb", 8)) {       /* one block per warp: beyond that the blocks of a warp queue up */
+            p->pro = SG_PRO_QUANT;
+            p->src = src;
+            return 0;
+        }
+        *rc = ckb200_dev_quantize_q8_k(src, xq_buf, 1, p->nb * 256, st);
+    }
+    p->pro = SG_PRO_GLOBAL;
+    p->xq = xq_buf;
+    return 0;
 }
 
 static int issue_step_fused(CKB200Model *m, void *st)
@@ -653,45 +706,41 @@ static int issue_step_fused(CKB200Model *m, void *st)
         /* 1: q | k | v */
         p.nseg = 3;
         p.nb = m->Da / 256;
-        p.pro = SG_PRO_NORM;
-        p.x_in = cur;
-        p.delta = delta;
-        p.gamma = (const float *)t[CKB_T_LN1].w;
-        p.x_out = delta ? nxt : NULL;
+        int moved = fused_input(m, &p, SG_PRO_NORM, cur, nxt, delta, (const float *)t[CKB_T_LN1].w, NULL, m->hq, st, &rc);
+        if (rc) return rc;
         seg_set(&p.seg[0], &t[CKB_T_WQ], m->q, SG_EPI_ROPE_Q);
         seg_set(&p.seg[1], &t[CKB_T_WK], kc, SG_EPI_ROPE_K);
         seg_set(&p.seg[2], &t[CKB_T_WV], vc, SG_EPI_STORE_V);
         if ((rc = plan_and_launch(&p, st))) return rc;
-        if (delta) { float *tmp = cur; cur = nxt; nxt = tmp; }
+        if (moved) { float *tmp = cur; cur = nxt; nxt = tmp; }
         /* 2: attention, merge inside */
+        ckb_attn_hint_early_rows(ckb_tune_get("model_attn_early_rows", 1));
         if ((rc = ckb200_dev_attention_decode_fused(m->q, kc, vc, m->att, m->Ala, 1, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
                                                     m->attn_splits, m->attn_scratch, m->attn_counters, m->pos_dev, NULL, 0, st))) return rc;
+        ckb_attn_hint_early_rows(0);
         /* 3: o projection */
         p = base;
         p.nseg = 1;
         p.nb = m->Ala / 256;
-        p.pro = SG_PRO_QUANT;
-        p.src = m->att;
+        fused_input(m, &p, SG_PRO_QUANT, NULL, NULL, NULL, NULL, m->att, m->aq, st, &rc);
+        if (rc) return rc;
         seg_set(&p.seg[0], &t[CKB_T_WO], m->o, SG_EPI_STORE);
         if ((rc = plan_and_launch(&p, st))) return rc;
         /* 4: gate | up with SwiGLU */
         p = base;
         p.nseg = 1;
         p.nb = m->Da / 256;
-        p.pro = SG_PRO_NORM;
-        p.x_in = cur;
-        p.delta = m->o;
-        p.gamma = (const float *)t[CKB_T_LN2].w;
-        p.x_out = nxt;
+        moved = fused_input(m, &p, SG_PRO_NORM, cur, nxt, m->o, (const float *)t[CKB_T_LN2].w, NULL, m->hq, st, &rc);
+        if (rc) return rc;
         seg_set(&p.seg[0], &t[CKB_T_W1], m->mf, SG_EPI_SWIGLU);
         if ((rc = plan_and_launch(&p, st))) return rc;
-        { float *tmp = cur; cur = nxt; nxt = tmp; }
+        if (moved) { float *tmp = cur; cur = nxt; nxt = tmp; }
         /* 5: down projection */
         p = base;
         p.nseg = 1;
         p.nb = round256(m->Il) / 256;
-        p.pro = SG_PRO_QUANT;
-        p.src = m->mf;
+        fused_input(m, &p, SG_PRO_QUANT, NULL, NULL, NULL, NULL, m->mf, m->mq, st, &rc);
+        if (rc) return rc;
         seg_set(&p.seg[0], &t[CKB_T_W2], m->prev, SG_EPI_STORE);
         if ((rc = plan_and_launch(&p, st))) return rc;
         delta = m->prev;
@@ -699,10 +748,8 @@ static int issue_step_fused(CKB200Model *m, void *st)
     StepGemvParams p = base;
     p.nseg = 1;
     p.nb = m->Da / 256;
-    p.pro = SG_PRO_NORM;
-    p.x_in = cur;
-    p.delta = delta;
-    p.gamma = (const float *)m->final_gamma.w;
+    fused_input(m, &p, SG_PRO_NORM, cur, nxt, delta, (const float *)m->final_gamma.w, NULL, m->hq, st, &rc);
+    if (rc) return rc;
     p.x_out = NULL;
     p.pos_advance = m->pos_dev;
     seg_set(&p.seg[0], &m->lm_head, m->logits, SG_EPI_STORE);
@@ -750,8 +797,14 @@ static int issue_step(CKB200Model *m, void *st)
          * Attention, split merge and quantisation stay three launches: chained with programmatic dependent launch inside
          * the step's graph they measured faster than the single-launch form (ckb200_dev_attention_decode_fused), whose
          * merge and quantise tails run serially in the last CTAs. */
-        if ((rc = ckb200_dev_attention_decode_ws(m->q, kc, vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
-                                                 m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
+        ckb_attn_hint_early_rows(ckb_tune_get("model_attn_early_rows", 1));
+        if (ckb_tune_get("model_attn_cluster", 0)) {
+            /* one launch: the CTAs of a kv head form a thread-block cluster and merge their partial results in distributed shared memory */
+            if ((rc = ckb200_dev_attention_decode_fused(m->q, kc, vc, m->att, B == 1 ? m->Ala : m->Al, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len,
+                                                        m->d, m->d, m->attn_splits, m->attn_scratch, m->attn_counters, m->pos_dev, NULL, 0, st))) return rc;
+        } else if ((rc = ckb200_dev_attention_decode_ws(m->q, kc, vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
+                                                        m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
+        ckb_attn_hint_early_rows(0);
         if ((rc = quant_rows(&t[CKB_T_WO], m->att, m->Ala, m->aq, B, st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
         if ((rc = reduce_norm_quant(m, m->o, &t[CKB_T_LN2], &t[CKB_T_W1], st))) return rc;

@@ -32,6 +32,8 @@ typedef struct {
     int fmt;
     int epi;
     int cta0, ncta;         /* the CTAs [cta0, cta0 + ncta) of the grid work on this segment */
+    int split;              /* the passes of a row go to different warps of a CTA (small matrices with long rows); needs
+                               ckb_step_gemv_passes() <= 8 for the segment's format */
 } StepSeg;
 
 typedef struct {
@@ -49,12 +51,18 @@ typedef struct {
     const int *pos;         /* device position (rope and cache epilogues) */
     int *pos_advance;       /* when not NULL the first CTA stores *pos_advance + 1 there after its rows (end of a step) */
     int head_dim, max_seq;
+    int dry_run;            /* rehearse prologue, product and epilogue before the dependency wait (stores off): warms the instruction
+                               caches; an instantiation of its own with more registers, for small matrices */
 } StepGemvParams;
 
 /* grid = total CTAs (sum of ncta).  Returns 0 or a CKB_ERR_* code; -1 when the shape is outside what the kernel handles. */
 int ckb_launch_step_gemv(const StepGemvParams *p, int grid, void *stream);
+/* passes a warp needs for one row of nb superblocks in the given format */
+int ckb_step_gemv_passes(int nb, int fmt);
+/* the largest row (in superblocks) whose SG_PRO_NORM prologue the kernel handles */
+#define SG_NORM_MAX_NB 8
 /* resident CTAs per SM of the instantiation that handles rows of nb superblocks with this prologue (for sizing the grid) */
-int ckb_step_gemv_ctas_per_sm(int nb, int pro);
+int ckb_step_gemv_ctas_per_sm(int nb, int pro, int dry_run);
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict
     extern __shared__ __align__(16) float row[];
     __shared__ float red[32];
     pdl_trigger();
+    const ArqGamma pre = arq_prefetch_gamma(gamma, d_model);
     pdl_wait();
     const int t = blockIdx.x;
     float *xr = x + (size_t)t * aligned;
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q8k_kernel(float *__restrict
             arq_keep_piece(v, i, d_model, row, ss);
         }
     }
-    arq_norm_quant(ss, row, red, gamma, out_q8, norm_out, t, d_model, aligned, eps);
+    arq_norm_quant(ss, row, red, gamma, out_q8, norm_out, t, d_model, aligned, eps, &pre);
 }
 
 // add_rmsnorm_q8k for a consumer that takes Q8_0 activations (Q8_0 / Q5_0 weights): the same row kernel, Q8_0 blocks of the
@@ -116,15 +117,24 @@ __global__ void rope_kv_store_kernel(float *__restrict__ q, const float *__restr
                                      int d, int max_seq, long long kv_batch_stride)
 {
     pdl_trigger();
-    pdl_wait();
+    // The position changes only at the end of a step (advance_pos, after which the next step begins with a fully ordered launch)
+    // and the tables are constants: both are read before the dependency wait, off the critical path.
     const int pos = __ldcg(pos_dev);
-    if (pos < 0 || pos >= max_seq) return;
     const int half = d / 2;
     const int per_seq = (H + 2 * Hkv) * half;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch * per_seq; i += gridDim.x * blockDim.x) {
+    const int first = blockIdx.x * blockDim.x + threadIdx.x;
+    float c0 = 0.0f, s0 = 0.0f;
+    if (pos >= 0 && pos < max_seq && first < batch * per_seq) {
+        const int j0 = (first % per_seq) % half;
+        c0 = cos_cache[(size_t)pos * half + j0];
+        s0 = sin_cache[(size_t)pos * half + j0];
+    }
+    pdl_wait();
+    if (pos < 0 || pos >= max_seq) return;
+    for (int i = first; i < batch * per_seq; i += gridDim.x * blockDim.x) {
         const int s = i / per_seq, r = i - s * per_seq;
         const int h = r / half, j = r - h * half;
-        const float c = cos_cache[(size_t)pos * half + j], sn = sin_cache[(size_t)pos * half + j];
+        const float c = i == first ? c0 : cos_cache[(size_t)pos * half + j], sn = i == first ? s0 : sin_cache[(size_t)pos * half + j];
         if (h < H) {
             float *row = q + ((size_t)s * H + h) * d;
             const float a = __ldcg(row + j), b = __ldcg(row + j + half);

@@ -534,7 +534,11 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                                          "cosine_vs_first_form_rank0": cos, "max_abs_logit": float(mine.abs().max().item())}
                 decode_tp.append(d)
             lib.ckb200_tune_set(b"tp_p2p", 1)
-            lib.ckb200_tune_set(b"tp_fused_norm", 1)
+            lib.ckb200_tune_set(b"tp_fused_norm", -1)                    # the library's own choice by rank count
+            d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}, batch 1 (default exchange)", LLAMA3_70B, 4096, 20, measured_peak()[0],
+                             batch=1, tp_rank=rank, tp_size=world, dist=dist)
+            d["exchange"] = "default"
+            decode_tp.append(d)
             d = decode_bench(lib, f"Llama-3-70B shape, Q4_K_M mix, TP={world}, batch 32", LLAMA3_70B, 4096, 4, measured_peak()[0],
                              batch=32, tp_rank=rank, tp_size=world, dist=dist)
             d["exchange"] = "default"

@@ -276,7 +276,12 @@ extern "C" int ckb200_tp_add_rmsnorm_q8k(void *ctx, float *x, const float *delta
                                          int aligned_embed_dim, float eps, void *stream)
 {
     (void)ctx;
-    if (!g_p2p.ready || !ckb_tune_get("tp_p2p", 1) || !ckb_tune_get("tp_fused_norm", 1)) return -1;
+    if (!g_p2p.ready || !ckb_tune_get("tp_p2p", 1)) return -1;
+    // One CTA per token row stores to and then polls every peer in turn: with two ranks that is as fast as the 16-CTA all-reduce
+    // kernel plus the norm kernel and saves a launch; from four ranks up the serial peer loop loses (8 ranks, 70B shape, batch 1:
+    // 9.1 ms per token against 6.1), so the default there is all-reduce kernel + norm kernel.  tp_fused_norm = 1 / 0 forces either.
+    const int fused = ckb_tune_get("tp_fused_norm", -1);
+    if (fused == 0 || (fused < 0 && g_p2p.view.world > 2)) return -1;
     if (!x || !delta || !gamma || !out_q8 || tokens <= 0 || d_model <= 0) return -1;
     if (aligned_embed_dim % QK_K || aligned_embed_dim < d_model || aligned_embed_dim > 1024 * 4 * ARQ_MAX_V4) return -1;
     if ((size_t)tokens * aligned_embed_dim > 2 * g_p2p.view.max_lines || (((uintptr_t)x | (uintptr_t)delta) & 15)) return -1;

@@ -92,7 +92,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, cfg: dict):
     launches_fused = lib.ckb200_launch_count() - launches0
     unfused = run(0)
     launches_unfused = lib.ckb200_launch_count() - launches0 - launches_fused
-    lib.ckb200_tune_set(b"tp_fused_norm", 1)
+    lib.ckb200_tune_set(b"tp_fused_norm", -1)
     assert launches_fused < launches_unfused, (launches_fused, launches_unfused)     # the fused form really ran
     assert np.array_equal(fused, unfused)            # same sums in the same order: the two forms agree bit for bit
     np.save(os.path.join(out_dir, f"rank{rank}.npy"), fused)

@@ -678,6 +678,33 @@ def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
     attn_flops = 4.0 * (m_tokens * (m_tokens + 1) / 2) * d * H
     out["causal_attention"] = {"shape": f"H={H} Hkv={Hkv} d={d} T={m_tokens}", "ms": attn_ms, "tflops_fp32": attn_flops / attn_ms / 1e9,
                                "note": "exact fp32 FMA on the CUDA cores (the parity tolerance leaves no room for fp16/tf32 scores)"}
+    # the prefill GEMMs the reference's thread-pool seam dispatches (version/v7/src/ck_parallel_prefill.h:44-48), from the reference's
+    # own weight layouts: Q6_K (rows re-laid per call, then the tcgen05 kernel) and Q8_0 (int8 MMAs, bit-identical to the scalar loop)
+    seam = {}
+    for fmt, entry, (n, k) in (("q6_k", lib.ckb200_dev_gemm_nt_q6_k_q8_k, (4096, 4096)), ("q8_0", lib.ckb200_dev_gemm_nt_q8_0_q8_0, (4096, 4096))):
+        w = torch.from_numpy(synth.make_weights(fmt, n, k, seed=4)).to(dev)
+        a = torch.from_numpy(synth.make_x(k, seed=4, rows=m_tokens)).to(dev)
+        aq = torch.empty(m_tokens * synth.row_bytes("q8_k" if fmt == "q6_k" else "q8_0", k) + 64, dtype=torch.uint8, device=dev)
+        quant = lib.ckb200_dev_quantize_q8_k if fmt == "q6_k" else lib.ckb200_dev_quantize_q8_0
+        assert quant(C.c_void_p(a.data_ptr()), C.c_void_p(aq.data_ptr()), m_tokens, k, stream_ptr) == 0
+        c = torch.empty(m_tokens, n, dtype=torch.float32, device=dev)
+
+        def run2(entry=entry, aq=aq, w=w, c=c, n=n, k=k):
+            if entry(C.c_void_p(aq.data_ptr()), C.c_void_p(w.data_ptr()), None, C.c_void_p(c.data_ptr()), m_tokens, n, k, stream_ptr) != 0:
+                raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+        for _ in range(3):
+            run2()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            run2()
+        e1.record(st)
+        torch.cuda.synchronize()
+        ms2 = e0.elapsed_time(e1) / iters
+        seam[f"gemm_nt_{fmt}_q8_{'k' if fmt == 'q6_k' else '0'} {n}x{k}"] = {"ms": ms2, "tflops": 2.0 * m_tokens * n * k / ms2 / 1e9}
+    out["reference_layout_gemms"] = seam
     out["tflops"] = flops_total / ms_total / 1e9
     out["roofline"] = {"bound": "tensor", "achieved": out["tflops"], "peak": tensor_peak, "unit": "TFLOP/s", "frac": out["tflops"] / tensor_peak,
                        "note": "2*M*N*K of the f16 MMA; peak = measured cuBLAS bf16 burst"}

@@ -36,12 +36,54 @@ extern "C" int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, con
     }
     return gemm_nt_by_rows(ckb200_dev_gemv_q4_k_q8_k, (size_t)(K / 256) * ckb::Q8K_BYTES, A_q8, B, bias, C, M, N, K, stream);
 }
+// From 16 tokens up the reference's 210-byte rows are re-laid row-planar into the library's scratch (one pass over B, a few
+// microseconds against the product itself) and the tensor-core kernel runs over that copy; the scratch belongs to the library's
+// pool, so a caller that records its launches in a CUDA graph keeps its own planar copy and calls ckb200_dev_gemm_nt_q6_k_planar_q8_k.
+extern "C" size_t ckb200_q6_k_planar_bytes(int rows, int cols);
+extern "C" int ckb200_dev_q6_k_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+extern "C" int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);
 extern "C" int ckb200_dev_gemm_nt_q6_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
 {
+    if (A_q8 && B && C && N > 0 && K > 0 && K % 256 == 0 && M >= ckb_tune_get("gemm_tc_min_tokens", 16) && ckb_tune_get("gemm_tc", 1) && !((uintptr_t)B & 1)) {
+        const size_t bytes = ckb200_q6_k_planar_bytes(N, K);
+        void *planar = bytes ? ckb_scratch(CKB_SLOT_P, bytes) : nullptr;
+        if (planar) {
+            const int rc = ckb200_dev_q6_k_to_planar(planar, B, N, K, stream);
+            if (rc) return rc;
+            return ckb200_dev_gemm_nt_q6_k_planar_q8_k(A_q8, planar, bias, C, M, N, K, stream);
+        }
+    }
     return gemm_nt_by_rows(ckb200_dev_gemv_q6_k_q8_k, (size_t)(K / 256) * ckb::Q8K_BYTES, A_q8, B, bias, C, M, N, K, stream);
 }
+// Q8_0 x Q8_0 from 16 tokens up: both operands are re-laid row-planar (the activations always, the weights unless the caller
+// already has a planar copy) and the integer tensor-core kernel of gemm_q80_mma.cu reads every weight tile once per 128 tokens.
+extern "C" size_t ckb200_q8_0_planar_bytes(int rows, int cols);
+extern "C" int ckb200_dev_q8_0_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+extern "C" int ckb_launch_gemm_q80_mma(const void *A_planar, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);
+
+// B_planar may be NULL (then B_raw is converted into the library's scratch).  Returns -1 when the tensor-core path does not apply.
+extern "C" int ckb_gemm_nt_q80_tc(const void *A_raw, const void *B_raw, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream)
+{
+    if (!A_raw || !C || M < ckb_tune_get("gemm_tc_min_tokens", 16) || N <= 0 || K <= 0 || K % 128 || !ckb_tune_get("gemm_tc", 1)) return -1;
+    if (((uintptr_t)A_raw & 1) || (!B_planar && (!B_raw || ((uintptr_t)B_raw & 1)))) return -1;
+    const size_t a_bytes = (ckb200_q8_0_planar_bytes(M, K) + 255) & ~(size_t)255, b_bytes = B_planar ? 0 : ckb200_q8_0_planar_bytes(N, K);
+    uint8_t *ws = (uint8_t *)ckb_scratch(CKB_SLOT_P, a_bytes + b_bytes);
+    if (!ws) return CKB_ERR_CUDA;
+    int rc = ckb200_dev_q8_0_to_planar(ws, A_raw, M, K, stream);
+    if (!rc && !B_planar) {
+        rc = ckb200_dev_q8_0_to_planar(ws + a_bytes, B_raw, N, K, stream);
+        B_planar = ws + a_bytes;
+    }
+    if (rc) return rc;
+    return ckb_launch_gemm_q80_mma(ws, B_planar, bias, C, M, N, K, stream);
+}
+
 extern "C" int ckb200_dev_gemm_nt_q8_0_q8_0(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
 {
+    if (A_q8 && B && C) {
+        const int rc = ckb_gemm_nt_q80_tc(A_q8, B, nullptr, bias, C, M, N, K, stream);
+        if (rc >= 0) return rc;
+    }
     return gemm_nt_by_rows(ckb200_dev_gemv_q8_0_q8_0, (size_t)(K / 32) * ckb::Q80_BYTES, A_q8, B, bias, C, M, N, K, stream);
 }
 

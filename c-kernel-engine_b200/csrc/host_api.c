@@ -25,6 +25,8 @@
 
 enum { F_Q4K = 0, F_Q6K = 1, F_Q80 = 2, F_Q50 = 3 };     /* F_Q50: Q5_0 weights (22-byte blocks) with Q8_0 activations */
 
+int ckb_gemm_nt_q80_tc(const void *A_raw, const void *B_raw, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream);   /* gemm.cu */
+
 static size_t w_row_bytes(int fmt, int K)
 {
     switch (fmt) {
@@ -83,7 +85,19 @@ static void host_gemv_rows(int fmt, float *y, const void *W, const void *x_q8, i
     int back;
     float *dY = (float *)ckb_stage_out(y + r0, (size_t)rows * sizeof(float), CKB_SLOT_Y, &back);
     if (!dW || !dX || !dY) return;
-    if (dev_gemv(fmt, dY, dW, dX, rows, K) != 0) return;
+    /* resident weights in one of the 2-byte-aligned formats: the row-planar copy (built once) streams at aligned 16-byte loads */
+    const void *planar = (fmt != F_Q4K && ckb200_device_ptr(Wr) == dW) ? ckb_planar_shadow(fmt, dW, rows, K) : NULL;
+    int rc;
+    if (planar) {
+        switch (fmt) {
+            case F_Q6K: rc = ckb200_dev_gemv_q6_k_planar_q8_k(dY, planar, dX, rows, K, NULL); break;
+            case F_Q50: rc = ckb200_dev_gemv_q5_0_planar_q8_0(dY, planar, dX, rows, K, NULL); break;
+            default: rc = ckb200_dev_gemv_q8_0_planar_q8_0(dY, planar, dX, rows, K, NULL); break;
+        }
+    } else {
+        rc = dev_gemv(fmt, dY, dW, dX, rows, K);
+    }
+    if (rc != 0) return;
     ckb_finish_out(y + r0, dY, (size_t)rows * sizeof(float), back);
 }
 
@@ -169,9 +183,19 @@ static void host_gemm_nt(int fmt, const void *A_q8, const void *B, const float *
     int rc;
     switch (fmt) {
         case F_Q4K: rc = ckb200_dev_gemm_nt_q4_k_q8_k(dA, dB, dbias, dC, M, N, K, NULL); break;
-        case F_Q6K: rc = ckb200_dev_gemm_nt_q6_k_q8_k(dA, dB, dbias, dC, M, N, K, NULL); break;
+        case F_Q6K: {
+            /* resident weights: the tensor-core kernel over their row-planar copy; others are re-laid per call inside the device entry */
+            const void *planar = ckb200_device_ptr(B) == dB ? ckb_planar_shadow(F_Q6K, dB, N, K) : NULL;
+            rc = planar ? ckb200_dev_gemm_nt_q6_k_planar_q8_k(dA, planar, dbias, dC, M, N, K, NULL) : ckb200_dev_gemm_nt_q6_k_q8_k(dA, dB, dbias, dC, M, N, K, NULL);
+            break;
+        }
         case F_Q50: rc = ckb200_dev_gemm_nt_q5_0_q8_0(dA, dB, dbias, dC, M, N, K, NULL); break;
-        default: rc = ckb200_dev_gemm_nt_q8_0_q8_0(dA, dB, dbias, dC, M, N, K, NULL); break;
+        default: {
+            const void *planar = ckb200_device_ptr(B) == dB ? ckb_planar_shadow(F_Q80, dB, N, K) : NULL;
+            rc = planar ? ckb_gemm_nt_q80_tc(dA, NULL, planar, dbias, dC, M, N, K, NULL) : -1;
+            if (rc < 0) rc = ckb200_dev_gemm_nt_q8_0_q8_0(dA, dB, dbias, dC, M, N, K, NULL);
+            break;
+        }
     }
     if (rc != 0) return;
     ckb_finish_out(C, dC, c_b, back);

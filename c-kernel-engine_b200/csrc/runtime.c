@@ -200,14 +200,69 @@ int ckb200_register_weights(const void *host_ptr, size_t bytes)
     return 0;
 }
 
+/* ---- row-planar shadows of registered weights (the reference's 210- / 34- / 22-byte blocks are only 2-byte aligned) */
+size_t ckb200_q6_k_planar_bytes(int rows, int cols);
+size_t ckb200_q8_0_planar_bytes(int rows, int cols);
+size_t ckb200_q5_0_planar_bytes(int rows, int cols);
+int ckb200_dev_q6_k_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+int ckb200_dev_q8_0_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+int ckb200_dev_q5_0_to_planar(void *dst, const void *src, int rows, int cols, void *stream);
+
+#define CKB_MAX_SHADOW 256
+static struct { const uint8_t *raw; void *planar; int fmt, rows, cols; } g_shadow[CKB_MAX_SHADOW];
+static int g_nshadow;
+
+static void drop_shadows_in(const uint8_t *dev, size_t bytes)
+{
+    for (int i = 0; i < g_nshadow;) {
+        if (g_shadow[i].raw >= dev && g_shadow[i].raw < dev + bytes) {
+            cudaFree(g_shadow[i].planar);
+            g_shadow[i] = g_shadow[--g_nshadow];
+        } else {
+            ++i;
+        }
+    }
+}
+
+const void *ckb_planar_shadow(int fmt, const void *dev_raw, int rows, int cols)
+{
+    const uint8_t *p = (const uint8_t *)dev_raw;
+    if (!ckb200_tune_get("planar_shadow", 1)) return NULL;
+    for (int i = 0; i < g_nshadow; ++i)
+        if (g_shadow[i].raw == p && g_shadow[i].fmt == fmt && g_shadow[i].rows == rows && g_shadow[i].cols == cols) return g_shadow[i].planar;
+    int inside = 0;
+    pthread_mutex_lock(&g_lock);
+    for (int i = 0; i < g_nreg; ++i)
+        if (p >= g_reg[i].dev && p < g_reg[i].dev + g_reg[i].bytes) { inside = 1; break; }
+    pthread_mutex_unlock(&g_lock);
+    if (!inside || g_nshadow == CKB_MAX_SHADOW || ((uintptr_t)p & 15)) return NULL;
+    const size_t bytes = fmt == 1 ? ckb200_q6_k_planar_bytes(rows, cols) : (fmt == 2 ? ckb200_q8_0_planar_bytes(rows, cols) : ckb200_q5_0_planar_bytes(rows, cols));
+    if (!bytes) return NULL;
+    void *dst = NULL;
+    if (cudaMalloc(&dst, bytes + 256) != cudaSuccess) { cudaGetLastError(); return NULL; }
+    const int rc = fmt == 1 ? ckb200_dev_q6_k_to_planar(dst, p, rows, cols, NULL) : (fmt == 2 ? ckb200_dev_q8_0_to_planar(dst, p, rows, cols, NULL)
+                                                                                             : ckb200_dev_q5_0_to_planar(dst, p, rows, cols, NULL));
+    if (rc) { cudaFree(dst); return NULL; }
+    g_shadow[g_nshadow].raw = p;
+    g_shadow[g_nshadow].planar = dst;
+    g_shadow[g_nshadow].fmt = fmt;
+    g_shadow[g_nshadow].rows = rows;
+    g_shadow[g_nshadow].cols = cols;
+    ++g_nshadow;
+    return dst;
+}
+
 int ckb200_unregister_weights(const void *host_ptr)
 {
     pthread_mutex_lock(&g_lock);
     for (int i = 0; i < g_nreg; ++i)
         if (g_reg[i].host == (const uint8_t *)host_ptr) {
             uint8_t *dev = g_reg[i].dev;
+            const size_t bytes = g_reg[i].bytes;
             g_reg[i] = g_reg[--g_nreg];
             pthread_mutex_unlock(&g_lock);
+            cudaStreamSynchronize(g.stream);
+            drop_shadows_in(dev, bytes);
             cudaFree(dev);
             return 0;
         }

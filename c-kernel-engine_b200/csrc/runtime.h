@@ -9,7 +9,7 @@
 extern "C" {
 #endif
 
-enum { CKB_SLOT_W = 0, CKB_SLOT_X = 1, CKB_SLOT_Y = 2, CKB_SLOT_A = 3, CKB_SLOT_B = 4, CKB_SLOT_C = 5, CKB_SLOT_T = 6, CKB_SLOT_G = 7, CKB_NSLOTS = 8 };
+enum { CKB_SLOT_W = 0, CKB_SLOT_X = 1, CKB_SLOT_Y = 2, CKB_SLOT_A = 3, CKB_SLOT_B = 4, CKB_SLOT_C = 5, CKB_SLOT_T = 6, CKB_SLOT_G = 7, CKB_SLOT_P = 8, CKB_NSLOTS = 9 };
 
 int ckb_ensure_init(void);                 /* 0 or CKB_ERR_NO_DEVICE; initialises on first use */
 int ckb_sm_count(void);
@@ -19,6 +19,10 @@ int ckb_tune_get(const char *key, int dflt);
 int ckb_is_device_ptr(const void *p);      /* device or managed memory */
 int ckb_sync_check(cudaStream_t st, const char *what);   /* sync + device error word -> 0, CKB_ERR_CUDA or CKB_ERR_DEVICE_WAIT */
 long long ckb_wait_limit_cycles(void);     /* tune key wait_limit_ms in SM cycles */
+/* Row-planar copy (aligned 16-byte loads: gemv_q6k_planar.cu, gemv_q80_planar.cu, gemv_q50_planar.cu) of `rows` rows of a
+ * REGISTERED weight range, built on first use and kept until the range is unregistered; NULL when dev_raw is not inside a
+ * registered range or the cache is full.  fmt: 1 Q6_K, 2 Q8_0, 3 Q5_0. */
+const void *ckb_planar_shadow(int fmt, const void *dev_raw, int rows, int cols);
 
 /* Device scratch that grows on demand (never shrinks); one buffer per slot. */
 void *ckb_scratch(int slot, size_t bytes);

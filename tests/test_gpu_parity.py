@@ -629,3 +629,68 @@ def test_add_rmsnorm_q8_0_matches_the_three_kernel_form(ck, tokens, d_model, ali
     assert ck.ckb200_synchronize() == 0
     assert torch.equal(x1, x2)
     assert torch.equal(q1, q2)
+
+
+# ---------------------------------------------------------------- prefill GEMMs behind the reference's names, from the reference's own layouts
+
+@pytest.mark.parametrize("m,n,k", [(16, 128, 256), (64, 200, 1024), (512, 384, 4096), (130, 96, 4864)])
+def test_gemm_nt_q6_k_reference_layout_runs_on_tensor_cores(ck, orc, m, n, k):
+    """gemm_nt_q6_k_q8_k[_parallel_dispatch] on the reference's 210-byte rows: from 16 tokens up the rows are re-laid per call
+    and the tcgen05 kernel runs (two launches, not one GEMV per token)."""
+    w = synth.make_weights("q6_k", n, k, seed=m + n)
+    aq = cases.quantize_act(orc, "oracle_", "q6_k", synth.make_x(k, seed=m, rows=m), rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32)
+    want = cases.gemm_nt(orc, "oracle_", "q6_k", aq, w, bias, m, n, k)
+    ck.ckb200_launch_count.restype = C.c_longlong
+    n0 = ck.ckb200_launch_count()
+    got = cases.gemm_nt(ck, "", "q6_k", aq, w, bias, m, n, k)
+    assert ck.ckb200_launch_count() - n0 <= 5, "one GEMV per token is not a prefill GEMM"
+    assert_fp32_close(got, want, f"q6_k gemm_nt {m}x{n}x{k}")
+    c2 = np.full((m, n), np.nan, dtype=np.float32)
+    cases.fn(ck, "", "gemm_nt_q6_k_q8_k_parallel_dispatch")(cases.vptr(aq), cases.vptr(w), cases.fptr(bias), cases.fptr(c2), m, n, k)
+    assert np.array_equal(c2, got)
+
+
+@pytest.mark.parametrize("m,n,k,with_bias", [(16, 128, 128, False), (64, 200, 896, True), (512, 384, 4096, True), (130, 1000, 4864, False), (300, 130, 1024, True)])
+def test_gemm_nt_q8_0_integer_tensor_core(ck, orc, m, n, k, with_bias):
+    """gemm_nt_q8_0_q8_0 from 16 tokens up: int8 MMAs, one block of 32 per instruction, scaled block by block in the reference's
+    order - the same bits as the scalar loop."""
+    w = synth.make_weights("q8_0", n, k, seed=m + n)
+    aq = cases.quantize_act(orc, "oracle_", "q8_0", synth.make_x(k, seed=m, rows=m), rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32) if with_bias else None
+    want = cases.gemm_nt(orc, "oracle_", "q8_0", aq, w, bias, m, n, k)
+    ck.ckb200_launch_count.restype = C.c_longlong
+    n0 = ck.ckb200_launch_count()
+    got = cases.gemm_nt(ck, "", "q8_0", aq, w, bias, m, n, k)
+    launches = ck.ckb200_launch_count() - n0
+    if k % 128 == 0:
+        assert launches <= 4, launches
+        assert np.array_equal(got, want), float(np.max(np.abs(got - want)))
+    else:
+        assert_fp32_close(got, want, "q8_0 gemm_nt by rows")
+    c2 = np.full((m, n), np.nan, dtype=np.float32)
+    b = cases.fptr(bias) if bias is not None else cases.c_float_p()
+    cases.fn(ck, "", "gemm_nt_q8_0_q8_0_parallel_dispatch")(cases.vptr(aq), cases.vptr(w), b, cases.fptr(c2), m, n, k)
+    assert np.array_equal(c2, got)
+
+
+@pytest.mark.parametrize("fmt,m,k", [("q6_k", 300, 2048), ("q8_0", 200, 896), ("q5_0", 130, 4096)])
+def test_registered_weights_in_unaligned_formats_get_a_planar_copy(ck, orc, fmt, m, k):
+    """Resident Q6_K / Q8_0 / Q5_0 weights behind the host-pointer GEMV (and GEMM) are read from a row-planar copy built on first
+    use; same results as on unregistered weights, and unregistering drops the copy."""
+    w = synth.make_weights(fmt, m, k, seed=k)
+    xq = cases.quantize_act(orc, "oracle_", fmt, synth.make_x(k, seed=1))
+    want = cases.gemv(orc, "oracle_", fmt, w, xq, m, k)
+    plain = cases.gemv(ck, "", fmt, w, xq, m, k)
+    assert_fp32_close(plain, want, fmt)
+    assert ck.ckb200_register_weights(cases.vptr(w), C.c_size_t(w.nbytes)) == 0
+    try:
+        for _ in range(2):                                   # first call builds the copy, second reuses it
+            assert_fp32_close(cases.gemv(ck, "", fmt, w, xq, m, k), want, fmt + " registered")
+        if fmt != "q5_0":
+            mt = 32
+            aq = cases.quantize_act(orc, "oracle_", fmt, synth.make_x(k, seed=2, rows=mt), rows=mt)
+            assert_fp32_close(cases.gemm_nt(ck, "", fmt, aq, w, None, mt, m, k), cases.gemm_nt(orc, "oracle_", fmt, aq, w, None, mt, m, k), fmt + " registered gemm")
+    finally:
+        assert ck.ckb200_unregister_weights(cases.vptr(w)) == 0
+    assert_fp32_close(cases.gemv(ck, "", fmt, w, xq, m, k), want, fmt + " after unregister")

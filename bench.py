@@ -596,6 +596,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
                 lib.ckb200_clear_error()
             try:
                 line["prefill"] = prefill_bench(lib, 512, 20, sp, torch, measured_tensor_peak())
+                line["prefill"]["whole_stack"] = prefill_step_bench(lib)
             except Exception as exc:
                 line["prefill"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()
@@ -711,6 +712,44 @@ def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
     if lib.ckb200_synchronize() != 0:
         raise RuntimeError(lib.ckb200_last_error_message().decode())
     return out
+
+
+LLAMA3_8B = dict(embed_dim=4096, num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=14336, num_layers=32, vocab_size=128256,
+                 max_seq_len=1024, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=0, fmt_o=0, fmt_gate_up=0, fmt_down=0, fmt_lm_head=0)
+
+
+def prefill_step_bench(lib, tokens=512, iters=5):
+    """The whole Llama-3-8B-shaped stack (32 layers, Q4_K weights, Q8_K activations, causal attention) over a 512-token prompt through
+    ckb200_model_prefill: prompt ids in from the host, the last token's logits back, per iteration from an empty cache."""
+    so = pkg.model_api
+    so.bind_model_api(lib)
+    handle = lib.ckb200_model_create(C.byref(so.make_cfg(LLAMA3_8B, batch=1)))
+    if not handle:
+        msg = lib.ckb200_last_error_message().decode()
+        lib.ckb200_clear_error()
+        return {"error": msg}
+    try:
+        assert lib.ckb200_model_fill_synthetic(handle, 1) == 0
+        prompt = np.random.default_rng(0).integers(0, LLAMA3_8B["vocab_size"], size=tokens).astype(np.int32)
+        logits = np.zeros((1, LLAMA3_8B["vocab_size"]), np.float32)
+        lib.ckb200_model_reset.argtypes = [C.c_void_p]
+        times = []
+        launches = 0
+        for i in range(iters + 1):
+            assert lib.ckb200_model_reset(handle) == 0
+            n0 = lib.ckb200_launch_count()
+            t0 = time.perf_counter()
+            assert lib.ckb200_model_prefill(handle, vptr(prompt), tokens, vptr(logits)) == 0, lib.ckb200_last_error_message()
+            if i:
+                times.append(time.perf_counter() - t0)
+            launches = lib.ckb200_launch_count() - n0
+        ms = statistics.median(times) * 1e3
+        flops = 2.0 * tokens * sum(n * k for n, k in ((4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (28672, 4096), (4096, 14336))) * LLAMA3_8B["num_layers"]
+        return {"workload": f"Llama-3-8B-shaped prefill, {tokens}-token prompt, 32 layers, Q4_K x Q8_K, causal attention, host ids in / last logits out",
+                "ms": ms, "prompt_tokens_per_s": tokens / ms * 1e3, "projection_tflops": flops / ms / 1e9, "launches": int(launches),
+                "finite": bool(np.isfinite(logits).all())}
+    finally:
+        lib.ckb200_model_free(handle)
 
 
 def run_prefill_only(args):

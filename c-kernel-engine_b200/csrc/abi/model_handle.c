@@ -103,10 +103,12 @@ CK_EXPORT void ck_model_forward(void *model, const int *tokens, int num_tokens)
     Handle *h = (Handle *)model;
     if (!h || !tokens || num_tokens <= 0) return;
     ckb200_model_reset(h->m);
-    for (int i = 0; i < num_tokens; ++i) {
-        const int32_t t = tokens[i];
-        if (ckb200_model_decode(h->m, &t, i == num_tokens - 1 ? h->logits : NULL)) return;
-    }
+    int32_t *ids = (int32_t *)malloc((size_t)num_tokens * sizeof(int32_t));
+    if (!ids) return;
+    for (int i = 0; i < num_tokens; ++i) ids[i] = tokens[i];
+    if (ckb200_model_prefill(h->m, ids, num_tokens, h->logits))           /* one batched pass from the empty cache */
+        for (int i = 0; i < g_cfg.vocab_size; ++i) h->logits[i] = NAN;
+    free(ids);
 }
 
 CK_EXPORT float *ck_model_get_logits(void *model) { return model ? ((Handle *)model)->logits : NULL; }

@@ -67,8 +67,10 @@ static int step(int32_t token, int want_logits)
 CK_EXPORT int ck_model_embed_tokens(const int32_t *tokens, int count)
 {
     if (!g_model || !tokens || count <= 0) return -1;
-    for (int i = 0; i < count; ++i)
-        if (step(tokens[i], i == count - 1)) return -1;
+    if (g_pos + count > ckb200_model_config(g_model)->max_seq_len) return -1;
+    /* a prompt from an empty cache runs as one batched pass (tensor-core GEMMs, causal prefill attention), otherwise token by token */
+    if (ckb200_model_prefill(g_model, tokens, count, g_logits) != 0) return -1;
+    g_pos += count;
     return 0;
 }
 

@@ -81,6 +81,10 @@ struct CKB200Model {
     float *x2;              /* second residual row of the fused step (each fused launch reads one and writes the other) */
     float *mf;              /* fp32 SwiGLU output of the fused step, round256(Il) wide, tail zero */
     int *attn_counters;     /* arrival counters of the attention kernel's in-launch split merge */
+    /* batched prefill (grown on demand to the longest prompt seen): token-major rows and head-major attention tensors */
+    int pf_tokens;
+    float *pf_x, *pf_delta, *pf_o, *pf_q, *pf_k, *pf_v, *pf_qh, *pf_oh, *pf_gu;
+    uint8_t *pf_hq, *pf_aq, *pf_mq;
     uint8_t *hq, *aq, *mq;
     int32_t *tokens_dev, *pos_dev;
     int32_t *tokens_pinned;
@@ -94,6 +98,8 @@ struct CKB200Model {
      * joined with events, which a stream capture turns into parallel branches of the step's graph) */
     cudaStream_t side[2];
     cudaEvent_t ev_fork, ev_join[2];
+    cudaEvent_t ev_tokens;  /* the last copy out of tokens_pinned: the next call waits for it before it overwrites the buffer */
+    int tokens_in_flight;
     int have_prev;
     ckb200_allreduce_fn allreduce;
     void *allreduce_ctx;
@@ -261,6 +267,7 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
         if (ok && ckb_check_cuda((int)cudaEventCreateWithFlags(&m->ev_join[i], cudaEventDisableTiming), "join event")) ok = 0;
     }
     if (ok && ckb_check_cuda((int)cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming), "fork event")) ok = 0;
+    if (ok && ckb_check_cuda((int)cudaEventCreateWithFlags(&m->ev_tokens, cudaEventDisableTiming), "tokens event")) ok = 0;
     if (!ok) { ckb200_model_free(m); return NULL; }
 #undef DEV_ALLOC
     /* offsets -> pointers */
@@ -297,7 +304,8 @@ void ckb200_model_free(CKB200Model *m)
     cudaStreamSynchronize(ckb_stream(NULL));
     if (m->graph_ready) cudaGraphExecDestroy(m->graph);
     void *ptrs[] = { m->arena, m->planar_arena, m->kv, m->rope_cos, m->rope_sin, m->x, m->prev, m->o, m->q, m->k, m->v, m->att, m->gu, m->logits,
-                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch, m->gemm_ws, m->x2, m->mf, m->attn_counters };
+                     m->hq, m->aq, m->mq, m->tokens_dev, m->pos_dev, m->attn_scratch, m->gemm_ws, m->x2, m->mf, m->attn_counters,
+                     m->pf_x, m->pf_delta, m->pf_o, m->pf_q, m->pf_k, m->pf_v, m->pf_qh, m->pf_oh, m->pf_gu, m->pf_hq, m->pf_aq, m->pf_mq };
     for (size_t i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) if (ptrs[i]) cudaFree(ptrs[i]);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     for (int i = 0; i < 2; ++i) {
@@ -305,6 +313,7 @@ void ckb200_model_free(CKB200Model *m)
         if (m->ev_join[i]) cudaEventDestroy(m->ev_join[i]);
     }
     if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_tokens) cudaEventDestroy(m->ev_tokens);
     free(m->layers);
     free(m);
 }
@@ -830,8 +839,13 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
         return ckb_fail(CKB_ERR_LIMIT, "model_decode: position %d is past the context of %d tokens (reset or set_pos first)", m->host_pos, m->c.max_seq_len);
     cudaStream_t st = ckb_stream(NULL);
     const int B = m->c.batch;
+    /* a call without logits_host returns while its step is still queued: the pinned staging buffer may only be reused once the
+     * copy out of it has run */
+    if (m->tokens_in_flight && ckb_check_cuda((int)cudaEventSynchronize(m->ev_tokens), "tokens staging")) return CKB_ERR_CUDA;
     memcpy(m->tokens_pinned, tokens, (size_t)B * sizeof(int32_t));
     if (ckb_check_cuda((int)cudaMemcpyAsync(m->tokens_dev, m->tokens_pinned, (size_t)B * sizeof(int32_t), cudaMemcpyHostToDevice, st), "tokens H2D")) return CKB_ERR_CUDA;
+    if (ckb_check_cuda((int)cudaEventRecord(m->ev_tokens, st), "tokens event")) return CKB_ERR_CUDA;
+    m->tokens_in_flight = 1;
     { const int rc = ensure_planar(m, st); if (rc) return rc; }
     const int use_graph = ckb_tune_get("model_graph", 1);
     if (use_graph && !m->graph_ready) {
@@ -868,6 +882,127 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
         return ckb_sync_check(st, "model_decode");        /* a timed-out exchange must not come back as rc 0 with stale logits */
     }
     return 0;
+}
+
+/* ------------------------------------------------------------------ batched prefill
+ *
+ * A prompt of T tokens as ONE pass (the reference's generated ck_prefill, version/v7/scripts/codegen_prefill_v7.py:194-208): per
+ * layer the T rows are normalised and quantised together, every projection is one quantised GEMM on the tensor cores (the
+ * weights are read once for all tokens), RoPE and the KV-cache fill run over all tokens, attention is the causal prefill
+ * kernel.  Only the last token's logits are produced.  Used from an empty cache (position 0) by one sequence on one GPU with
+ * K-quant projections; every other case (and prompts shorter than 16 tokens) falls back to T decode steps. */
+
+int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *stream);
+int ckb200_dev_prefill_rope_scatter(const float *q_tm, const float *k_tm, const float *v_tm, float *q_hm, float *k_cache, float *v_cache, const float *cos_cache,
+                                    const float *sin_cache, int tokens, int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int pos0, void *stream);
+int ckb200_dev_prefill_gather_q8k(const float *out_hm, void *out_q8, int tokens, int num_heads, int head_dim, int cols, void *stream);
+
+static int prefill_ok(const CKB200Model *m, int T)
+{
+    if (m->c.batch != 1 || m->c.tp_size != 1 || T < 16 || m->host_pos != 0 || T > m->c.max_seq_len || !ckb_tune_get("model_prefill", 1)) return 0;
+    for (int l = 0; l < m->c.num_layers; ++l) {
+        static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
+        for (int i = 0; i < 6; ++i) {
+            const Tensor *t = &m->layers[l].t[which[i]];
+            if (!(t->fmt == FMT_Q4K || (t->fmt == FMT_Q6K && t->planar))) return 0;
+        }
+    }
+    const int group = m->Hl / m->Hkvl;
+    return m->Il % 256 == 0 && m->d % 8 == 0 && (m->d == 64 || m->d == 128) && group <= 8 && m->Hl % m->Hkvl == 0;
+}
+
+static int prefill_buffers(CKB200Model *m, int T)
+{
+    if (T <= m->pf_tokens) return 0;
+    cudaStreamSynchronize(ckb_stream(NULL));
+    void **ptrs[] = { (void **)&m->pf_x, (void **)&m->pf_delta, (void **)&m->pf_o, (void **)&m->pf_q, (void **)&m->pf_k, (void **)&m->pf_v, (void **)&m->pf_qh,
+                      (void **)&m->pf_oh, (void **)&m->pf_gu, (void **)&m->pf_hq, (void **)&m->pf_aq, (void **)&m->pf_mq };
+    for (unsigned i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i) { if (*ptrs[i]) cudaFree(*ptrs[i]); *ptrs[i] = NULL; }
+    m->pf_tokens = 0;
+    const size_t t = (size_t)T, kvw = (size_t)m->Hkvl * m->d;
+    const size_t sizes[] = { t * m->Da * 4, t * m->Da * 4, t * m->Da * 4, t * m->Al * 4, t * kvw * 4, t * kvw * 4, t * m->Al * 4, t * m->Al * 4, t * 2 * m->Il * 4,
+                             t * (m->Da / 256) * 292, t * (m->Ala / 256) * 292, t * (m->Il / 256) * 292 };
+    for (unsigned i = 0; i < sizeof ptrs / sizeof ptrs[0]; ++i)
+        if (ckb_check_cuda((int)cudaMalloc(ptrs[i], sizes[i] + 256), "cudaMalloc(prefill)")) return CKB_ERR_CUDA;
+    /* rows wider than the data (Da > D) keep a zero tail: the GEMMs write only the first D columns */
+    cudaMemsetAsync(m->pf_delta, 0, sizes[1], ckb_stream(NULL));
+    cudaMemsetAsync(m->pf_o, 0, sizes[2], ckb_stream(NULL));
+    m->pf_tokens = T;
+    return 0;
+}
+
+static int prefill_gemm(const Tensor *w, const uint8_t *xq, float *y, int ldc, int T, void *st)
+{
+    const int rc = ckb_launch_gemm_tc(w->fmt == FMT_Q6K, xq, w->fmt == FMT_Q6K ? w->planar : w->w, NULL, y, ldc, T, w->rows, w->cols, 16, st);
+    return rc == -1 ? ckb_fail(CKB_ERR_SHAPE, "prefill: projection %d x %d not handled by the tensor-core GEMM", w->rows, w->cols) : rc;
+}
+
+static int issue_prefill(CKB200Model *m, int T, void *st)
+{
+    const CKB200ModelConfig *c = &m->c;
+    const int L = c->num_layers, kvw = m->Hkvl * m->d;
+    int rc;
+    switch (m->emb.fmt) {
+        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
+        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
+        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
+    }
+    if (rc) return rc;
+    const float *delta = NULL;
+    for (int l = 0; l < L; ++l) {
+        Tensor *t = m->layers[l].t;
+        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + m->kv_batch_stride;
+        if ((rc = ckb200_dev_add_rmsnorm_q8k(m->pf_x, delta, (const float *)t[CKB_T_LN1].w, m->pf_hq, NULL, T, m->D, m->Da, c->rms_eps, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_WQ], m->pf_hq, m->pf_q, m->Al, T, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_WK], m->pf_hq, m->pf_k, kvw, T, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_WV], m->pf_hq, m->pf_v, kvw, T, st))) return rc;
+        if ((rc = ckb200_dev_prefill_rope_scatter(m->pf_q, m->pf_k, m->pf_v, m->pf_qh, kc, vc, m->rope_cos, m->rope_sin, T, m->Hl, m->Hkvl, m->d, c->max_seq_len, 0, st))) return rc;
+        if ((rc = ckb200_dev_attention_prefill(m->pf_qh, kc, vc, m->pf_oh, m->Hl, m->Hkvl, T, m->d, m->d, c->max_seq_len, 1, st))) return rc;
+        if ((rc = ckb200_dev_prefill_gather_q8k(m->pf_oh, m->pf_aq, T, m->Hl, m->d, m->Ala, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_WO], m->pf_aq, m->pf_o, m->Da, T, st))) return rc;
+        if ((rc = ckb200_dev_add_rmsnorm_q8k(m->pf_x, m->pf_o, (const float *)t[CKB_T_LN2].w, m->pf_hq, NULL, T, m->D, m->Da, c->rms_eps, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_W1], m->pf_hq, m->pf_gu, 2 * m->Il, T, st))) return rc;
+        if ((rc = ckb200_dev_swiglu_q8k(m->pf_gu, m->pf_mq, T, m->Il, st))) return rc;
+        if ((rc = prefill_gemm(&t[CKB_T_W2], m->pf_mq, m->pf_delta, m->Da, T, st))) return rc;
+        delta = m->pf_delta;
+    }
+    /* logits of the last token only: its residual row, final norm, LM head as a GEMV */
+    const size_t last = (size_t)(T - 1) * m->Da;
+    if ((rc = ckb200_dev_add_rmsnorm_q8k(m->pf_x + last, delta ? delta + last : NULL, (const float *)m->final_gamma.w, m->hq, NULL, 1, m->D, m->Da, c->rms_eps, st))) return rc;
+    return matvec(m, &m->lm_head, m->hq, m->logits, m->Vl, st);
+}
+
+int ckb200_model_prefill(CKB200Model *m, const int32_t *tokens, int count, float *logits_host)
+{
+    if (!m || !tokens || count <= 0) return ckb_fail(CKB_ERR_STATE, "model_prefill: NULL model or tokens");
+    if (m->host_pos + count > m->c.max_seq_len)
+        return ckb_fail(CKB_ERR_LIMIT, "model_prefill: %d tokens from position %d run past the context of %d tokens", count, m->host_pos, m->c.max_seq_len);
+    cudaStream_t st = ckb_stream(NULL);
+    { const int rc = ensure_planar(m, st); if (rc) return rc; }
+    if (!prefill_ok(m, count)) {
+        for (int i = 0; i < count; ++i) {
+            const int rc = ckb200_model_decode(m, tokens + i, i == count - 1 ? logits_host : NULL);
+            if (rc) return rc;
+        }
+        return 0;
+    }
+    if (prefill_buffers(m, count)) return CKB_ERR_CUDA;
+    int32_t *ids = NULL;
+    if (ckb_check_cuda((int)cudaMalloc((void **)&ids, (size_t)count * sizeof(int32_t)), "cudaMalloc(prompt ids)")) return CKB_ERR_CUDA;
+    int rc = ckb_check_cuda((int)cudaMemcpyAsync(ids, tokens, (size_t)count * sizeof(int32_t), cudaMemcpyHostToDevice, st), "prompt ids H2D");
+    int32_t *saved = m->tokens_dev;
+    m->tokens_dev = ids;
+    if (!rc) rc = issue_prefill(m, count, st);
+    m->tokens_dev = saved;
+    if (!rc) {
+        const int32_t p = count;
+        rc = ckb_check_cuda((int)cudaMemcpyAsync(m->pos_dev, &p, sizeof p, cudaMemcpyHostToDevice, st), "prefill pos");
+    }
+    if (!rc && logits_host) rc = ckb_check_cuda((int)cudaMemcpyAsync(logits_host, m->logits, (size_t)m->Vl * sizeof(float), cudaMemcpyDeviceToHost, st), "logits D2H");
+    if (!rc) rc = ckb_sync_check(st, "model_prefill");
+    cudaFree(ids);
+    if (!rc) m->host_pos = count;
+    return rc;
 }
 
 /* Enqueue `steps` decode steps that keep feeding the same token ids (benchmark loop; no host sync). */

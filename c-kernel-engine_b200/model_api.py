@@ -57,6 +57,7 @@ def bind_model_api(lib):
     lib.ckb200_model_get_pos.argtypes = [C.c_void_p]
     lib.ckb200_model_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ckb200_model_decode_repeat.argtypes = [C.c_void_p, C.c_int]
+    lib.ckb200_model_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     lib.ckb200_model_fill_synthetic.argtypes = [C.c_void_p, C.c_ulonglong]
     lib.ckb200_model_fill_kv_synthetic.argtypes = [C.c_void_p, C.c_int, C.c_ulonglong]
     lib.ckb200_model_weight_bytes.argtypes = [C.c_void_p]

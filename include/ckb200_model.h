@@ -67,6 +67,12 @@ void ckb200_model_set_allreduce(CKB200Model *m, ckb200_allreduce_fn fn, void *ct
 void ckb200_model_set_tp_norm(CKB200Model *m, ckb200_tp_norm_fn fn, void *ctx);
 /* one decode step: tokens[batch] in, logits[batch][vocab] out (logits_host may be NULL: no copy, no sync) */
 int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_host);
+/* A prompt of `count` tokens appended at the current position; logits_host (may be NULL) receives the last token's logits.
+ * From an empty cache (position 0), with 16 tokens or more, one sequence on one GPU and K-quant projections this is ONE batched
+ * pass - per layer: rows normalised and quantised together, every projection a tensor-core GEMM, RoPE + KV fill over all tokens,
+ * causal prefill attention (the reference's generated ck_prefill, version/v7/scripts/codegen_prefill_v7.py:194-208) - otherwise
+ * `count` decode steps.  Either way the cache and the position end as after `count` decode calls. */
+int ckb200_model_prefill(CKB200Model *m, const int32_t *tokens, int count, float *logits_host);
 int ckb200_model_decode_repeat(CKB200Model *m, int steps);              /* re-launch the captured step `steps` times */
 float *ckb200_model_logits_device(CKB200Model *m);
 void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v);       /* [batch][Hkv][max_seq][head_dim] fp32 */

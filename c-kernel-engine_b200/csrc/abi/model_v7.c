@@ -20,10 +20,8 @@ static CKB200Model *g_model;
 static float *g_logits;
 static int g_pos;
 
-CK_EXPORT int ck_model_init(const char *weights_path)
+static int finish_init(void)
 {
-    if (g_model) return 0;
-    g_model = ckb200_model_open(weights_path, 1);
     if (!g_model) return -1;
     g_logits = (float *)ckb200_host_alloc((size_t)ckb200_model_config(g_model)->vocab_size * sizeof(float));
     if (!g_logits) { ckb200_model_free(g_model); g_model = NULL; return -1; }
@@ -32,10 +30,20 @@ CK_EXPORT int ck_model_init(const char *weights_path)
     return 0;
 }
 
+CK_EXPORT int ck_model_init(const char *weights_path)
+{
+    if (g_model) return 0;
+    g_model = ckb200_model_open(weights_path, 1);
+    return finish_init();
+}
+
+/* weights.bump + weights_manifest.map as the reference's converter writes them */
 CK_EXPORT int ck_model_init_with_manifest(const char *weights_path, const char *manifest_path)
 {
-    (void)manifest_path;
-    return ck_model_init(weights_path);
+    if (g_model) return 0;
+    if (!manifest_path) return ck_model_init(weights_path);
+    g_model = ckb200_model_open_bump(weights_path, manifest_path, 1);
+    return finish_init();
 }
 
 CK_EXPORT void ck_model_free(void)

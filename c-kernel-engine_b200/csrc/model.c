@@ -1033,7 +1033,8 @@ size_t ckb200_model_weight_bytes(CKB200Model *m)
  * ckb200_model_open(spec, batch):
  *   "synthetic:<shape>[:seed]"  a named model SHAPE with device-generated random weights
  *                               (qwen2-0.5b, llama3-8b, llama3-70b, mini); for benchmarks and smoke runs
- *   "<path>"                    a file in the container format below (what tests and converters write)
+ *   "<path>"                    a BUMPWGT5 file of the reference's converter (bump_loader.c; its sidecar map is looked for
+ *                               beside it), or a file in the container format below (what tests write)
  *
  * File: magic "CKB2MDL1", u32 version = 1, the config (8 ints, 2 floats, 12 ints as in CKB200ModelConfig),
  * then the tensors in canonical order - per layer ln1, wq, wk, wv, wo, ln2, w1, w2; final gamma; LM head;
@@ -1095,7 +1096,14 @@ done:
 CKB200Model *ckb200_model_open(const char *spec, int batch)
 {
     if (!spec) { ckb_fail(CKB_ERR_STATE, "model_open: NULL spec"); return NULL; }
-    if (strncmp(spec, "synthetic:", 10) != 0) return open_file(spec, batch);
+    if (strncmp(spec, "synthetic:", 10) != 0) {
+        /* the reference's own weight file (BUMPWGT5 + sidecar map beside it) or this library's container */
+        char magic[8] = { 0 };
+        FILE *f = fopen(spec, "rb");
+        if (f) { if (fread(magic, 1, 8, f) != 8) magic[0] = 0; fclose(f); }
+        if (!memcmp(magic, "BUMPWGT5", 8)) return ckb200_model_open_bump(spec, NULL, batch);
+        return open_file(spec, batch);
+    }
     char name[64];
     unsigned long long seed = 1;
     const char *p = spec + 10, *colon = strchr(p, ':');

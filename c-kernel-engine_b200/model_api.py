@@ -46,6 +46,12 @@ def bind_model_api(lib):
     lib.ckb200_model_create.argtypes = [C.POINTER(CfgStruct)]
     lib.ckb200_model_free.argtypes = [C.c_void_p]
     lib.ckb200_model_free.restype = None
+    lib.ckb200_model_open.restype = C.c_void_p
+    lib.ckb200_model_open.argtypes = [C.c_char_p, C.c_int]
+    lib.ckb200_model_open_bump.restype = C.c_void_p
+    lib.ckb200_model_open_bump.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
+    lib.ckb200_model_config.restype = C.POINTER(CfgStruct)
+    lib.ckb200_model_config.argtypes = [C.c_void_p]
     lib.ckb200_model_upload_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
     lib.ckb200_model_tensor_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
     lib.ckb200_model_tensor_bytes.restype = C.c_size_t

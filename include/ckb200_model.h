@@ -49,8 +49,13 @@ typedef int (*ckb200_allreduce_fn)(void *ctx, float *buf, size_t count, void *st
 typedef int (*ckb200_tp_norm_fn)(void *ctx, float *x, const float *delta, const float *gamma, void *out_q8, int tokens, int d_model,
                                  int aligned_embed_dim, float eps, void *stream);
 
-/* "synthetic:<qwen2-0.5b|llama3-8b|llama3-70b|mini>[:seed]" or the path of a CKB2MDL1 model file; batch <= 0 keeps the default */
+/* "synthetic:<qwen2-0.5b|llama3-8b|llama3-70b|mini>[:seed]" or the path of a BUMPWGT5 or CKB2MDL1 model file; batch <= 0 keeps the default */
 CKB200Model *ckb200_model_open(const char *spec, int batch);
+/* A BUMPWGT5 file of the reference's converter (include/ckernel_bump_v5.h) with its sidecar map (name|dtype|file_offset|size|
+ * runtime_offset per line, version/v7/src/ckernel_model_load_v7.c:127-310); manifest_path NULL = weights_manifest.map beside the
+ * file.  Both SHA-256 digests of the file are verified; what the step executor cannot run is refused with a message. */
+CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_path, int batch);
+void ckb200_sha256(const void *data, size_t bytes, uint8_t out32[32]);
 const CKB200ModelConfig *ckb200_model_config(CKB200Model *m);
 int ckb200_model_reset(CKB200Model *m);                                  /* zero the KV cache, pos = 0 (ck_model_kv_cache_reset) */
 CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg);          /* NULL on failure (see ckb200_last_error) */

@@ -893,9 +893,6 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
  * K-quant projections; every other case (and prompts shorter than 16 tokens) falls back to T decode steps. */
 
 int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *stream);
-int ckb200_dev_prefill_rope_scatter(const float *q_tm, const float *k_tm, const float *v_tm, float *q_hm, float *k_cache, float *v_cache, const float *cos_cache,
-                                    const float *sin_cache, int tokens, int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int pos0, void *stream);
-int ckb200_dev_prefill_gather_q8k(const float *out_hm, void *out_q8, int tokens, int num_heads, int head_dim, int cols, void *stream);
 
 static int prefill_ok(const CKB200Model *m, int T)
 {

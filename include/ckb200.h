@@ -224,6 +224,13 @@ int ckb200_dev_rope_precompute_cache(float *cos_cache, float *sin_cache, int max
 int ckb200_dev_rope_forward_qk_pairwise(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
                                         int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
                                         int rotary_dim, const int *pos_dev, void *stream);
+/* Glue of the batched prefill pass (the generated ck_prefill, version/v7/scripts/codegen_prefill_v7.py:194-208, does these per token):
+ * rotate-half RoPE of token-major q [T][H*d] and k [T][Hkv*d] at positions pos0 + t, q scattered to head-major [H][T][d], k and v
+ * rows written into the caches [Hkv][max_seq_len][d]; and the way back: head-major attention output [H][T][d] gathered to token
+ * rows and quantised to Q8_K rows of `cols` elements (zero-padded). */
+int ckb200_dev_prefill_rope_scatter(const float *q_tm, const float *k_tm, const float *v_tm, float *q_hm, float *k_cache, float *v_cache, const float *cos_cache,
+                                    const float *sin_cache, int tokens, int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int pos0, void *stream);
+int ckb200_dev_prefill_gather_q8k(const float *out_hm, void *out_q8, int tokens, int num_heads, int head_dim, int cols, void *stream);
 /* swiglu_forward (src/kernels/swiglu_kernels.c:140-216): input [T][2D] gate then up, output [T][D]. */
 int ckb200_dev_swiglu_forward(const float *input, float *output, int tokens, int dim, void *stream);
 /* ck_residual_add_token_major (src/ckernel_orchestration.c:139-149). */

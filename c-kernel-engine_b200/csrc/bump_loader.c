@@ -26,6 +26,7 @@
 
 #include "../../include/ckb200.h"
 #include "../../include/ckb200_model.h"
+#include "bump_file.h"
 #include "launch.h"
 
 /* ------------------------------------------------------------------ SHA-256 (FIPS 180-4) */
@@ -210,20 +211,36 @@ static int upload_gamma(CKB200Model *m, FILE *f, const MapEntry *e, int n, const
     return rc;
 }
 
-CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_path, int batch)
+/* ------------------------------------------------------------------ an opened, verified file (shared with the lowered-IR executor) */
+
+struct CkbBump {
+    FILE *f;
+    BumpHeader h;
+    char *meta;              /* the JSON metadata blob (NUL-terminated) or NULL */
+    MapEntry *ent;
+    int n;
+    uint64_t payload_end;
+};
+
+void ckb_bump_close(CkbBump *b)
+{
+    if (!b) return;
+    if (b->f) fclose(b->f);
+    free(b->meta);
+    free(b->ent);
+    free(b);
+}
+
+CkbBump *ckb_bump_open(const char *bump_path, const char *manifest_path)
 {
     if (!bump_path) { ckb_fail(CKB_ERR_STATE, "bump: NULL path"); return NULL; }
-    FILE *f = fopen(bump_path, "rb");
-    if (!f) { ckb_fail(CKB_ERR_STATE, "bump: cannot open %s", bump_path); return NULL; }
-    CKB200Model *m = NULL;
-    MapEntry *ent = NULL;
-    char *meta = NULL;
-    void *buf = NULL;
-    size_t cap = 0;
-    FILE *mf = NULL;
+    CkbBump *b = (CkbBump *)calloc(1, sizeof *b);
+    if (!b) return NULL;
+    b->f = fopen(bump_path, "rb");
+    if (!b->f) { ckb_fail(CKB_ERR_STATE, "bump: cannot open %s", bump_path); free(b); return NULL; }
+    FILE *f = b->f, *mf = NULL;
     uint8_t hb[BUMP_HEADER], fb[BUMP_FOOTER];
-    BumpHeader h;
-    if (fread(hb, 1, BUMP_HEADER, f) != BUMP_HEADER || parse_header(hb, &h)) { ckb_fail(CKB_ERR_STATE, "bump: %s is not a BUMPWGT5 file", bump_path); goto fail; }
+    if (fread(hb, 1, BUMP_HEADER, f) != BUMP_HEADER || parse_header(hb, &b->h)) { ckb_fail(CKB_ERR_STATE, "bump: %s is not a BUMPWGT5 file", bump_path); goto fail; }
     if (fseeko(f, 0, SEEK_END)) goto fail;
     const uint64_t file_size = (uint64_t)ftello(f);
     uint64_t payload_end = file_size;
@@ -231,13 +248,14 @@ CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_
         const uint64_t meta_size = rd64(fb + 8);
         if (meta_size > file_size - BUMP_FOOTER - BUMP_DATA_START) { ckb_fail(CKB_ERR_STATE, "bump: metadata size in the footer exceeds the file"); goto fail; }
         payload_end = file_size - BUMP_FOOTER - meta_size;
-        meta = (char *)malloc(meta_size + 1);
-        if (!meta || read_at(f, payload_end, meta, meta_size)) { ckb_fail(CKB_ERR_STATE, "bump: cannot read the metadata blob"); goto fail; }
-        meta[meta_size] = 0;
+        b->meta = (char *)malloc(meta_size + 1);
+        if (!b->meta || read_at(f, payload_end, b->meta, meta_size)) { ckb_fail(CKB_ERR_STATE, "bump: cannot read the metadata blob"); goto fail; }
+        b->meta[meta_size] = 0;
         uint8_t dig[32];
-        ckb200_sha256(meta, meta_size, dig);
+        ckb200_sha256(b->meta, meta_size, dig);
         if (memcmp(dig, fb + 16, 32)) { ckb_fail(CKB_ERR_STATE, "bump: metadata SHA-256 mismatch in %s", bump_path); goto fail; }
     }
+    b->payload_end = payload_end;
     {   /* payload digest: dtype table + tensors, [data start, payload end) */
         Sha256 s;
         sha_init(&s);
@@ -253,7 +271,7 @@ CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_
         free(chunk);
         uint8_t dig[32];
         sha_final(&s, dig);
-        if (memcmp(dig, h.checksum, 32)) { ckb_fail(CKB_ERR_STATE, "bump: payload SHA-256 mismatch in %s (file corrupted or truncated)", bump_path); goto fail; }
+        if (memcmp(dig, b->h.checksum, 32)) { ckb_fail(CKB_ERR_STATE, "bump: payload SHA-256 mismatch in %s (file corrupted or truncated)", bump_path); goto fail; }
     }
     /* the sidecar map: given, or weights_manifest.map beside the file */
     char derived[4096];
@@ -264,26 +282,60 @@ CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_
     }
     mf = fopen(manifest_path, "r");
     if (!mf) { ckb_fail(CKB_ERR_STATE, "bump: cannot open the manifest map %s", manifest_path); goto fail; }
-    int n = 0, ncap = 0;
+    int ncap = 0;
     char line[4096];
     while (fgets(line, sizeof line, mf)) {
         if (line[0] == '#' || line[0] == '\n' || line[0] == '\r') continue;
         line[strcspn(line, "\r\n")] = 0;
         char *name = strtok(line, "|"), *dtype = strtok(NULL, "|"), *off = strtok(NULL, "|"), *size = strtok(NULL, "|"), *rt = strtok(NULL, "|");
         if (!name || !dtype || !off || !size || !rt) { ckb_fail(CKB_ERR_STATE, "bump: malformed manifest line (name|dtype|file_offset|size|runtime_offset)"); goto fail; }
-        if (n == ncap) {
+        if (b->n == ncap) {
             ncap = ncap ? 2 * ncap : 256;
-            MapEntry *g = (MapEntry *)realloc(ent, (size_t)ncap * sizeof *ent);
+            MapEntry *g = (MapEntry *)realloc(b->ent, (size_t)ncap * sizeof *b->ent);
             if (!g) goto fail;
-            ent = g;
+            b->ent = g;
         }
-        snprintf(ent[n].name, sizeof ent[n].name, "%s", name);
-        snprintf(ent[n].dtype, sizeof ent[n].dtype, "%s", dtype);
-        ent[n].off = strtoull(off, NULL, 0);
-        ent[n].size = strtoull(size, NULL, 0);
-        if (ent[n].off < BUMP_DATA_START || ent[n].off + ent[n].size > payload_end) { ckb_fail(CKB_ERR_STATE, "bump: tensor %s lies outside the payload", name); goto fail; }
-        ++n;
+        MapEntry *e = &b->ent[b->n];
+        snprintf(e->name, sizeof e->name, "%s", name);
+        snprintf(e->dtype, sizeof e->dtype, "%s", dtype);
+        e->off = strtoull(off, NULL, 0);
+        e->size = strtoull(size, NULL, 0);
+        if (e->off < BUMP_DATA_START || e->off + e->size > payload_end) { ckb_fail(CKB_ERR_STATE, "bump: tensor %s lies outside the payload", name); goto fail; }
+        ++b->n;
     }
+    fclose(mf);
+    return b;
+fail:
+    if (mf) fclose(mf);
+    ckb_bump_close(b);
+    return NULL;
+}
+
+int ckb_bump_find(const CkbBump *b, const char *name, const char **dtype, uint64_t *off, uint64_t *size)
+{
+    const MapEntry *e = find_entry(b->ent, b->n, name);
+    if (!e) return -1;
+    if (dtype) *dtype = e->dtype;
+    if (off) *off = e->off;
+    if (size) *size = e->size;
+    return 0;
+}
+
+int ckb_bump_read(const CkbBump *b, uint64_t off, void *dst, size_t n) { return read_at(b->f, off, dst, n); }
+const char *ckb_bump_meta(const CkbBump *b) { return b->meta; }
+
+CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_path, int batch)
+{
+    CkbBump *bf = ckb_bump_open(bump_path, manifest_path);
+    if (!bf) return NULL;
+    FILE *f = bf->f;
+    const BumpHeader h = bf->h;
+    const char *meta = bf->meta;
+    MapEntry *ent = bf->ent;
+    const int n = bf->n;
+    CKB200Model *m = NULL;
+    void *buf = NULL;
+    size_t cap = 0;
     /* configuration: header dimensions, metadata for what the header lacks, formats from the map */
     CKB200ModelConfig cfg;
     memset(&cfg, 0, sizeof cfg);
@@ -346,13 +398,12 @@ CKB200Model *ckb200_model_open_bump(const char *bump_path, const char *manifest_
     if (!rc) rc = upload_named(m, f, ent, n, out_w ? "output.weight" : "token_emb", -1, CKB_T_LM_HEAD, &buf, &cap);
     if (!rc && out_w) rc = upload_named(m, f, ent, n, "token_emb", -1, CKB_T_EMBEDDING, &buf, &cap);
     if (rc) goto fail;
-    free(buf); free(ent); free(meta);
-    fclose(mf); fclose(f);
+    free(buf);
+    ckb_bump_close(bf);
     return m;
 fail:
     if (m) ckb200_model_free(m);
-    free(buf); free(ent); free(meta);
-    if (mf) fclose(mf);
-    fclose(f);
+    free(buf);
+    ckb_bump_close(bf);
     return NULL;
 }

@@ -160,7 +160,7 @@ __global__ void kv_store_f16_kernel(unsigned short *__restrict__ kc, unsigned sh
 // one CTA per token: dequantise the table row of its id (out-of-range ids read row 0), zero the padding
 template <int FMT>
 __global__ void embedding_kernel(const int32_t *__restrict__ ids, int count, int vocab, const uint8_t *__restrict__ table,
-                                 const float *__restrict__ pos_emb, float *__restrict__ out, int embed, int aligned, int add_pos)
+                                 const float *__restrict__ pos_emb, float *__restrict__ out, int embed, int aligned, int table_cols, int add_pos)
 {
     constexpr int BS = DqTraits<FMT>::BS, BE = DqTraits<FMT>::BE;
     const int t = blockIdx.x;
@@ -171,7 +171,7 @@ __global__ void embedding_kernel(const int32_t *__restrict__ ids, int count, int
     }
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;
-    const size_t row_bytes = (size_t)((aligned + BE - 1) / BE) * BS;
+    const size_t row_bytes = (size_t)((table_cols + BE - 1) / BE) * BS;
     const uint8_t *row = table + (size_t)id * row_bytes;
     for (int i = threadIdx.x; i < aligned; i += blockDim.x) {
         float v = 0.0f;
@@ -250,6 +250,16 @@ extern "C" int ckb200_dev_rope_forward_qk(float *q, float *k, const float *cos_c
     return ckb_check_launch("rope_forward_qk");
 }
 
+// rope_forward_qk_with_rotary_dim (src/kernels/rope_kernels.c:320-417, :821-837): the half-split rotation over the first rotary_dim
+// channels only (pairs i, i + rotary_dim / 2; table rows of rotary_dim / 2 values); the channels above pass through
+extern "C" int ckb200_dev_rope_forward_qk_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                                          int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                                          int rotary_dim, const int *pos_dev, void *stream)
+{
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    return ckb200_dev_rope_forward_qk(q, k, cos_cache, sin_cache, num_heads, num_kv_heads, num_tokens, rotary_dim, aligned_head_dim, pos_offset, pos_dev, stream);
+}
+
 extern "C" int ckb200_dev_swiglu_forward(const float *input, float *output, int tokens, int dim, void *stream)
 {
     if (!input || !output || tokens <= 0 || dim <= 0) return 0;
@@ -291,21 +301,35 @@ extern "C" int ckb200_dev_kv_cache_store_f16(uint16_t *kv_cache_k, uint16_t *kv_
 
 template <int FMT>
 static int launch_embedding(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb, float *out,
-                            int embed, int aligned, int ctx, int add_pos, void *stream)
+                            int embed, int aligned, int table_cols, int ctx, int add_pos, void *stream)
 {
     if (!ids || !table || !out || ctx <= 0 || aligned <= 0) return 0;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     int n = count < 0 ? 0 : (count > ctx ? ctx : count);
-    embedding_kernel<FMT><<<ctx, 256, 0, ckb_stream(stream)>>>(ids, n, vocab, (const uint8_t *)table, pos_emb, out, embed, aligned, add_pos);
+    embedding_kernel<FMT><<<ctx, 256, 0, ckb_stream(stream)>>>(ids, n, vocab, (const uint8_t *)table, pos_emb, out, embed, aligned, table_cols, add_pos);
     return ckb_check_launch("embedding_forward");
+}
+
+// Rows of a table whose width differs from the output stride: a block-32 table of a hidden size that is not a multiple of 256
+// (rows of table_cols elements) feeding activation rows padded to out_stride.  fmt: 0 Q4_K, 1 Q6_K, 2 Q8_0.
+extern "C" int ckb200_dev_embedding_rows(const int32_t *ids, int count, int vocab, const void *table, int fmt, int table_cols, float *out, int out_stride,
+                                         int embed, void *stream)
+{
+    if (embed > table_cols || embed > out_stride) return ckb_fail(CKB_ERR_SHAPE, "embedding_rows: embed %d exceeds the table row %d or the output row %d", embed, table_cols, out_stride);
+    switch (fmt) {
+        case 0: return launch_embedding<DQ_Q4K>(ids, count, vocab, table, NULL, out, embed, out_stride, table_cols, count, 0, stream);
+        case 1: return launch_embedding<DQ_Q6K>(ids, count, vocab, table, NULL, out, embed, out_stride, table_cols, count, 0, stream);
+        case 2: return launch_embedding<DQ_Q80>(ids, count, vocab, table, NULL, out, embed, out_stride, table_cols, count, 0, stream);
+    }
+    return ckb_fail(CKB_ERR_SHAPE, "embedding_rows: format %d has no embedding kernel", fmt);
 }
 
 extern "C" int ckb200_dev_embedding_forward_q4_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
                                                  float *out, int embed, int aligned, int ctx, int add_pos, void *stream)
-{ return launch_embedding<DQ_Q4K>(ids, count, vocab, table, pos_emb, out, embed, aligned, ctx, add_pos, stream); }
+{ return launch_embedding<DQ_Q4K>(ids, count, vocab, table, pos_emb, out, embed, aligned, aligned, ctx, add_pos, stream); }
 extern "C" int ckb200_dev_embedding_forward_q6_k(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
                                                  float *out, int embed, int aligned, int ctx, int add_pos, void *stream)
-{ return launch_embedding<DQ_Q6K>(ids, count, vocab, table, pos_emb, out, embed, aligned, ctx, add_pos, stream); }
+{ return launch_embedding<DQ_Q6K>(ids, count, vocab, table, pos_emb, out, embed, aligned, aligned, ctx, add_pos, stream); }
 extern "C" int ckb200_dev_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
                                                  float *out, int embed, int aligned, int ctx, int add_pos, void *stream)
-{ return launch_embedding<DQ_Q80>(ids, count, vocab, table, pos_emb, out, embed, aligned, ctx, add_pos, stream); }
+{ return launch_embedding<DQ_Q80>(ids, count, vocab, table, pos_emb, out, embed, aligned, aligned, ctx, add_pos, stream); }

@@ -362,6 +362,48 @@ void attention_forward_decode_head_major_gqa_flash_sliding(const float *q_token,
     ckb_finish_out(out_token, dout, q_b, back);
 }
 
+/* the llama template's attention (src/kernels/attention_kernels.c:3006-3046, :3408-3448) */
+void attention_forward_decode_head_major_gqa_flash_f16kv(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
+                                                         int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
+                                                         int aligned_head_dim)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    if (ckb_ensure_init()) return;
+    const size_t q_b = (size_t)num_heads * aligned_head_dim * sizeof(float);
+    const size_t kv_b = (size_t)num_kv_heads * cache_capacity * aligned_head_dim * sizeof(float);
+    const float *dq = (const float *)ckb_stage_in(q_token, q_b, CKB_SLOT_X, 0);
+    const float *dk = (const float *)ckb_stage_in(k_cache, kv_b, CKB_SLOT_A, 0);
+    const float *dv = (const float *)ckb_stage_in(v_cache, kv_b, CKB_SLOT_B, 0);
+    int back;
+    float *dout = (float *)ckb_stage_out(out_token, q_b, CKB_SLOT_Y, &back);
+    if (!dq || !dk || !dv || !dout) return;
+    if (ckb200_dev_attention_decode_f16kv(dq, dk, dv, dout, num_heads, num_kv_heads, kv_tokens, cache_capacity, head_dim, aligned_head_dim, NULL, NULL) != 0)
+        return;
+    ckb_finish_out(out_token, dout, q_b, back);
+}
+
+void attention_forward_causal_head_major_gqa_flash_strided_f16kv(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                 int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                 int kv_stride_tokens)
+{
+    if (!q || !k || !v || !output) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || kv_stride_tokens < num_tokens) return;
+    if (head_dim <= 0 || aligned_head_dim < head_dim) return;
+    if (ckb_ensure_init()) return;
+    const size_t q_b = (size_t)num_heads * num_tokens * aligned_head_dim * sizeof(float);
+    const size_t kv_b = (size_t)num_kv_heads * kv_stride_tokens * aligned_head_dim * sizeof(float);
+    const float *dq = (const float *)ckb_stage_in(q, q_b, CKB_SLOT_X, 0);
+    const float *dk = (const float *)ckb_stage_in(k, kv_b, CKB_SLOT_A, 0);
+    const float *dv = (const float *)ckb_stage_in(v, kv_b, CKB_SLOT_B, 0);
+    int back;
+    float *dout = (float *)ckb_stage_out(output, q_b, CKB_SLOT_Y, &back);
+    if (!dq || !dk || !dv || !dout) return;
+    if (ckb200_dev_attention_prefill_f16kv(dq, dk, dv, dout, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, NULL) != 0) return;
+    ckb_finish_out(output, dout, q_b, back);
+}
+
 /* attention_flash_decode(out, q, k, v, T_q, T_k, H, D_h, scale) (src/kernels/attention_flash_true.c:696-722) for the
  * decode case T_q = 1: out/q [H][D_h], k/v [T_k][H][D_h] token-major.  With H = 1 this is exactly one head of the
  * head-major cache, which is how the reference's decode entry point calls it. */

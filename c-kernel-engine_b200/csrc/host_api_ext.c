@@ -161,6 +161,27 @@ void rope_forward_qk_pairwise_with_rotary_dim(float *q, float *k, const float *c
     ckb_finish_out(k, dk, kb, dk != k);
 }
 
+/* rope_forward_qk_with_rotary_dim (src/kernels/rope_kernels.c:821-837): half-split pairs over the first rotary_dim channels */
+void rope_forward_qk_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads, int num_kv_heads,
+                                     int num_tokens, int head_dim, int aligned_head_dim, int pos_offset, int rotary_dim)
+{
+    if (!q || !k || !cos_cache || !sin_cache || num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || head_dim <= 1) return;
+    if (ckb_ensure_init()) return;
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    const size_t qb = (size_t)num_heads * num_tokens * aligned_head_dim * sizeof(float);
+    const size_t kb = (size_t)num_kv_heads * num_tokens * aligned_head_dim * sizeof(float);
+    const size_t cb = (size_t)(pos_offset + num_tokens) * (rotary_dim / 2) * sizeof(float);
+    float *dq = (float *)ckb_stage_in(q, qb, CKB_SLOT_X, 0);
+    float *dk = (float *)ckb_stage_in(k, kb, CKB_SLOT_Y, 0);
+    const float *dc = (const float *)ckb_stage_in(cos_cache, cb, CKB_SLOT_A, 1);
+    const float *ds = (const float *)ckb_stage_in(sin_cache, cb, CKB_SLOT_B, 1);
+    if (!dq || !dk || !dc || !ds) return;
+    if (ckb200_dev_rope_forward_qk_with_rotary_dim(dq, dk, dc, ds, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, pos_offset, rotary_dim, NULL,
+                                                   NULL) != 0) return;
+    if (dq != q) cudaMemcpyAsync(q, dq, qb, cudaMemcpyDeviceToHost, ckb_stream(NULL));
+    ckb_finish_out(k, dk, kb, dk != k);
+}
+
 /* ------------------------------------------------------------------ small copies */
 
 /* add_inplace_f32 (include/ckernel_engine.h:1894, src/kernels/add_kernels_bf16.c:304): a[i] += b[i] */

@@ -691,11 +691,7 @@ static int issue_step_fused(CKB200Model *m, void *st)
     const CKB200ModelConfig *c = &m->c;
     const int L = c->num_layers;
     int rc;
-    switch (m->emb.fmt) {
-        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
-        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
-        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, 1, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, 1, 0, st); break;
-    }
+    rc = ckb200_dev_embedding_rows(m->tokens_dev, 1, c->vocab_size, m->emb.w, m->emb.fmt, m->emb.cols, m->x, m->Da, m->D, st);
     if (rc) return rc;
     float *cur = m->x, *nxt = m->x2;
     const float *delta = NULL;
@@ -772,11 +768,7 @@ static int issue_step(CKB200Model *m, void *st)
     const int B = c->batch, L = c->num_layers;
     int rc;
     /* embedding of the B current tokens -> x */
-    switch (m->emb.fmt) {
-        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
-        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
-        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, B, c->vocab_size, m->emb.w, NULL, m->x, m->D, m->Da, B, 0, st); break;
-    }
+    rc = ckb200_dev_embedding_rows(m->tokens_dev, B, c->vocab_size, m->emb.w, m->emb.fmt, m->emb.cols, m->x, m->Da, m->D, st);
     if (rc) return rc;
     float *delta = NULL;
     for (int l = 0; l < L; ++l) {
@@ -939,11 +931,7 @@ static int issue_prefill(CKB200Model *m, int T, void *st)
     const CKB200ModelConfig *c = &m->c;
     const int L = c->num_layers, kvw = m->Hkvl * m->d;
     int rc;
-    switch (m->emb.fmt) {
-        case FMT_Q4K: rc = ckb200_dev_embedding_forward_q4_k(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
-        case FMT_Q6K: rc = ckb200_dev_embedding_forward_q6_k(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
-        default: rc = ckb200_dev_embedding_forward_q8_0(m->tokens_dev, T, c->vocab_size, m->emb.w, NULL, m->pf_x, m->D, m->Da, T, 0, st); break;
-    }
+    rc = ckb200_dev_embedding_rows(m->tokens_dev, T, c->vocab_size, m->emb.w, m->emb.fmt, m->emb.cols, m->pf_x, m->Da, m->D, st);
     if (rc) return rc;
     const float *delta = NULL;
     for (int l = 0; l < L; ++l) {

@@ -203,6 +203,14 @@ int ckb200_dev_attention_prefill_window(const float *q, const float *k, const fl
 int ckb200_dev_attention_decode_sliding(const float *q, const float *k_cache, const float *v_cache, float *out, int batch,
                                         long long kv_batch_stride, int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity,
                                         int head_dim, int aligned_head_dim, int sliding_window, void *stream);
+/* attention_forward_decode_head_major_gqa_flash_f16kv (src/kernels/attention_kernels.c:3408-3448) and
+ * attention_forward_causal_head_major_gqa_flash_strided_f16kv (:3006-3046), the form the llama template binds: q, k, v go
+ * through fp16 and the output accumulator is rounded to fp16 after every key, in key order.  One sequence; with pos_dev the
+ * context length is *pos_dev + 1.  At most 25 600 keys (the per-key factors of the ordered walk live in shared memory). */
+int ckb200_dev_attention_decode_f16kv(const float *q, const float *k_cache, const float *v_cache, float *out, int num_heads, int num_kv_heads,
+                                      int kv_tokens, int cache_capacity, int head_dim, int aligned_head_dim, const int *pos_dev, void *stream);
+int ckb200_dev_attention_prefill_f16kv(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int num_tokens,
+                                       int head_dim, int aligned_head_dim, int kv_stride_tokens, void *stream);
 
 /* kv_cache_store (src/kernels/kv_cache_kernels.c:111-129): k, v [Hkv][head_dim] -> cache[Hkv][max_seq][head_dim] at pos
  * (or at *pos_dev when given). */
@@ -216,6 +224,11 @@ int ckb200_dev_rope_precompute_cache_split(float *cos_cache, float *sin_cache, i
 int ckb200_dev_rope_forward_qk(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
                                int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
                                const int *pos_dev, void *stream);
+/* rope_forward_qk_with_rotary_dim (src/kernels/rope_kernels.c:821-837): half-split pairs (i, i + rotary_dim / 2) of the first
+ * rotary_dim channels, tables with rows of rotary_dim / 2 values (rope_precompute_cache). */
+int ckb200_dev_rope_forward_qk_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
+                                               int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
+                                               int rotary_dim, const int *pos_dev, void *stream);
 /* rope_precompute_cache (src/kernels/rope_kernels.c:270-316): rows of rotary_dim / 2 values (rotary_dim <= 0 or > head_dim means
  * head_dim), positions divided by scaling_factor when linear_scaling != 0; and rope_forward_qk_pairwise_with_rotary_dim
  * (:839-866): pairs (2i, 2i+1) of the first rotary_dim elements of every head row are rotated. */
@@ -242,6 +255,10 @@ int ckb200_dev_embedding_forward_q6_k(const int32_t *ids, int count, int vocab, 
                                       float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
 int ckb200_dev_embedding_forward_q8_0(const int32_t *ids, int count, int vocab, const void *table, const float *pos_emb,
                                       float *out, int embed, int aligned, int ctx, int add_pos, void *stream);
+/* The same lookup for a table whose rows are table_cols elements wide while the output rows are out_stride floats apart (a
+ * block-32 table of a hidden size that is not a multiple of 256 feeding padded activation rows); fmt 0 Q4_K, 1 Q6_K, 2 Q8_0. */
+int ckb200_dev_embedding_rows(const int32_t *ids, int count, int vocab, const void *table, int fmt, int table_cols, float *out, int out_stride,
+                              int embed, void *stream);
 
 /* ------------------------------------------------------------------ fused glue of a device-resident step
  * Each merges ops that the reference's generated decode function issues back to back

@@ -108,6 +108,13 @@ void attention_forward_causal_head_major_gqa_flash_strided_sliding(const float *
 void attention_forward_decode_head_major_gqa_flash_sliding(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
                                                            int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
                                                            int aligned_head_dim, int sliding_window);
+/* fp16-rounded K/V with an fp16-rounded accumulator, key order kept (src/kernels/attention_kernels.c:3006-3046, :3408-3448) */
+void attention_forward_decode_head_major_gqa_flash_f16kv(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
+                                                         int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
+                                                         int aligned_head_dim);
+void attention_forward_causal_head_major_gqa_flash_strided_f16kv(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                 int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                 int kv_stride_tokens);
 /* fp16 KV cache: include/ckernel_engine.h:1232-1241, :1682-1690 */
 void attention_forward_decode_head_major_gqa_flash_f16cache(const float *q_token, const uint16_t *k_cache, const uint16_t *v_cache,
                                                             float *out_token, int num_heads, int num_kv_heads, int kv_tokens,
@@ -181,6 +188,8 @@ void rope_precompute_cache(float *cos_cache, float *sin_cache, int max_seq_len, 
 void rope_forward_qk_pairwise_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads,
                                               int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim, int pos_offset,
                                               int rotary_dim);
+void rope_forward_qk_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads, int num_kv_heads,
+                                     int num_tokens, int head_dim, int aligned_head_dim, int pos_offset, int rotary_dim);    /* rope_kernels.c:821-837 */
 
 /* ---- small copies: add_inplace_f32 include/ckernel_engine.h:1894 (src/kernels/add_kernels_bf16.c:304-330),
  *      logits_copy_to_position src/kernels/kv_cache_kernels.c:178-191 */

@@ -661,6 +661,75 @@ void oracle_attention_forward_decode_head_major_gqa_flash_sliding(const float *q
     }
 }
 
+/* ---- "Llama-parity" attention (src/kernels/attention_kernels.c:1673-1744): q, k and v pass through fp16 before use and the
+ * output accumulator is rounded to fp16 after every update, key by key, with the online max / sum recurrence.  The result depends
+ * on the order of the keys, so a device kernel has to walk them in the same order. ---- */
+static float orc_r16(float x) { return oracle_fp16_to_fp32(oracle_fp32_to_fp16(x)); }
+
+static void orc_flash_query_f16kv(const float *q, const float *kh, const float *vh, int kv_tokens, int hd, int ad, float scale, float *out)
+{
+    for (int d = 0; d < ad; ++d) out[d] = 0.0f;
+    if (kv_tokens <= 0) return;
+    float sum = 0.0f, mx = -INFINITY;
+    for (int j = 0; j < kv_tokens; ++j) {
+        const float *k = kh + (size_t)j * ad, *v = vh + (size_t)j * ad;
+        float dot = 0.0f;
+        for (int d = 0; d < hd; ++d) dot += orc_r16(q[d]) * orc_r16(k[d]);
+        const float score = dot * scale, prev = mx;
+        float max_scale = 1.0f, value_scale = 1.0f;
+        if (score > mx) {
+            mx = score;
+            max_scale = isfinite(prev) ? expf(prev - mx) : 0.0f;
+            for (int d = 0; d < hd; ++d) out[d] = orc_r16(out[d] * max_scale);
+        } else {
+            value_scale = expf(score - mx);
+        }
+        for (int d = 0; d < hd; ++d) out[d] = orc_r16(out[d] + value_scale * orc_r16(v[d]));
+        sum = sum * max_scale + value_scale;
+    }
+    if (sum > 0.0f) {
+        const float inv = 1.0f / sum;
+        for (int d = 0; d < hd; ++d) out[d] *= inv;
+    } else {
+        for (int d = 0; d < hd; ++d) out[d] = 0.0f;
+    }
+}
+
+/* src/kernels/attention_kernels.c:3408-3448 */
+void oracle_attention_forward_decode_head_major_gqa_flash_f16kv(const float *q_token, const float *k_cache, const float *v_cache, float *out_token,
+                                                                int num_heads, int num_kv_heads, int kv_tokens, int cache_capacity, int head_dim,
+                                                                int aligned_head_dim)
+{
+    if (!q_token || !k_cache || !v_cache || !out_token) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || kv_tokens <= 0 || cache_capacity <= 0) return;
+    if (kv_tokens > cache_capacity || head_dim <= 0 || aligned_head_dim <= 0) return;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const size_t hs = (size_t)cache_capacity * aligned_head_dim;
+    for (int h = 0; h < num_heads; ++h) {
+        const int kvh = (int)((long long)h * num_kv_heads / num_heads);
+        orc_flash_query_f16kv(q_token + (size_t)h * aligned_head_dim, k_cache + kvh * hs, v_cache + kvh * hs, kv_tokens, head_dim, aligned_head_dim, scale,
+                              out_token + (size_t)h * aligned_head_dim);
+    }
+}
+
+/* src/kernels/attention_kernels.c:3006-3046: query i of a prompt sees keys 0..i */
+void oracle_attention_forward_causal_head_major_gqa_flash_strided_f16kv(const float *q, const float *k, const float *v, float *output, int num_heads,
+                                                                        int num_kv_heads, int num_tokens, int head_dim, int aligned_head_dim,
+                                                                        int kv_stride_tokens)
+{
+    if (!q || !k || !v || !output) return;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_tokens <= 0 || kv_stride_tokens < num_tokens) return;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const size_t hs = (size_t)kv_stride_tokens * aligned_head_dim;
+    for (int h = 0; h < num_heads; ++h) {
+        const int kvh = (int)((long long)h * num_kv_heads / num_heads);
+        for (int i = 0; i < num_tokens; ++i) {
+            const size_t row = ((size_t)h * num_tokens + i) * aligned_head_dim;
+            orc_flash_query_f16kv(q + row, k + kvh * hs, v + kvh * hs, i + 1, head_dim, aligned_head_dim, scale, output + row);
+        }
+    }
+}
+
 /* ---- KV cache store (src/kernels/kv_cache_kernels.c:70-129) ---- */
 void oracle_kv_cache_store(float *kc, float *vc, const float *k, const float *v, int layer, int pos,
                            int num_kv_heads, int head_dim, int max_seq_len)
@@ -751,6 +820,15 @@ void oracle_rope_forward_qk(float *q, float *k, const float *cos_cache, const fl
     orc_rope_heads(k, cos_cache, sin_cache, num_kv_heads, num_tokens, head_dim, aligned_head_dim, pos_offset);
 }
 
+/* rope_forward_qk_with_rotary_dim (src/kernels/rope_kernels.c:320-417, :821-837): pairs (i, i + rotary_dim / 2), rows of rotary_dim / 2 */
+void oracle_rope_forward_qk_with_rotary_dim(float *q, float *k, const float *cos_cache, const float *sin_cache, int num_heads, int num_kv_heads,
+                                            int num_tokens, int head_dim, int aligned_head_dim, int pos_offset, int rotary_dim)
+{
+    if (rotary_dim <= 0 || rotary_dim > head_dim) rotary_dim = head_dim;
+    orc_rope_heads(q, cos_cache, sin_cache, num_heads, num_tokens, rotary_dim, aligned_head_dim, pos_offset);
+    orc_rope_heads(k, cos_cache, sin_cache, num_kv_heads, num_tokens, rotary_dim, aligned_head_dim, pos_offset);
+}
+
 /* ---- RMSNorm (src/kernels/rmsnorm_kernels.c:38-71 scalar form; :245-248 zero pad) ---- */
 void oracle_rmsnorm_forward(const float *in, const float *gamma, float *out, float *rstd_cache, int tokens,
                             int d_model, int aligned, float eps)
@@ -783,6 +861,11 @@ void oracle_residual_add_token_major(const float *a, const float *b, float *out,
 {
     const size_t n = (size_t)tokens * aligned;
     for (size_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
+}
+
+void oracle_ck_residual_add_token_major(const float *a, const float *b, float *out, int tokens, int aligned)      /* the reference's symbol */
+{
+    oracle_residual_add_token_major(a, b, out, tokens, aligned);
 }
 
 /* ---- embedding lookup (src/kernels/embedding_kernels.c:76-129 q4_k, :131-184 q8_0, :186-239 q6_k) ---- */

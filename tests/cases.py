@@ -193,6 +193,24 @@ def attention_decode_f16cache(lib, prefix, q, kc16, vc16, tokens: int, hd: int |
     return out
 
 
+def attention_decode_f16kv(lib, prefix, q, kc, vc, tokens: int, hd: int | None = None) -> np.ndarray:
+    heads, d = q.shape
+    kv_heads, cap, _ = kc.shape
+    out = np.full((heads, d), np.nan, dtype=np.float32)
+    fn(lib, prefix, "attention_forward_decode_head_major_gqa_flash_f16kv")(
+        fptr(q), fptr(kc), fptr(vc), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(cap), C.c_int(hd or d), C.c_int(d))
+    return out
+
+
+def attention_prefill_f16kv(lib, prefix, q, k, v, hd: int) -> np.ndarray:
+    heads, tokens, ad = q.shape
+    kv_heads, stride, _ = k.shape
+    out = np.full((heads, tokens, ad), np.nan, dtype=np.float32)
+    fn(lib, prefix, "attention_forward_causal_head_major_gqa_flash_strided_f16kv")(
+        fptr(q), fptr(k), fptr(v), fptr(out), C.c_int(heads), C.c_int(kv_heads), C.c_int(tokens), C.c_int(hd), C.c_int(ad), C.c_int(stride))
+    return out
+
+
 def kv_cache_store_f16(lib, prefix, kc16, vc16, k, v, pos: int):
     kv_heads, cap, d = kc16.shape
     fn(lib, prefix, "kv_cache_store_f16")(vptr(kc16), vptr(vc16), fptr(k), fptr(v), C.c_int(0), C.c_int(pos), C.c_int(kv_heads),
@@ -302,6 +320,10 @@ def logits_copy(lib, prefix, src: np.ndarray, rows: int, position: int) -> np.nd
     return dst
 
 
+F16KV_DECODE = [(8, 2, 128, 300, 320, 81), (14, 2, 64, 70, 96, 82), (4, 4, 64, 1, 8, 83)]      # heads, kv heads, d, tokens, capacity, seed
+F16KV_PREFILL = [(8, 4, 64, 64, 37, 40, 84), (4, 2, 72, 64, 9, 9, 85)]                          # heads, kv heads, ad, head_dim, tokens, kv stride, seed
+
+
 def boundary_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
     """Seeded cases for the entry points above; run through the reference (golden file), the oracle and the CUDA library."""
     out: dict[str, np.ndarray] = {}
@@ -335,6 +357,13 @@ def boundary_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
     rope_qk_pairwise(lib, prefix, q, k, cos2, sin2, pos=30, hd=64, rotary_dim=32)
     out["rope_pair_partial_q"], out["rope_pair_partial_k"] = q, k
 
+    for i, (heads, kv_heads, d, tokens, cap, seed) in enumerate(F16KV_DECODE):
+        q, kc, vc = attention_inputs(seed, heads, kv_heads, d, tokens, cap)
+        out[f"attn_f16kv_decode_{i}"] = attention_decode_f16kv(lib, prefix, q, kc, vc, tokens)
+    for i, (heads, kv_heads, ad, hd, tokens, stride, seed) in enumerate(F16KV_PREFILL):
+        q, k, v = prefill_attention_inputs(seed, heads, kv_heads, ad, hd, tokens, stride)
+        out[f"attn_f16kv_prefill_{i}"] = attention_prefill_f16kv(lib, prefix, q, k, v, hd)
+
     a = rng.standard_normal(1000).astype(np.float32)
     b = rng.standard_normal(1000).astype(np.float32)
     out["add_inplace"] = add_inplace(lib, prefix, a, b)
@@ -343,7 +372,7 @@ def boundary_outputs(lib, prefix: str) -> dict[str, np.ndarray]:
 
 
 # Outputs the oracle reproduces bit for bit (the reference computes them in scalar order, or they are integer work plus one fp32 product per block)
-BOUNDARY_BIT_EXACT = ("gemm_nt_f32_q6_k", "gemm_f32_q6_k", "add_inplace", "logits_copy", "gemv_contract", "gemm_nt_contract", "rope_")
+BOUNDARY_BIT_EXACT = ("gemm_nt_f32_q6_k", "gemm_f32_q6_k", "add_inplace", "logits_copy", "gemv_contract", "gemm_nt_contract", "rope_", "attn_f16kv_")
 
 # ----------------------------------------------------------------------------- the golden case list
 

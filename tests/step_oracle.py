@@ -22,6 +22,14 @@ def cols_for(fmt, k):
     return (k + 31) // 32 * 32 if fmt in (2, 3) else round256(k)
 
 
+def embed_row(lib, fmt, table, token, vocab, d, table_cols, da):
+    """One embedding row, padded with zeros to da floats.  The reference's lookup takes its table row stride from the aligned width it is given
+    (src/kernels/embedding_kernels.c:155), so it is called with the table's own row width."""
+    x = np.zeros(da, np.float32)
+    x[:table_cols] = cases.embedding(lib, "oracle_", FMT[fmt], [token], table, vocab, d, table_cols)[0]
+    return x
+
+
 class CpuModel:
     """Whole (unsharded) model on the host: random weights in the reference's block formats."""
 
@@ -64,7 +72,7 @@ class CpuModel:
         c = self.cfg
         D, H, Hkv, d, I = c["embed_dim"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["intermediate_size"]
         efmt, _, ecols, edata = self.lm_head
-        x = cases.embedding(lib, "oracle_", FMT[efmt], [token], edata, c["vocab_size"], D, self.Da)[0].copy()
+        x = embed_row(lib, efmt, edata, token, c["vocab_size"], D, ecols, self.Da)
         cos, sin = cases.rope_cache(lib, "oracle_", c["max_seq_len"], d, c["rope_theta"])
         for l, lay in enumerate(self.layers):
             h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN1"], D, c["rms_eps"])[0]
@@ -160,8 +168,8 @@ class TpShard:
         cpu, c, tp = self.cpu, self.cpu.cfg, self.tp
         D, d = c["embed_dim"], c["head_dim"]
         Hl, Hkvl, Il = c["num_heads"] // tp, c["num_kv_heads"] // tp, c["intermediate_size"] // tp
-        efmt, _, _, edata = cpu.lm_head
-        x = cases.embedding(lib, "oracle_", FMT[efmt], [token], edata, c["vocab_size"], D, cpu.Da)[0].copy()
+        efmt, _, ecols, edata = cpu.lm_head
+        x = embed_row(lib, efmt, edata, token, c["vocab_size"], D, ecols, cpu.Da)
         cos, sin = cases.rope_cache(lib, "oracle_", c["max_seq_len"], d, c["rope_theta"])
         for l, lay in enumerate(self.layers):
             h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN1"], D, c["rms_eps"])[0]

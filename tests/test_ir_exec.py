@@ -177,3 +177,32 @@ def test_decode_past_the_context_is_refused(ck, tmp_path):
         ck.ckb200_clear_error()
     finally:
         ck.ckb200_ir_free(h)
+
+
+@pytest.mark.gpu
+def test_v7_abi_replays_the_call_ir_beside_the_weights(ck, orc, pkg, tmp_path):
+    """The reference's run folder (weights.bump, weights_manifest.map, lowered_decode_call.json) opened through ck_model_init as ck_chat.py does."""
+    import shutil
+    cfg, cpu, bump, mp = write_model(tmp_path, "llama_kquant")
+    shutil.copyfile(ir_cases.fixture_path("llama_kquant"), tmp_path / "lowered_decode_call.json")
+    want_model = ir_oracle.IrCpuModel(ir_cases.fixture_path("llama_kquant"), bump, mp, orc)
+    v7 = C.CDLL(pkg.find_lib("libckb200_model_v7.so"))
+    assert v7.ck_model_init(str(bump).encode()) == 0, ck.ckb200_last_error_message()
+    try:
+        V = v7.ck_model_get_vocab_size()
+        assert V == cfg["vocab_size"] and v7.ck_model_get_context_window() == cfg["max_seq_len"]
+        prompt = np.array(TOKENS, np.int32)
+        assert v7.ck_model_embed_tokens(prompt.ctypes.data_as(C.POINTER(C.c_int32)), len(TOKENS)) == 0
+        out = np.zeros(V, np.float32)
+        assert v7.ck_model_forward(cases.fptr(out)) == 0
+        for tok in TOKENS:
+            want = want_model.decode(tok)
+        assert cosine(out, want) >= 0.9999 and float(np.max(np.abs(out - want))) <= 2e-2 * float(np.max(np.abs(want)))
+        assert v7.ck_model_decode(C.c_int32(9), cases.fptr(out)) == 0
+        want = want_model.decode(9)
+        assert cosine(out, want) >= 0.9999
+        assert v7.ck_model_get_active_tokens() == len(TOKENS) + 1
+        v7.ck_model_kv_cache_reset()
+        assert v7.ck_model_get_active_tokens() == 0
+    finally:
+        v7.ck_model_free()

@@ -24,12 +24,17 @@
 //        warp 1       issuer: tcgen05.mma from one elected lane; tcgen05.commit frees stages and publishes accumulators
 //        warps 4-11   two expander warpgroups: weights -> fp16 operand tiles, alternate k-stages (Q4_K) or halves (Q6_K)
 //        warps 12-19  drain: tcgen05.ld of T|T2 (two TMEM buffers, 512 columns), fp32 sums in registers
-//    One ring carries both operands: 3 stages of 128-deep k-steps for the 128-token tile (5 of 64-deep for the 32-token tile).  A
-//    stage has ONE "full" barrier (the expander warps that fill it + the loader's expect_tx arrival + the copy's bytes) and ONE
-//    "empty" barrier (a tcgen05.commit) that the loader and the expanders both wait on: the issuer's timeline is a chain of barrier
-//    waits, MMA issues and commits of roughly 100-180 cycles each, so every stage costs it one wait and one commit, not two of
-//    each, and the deeper stage puts eight MMAs (540 tensor cycles) behind each such pair instead of four.
+//    One ring of 6 stages carries both operands of a 64-deep k-stage.  A stage has ONE "full" barrier (4 expander
+//    warps + the loader's expect_tx arrival + the copy's bytes) and ONE "empty" barrier (a tcgen05.commit) that the
+//    loader and the expanders both wait on: the issuer's timeline is a chain of barrier waits, MMA issues and commits
+//    of roughly 100-180 cycles each, so every stage costs it one wait and one commit, not two of each.
 // Every wait is bounded; a timeout sets the device error word, the CTA drains, frees TMEM and returns.
+//
+// Measured and not kept (each correct, each 3-8 % slower than this form): 128-deep ring stages (eight MMAs per barrier round), weight
+// bytes loaded a superblock ahead into two register sets with an L2 prefetch (the expanders no longer wait for loads), two issuer
+// warps on alternate superblocks (one accumulator buffer each).  The roles are co-limited: issuer chain, expanders, drain and the
+// shared-memory data pipe (63 % busy: operand reads by the tensor core, tile writes, bulk copies) each need about a thousand cycles
+// per 128-deep step, and they share four schedulers, so relieving one of them moves the wait to the next.
 #include "quant_units.cuh"
 #include "launch.h"
 #include "pdl.cuh"
@@ -48,20 +53,15 @@ constexpr int TC_AUX = 2 * TC_CHUNK;                  // 16-deep tile (mins / bs
 // per-stage chain (weight loads, barrier waits, MMA issue, commit) is overlapped by the neighbour.
 template <int NT>
 struct TcCfg {
-    // A ring stage carries both operands of KD 64-deep k-steps.  The issuer pays one barrier wait and one commit per stage (each a
-    // round trip of 100-200 cycles), so the prefill shape runs 128-deep stages: eight MMAs per wait instead of four.
-    static constexpr int KD = NT == 128 ? 2 : 1;
-    static constexpr int STAGES = NT == 128 ? 3 : 5;          // ring depth
-    static constexpr int SPB = 4 / KD, SPB_SHIFT = KD == 2 ? 1 : 2;      // ring stages per superblock
+    static constexpr int STAGES = NT == 128 ? 6 : 5;          // ring depth (a stage = weight tile + activation tile)
     static constexpr int B_CHUNK = NT * 16;                   // one 8-element k-chunk of NT tokens
     static constexpr int B_STAGE = 8 * B_CHUNK;               // 64-deep k-stage of NT tokens
     static constexpr int B_AUX = 2 * B_CHUNK;                 // 16-deep bsum tile
     // activation blob of one (token tile, superblock): 4 k-stages, the bsum tile, NT block scales
     static constexpr int XBLOB_B2 = 4 * B_STAGE, XBLOB_DX = XBLOB_B2 + B_AUX, XBLOB = XBLOB_DX + NT * 4;   // a multiple of 16
     static constexpr int OFF_A = 0;                                      // weight tiles   [STAGES][16 KB]
-    static constexpr int A_RING = KD * TC_STAGE, B_RING = KD * B_STAGE;  // bytes of one ring stage per operand
-    static constexpr int OFF_B = OFF_A + STAGES * A_RING;                // activation tiles
-    static constexpr int OFF_A2 = OFF_B + STAGES * B_RING;               // mins tiles     [2][4 KB]
+    static constexpr int OFF_B = OFF_A + STAGES * TC_STAGE;              // activation tiles
+    static constexpr int OFF_A2 = OFF_B + STAGES * B_STAGE;              // mins tiles     [2][4 KB]
     static constexpr int OFF_B2 = OFF_A2 + 2 * TC_AUX;                   // bsum tiles     [2]
     static constexpr int OFF_DX = OFF_B2 + 2 * B_AUX;                    // block scales   [2][NT] fp32
     static constexpr int OFF_BAR = OFF_DX + 2 * NT * 4;
@@ -248,14 +248,10 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n0 = blockIdx.x * TC_ROWS, mt = blockIdx.y, m0 = mt * NT;
-    const uint32_t stages = (uint32_t)nb * (uint32_t)Cfg::SPB;           // ring stages of this slice
-    constexpr uint32_t SPB = Cfg::SPB, SPB_SHIFT = Cfg::SPB_SHIFT, KD = Cfg::KD;
+    const uint32_t stages = (uint32_t)nb * 4u;
 
     if (tid == 0) {
-        // arrivals on a stage's "full" barrier: the loader plus the expander warps that write into it (with 128-deep stages both
-        // Q4_K expander sets fill one stage, a 64-deep half each; a Q6_K set fills a whole stage by itself)
-        constexpr int FULL_ARRIVALS = (WF == TC_W_Q4K && Cfg::KD == 2) ? 9 : 5;
-        for (int i = 0; i < TC_STAGES; ++i) { mbar_init(BAR(BAR_FULL + i), FULL_ARRIVALS); mbar_init(BAR(BAR_EMPTY + i), 1); }
+        for (int i = 0; i < TC_STAGES; ++i) { mbar_init(BAR(BAR_FULL + i), 5); mbar_init(BAR(BAR_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(BAR_A2_EMPTY + i), 1);
             mbar_init(BAR(BAR_B2_EMPTY + i), 1 + Cfg::DRAIN_WARPS);   // the T2 MMA (or, for Q6_K, the unit's last commit) and the drain warps
@@ -284,19 +280,18 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             // ------------------------------------------------------------ loader
             uint32_t issued = 0;
             for (uint32_t it = 0; it < stages; ++it) {
-                const uint32_t b = it >> SPB_SHIFT, s = it & (SPB - 1u), i = it % TC_STAGES, x = b & 1u;
-                const bool last = s == SPB - 1u;       // the superblock's last ring stage
+                const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, x = b & 1u;
                 const uint8_t *blob = xt + ((size_t)mt * nb_row + kb0 + b) * Cfg::XBLOB;
                 TC_WAIT(BAR(BAR_EMPTY + i), ((it / TC_STAGES) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT);
-                if (last) { TC_WAIT(BAR(BAR_B2_EMPTY + x), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }
+                if (s == 3) { TC_WAIT(BAR(BAR_B2_EMPTY + x), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }
                 if (tc_elect_one()) {
                     // the bsum tile of the superblock rides on the barrier of its last k-stage (the issuer needs it for the T2 MMA
                     // right after that stage); the block scales have their own barrier, for the drain warps
-                    const bool with_bsums = last && WF == TC_W_Q4K;
-                    mbar_arrive_expect_tx(BAR(BAR_FULL + i), Cfg::B_RING + (with_bsums ? Cfg::B_AUX : 0));
-                    bulk_g2s(sB + i * Cfg::B_RING, blob + s * Cfg::B_RING, Cfg::B_RING, BAR(BAR_FULL + i));
+                    const bool with_bsums = s == 3 && WF == TC_W_Q4K;
+                    mbar_arrive_expect_tx(BAR(BAR_FULL + i), Cfg::B_STAGE + (with_bsums ? Cfg::B_AUX : 0));
+                    bulk_g2s(sB + i * Cfg::B_STAGE, blob + s * Cfg::B_STAGE, Cfg::B_STAGE, BAR(BAR_FULL + i));
                     if (with_bsums) bulk_g2s(sB2 + x * Cfg::B_AUX, blob + Cfg::XBLOB_B2, Cfg::B_AUX, BAR(BAR_FULL + i));
-                    if (last) {
+                    if (s == 3) {
                         mbar_arrive_expect_tx(BAR(BAR_DX_FULL + x), NT * 4);
                         bulk_g2s(sDX + x * NT * 4, blob + Cfg::XBLOB_DX, NT * 4, BAR(BAR_DX_FULL + x));
                     }
@@ -311,24 +306,22 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
             // ------------------------------------------------------------ issuer: the warp runs the loop and the waits uniformly
             // (descriptors and addresses stay in uniform registers), one elected lane issues
             const uint64_t dA = tc_smem_desc(sA, TC_CHUNK), dB = tc_smem_desc(sB, Cfg::B_CHUNK), dA2 = tc_smem_desc(sA2, TC_CHUNK), dB2 = tc_smem_desc(sB2, Cfg::B_CHUNK);
-            uint32_t i = 0, ring_phase = 0;            // ring slot and its parity, stepped instead of divided out of `it`
             for (uint32_t it = 0; it < stages; ++it) {
-                const uint32_t b = it >> SPB_SHIFT, s = it & (SPB - 1u), buf = b & 1u, tacc = tmem + Cfg::T_BUF * buf;
+                const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, buf = b & 1u, tacc = tmem + Cfg::T_BUF * buf;
                 if (s == 0) {
                     TC_WAIT(BAR(BAR_T_EMPTY + buf), ((b >> 1) & 1u) ^ 1u, DEV_ERR_MMA_WAIT);
                     tc_fence_after();                  // orders the drain's tcgen05.ld of this buffer before the MMAs that overwrite it
                 }
                 if (lane == 0) TC_TRACE(0, 3 * it + 0);
-                TC_WAIT(BAR(BAR_FULL + i), ring_phase, DEV_ERR_FULL_WAIT);
+                TC_WAIT(BAR(BAR_FULL + i), (it / TC_STAGES) & 1u, DEV_ERR_FULL_WAIT);
                 if (lane == 0) TC_TRACE(0, 3 * it + 1);
-                const uint64_t da = dA + (uint64_t)(i * (Cfg::A_RING >> 4)), db = dB + (uint64_t)(i * (Cfg::B_RING >> 4));
+                const uint64_t da = dA + (uint64_t)(i * (TC_STAGE >> 4)), db = dB + (uint64_t)(i * (Cfg::B_STAGE >> 4));
                 if (tc_elect_one()) {
-                    // the 64-deep halves of a ring stage lie one after the other, each as eight 8-element k-chunks: 16-deep step k is at k * 2 chunks
 #pragma unroll
-                    for (int k = 0; k < 4 * (int)KD; ++k)
+                    for (int k = 0; k < 4; ++k)
                         tc_mma(tacc, da + (uint64_t)(k * (2 * TC_CHUNK >> 4)), db + (uint64_t)(k * (2 * Cfg::B_CHUNK >> 4)), Cfg::IDESC, (s | (uint32_t)k) ? 1u : 0u);
                     tc_commit(BAR(BAR_EMPTY + i));
-                    if (s == SPB - 1u) {
+                    if (s == 3) {
                         if constexpr (WF == TC_W_Q4K) {
                             tc_mma(tacc + Cfg::T2_OFF, dA2 + (uint64_t)(buf * (TC_AUX >> 4)), dB2 + (uint64_t)(buf * (Cfg::B_AUX >> 4)), Cfg::IDESC, 0u);
                             tc_commit(BAR(BAR_A2_EMPTY + buf));
@@ -338,7 +331,6 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                     }
                     TC_TRACE(0, 3 * it + 2);
                 }
-                if (++i == TC_STAGES) { i = 0; ring_phase ^= 1u; }
             }
         }
     } else if (warp < 12) {
@@ -366,11 +358,10 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                 const uint32_t qhw[8] = {qh[0].x, qh[0].y, qh[0].z, qh[0].w, qh[1].x, qh[1].y, qh[1].z, qh[1].w};
 #pragma unroll 1
                 for (uint32_t hi = 0; hi < 2; ++hi) {
-                    // 64-deep step 4b + 2n + hi of the slice -> ring stage, and the half of it this step fills
-                    const uint32_t it64 = 4u * b + 2u * n + hi, it = it64 / KD, half = it64 % KD, i = it % TC_STAGES;
+                    const uint32_t it = 4u * b + 2u * n + hi, i = it % TC_STAGES;
                     const uint32_t scw = hi ? sc8.y : sc8.x;       // scale groups 8n + 4hi + {0, 1, 2, 3}
-                    if (half == 0 && !mbar_wait_spin(BAR(BAR_EMPTY + i), ((it / TC_STAGES) & 1u) ^ 1u)) { atomicExch(dev_err, DEV_ERR_EMPTY_WAIT); go = false; break; }
-                    uint8_t *dst = smem + TC_OFF_A + i * Cfg::A_RING + half * TC_STAGE;
+                    if (!mbar_wait_spin(BAR(BAR_EMPTY + i), ((it / TC_STAGES) & 1u) ^ 1u)) { atomicExch(dev_err, DEV_ERR_EMPTY_WAIT); go = false; break; }
+                    uint8_t *dst = smem + TC_OFF_A + i * TC_STAGE;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {                  // chunk c: weights (c < 4 ? ql[l] : ql[32 + l]) with l = 8 (c & 3) .. + 7
                         const int sb = 2 * (c >> 2) + ((c & 3) >> 1);
@@ -391,11 +382,9 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                         }
                         *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
-                    if (half == KD - 1u) {
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(BAR(BAR_FULL + i));
-                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(BAR_FULL + i));
                 }
             }
         } else {
@@ -408,16 +397,14 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                 cur_b = __ldg(reinterpret_cast<const uint4 *>(p0 + 16));
                 hdr = __ldg(reinterpret_cast<const uint4 *>(wrow));
             }
-            // 64-deep steps it64 = set, set + 2, ...: with 128-deep ring stages set e fills half e of every stage
-            const uint32_t steps64 = (uint32_t)nb * 4u;
-            for (uint32_t it64 = (uint32_t)set; it64 < steps64; it64 += 2) {
-                const uint32_t b = it64 >> 2, s = it64 & 3u, it = it64 / KD, half = it64 % KD, i = it % TC_STAGES, x2 = b & 1u;
+            for (uint32_t it = (uint32_t)set; it < stages; it += 2) {
+                const uint32_t b = it >> 2, s = it & 3u, i = it % TC_STAGES, x2 = b & 1u;
                 uint4 nxt_a = cur_a, nxt_b = cur_b, hdr_next = hdr;
-                if (it64 + 2 < steps64) {                 // this thread's next quarter, possibly of the next superblock
-                    const uint8_t *pn = wrow + (size_t)((it64 + 2) >> 2) * Q4K_BYTES;
-                    nxt_a = __ldg(reinterpret_cast<const uint4 *>(pn + 16 + 32 * ((it64 + 2) & 3u)));
-                    nxt_b = __ldg(reinterpret_cast<const uint4 *>(pn + 32 + 32 * ((it64 + 2) & 3u)));
-                    if (((it64 + 2) >> 2) != b) hdr_next = __ldg(reinterpret_cast<const uint4 *>(pn));
+                if (it + 2 < stages) {                    // this thread's next quarter, possibly of the next superblock
+                    const uint8_t *pn = wrow + (size_t)((it + 2) >> 2) * Q4K_BYTES;
+                    nxt_a = __ldg(reinterpret_cast<const uint4 *>(pn + 16 + 32 * ((it + 2) & 3u)));
+                    nxt_b = __ldg(reinterpret_cast<const uint4 *>(pn + 32 + 32 * ((it + 2) & 3u)));
+                    if (((it + 2) >> 2) != b) hdr_next = __ldg(reinterpret_cast<const uint4 *>(pn));
                 }
                 uint32_t sc2, m2;
                 q4k_scales(hdr.y, hdr.z, hdr.w, (int)s, sc2, m2);
@@ -426,13 +413,13 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                 const __half2 b_lo = __floats2half2_rn(-1024.0f * sclo, -1024.0f * sclo), b_hi = __floats2half2_rn(-1024.0f * schi, -1024.0f * schi);
                 const float mlo = (float)(m2 & 255u), mhi = (float)(m2 >> 8);
                 const __half2 mm_lo = __floats2half2_rn(mlo, mlo), mm_hi = __floats2half2_rn(mhi, mhi);
-                if (tid == 128) TC_TRACE(1, 3 * (it64 >> 1) + 0);
+                if (tid == 128) TC_TRACE(1, 3 * (it >> 1) + 0);
                 TC_WAIT(BAR(BAR_EMPTY + i), ((it / TC_STAGES) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT);
                 if (s < 2) { TC_WAIT(BAR(BAR_A2_EMPTY + x2), ((b >> 1) & 1u) ^ 1u, DEV_ERR_EMPTY_WAIT); }   // this set's first write of the superblock's mins
-                if (tid == 128) TC_TRACE(1, 3 * (it64 >> 1) + 1);
+                if (tid == 128) TC_TRACE(1, 3 * (it >> 1) + 1);
                 const uint32_t ml = 0x0F0F0F0Fu;
                 const uint32_t w[8] = {cur_a.x, cur_a.y, cur_a.z, cur_a.w, cur_b.x, cur_b.y, cur_b.z, cur_b.w};
-                uint8_t *dst = smem + TC_OFF_A + i * Cfg::A_RING + half * TC_STAGE;
+                uint8_t *dst = smem + TC_OFF_A + i * TC_STAGE;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {     // low nibbles = sub-block 2s: k-chunks 0-3 of the stage; high nibbles = sub-block 2s+1: k-chunks 4-7
                     *reinterpret_cast<uint4 *>(dst + tc_tile_offset(row, c)) = q4_chunk_to_half(w[2 * c] & ml, w[2 * c + 1] & ml, s_lo, b_lo);
@@ -449,7 +436,7 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                 cur_a = nxt_a;
                 cur_b = nxt_b;
                 hdr = hdr_next;
-                if (tid == 128) TC_TRACE(1, 3 * (it64 >> 1) + 2);
+                if (tid == 128) TC_TRACE(1, 3 * (it >> 1) + 2);
             }
         }
     } else {
@@ -509,6 +496,11 @@ gemm_kq_tc_kernel(const uint8_t *__restrict__ xt, const uint8_t *__restrict__ B,
                         }
                     }
             }
+            // Every lane has read block scales from shared memory with plain loads, and lane 0's arrival below tells the loader that
+            // the buffer may be overwritten (by a bulk copy, which neither the compiler nor the warp barrier knows about).  The fence
+            // makes each lane's loads complete before the warp barrier, so that none of them can still be in flight when the copy
+            // lands.  Without it a pipeline that is not starved elsewhere corrupts a few 4-token groups of a 32-row quarter per call.
+            __threadfence_block();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {

@@ -55,6 +55,8 @@ static const struct { const char *symbol; int op; } g_symbols[] = {
 typedef struct {
     int op;
     char symbol[64];
+    char opname[40];            /* the IR's op label (q_proj, mlp_gate_up, ...) and layer, for the per-op timing report */
+    int layer;
     void *p[IR_MAX_ARGS];       /* pointer arguments in the order of the reference's signature; NULL for null / runtime scalars */
     long long i[IR_MAX_ARGS];   /* integer arguments */
     float f[IR_MAX_ARGS];
@@ -84,6 +86,8 @@ struct CKB200IrModel {
     cudaEvent_t ev_token;
     int token_in_flight;
     int launches;
+    cudaEvent_t *prof_ev;        /* nops + 1 events, created on the first profiled step */
+    int prof_token;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -178,6 +182,8 @@ static int bind_op(CKB200IrModel *m, const JsonValue *jop, IrOp *o)
     Binder b = { m, jop, symbol, (int)json_num(json_get(jop, "layer"), -1), 0 };
     memset(o, 0, sizeof *o);
     snprintf(o->symbol, sizeof o->symbol, "%s", symbol);
+    snprintf(o->opname, sizeof o->opname, "%s", json_str(json_get(jop, "op"), ""));
+    o->layer = b.layer;
     o->op = -1;
     for (size_t i = 0; i < sizeof g_symbols / sizeof g_symbols[0]; ++i) if (!strcmp(g_symbols[i].symbol, symbol)) o->op = g_symbols[i].op;
     if (o->op < 0) return ckb_fail(CKB_ERR_STATE, "ir: op %d calls '%s', which this executor has no kernel for", (int)json_num(json_get(jop, "idx"), -1), symbol);
@@ -304,6 +310,7 @@ void ckb200_ir_free(CKB200IrModel *m)
     if (!m) return;
     if (m->graph) cudaGraphExecDestroy(m->graph);
     if (m->ev_token) cudaEventDestroy(m->ev_token);
+    if (m->prof_ev) { for (int i = 0; i <= m->nops; ++i) cudaEventDestroy(m->prof_ev[i]); free(m->prof_ev); }
     if (m->arena) cudaFree(m->arena);
     if (m->token_pinned) cudaFreeHost(m->token_pinned);
     free(m->ops);
@@ -506,6 +513,55 @@ fail:
     return NULL;
 }
 
+/* ---------------------------------------------------------------- per-op timing
+ *
+ * The reference's generated code, built with --profile, brackets every kernel call with clock_gettime and writes
+ * mode,kernel,op,layer,time_us,token_id rows to CK_PROFILE_CSV / CK_PROFILE_JSON or stderr, one batch per token
+ * (version/v7/scripts/codegen_v7.py:1595-1685).  With CK_PROFILE set in the environment a step is issued op by op with a CUDA event
+ * between ops (no graph) and the same rows are written, the times being device times. */
+
+static int profile_on(void)
+{
+    const char *e = getenv("CK_PROFILE");
+    return e && *e && strcmp(e, "0");
+}
+
+static int profiled_step(CKB200IrModel *m, cudaStream_t st)
+{
+    if (!m->prof_ev) {
+        m->prof_ev = (cudaEvent_t *)calloc((size_t)m->nops + 1, sizeof *m->prof_ev);
+        if (!m->prof_ev) return CKB_ERR_STATE;
+        for (int i = 0; i <= m->nops; ++i)
+            if (ckb_check_cuda((int)cudaEventCreate(&m->prof_ev[i]), "ir profile event")) return CKB_ERR_CUDA;
+    }
+    cudaEventRecord(m->prof_ev[0], st);
+    for (int i = 0; i < m->nops; ++i) {
+        const int rc = run_op(m, &m->ops[i], st);
+        if (rc) return rc;
+        cudaEventRecord(m->prof_ev[i + 1], st);
+    }
+    int rc = ckb200_dev_advance_pos(m->pos_dev, st);
+    if (rc) return rc;
+    if (ckb_check_cuda((int)cudaStreamSynchronize(st), "ir profiled step")) return CKB_ERR_CUDA;
+    const char *csv = getenv("CK_PROFILE_CSV"), *json = getenv("CK_PROFILE_JSON");
+    FILE *fc = csv ? fopen(csv, m->prof_token == 0 ? "w" : "a") : (json ? NULL : stderr);
+    FILE *fj = json ? fopen(json, "w") : NULL;
+    if (fc && (m->prof_token == 0 || fc == stderr)) fprintf(fc, "mode,kernel,op,layer,time_us,token_id\n");
+    if (fj) fprintf(fj, "{\n  \"entries\": [\n");
+    for (int i = 0; i < m->nops; ++i) {
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, m->prof_ev[i], m->prof_ev[i + 1]);
+        const IrOp *o = &m->ops[i];
+        if (fc) fprintf(fc, "decode,%s,%s,%d,%.1f,%d\n", o->symbol, o->opname, o->layer, ms * 1000.0, m->prof_token);
+        if (fj) fprintf(fj, "    {\"mode\":\"decode\",\"kernel\":\"%s\",\"op\":\"%s\",\"layer\":%d,\"time_us\":%.1f,\"token_id\":%d}%s\n", o->symbol, o->opname,
+                        o->layer, ms * 1000.0, m->prof_token, i < m->nops - 1 ? "," : "");
+    }
+    if (fj) { fprintf(fj, "  ],\n  \"total_entries\": %d,\n  \"token_id\": %d\n}\n", m->nops, m->prof_token); fclose(fj); }
+    if (fc && fc != stderr) fclose(fc);
+    ++m->prof_token;
+    return 0;
+}
+
 /* ---------------------------------------------------------------- run */
 
 int ckb200_ir_decode(CKB200IrModel *m, int32_t token, float *logits_host)
@@ -519,7 +575,9 @@ int ckb200_ir_decode(CKB200IrModel *m, int32_t token, float *logits_host)
     cudaEventRecord(m->ev_token, st);
     m->token_in_flight = 1;
     int rc = 0;
-    if (ckb_tune_get("model_graph", 1)) {
+    if (profile_on()) {
+        if ((rc = profiled_step(m, st))) return rc;
+    } else if (ckb_tune_get("model_graph", 1)) {
         if (!m->graph) {
             /* the first token runs eagerly (kernels set their attributes and pools grow outside a capture), then the step is captured */
             cudaGraph_t g = NULL;

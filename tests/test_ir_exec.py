@@ -206,3 +206,34 @@ def test_v7_abi_replays_the_call_ir_beside_the_weights(ck, orc, pkg, tmp_path):
         assert v7.ck_model_get_active_tokens() == 0
     finally:
         v7.ck_model_free()
+
+
+@pytest.mark.gpu
+def test_ck_profile_writes_the_reference_rows(ck, tmp_path, monkeypatch):
+    """CK_PROFILE / CK_PROFILE_CSV / CK_PROFILE_JSON as in the reference's --profile builds (version/v7/scripts/codegen_v7.py:1595-1685)."""
+    bind(ck)
+    cfg, cpu, bump, mp = write_model(tmp_path, "qwen2_kquant")
+    h = ck.ckb200_ir_open(ir_cases.fixture_path("qwen2_kquant").encode(), str(bump).encode(), str(mp).encode())
+    assert h, ck.ckb200_last_error_message()
+    csv, js = tmp_path / "prof.csv", tmp_path / "prof.json"
+    try:
+        plain = np.zeros(cfg["vocab_size"], np.float32)
+        assert ck.ckb200_ir_decode(h, 3, cases.vptr(plain)) == 0
+        assert ck.ckb200_ir_reset(h) == 0
+        monkeypatch.setenv("CK_PROFILE", "1")
+        monkeypatch.setenv("CK_PROFILE_CSV", str(csv))
+        monkeypatch.setenv("CK_PROFILE_JSON", str(js))
+        timed = np.zeros(cfg["vocab_size"], np.float32)
+        assert ck.ckb200_ir_decode(h, 3, cases.vptr(timed)) == 0
+        assert ck.ckb200_ir_decode(h, 4, None) == 0
+        assert np.array_equal(plain, timed)                       # timing changes nothing about the step
+    finally:
+        ck.ckb200_ir_free(h)
+    rows = csv.read_text().strip().splitlines()
+    nops = len(json.load(open(ir_cases.fixture_path("qwen2_kquant")))["operations"])
+    assert rows[0] == "mode,kernel,op,layer,time_us,token_id" and len(rows) == 1 + 2 * nops
+    first = rows[1].split(",")
+    assert first[:4] == ["decode", "embedding_forward_q6_k", "dense_embedding_lookup", "-1"] and float(first[4]) >= 0 and first[5] == "0"
+    assert rows[-1].split(",")[5] == "1"
+    doc = json.loads(js.read_text())
+    assert doc["total_entries"] == nops and doc["token_id"] == 1 and doc["entries"][4]["op"] == "q_proj"

@@ -68,6 +68,9 @@ extern "C" int ckb200_dev_dequant_q4_k_row(const void *src, float *dst, size_t n
 extern "C" int ckb200_dev_dequant_q6_k_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q6K>(src, dst, n, stream); }
 extern "C" int ckb200_dev_dequant_q8_0_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q80>(src, dst, n, stream); }
 extern "C" int ckb200_dev_dequant_q5_0_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q50>(src, dst, n, stream); }
+extern "C" int ckb200_dev_dequant_q4_0_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q40>(src, dst, n, stream); }
+extern "C" int ckb200_dev_dequant_q4_1_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q41>(src, dst, n, stream); }
+extern "C" int ckb200_dev_dequant_q5_1_row(const void *src, float *dst, size_t n, void *stream) { return launch_dequant<DQ_Q51>(src, dst, n, stream); }
 
 template <int FMT>
 static int launch_gemv_f32(float *y, const void *W, const float *x, int M, int K, void *stream)
@@ -84,6 +87,12 @@ extern "C" int ckb200_dev_gemv_q4_k(float *y, const void *W, const float *x, int
 extern "C" int ckb200_dev_gemv_q6_k(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q6K>(y, W, x, M, K, stream); }
 extern "C" int ckb200_dev_gemv_q8_0(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q80>(y, W, x, M, K, stream); }
 extern "C" int ckb200_dev_gemv_q5_0(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q50>(y, W, x, M, K, stream); }
+// gemv_q4_0 / gemv_q4_1 / gemv_q5_1 (src/kernels/gemm_kernels_q4_0.c:49-145, gemm_kernels_q4_1.c:50-152, gemm_kernels_q5_1.c:52-200) and the fp32
+// fall-back of gemv_q5_k for rows that are not quantised (src/kernels/gemm_kernels_q5_k.c:211-245), each in its function's element order
+extern "C" int ckb200_dev_gemv_q4_0(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q40_G>(y, W, x, M, K, stream); }
+extern "C" int ckb200_dev_gemv_q4_1(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q41_G>(y, W, x, M, K, stream); }
+extern "C" int ckb200_dev_gemv_q5_1(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q51_G>(y, W, x, M, K, stream); }
+extern "C" int ckb200_dev_gemv_q5_k_f32(float *y, const void *W, const float *x, int M, int K, void *stream) { return launch_gemv_f32<DQ_Q5K_F>(y, W, x, M, K, stream); }
 
 extern "C" int ckb200_dev_add_bias_rows(float *c, const float *bias, int rows, int n, void *stream)
 {

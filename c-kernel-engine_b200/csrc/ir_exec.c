@@ -35,7 +35,7 @@
 
 enum {
     OP_EMBED_Q4K, OP_EMBED_Q6K, OP_EMBED_Q80, OP_MEMCPY, OP_RMSNORM, OP_QUANT_Q8K, OP_QUANT_Q80,
-    OP_GEMV_Q4K_Q8K, OP_GEMV_Q6K_Q8K, OP_GEMV_Q80_Q80, OP_GEMV_Q50_Q80, OP_GEMV_Q4K_F32, OP_GEMV_Q6K_F32, OP_GEMV_Q80_F32, OP_GEMV_Q50_F32,
+    OP_GEMV_Q4K_Q8K, OP_GEMV_Q6K_Q8K, OP_GEMV_Q80_Q80, OP_GEMV_Q50_Q80, OP_GEMV_Q5K_Q8K, OP_GEMV_Q4K_F32, OP_GEMV_Q6K_F32, OP_GEMV_Q80_F32, OP_GEMV_Q50_F32,
     OP_ROPE_HALF, OP_ROPE_PAIR, OP_KV_STORE, OP_ATTN, OP_ATTN_F16KV, OP_ATTN_SLIDING, OP_RESIDUAL_ADD, OP_SWIGLU, OP_ADD_INPLACE
 };
 
@@ -43,6 +43,7 @@ static const struct { const char *symbol; int op; } g_symbols[] = {
     { "embedding_forward_q4_k", OP_EMBED_Q4K }, { "embedding_forward_q6_k", OP_EMBED_Q6K }, { "embedding_forward_q8_0", OP_EMBED_Q80 },
     { "memcpy", OP_MEMCPY }, { "rmsnorm_forward", OP_RMSNORM }, { "quantize_row_q8_k", OP_QUANT_Q8K }, { "quantize_row_q8_0", OP_QUANT_Q80 },
     { "gemv_q4_k_q8_k", OP_GEMV_Q4K_Q8K }, { "gemv_q6_k_q8_k", OP_GEMV_Q6K_Q8K }, { "gemv_q8_0_q8_0", OP_GEMV_Q80_Q80 }, { "gemv_q5_0_q8_0", OP_GEMV_Q50_Q80 },
+    { "gemv_q5_k_q8_k", OP_GEMV_Q5K_Q8K },
     { "gemv_q4_k", OP_GEMV_Q4K_F32 }, { "gemv_q6_k", OP_GEMV_Q6K_F32 }, { "gemv_q8_0", OP_GEMV_Q80_F32 }, { "gemv_q5_0", OP_GEMV_Q50_F32 },
     { "rope_forward_qk_with_rotary_dim", OP_ROPE_HALF }, { "rope_forward_qk", OP_ROPE_HALF }, { "rope_forward_qk_pairwise_with_rotary_dim", OP_ROPE_PAIR },
     { "kv_cache_store", OP_KV_STORE }, { "attention_forward_decode_head_major_gqa_flash", OP_ATTN },
@@ -206,7 +207,7 @@ static int bind_op(CKB200IrModel *m, const JsonValue *jop, IrOp *o)
     case OP_QUANT_Q8K: case OP_QUANT_Q80:
         o->p[0] = arg_ptr(&b, "x", NULL); o->p[1] = arg_ptr(&b, "y", NULL); o->i[0] = (long long)arg_num(&b, "k");
         break;
-    case OP_GEMV_Q4K_Q8K: case OP_GEMV_Q6K_Q8K: case OP_GEMV_Q80_Q80: case OP_GEMV_Q50_Q80:
+    case OP_GEMV_Q4K_Q8K: case OP_GEMV_Q6K_Q8K: case OP_GEMV_Q80_Q80: case OP_GEMV_Q50_Q80: case OP_GEMV_Q5K_Q8K:
         o->p[0] = arg_ptr(&b, "y", NULL); o->p[1] = arg_ptr(&b, "W", &w); o->p[2] = arg_ptr(&b, "x_q8", NULL);
         o->i[0] = (long long)arg_num(&b, "M"); o->i[1] = (long long)arg_num(&b, "K");
         o->p[3] = w;                                         /* resolved to the planar copy after all ops are bound */
@@ -268,6 +269,7 @@ static int run_op(CKB200IrModel *m, const IrOp *o, void *st)
     case OP_GEMV_Q50_Q80:
         return o->p[3] ? ckb200_dev_gemv_q5_0_planar_q8_0((float *)o->p[0], o->p[3], o->p[2], (int)o->i[0], (int)o->i[1], st)
                        : ckb200_dev_gemv_q5_0_q8_0((float *)o->p[0], o->p[1], o->p[2], (int)o->i[0], (int)o->i[1], st);
+    case OP_GEMV_Q5K_Q8K: return ckb200_dev_gemv_q5_k_q8_k((float *)o->p[0], o->p[1], o->p[2], (int)o->i[0], (int)o->i[1], st);
     case OP_GEMV_Q4K_F32: return ckb200_dev_gemv_q4_k((float *)o->p[0], o->p[1], (const float *)o->p[2], (int)o->i[0], (int)o->i[1], st);
     case OP_GEMV_Q6K_F32: return ckb200_dev_gemv_q6_k((float *)o->p[0], o->p[1], (const float *)o->p[2], (int)o->i[0], (int)o->i[1], st);
     case OP_GEMV_Q80_F32: return ckb200_dev_gemv_q8_0((float *)o->p[0], o->p[1], (const float *)o->p[2], (int)o->i[0], (int)o->i[1], st);

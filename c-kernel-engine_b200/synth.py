@@ -18,8 +18,8 @@ import numpy as np
 
 QK_K = 256
 QK8_0 = 32
-BLOCK_BYTES = {"q4_k": 144, "q6_k": 210, "q8_0": 34, "q8_k": 292, "q5_0": 22}
-BLOCK_ELEMS = {"q4_k": 256, "q6_k": 256, "q8_0": 32, "q8_k": 256, "q5_0": 32}
+BLOCK_BYTES = {"q4_k": 144, "q6_k": 210, "q8_0": 34, "q8_k": 292, "q5_0": 22, "q5_k": 176, "q4_0": 18, "q4_1": 20, "q5_1": 24, "q8_1": 36}
+BLOCK_ELEMS = {"q4_k": 256, "q6_k": 256, "q8_0": 32, "q8_k": 256, "q5_0": 32, "q5_k": 256, "q4_0": 32, "q4_1": 32, "q5_1": 32, "q8_1": 32}
 
 
 def row_bytes(fmt: str, k: int) -> int:
@@ -76,7 +76,33 @@ def make_q5_0(rng: np.random.Generator, rows: int, k: int) -> np.ndarray:
     return out.reshape(-1)
 
 
-MAKERS = {"q4_k": make_q4_k, "q6_k": make_q6_k, "q8_0": make_q8_0, "q5_0": make_q5_0}
+
+
+def _half_bytes(rng, lo, hi, n):
+    return rng.uniform(lo, hi, n).astype(np.float16).view(np.uint8).reshape(n, 2)
+
+
+def make_q5_k(rng: np.random.Generator, rows: int, k: int) -> np.ndarray:
+    """fp16 d, fp16 dmin, 12 scale bytes, 32 bytes of fifth bits, 128 nibble bytes (src/kernels/gemm_kernels_q5_k.c:49-55)"""
+    nb = rows * (k // QK_K)
+    out = rng.integers(0, 256, (nb, 176), dtype=np.uint8)
+    out[:, 0:2] = _half_bytes(rng, 0.0, 0.02, nb)
+    out[:, 2:4] = _half_bytes(rng, 0.0, 0.01, nb)
+    return out.reshape(-1)
+
+
+def make_block32(rng: np.random.Generator, rows: int, k: int, fmt: str) -> np.ndarray:
+    """Q4_0 (d, 16 nibble bytes), Q4_1 (d, m, nibbles), Q5_1 (d, m, 4 bytes of fifth bits, nibbles): include/ckernel_quant.h:33-92"""
+    nb = rows * (k // 32)
+    out = rng.integers(0, 256, (nb, BLOCK_BYTES[fmt]), dtype=np.uint8)
+    out[:, 0:2] = _half_bytes(rng, 0.0, 0.02, nb)
+    if fmt != "q4_0":
+        out[:, 2:4] = _half_bytes(rng, -0.05, 0.05, nb)
+    return out.reshape(-1)
+
+
+MAKERS = {"q4_k": make_q4_k, "q6_k": make_q6_k, "q8_0": make_q8_0, "q5_0": make_q5_0, "q5_k": make_q5_k, "q4_0": lambda r, rows, k: make_block32(r, rows, k, "q4_0"),
+          "q4_1": lambda r, rows, k: make_block32(r, rows, k, "q4_1"), "q5_1": lambda r, rows, k: make_block32(r, rows, k, "q5_1")}
 
 
 def make_weights(fmt: str, rows: int, k: int, seed: int = 0) -> np.ndarray:

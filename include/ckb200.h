@@ -98,6 +98,23 @@ int ckb200_dev_gemv_q5_0_q8_0(float *y, const void *W, const void *x_q8, int M, 
 /* dequant_q5_0_row (src/kernels/dequant_kernels.c:198-206) and the fp32-activation gemv_q5_0 (src/kernels/gemm_kernels_q5_0.c:67-111) */
 int ckb200_dev_dequant_q5_0_row(const void *src, float *dst, size_t n_elements, void *stream);
 int ckb200_dev_gemv_q5_0(float *y, const void *W, const float *x, int M, int K, void *stream);
+/* Further weight formats (parity path, not tuned).  Q5_K x Q8_K (src/kernels/gemm_kernels_q5_k.c:128-208, :305-367) and Q5_1 x Q8_1 with its
+ * activation quantiser (src/kernels/gemm_kernels_q5_1_q8_1.c:27-122): integer block sums combined in the reference's fp32 order, bit-identical
+ * to the scalar loops; M tokens per call (M = 1: the GEMV).  Row dequantisers of Q4_0 / Q4_1 / Q5_1 (src/kernels/dequant_kernels.c:40-260) and
+ * fp32-activation GEMVs in the element order of the reference's own GEMVs (src/kernels/gemm_kernels_q4_0.c:49-78, gemm_kernels_q4_1.c:50-84,
+ * gemm_kernels_q5_1.c:52-100); gemv_q5_k_f32 is the fp32 fall-back of gemv_q5_k (src/kernels/gemm_kernels_q5_k.c:211-245). */
+int ckb200_dev_gemm_nt_q5_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
+int ckb200_dev_gemv_q5_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K, void *stream);
+int ckb200_dev_quantize_q8_1(const float *x, void *y, int rows, int k, void *stream);
+int ckb200_dev_gemm_nt_q5_1_q8_1(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream);
+int ckb200_dev_dequant_q4_0_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_dequant_q4_1_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_dequant_q5_1_row(const void *src, float *dst, size_t n_elements, void *stream);
+int ckb200_dev_gemv_q4_0(float *y, const void *W, const float *x, int M, int K, void *stream);
+int ckb200_dev_gemv_q4_1(float *y, const void *W, const float *x, int M, int K, void *stream);
+int ckb200_dev_gemv_q5_1(float *y, const void *W, const float *x, int M, int K, void *stream);
+int ckb200_dev_gemv_q5_k_f32(float *y, const void *W, const float *x, int M, int K, void *stream);
+
 /* Resident Q5_0 weights in a row-planar layout (all nibble bytes | all fifth-bit words | all d, rows padded to 16 B; the same
  * bits, aligned loads): size, conversion from the reference's rows, and the GEMV over it. */
 size_t ckb200_q5_0_planar_bytes(int rows, int cols);

@@ -217,6 +217,39 @@ void ck_test_rmsnorm(const float *input, const float *weight, float *output, int
 void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta);
 void ck_test_swiglu(const float *gate_up, float *output, int n_tokens, int intermediate_dim);
 
+/* ---- further weight formats: Q5_K (src/kernels/gemm_kernels_q5_k.c:305-520), Q5_1 x Q8_1 (src/kernels/gemm_kernels_q5_1_q8_1.c:75-175),
+ *      Q4_0 / Q4_1 / Q5_1 with fp32 activations (src/kernels/gemm_kernels_q4_0.c, gemm_kernels_q4_1.c, gemm_kernels_q5_1.c, dequant_kernels.c) ---- */
+void gemv_q5_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K);
+void gemv_q5_k_q8_k_ref(float *y, const void *W, const void *x_q8, int M, int K);
+void gemm_nt_q5_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q5_k_q8_k_ref(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemv_q5_k(float *y, const void *W, const float *x, int M, int K);
+void gemv_q5_k_ref(float *y, const void *W, const float *x, int M, int K);
+void gemm_nt_q5_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q5_k_ref(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemv_q5_1_q8_1(float *y, const void *W, const float *x, int M, int K);
+void gemv_q5_1_q8_1_ref(float *y, const void *W, const void *x_q8, int M, int K);
+void gemm_nt_q5_1_q8_1(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemm_nt_q5_1_q8_1_ref(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K);
+void gemv_q4_0(float *y, const void *W, const float *x, int M, int K);
+void gemv_q4_0_ref(float *y, const void *W, const float *x, int M, int K);
+void gemm_q4_0(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_nt_q4_0(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+float dot_q4_0(const void *w, const float *x, int K);
+void dequant_q4_0_row(const void *src, float *dst, size_t n_elements);
+void gemv_q4_1(float *y, const void *W, const float *x, int M, int K);
+void gemv_q4_1_ref(float *y, const void *W, const float *x, int M, int K);
+void gemm_q4_1(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_nt_q4_1(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+float dot_q4_1(const void *w, const float *x, int K);
+void dequant_q4_1_row(const void *src, float *dst, size_t n_elements);
+void gemv_q5_1(float *y, const void *W, const float *x, int M, int K);
+void gemv_q5_1_ref(float *y, const void *W, const float *x, int M, int K);
+void gemm_q5_1(float *Y, const void *W, const float *X, int M, int N, int K);
+void gemm_nt_q5_1(const float *A, const void *B, const float *bias, float *C, int M, int N, int K);
+float dot_q5_1(const void *w, const float *x, int K);
+void dequant_q5_1_row(const void *src, float *dst, size_t n_elements);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1054,3 +1054,230 @@ void oracle_logits_copy_to_position(const float *src, float *dst, int position, 
     if (!src || !dst || position < 0 || vocab_size <= 0) return;
     memmove(dst + (size_t)position * (size_t)vocab_size, src, (size_t)vocab_size * sizeof(float));
 }
+
+/* =====================================================================================================================
+ * Further weight formats of the reference: Q5_K, and the 32-element formats Q4_0, Q4_1, Q5_1 (with Q8_1 activations).
+ * Block layouts: Q5_K 176 B = fp16 d, fp16 dmin, scales[12], qh[32], qs[128] (src/kernels/gemm_kernels_q5_k.c:49-55);
+ * Q4_0 18 B = fp16 d, qs[16]; Q4_1 20 B = fp16 d, fp16 m, qs[16]; Q5_1 24 B = fp16 d, fp16 m, qh[4], qs[16]
+ * (include/ckernel_quant.h:33-92); Q8_1 36 B = fp16 d, fp16 s = d * sum(q), qs[32] (src/kernels/gemm_kernels_q5_1_q8_1.c:21-25).
+ * ===================================================================================================================== */
+
+static float orc_h(const uint8_t *p) { return oracle_fp16_to_fp32((uint16_t)(p[0] | (p[1] << 8))); }
+
+/* the 6-bit scale / min pairs of Q4_K and Q5_K (src/kernels/gemm_kernels_q5_k.c:59-81) */
+static void orc_k_scales(const uint8_t *s, uint8_t sc[8], uint8_t mn[8])
+{
+    for (int j = 0; j < 4; ++j) {
+        sc[j] = s[j] & 63;
+        mn[j] = s[j + 4] & 63;
+        sc[j + 4] = (uint8_t)((s[j + 8] & 15) | ((s[j] >> 6) << 4));
+        mn[j + 4] = (uint8_t)((s[j + 8] >> 4) | ((s[j + 4] >> 6) << 4));
+    }
+}
+
+/* one 256-element block, Q5_K x Q8_K (src/kernels/gemm_kernels_q5_k.c:128-208): groups of 64 elements share 32 nibble bytes (low
+ * nibbles first), bit 2j / 2j + 1 of qh[l] is the fifth bit; integer sums, then d * dot - dmin * sum(mins * bsums) */
+static float orc_dot_q5_k_q8_k_block(const uint8_t *w, const uint8_t *x)
+{
+    uint8_t sc[8], mn[8];
+    orc_k_scales(w + 4, sc, mn);
+    const uint8_t *qh = w + 16, *qs = w + 48;
+    const int8_t *q8 = (const int8_t *)(x + 4);
+    const int16_t *bsums = (const int16_t *)(x + 260);
+    float xd;
+    memcpy(&xd, x, 4);
+    int sumi = 0, doti = 0;
+    for (int j = 0; j < 16; ++j) sumi += (int)bsums[j] * (int)mn[j / 2];
+    for (int sb = 0; sb < 8; ++sb) {
+        int s = 0;
+        for (int l = 0; l < 32; ++l) {
+            const uint8_t byte = qs[32 * (sb >> 1) + l];
+            const int a = ((sb & 1) ? (byte >> 4) : (byte & 15)) + (((qh[l] >> sb) & 1) ? 16 : 0);
+            s += a * (int)q8[32 * sb + l];
+        }
+        doti += (int)sc[sb] * s;
+    }
+    const float d = orc_h(w) * xd, dmin = orc_h(w + 2) * xd;
+    return d * (float)doti - dmin * (float)sumi;
+}
+
+void oracle_gemv_q5_k_q8_k(float *y, const void *W, const void *x_q8, int M, int K)
+{
+    if (!y || !W || !x_q8 || M <= 0 || K <= 0 || K % 256) return;
+    const int nb = K / 256;
+    for (int m = 0; m < M; ++m) {
+        float sum = 0.0f;
+        for (int b = 0; b < nb; ++b) sum += orc_dot_q5_k_q8_k_block((const uint8_t *)W + ((size_t)m * nb + b) * 176, (const uint8_t *)x_q8 + (size_t)b * 292);
+        y[m] = sum;
+    }
+}
+
+void oracle_gemm_nt_q5_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A_q8 || !B || !C || M <= 0 || N <= 0 || K <= 0 || K % 256) return;
+    const int nb = K / 256;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float sum = 0.0f;
+            for (int b = 0; b < nb; ++b)
+                sum += orc_dot_q5_k_q8_k_block((const uint8_t *)B + ((size_t)n * nb + b) * 176, (const uint8_t *)A_q8 + ((size_t)m * nb + b) * 292);
+            C[(size_t)m * N + n] = sum + (bias ? bias[n] : 0.0f);
+        }
+}
+
+/* the fp32 fall-back of gemv_q5_k / gemm_nt_q5_k (src/kernels/gemm_kernels_q5_k.c:211-283) reads the block differently: sub-block sb
+ * takes nibble i % 2 of qs[16 sb + i / 2] and bit i % 8 of qh[4 sb + i / 8] */
+static float orc_q5_k_elem_fp32_layout(const uint8_t *w, int e)
+{
+    uint8_t sc[8], mn[8];
+    orc_k_scales(w + 4, sc, mn);
+    const int sb = e >> 5, i = e & 31;
+    const uint8_t q = (uint8_t)(((w[48 + sb * 16 + i / 2] >> (4 * (i % 2))) & 15) | (((w[16 + sb * 4 + i / 8] >> (i % 8)) & 1) << 4));
+    return orc_h(w) * (float)sc[sb] * (float)q - orc_h(w + 2) * (float)mn[sb];
+}
+
+static void orc_gemm_nt_q5_k_fp32(const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    const int nb = K / 256;            /* whole blocks only; rows of A are K floats apart */
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float sum = 0.0f;
+            for (int b = 0; b < nb; ++b)
+                for (int e = 0; e < 256; ++e) sum += orc_q5_k_elem_fp32_layout((const uint8_t *)B + ((size_t)n * nb + b) * 176, e) * A[(size_t)m * K + b * 256 + e];
+            C[(size_t)m * N + n] = sum + (bias ? bias[n] : 0.0f);
+        }
+}
+
+/* gemm_nt_q5_k / gemv_q5_k (src/kernels/gemm_kernels_q5_k.c:369-434): fp32 activations are quantised to Q8_K per row (rows of up to 128
+ * blocks), longer rows take the fp32 fall-back */
+void oracle_gemm_nt_q5_k(const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return;
+    if (K % 256 || K / 256 > 128) { orc_gemm_nt_q5_k_fp32(A, B, bias, C, M, N, K); return; }
+    uint8_t *q = (uint8_t *)malloc((size_t)(K / 256) * 292);
+    for (int m = 0; m < M; ++m) {
+        oracle_quantize_row_q8_k(A + (size_t)m * K, q, K);
+        oracle_gemm_nt_q5_k_q8_k(q, B, bias, C + (size_t)m * N, 1, N, K);
+    }
+    free(q);
+}
+
+void oracle_gemv_q5_k(float *y, const void *W, const float *x, int M, int K) { oracle_gemm_nt_q5_k(x, W, NULL, y, 1, M, K); }
+
+/* ---- Q8_1 activations and Q5_1 x Q8_1 (src/kernels/gemm_kernels_q5_1_q8_1.c:27-122) ---- */
+void oracle_quantize_row_q8_1(const float *x, void *vy, int k)
+{
+    uint8_t *y = (uint8_t *)vy;
+    for (int b = 0; b < k / 32; ++b) {
+        const float *xb = x + (size_t)b * 32;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) { const float av = xb[j] >= 0.0f ? xb[j] : -xb[j]; if (av > amax) amax = av; }
+        const float d = amax / 127.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
+        const uint16_t dh = oracle_fp32_to_fp16(d);
+        int sum = 0;
+        for (int j = 0; j < 32; ++j) { const int q = (int)roundf(xb[j] * id); ((int8_t *)(y + 4))[j] = (int8_t)q; sum += q; }
+        const uint16_t sh = oracle_fp32_to_fp16((float)sum * d);
+        y[0] = (uint8_t)dh; y[1] = (uint8_t)(dh >> 8); y[2] = (uint8_t)sh; y[3] = (uint8_t)(sh >> 8);
+        y += 36;
+    }
+}
+
+static float orc_dot_q5_1_q8_1_block(const uint8_t *w, const uint8_t *x)
+{
+    uint32_t qh;
+    memcpy(&qh, w + 4, 4);
+    const uint8_t *qs = w + 8;
+    const int8_t *q8 = (const int8_t *)(x + 4);
+    int s0 = 0, s1 = 0;
+    for (int j = 0; j < 16; ++j) {
+        const int q0 = (qs[j] & 15) | (int)(((qh >> j) << 4) & 0x10), q1 = (qs[j] >> 4) | (int)((qh >> (j + 12)) & 0x10);
+        s0 += q0 * (int)q8[j];
+        s1 += q1 * (int)q8[j + 16];
+    }
+    return (orc_h(w) * orc_h(x)) * (float)(s0 + s1) + orc_h(w + 2) * orc_h(x + 2);
+}
+
+void oracle_gemm_nt_q5_1_q8_1_ref(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A_q8 || !B || !C || M <= 0 || N <= 0 || K <= 0 || K % 32) return;
+    const int nb = K / 32;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float sum = 0.0f;
+            for (int b = 0; b < nb; ++b) sum += orc_dot_q5_1_q8_1_block((const uint8_t *)B + ((size_t)n * nb + b) * 24, (const uint8_t *)A_q8 + ((size_t)m * nb + b) * 36);
+            C[(size_t)m * N + n] = sum + (bias ? bias[n] : 0.0f);
+        }
+}
+
+void oracle_gemv_q5_1_q8_1_ref(float *y, const void *W, const void *x_q8, int M, int K) { oracle_gemm_nt_q5_1_q8_1_ref(x_q8, W, NULL, y, 1, M, K); }
+
+/* fp32 in, quantised inside, rows of at most 256 blocks (src/kernels/gemm_kernels_q5_1_q8_1.c:125-175) */
+void oracle_gemm_nt_q5_1_q8_1(const float *A, const void *B, const float *bias, float *C, int M, int N, int K)
+{
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0 || K % 32 || K / 32 > 256) return;
+    uint8_t *q = (uint8_t *)malloc((size_t)(K / 32) * 36);
+    for (int m = 0; m < M; ++m) {
+        oracle_quantize_row_q8_1(A + (size_t)m * K, q, K);
+        oracle_gemm_nt_q5_1_q8_1_ref(q, B, bias, C + (size_t)m * N, 1, N, K);
+    }
+    free(q);
+}
+
+void oracle_gemv_q5_1_q8_1(float *y, const void *W, const float *x, int M, int K) { oracle_gemm_nt_q5_1_q8_1(x, W, NULL, y, 1, M, K); }
+
+/* ---- Q4_0 / Q4_1 / Q5_1 with fp32 activations.  Row dequantisers put element j in the low nibble of qs[j] and element j + 16 in the high
+ * nibble (src/kernels/dequant_kernels.c:40-56, :119-139, :220-252); the GEMVs pair the nibbles of qs[i] with x[2i] and x[2i + 1]
+ * (src/kernels/gemm_kernels_q4_0.c:49-78, gemm_kernels_q4_1.c:50-84, gemm_kernels_q5_1.c:52-100).  Both are restated as they are. ---- */
+enum { ORC_Q40 = 0, ORC_Q41 = 1, ORC_Q51 = 2 };
+static const int orc_legacy_bytes[3] = { 18, 20, 24 };
+
+static float orc_legacy_elem(int fmt, const uint8_t *p, int e, int gemv_order)
+{
+    const float d = orc_h(p);
+    const int byte_i = gemv_order ? e >> 1 : e & 15, hi = gemv_order ? e & 1 : e >> 4;
+    if (fmt == ORC_Q40) {
+        const uint8_t b = p[2 + byte_i];
+        return d * (float)(int8_t)((hi ? (b >> 4) : (b & 15)) - 8);
+    }
+    const float m = orc_h(p + 2);
+    if (fmt == ORC_Q41) {
+        const uint8_t b = p[4 + byte_i];
+        return d * (float)(hi ? (b >> 4) : (b & 15)) + m;
+    }
+    uint32_t qh;
+    memcpy(&qh, p + 4, 4);
+    const uint8_t b = p[8 + byte_i];
+    const int fifth = gemv_order ? (int)((qh >> e) & 1) : (int)((qh >> (hi ? byte_i + 16 : byte_i)) & 1);
+    return d * (float)((hi ? (b >> 4) : (b & 15)) | (fifth << 4)) + m;
+}
+
+static void orc_legacy_dequant(int fmt, const void *src, float *dst, size_t n)
+{
+    for (size_t i = 0; i < n; ++i) dst[i] = orc_legacy_elem(fmt, (const uint8_t *)src + (i / 32) * orc_legacy_bytes[fmt], (int)(i % 32), 0);
+}
+void oracle_dequant_q4_0_row(const void *src, float *dst, size_t n) { orc_legacy_dequant(ORC_Q40, src, dst, n); }
+void oracle_dequant_q4_1_row(const void *src, float *dst, size_t n) { orc_legacy_dequant(ORC_Q41, src, dst, n); }
+void oracle_dequant_q5_1_row(const void *src, float *dst, size_t n) { orc_legacy_dequant(ORC_Q51, src, dst, n); }
+
+static void orc_legacy_gemv(int fmt, float *y, const void *W, const float *x, int M, int K)
+{
+    const int nb = K / 32;
+    for (int r = 0; r < M; ++r) {
+        float sum = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const uint8_t *p = (const uint8_t *)W + ((size_t)r * nb + b) * orc_legacy_bytes[fmt];
+            for (int e = 0; e < 32; ++e) {
+                if (fmt == ORC_Q40) {      /* d * q * x, left to right (gemm_kernels_q4_0.c:71-72) */
+                    const uint8_t bt = p[2 + (e >> 1)];
+                    sum += orc_h(p) * (float)(int8_t)(((e & 1) ? (bt >> 4) : (bt & 15)) - 8) * x[b * 32 + e];
+                } else {
+                    sum += orc_legacy_elem(fmt, p, e, 1) * x[b * 32 + e];
+                }
+            }
+        }
+        y[r] = sum;
+    }
+}
+void oracle_gemv_q4_0_ref(float *y, const void *W, const float *x, int M, int K) { orc_legacy_gemv(ORC_Q40, y, W, x, M, K); }
+void oracle_gemv_q4_1_ref(float *y, const void *W, const float *x, int M, int K) { orc_legacy_gemv(ORC_Q41, y, W, x, M, K); }
+void oracle_gemv_q5_1_ref(float *y, const void *W, const float *x, int M, int K) { orc_legacy_gemv(ORC_Q51, y, W, x, M, K); }

@@ -48,3 +48,56 @@ def setup(lib, rank: int, world: int, device=None, p2p_floats: int = 0) -> None:
     if lib.ckb200_tp_p2p_connect(raw) != 0:
         raise RuntimeError(_err(lib))
     dist.barrier()          # every rank has mapped every buffer before anyone's first push
+
+
+class PeerLeft(RuntimeError):
+    """A tensor-parallel peer announced that it stopped, or stopped reporting, before this step."""
+
+
+class Membership:
+    """Host-side liveness of the tensor-parallel group, checked BEFORE a step is launched.
+
+    The exchange kernels wait for their peers' stores; a rank that is gone would leave the others in a bounded wait (seconds) and with an
+    error to clean up.  So every rank records the number of the step it is about to launch in a key-value store shared by the group
+    (a torch.distributed store: TCPStore, FileStore, or the store behind the default process group), and launches step s only after every
+    peer has announced step s too (one store round trip per step; a peer that merely finished step s - 1 may still be about to leave).  A
+    rank leaves only between steps: it calls leave(), which the others see instead of its next announcement; a rank that dies silently is
+    noticed when the time limit runs out.  No kernel, collective or device is involved.
+    """
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "ckb200/tp"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+        self.store.set(self._key("step", rank), "0")
+
+    def _key(self, what: str, rank: int) -> str:
+        return f"{self.prefix}/{what}/{rank}"
+
+    def leave(self, reason: str = "left") -> None:
+        self.store.set(self._key("left", self.rank), reason)
+
+    def _peer_state(self, peer: int):
+        """(step reached, reason it left or None); keys that do not exist yet read as step -1"""
+        left = None
+        if self.store.check([self._key("left", peer)]):
+            left = self.store.get(self._key("left", peer)).decode()
+        step = int(self.store.get(self._key("step", peer)).decode()) if self.store.check([self._key("step", peer)]) else -1
+        return step, left
+
+    def before_step(self, step: int) -> None:
+        """Announce `step`, then wait (up to the time limit) until every peer has announced it as well.  Raises PeerLeft."""
+        import time
+
+        self.store.set(self._key("step", self.rank), str(step))
+        deadline = time.monotonic() + self.timeout_s
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            while True:
+                reached, left = self._peer_state(peer)
+                if reached >= step:                    # the peer is about to launch (or has launched) the same step
+                    break
+                if left is not None:
+                    raise PeerLeft(f"rank {peer} {left} after step {reached}; step {step} not launched on rank {self.rank}")
+                if time.monotonic() > deadline:
+                    raise PeerLeft(f"rank {peer} has not reported for {self.timeout_s:.1f} s (last step {reached}); step {step} not launched on rank {self.rank}")
+                time.sleep(0.002)

@@ -761,6 +761,14 @@ def run_prefill_only(args):
     print(json.dumps(prefill_bench(lib, args.prefill_only, args.launches, None, torch, measured_tensor_peak())))
 
 
+def run_prefill_stack_only(args):
+    """Two whole-stack prefill passes (Llama-3-8B shape): the command behind the prefill launch list."""
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    lib.ckb200_launch_count.restype = C.c_longlong
+    print(json.dumps(prefill_step_bench(lib, args.prefill_stack_only, iters=1)))
+
+
 def run_single(args):
     """A few plain (un-captured) launches of one GEMV on rotating weight copies: the small case for ncu captures.
     FMT: q4_k, q6_k (ring kernel on the reference's rows), q6_k_planar, q8_0, q8_0_planar, q5_0, q5_0_planar."""
@@ -846,6 +854,33 @@ def attention_bench(lib, torch, peak, iters=40):
             out.append({"kv_cache": kind, "batch": batch, "us": ms * 1e3, "kv_bytes": nbytes, "gbs": nbytes / ms / 1e6, "frac_of_measured_peak": nbytes / ms / 1e6 / peak,
                         "splits": splits})
             del kc, vc
+    # the llama template's attention (fp32 cache read through fp16 rounding, accumulator rounded after every key): an ordered walk, latency-bound
+    q = torch.randn(1, H, d, device=dev)
+    o = torch.empty_like(q)
+    kc = torch.randn(12, Hkv, T, d, device=dev)
+    vc = torch.randn(12, Hkv, T, d, device=dev)
+
+    def run_f16kv(i):
+        l = i % 12
+        rc = lib.ckb200_dev_attention_decode_f16kv(C.c_void_p(q.data_ptr()), C.c_void_p(kc[l].data_ptr()), C.c_void_p(vc[l].data_ptr()), C.c_void_p(o.data_ptr()),
+                                                   H, Hkv, T, T, d, d, None, None)
+        if rc != 0:
+            raise RuntimeError(lib.ckb200_last_error_message().decode())
+
+    torch.cuda.synchronize()
+    for i in range(3):
+        run_f16kv(i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for i in range(iters):
+        run_f16kv(i)
+    e1.record(st)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    nbytes = 2 * Hkv * T * d * 4 + 2 * H * d * 4
+    out.append({"kv_cache": "fp32 read as fp16, fp16-rounded accumulator (attention_forward_decode_head_major_gqa_flash_f16kv)", "batch": 1, "us": ms * 1e3,
+                "kv_bytes": nbytes, "gbs": nbytes / ms / 1e6, "frac_of_measured_peak": nbytes / ms / 1e6 / peak, "splits": 1,
+                "note": "keys are walked in order (the rounding sequence is part of the result): about 15 cycles per key"})
     if lib.ckb200_synchronize() != 0:
         raise RuntimeError(lib.ckb200_last_error_message().decode())
     return out
@@ -871,6 +906,10 @@ def run_attention_only(args):
         l = i % nl
         assert lib.ckb200_dev_attention_decode_ws(C.c_void_p(q.data_ptr()), C.c_void_p(kc[l].data_ptr()), C.c_void_p(vc[l].data_ptr()), C.c_void_p(out.data_ptr()),
                                                   1, C.c_longlong(Hkv * cap * d), H, Hkv, T, cap, d, d, splits, C.c_void_p(scratch.data_ptr()), None, None) == 0
+    for i in range(args.launches):          # and the fp16-rounded form on the same caches
+        l = i % nl
+        assert lib.ckb200_dev_attention_decode_f16kv(C.c_void_p(q.data_ptr()), C.c_void_p(kc[l].data_ptr()), C.c_void_p(vc[l].data_ptr()), C.c_void_p(out.data_ptr()),
+                                                     H, Hkv, T, cap, d, d, None, None) == 0
     assert lib.ckb200_synchronize() == 0
     print(json.dumps({"attention_only": T, "launches": args.launches, "splits": splits, "kv_bytes_per_launch": 2 * Hkv * T * d * 4}))
 
@@ -910,6 +949,7 @@ def main():
     ap.add_argument("--single", default=None, metavar="FMT:MxK", help="profiling aid: plain launches of one GEMV, e.g. q4_k:14336x4096, q6_k_planar:14336x4096")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
+    ap.add_argument("--prefill-stack-only", type=int, default=None, metavar="T", help="profiling aid: whole-stack prefill of a T-token prompt, twice")
     ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
     ap.add_argument("--batch", type=int, default=1, help="sequences per step of --decode-only")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
@@ -928,6 +968,8 @@ def main():
         return run_attention_only(args)
     if args.prefill_only:
         return run_prefill_only(args)
+    if args.prefill_stack_only:
+        return run_prefill_stack_only(args)
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -240,7 +240,7 @@ void ck_test_swiglu(const float *gate_up, float *output, int n_tokens, int inter
 
 /* q [T][H*D], k [T][Hkv*D] token-major, rotate-half with a table built for theta: the wrapper transposes to the kernels'
  * head-major layout and back (src/ck_parity_api.c:552-628) */
-void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta)
+static void test_rope_common(int pairwise, float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta)
 {
     if (!q || !k || n_tokens <= 0 || n_heads <= 0 || n_heads_kv <= 0 || head_dim <= 1 || pos_offset < 0) return;
     const int half = head_dim / 2, max_seq = pos_offset + n_tokens;
@@ -256,7 +256,8 @@ void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv,
             for (int h = 0; h < n_heads_kv; ++h)
                 memcpy(kr + ((size_t)h * n_tokens + t) * head_dim, k + ((size_t)t * n_heads_kv + h) * head_dim, (size_t)head_dim * sizeof(float));
         }
-        rope_forward_qk(qr, kr, cs, sn, n_heads, n_heads_kv, n_tokens, head_dim, head_dim, pos_offset);
+        if (pairwise) rope_forward_qk_pairwise_with_rotary_dim(qr, kr, cs, sn, n_heads, n_heads_kv, n_tokens, head_dim, head_dim, pos_offset, head_dim);
+        else rope_forward_qk(qr, kr, cs, sn, n_heads, n_heads_kv, n_tokens, head_dim, head_dim, pos_offset);
         for (int t = 0; t < n_tokens; ++t) {
             for (int h = 0; h < n_heads; ++h)
                 memcpy(q + ((size_t)t * n_heads + h) * head_dim, qr + ((size_t)h * n_tokens + t) * head_dim, (size_t)head_dim * sizeof(float));
@@ -267,4 +268,22 @@ void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv,
     free(cs);
     free(qr);
     free(kr);
+}
+
+void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta)
+{
+    test_rope_common(0, q, k, n_tokens, n_heads, n_heads_kv, head_dim, pos_offset, theta);
+}
+
+/* the interleaved (pair-rotated) form with the same arguments (src/ck_parity_api.c:630-687) */
+void ck_test_rope_interleaved(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta)
+{
+    test_rope_common(1, q, k, n_tokens, n_heads, n_heads_kv, head_dim, pos_offset, theta);
+}
+
+/* src/ck_parity_api.c:199-202 and :861-881 */
+void ck_test_dequant_q4_0(const void *src, float *dst, int n) { dequant_q4_0_row(src, dst, (size_t)n); }
+void ck_test_attention_causal(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int tokens, int seq_len, int head_dim)
+{
+    attention_forward_causal_head_major_gqa_flash_strided(q, k, v, out, num_heads, num_kv_heads, tokens, head_dim, head_dim, seq_len);
 }

@@ -215,6 +215,10 @@ void ck_test_gemm_q8_0(const void *weight_q8_0, const float *input_f32, float *o
 void ck_test_gemm_q5_0(const void *weight_q5_0, const float *input_f32, float *output, int rows, int cols, int n_tokens);
 void ck_test_rmsnorm(const float *input, const float *weight, float *output, int n_tokens, int dim, float eps);
 void ck_test_rope(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta);
+void ck_test_rope_interleaved(float *q, float *k, int n_tokens, int n_heads, int n_heads_kv, int head_dim, int pos_offset, float theta);   /* :630-687 */
+void ck_test_dequant_q4_0(const void *src, float *dst, int n);                                                                                /* :199-202 */
+void ck_test_attention_causal(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int tokens,
+                              int seq_len, int head_dim);                                                                                    /* :861-881 */
 void ck_test_swiglu(const float *gate_up, float *output, int n_tokens, int intermediate_dim);
 
 /* ---- further weight formats: Q5_K (src/kernels/gemm_kernels_q5_k.c:305-520), Q5_1 x Q8_1 (src/kernels/gemm_kernels_q5_1_q8_1.c:75-175),

@@ -307,6 +307,17 @@ def parity_api_cases(lib, quant_lib, quant_prefix):
     so = np.zeros((2, 96), np.float32)
     lib.ck_test_swiglu(cases.fptr(gu), cases.fptr(so), 2, 96)
     out["swiglu"] = so
+    qi, ki = rng.standard_normal((3, 4 * 64)).astype(np.float32), rng.standard_normal((3, 2 * 64)).astype(np.float32)
+    lib.ck_test_rope_interleaved(cases.fptr(qi), cases.fptr(ki), 3, 4, 2, 64, 5, C.c_float(1.0e4))
+    out["rope_interleaved_q"], out["rope_interleaved_k"] = qi, ki
+    w40 = synth.make_weights("q4_0", 4, 128, 97)
+    d40 = np.zeros(512, np.float32)
+    lib.ck_test_dequant_q4_0(cases.vptr(w40), cases.fptr(d40), 512)
+    out["dequant_q4_0"] = d40
+    aq, ak, av = cases.prefill_attention_inputs(98, 4, 2, 64, 64, 9, 9)
+    ao = np.zeros_like(aq)
+    lib.ck_test_attention_causal(cases.fptr(aq), cases.fptr(ak), cases.fptr(av), cases.fptr(ao), 4, 2, 9, 9, 64)
+    out["attention_causal"] = ao
     return out
 
 

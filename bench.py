@@ -224,15 +224,20 @@ LLAMA3_70B = dict(embed_dim=8192, num_heads=64, num_kv_heads=8, head_dim=128, in
                   max_seq_len=4352, rms_eps=1e-5, rope_theta=5.0e5, fmt_q=0, fmt_k=0, fmt_v=1, fmt_o=0, fmt_gate_up=0, fmt_down=1, fmt_lm_head=1)
 
 
-def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None, keep_logits=None):
+def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1, dist=None, keep_logits=None, kv_f16=False):
     """Decode tokens/s of a model SHAPE with random weights (device-generated) and a synthetic N(0,1) KV cache of `ctx` tokens.
-    With keep_logits (a list) the logits of one extra step at position ctx are appended to it as a device tensor."""
+    With keep_logits (a list) the logits of one extra step at position ctx are appended to it as a device tensor.
+    kv_f16: the executor keeps IEEE fp16 caches (the reference's kv_cache_store_f16 / _f16cache attention pair)."""
     import torch
 
     so = pkg.model_api
     so.bind_model_api(lib)
     st = so.make_cfg(cfg, batch=batch, tp_rank=tp_rank, tp_size=tp_size)
-    handle = lib.ckb200_model_create(C.byref(st))
+    lib.ckb200_tune_set(b"model_kv_f16", int(kv_f16))
+    try:
+        handle = lib.ckb200_model_create(C.byref(st))
+    finally:
+        lib.ckb200_tune_set(b"model_kv_f16", 0)
     if not handle:
         msg = lib.ckb200_last_error_message().decode()
         lib.ckb200_clear_error()
@@ -265,7 +270,7 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         wbytes = lib.ckb200_model_weight_bytes(handle)                    # this rank's shard
-        kv_bytes = 2 * cfg["num_layers"] * max(1, cfg["num_kv_heads"] // tp_size) * (ctx + steps // 2) * cfg["head_dim"] * 4 * batch
+        kv_bytes = 2 * cfg["num_layers"] * max(1, cfg["num_kv_heads"] // tp_size) * (ctx + steps // 2) * cfg["head_dim"] * (2 if kv_f16 else 4) * batch
         gbs = (wbytes + kv_bytes) / ms / 1e6
         # end to end: token id from the host, logits back to the host, every step
         logits = np.zeros((batch, cfg["vocab_size"]), np.float32)
@@ -279,7 +284,7 @@ def decode_bench(lib, name, cfg, ctx, steps, peak, batch=1, tp_rank=0, tp_size=1
             assert lib.ckb200_model_set_pos(handle, ctx) == 0
             assert lib.ckb200_model_decode(handle, vptr(ids), vptr(logits)) == 0
             keep_logits.append(torch.from_numpy(logits[0].copy()).to(torch.device("cuda", torch.cuda.current_device())))
-        return {"model_shape": name, "batch": batch, "context": ctx, "tp": tp_size, "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
+        return {"model_shape": name, "batch": batch, "context": ctx, "tp": tp_size, "kv_cache": "f16" if kv_f16 else "f32", "tok_s": batch * 1e3 / ms, "ms_per_token": ms, "launches_per_token": int(launches),
                 "weight_bytes": int(wbytes), "kv_bytes": int(kv_bytes), "hbm_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peak,
                 "e2e_tok_s": batch * 1e3 / e2e_ms, "e2e_ms_per_token": e2e_ms}
     finally:
@@ -585,7 +590,9 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             try:
                 line["decode"] = [decode_bench(lib, "Qwen2-0.5B shape, Q4_K_M mix", QWEN2_05B, 1024, 200, peak),
                                   decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU", LLAMA3_70B, 4096, 10, peak),
-                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32", LLAMA3_70B, 4096, 4, peak, batch=32)]
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32", LLAMA3_70B, 4096, 4, peak, batch=32),
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32, fp16 cache", LLAMA3_70B, 4096, 4, peak, batch=32,
+                                               kv_f16=True)]
             except Exception as exc:                      # the headline metric above must survive a failure here
                 line["decode"] = {"error": repr(exc)}
                 lib.ckb200_clear_error()

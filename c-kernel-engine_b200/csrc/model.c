@@ -73,8 +73,10 @@ struct CKB200Model {
     uint8_t *planar_arena;  /* row-planar copies of the Q6_K projection matrices, rebuilt from `arena` when weights change */
     size_t planar_bytes;
     int planar_ready;
-    float *kv;              /* [L][2][B][Hkvl][S][d] */
-    long long kv_layer_stride, kv_batch_stride;
+    uint8_t *kv;            /* [L][2][B][Hkvl][S][d], elements of kv_eb bytes */
+    int kv_eb;              /* 4: fp32 cache; 2: IEEE fp16 cache (tune model_kv_f16 at creation: kv_cache_store_f16 and the
+                             * _f16cache attention of the reference, half the cache bytes per key) */
+    long long kv_layer_stride, kv_batch_stride;     /* in elements */
     float *rope_cos, *rope_sin;
     /* activations */
     float *x, *prev, *q, *k, *v, *att, *o, *gu, *logits, *attn_scratch;
@@ -108,6 +110,12 @@ struct CKB200Model {
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t kv_bytes(const struct CKB200Model *m) { return (size_t)m->c.num_layers * (size_t)m->kv_layer_stride * (size_t)m->kv_eb; }
+/* key (is_v = 0) or value cache of one layer: [B][Hkvl][S][d] */
+static void *kv_at(const struct CKB200Model *m, int layer, int is_v)
+{
+    return m->kv + ((size_t)layer * (size_t)m->kv_layer_stride + (is_v ? (size_t)m->c.batch * (size_t)m->kv_batch_stride : 0)) * (size_t)m->kv_eb;
+}
 static int round256(int v) { return (v + 255) / 256 * 256; }
 
 static size_t fmt_row_bytes(int fmt, int cols)
@@ -164,6 +172,13 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     }
     if (tp > 1 && (m->Al % 256 || m->Il % 256)) {
         ckb_fail(CKB_ERR_SHAPE, "model_create: tp=%d needs the per-rank attention width %d and FFN width %d to be multiples of 256", tp, m->Al, m->Il);
+        free(m);
+        return NULL;
+    }
+    m->kv_eb = ckb_tune_get("model_kv_f16", 0) ? 2 : 4;
+    if (m->kv_eb == 2 && ((m->d != 64 && m->d != 128) || m->Hl / m->Hkvl > 8 || ((long long)m->Hkvl * cfg->max_seq_len * m->d) % 8)) {
+        ckb_fail(CKB_ERR_SHAPE, "model_create: the fp16 cache needs a head size of 64 or 128 and at most 8 query heads per kv head (have %d, %d)", m->d,
+                 m->Hl / m->Hkvl);
         free(m);
         return NULL;
     }
@@ -225,7 +240,7 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     if (m->planar_bytes) DEV_ALLOC(m->planar_arena, m->planar_bytes);
     m->kv_batch_stride = (long long)m->Hkvl * S * m->d;
     m->kv_layer_stride = 2LL * B * m->kv_batch_stride;
-    DEV_ALLOC(m->kv, (size_t)L * m->kv_layer_stride * sizeof(float));
+    DEV_ALLOC(m->kv, kv_bytes(m));
     DEV_ALLOC(m->rope_cos, (size_t)S * (m->d / 2) * sizeof(float));
     DEV_ALLOC(m->rope_sin, (size_t)S * (m->d / 2) * sizeof(float));
     DEV_ALLOC(m->x, (size_t)B * m->Da * sizeof(float));
@@ -284,7 +299,7 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
 
     cudaStream_t st = ckb_stream(NULL);
     cudaMemsetAsync(m->arena, 0, m->arena_bytes, st);
-    cudaMemsetAsync(m->kv, 0, (size_t)L * m->kv_layer_stride * sizeof(float), st);
+    cudaMemsetAsync(m->kv, 0, kv_bytes(m), st);
     cudaMemsetAsync(m->att, 0, (size_t)B * m->Ala * sizeof(float), st);       /* zero tail of the attention rows stays zero */
     cudaMemsetAsync(m->x, 0, (size_t)B * m->Da * sizeof(float), st);
     cudaMemsetAsync(m->prev, 0, (size_t)B * m->Da * sizeof(float), st);
@@ -386,19 +401,19 @@ int ckb200_model_fill_kv_synthetic(CKB200Model *m, int tokens, unsigned long lon
     if (!m || tokens < 0 || tokens > m->c.max_seq_len) return ckb_fail(CKB_ERR_STATE, "model_fill_kv_synthetic: bad token count %d", tokens);
     const int L = m->c.num_layers, B = m->c.batch, S = m->c.max_seq_len;
     cudaStream_t st = ckb_stream(NULL);
-    cudaMemsetAsync(m->kv, 0, (size_t)L * m->kv_layer_stride * sizeof(float), st);
+    cudaMemsetAsync(m->kv, 0, kv_bytes(m), st);
     if (tokens > 0) {
         /* N(0,1) in the first `tokens` positions of every head: fill a compact buffer, then strided copy */
-        const size_t heads = (size_t)L * 2 * B * m->Hkvl;
-        float *tmp = NULL;
+        const size_t heads = (size_t)L * 2 * B * m->Hkvl, eb = (size_t)m->kv_eb;
+        uint8_t *tmp = NULL;
         const size_t row = (size_t)tokens * m->d;
         const size_t chunk_heads = heads < 4096 ? heads : 4096;
-        if (ckb_check_cuda((int)cudaMalloc((void **)&tmp, chunk_heads * row * sizeof(float)), "cudaMalloc(kv fill)")) return CKB_ERR_CUDA;
+        if (ckb_check_cuda((int)cudaMalloc((void **)&tmp, chunk_heads * row * eb), "cudaMalloc(kv fill)")) return CKB_ERR_CUDA;
         for (size_t h0 = 0; h0 < heads; h0 += chunk_heads) {
             const size_t n = heads - h0 < chunk_heads ? heads - h0 : chunk_heads;
-            ckb200_dev_fill_normal(tmp, (long long)(n * row), 0, seed + h0, NULL);
-            cudaMemcpy2DAsync(m->kv + h0 * (size_t)S * m->d, (size_t)S * m->d * sizeof(float), tmp, row * sizeof(float), row * sizeof(float), n,
-                              cudaMemcpyDeviceToDevice, st);
+            if (m->kv_eb == 2) ckb200_dev_fill_normal_f16((uint16_t *)tmp, (long long)(n * row), 0, seed + h0, NULL);
+            else ckb200_dev_fill_normal((float *)tmp, (long long)(n * row), 0, seed + h0, NULL);
+            cudaMemcpy2DAsync(m->kv + h0 * (size_t)S * m->d * eb, (size_t)S * m->d * eb, tmp, row * eb, row * eb, n, cudaMemcpyDeviceToDevice, st);
         }
         cudaStreamSynchronize(st);
         cudaFree(tmp);
@@ -446,8 +461,9 @@ float *ckb200_model_logits_device(CKB200Model *m) { return m ? m->logits : NULL;
 void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v)
 {
     if (!m || layer < 0 || layer >= m->c.num_layers) return NULL;
-    return m->kv + (size_t)layer * m->kv_layer_stride + (is_v ? (size_t)m->c.batch * m->kv_batch_stride : 0);
+    return kv_at(m, layer, is_v);
 }
+int ckb200_model_kv_element_bytes(CKB200Model *m) { return m ? m->kv_eb : 0; }
 
 /* ------------------------------------------------------------------ the step */
 
@@ -578,7 +594,7 @@ static int fused_fmt(const Tensor *t) { return t->fmt == FMT_Q4K ? SG_FMT_Q4K : 
 
 static int fused_step_ok(const CKB200Model *m)
 {
-    if (m->c.batch != 1 || m->c.tp_size != 1 || !ckb_tune_get("model_fused_step", 0)) return 0;
+    if (m->c.batch != 1 || m->c.tp_size != 1 || m->kv_eb != 4 || !ckb_tune_get("model_fused_step", 0)) return 0;
     for (int l = 0; l < m->c.num_layers; ++l) {
         static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
         for (int i = 0; i < 6; ++i)
@@ -706,7 +722,7 @@ static int issue_step_fused(CKB200Model *m, void *st)
     base.eps = c->rms_eps;
     for (int l = 0; l < L; ++l) {
         Tensor *t = m->layers[l].t;
-        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + m->kv_batch_stride;
+        float *kc = (float *)kv_at(m, l, 0), *vc = (float *)kv_at(m, l, 1);
         StepGemvParams p = base;
         /* 1: q | k | v */
         p.nseg = 3;
@@ -773,7 +789,7 @@ static int issue_step(CKB200Model *m, void *st)
     float *delta = NULL;
     for (int l = 0; l < L; ++l) {
         Tensor *t = m->layers[l].t;
-        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + (size_t)B * m->kv_batch_stride;
+        void *kc = kv_at(m, l, 0), *vc = kv_at(m, l, 1);
         if ((rc = reduce_norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
         if (fmt_block32(t[CKB_T_WK].fmt) != fmt_block32(t[CKB_T_WQ].fmt) || fmt_block32(t[CKB_T_WV].fmt) != fmt_block32(t[CKB_T_WQ].fmt))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
@@ -792,7 +808,16 @@ static int issue_step(CKB200Model *m, void *st)
             if ((rc = matvec(m, &t[CKB_T_WK], m->hq, m->k, m->Hkvl * m->d, st))) return rc;
             if ((rc = matvec(m, &t[CKB_T_WV], m->hq, m->v, m->Hkvl * m->d, st))) return rc;
         }
-        if ((rc = ckb200_dev_rope_kv_store(m->q, m->k, m->v, kc, vc, m->rope_cos, m->rope_sin, m->pos_dev, B, m->Hl, m->Hkvl, m->d,
+        if (m->kv_eb == 2) {
+            /* fp16 caches: the rotation stays fp32, k and v are rounded once on the store, attention widens them again */
+            if ((rc = ckb200_dev_rope_kv_store_f16(m->q, m->k, m->v, (uint16_t *)kc, (uint16_t *)vc, m->rope_cos, m->rope_sin, m->pos_dev, B, m->Hl,
+                                                   m->Hkvl, m->d, c->max_seq_len, m->kv_batch_stride, st))) return rc;
+            if ((rc = ckb200_dev_attention_decode_f16cache_ws(m->q, (const uint16_t *)kc, (const uint16_t *)vc, m->att, B, m->kv_batch_stride, m->Hl,
+                                                              m->Hkvl, 1, c->max_seq_len, m->d, m->d, m->attn_splits, m->attn_scratch, m->pos_dev, st)))
+                return rc;
+            goto attention_done;
+        }
+        if ((rc = ckb200_dev_rope_kv_store(m->q, m->k, m->v, (float *)kc, (float *)vc, m->rope_cos, m->rope_sin, m->pos_dev, B, m->Hl, m->Hkvl, m->d,
                                            c->max_seq_len, m->kv_batch_stride, st))) return rc;
         /* attention rows are contiguous [B][Al]; with B == 1 the row sits in an Ala-wide buffer whose tail stays zero.
          * Attention, split merge and quantisation stay three launches: chained with programmatic dependent launch inside
@@ -801,10 +826,12 @@ static int issue_step(CKB200Model *m, void *st)
         ckb_attn_hint_early_rows(ckb_tune_get("model_attn_early_rows", 1));
         if (ckb_tune_get("model_attn_cluster", 0)) {
             /* one launch: the CTAs of a kv head form a thread-block cluster and merge their partial results in distributed shared memory */
-            if ((rc = ckb200_dev_attention_decode_fused(m->q, kc, vc, m->att, B == 1 ? m->Ala : m->Al, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len,
-                                                        m->d, m->d, m->attn_splits, m->attn_scratch, m->attn_counters, m->pos_dev, NULL, 0, st))) return rc;
-        } else if ((rc = ckb200_dev_attention_decode_ws(m->q, kc, vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d,
-                                                        m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
+            if ((rc = ckb200_dev_attention_decode_fused(m->q, (const float *)kc, (const float *)vc, m->att, B == 1 ? m->Ala : m->Al, B, m->kv_batch_stride,
+                                                        m->Hl, m->Hkvl, 1, c->max_seq_len, m->d, m->d, m->attn_splits, m->attn_scratch, m->attn_counters,
+                                                        m->pos_dev, NULL, 0, st))) return rc;
+        } else if ((rc = ckb200_dev_attention_decode_ws(m->q, (const float *)kc, (const float *)vc, m->att, B, m->kv_batch_stride, m->Hl, m->Hkvl, 1,
+                                                        c->max_seq_len, m->d, m->d, m->attn_splits, m->attn_scratch, m->pos_dev, st))) return rc;
+    attention_done:
         ckb_attn_hint_early_rows(0);
         if ((rc = quant_rows(&t[CKB_T_WO], m->att, m->Ala, m->aq, B, st))) return rc;
         if ((rc = matvec(m, &t[CKB_T_WO], m->aq, m->o, m->Da, st))) return rc;
@@ -888,7 +915,7 @@ int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bia
 
 static int prefill_ok(const CKB200Model *m, int T)
 {
-    if (m->c.batch != 1 || m->c.tp_size != 1 || T < 16 || m->host_pos != 0 || T > m->c.max_seq_len || !ckb_tune_get("model_prefill", 1)) return 0;
+    if (m->c.batch != 1 || m->c.tp_size != 1 || m->kv_eb != 4 || T < 16 || m->host_pos != 0 || T > m->c.max_seq_len || !ckb_tune_get("model_prefill", 1)) return 0;
     for (int l = 0; l < m->c.num_layers; ++l) {
         static const int which[6] = { CKB_T_WQ, CKB_T_WK, CKB_T_WV, CKB_T_WO, CKB_T_W1, CKB_T_W2 };
         for (int i = 0; i < 6; ++i) {
@@ -936,7 +963,7 @@ static int issue_prefill(CKB200Model *m, int T, void *st)
     const float *delta = NULL;
     for (int l = 0; l < L; ++l) {
         Tensor *t = m->layers[l].t;
-        float *kc = m->kv + (size_t)l * m->kv_layer_stride, *vc = kc + m->kv_batch_stride;
+        float *kc = (float *)kv_at(m, l, 0), *vc = (float *)kv_at(m, l, 1);
         if ((rc = ckb200_dev_add_rmsnorm_q8k(m->pf_x, delta, (const float *)t[CKB_T_LN1].w, m->pf_hq, NULL, T, m->D, m->Da, c->rms_eps, st))) return rc;
         if ((rc = prefill_gemm(&t[CKB_T_WQ], m->pf_hq, m->pf_q, m->Al, T, st))) return rc;
         if ((rc = prefill_gemm(&t[CKB_T_WK], m->pf_hq, m->pf_k, kvw, T, st))) return rc;
@@ -1115,6 +1142,6 @@ int ckb200_model_reset(CKB200Model *m)
 {
     if (!m) return CKB_ERR_STATE;
     cudaStream_t st = ckb_stream(NULL);
-    cudaMemsetAsync(m->kv, 0, (size_t)m->c.num_layers * m->kv_layer_stride * sizeof(float), st);
+    cudaMemsetAsync(m->kv, 0, kv_bytes(m), st);
     return ckb200_model_set_pos(m, 0);
 }

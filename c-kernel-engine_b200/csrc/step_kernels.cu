@@ -110,9 +110,14 @@ __global__ void __launch_bounds__(128) swiglu_q8k_kernel(const float *__restrict
 }
 
 // One token per sequence.  q [B][H][d] is rotated in place; k [B][Hkv][d] is rotated and written, v copied,
-// into the caches [B][Hkv][max_seq][d] at position *pos_dev (the same position for every sequence).
+// into the caches [B][Hkv][max_seq][d] at position *pos_dev (the same position for every sequence).  CT is the cache
+// element: float, or __half rounded to nearest even as kv_cache_store_f16 does (src/kernels/kv_cache_kernels.c).
+__device__ __forceinline__ void cache_put(float *p, float x) { *p = x; }
+__device__ __forceinline__ void cache_put(__half *p, float x) { *p = __float2half_rn(x); }
+
+template <typename CT>
 __global__ void rope_kv_store_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-                                     float *__restrict__ kc, float *__restrict__ vc, const float *__restrict__ cos_cache,
+                                     CT *__restrict__ kc, CT *__restrict__ vc, const float *__restrict__ cos_cache,
                                      const float *__restrict__ sin_cache, const int *__restrict__ pos_dev, int batch, int H, int Hkv,
                                      int d, int max_seq, long long kv_batch_stride)
 {
@@ -143,16 +148,16 @@ __global__ void rope_kv_store_kernel(float *__restrict__ q, const float *__restr
         } else if (h < H + Hkv) {
             const int hk = h - H;
             const float *row = k + ((size_t)s * Hkv + hk) * d;
-            float *dst = kc + (size_t)s * kv_batch_stride + ((size_t)hk * max_seq + pos) * d;
+            CT *dst = kc + (size_t)s * kv_batch_stride + ((size_t)hk * max_seq + pos) * d;
             const float a = __ldcg(row + j), b = __ldcg(row + j + half);
-            dst[j] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
-            dst[j + half] = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
+            cache_put(dst + j, __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+            cache_put(dst + j + half, __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c)));
         } else {
             const int hk = h - H - Hkv;
             const float *row = v + ((size_t)s * Hkv + hk) * d;
-            float *dst = vc + (size_t)s * kv_batch_stride + ((size_t)hk * max_seq + pos) * d;
-            dst[j] = __ldcg(row + j);
-            dst[j + half] = __ldcg(row + j + half);
+            CT *dst = vc + (size_t)s * kv_batch_stride + ((size_t)hk * max_seq + pos) * d;
+            cache_put(dst + j, __ldcg(row + j));
+            cache_put(dst + j + half, __ldcg(row + j + half));
         }
     }
 }
@@ -210,13 +215,14 @@ __global__ void fill_blocks_kernel(uint8_t *__restrict__ w, long long nblocks, i
 }
 
 // mode 0: N(0,1) (Box-Muller), mode 1: 1 + 0.1 * N(0,1)
-__global__ void fill_normal_kernel(float *__restrict__ x, long long n, int mode, uint64_t seed)
+template <typename T>
+__global__ void fill_normal_kernel(T *__restrict__ x, long long n, int mode, uint64_t seed)
 {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const float u0 = ((mix32(seed * 977 + 2 * i) & 0xFFFFFF) + 1) * (1.0f / 16777217.0f);
         const float u1 = (mix32(seed * 977 + 2 * i + 1) & 0xFFFFFF) * (1.0f / 16777216.0f);
         const float z = sqrtf(-2.0f * logf(u0)) * cospif(2.0f * u1);
-        x[i] = mode == 1 ? 1.0f + 0.1f * z : z;
+        cache_put(x + i, mode == 1 ? 1.0f + 0.1f * z : z);
     }
 }
 
@@ -288,8 +294,21 @@ extern "C" int ckb200_dev_rope_kv_store(float *q, const float *k, const float *v
     if (!q || !k || !v || !k_cache || !v_cache || !cos_cache || !sin_cache || !pos_dev || batch <= 0) return 0;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     const long long n = (long long)batch * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
-    return launch_pdl("rope_kv_store", rope_kv_store_kernel, dim3(grid_for(n, 128, 1024)), dim3(128), 0, ckb_stream(stream), q, k, v, k_cache,
+    return launch_pdl("rope_kv_store", rope_kv_store_kernel<float>, dim3(grid_for(n, 128, 1024)), dim3(128), 0, ckb_stream(stream), q, k, v, k_cache,
                       v_cache, cos_cache, sin_cache, pos_dev, batch, num_heads, num_kv_heads, head_dim, max_seq_len, kv_batch_stride);
+}
+
+// The same step with IEEE fp16 caches (rope_forward_qk + kv_cache_store_f16): q and k are rotated in fp32, k and v rounded once on the store.
+extern "C" int ckb200_dev_rope_kv_store_f16(float *q, const float *k, const float *v, uint16_t *k_cache, uint16_t *v_cache, const float *cos_cache,
+                                            const float *sin_cache, const int *pos_dev, int batch, int num_heads, int num_kv_heads,
+                                            int head_dim, int max_seq_len, long long kv_batch_stride, void *stream)
+{
+    if (!q || !k || !v || !k_cache || !v_cache || !cos_cache || !sin_cache || !pos_dev || batch <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    const long long n = (long long)batch * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
+    return launch_pdl("rope_kv_store_f16", rope_kv_store_kernel<__half>, dim3(grid_for(n, 128, 1024)), dim3(128), 0, ckb_stream(stream), q, k, v,
+                      reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), cos_cache, sin_cache, pos_dev, batch, num_heads,
+                      num_kv_heads, head_dim, max_seq_len, kv_batch_stride);
 }
 
 extern "C" int ckb200_dev_advance_pos(int *pos_dev, void *stream)
@@ -318,6 +337,14 @@ extern "C" int ckb200_dev_fill_normal(float *x, long long n, int mode, unsigned 
 {
     if (!x || n <= 0) return 0;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
-    fill_normal_kernel<<<grid_for(n, 256, 8192), 256, 0, ckb_stream(stream)>>>(x, n, mode, seed);
+    fill_normal_kernel<float><<<grid_for(n, 256, 8192), 256, 0, ckb_stream(stream)>>>(x, n, mode, seed);
     return ckb_check_launch("fill_normal");
+}
+
+extern "C" int ckb200_dev_fill_normal_f16(uint16_t *x, long long n, int mode, unsigned long long seed, void *stream)
+{
+    if (!x || n <= 0) return 0;
+    if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
+    fill_normal_kernel<__half><<<grid_for(n, 256, 8192), 256, 0, ckb_stream(stream)>>>(reinterpret_cast<__half *>(x), n, mode, seed);
+    return ckb_check_launch("fill_normal_f16");
 }

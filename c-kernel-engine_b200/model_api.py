@@ -57,6 +57,7 @@ def bind_model_api(lib):
     lib.ckb200_model_tensor_bytes.restype = C.c_size_t
     lib.ckb200_model_kv_device.argtypes = [C.c_void_p, C.c_int, C.c_int]
     lib.ckb200_model_kv_device.restype = C.c_void_p
+    lib.ckb200_model_kv_element_bytes.argtypes = [C.c_void_p]
     lib.ckb200_model_logits_device.argtypes = [C.c_void_p]
     lib.ckb200_model_logits_device.restype = C.c_void_p
     lib.ckb200_model_set_pos.argtypes = [C.c_void_p, C.c_int]

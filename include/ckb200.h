@@ -293,11 +293,16 @@ int ckb200_dev_swiglu_q8k(const float *gate_up, void *out_q8, int tokens, int di
 int ckb200_dev_rope_kv_store(float *q, const float *k, const float *v, float *k_cache, float *v_cache, const float *cos_cache,
                              const float *sin_cache, const int *pos_dev, int batch, int num_heads, int num_kv_heads,
                              int head_dim, int max_seq_len, long long kv_batch_stride, void *stream);
+/* the same with IEEE fp16 caches (kv_cache_store_f16): rotation in fp32, one rounding on the store */
+int ckb200_dev_rope_kv_store_f16(float *q, const float *k, const float *v, uint16_t *k_cache, uint16_t *v_cache, const float *cos_cache,
+                                 const float *sin_cache, const int *pos_dev, int batch, int num_heads, int num_kv_heads,
+                                 int head_dim, int max_seq_len, long long kv_batch_stride, void *stream);
 int ckb200_dev_advance_pos(int *pos_dev, void *stream);                       /* model->pos++ on the device */
 int ckb200_dev_add_inplace(float *x, const float *delta, long long n, void *stream);
 /* synthetic data generated on the device (benchmarks of shapes too large to build on the host) */
 int ckb200_dev_fill_blocks(void *w, long long nblocks, int fmt, unsigned long long seed, void *stream);
 int ckb200_dev_fill_normal(float *x, long long n, int mode, unsigned long long seed, void *stream);
+int ckb200_dev_fill_normal_f16(uint16_t *x, long long n, int mode, unsigned long long seed, void *stream);
 
 #ifdef __cplusplus
 }

@@ -80,7 +80,10 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
 int ckb200_model_prefill(CKB200Model *m, const int32_t *tokens, int count, float *logits_host);
 int ckb200_model_decode_repeat(CKB200Model *m, int steps);              /* re-launch the captured step `steps` times */
 float *ckb200_model_logits_device(CKB200Model *m);
-void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v);       /* [batch][Hkv][max_seq][head_dim] fp32 */
+void *ckb200_model_kv_device(CKB200Model *m, int layer, int is_v);       /* [batch][Hkv][max_seq][head_dim], fp32 unless ... */
+int ckb200_model_kv_element_bytes(CKB200Model *m);                       /* ... 2: the model was created with tune model_kv_f16 = 1 (IEEE fp16
+                                                                          * cache: kv_cache_store_f16 + the _f16cache decode attention,
+                                                                          * src/kernels/kv_cache_kernels.c, attention_kernels.c:3450-3557) */
 size_t ckb200_model_weight_bytes(CKB200Model *m);                        /* quantised bytes one step streams */
 
 

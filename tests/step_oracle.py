@@ -33,8 +33,10 @@ def embed_row(lib, fmt, table, token, vocab, d, table_cols, da):
 class CpuModel:
     """Whole (unsharded) model on the host: random weights in the reference's block formats."""
 
-    def __init__(self, cfg: dict, seed: int):
+    def __init__(self, cfg: dict, seed: int, kv_f16: bool = False):
+        """kv_f16: keep the caches as IEEE halves (kv_cache_store_f16 + the _f16cache decode attention of the reference)."""
         self.cfg = cfg
+        self.kv_f16 = kv_f16
         D, H, Hkv, d, I, L, V = (cfg[k] for k in ("embed_dim", "num_heads", "num_kv_heads", "head_dim", "intermediate_size", "num_layers", "vocab_size"))
         self.Da, self.A, self.Aa = round256(D), H * d, round256(H * d)
         rng = np.random.default_rng(seed)
@@ -60,6 +62,9 @@ class CpuModel:
         rng = np.random.default_rng(seed)
         self.kc[:, :, :tokens] = rng.standard_normal(self.kc[:, :, :tokens].shape).astype(np.float32)
         self.vc[:, :, :tokens] = rng.standard_normal(self.vc[:, :, :tokens].shape).astype(np.float32)
+        if self.kv_f16:
+            self.kc16 = self.kc.astype(np.float16).view(np.uint16)
+            self.vc16 = self.vc.astype(np.float16).view(np.uint16)
 
     def _matvec(self, lib, w, x_row):
         fmt, rows, cols, data = w
@@ -80,8 +85,12 @@ class CpuModel:
             k = self._matvec(lib, lay["WK"], h).reshape(Hkv, 1, d).copy()
             v = self._matvec(lib, lay["WV"], h).reshape(Hkv, d).copy()
             cases.rope_qk(lib, "oracle_", q, k, cos, sin, pos)
-            cases.kv_cache_store(lib, "oracle_", self.kc[l], self.vc[l], np.ascontiguousarray(k.reshape(Hkv, d)), v, pos)
-            att = cases.attention_decode(lib, "oracle_", np.ascontiguousarray(q.reshape(H, d)), self.kc[l], self.vc[l], pos + 1).reshape(-1)
+            if self.kv_f16:
+                cases.kv_cache_store_f16(lib, "oracle_", self.kc16[l], self.vc16[l], np.ascontiguousarray(k.reshape(Hkv, d)), v, pos)
+                att = cases.attention_decode_f16cache(lib, "oracle_", np.ascontiguousarray(q.reshape(H, d)), self.kc16[l], self.vc16[l], pos + 1).reshape(-1)
+            else:
+                cases.kv_cache_store(lib, "oracle_", self.kc[l], self.vc[l], np.ascontiguousarray(k.reshape(Hkv, d)), v, pos)
+                att = cases.attention_decode(lib, "oracle_", np.ascontiguousarray(q.reshape(H, d)), self.kc[l], self.vc[l], pos + 1).reshape(-1)
             o = self._matvec(lib, lay["WO"], att)
             x[:D] += o
             h = cases.rmsnorm(lib, "oracle_", x.reshape(1, -1), lay["LN2"], D, c["rms_eps"])[0]
@@ -108,7 +117,7 @@ def upload_whole_model(lib, handle, cpu: CpuModel, batch: int):
     assert lib.ckb200_model_upload_tensor(handle, -1, T["FINAL_GAMMA"], cases.vptr(cpu.final_gamma), cpu.final_gamma.nbytes) == 0
     assert lib.ckb200_model_upload_tensor(handle, -1, T["LM_HEAD"], cases.vptr(cpu.lm_head[3]), cpu.lm_head[3].nbytes) == 0
     for l in range(len(cpu.layers)):
-        for is_v, cache in ((0, cpu.kc), (1, cpu.vc)):
+        for is_v, cache in ((0, cpu.kc16), (1, cpu.vc16)) if cpu.kv_f16 else ((0, cpu.kc), (1, cpu.vc)):
             base = lib.ckb200_model_kv_device(handle, l, is_v)
             slab = np.ascontiguousarray(cache[l])
             for b in range(batch):

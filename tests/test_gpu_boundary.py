@@ -177,7 +177,8 @@ def test_bounded_wait_runs_out_and_is_reported(ck):
         ck.ckb200_clear_error()
 
 
-@pytest.mark.parametrize("heads,kv_heads,d,tokens,cap", [(32, 8, 128, 1500, 2048), (14, 2, 64, 1024, 1024), (6, 3, 64, 33, 40), (2, 1, 128, 4096, 4096)])
+@pytest.mark.parametrize("heads,kv_heads,d,tokens,cap", [(32, 8, 128, 1500, 2048), (14, 2, 64, 1024, 1024), (6, 3, 64, 33, 40), (2, 1, 128, 4096, 4096),
+                                                        (4, 2, 256, 300, 320), (3, 1, 80, 77, 77)])   # wider than 128: every thread walks; 80: odd row width
 def test_f16kv_decode_attention_walks_the_keys_in_order(ck, orc, heads, kv_heads, d, tokens, cap):
     """attention_forward_decode_head_major_gqa_flash_f16kv: the accumulator is rounded to fp16 after every key, so only a kernel that keeps the
     reference's key order stays within fp16 rounding flips of it (a split-K kernel drifts by about 1 % at these lengths)."""
@@ -187,6 +188,26 @@ def test_f16kv_decode_attention_walks_the_keys_in_order(ck, orc, heads, kv_heads
     assert close(got, want, 2e-3)
     exact = cases.attention_decode(orc, "oracle_", q, kc, vc, tokens)
     assert not close(want, exact, 1e-4) or tokens < 64          # the fp16 form is a different function, not a relabelled fp32 kernel
+
+
+@pytest.mark.parametrize("v_scale,tol", [(2.0e-5, 2e-2), (3.0e-8, 0.3), (8.0e3, 2e-3)])
+def test_f16kv_decode_attention_outside_the_normal_fp16_range(ck, orc, v_scale, tol):
+    """Values so small that the accumulator lives among fp16's subnormals (steps of 2^-24: the looser bounds) or vanishes, and so large
+    that about 8 % of the outputs overflow to infinity: the kernel's arithmetic shortcut for the rounding does not hold there and it has to
+    notice.  An accumulator that passes within a rounding step of the overflow threshold may land on either side (the scores differ in
+    the last place), so a few outputs may disagree on finiteness; the rest must agree as closely as in the normal range."""
+    heads, kv_heads, d, tokens = 8, 2, 128, 700
+    q, kc, vc = cases.attention_inputs(5, heads, kv_heads, d, tokens, tokens)
+    vc = (vc * np.float32(v_scale)).astype(np.float32)
+    want = cases.attention_decode_f16kv(orc, "oracle_", q, kc, vc, tokens)
+    got = cases.attention_decode_f16kv(ck, "", q, kc, vc, tokens)
+    assert not np.isnan(want).any() and not np.isnan(got).any()
+    both = np.isfinite(got) & np.isfinite(want)
+    assert float(np.mean(np.isfinite(got) != np.isfinite(want))) <= 0.01
+    if v_scale > 1:
+        assert 0.02 < float(np.mean(np.isinf(got))) < 0.2
+        assert np.array_equal(got[np.isinf(got) & np.isinf(want)], want[np.isinf(got) & np.isinf(want)])       # the sign of the infinity
+    assert close(np.where(both, got, 0), np.where(both, want, 0), tol)
 
 
 def test_f16kv_prefill_attention(ck, orc):

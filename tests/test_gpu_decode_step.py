@@ -61,6 +61,59 @@ def test_decode_steps_match_cpu_step(ck, orc, cfg, batch, use_graph):
         ck.ckb200_tune_set(b"model_graph", 1)
 
 
+@pytest.mark.parametrize("cfg,batch", [(MINI_QWEN, 1), (MINI_LLAMA, 2)])
+def test_decode_steps_with_fp16_cache(ck, orc, cfg, batch):
+    """tune model_kv_f16 = 1 at creation: k and v are rounded to IEEE halves on the store (kv_cache_store_f16) and attention widens
+    them again (the reference's _f16cache decode attention); the CPU step keeps its caches the same way."""
+    so.bind_model_api(ck)
+    cpu = so.CpuModel(cfg, seed=17, kv_f16=True)
+    start = 33
+    cpu.prefill_kv(start, seed=18)
+    st = so.make_cfg(cfg, batch=batch)
+    ck.ckb200_tune_set(b"model_kv_f16", 1)
+    try:
+        handle = ck.ckb200_model_create(C.byref(st))
+    finally:
+        ck.ckb200_tune_set(b"model_kv_f16", 0)
+    assert handle, ck.ckb200_last_error_message()
+    try:
+        assert ck.ckb200_model_kv_element_bytes(handle) == 2
+        so.upload_whole_model(ck, handle, cpu, batch)
+        assert ck.ckb200_model_set_pos(handle, start) == 0
+        V, Hkv, d, S = cfg["vocab_size"], cfg["num_kv_heads"], cfg["head_dim"], cfg["max_seq_len"]
+        for step, tok in enumerate([9, 41, 300]):
+            want = cpu.decode(orc, tok, start + step)
+            ids = np.full(batch, tok, dtype=np.int32)
+            logits = np.full((batch, V), np.nan, dtype=np.float32)
+            assert ck.ckb200_model_decode(handle, cases.vptr(ids), cases.vptr(logits)) == 0, ck.ckb200_last_error_message()
+            for b in range(batch):
+                assert cosine(logits[b], want) >= 0.9999, (step, b)
+                assert float(np.max(np.abs(logits[b] - want))) / float(np.max(np.abs(want))) < 5e-3, (step, b)
+        # the stored halves of layer 0 (whose inputs do not depend on earlier attention) are the CPU step's, up to the last place of a half
+        got = np.zeros((batch, Hkv, S, d), np.uint16)
+        assert ck.ckb200_copy_to_host(cases.vptr(got), C.c_void_p(ck.ckb200_model_kv_device(handle, 0, 1)), got.nbytes) == 0
+        a, w = got[0].view(np.float16).astype(np.float32), cpu.vc16[0].view(np.float16).astype(np.float32)
+        np.testing.assert_array_equal(a[:, :start], w[:, :start])
+        np.testing.assert_allclose(a[:, start:start + 3], w[:, start:start + 3], rtol=2e-3, atol=1e-4)
+        assert not a[:, start + 3:].any()
+        # prompts on such a model go through the step path (the batched prefill writes fp32 caches)
+        assert ck.ckb200_model_reset(handle) == 0
+    finally:
+        ck.ckb200_model_free(handle)
+
+
+def test_fp16_cache_refuses_unsupported_head_size(ck):
+    so.bind_model_api(ck)
+    cfg = dict(MINI_QWEN, head_dim=32, num_heads=12, num_kv_heads=4)
+    ck.ckb200_tune_set(b"model_kv_f16", 1)
+    try:
+        assert not ck.ckb200_model_create(C.byref(so.make_cfg(cfg, batch=1)))
+        assert b"fp16 cache" in ck.ckb200_last_error_message()
+    finally:
+        ck.ckb200_tune_set(b"model_kv_f16", 0)
+        ck.ckb200_clear_error()
+
+
 def test_synthetic_fill_and_repeat(ck):
     """Device-side synthetic weights: the step runs, logits are finite, the position advances per replay."""
     so.bind_model_api(ck)

@@ -13,10 +13,10 @@
 //   3. per output element d (one thread each), key by key:  o = r16(o * max_scale_j) when key j set a new maximum, then
 //      o = r16(o + value_scale_j * r16(v_jd));  and  sum = sum * max_scale_j + value_scale_j
 //      - the only serial part.  The value rows arrive through a cp.async ring in shared memory, so the walk never waits for DRAM.
-//        For heads of at most 128 elements the four warps that own no output element turn each staged chunk into the products
-//        value_scale_j * r16(v_jd) one chunk ahead of the walk, and the walk itself takes eight keys at a time: when none of them
-//        sets a new maximum (almost always) the chain per key is one add and the three-operation arithmetic form of the fp16
-//        rounding (r16_fast), checked afterwards for the ranges where that form is not exact and redone key by key if needed.
+//        For heads of at most 128 elements the four warps that own no output element start the copies and turn each staged chunk into
+//        the products value_scale_j * r16(v_jd) one chunk ahead of the walk (rounding by arithmetic, so that the conversion unit stays
+//        free for the walk), and the walk takes eight keys at a time with their operands loaded a group ahead: when none of the eight
+//        sets a new maximum (almost always) the chain per key is one add and the conversion pair.
 // One CTA of 256 threads per (query head, query token).  Scores and the per-key pairs live in shared memory (8 bytes per key).
 // Against the reference the dot products are summed in another order and expf is the device's, so parity is by tolerance; the
 // rounding sequence itself is the reference's.
@@ -35,19 +35,19 @@ constexpr int FK_CHUNK = 32;                       // value rows per staged chun
 constexpr int FK_MIN_STAGES = 4, FK_MAX_STAGES = 8; // chunks in the ring: as many as the shared memory left by the per-key arrays holds
 
 __device__ __forceinline__ float r16(float x) { return __half2float(__float2half_rn(x)); }
-// fp32 -> nearest fp16 (ties to even) -> fp32 without the two conversion instructions, whose latency would sit on the dependent chain of
-// the walk: Veltkamp's split with 2^13 + 1 keeps 11 significant bits.  Exact for 2^-14 <= |x| < 65520 (fp16's normal range up to the
-// value that rounds to infinity); compared there with the conversion pair on five million random values and every tie of the fp16 grid.
-// Outside that range (fp16 subnormals, zero, overflow) the caller has to use r16.
+// fp32 -> nearest fp16 (ties to even) -> fp32 on the fp32 pipe: Veltkamp's split with 2^13 + 1 keeps 11 significant bits.  Exact for
+// 2^-14 <= |x| < 65520 (fp16's normal range up to the value that rounds to infinity); compared there with the conversion pair on five
+// million random values and every tie of the fp16 grid.  Outside that range (fp16 subnormals, zero, overflow) the caller has to use r16.
+// On a dependent chain it is no faster than the conversion pair (17.6 against 16.4 cycles per add-and-round in a loop of its own); it is
+// used where many independent values are rounded while another warp's chain needs the conversion unit.
 constexpr float FK_FAST_MIN = 6.103515625e-05f, FK_FAST_MAX = 65520.0f;
 __device__ __forceinline__ float r16_fast(float x)
 {
     const float c = __fmul_rn(x, 8193.0f);
     return __fsub_rn(c, __fsub_rn(c, x));
 }
-// r16 for any input at the arithmetic form's cost when the value is in fp16's normal range: the fp32 -> fp16 conversion instruction
-// issues at a small fraction of the fp32 rate (the first form of this kernel spent most of its time in it), so it is kept for the rare
-// values outside that range (and for NaN, which fails both comparisons).
+// r16 for any input: the arithmetic form when the value is in fp16's normal range, the conversion pair otherwise (and for NaN, which fails
+// both comparisons).  Used where the result feeds more fp32 arithmetic and the branch is rarely taken.
 __device__ __forceinline__ float r16x(float x)
 {
     const float ax = fabsf(x);
@@ -334,17 +334,11 @@ __global__ void __launch_bounds__(FK_THREADS) attn_f16kv_kernel(const float *__r
                             const float newmax = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
                             bool exact = newmax < 0.0f;       // the same for every thread: the factors belong to the keys
                             if (exact) {
-                                float of = o, sf = sum, lo = INFINITY, hi = 0.0f;
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
-                                    const float x = __fadd_rn(of, pp[e]);
-                                    lo = fminf(lo, fabsf(x));
-                                    hi = fmaxf(hi, fabsf(x));
-                                    of = r16_fast(x);
-                                    sf = __fadd_rn(sf, w[e]);
+                                    o = r16(__fadd_rn(o, pp[e]));
+                                    sum = __fadd_rn(sum, w[e]);
                                 }
-                                exact = lo >= FK_FAST_MIN && hi < FK_FAST_MAX;    // false for a NaN as well
-                                if (exact) { o = of; sum = sf; }
                             }
                             if (!exact) {
 #pragma unroll

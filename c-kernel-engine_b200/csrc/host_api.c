@@ -98,7 +98,10 @@ static void host_gemv_rows(int fmt, float *y, const void *W, const void *x_q8, i
         rc = dev_gemv(fmt, dY, dW, dX, rows, K);
     }
     if (rc != 0) return;
-    ckb_finish_out(y + r0, dY, (size_t)rows * sizeof(float), back);
+    /* the Q4_K kernels (unless the ring variant was asked for) and the planar kernels have no bounded wait; the ring kernels that
+     * read the other formats in the reference layout do */
+    if ((fmt == F_Q4K && ckb200_tune_get("gemv_q4_k", 0) != 1) || planar) ckb_finish_out_nowait(y + r0, dY, (size_t)rows * sizeof(float), back);
+    else ckb_finish_out(y + r0, dY, (size_t)rows * sizeof(float), back);
 }
 
 static void host_gemv(int fmt, float *y, const void *W, const void *x_q8, int M, int K)

@@ -33,6 +33,7 @@ const void *ckb_stage_in(const void *host, size_t bytes, int slot, int try_regis
 void *ckb_stage_out(void *host, size_t bytes, int slot, int *needs_copy_back);
 /* D2H copy when needed, then synchronise the library stream. */
 int ckb_finish_out(void *host, const void *dev, size_t bytes, int needs_copy_back);
+int ckb_finish_out_nowait(void *host, const void *dev, size_t bytes, int needs_copy_back);   /* kernels without bounded waits */
 
 #ifdef __cplusplus
 }

@@ -210,6 +210,32 @@ def test_f16kv_decode_attention_outside_the_normal_fp16_range(ck, orc, v_scale, 
     assert close(np.where(both, got, 0), np.where(both, want, 0), tol)
 
 
+@pytest.mark.parametrize("fmt,m,k", [("q4_k", 301, 1024), ("q8_0", 77, 160), ("q6_k", 64, 512)])
+def test_host_call_with_pinned_buffers_matches_pageable(ck, orc, fmt, m, k):
+    """XX
+    (the Q8_0 activation row of 170 bytes also takes the byte tail of that kernel): same kernels, so the same bits as with ordinary
+    host buffers, with the result row at an odd offset inside the pinned block as well."""
+    ck.ckb200_host_alloc.restype = C.c_void_p
+    w = cases.synth.make_weights(fmt, m, k, seed=31)
+    xq = cases.quantize_act(orc, "oracle_", fmt, cases.synth.make_x(k, seed=32))
+    want = cases.gemv(ck, "", fmt, w, xq, m, k)
+    assert close(want, cases.gemv(orc, "oracle_", fmt, w, xq, m, k), 1e-5)
+    hx = ck.ckb200_host_alloc(C.c_size_t(xq.nbytes + 64))
+    hy = ck.ckb200_host_alloc(C.c_size_t(4 * m + 64))
+    assert hx and hy
+    try:
+        for x_off, y_off in ((0, 0), (4, 4)):
+            C.memmove(hx + x_off, xq.ctypes.data, xq.nbytes)
+            C.memset(hy, 0xFF, 4 * m + 64)
+            cases.fn(ck, "", cases.GEMV_SYMBOL[fmt])(C.c_void_p(hy + y_off), cases.vptr(w), C.c_void_p(hx + x_off), C.c_int(m), C.c_int(k))
+            got = np.frombuffer((C.c_char * (4 * m + 64)).from_address(hy), dtype=np.uint8).copy()
+            assert np.array_equal(got[y_off:y_off + 4 * m].view(np.float32), want)
+            assert (got[:y_off] == 0xFF).all() and (got[y_off + 4 * m:] == 0xFF).all()          # nothing written around the row
+    finally:
+        ck.ckb200_host_free(C.c_void_p(hx))
+        ck.ckb200_host_free(C.c_void_p(hy))
+
+
 def test_f16kv_prefill_attention(ck, orc):
     q, k, v = cases.prefill_attention_inputs(91, 8, 2, 128, 128, 200, 256)
     want = cases.attention_prefill_f16kv(orc, "oracle_", q, k, v, 128)

@@ -212,9 +212,9 @@ def test_f16kv_decode_attention_outside_the_normal_fp16_range(ck, orc, v_scale, 
 
 @pytest.mark.parametrize("fmt,m,k", [("q4_k", 301, 1024), ("q8_0", 77, 160), ("q6_k", 64, 512)])
 def test_host_call_with_pinned_buffers_matches_pageable(ck, orc, fmt, m, k):
-    """XX
-    (the Q8_0 activation row of 170 bytes also takes the byte tail of that kernel): same kernels, so the same bits as with ordinary
-    host buffers, with the result row at an odd offset inside the pinned block as well."""
+    """A result row in memory from ckb200_host_alloc is written across the bus by a kernel in the call's stream instead of the copy
+    engine (at offset 4 it is not 16-byte aligned: the byte path of that kernel): same GEMV kernels, so the same bits as with ordinary
+    host buffers, and nothing written around the row."""
     ck.ckb200_host_alloc.restype = C.c_void_p
     w = cases.synth.make_weights(fmt, m, k, seed=31)
     xq = cases.quantize_act(orc, "oracle_", fmt, cases.synth.make_x(k, seed=32))

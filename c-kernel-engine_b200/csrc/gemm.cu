@@ -28,10 +28,14 @@ static int gemm_nt_by_rows(gemv_fn fn, size_t a_row_bytes, const void *A_q8, con
     return bias ? ckb200_dev_add_bias_rows(C, bias, M, N, stream) : 0;
 }
 
+// Up to 64 tokens: the integer-MMA kernel that streams the weights through registers (gemm_q4k_mma.cu); above that the tcgen05 kernel.
+extern "C" int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
 extern "C" int ckb200_dev_gemm_nt_q4_k_q8_k(const void *A_q8, const void *B, const float *bias, float *C, int M, int N, int K, void *stream)
 {
     if (A_q8 && B && C && M > 0 && N > 0 && K > 0) {
-        const int rc = ckb_launch_gemm_q4k_tc(A_q8, B, bias, C, M, N, K, stream);
+        int rc = ckb_launch_gemm_q4k_mma(A_q8, B, bias, C, N, M, N, K, stream);
+        if (rc >= 0) return rc;
+        rc = ckb_launch_gemm_q4k_tc(A_q8, B, bias, C, M, N, K, stream);
         if (rc >= 0) return rc;
     }
     return gemm_nt_by_rows(ckb200_dev_gemv_q4_k_q8_k, (size_t)(K / 256) * ckb::Q8K_BYTES, A_q8, B, bias, C, M, N, K, stream);

@@ -42,6 +42,8 @@ void ckb_attn_hint_early_rows(int on);      /* attention.cu */
 int ckb_launch_gemm_tc_ws(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *ws,
                           size_t ws_bytes, void *stream);
 size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
+/* integer-MMA kernel of gemm_q4k_mma.cu for up to 64 tokens (Q4_K rows, no workspace); -1 when it does not take the call */
+int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
 
 enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2, FMT_Q50 = 3 };
 /* formats with 32-element blocks take Q8_0 activations, the K-quants take Q8_K */
@@ -487,8 +489,13 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
 /* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
 static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, int y_stride, void *st)
 {
+    /* batched decode: the weights are streamed once for all sequences.  Q4_K from 4 sequences up on the integer-MMA kernel (no workspace),
+     * otherwise from 16 up on the tcgen05 kernel */
+    if (w->fmt == FMT_Q4K && m->c.batch > 1) {
+        const int rc = ckb_launch_gemm_q4k_mma(xq, w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols, st);
+        if (rc >= 0) return rc;
+    }
     if (m->c.batch >= MODEL_GEMM_MIN_BATCH && (w->fmt == FMT_Q4K || (w->fmt == FMT_Q6K && w->planar))) {
-        /* batched decode: the weights are streamed once for all sequences */
         const int rc = ckb_launch_gemm_tc_ws(w->fmt == FMT_Q6K, xq, w->fmt == FMT_Q6K ? w->planar : w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols,
                                              MODEL_GEMM_MIN_BATCH, m->gemm_ws, m->gemm_ws_bytes, st);
         if (rc >= 0) return rc;

@@ -590,6 +590,7 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
             try:
                 line["decode"] = [decode_bench(lib, "Qwen2-0.5B shape, Q4_K_M mix", QWEN2_05B, 1024, 200, peak),
                                   decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU", LLAMA3_70B, 4096, 10, peak),
+                                  decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 8", LLAMA3_70B, 4096, 6, peak, batch=8),
                                   decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32", LLAMA3_70B, 4096, 4, peak, batch=32),
                                   decode_bench(lib, "Llama-3-70B shape, Q4_K_M mix, 1 GPU, batch 32, fp16 cache", LLAMA3_70B, 4096, 4, peak, batch=32,
                                                kv_f16=True)]

@@ -45,6 +45,11 @@ size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
 /* integer-MMA kernel of gemm_q4k_mma.cu for up to 64 tokens (Q4_K rows, no workspace); -1 when it does not take the call */
 int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
 
+/* From this many sequences a projection runs as one batched product instead of a GEMV per sequence.  The tcgen05 kernel's time
+ * hardly depends on the token count below 32 (it is bound by expanding the weights), so for the Q6_K matrices it wins from about
+ * three sequences: 86 us for the 8192 x 28672 down projection against 36 us per GEMV. */
+#define MODEL_GEMM_MIN_BATCH 4
+
 enum { FMT_Q4K = 0, FMT_Q6K = 1, FMT_Q80 = 2, FMT_Q50 = 3 };
 /* formats with 32-element blocks take Q8_0 activations, the K-quants take Q8_K */
 static int fmt_block32(int fmt) { return fmt == FMT_Q80 || fmt == FMT_Q50; }
@@ -262,7 +267,7 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
     DEV_ALLOC(m->attn_counters, ckb200_attention_decode_counter_bytes(B, m->Hkvl) + 256);
     DEV_ALLOC(m->tokens_dev, (size_t)B * sizeof(int32_t));
     DEV_ALLOC(m->pos_dev, 256);
-    if (B >= 16) {
+    if (B >= MODEL_GEMM_MIN_BATCH) {
         /* largest projection of the step (row counts and input widths as planned above) */
         size_t need = 0;
         const int shapes[][2] = { { m->Hl * m->d, m->Da }, { m->D, m->Ala }, { 2 * m->Il, m->Da }, { m->D, round256(m->Il) }, { m->Vl, m->Da } };
@@ -484,7 +489,6 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
     }
 }
 
-#define MODEL_GEMM_MIN_BATCH 16
 
 /* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
 static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, int y_stride, void *st)

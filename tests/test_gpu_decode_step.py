@@ -29,8 +29,8 @@ def cosine(a, b):
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
 
 
-@pytest.mark.parametrize("cfg,batch,use_graph", [(MINI_QWEN, 1, 1), (MINI_QWEN, 1, 0), (MINI_LLAMA, 2, 1), (MINI_LLAMA, 16, 1),
-                                                 (MINI_Q5_0, 1, 1), (MINI_Q5_0, 1, 0)])   # 16 sequences: tensor-core GEMMs
+@pytest.mark.parametrize("cfg,batch,use_graph", [(MINI_QWEN, 1, 1), (MINI_QWEN, 1, 0), (MINI_LLAMA, 2, 1), (MINI_LLAMA, 16, 1), (MINI_LLAMA, 5, 1),
+                                                 (MINI_LLAMA, 33, 1), (MINI_Q5_0, 1, 1), (MINI_Q5_0, 1, 0)])   # from 4 sequences: tensor-core GEMMs
 def test_decode_steps_match_cpu_step(ck, orc, cfg, batch, use_graph):
     so.bind_model_api(ck)
     ck.ckb200_tune_set(b"model_graph", use_graph)

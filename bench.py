@@ -922,6 +922,41 @@ def run_attention_only(args):
     print(json.dumps({"attention_only": T, "launches": args.launches, "splits": splits, "kv_bytes_per_launch": 2 * Hkv * T * d * 4}))
 
 
+def run_small_gemm_only(args):
+    """Plain launches of gemm_nt_q4_k_q8_k for a handful of tokens (M,N,K): the small case behind profiles/gemm_q4k_mma_*.md, with event timing."""
+    import torch
+
+    lib = pkg.load_lib()
+    assert lib.ckb200_init(0) == 0
+    M, N, K = (int(v) for v in args.small_gemm_only.split(","))
+    dev = torch.device("cuda", 0)
+    nb = K // 256
+    copies = max(1, min(8, int(300e6 // (N * nb * 144))))              # rotate over more than L2 of weights where that stays small
+    W = torch.empty(copies * N * nb * 144, dtype=torch.uint8, device=dev)
+    assert lib.ckb200_dev_fill_blocks(C.c_void_p(W.data_ptr()), C.c_longlong(copies * N * nb), 0, C.c_ulonglong(5), None) == 0
+    x = torch.randn(M, K, device=dev)
+    xq = torch.empty(M * nb * 292, dtype=torch.uint8, device=dev)
+    assert lib.ckb200_dev_quantize_q8_k(C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), M, K, None) == 0
+    out = torch.zeros(M, N, device=dev)
+    lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def launch(i):
+        w = W.data_ptr() + (i % copies) * N * nb * 144
+        assert lib.ckb200_dev_gemm_nt_q4_k_q8_k(C.c_void_p(xq.data_ptr()), C.c_void_p(w), None, C.c_void_p(out.data_ptr()), M, N, K, None) == 0
+
+    for i in range(3):
+        launch(i)
+    e0.record(lstream)
+    for i in range(args.launches):
+        launch(i)
+    e1.record(lstream)
+    assert lib.ckb200_synchronize() == 0
+    us = e0.elapsed_time(e1) / args.launches * 1e3
+    print(json.dumps({"small_gemm_only": [M, N, K], "launches": args.launches, "us_per_launch": us, "weight_bytes": N * nb * 144,
+                      "weights_tb_s": N * nb * 144 / us / 1e6}))
+
+
 def run_decode_only(args):
     """Eager (un-captured) decode steps of a model shape: the command behind the decode launch lists in profiles/."""
     so = pkg.model_api
@@ -958,6 +993,7 @@ def main():
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
     ap.add_argument("--prefill-stack-only", type=int, default=None, metavar="T", help="profiling aid: whole-stack prefill of a T-token prompt, twice")
+    ap.add_argument("--small-gemm-only", default=None, metavar="M,N,K", help="profiling aid: gemm_nt_q4_k_q8_k launches for a few tokens")
     ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
     ap.add_argument("--batch", type=int, default=1, help="sequences per step of --decode-only")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")
@@ -974,6 +1010,8 @@ def main():
         return run_decode_only(args)
     if args.attention_only:
         return run_attention_only(args)
+    if args.small_gemm_only:
+        return run_small_gemm_only(args)
     if args.prefill_only:
         return run_prefill_only(args)
     if args.prefill_stack_only:

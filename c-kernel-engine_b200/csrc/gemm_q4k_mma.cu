@@ -23,6 +23,8 @@
 // A CTA is 8 warps: RT row tiles (16 rows each) x KS slices of K; the slices are added in a fixed order through shared memory, so
 // the result does not depend on timing.  Integer parts are exact; against the reference's per-sub-block fp32 accumulation the
 // result differs by fp32 rounding only (same tolerance as the GEMV).
+#include <cuda.h>
+
 #include "device_common.cuh"
 #include "launch.h"
 #include "pdl.cuh"
@@ -56,6 +58,107 @@ __device__ __forceinline__ void qm4_mma_us(int (&d)[4], const uint32_t (&a)[4], 
 {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(zero));
+}
+
+// One superblock of a warp's 16 RW rows against all token slots.  ws: the warp's row g of its first 16-row tile in shared memory (rows
+// WP bytes apart, raw 144-byte Q4_K blocks); xs: token slot 0 (slots XP bytes apart, raw Q8_K block at xs: fp32 d, 256 quants, 16 int16 sums).
+template <int NT, int RW, int WP, int XP>
+__device__ __forceinline__ void qm4_superblock(const uint8_t *ws, const uint8_t *xs, float (&acc)[RW][NT][4], int g, int t, int zero)
+{
+    // per 16-row tile: rows g and g + 8; 6-bit scales and minima four to a word (include/ckernel_quant.h:227-251)
+    uint32_t scw[RW][2][2], mnw[RW][2][2], dd[RW][2];
+#pragma unroll
+    for (int rw = 0; rw < RW; ++rw)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(ws + (size_t)rw * (16 * WP) + r * 8 * WP);
+            dd[rw][r] = hdr.x;
+            scw[rw][r][0] = hdr.y & 0x3F3F3F3Fu;
+            mnw[rw][r][0] = hdr.z & 0x3F3F3F3Fu;
+            scw[rw][r][1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+            mnw[rw][r][1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+        }
+    int S[RW][NT][4];
+#pragma unroll
+    for (int rw = 0; rw < RW; ++rw)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) S[rw][nt][e] = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint2 q[RW][2];
+#pragma unroll
+        for (int rw = 0; rw < RW; ++rw) {
+            q[rw][0] = *reinterpret_cast<const uint2 *>(ws + (size_t)rw * (16 * WP) + 16 + 32 * c + 8 * t);
+            q[rw][1] = *reinterpret_cast<const uint2 *>(ws + (size_t)rw * (16 * WP) + 8 * WP + 16 + 32 * c + 8 * t);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int j = 2 * c + h;
+            uint32_t a[RW][4];
+            int sc[RW][2];
+#pragma unroll
+            for (int rw = 0; rw < RW; ++rw) {
+                a[rw][0] = (q[rw][0].x >> (4 * h)) & 0x0F0F0F0Fu;
+                a[rw][1] = (q[rw][1].x >> (4 * h)) & 0x0F0F0F0Fu;
+                a[rw][2] = (q[rw][0].y >> (4 * h)) & 0x0F0F0F0Fu;
+                a[rw][3] = (q[rw][1].y >> (4 * h)) & 0x0F0F0F0Fu;
+                sc[rw][0] = (int)__byte_perm(scw[rw][0][j >> 2], 0u, 0x4440u + (j & 3));
+                sc[rw][1] = (int)__byte_perm(scw[rw][1][j >> 2], 0u, 0x4440u + (j & 3));
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t *bp = reinterpret_cast<const uint32_t *>(xs + (size_t)(nt * 8 + g) * XP + 4 + 32 * j + 8 * t);
+                const uint32_t b0 = bp[0], b1 = bp[1];
+#pragma unroll
+                for (int rw = 0; rw < RW; ++rw) {
+                    int cc[4];
+                    qm4_mma_ss(cc, a[rw], b0, b1, zero);
+                    S[rw][nt][0] += sc[rw][0] * cc[0];
+                    S[rw][nt][1] += sc[rw][0] * cc[1];
+                    S[rw][nt][2] += sc[rw][1] * cc[2];
+                    S[rw][nt][3] += sc[rw][1] * cc[3];
+                }
+            }
+        }
+    }
+    // minima: k index i = 0 .. 15 is the 16-element block sum i, which belongs to sub-block i / 2
+    uint32_t am[RW][4];
+    float dw[RW][2], mw[RW][2];
+#pragma unroll
+    for (int rw = 0; rw < RW; ++rw) {
+        const uint32_t sel = (t & 1) ? 0x3322u : 0x1100u;
+        am[rw][0] = __byte_perm((t & 2) ? mnw[rw][0][1] : mnw[rw][0][0], 0u, sel);
+        am[rw][1] = __byte_perm((t & 2) ? mnw[rw][1][1] : mnw[rw][1][0], 0u, sel);
+        am[rw][2] = 0u;
+        am[rw][3] = 0u;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            dw[rw][r] = half_bits_to_float(dd[rw][r] & 0xFFFFu);
+            mw[rw][r] = half_bits_to_float(dd[rw][r] >> 16);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const uint32_t *bsp = reinterpret_cast<const uint32_t *>(xs + (size_t)(nt * 8 + g) * XP + 260 + 8 * t);
+        const uint32_t bs0 = bsp[0], bs1 = bsp[1];
+        const uint32_t lo = __byte_perm(bs0, bs1, 0x6420u), hi = __byte_perm(bs0, bs1, 0x7531u);
+        const float dxa = *reinterpret_cast<const float *>(xs + (size_t)(nt * 8 + 2 * t) * XP);
+        const float dxb = *reinterpret_cast<const float *>(xs + (size_t)(nt * 8 + 2 * t + 1) * XP);
+#pragma unroll
+        for (int rw = 0; rw < RW; ++rw) {
+            int Lo[4], Hi[4];
+            qm4_mma_uu(Lo, am[rw], lo, 0u, zero);
+            qm4_mma_us(Hi, am[rw], hi, 0u, zero);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float d = dw[rw][e >> 1], dm = mw[rw][e >> 1], x = (e & 1) ? dxb : dxa;
+                const int ms = Hi[e] * 256 + Lo[e];
+                acc[rw][nt][e] += __fmul_rn(d, x) * (float)S[rw][nt][e] - __fmul_rn(dm, x) * (float)ms;
+            }
+        }
+    }
 }
 
 template <int NT, int RW, int KS, int D> struct Qm4Smem {
@@ -164,100 +267,7 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_kernel(const uint8_t
         const uint8_t *ws = stage + (size_t)warp * L::WSTAGE + g * QM4_WPITCH;
         const uint8_t *xs = stage + QM4_WARPS * L::WSTAGE + (size_t)ks * L::XSLICE + (x_aligned ? (int)(((size_t)b * Q8K_BYTES) & 15) : 0);
 
-        // per 16-row tile: rows g and g + 8; 6-bit scales and minima four to a word (include/ckernel_quant.h:227-251)
-        uint32_t scw[RW][2][2], mnw[RW][2][2], dd[RW][2];
-#pragma unroll
-        for (int rw = 0; rw < RW; ++rw)
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const uint4 hdr = *reinterpret_cast<const uint4 *>(ws + (size_t)rw * QM4_WTILE + r * 8 * QM4_WPITCH);
-                dd[rw][r] = hdr.x;
-                scw[rw][r][0] = hdr.y & 0x3F3F3F3Fu;
-                mnw[rw][r][0] = hdr.z & 0x3F3F3F3Fu;
-                scw[rw][r][1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-                mnw[rw][r][1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-            }
-        int S[RW][NT][4];
-#pragma unroll
-        for (int rw = 0; rw < RW; ++rw)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) S[rw][nt][e] = 0;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint2 q[RW][2];
-#pragma unroll
-            for (int rw = 0; rw < RW; ++rw) {
-                q[rw][0] = *reinterpret_cast<const uint2 *>(ws + (size_t)rw * QM4_WTILE + 16 + 32 * c + 8 * t);
-                q[rw][1] = *reinterpret_cast<const uint2 *>(ws + (size_t)rw * QM4_WTILE + 8 * QM4_WPITCH + 16 + 32 * c + 8 * t);
-            }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int j = 2 * c + h;
-                uint32_t a[RW][4];
-                int sc[RW][2];
-#pragma unroll
-                for (int rw = 0; rw < RW; ++rw) {
-                    a[rw][0] = (q[rw][0].x >> (4 * h)) & 0x0F0F0F0Fu;
-                    a[rw][1] = (q[rw][1].x >> (4 * h)) & 0x0F0F0F0Fu;
-                    a[rw][2] = (q[rw][0].y >> (4 * h)) & 0x0F0F0F0Fu;
-                    a[rw][3] = (q[rw][1].y >> (4 * h)) & 0x0F0F0F0Fu;
-                    sc[rw][0] = (int)__byte_perm(scw[rw][0][j >> 2], 0u, 0x4440u + (j & 3));
-                    sc[rw][1] = (int)__byte_perm(scw[rw][1][j >> 2], 0u, 0x4440u + (j & 3));
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(xs + (size_t)(nt * 8 + g) * QM4_XPITCH + 4 + 32 * j + 8 * t);
-                    const uint32_t b0 = bp[0], b1 = bp[1];
-#pragma unroll
-                    for (int rw = 0; rw < RW; ++rw) {
-                        int cc[4];
-                        qm4_mma_ss(cc, a[rw], b0, b1, zero);
-                        S[rw][nt][0] += sc[rw][0] * cc[0];
-                        S[rw][nt][1] += sc[rw][0] * cc[1];
-                        S[rw][nt][2] += sc[rw][1] * cc[2];
-                        S[rw][nt][3] += sc[rw][1] * cc[3];
-                    }
-                }
-            }
-        }
-        // minima: k index i = 0 .. 15 is the 16-element block sum i, which belongs to sub-block i / 2
-        uint32_t am[RW][4];
-        float dw[RW][2], mw[RW][2];
-#pragma unroll
-        for (int rw = 0; rw < RW; ++rw) {
-            const uint32_t sel = (t & 1) ? 0x3322u : 0x1100u;
-            am[rw][0] = __byte_perm((t & 2) ? mnw[rw][0][1] : mnw[rw][0][0], 0u, sel);
-            am[rw][1] = __byte_perm((t & 2) ? mnw[rw][1][1] : mnw[rw][1][0], 0u, sel);
-            am[rw][2] = 0u;
-            am[rw][3] = 0u;
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                dw[rw][r] = half_bits_to_float(dd[rw][r] & 0xFFFFu);
-                mw[rw][r] = half_bits_to_float(dd[rw][r] >> 16);
-            }
-        }
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t *bsp = reinterpret_cast<const uint32_t *>(xs + (size_t)(nt * 8 + g) * QM4_XPITCH + 260 + 8 * t);
-            const uint32_t bs0 = bsp[0], bs1 = bsp[1];
-            const uint32_t lo = __byte_perm(bs0, bs1, 0x6420u), hi = __byte_perm(bs0, bs1, 0x7531u);
-            const float dxa = *reinterpret_cast<const float *>(xs + (size_t)(nt * 8 + 2 * t) * QM4_XPITCH);
-            const float dxb = *reinterpret_cast<const float *>(xs + (size_t)(nt * 8 + 2 * t + 1) * QM4_XPITCH);
-#pragma unroll
-            for (int rw = 0; rw < RW; ++rw) {
-                int Lo[4], Hi[4];
-                qm4_mma_uu(Lo, am[rw], lo, 0u, zero);
-                qm4_mma_us(Hi, am[rw], hi, 0u, zero);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float d = dw[rw][e >> 1], dm = mw[rw][e >> 1], x = (e & 1) ? dxb : dxa;
-                    const int ms = Hi[e] * 256 + Lo[e];
-                    acc[rw][nt][e] += __fmul_rn(d, x) * (float)S[rw][nt][e] - __fmul_rn(dm, x) * (float)ms;
-                }
-            }
-        }
+        qm4_superblock<NT, RW, QM4_WPITCH, QM4_XPITCH>(ws, xs, acc, g, t, zero);
     }
     qm4_wait<0>();
     __syncthreads();                                           // the staging area becomes the reduction buffer
@@ -289,6 +299,189 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_kernel(const uint8_t
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// The same product with both operands brought in by the tensor-memory accelerator.  In the kernel above a third of every step went
+// into issuing the step's 16-byte copies (about 2900 requests per CTA and step through the load/store units: measured with clock64,
+// and neither spreading the requests over the step nor a warp of its own for them helped).  Here one thread issues, per step and K
+// slice, ONE tiled copy for the 144-byte blocks of all the slice's rows (a box of 144 bytes x rows out of the matrix seen as
+// N rows of nb * 144 bytes) and one for the 304-byte windows of all tokens; rows past N and token slots past M are filled with
+// zeros by the copy itself.  Completion is counted on an mbarrier per stage; the waits are bounded.  Needs 16-byte-aligned
+// activation rows (K a multiple of 1024), otherwise the kernel above runs.
+constexpr int QM4_XWIN = 16 * QM4_XCOPY;                       // 304 bytes: a 292-byte block from its 16-byte-aligned start
+
+__device__ __forceinline__ void qm4_tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+template <int NT, int RW, int KS, int D> struct Qm4TmaSmem {
+    static constexpr int MT = 8 * NT;
+    static constexpr int ROWS = 16 * RW * (QM4_WARPS / KS);    // rows of one K slice = rows of the CTA
+    static constexpr int WSLICE = ROWS * Q4K_BYTES;            // dense 144-byte rows
+    static constexpr int XSLICE = ((MT * QM4_XWIN + 127) / 128) * 128;
+    static constexpr int STAGE = KS * (WSLICE + XSLICE);
+    static constexpr int BYTES = D * STAGE;
+    static_assert(WSLICE % 128 == 0, "copy destinations stay 128-byte aligned");
+};
+
+template <int NT, int RW, int RT, int KS, int D>
+__global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                                                                       const float *__restrict__ bias, float *__restrict__ C, int ldc, int M, int N, int nb,
+                                                                       int *__restrict__ dev_err)
+{
+    static_assert(RT * KS == QM4_WARPS, "8 warps");
+    using L = Qm4TmaSmem<NT, RW, KS, D>;
+    extern __shared__ __align__(128) uint8_t qm4_smem[];
+    __shared__ __align__(8) uint64_t full[D];
+    const uint32_t s_base = smem_u32(qm4_smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt = warp % RT, ks = warp / RT;
+    const int row0 = blockIdx.x * L::ROWS;                     // first row of the CTA
+    const int per = (nb + KS - 1) / KS;
+    const int b_first = ks * per;
+
+    if (tid == 0) {
+        for (int i = 0; i < D; ++i) mbar_init(smem_u32(&full[i]), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_trigger();
+
+    // thread 0: the copies of step s; weights and activations of a stage complete the same barrier
+    auto expect = [&](int s) {
+        int slices = 0;
+        for (int k = 0; k < KS; ++k) slices += (k * per + s < nb);
+        mbar_arrive_expect_tx(smem_u32(&full[s % D]), (uint32_t)slices * (uint32_t)(L::WSLICE + L::MT * QM4_XWIN));
+    };
+    auto issue_w = [&](int s) {
+        const uint32_t st = s_base + (uint32_t)(s % D) * L::STAGE;
+        for (int k = 0; k < KS; ++k) {
+            const int b = k * per + s;
+            if (b < nb) qm4_tma_2d(st + (uint32_t)k * (L::WSLICE + L::XSLICE), &tm_w, b * Q4K_BYTES, row0, smem_u32(&full[s % D]));
+        }
+    };
+    auto issue_x = [&](int s) {
+        const uint32_t st = s_base + (uint32_t)(s % D) * L::STAGE + L::WSLICE;
+        for (int k = 0; k < KS; ++k) {
+            const int b = k * per + s;
+            // the activation matrix is described in 4-byte elements (a box side is at most 256 elements): window start / 4
+            if (b < nb) qm4_tma_2d(st + (uint32_t)k * (L::WSLICE + L::XSLICE), &tm_x, ((b * Q8K_BYTES) & ~15) / 4, 0, smem_u32(&full[s % D]));
+        }
+    };
+
+    const int zero = 0;
+    float acc[RW][NT][4];
+#pragma unroll
+    for (int rw = 0; rw < RW; ++rw)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[rw][nt][e] = 0.0f;
+
+    if (tid == 0) {
+        for (int s = 0; s < D - 1 && s < per; ++s) { expect(s); issue_w(s); }     // weights are not written by any kernel: before the dependency wait
+    }
+    pdl_wait();
+    if (tid == 0) {
+        for (int s = 0; s < D - 1 && s < per; ++s) issue_x(s);
+    }
+
+    bool ok = true;
+    for (int s = 0; s < per; ++s) {
+        const int b = b_first + s;
+        __syncthreads();                                       // step s - 1 is finished everywhere: its stage may be refilled
+        if (tid == 0 && s + D - 1 < per) { expect(s + D - 1); issue_w(s + D - 1); issue_x(s + D - 1); }
+        if (b >= nb) continue;
+        if (ok && !mbar_wait_spin(smem_u32(&full[s % D]), (uint32_t)(s / D) & 1u)) {
+            ok = false;                                        // keep taking part in the barriers; the host sees the error word
+            if (lane == 0) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
+        }
+        const uint8_t *slice = qm4_smem + (size_t)(s % D) * L::STAGE + (size_t)ks * (L::WSLICE + L::XSLICE);
+        const uint8_t *ws = slice + (size_t)(rt * 16 * RW + g) * Q4K_BYTES;
+        const uint8_t *xs = slice + L::WSLICE + ((b * Q8K_BYTES) & 15);
+        qm4_superblock<NT, RW, Q4K_BYTES, QM4_XWIN>(ws, xs, acc, g, t, zero);
+    }
+    __syncthreads();                                           // the staging area becomes the reduction buffer (every issued copy was waited for)
+
+    float *red = reinterpret_cast<float *>(qm4_smem);
+    constexpr int PER_WARP = RW * NT * 4;
+    if (KS > 1 && ks > 0) {
+#pragma unroll
+        for (int rw = 0; rw < RW; ++rw)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) red[(((size_t)(ks - 1) * RT + rt) * PER_WARP + (rw * NT + nt) * 4 + e) * 32 + lane] = acc[rw][nt][e];
+    }
+    if (KS > 1) __syncthreads();
+    if (ks == 0) {
+        const int n0 = row0 + rt * 16 * RW;
+#pragma unroll
+        for (int rw = 0; rw < RW; ++rw)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = acc[rw][nt][e];
+                    for (int k = 1; k < KS; ++k) v += red[(((size_t)(k - 1) * RT + rt) * PER_WARP + (rw * NT + nt) * 4 + e) * 32 + lane];
+                    const int row = n0 + 16 * rw + g + ((e & 2) ? 8 : 0), tok = nt * 8 + 2 * t + (e & 1);
+                    if (row < N && tok < M) C[(size_t)tok * ldc + row] = bias ? v + bias[row] : v;
+                }
+    }
+}
+
+// Tiled copy descriptors: a matrix of `rows` rows of `row_bytes` bytes (row pitch = row_bytes, a multiple of 16), boxes of box_bytes x box_rows,
+// in elements of `elem` bytes (1 or 4).
+typedef CUresult (*qm4_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static qm4_encode_fn qm4_encoder()
+{
+    static qm4_encode_fn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (qm4_encode_fn)p;
+        else cudaGetLastError();
+    }
+    return fn;
+}
+static bool qm4_make_map(CUtensorMap *map, const void *base, size_t row_bytes, size_t rows, unsigned box_bytes, unsigned box_rows, unsigned elem)
+{
+    qm4_encode_fn enc = qm4_encoder();
+    if (!enc || row_bytes % 16 || box_bytes % 16 || box_bytes / elem > 256 || box_rows > 256) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / elem), (cuuint64_t)rows}, strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {box_bytes / elem, box_rows}, estr[2] = {1, 1};
+    return enc(map, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// -1: this form does not apply (no driver entry point, activations not 16-byte aligned, shared memory)
+template <int NT, int RW, int RT, int KS, int D>
+static int qm4_launch_tma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
+{
+    using L = Qm4TmaSmem<NT, RW, KS, D>;
+    static_assert((KS - 1) * RT * RW * NT * 4 * 32 * 4 <= L::BYTES, "the reduction buffer fits into the staging area");
+    static_assert(L::BYTES <= 226 * 1024, "shared memory");
+    static_assert(L::ROWS <= 256 && L::MT <= 256 && QM4_XWIN / 4 <= 256 && Q4K_BYTES <= 256, "box limits");
+    if (((uintptr_t)A_q8 & 15) || nb % 4 || ((uintptr_t)B & 15)) return -1;
+    CUtensorMap tm_w, tm_x;
+    if (!qm4_make_map(&tm_w, B, (size_t)nb * Q4K_BYTES, (size_t)N, Q4K_BYTES, L::ROWS, 1)) return -1;
+    if (!qm4_make_map(&tm_x, A_q8, (size_t)nb * Q8K_BYTES, (size_t)M, QM4_XWIN, L::MT, 4)) return -1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_q4k_mma_tma_kernel<NT, RW, RT, KS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES), "gemm_q4k_mma smem"))
+            return CKB_ERR_CUDA;
+        attr_set = true;
+    }
+    const int grid = (N + L::ROWS - 1) / L::ROWS;
+    return launch_pdl("gemm_q4k_mma_tma", gemm_q4k_mma_tma_kernel<NT, RW, RT, KS, D>, dim3(grid), dim3(QM4_THREADS), (size_t)L::BYTES, st, tm_w, tm_x, bias, C, ldc, M, N,
+                      nb, ckb_device_error_word());
+}
+
 template <int NT, int RW, int RT, int KS, int D>
 static int qm4_launch(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
 {
@@ -314,6 +507,16 @@ static int qm4_shape(int shape, const void *A_q8, const void *B, const float *bi
     constexpr int per_stage1 = QM4_WARPS * RW * QM4_WTILE + 8 * NT * QM4_XPITCH, per_stage2 = per_stage1 + 8 * NT * QM4_XPITCH, per_stage4 = per_stage2 + 2 * 8 * NT * QM4_XPITCH;
     constexpr int D1 = 4 * per_stage1 <= 227 * 1024 ? 4 : (3 * per_stage1 <= 227 * 1024 ? 3 : 2), D2 = 4 * per_stage2 <= 227 * 1024 ? 4 : (3 * per_stage2 <= 227 * 1024 ? 3 : 2);
     constexpr int D4 = 4 * per_stage4 <= 227 * 1024 ? 4 : (3 * per_stage4 <= 227 * 1024 ? 3 : 2);
+    if (ckb_tune_get("gemm_q4k_mma_tma", 1)) {
+        // stages of the tiled-copy form: dense rows, so more of them fit
+        constexpr int w1 = QM4_WARPS * 16 * RW * Q4K_BYTES;
+        constexpr int t1 = w1 + Qm4TmaSmem<NT, RW, 1, 1>::XSLICE, t2 = w1 + 2 * Qm4TmaSmem<NT, RW, 2, 1>::XSLICE, t4 = w1 + 4 * Qm4TmaSmem<NT, RW, 4, 1>::XSLICE;
+        constexpr int T1 = 4 * t1 <= 226 * 1024 ? 4 : 3, T2 = 4 * t2 <= 226 * 1024 ? 4 : 3, T4 = 4 * t4 <= 226 * 1024 ? 4 : (3 * t4 <= 226 * 1024 ? 3 : 2);
+        const int rc = shape == 1 ? qm4_launch_tma<NT, RW, 8, 1, T1>(A_q8, B, bias, C, ldc, M, N, nb, st)
+                                  : (shape == 2 ? qm4_launch_tma<NT, RW, 4, 2, T2>(A_q8, B, bias, C, ldc, M, N, nb, st)
+                                                : qm4_launch_tma<NT, RW, 2, 4, T4>(A_q8, B, bias, C, ldc, M, N, nb, st));
+        if (rc >= 0) return rc;
+    }
     if (shape == 1) return qm4_launch<NT, RW, 8, 1, D1>(A_q8, B, bias, C, ldc, M, N, nb, st);
     if (shape == 2) return qm4_launch<NT, RW, 4, 2, D2>(A_q8, B, bias, C, ldc, M, N, nb, st);
     return qm4_launch<NT, RW, 2, 4, D4>(A_q8, B, bias, C, ldc, M, N, nb, st);

@@ -226,14 +226,16 @@ def test_gemm_nt_q4_k_tensor_core(ck, orc, m, n, k, with_bias):
     assert_fp32_close(by_rows, want, "q4_k per-token path")
 
 
+@pytest.mark.parametrize("tma", [1, 0])
 @pytest.mark.parametrize("shape,rw", [(1, 2), (2, 2), (4, 2), (1, 1), (4, 1)])
 @pytest.mark.parametrize("m,n,k", [(16, 128, 256), (1, 40, 512), (8, 129, 1024), (9, 64, 2048), (17, 300, 1280), (32, 1000, 4096), (33, 77, 768), (64, 260, 2560)])
-def test_gemm_nt_q4_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
+def test_gemm_nt_q4_k_integer_mma_small_batches(ck, orc, tma, shape, rw, m, n, k):
     """Up to 64 tokens gemm_nt_q4_k_q8_k runs on the integer-MMA kernel that streams the weights through registers: all four token-tile
     counts (8, 16, 32, 64 slots) with ragged token and row counts, the three CTA shapes (8 row warps, 4 x 2 K slices, 2 x 4 K slices;
     superblock counts that do not divide by the slices, a slice without work for k = 256), one and two 16-row tiles per warp, and both
-    ways of staging the activations (16-byte windows when K is a multiple of 1024, 4-byte copies otherwise).  The integer sums are
-    exact, the slices are added in a fixed order: two runs agree bit for bit."""
+    ways of staging the activations (16-byte windows when K is a multiple of 1024, 4-byte copies otherwise); with tma = 1 the shapes
+    whose K is a multiple of 1024 take the form fed by tiled bulk copies (rows past N and token slots past M are zero-filled by the
+    copy).  The integer sums are exact, the slices are added in a fixed order: two runs agree bit for bit."""
     w = synth.make_weights("q4_k", n, k, seed=m + n)
     a = synth.make_x(k, seed=m, rows=m)
     aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
@@ -243,6 +245,7 @@ def test_gemm_nt_q4_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
         ck.ckb200_tune_set(b"gemm_q4k_mma_min", 1)
         ck.ckb200_tune_set(b"gemm_q4k_mma_shape", shape)
         ck.ckb200_tune_set(b"gemm_q4k_mma_rw", rw)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_tma", tma)
         ck.ckb200_launch_count.restype = C.c_longlong
         n0 = ck.ckb200_launch_count()
         got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
@@ -252,6 +255,7 @@ def test_gemm_nt_q4_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
         ck.ckb200_tune_set(b"gemm_q4k_mma_min", 4)
         ck.ckb200_tune_set(b"gemm_q4k_mma_shape", 0)
         ck.ckb200_tune_set(b"gemm_q4k_mma_rw", 0)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_tma", 1)
     assert_fp32_close(got, want, "q4_k integer-MMA path")
     assert np.array_equal(got, again)
 

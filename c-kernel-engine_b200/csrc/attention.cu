@@ -321,6 +321,7 @@ static int g_attn_early_rows = 0;
 extern "C" void ckb_attn_hint_early_rows(int on) { g_attn_early_rows = on; }
 
 extern "C" int ckb_launch_attn_tile(const AttnParams *p, int batch, void *stream);
+extern "C" int ckb_launch_attn_f16mma(const AttnParams *p, int batch, void *stream);
 extern "C" int ckb_launch_attn_cluster(const AttnParams *p, int batch, int ranks, void *stream);     // attention_tile.cu
 
 extern "C" size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits)
@@ -493,7 +494,8 @@ extern "C" int ckb200_dev_attention_decode_f16cache_ws(const float *q, const uin
     p.splits = splits;
     p.counters = NULL; p.q8_out = NULL; p.out_stride = num_heads * aligned_head_dim; p.q8_cols = 0; p.kv_f16 = 1; p.early_rows = 0;
     cudaStream_t st = ckb_stream(stream);
-    const int rc = ckb_launch_attn_tile(&p, batch, st);
+    int rc = ckb_launch_attn_f16mma(&p, batch, st);           // tensor-core form (attention_f16mma.cu); -1: not for this call
+    if (rc < 0) rc = ckb_launch_attn_tile(&p, batch, st);
     if (rc) return rc;
     if (splits > 1)
         return launch_pdl("attn_merge", attn_merge_kernel, dim3(batch * num_heads), dim3(128), 0, st, (const float *)scratch, out, splits, aligned_head_dim);

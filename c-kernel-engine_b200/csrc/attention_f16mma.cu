@@ -60,7 +60,7 @@ __device__ __forceinline__ uint32_t fm_swz(int r, int c) { return (uint32_t)(r *
 
 template <int AD>
 __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, AttnParams p,
-                                                                    int *__restrict__ dev_err)
+                                                                    int *__restrict__ dev_err, int early_trigger)
 {
     constexpr int BOXES = AD / 64;                             // 64 halves = 128 bytes of a row per box
     constexpr int BOX_BYTES = FM_TILE * 128;                   // 8 KB
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid
         mbar_fence_init();
     }
     __syncthreads();
-    pdl_trigger();
+    if (early_trigger) pdl_trigger();
     pdl_wait();                                                // q and the newest cache row come from the kernels before this one
 
     const int T = attn_kv_tokens(p);
@@ -207,6 +207,9 @@ __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid
         }
     }
     __syncthreads();                                           // all copies have landed and been used: the stages become the merge buffer
+    // The kernels behind this one start now, not earlier: this kernel fills the shared memory of every SM it runs on, so dependents
+    // that were launched early could not become resident beside it and would only queue in front of its own remaining CTAs.
+    if (!early_trigger) pdl_trigger();
 
     // merge the four warps: [warp][head][AD + 2] floats (output, maximum, sum)
     float *mg = reinterpret_cast<float *>(fm_smem);
@@ -287,7 +290,13 @@ static int fm_launch(const AttnParams *p, int batch, const CUtensorMap &tk, cons
         if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_f16mma_kernel<AD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attn_f16mma smem")) return CKB_ERR_CUDA;
         attr_set = true;
     }
-    return launch_pdl("attn_f16mma", attn_f16mma_kernel<AD>, dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st, tk, tv, *p, ckb_device_error_word());
+    const int mode = ckb_tune_get("attn_f16_mma_pdl", 1);      // 1: programmatic dependent launch, trigger after the key loop; 2: trigger at the start; 0: plain launch
+    if (mode == 0) {
+        attn_f16mma_kernel<AD><<<dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st>>>(tk, tv, *p, ckb_device_error_word(), 0);
+        return ckb_check_launch("attn_f16mma");
+    }
+    return launch_pdl("attn_f16mma", attn_f16mma_kernel<AD>, dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st, tk, tv, *p, ckb_device_error_word(),
+                      mode == 2 ? 1 : 0);
 }
 
 }  // namespace ckb
@@ -298,7 +307,10 @@ using namespace ckb;
 // Returns -1 when this kernel does not take the call: the caller runs the tile kernel.
 extern "C" int ckb_launch_attn_f16mma(const AttnParams *p, int batch, void *stream)
 {
-    if (!ckb_tune_get("attn_f16_mma", 1) || (p->ad != 64 && p->ad != 128) || p->H % p->Hkv || p->H / p->Hkv > 8) return -1;
+    // One sequence stays with the tile kernel: inside a decode step it is the faster of the two there (11.5 against 11.9 ms per token on
+    // the 70B shape: it fetches the older cache rows before its predecessor has finished), from a few sequences up this one wins clearly.
+    if (!ckb_tune_get("attn_f16_mma", 1) || batch < ckb_tune_get("attn_f16_mma_min_batch", 2)) return -1;
+    if ((p->ad != 64 && p->ad != 128) || p->H % p->Hkv || p->H / p->Hkv > 8) return -1;
     if ((((uintptr_t)p->k | (uintptr_t)p->v) & 15) || (p->kv_batch_stride % 8) || ((uintptr_t)p->q & 7) || p->counters || p->q8_out) return -1;
     const long long rows = (long long)p->Hkv * p->cap;
     if (batch > 1 && rows * p->ad > p->kv_batch_stride) return -1;

@@ -353,18 +353,31 @@ def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
         assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
 
 
+@pytest.mark.parametrize("tensor_cores", [0, 1])
 @pytest.mark.parametrize("heads,kvh,d,tokens,cap", [(14, 2, 64, 1025, 2048), (64, 8, 128, 4096, 4096), (8, 4, 64, 64, 64), (4, 4, 64, 1, 16),
-                                                    (6, 2, 128, 5, 8), (16, 2, 128, 333, 512)])
-def test_attention_decode_f16_cache(ck, orc, heads, kvh, d, tokens, cap):
-    """Decode attention over an IEEE fp16 KV cache (half the bytes), every split count, against the oracle."""
+                                                    (6, 2, 128, 5, 8), (16, 2, 128, 333, 512), (8, 1, 128, 130, 131)])
+def test_attention_decode_f16_cache(ck, orc, tensor_cores, heads, kvh, d, tokens, cap):
+    """Decode attention over an IEEE fp16 KV cache (half the bytes), every split count, against the oracle: the tile kernel that widens
+    the cache to fp32, and the tensor-core kernel (query and probabilities split into two fp16 pieces) that batches of sequences get;
+    cache rows past the context hold infinities and NaNs, which must not reach the result."""
     q, kc, vc = cases.attention_inputs(tokens + heads, heads, kvh, d, tokens, cap)
     kc16, vc16 = kc.astype(np.float16).view(np.uint16), vc.astype(np.float16).view(np.uint16)
+    kc16[:, tokens:] = 0x7C00                                   # +inf
+    vc16[:, tokens:] = 0x7E00                                   # NaN
     want = cases.attention_decode_f16cache(orc, "oracle_", q, kc16, vc16, tokens)
-    for splits in (0, 1, 3, 16):
-        ck.ckb200_tune_set(b"attn_splits", splits)
-        got = cases.attention_decode_f16cache(ck, "", q, kc16, vc16, tokens)
+    assert np.isfinite(want).all()
+    try:
+        ck.ckb200_tune_set(b"attn_f16_mma", tensor_cores)
+        ck.ckb200_tune_set(b"attn_f16_mma_min_batch", 1)
+        for splits in (0, 1, 3, 16):
+            ck.ckb200_tune_set(b"attn_splits", splits)
+            got = cases.attention_decode_f16cache(ck, "", q, kc16, vc16, tokens)
+            ck.ckb200_tune_set(b"attn_splits", 0)
+            assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+    finally:
         ck.ckb200_tune_set(b"attn_splits", 0)
-        assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+        ck.ckb200_tune_set(b"attn_f16_mma", 1)
+        ck.ckb200_tune_set(b"attn_f16_mma_min_batch", 2)
 
 
 def test_kv_cache_store_f16_bit_exact_then_attend(ck, orc):

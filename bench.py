@@ -920,6 +920,37 @@ def run_attention_only(args):
                                                      H, Hkv, T, cap, d, d, None, None) == 0
     assert lib.ckb200_synchronize() == 0
     print(json.dumps({"attention_only": T, "launches": args.launches, "splits": splits, "kv_bytes_per_launch": 2 * Hkv * T * d * 4}))
+    if args.batch > 1:
+        # the same shape for --batch sequences over IEEE fp16 caches (the tensor-core kernel), timed with events
+        B = args.batch
+        del kc, vc
+        q = torch.randn(B, H, d, device=dev)
+        out = torch.empty_like(q)
+        kc16 = torch.randn(2, B, Hkv, cap, d, device=dev, dtype=torch.float16)
+        vc16 = torch.randn(2, B, Hkv, cap, d, device=dev, dtype=torch.float16)
+        splits = lib.ckb200_attention_decode_splits(B, Hkv, T)
+        scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(B, H, d, splits)) // 4, device=dev)
+        lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+
+        def launch16(i):
+            l = i % 2
+            assert lib.ckb200_dev_attention_decode_f16cache_ws(C.c_void_p(q.data_ptr()), C.c_void_p(kc16[l].data_ptr()), C.c_void_p(vc16[l].data_ptr()),
+                                                               C.c_void_p(out.data_ptr()), B, C.c_longlong(Hkv * cap * d), H, Hkv, T, cap, d, d, splits,
+                                                               C.c_void_p(scratch.data_ptr()), None, None) == 0
+
+        for i in range(2):
+            launch16(i)
+        e0.record(lstream)
+        for i in range(args.launches):
+            launch16(i)
+        e1.record(lstream)
+        assert lib.ckb200_synchronize() == 0
+        us = e0.elapsed_time(e1) / args.launches * 1e3
+        kv_bytes = 2 * B * Hkv * T * d * 2
+        print(json.dumps({"attention_only": T, "batch": B, "kv_cache": "fp16", "launches": args.launches, "splits": splits, "us_per_launch": us,
+                          "kv_bytes_per_launch": kv_bytes, "tb_s": kv_bytes / us / 1e6}))
 
 
 def run_small_gemm_only(args):

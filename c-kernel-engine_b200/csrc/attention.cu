@@ -381,8 +381,9 @@ extern "C" int ckb200_dev_attention_decode_ws(const float *q, const float *k_cac
     if (splits > 1 && !scratch) return ckb_fail(CKB_ERR_STATE, "attention decode: %d splits need a scratch buffer", splits);
     p.splits = splits;
     const dim3 grid(splits, num_kv_heads, batch);
-    int rc;
-    if (ckb_tune_get("attn_tile", 1))
+    int rc = ckb_launch_attn_f16mma(&p, batch, st);           // batches of sequences: the tensor-core form (attention_f16mma.cu); -1: not for this call
+    if (rc >= 0) {
+    } else if (ckb_tune_get("attn_tile", 1))
         rc = ckb_launch_attn_tile(&p, batch, st);
     else
         rc = aligned_head_dim == 64 ? launch_pdl("attn_decode", attn_decode_kernel<64>, grid, dim3(ATTN_NW * 32), 0, st, p)

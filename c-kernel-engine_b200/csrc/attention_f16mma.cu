@@ -14,6 +14,11 @@
 // a 3-d tensor ad x rows x sequences), fragments by ldmatrix (transposed for the values); each of the four warps takes 16 keys of the
 // tile with its own running maximum and sum, the warps and then the splits are merged exactly (log-sum-exp) as in the fp32 path.
 // CTA per (split, kv head, sequence), three stages of 32 KB, two CTAs per SM.  Waits on the copies are bounded.
+//
+// The same kernel serves fp32 caches (F32 = true): a key or value element is split into two fp16 pieces like the query, k = k_hi + k_lo,
+// when a lane builds its B fragment from the fp32 tile, and every product takes two instructions (A x hi, A x lo) - twice the
+// tensor-core work and some conversions, which still fit under the time HBM needs for twice the bytes.  fp16's range applies to
+// the pieces: cache values of magnitude 65504 or more are not supported by this form (the tile kernel of attention_tile.cu is).
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -58,11 +63,11 @@ __device__ __forceinline__ void fm_split2(float a, float b, uint32_t &hi, uint32
 // byte offset of the 16-byte chunk (row r, chunk c) in a 128-byte-swizzled box of 128-byte rows
 __device__ __forceinline__ uint32_t fm_swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
-template <int AD>
-__global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, AttnParams p,
+template <int AD, bool F32>
+__global__ void __launch_bounds__(FM_THREADS, F32 ? 1 : 2) attn_f16mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, AttnParams p,
                                                                     int *__restrict__ dev_err, int early_trigger)
 {
-    constexpr int BOXES = AD / 64;                             // 64 halves = 128 bytes of a row per box
+    constexpr int BOXES = F32 ? AD / 32 : AD / 64;             // 128 bytes of a row per box: 64 halves or 32 floats
     constexpr int BOX_BYTES = FM_TILE * 128;                   // 8 KB
     constexpr int STAGE = 2 * BOXES * BOX_BYTES;               // K boxes, then V boxes
     constexpr int KS = AD / 16, NTD = AD / 8;
@@ -93,8 +98,8 @@ __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid
         mbar_arrive_expect_tx(bar, STAGE);
 #pragma unroll
         for (int x = 0; x < BOXES; ++x) {
-            fm_tma_3d(st + x * BOX_BYTES, &tm_k, 64 * x, row, b, bar);
-            fm_tma_3d(st + (BOXES + x) * BOX_BYTES, &tm_v, 64 * x, row, b, bar);
+            fm_tma_3d(st + x * BOX_BYTES, &tm_k, (F32 ? 32 : 64) * x, row, b, bar);
+            fm_tma_3d(st + (BOXES + x) * BOX_BYTES, &tm_v, (F32 ? 32 : 64) * x, row, b, bar);
         }
     };
     if (tid == 0)
@@ -154,12 +159,28 @@ __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid
             for (int e = 0; e < 4; ++e) s[n][e] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            // matrices: (keys 0-7, d chunk 2ks), (keys 0-7, chunk 2ks + 1), (keys 8-15, chunk 2ks), (keys 8-15, chunk 2ks + 1)
-            const int r = 16 * warp + (mi >> 1) * 8 + rr, chunk = 2 * ks + (mi & 1);
-            uint32_t kb[4];
-            fm_ldmatrix(kb, st + (chunk >> 3) * BOX_BYTES + fm_swz(r, chunk & 7));
-            fm_mma(s[0], aq[ks], kb[0], kb[1]);
-            fm_mma(s[1], aq[ks], kb[2], kb[3]);
+            if constexpr (F32) {
+                // lane (g, t) of key tile n: key 8n + g, elements 16ks + 2t, + 1 (b0) and + 8, + 9 (b1): two 8-byte loads, split into pieces
+                const uint8_t *tile = fm_smem + (size_t)(i % FM_STAGES) * STAGE;
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    const int r = 16 * warp + 8 * n + g, f0 = 16 * ks + 2 * t, f1 = f0 + 8;
+                    const float2 k0 = *reinterpret_cast<const float2 *>(tile + (f0 >> 5) * BOX_BYTES + fm_swz(r, (f0 & 31) >> 2) + (f0 & 3) * 4);
+                    const float2 k1 = *reinterpret_cast<const float2 *>(tile + (f1 >> 5) * BOX_BYTES + fm_swz(r, (f1 & 31) >> 2) + (f1 & 3) * 4);
+                    uint32_t h0, l0, h1, l1;
+                    fm_split2(k0.x, k0.y, h0, l0);
+                    fm_split2(k1.x, k1.y, h1, l1);
+                    fm_mma(s[n], aq[ks], h0, h1);
+                    fm_mma(s[n], aq[ks], l0, l1);
+                }
+            } else {
+                // matrices: (keys 0-7, d chunk 2ks), (keys 0-7, chunk 2ks + 1), (keys 8-15, chunk 2ks), (keys 8-15, chunk 2ks + 1)
+                const int r = 16 * warp + (mi >> 1) * 8 + rr, chunk = 2 * ks + (mi & 1);
+                uint32_t kb[4];
+                fm_ldmatrix(kb, st + (chunk >> 3) * BOX_BYTES + fm_swz(r, chunk & 7));
+                fm_mma(s[0], aq[ks], kb[0], kb[1]);
+                fm_mma(s[1], aq[ks], kb[2], kb[3]);
+            }
         }
         float sc[2][2];
         float mt = -INFINITY;
@@ -196,14 +217,32 @@ __global__ void __launch_bounds__(FM_THREADS, 2) attn_f16mma_kernel(const __grid
         uint32_t ap[4];
         fm_split2(pr[0][0] * FM_PSCALE, pr[0][1] * FM_PSCALE, ap[0], ap[1]);
         fm_split2(pr[1][0] * FM_PSCALE, pr[1][1] * FM_PSCALE, ap[2], ap[3]);
+        if constexpr (F32) {
+            // lane (g, t) of output tile n: element 8n + g of keys 2t, 2t + 1 (b0) and 2t + 8, 2t + 9 (b1): four 4-byte loads, no bank conflicts
+            const uint8_t *tile = fm_smem + (size_t)(i % FM_STAGES) * STAGE + BOXES * BOX_BYTES;
 #pragma unroll
-        for (int n2 = 0; n2 < NTD / 2; ++n2) {
-            // transposed matrices: (keys 0-7, d chunk 2 n2), (keys 8-15, same chunk), (keys 0-7, chunk 2 n2 + 1), (keys 8-15, chunk 2 n2 + 1)
-            const int r = 16 * warp + (mi & 1) * 8 + rr, chunk = 2 * n2 + (mi >> 1);
-            uint32_t vb[4];
-            fm_ldmatrix_t(vb, st + (BOXES + (chunk >> 3)) * BOX_BYTES + fm_swz(r, chunk & 7));
-            fm_mma(o[2 * n2], ap, vb[0], vb[1]);
-            fm_mma(o[2 * n2 + 1], ap, vb[2], vb[3]);
+            for (int n = 0; n < NTD; ++n) {
+                const int f = 8 * n + g, r = 16 * warp + 2 * t;
+                const uint8_t *col = tile + (f >> 5) * BOX_BYTES + (f & 3) * 4;
+                const int c = (f & 31) >> 2;
+                const float v0 = *reinterpret_cast<const float *>(col + fm_swz(r, c)), v1 = *reinterpret_cast<const float *>(col + fm_swz(r + 1, c));
+                const float v2 = *reinterpret_cast<const float *>(col + fm_swz(r + 8, c)), v3 = *reinterpret_cast<const float *>(col + fm_swz(r + 9, c));
+                uint32_t h0, l0, h1, l1;
+                fm_split2(v0, v1, h0, l0);
+                fm_split2(v2, v3, h1, l1);
+                fm_mma(o[n], ap, h0, h1);
+                fm_mma(o[n], ap, l0, l1);
+            }
+        } else {
+#pragma unroll
+            for (int n2 = 0; n2 < NTD / 2; ++n2) {
+                // transposed matrices: (keys 0-7, d chunk 2 n2), (keys 8-15, same chunk), (keys 0-7, chunk 2 n2 + 1), (keys 8-15, chunk 2 n2 + 1)
+                const int r = 16 * warp + (mi & 1) * 8 + rr, chunk = 2 * n2 + (mi >> 1);
+                uint32_t vb[4];
+                fm_ldmatrix_t(vb, st + (BOXES + (chunk >> 3)) * BOX_BYTES + fm_swz(r, chunk & 7));
+                fm_mma(o[2 * n2], ap, vb[0], vb[1]);
+                fm_mma(o[2 * n2 + 1], ap, vb[2], vb[3]);
+            }
         }
     }
     __syncthreads();                                           // all copies have landed and been used: the stages become the merge buffer
@@ -268,34 +307,35 @@ static fm_encode_fn fm_encoder()
     }
     return fn;
 }
-// a cache [batch][Hkv * cap rows][ad] of fp16 with `batch_stride` elements between sequences: boxes of 64 elements x 64 rows, 128-byte swizzle
-static bool fm_make_map(CUtensorMap *map, const void *base, int ad, long long rows, int batch, long long batch_stride)
+// a cache [batch][Hkv * cap rows][ad] of `eb`-byte elements with `batch_stride` elements between sequences: boxes of 128 bytes x 64 rows, 128-byte swizzle
+static bool fm_make_map(CUtensorMap *map, const void *base, int ad, long long rows, int batch, long long batch_stride, int eb)
 {
     fm_encode_fn enc = fm_encoder();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)ad, (cuuint64_t)rows, (cuuint64_t)batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)ad * 2, (cuuint64_t)batch_stride * 2};
-    const cuuint32_t box[3] = {64, FM_TILE, 1}, estr[3] = {1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    const cuuint64_t strides[2] = {(cuuint64_t)ad * eb, (cuuint64_t)batch_stride * eb};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / eb), FM_TILE, 1}, estr[3] = {1, 1, 1};
+    return enc(map, eb == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int AD>
+template <int AD, bool F32>
 static int fm_launch(const AttnParams *p, int batch, const CUtensorMap &tk, const CUtensorMap &tv, cudaStream_t st)
 {
-    constexpr int stages = FM_STAGES * 2 * (AD / 64) * FM_TILE * 128, smem = stages + 1024;
+    constexpr int stages = FM_STAGES * 2 * (F32 ? AD / 32 : AD / 64) * FM_TILE * 128, smem = stages + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory");
     static_assert(FM_WARPS * 8 * (AD + 2) * 4 <= stages, "the merge buffer fits into the stages");
     static bool attr_set = false;
     if (!attr_set) {
-        if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_f16mma_kernel<AD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attn_f16mma smem")) return CKB_ERR_CUDA;
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(attn_f16mma_kernel<AD, F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attn_f16mma smem")) return CKB_ERR_CUDA;
         attr_set = true;
     }
     const int mode = ckb_tune_get("attn_f16_mma_pdl", 1);      // 1: programmatic dependent launch, trigger after the key loop; 2: trigger at the start; 0: plain launch
     if (mode == 0) {
-        attn_f16mma_kernel<AD><<<dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st>>>(tk, tv, *p, ckb_device_error_word(), 0);
+        attn_f16mma_kernel<AD, F32><<<dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st>>>(tk, tv, *p, ckb_device_error_word(), 0);
         return ckb_check_launch("attn_f16mma");
     }
-    return launch_pdl("attn_f16mma", attn_f16mma_kernel<AD>, dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st, tk, tv, *p, ckb_device_error_word(),
+    return launch_pdl("attn_f16mma", attn_f16mma_kernel<AD, F32>, dim3(p->splits, p->Hkv, batch), dim3(FM_THREADS), (size_t)smem, st, tk, tv, *p, ckb_device_error_word(),
                       mode == 2 ? 1 : 0);
 }
 
@@ -303,20 +343,22 @@ static int fm_launch(const AttnParams *p, int batch, const CUtensorMap &tk, cons
 
 using namespace ckb;
 
-// p as for the tile kernel with kv_f16 = 1 (k and v point at fp16 data, kv_batch_stride in elements, part sized for p->splits).
+// p as for the tile kernel (with kv_f16 = 1: k and v point at fp16 data; kv_batch_stride in elements; part sized for p->splits).
 // Returns -1 when this kernel does not take the call: the caller runs the tile kernel.
 extern "C" int ckb_launch_attn_f16mma(const AttnParams *p, int batch, void *stream)
 {
     // One sequence stays with the tile kernel: inside a decode step it is the faster of the two there (11.5 against 11.9 ms per token on
     // the 70B shape: it fetches the older cache rows before its predecessor has finished), from a few sequences up this one wins clearly.
-    if (!ckb_tune_get("attn_f16_mma", 1) || batch < ckb_tune_get("attn_f16_mma_min_batch", 2)) return -1;
+    const int eb = p->kv_f16 ? 2 : 4;
+    if (!ckb_tune_get(p->kv_f16 ? "attn_f16_mma" : "attn_f32_mma", 1) || batch < ckb_tune_get("attn_f16_mma_min_batch", 2)) return -1;
     if ((p->ad != 64 && p->ad != 128) || p->H % p->Hkv || p->H / p->Hkv > 8) return -1;
-    if ((((uintptr_t)p->k | (uintptr_t)p->v) & 15) || (p->kv_batch_stride % 8) || ((uintptr_t)p->q & 7) || p->counters || p->q8_out) return -1;
+    if ((((uintptr_t)p->k | (uintptr_t)p->v) & 15) || (p->kv_batch_stride * eb) % 16 || ((uintptr_t)p->q & 7) || p->counters || p->q8_out) return -1;
     const long long rows = (long long)p->Hkv * p->cap;
     if (batch > 1 && rows * p->ad > p->kv_batch_stride) return -1;
     const long long stride = batch > 1 ? p->kv_batch_stride : rows * p->ad;
     CUtensorMap tk, tv;
-    if (!fm_make_map(&tk, p->k, p->ad, rows, batch, stride) || !fm_make_map(&tv, p->v, p->ad, rows, batch, stride)) return -1;
+    if (!fm_make_map(&tk, p->k, p->ad, rows, batch, stride, eb) || !fm_make_map(&tv, p->v, p->ad, rows, batch, stride, eb)) return -1;
     cudaStream_t st = ckb_stream(stream);
-    return p->ad == 64 ? fm_launch<64>(p, batch, tk, tv, st) : fm_launch<128>(p, batch, tk, tv, st);
+    if (p->kv_f16) return p->ad == 64 ? fm_launch<64, false>(p, batch, tk, tv, st) : fm_launch<128, false>(p, batch, tk, tv, st);
+    return p->ad == 64 ? fm_launch<64, true>(p, batch, tk, tv, st) : fm_launch<128, true>(p, batch, tk, tv, st);
 }

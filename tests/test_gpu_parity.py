@@ -330,13 +330,21 @@ ATTN_CASES = [  # heads, kv_heads, d(aligned), head_dim, tokens, capacity
 ]
 
 
+@pytest.mark.parametrize("tensor_cores", [0, 1])
 @pytest.mark.parametrize("heads,kvh,ad,hd,tokens,cap", ATTN_CASES)
-def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
+def test_attention_decode(ck, orc, tensor_cores, heads, kvh, ad, hd, tokens, cap):
+    """tensor_cores = 1 also sends a single sequence to the kernel that batches of sequences get (keys, values, query and probabilities
+    split into fp16 pieces on the tensor cores; shapes outside it fall through to the same kernels as with 0).  Cache rows past the
+    context hold infinities and NaNs."""
     q, kc, vc = cases.attention_inputs(tokens + heads, heads, kvh, ad, tokens, cap)
     if hd < ad:
         q[:, hd:] = 0
         kc[:, :, hd:] = 0
         vc[:, :, hd:] = 0
+    kc[:, tokens:] = np.inf
+    vc[:, tokens:] = np.nan
+    ck.ckb200_tune_set(b"attn_f32_mma", tensor_cores)
+    ck.ckb200_tune_set(b"attn_f16_mma_min_batch", 1 if tensor_cores else 2)
 
     def run(lib, prefix):
         out = np.full((heads, ad), np.nan, dtype=np.float32)
@@ -346,11 +354,16 @@ def test_attention_decode(ck, orc, heads, kvh, ad, hd, tokens, cap):
         return out
 
     want = run(orc, "oracle_")
-    for splits in (0, 1, 3, 16):
-        ck.ckb200_tune_set(b"attn_splits", splits)
-        got = run(ck, "")
+    try:
+        for splits in (0, 1, 3, 16):
+            ck.ckb200_tune_set(b"attn_splits", splits)
+            got = run(ck, "")
+            ck.ckb200_tune_set(b"attn_splits", 0)
+            assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+    finally:
         ck.ckb200_tune_set(b"attn_splits", 0)
-        assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, (splits, float(np.max(np.abs(got - want))))
+        ck.ckb200_tune_set(b"attn_f32_mma", 1)
+        ck.ckb200_tune_set(b"attn_f16_mma_min_batch", 2)
 
 
 @pytest.mark.parametrize("tensor_cores", [0, 1])

@@ -951,6 +951,28 @@ def run_attention_only(args):
         kv_bytes = 2 * B * Hkv * T * d * 2
         print(json.dumps({"attention_only": T, "batch": B, "kv_cache": "fp16", "launches": args.launches, "splits": splits, "us_per_launch": us,
                           "kv_bytes_per_launch": kv_bytes, "tb_s": kv_bytes / us / 1e6}))
+        # and over fp32 caches (keys and values split into fp16 pieces in the kernel)
+        del kc16, vc16
+        kc32 = torch.randn(2, B, Hkv, cap, d, device=dev)
+        vc32 = torch.randn(2, B, Hkv, cap, d, device=dev)
+        torch.cuda.synchronize()
+
+        def launch32(i):
+            l = i % 2
+            assert lib.ckb200_dev_attention_decode_ws(C.c_void_p(q.data_ptr()), C.c_void_p(kc32[l].data_ptr()), C.c_void_p(vc32[l].data_ptr()),
+                                                      C.c_void_p(out.data_ptr()), B, C.c_longlong(Hkv * cap * d), H, Hkv, T, cap, d, d, splits,
+                                                      C.c_void_p(scratch.data_ptr()), None, None) == 0
+
+        for i in range(2):
+            launch32(i)
+        e0.record(lstream)
+        for i in range(args.launches):
+            launch32(i)
+        e1.record(lstream)
+        assert lib.ckb200_synchronize() == 0
+        us = e0.elapsed_time(e1) / args.launches * 1e3
+        print(json.dumps({"attention_only": T, "batch": B, "kv_cache": "fp32", "launches": args.launches, "splits": splits, "us_per_launch": us,
+                          "kv_bytes_per_launch": 2 * kv_bytes, "tb_s": 2 * kv_bytes / us / 1e6}))
 
 
 def run_small_gemm_only(args):

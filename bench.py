@@ -686,7 +686,7 @@ def prefill_bench(lib, m_tokens, iters, stream_ptr, torch, tensor_peak):
     attn_ms = e0.elapsed_time(e1) / iters
     attn_flops = 4.0 * (m_tokens * (m_tokens + 1) / 2) * d * H
     out["causal_attention"] = {"shape": f"H={H} Hkv={Hkv} d={d} T={m_tokens}", "ms": attn_ms, "tflops_fp32": attn_flops / attn_ms / 1e9,
-                               "note": "exact fp32 FMA on the CUDA cores (the parity tolerance leaves no room for fp16/tf32 scores)"}
+                               "note": "tensor cores at fp32 accuracy: every operand split into two fp16 pieces, three mma.sync per product (tflops_fp32 counts each product once)"}
     # the prefill GEMMs the reference's thread-pool seam dispatches (version/v7/src/ck_parallel_prefill.h:44-48), from the reference's
     # own weight layouts: Q6_K (rows re-laid per call, then the tcgen05 kernel) and Q8_0 (int8 MMAs, bit-identical to the scalar loop)
     seam = {}

@@ -173,6 +173,8 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float *__restri
 using namespace ckb;
 
 // q, out [H][T][ad]; k, v [Hkv][kv_stride_tokens][ad]; causal != 0: token i sees keys 0 .. i, else all T keys.
+extern "C" int ckb_launch_attn_prefill_mma(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads, int num_tokens, int head_dim,
+                                           int aligned_head_dim, int kv_stride_tokens, int causal, void *stream);
 extern "C" int ckb200_dev_attention_prefill_window(const float *q, const float *k, const float *v, float *out, int num_heads, int num_kv_heads,
                                                    int num_tokens, int head_dim, int aligned_head_dim, int kv_stride_tokens, int causal,
                                                    int sliding_window, void *stream)
@@ -187,6 +189,11 @@ extern "C" int ckb200_dev_attention_prefill_window(const float *q, const float *
         return ckb_fail(CKB_ERR_SHAPE, "attention prefill: %d heads / %d kv heads / head size %d is outside this kernel (groups <= %d, aligned head size 64 or 128)",
                         num_heads, num_kv_heads, aligned_head_dim, AP_MAX_GROUP);
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return ckb_fail(CKB_ERR_ALIGN, "attention prefill: pointers must be 16-byte aligned");
+    if (window == 0) {
+        // without a sliding window: the tensor-core kernel of attention_prefill_mma.cu (-1: not for this call)
+        const int rc = ckb_launch_attn_prefill_mma(q, k, v, out, num_heads, num_kv_heads, num_tokens, head_dim, aligned_head_dim, kv_stride_tokens, causal, stream);
+        if (rc >= 0) return rc;
+    }
     // 2 * BT * G threads per key set (a multiple of 32); two key sets when both fit 256 threads
     const int BT = G == 1 ? 64 : (G == 2 ? 32 : ((G == 6 || G == 8) ? 8 : 16));
     const int nsets = 2 * (2 * BT * G) <= 256 ? 2 : 1;

@@ -459,13 +459,19 @@ PREFILL_ATTN_CASES = [  # heads, kv_heads, ad, head_dim, tokens, kv stride, caus
 ]
 
 
-@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,stride,causal", PREFILL_ATTN_CASES)
-def test_attention_prefill(ck, orc, heads, kvh, ad, hd, tokens, stride, causal):
+@pytest.mark.parametrize("tensor_cores", [1, 0])
+@pytest.mark.parametrize("heads,kvh,ad,hd,tokens,stride,causal", PREFILL_ATTN_CASES + [(8, 2, 128, 128, 333, 400, True), (8, 1, 64, 64, 200, 200, False)])
+def test_attention_prefill(ck, orc, tensor_cores, heads, kvh, ad, hd, tokens, stride, causal):
     """Causal / full prefill attention through the reference-named entry points against the oracle: fp32 within
-    ATTN_ABS_TOL absolute on outputs of order one; pad columns of the output are zero."""
+    ATTN_ABS_TOL absolute on outputs of order one; pad columns of the output are zero.  Both kernels: the tensor-core one (every
+    operand split into two fp16 pieces) and the CUDA-core one it replaced."""
     q, k, v = cases.prefill_attention_inputs(tokens + heads, heads, kvh, ad, hd, tokens, stride)
     want = cases.attention_prefill(orc, "oracle_", q, k, v, hd, causal)
-    got = cases.attention_prefill(ck, "", q, k, v, hd, causal)
+    ck.ckb200_tune_set(b"attn_prefill_mma", tensor_cores)
+    try:
+        got = cases.attention_prefill(ck, "", q, k, v, hd, causal)
+    finally:
+        ck.ckb200_tune_set(b"attn_prefill_mma", 1)
     assert float(np.max(np.abs(got - want))) <= ATTN_ABS_TOL, float(np.max(np.abs(got - want)))
     assert np.all(got[:, :, hd:] == 0)
 

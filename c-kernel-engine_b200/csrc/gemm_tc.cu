@@ -651,11 +651,14 @@ extern "C" int ckb_launch_gemm_q4k_tc(const void *A_q8, const void *B, const flo
 // gemm_nt_q6_k_q8_k (src/kernels/gemm_kernels_q6k_q8k.c:1243-1268) over weights in the row-planar layout
 extern "C" int ckb200_dev_gemv_q6_k_planar_q8_k(float *, const void *, const void *, int, int, void *);
 extern "C" int ckb200_dev_add_bias_rows(float *, const float *, int, int, void *);
+extern "C" int ckb_launch_gemm_q6k_mma(const void *A_q8, const void *B_planar, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
 extern "C" int ckb200_dev_gemm_nt_q6_k_planar_q8_k(const void *A_q8, const void *B_planar, const float *bias, float *C, int M, int N, int K, void *stream)
 {
     if (!A_q8 || !B_planar || !C || M <= 0 || N <= 0 || K <= 0) return 0;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
-    const int rc = ckb_launch_gemm_tc(TC_W_Q6K_PLANAR, A_q8, B_planar, bias, C, N, M, N, K, ckb_tune_get("gemm_tc_min_tokens", 16), stream);
+    int rc = ckb_launch_gemm_q6k_mma(A_q8, B_planar, bias, C, N, M, N, K, stream);        // 4 to 64 tokens: integer MMA over the planes (gemm_q6k_mma.cu)
+    if (rc >= 0) return rc;
+    rc = ckb_launch_gemm_tc(TC_W_Q6K_PLANAR, A_q8, B_planar, bias, C, N, M, N, K, ckb_tune_get("gemm_tc_min_tokens", 16), stream);
     if (rc >= 0) return rc;
     for (int m = 0; m < M; ++m) {
         const int r2 = ckb200_dev_gemv_q6_k_planar_q8_k(C + (size_t)m * N, B_planar, (const uint8_t *)A_q8 + (size_t)m * (K / QK_K) * Q8K_BYTES, N, K, stream);

@@ -44,6 +44,7 @@ int ckb_launch_gemm_tc_ws(int wf, const void *A_q8, const void *B, const float *
 size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
 /* integer-MMA kernel of gemm_q4k_mma.cu for up to 64 tokens (Q4_K rows, no workspace); -1 when it does not take the call */
 int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
+int ckb_launch_gemm_q6k_mma(const void *A_q8, const void *B_planar, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);   /* gemm_q6k_mma.cu */
 
 /* From this many sequences a projection runs as one batched product instead of a GEMV per sequence.  The tcgen05 kernel's time
  * hardly depends on the token count below 32 (it is bound by expanding the weights), so for the Q6_K matrices it wins from about
@@ -497,6 +498,10 @@ static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, 
      * otherwise from 16 up on the tcgen05 kernel */
     if (w->fmt == FMT_Q4K && m->c.batch > 1) {
         const int rc = ckb_launch_gemm_q4k_mma(xq, w->w, NULL, y, y_stride, m->c.batch, w->rows, w->cols, st);
+        if (rc >= 0) return rc;
+    }
+    if (w->fmt == FMT_Q6K && w->planar && m->c.batch > 1) {
+        const int rc = ckb_launch_gemm_q6k_mma(xq, w->planar, NULL, y, y_stride, m->c.batch, w->rows, w->cols, st);
         if (rc >= 0) return rc;
     }
     if (m->c.batch >= MODEL_GEMM_MIN_BATCH && (w->fmt == FMT_Q4K || (w->fmt == FMT_Q6K && w->planar))) {

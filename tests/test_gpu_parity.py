@@ -629,6 +629,49 @@ def test_gemm_nt_q6_k_planar_tensor_core(ck, orc, m, n, k, big_scales):
         assert_fp32_close(got, want, "q6_k planar gemm")
 
 
+@pytest.mark.parametrize("shape,rw", [(1, 2), (2, 2), (4, 2), (1, 1), (4, 1)])
+@pytest.mark.parametrize("m,n,k", [(4, 40, 1024), (8, 129, 1024), (9, 64, 2048), (16, 300, 4096), (32, 1000, 3072), (33, 77, 1024), (64, 260, 5120)])
+def test_gemm_nt_q6_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
+    """4 to 64 tokens over planar Q6_K weights run on the integer-MMA kernel (K a multiple of 1024): all four token-tile counts with
+    ragged token and row counts, the three CTA shapes, one and two 16-row tiles per warp, scales over the whole int8 range (exact
+    for every scale, unlike the fp16 operand of the tcgen05 kernel).  Two runs agree bit for bit."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    w = synth.make_weights("q6_k", n, k, seed=m + n).reshape(n, k // 256, 210).copy()
+    w[:, :, 192:208] = np.random.default_rng(m).integers(-128, 128, size=(n, k // 256, 16)).astype(np.int8).view(np.uint8)
+    w = w.reshape(-1)
+    a = synth.make_x(k, seed=m, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", "q6_k", a, rows=m)
+    bias = np.random.default_rng(n).standard_normal(n).astype(np.float32) if m % 2 else None
+    want = cases.gemm_nt(orc, "oracle_", "q6_k", aq, w, bias, m, n, k)
+    ck.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+    ck.ckb200_launch_count.restype = C.c_longlong
+    raw, taq = torch.from_numpy(w).to(dev), torch.from_numpy(aq).to(dev)
+    tb = torch.from_numpy(bias).to(dev) if bias is not None else None
+    planar = torch.empty(ck.ckb200_q6_k_planar_bytes(n, k), dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+    assert ck.ckb200_dev_q6_k_to_planar(C.c_void_p(planar.data_ptr()), C.c_void_p(raw.data_ptr()), n, k, None) == 0
+    outs = []
+    try:
+        ck.ckb200_tune_set(b"gemm_q6k_mma_shape", shape)
+        ck.ckb200_tune_set(b"gemm_q6k_mma_rw", rw)
+        for _ in range(2):
+            c = torch.full((m, n), float("nan"), device=dev)
+            torch.cuda.synchronize()
+            n0 = ck.ckb200_launch_count()
+            assert ck.ckb200_dev_gemm_nt_q6_k_planar_q8_k(C.c_void_p(taq.data_ptr()), C.c_void_p(planar.data_ptr()), C.c_void_p(tb.data_ptr() if tb is not None else None),
+                                                          C.c_void_p(c.data_ptr()), m, n, k, None) == 0
+            assert ck.ckb200_launch_count() - n0 == 1            # one kernel: not the tcgen05 path (tiles + kernel), not a loop of GEMVs
+            assert ck.ckb200_synchronize() == 0
+            outs.append(c.cpu().numpy())
+    finally:
+        ck.ckb200_tune_set(b"gemm_q6k_mma_shape", 0)
+        ck.ckb200_tune_set(b"gemm_q6k_mma_rw", 0)
+    assert_fp32_close(outs[0], want, "q6_k integer-MMA path")
+    assert np.array_equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("m,k", [(1, 32), (3, 96), (7, 896), (33, 4096), (130, 4864), (5, 14336), (2, 28672), (4100, 896)])
 def test_gemv_q8_0_planar_layout(ck, orc, m, k):
     import torch

@@ -365,7 +365,7 @@ using namespace ckb;
 extern "C" int ckb_launch_gemm_q6k_mma(const void *A_q8, const void *B_planar, const float *bias, float *C, int ldc, int M, int N, int K, void *stream)
 {
     if (!A_q8 || !B_planar || !C || N <= 0 || K <= 0 || K % 1024) return -1;
-    if (M < ckb_tune_get("gemm_q6k_mma_min", 4) || M > ckb_tune_get("gemm_q6k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q6k_mma", 1)) return -1;
+    if (M < ckb_tune_get("gemm_q6k_mma_min", 2) || M > ckb_tune_get("gemm_q6k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q6k_mma", 1)) return -1;
     if (((uintptr_t)B_planar & 15) || ((uintptr_t)A_q8 & 15)) return -1;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);

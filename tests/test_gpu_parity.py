@@ -252,7 +252,7 @@ def test_gemm_nt_q4_k_integer_mma_small_batches(ck, orc, tma, shape, rw, m, n, k
         assert ck.ckb200_launch_count() - n0 == 1                # one kernel, no per-token loop
         again = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
     finally:
-        ck.ckb200_tune_set(b"gemm_q4k_mma_min", 4)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_min", 2)
         ck.ckb200_tune_set(b"gemm_q4k_mma_shape", 0)
         ck.ckb200_tune_set(b"gemm_q4k_mma_rw", 0)
         ck.ckb200_tune_set(b"gemm_q4k_mma_tma", 1)

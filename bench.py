@@ -976,7 +976,8 @@ def run_attention_only(args):
 
 
 def run_small_gemm_only(args):
-    """Plain launches of gemm_nt_q4_k_q8_k for a handful of tokens (M,N,K): the small case behind profiles/gemm_q4k_mma_*.md, with event timing."""
+    """Plain launches of gemm_nt_q4_k_q8_k (or, with --small-gemm-fmt q6_k, of the planar Q6_K product) for a handful of tokens (M,N,K):
+    the small case behind profiles/gemm_q4k_mma_*.md and gemm_q6k_mma_*.md, with event timing."""
     import torch
 
     lib = pkg.load_lib()
@@ -984,9 +985,19 @@ def run_small_gemm_only(args):
     M, N, K = (int(v) for v in args.small_gemm_only.split(","))
     dev = torch.device("cuda", 0)
     nb = K // 256
-    copies = max(1, min(8, int(300e6 // (N * nb * 144))))              # rotate over more than L2 of weights where that stays small
-    W = torch.empty(copies * N * nb * 144, dtype=torch.uint8, device=dev)
-    assert lib.ckb200_dev_fill_blocks(C.c_void_p(W.data_ptr()), C.c_longlong(copies * N * nb), 0, C.c_ulonglong(5), None) == 0
+    q6 = args.small_gemm_fmt == "q6_k"
+    lib.ckb200_q6_k_planar_bytes.restype = C.c_size_t
+    wbytes = lib.ckb200_q6_k_planar_bytes(N, K) if q6 else N * nb * 144
+    copies = max(1, min(8, int(300e6 // wbytes)))                      # rotate over more than L2 of weights where that stays small
+    W = torch.empty(copies * wbytes, dtype=torch.uint8, device=dev)
+    if q6:                                                             # random Q6_K rows, re-laid row-planar as resident weights are
+        raw = torch.empty(N * nb * 210, dtype=torch.uint8, device=dev)
+        assert lib.ckb200_dev_fill_blocks(C.c_void_p(raw.data_ptr()), C.c_longlong(N * nb), 1, C.c_ulonglong(5), None) == 0
+        for c in range(copies):
+            assert lib.ckb200_dev_q6_k_to_planar(C.c_void_p(W.data_ptr() + c * wbytes), C.c_void_p(raw.data_ptr()), N, K, None) == 0
+        del raw
+    else:
+        assert lib.ckb200_dev_fill_blocks(C.c_void_p(W.data_ptr()), C.c_longlong(copies * N * nb), 0, C.c_ulonglong(5), None) == 0
     x = torch.randn(M, K, device=dev)
     xq = torch.empty(M * nb * 292, dtype=torch.uint8, device=dev)
     assert lib.ckb200_dev_quantize_q8_k(C.c_void_p(x.data_ptr()), C.c_void_p(xq.data_ptr()), M, K, None) == 0
@@ -994,9 +1005,11 @@ def run_small_gemm_only(args):
     lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    gemm = lib.ckb200_dev_gemm_nt_q6_k_planar_q8_k if q6 else lib.ckb200_dev_gemm_nt_q4_k_q8_k
+
     def launch(i):
-        w = W.data_ptr() + (i % copies) * N * nb * 144
-        assert lib.ckb200_dev_gemm_nt_q4_k_q8_k(C.c_void_p(xq.data_ptr()), C.c_void_p(w), None, C.c_void_p(out.data_ptr()), M, N, K, None) == 0
+        w = W.data_ptr() + (i % copies) * wbytes
+        assert gemm(C.c_void_p(xq.data_ptr()), C.c_void_p(w), None, C.c_void_p(out.data_ptr()), M, N, K, None) == 0
 
     for i in range(3):
         launch(i)
@@ -1006,8 +1019,8 @@ def run_small_gemm_only(args):
     e1.record(lstream)
     assert lib.ckb200_synchronize() == 0
     us = e0.elapsed_time(e1) / args.launches * 1e3
-    print(json.dumps({"small_gemm_only": [M, N, K], "launches": args.launches, "us_per_launch": us, "weight_bytes": N * nb * 144,
-                      "weights_tb_s": N * nb * 144 / us / 1e6}))
+    print(json.dumps({"small_gemm_only": [M, N, K], "fmt": args.small_gemm_fmt, "launches": args.launches, "us_per_launch": us, "weight_bytes": wbytes,
+                      "weights_tb_s": wbytes / us / 1e6}))
 
 
 def run_decode_only(args):
@@ -1046,7 +1059,8 @@ def main():
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--prefill-only", type=int, default=None, metavar="M", help="profiling aid: the prefill GEMM section alone at M tokens")
     ap.add_argument("--prefill-stack-only", type=int, default=None, metavar="T", help="profiling aid: whole-stack prefill of a T-token prompt, twice")
-    ap.add_argument("--small-gemm-only", default=None, metavar="M,N,K", help="profiling aid: gemm_nt_q4_k_q8_k launches for a few tokens")
+    ap.add_argument("--small-gemm-only", default=None, metavar="M,N,K", help="profiling aid: gemm_nt_q4_k_q8_k (or planar Q6_K) launches for a few tokens")
+    ap.add_argument("--small-gemm-fmt", default="q4_k", choices=["q4_k", "q6_k"])
     ap.add_argument("--attention-only", type=int, default=None, metavar="T", help="profiling aid: decode attention launches, 70B head shape, context T")
     ap.add_argument("--batch", type=int, default=1, help="sequences per step of --decode-only")
     ap.add_argument("--decode-only", default=None, choices=["qwen2-0.5b", "llama3-70b"], help="profiling aid: eager decode steps of one model shape")

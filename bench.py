@@ -838,7 +838,7 @@ def attention_bench(lib, torch, peak, iters=40):
             o = torch.empty_like(q)
             kc = torch.randn(nl, batch, Hkv, T, d, device=dev, dtype=dt)
             vc = torch.randn(nl, batch, Hkv, T, d, device=dev, dtype=dt)
-            splits = lib.ckb200_attention_decode_splits(batch, Hkv, T)
+            splits = lib.ckb200_attention_decode_splits_kv(batch, Hkv, T, eb)
             scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(batch, H, d, splits)) // 4, device=dev)
 
             def run(i):
@@ -928,8 +928,8 @@ def run_attention_only(args):
         out = torch.empty_like(q)
         kc16 = torch.randn(2, B, Hkv, cap, d, device=dev, dtype=torch.float16)
         vc16 = torch.randn(2, B, Hkv, cap, d, device=dev, dtype=torch.float16)
-        splits = lib.ckb200_attention_decode_splits(B, Hkv, T)
-        scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(B, H, d, splits)) // 4, device=dev)
+        splits = lib.ckb200_attention_decode_splits_kv(B, Hkv, T, 2)
+        scratch = torch.empty(max(256, lib.ckb200_attention_decode_scratch_bytes(B, H, d, 64)) // 4, device=dev)
         lstream = torch.cuda.ExternalStream(lib.ckb200_stream())
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -955,6 +955,7 @@ def run_attention_only(args):
         del kc16, vc16
         kc32 = torch.randn(2, B, Hkv, cap, d, device=dev)
         vc32 = torch.randn(2, B, Hkv, cap, d, device=dev)
+        splits = lib.ckb200_attention_decode_splits_kv(B, Hkv, T, 4)
         torch.cuda.synchronize()
 
         def launch32(i):

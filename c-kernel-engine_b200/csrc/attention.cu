@@ -330,15 +330,26 @@ extern "C" size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads
     return (size_t)batch * num_heads * splits * (aligned_head_dim + 2) * sizeof(float);
 }
 
-// Number of context splits the launcher would use (1 = no scratch needed).
-extern "C" int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens)
+// Number of context splits the launcher would use (1 = no scratch needed), given the size of a cache element
+// (4 = fp32, 2 = fp16).  From two sequences up the tensor-core kernel serves the call and holds one CTA per SM
+// over an fp32 cache, two over an fp16 cache; a CTA beyond those slots starts a second wave that costs as much
+// as the first (4 sequences of the 70B shape at 4096 keys over fp32: 41.8 us at 5 splits = 160 CTAs, 28.2 us
+// at 4 = 128), so the count there is rounded DOWN to what one wave holds.
+extern "C" int ckb200_attention_decode_splits_kv(int batch, int num_kv_heads, int kv_tokens, int kv_element_bytes)
 {
     const int forced = ckb_tune_get("attn_splits", 0);
     if (forced > 0) return forced;
     const int sms = ckb_sm_count();
-    const long long ctas_wanted = ckb_tune_get("attn_tile", 1) ? sms : 2LL * sms;   // the tile kernel fills an SM with one CTA
     const long long base = (long long)batch * num_kv_heads;
-    int splits = (int)((ctas_wanted + base - 1) / base);
+    const bool f16 = kv_element_bytes == 2;
+    const bool mma = batch >= ckb_tune_get("attn_f16_mma_min_batch", 2) && ckb_tune_get(f16 ? "attn_f16_mma" : "attn_f32_mma", 1);
+    int splits;
+    if (mma) {
+        splits = (int)(((f16 ? 2LL : 1LL) * sms) / base);
+    } else {
+        const long long ctas_wanted = ckb_tune_get("attn_tile", 1) ? sms : 2LL * sms;   // the tile kernel fills an SM with one CTA
+        splits = (int)((ctas_wanted + base - 1) / base);
+    }
     const int tiles = (kv_tokens + 63) / 64;                 // at least one 64-key tile per split
     if (splits > tiles) splits = tiles;
     if (splits > 256) splits = 256;
@@ -346,6 +357,11 @@ extern "C" int ckb200_attention_decode_splits(int batch, int num_kv_heads, int k
     const int tiles_per_split = (tiles + splits - 1) / splits;
     splits = (tiles + tiles_per_split - 1) / tiles_per_split;   // no split without work
     return splits;
+}
+
+extern "C" int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens)
+{
+    return ckb200_attention_decode_splits_kv(batch, num_kv_heads, kv_tokens, 4);
 }
 
 // Core launcher: scratch may be NULL when splits == 1.  With pos_dev the context length is read on the
@@ -508,7 +524,7 @@ extern "C" int ckb200_dev_attention_decode_f16cache(const float *q, const uint16
                                                     int head_dim, int aligned_head_dim, void *stream)
 {
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
-    const int splits = ckb200_attention_decode_splits(batch, num_kv_heads, kv_tokens);
+    const int splits = ckb200_attention_decode_splits_kv(batch, num_kv_heads, kv_tokens, 2);
     float *scratch = NULL;
     if (splits > 1) {
         scratch = (float *)ckb_scratch(CKB_SLOT_T, ckb200_attention_decode_scratch_bytes(batch, num_heads, aligned_head_dim, splits));

@@ -279,7 +279,7 @@ CKB200Model *ckb200_model_create(const CKB200ModelConfig *cfg)
         m->gemm_ws_bytes = need;
         DEV_ALLOC(m->gemm_ws, need);
     }
-    m->attn_splits = ckb200_attention_decode_splits(B, m->Hkvl, S);
+    m->attn_splits = ckb200_attention_decode_splits_kv(B, m->Hkvl, S, m->kv_eb);
     {
         size_t sb = ckb200_attention_decode_scratch_bytes(B, m->Hl, m->d, m->attn_splits);
         DEV_ALLOC(m->attn_scratch, sb ? sb : 256);

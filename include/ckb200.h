@@ -188,7 +188,8 @@ int ckb200_dev_attention_decode_fused(const float *q, const float *k_cache, cons
                                       int cache_capacity, int head_dim, int aligned_head_dim, int splits, float *scratch,
                                       int *counters, const int *pos_dev, void *q8_out, int q8_cols, void *stream);
 size_t ckb200_attention_decode_counter_bytes(int batch, int num_kv_heads);
-int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);
+int ckb200_attention_decode_splits(int batch, int num_kv_heads, int kv_tokens);          /* fp32 cache */
+int ckb200_attention_decode_splits_kv(int batch, int num_kv_heads, int kv_tokens, int kv_element_bytes);   /* 4 = fp32, 2 = fp16 */
 size_t ckb200_attention_decode_scratch_bytes(int batch, int num_heads, int aligned_head_dim, int splits);
 
 /* fp16 KV cache: kv_cache_store_f16 (src/kernels/kv_cache_kernels.c:131-163; round to nearest even, bit-exact) and

@@ -33,6 +33,7 @@
 namespace ckb {
 
 constexpr int QM4_THREADS = 256, QM4_WARPS = 8;
+constexpr int QM4_TMA_THREADS = QM4_THREADS + 32;             // the bulk-copy kernel: eight computing warps and the warp that issues the copies
 constexpr int QM4_XPITCH = 352;                                // bytes between token slots: 304 copied, and 88 words = 24 mod 32 banks
 constexpr int QM4_XCOPY = 19;                                  // 16-byte pieces that cover one 292-byte block from its 16-byte-aligned start
 constexpr int QM4_WPITCH = 160;                                // bytes between weight rows in a warp's ring (144 copied; 40 words = 8 mod 32)
@@ -326,14 +327,14 @@ template <int NT, int RW, int KS, int D> struct Qm4TmaSmem {
 };
 
 template <int NT, int RW, int RT, int KS, int D>
-__global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+__global__ void __launch_bounds__(QM4_TMA_THREADS) gemm_q4k_mma_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                                                                        const float *__restrict__ bias, float *__restrict__ C, int ldc, int M, int N, int nb,
                                                                        int *__restrict__ dev_err)
 {
     static_assert(RT * KS == QM4_WARPS, "8 warps");
     using L = Qm4TmaSmem<NT, RW, KS, D>;
     extern __shared__ __align__(128) uint8_t qm4_smem[];
-    __shared__ __align__(8) uint64_t full[D];
+    __shared__ __align__(8) uint64_t full[D], empty[D];
     const uint32_t s_base = smem_u32(qm4_smem);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -343,13 +344,13 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __g
     const int b_first = ks * per;
 
     if (tid == 0) {
-        for (int i = 0; i < D; ++i) mbar_init(smem_u32(&full[i]), 1);
+        for (int i = 0; i < D; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), QM4_WARPS); }
         mbar_fence_init();
     }
     __syncthreads();
     pdl_trigger();
 
-    // thread 0: the copies of step s; weights and activations of a stage complete the same barrier
+    // the issuing thread: the copies of step s; weights and activations of a stage complete the same barrier
     auto expect = [&](int s) {
         int slices = 0;
         for (int k = 0; k < KS; ++k) slices += (k * per + s < nb);
@@ -380,22 +381,31 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __g
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[rw][nt][e] = 0.0f;
 
-    if (tid == 0) {
-        for (int s = 0; s < D - 1 && s < per; ++s) { expect(s); issue_w(s); }     // weights are not written by any kernel: before the dependency wait
-    }
+    // The ninth warp only issues copies: a stage is refilled as soon as the eight computing warps have released it, and no
+    // computing warp waits for another between steps.
+    if (warp == QM4_WARPS) {
+        if (lane == 0) {
+            const int pro = per < D ? per : D;
+            for (int s = 0; s < pro; ++s) { expect(s); issue_w(s); }                     // weights are not written by any kernel: before the dependency wait
+            pdl_wait();
+            for (int s = 0; s < pro; ++s) issue_x(s);
+            for (int s = D; s < per; ++s) {
+                if (!mbar_wait_spin(smem_u32(&empty[s % D]), (uint32_t)(s / D - 1) & 1u)) { atomicExch(dev_err, DEV_ERR_FULL_WAIT); break; }
+                expect(s); issue_w(s); issue_x(s);
+            }
+        }
+    } else {
     pdl_wait();
-    if (tid == 0) {
-        for (int s = 0; s < D - 1 && s < per; ++s) issue_x(s);
-    }
-
     bool ok = true;
     for (int s = 0; s < per; ++s) {
         const int b = b_first + s;
-        __syncthreads();                                       // step s - 1 is finished everywhere: its stage may be refilled
-        if (tid == 0 && s + D - 1 < per) { expect(s + D - 1); issue_w(s + D - 1); issue_x(s + D - 1); }
+        if (s > 0) {                                           // step s - 1 is finished in this warp: one more release of its stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty[(s - 1) % D]));
+        }
         if (b >= nb) continue;
         if (ok && !mbar_wait_spin(smem_u32(&full[s % D]), (uint32_t)(s / D) & 1u)) {
-            ok = false;                                        // keep taking part in the barriers; the host sees the error word
+            ok = false;                                        // the host sees the error word
             if (lane == 0) atomicExch(dev_err, DEV_ERR_FULL_WAIT);
         }
         const uint8_t *slice = qm4_smem + (size_t)(s % D) * L::STAGE + (size_t)ks * (L::WSLICE + L::XSLICE);
@@ -403,11 +413,12 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __g
         const uint8_t *xs = slice + L::WSLICE + ((b * Q8K_BYTES) & 15);
         qm4_superblock<NT, RW, Q4K_BYTES, QM4_XWIN>(ws, xs, acc, g, t, zero);
     }
+    }
     __syncthreads();                                           // the staging area becomes the reduction buffer (every issued copy was waited for)
 
     float *red = reinterpret_cast<float *>(qm4_smem);
     constexpr int PER_WARP = RW * NT * 4;
-    if (KS > 1 && ks > 0) {
+    if (KS > 1 && ks > 0 && warp < QM4_WARPS) {
 #pragma unroll
         for (int rw = 0; rw < RW; ++rw)
 #pragma unroll
@@ -416,7 +427,7 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_tma_kernel(const __g
                 for (int e = 0; e < 4; ++e) red[(((size_t)(ks - 1) * RT + rt) * PER_WARP + (rw * NT + nt) * 4 + e) * 32 + lane] = acc[rw][nt][e];
     }
     if (KS > 1) __syncthreads();
-    if (ks == 0) {
+    if (ks == 0 && warp < QM4_WARPS) {
         const int n0 = row0 + rt * 16 * RW;
 #pragma unroll
         for (int rw = 0; rw < RW; ++rw)
@@ -478,7 +489,7 @@ static int qm4_launch_tma(const void *A_q8, const void *B, const float *bias, fl
         attr_set = true;
     }
     const int grid = (N + L::ROWS - 1) / L::ROWS;
-    return launch_pdl("gemm_q4k_mma_tma", gemm_q4k_mma_tma_kernel<NT, RW, RT, KS, D>, dim3(grid), dim3(QM4_THREADS), (size_t)L::BYTES, st, tm_w, tm_x, bias, C, ldc, M, N,
+    return launch_pdl("gemm_q4k_mma_tma", gemm_q4k_mma_tma_kernel<NT, RW, RT, KS, D>, dim3(grid), dim3(QM4_TMA_THREADS), (size_t)L::BYTES, st, tm_w, tm_x, bias, C, ldc, M, N,
                       nb, ckb_device_error_word());
 }
 
@@ -524,9 +535,8 @@ static int qm4_shape(int shape, const void *A_q8, const void *B, const float *bi
 
 // Shape by measurement on B200 (Llama-3-70B and 8B projection shapes, 8 to 64 tokens): the widest CTA (most rows per staged activation
 // block) that still gives three quarters of the SMs a CTA; K slices make up for rows when there are few.
-static int qm4_auto_shape(int rows_per_warp, int N, int nb)
+static int qm4_auto_shape(int rows_per_warp, int N, int nb, int want)
 {
-    const int want = 3 * ckb_sm_count() / 4;
     for (int shape = 1; shape < 4; shape *= 2) {
         const int rows = rows_per_warp * 8 / shape;
         if ((N + rows - 1) / rows >= want || nb < 2 * shape) return shape;
@@ -538,10 +548,18 @@ template <int NT>
 static int qm4_pick(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
 {
     int rw = ckb_tune_get("gemm_q4k_mma_rw", 0);               // 16-row tiles per warp: 0 auto, 1, 2 (64 token slots: always 1, registers)
+    const int want = 3 * ckb_sm_count() / 4;
+    // Up to 8 tokens one tile per warp is as fast or faster everywhere (57344 x 8192: 55 us against 60); 9 to 16 tokens only on very
+    // tall matrices.  There two K slices per CTA beat eight row warps when K is long (measured on the 70B and 8B projections).
+    const bool tall = (N + 63) / 64 >= 4 * want && nb >= 32;
+    const bool narrow = NT == 1 || (NT == 2 && tall);
     if (NT >= 8) rw = 1;
-    else if (rw != 1 && rw != 2) rw = (N + 63) / 64 >= 3 * ckb_sm_count() / 4 ? 2 : 1;
+    else if (rw != 1 && rw != 2) rw = !narrow && (N + 63) / 64 >= want ? 2 : 1;
     int shape = ckb_tune_get("gemm_q4k_mma_shape", 0);         // 1: 8 row warps, 2: 4 x 2 K slices, 4: 2 x 4 K slices, 0 auto
-    if (shape != 1 && shape != 2 && shape != 4) shape = qm4_auto_shape(16 * rw, N, nb);
+    if (shape != 1 && shape != 2 && shape != 4) {
+        shape = qm4_auto_shape(16 * rw, N, nb, narrow && rw == 1 ? 2 * want : want);       // small CTAs: two per SM wanted (8192 x 8192, 8 tokens: 9.8 us against 16.1)
+        if (shape == 1 && narrow && rw == 1 && nb >= 32) shape = 2;
+    }
     if constexpr (NT < 8) {
         if (rw == 2) return qm4_shape<NT, 2>(shape, A_q8, B, bias, C, ldc, M, N, nb, st);
     }

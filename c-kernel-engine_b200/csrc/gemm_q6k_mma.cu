@@ -23,7 +23,7 @@
 
 namespace ckb {
 
-constexpr int QM6_WARPS = 8, QM6_THREADS = 32 * QM6_WARPS;
+constexpr int QM6_WARPS = 8, QM6_THREADS = 32 * (QM6_WARPS + 1);   // eight computing warps and the warp that issues the copies
 constexpr int QM6_XWIN = 304;                                  // a 292-byte Q8_K block from its 16-byte-aligned start
 
 __device__ __forceinline__ void qm6_tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
@@ -64,8 +64,8 @@ template <int NT, int RW, int KS, int D> struct Qm6Smem {
     static constexpr int BYTES = D * STAGE;
 };
 
-template <int NT, int RW, int RT, int KS, int D>
-__global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_constant__ CUtensorMap tm_ql, const __grid_constant__ CUtensorMap tm_qh,
+template <int NT, int RW, int RT, int KS, int D, int OCC>
+__global__ void __launch_bounds__(QM6_THREADS, OCC) gemm_q6k_mma_kernel(const __grid_constant__ CUtensorMap tm_ql, const __grid_constant__ CUtensorMap tm_qh,
                                                                    const __grid_constant__ CUtensorMap tm_sc, const __grid_constant__ CUtensorMap tm_x,
                                                                    const float *__restrict__ bias, float *__restrict__ C, int ldc, int M, int N, int nb,
                                                                    int *__restrict__ dev_err)
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_
     static_assert(RT * KS == QM6_WARPS, "8 warps");
     using L = Qm6Smem<NT, RW, KS, D>;
     extern __shared__ __align__(16) uint8_t qm6_raw[];
-    __shared__ __align__(8) uint64_t full[D];
+    __shared__ __align__(8) uint64_t full[D], empty[D];
     uint8_t *smem = qm6_raw + ((1024u - (smem_u32(qm6_raw) & 1023u)) & 1023u);           // the launch asks for 1 KB more
     const uint32_t s_base = smem_u32(smem);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -84,13 +84,13 @@ __global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_
     const int b_first = ks * per;
 
     if (tid == 0) {
-        for (int i = 0; i < D; ++i) mbar_init(smem_u32(&full[i]), 1);
+        for (int i = 0; i < D; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), QM6_WARPS); }
         mbar_fence_init();
     }
     __syncthreads();
     pdl_trigger();
 
-    // thread 0: the copies of step s.  Plane offsets inside a planar row: ql at 0, qh at nb * 128, scales at nb * 192, d at nb * 208.
+    // the issuing thread: the copies of step s.  Plane offsets inside a planar row: ql at 0, qh at nb * 128, scales at nb * 192, d at nb * 208.
     auto expect = [&](int s) {
         int slices = 0;
         for (int k = 0; k < KS; ++k) slices += (k * per + s < nb);
@@ -125,17 +125,29 @@ __global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[rw][nt][e] = 0.0f;
 
-    if (tid == 0)
-        for (int s = 0; s < D - 1 && s < per; ++s) { expect(s); issue_w(s); }            // weights are not written by any kernel: before the dependency wait
+    // The ninth warp only issues copies: a stage is refilled as soon as the eight computing warps have released it, and no
+    // computing warp waits for another between steps (with one thread of a computing warp issuing the twenty copies of a step
+    // behind a CTA-wide barrier, three warps in four sat at that barrier).
+    if (warp == QM6_WARPS) {
+        if (lane == 0) {
+            const int pro = per < D ? per : D;
+            for (int s = 0; s < pro; ++s) { expect(s); issue_w(s); }                     // weights are not written by any kernel: before the dependency wait
+            pdl_wait();
+            for (int s = 0; s < pro; ++s) issue_x(s);
+            for (int s = D; s < per; ++s) {
+                if (!mbar_wait_spin(smem_u32(&empty[s % D]), (uint32_t)(s / D - 1) & 1u)) { atomicExch(dev_err, DEV_ERR_FULL_WAIT); break; }
+                expect(s); issue_w(s); issue_x(s);
+            }
+        }
+    } else {
     pdl_wait();
-    if (tid == 0)
-        for (int s = 0; s < D - 1 && s < per; ++s) issue_x(s);
-
     bool ok = true;
     for (int s = 0; s < per; ++s) {
         const int b = b_first + s;
-        __syncthreads();                                       // step s - 1 is finished everywhere: its stage may be refilled
-        if (tid == 0 && s + D - 1 < per) { expect(s + D - 1); issue_w(s + D - 1); issue_x(s + D - 1); }
+        if (s > 0) {                                           // step s - 1 is finished in this warp: one more release of its stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty[(s - 1) % D]));
+        }
         if (b >= nb) continue;
         if (ok && !mbar_wait_spin(smem_u32(&full[s % D]), (uint32_t)(s / D) & 1u)) {
             ok = false;
@@ -244,11 +256,12 @@ __global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_
             }
         }
     }
+    }
     __syncthreads();                                           // the staging area becomes the reduction buffer (every issued copy was waited for)
 
     float *red = reinterpret_cast<float *>(smem);
     constexpr int PER_WARP = RW * NT * 4;
-    if (KS > 1 && ks > 0) {
+    if (KS > 1 && ks > 0 && warp < QM6_WARPS) {
 #pragma unroll
         for (int rw = 0; rw < RW; ++rw)
 #pragma unroll
@@ -257,7 +270,7 @@ __global__ void __launch_bounds__(QM6_THREADS) gemm_q6k_mma_kernel(const __grid_
                 for (int e = 0; e < 4; ++e) red[(((size_t)(ks - 1) * RT + rt) * PER_WARP + (rw * NT + nt) * 4 + e) * 32 + lane] = acc[rw][nt][e];
     }
     if (KS > 1) __syncthreads();
-    if (ks == 0) {
+    if (ks == 0 && warp < QM6_WARPS) {
         const int n0 = row0 + rt * 16 * RW;
 #pragma unroll
         for (int rw = 0; rw < RW; ++rw)
@@ -299,12 +312,12 @@ static bool qm6_make_map(CUtensorMap *map, const void *base, size_t row_bytes, s
                swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NT, int RW, int RT, int KS, int D>
+template <int NT, int RW, int RT, int KS, int D, int OCC>
 static int qm6_launch(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
 {
     using L = Qm6Smem<NT, RW, KS, D>;
     static_assert((KS - 1) * RT * RW * NT * 4 * 32 * 4 <= L::BYTES, "the reduction buffer fits into the staging area");
-    static_assert(L::BYTES + 1024 <= 227 * 1024, "shared memory");
+    static_assert(OCC * (L::BYTES + 2048) <= 227 * 1024, "shared memory of the resident CTAs");
     static_assert(L::ROWS <= 256 && L::MT <= 256, "box limits");
     const size_t rb = q6p_row_bytes(nb);
     CUtensorMap tm_ql, tm_qh, tm_sc, tm_x;
@@ -313,36 +326,50 @@ static int qm6_launch(const void *A_q8, const void *B, const float *bias, float 
         return -1;
     static bool attr_set = false;
     if (!attr_set) {
-        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_q6k_mma_kernel<NT, RW, RT, KS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES + 1024), "gemm_q6k_mma smem"))
+        if (ckb_check_cuda((int)cudaFuncSetAttribute(gemm_q6k_mma_kernel<NT, RW, RT, KS, D, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES + 1024), "gemm_q6k_mma smem"))
             return CKB_ERR_CUDA;
         attr_set = true;
     }
     const int grid = (N + L::ROWS - 1) / L::ROWS;
-    return launch_pdl("gemm_q6k_mma", gemm_q6k_mma_kernel<NT, RW, RT, KS, D>, dim3(grid), dim3(QM6_THREADS), (size_t)(L::BYTES + 1024), st, tm_ql, tm_qh, tm_sc, tm_x, bias, C, ldc,
+    return launch_pdl("gemm_q6k_mma", gemm_q6k_mma_kernel<NT, RW, RT, KS, D, OCC>, dim3(grid), dim3(QM6_THREADS), (size_t)(L::BYTES + 1024), st, tm_ql, tm_qh, tm_sc, tm_x, bias, C, ldc,
                       M, N, nb, ckb_device_error_word());
 }
 
 template <int NT, int RW>
 static int qm6_shape(int shape, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
 {
-    constexpr int rows1 = 16 * RW * 8;
     constexpr int s1 = Qm6Smem<NT, RW, 1, 1>::SLICE, s2 = 2 * Qm6Smem<NT, RW, 2, 1>::SLICE, s4 = 4 * Qm6Smem<NT, RW, 4, 1>::SLICE;
-    constexpr int lim = 226 * 1024;
+    constexpr int lim = 225 * 1024;
     constexpr int D1 = 4 * s1 <= lim ? 4 : (3 * s1 <= lim ? 3 : 2), D2 = 4 * s2 <= lim ? 4 : (3 * s2 <= lim ? 3 : 2), D4 = 4 * s4 <= lim ? 4 : (3 * s4 <= lim ? 3 : 2);
-    (void)rows1;
-    if (shape == 1) return qm6_launch<NT, RW, 8, 1, D1>(A_q8, B, bias, C, ldc, M, N, nb, st);
-    if (shape == 2) return qm6_launch<NT, RW, 4, 2, D2>(A_q8, B, bias, C, ldc, M, N, nb, st);
-    return qm6_launch<NT, RW, 2, 4, D4>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    if (shape == 1) return qm6_launch<NT, RW, 8, 1, D1, 1>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    if (shape == 2) return qm6_launch<NT, RW, 4, 2, D2, 1>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    return qm6_launch<NT, RW, 2, 4, D4, 1>(A_q8, B, bias, C, ldc, M, N, nb, st);
+}
+
+// Up to 16 tokens the work of a step is mostly the unpacking of the weights, a chain of dependent integer instructions that eight
+// warps do not always hide: two CTAs per SM (one 16-row tile per warp, two stages each) keep sixteen computing warps resident.
+template <int NT>
+static int qm6_shape_pair(int shape, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
+{
+    if (shape == 1) return qm6_launch<NT, 1, 8, 1, 2, 2>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    if (shape == 2) return qm6_launch<NT, 1, 4, 2, 2, 2>(A_q8, B, bias, C, ldc, M, N, nb, st);
+    return qm6_launch<NT, 1, 2, 4, 2, 2>(A_q8, B, bias, C, ldc, M, N, nb, st);
 }
 
 template <int NT>
 static int qm6_pick(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int nb, cudaStream_t st)
 {
-    const int want = 3 * ckb_sm_count() / 4;
+    // CTAs per SM: 0 auto, 1, 2.  Two pay where there are rows for them: up to 8 tokens from about 28000 rows (an LM head: 188 ->
+    // 161 us at 128256 x 8192; the 70B down projection, 8192 rows, 45 us with one against 51), 9 to 16 tokens from 4736 rows.
+    int occ = ckb_tune_get("gemm_q6k_mma_occ", 0);
+    const int sms = ckb_sm_count();
+    if (occ != 1 && occ != 2) occ = (NT == 1 && (N + 127) / 128 >= 3 * sms / 2) || (NT == 2 && (N + 31) / 32 >= sms) ? 2 : 1;
+    if (NT > 2) occ = 1;
+    const int want = 3 * occ * sms / 4;
     int rw = ckb_tune_get("gemm_q6k_mma_rw", 0);               // 16-row tiles per warp: 0 auto, 1, 2 (64 token slots: always 1, registers)
-    if (NT >= 8) rw = 1;
+    if (NT >= 8 || occ == 2) rw = 1;
     else if (rw != 1 && rw != 2) rw = (N + 63) / 64 >= want ? 2 : 1;
-    int shape = ckb_tune_get("gemm_q6k_mma_shape", 0);         // 1: 8 row warps, 2: 4 x 2 K slices, 4: 2 x 4 K slices, 0: the widest CTA that fills 3/4 of the SMs
+    int shape = ckb_tune_get("gemm_q6k_mma_shape", 0);         // 1: 8 row warps, 2: 4 x 2 K slices, 4: 2 x 4 K slices, 0: the widest CTA that fills 3/4 of the slots
     if (shape != 1 && shape != 2 && shape != 4) {
         shape = 4;
         for (int cand = 1; cand < 4; cand *= 2) {
@@ -350,6 +377,9 @@ static int qm6_pick(const void *A_q8, const void *B, const float *bias, float *C
             if ((N + rows - 1) / rows >= want || nb < 2 * cand) { shape = cand; break; }
         }
         if (nb < 4 && shape == 4) shape = nb >= 2 ? 2 : 1;
+    }
+    if constexpr (NT <= 2) {
+        if (occ == 2) return qm6_shape_pair<NT>(shape, A_q8, B, bias, C, ldc, M, N, nb, st);
     }
     if constexpr (NT < 8) {
         if (rw == 2) return qm6_shape<NT, 2>(shape, A_q8, B, bias, C, ldc, M, N, nb, st);

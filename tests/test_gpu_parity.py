@@ -629,12 +629,13 @@ def test_gemm_nt_q6_k_planar_tensor_core(ck, orc, m, n, k, big_scales):
         assert_fp32_close(got, want, "q6_k planar gemm")
 
 
-@pytest.mark.parametrize("shape,rw", [(1, 2), (2, 2), (4, 2), (1, 1), (4, 1)])
+@pytest.mark.parametrize("shape,rw,occ", [(1, 2, 1), (2, 2, 1), (4, 2, 1), (1, 1, 1), (4, 1, 1), (1, 0, 2), (2, 0, 2), (4, 0, 2)])
 @pytest.mark.parametrize("m,n,k", [(4, 40, 1024), (8, 129, 1024), (9, 64, 2048), (16, 300, 4096), (32, 1000, 3072), (33, 77, 1024), (64, 260, 5120)])
-def test_gemm_nt_q6_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
+def test_gemm_nt_q6_k_integer_mma_small_batches(ck, orc, shape, rw, occ, m, n, k):
     """4 to 64 tokens over planar Q6_K weights run on the integer-MMA kernel (K a multiple of 1024): all four token-tile counts with
-    ragged token and row counts, the three CTA shapes, one and two 16-row tiles per warp, scales over the whole int8 range (exact
-    for every scale, unlike the fp16 operand of the tcgen05 kernel).  Two runs agree bit for bit."""
+    ragged token and row counts, the three CTA shapes, one and two 16-row tiles per warp, one CTA per SM and (up to 16 tokens) the
+    two-CTA form, scales over the whole int8 range (exact for every scale, unlike the fp16 operand of the tcgen05 kernel).  Two runs
+    agree bit for bit."""
     import torch
 
     dev = torch.device("cuda", 0)
@@ -656,6 +657,7 @@ def test_gemm_nt_q6_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
     try:
         ck.ckb200_tune_set(b"gemm_q6k_mma_shape", shape)
         ck.ckb200_tune_set(b"gemm_q6k_mma_rw", rw)
+        ck.ckb200_tune_set(b"gemm_q6k_mma_occ", occ)
         for _ in range(2):
             c = torch.full((m, n), float("nan"), device=dev)
             torch.cuda.synchronize()
@@ -668,6 +670,7 @@ def test_gemm_nt_q6_k_integer_mma_small_batches(ck, orc, shape, rw, m, n, k):
     finally:
         ck.ckb200_tune_set(b"gemm_q6k_mma_shape", 0)
         ck.ckb200_tune_set(b"gemm_q6k_mma_rw", 0)
+        ck.ckb200_tune_set(b"gemm_q6k_mma_occ", 0)
     assert_fp32_close(outs[0], want, "q6_k integer-MMA path")
     assert np.array_equal(outs[0], outs[1])
 

@@ -306,8 +306,11 @@ __global__ void __launch_bounds__(QM4_THREADS) gemm_q4k_mma_kernel(const uint8_t
 // and neither spreading the requests over the step nor a warp of its own for them helped).  Here one thread issues, per step and K
 // slice, ONE tiled copy for the 144-byte blocks of all the slice's rows (a box of 144 bytes x rows out of the matrix seen as
 // N rows of nb * 144 bytes) and one for the 304-byte windows of all tokens; rows past N and token slots past M are filled with
-// zeros by the copy itself.  Completion is counted on an mbarrier per stage; the waits are bounded.  Needs 16-byte-aligned
-// activation rows (K a multiple of 1024), otherwise the kernel above runs.
+// zeros by the copy itself.  That thread is the first lane of a ninth warp which does nothing else: completion is counted on a
+// `full` mbarrier per stage, each of the eight computing warps releases a stage on its `empty` mbarrier when it is done with it,
+// and there is no CTA-wide barrier inside the K loop (with the copies issued by a computing warp behind such a barrier, CTAs with
+// four K slices lost up to a third of their time at it).  All waits are bounded.  Needs 16-byte-aligned activation rows (K a
+// multiple of 1024), otherwise the kernel above runs.
 constexpr int QM4_XWIN = 16 * QM4_XCOPY;                       // 304 bytes: a 292-byte block from its 16-byte-aligned start
 
 __device__ __forceinline__ void qm4_tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)

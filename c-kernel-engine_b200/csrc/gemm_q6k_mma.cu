@@ -11,8 +11,10 @@
 //
 // The planes of a superblock arrive as four tiled bulk copies per step and K slice (ql with the 128-byte swizzle so that the eight
 // rows a fragment load touches fall into different banks; qh, scales and the 16-byte window around d as they lie), the Q8_K
-// windows of all tokens as a fifth; rows past N and token slots past M are zero-filled by the copies.  Needs K a multiple of 1024
-// and 16-byte-aligned activation rows (the tcgen05 kernel of gemm_tc.cu serves everything else).
+// windows of all tokens as a fifth; rows past N and token slots past M are zero-filled by the copies.  The copies are issued by
+// the first lane of a ninth warp; the eight computing warps wait for a stage on its `full` mbarrier and release it on its `empty`
+// one, so no warp waits for another inside the K loop.  Needs K a multiple of 1024 and 16-byte-aligned activation rows (the
+// tcgen05 kernel of gemm_tc.cu serves everything else).
 #include <cuda.h>
 
 #include "device_common.cuh"

@@ -929,6 +929,8 @@ int ckb200_model_decode(CKB200Model *m, const int32_t *tokens, float *logits_hos
 
 int ckb_launch_gemm_tc(int wf, const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, int min_tokens, void *stream);
 
+void ckb_gemm_tc_hint_same_activations(int on);              /* gemm_tc.cu */
+
 static int prefill_ok(const CKB200Model *m, int T)
 {
     if (m->c.batch != 1 || m->c.tp_size != 1 || m->kv_eb != 4 || T < 16 || m->host_pos != 0 || T > m->c.max_seq_len || !ckb_tune_get("model_prefill", 1)) return 0;
@@ -982,8 +984,11 @@ static int issue_prefill(CKB200Model *m, int T, void *st)
         float *kc = (float *)kv_at(m, l, 0), *vc = (float *)kv_at(m, l, 1);
         if ((rc = ckb200_dev_add_rmsnorm_q8k(m->pf_x, delta, (const float *)t[CKB_T_LN1].w, m->pf_hq, NULL, T, m->D, m->Da, c->rms_eps, st))) return rc;
         if ((rc = prefill_gemm(&t[CKB_T_WQ], m->pf_hq, m->pf_q, m->Al, T, st))) return rc;
-        if ((rc = prefill_gemm(&t[CKB_T_WK], m->pf_hq, m->pf_k, kvw, T, st))) return rc;
-        if ((rc = prefill_gemm(&t[CKB_T_WV], m->pf_hq, m->pf_v, kvw, T, st))) return rc;
+        ckb_gemm_tc_hint_same_activations(1);                  /* k and v read the rows q read: one set of operand tiles */
+        rc = prefill_gemm(&t[CKB_T_WK], m->pf_hq, m->pf_k, kvw, T, st);
+        if (!rc) rc = prefill_gemm(&t[CKB_T_WV], m->pf_hq, m->pf_v, kvw, T, st);
+        ckb_gemm_tc_hint_same_activations(0);
+        if (rc) return rc;
         if ((rc = ckb200_dev_prefill_rope_scatter(m->pf_q, m->pf_k, m->pf_v, m->pf_qh, kc, vc, m->rope_cos, m->rope_sin, T, m->Hl, m->Hkvl, m->d, c->max_seq_len, 0, st))) return rc;
         if ((rc = ckb200_dev_attention_prefill(m->pf_qh, kc, vc, m->pf_oh, m->Hl, m->Hkvl, T, m->d, m->d, c->max_seq_len, 1, st))) return rc;
         if ((rc = ckb200_dev_prefill_gather_q8k(m->pf_oh, m->pf_aq, T, m->Hl, m->d, m->Ala, st))) return rc;

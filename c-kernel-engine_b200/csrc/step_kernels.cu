@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_q80_kernel(float *__restrict
     arq_norm_quant_q80(ss, row, red, gamma, out_q80, t, d_model, cols, eps);
 }
 
-// one warp per 256-element block of the output: out = silu(gate) * up, quantised to Q8_K
+// one warp per 256-element block of the output: out = silu(gate) * up, quantised to Q8_K (VEC: gate_up is 16-byte aligned)
+template <bool VEC>
 __global__ void __launch_bounds__(128) swiglu_q8k_kernel(const float *__restrict__ gate_up, uint8_t *__restrict__ out_q8, int tokens, int dim)
 {
     pdl_trigger();
@@ -99,12 +100,23 @@ __global__ void __launch_bounds__(128) swiglu_q8k_kernel(const float *__restrict
     const int t = (int)(blk / nb), b = (int)(blk - (long long)t * nb);
     const float *g = gate_up + (size_t)t * 2 * dim + (size_t)b * QK_K + 8 * lane;
     const float *u = g + dim;
+    // a lane's 32 bytes as two 16-byte loads through L1 (the second finds the sector the first brought): eight 4-byte loads at a
+    // 32-byte stride asked L2 for every sector eight times
+    float gs[8], us[8];
+    if (VEC) {
+        const float4 g0 = *reinterpret_cast<const float4 *>(g), g1 = *reinterpret_cast<const float4 *>(g + 4);
+        const float4 u0 = *reinterpret_cast<const float4 *>(u), u1 = *reinterpret_cast<const float4 *>(u + 4);
+        gs[0] = g0.x; gs[1] = g0.y; gs[2] = g0.z; gs[3] = g0.w; gs[4] = g1.x; gs[5] = g1.y; gs[6] = g1.z; gs[7] = g1.w;
+        us[0] = u0.x; us[1] = u0.y; us[2] = u0.z; us[3] = u0.w; us[4] = u1.x; us[5] = u1.y; us[6] = u1.z; us[7] = u1.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { gs[j] = __ldcg(g + j); us[j] = __ldcg(u + j); }
+    }
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const float gv = __ldcg(g + j);
-        const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gv)));
-        v[j] = __fmul_rn(__fmul_rn(gv, sg), __ldcg(u + j));
+        const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gs[j])));
+        v[j] = __fmul_rn(__fmul_rn(gs[j], sg), us[j]);
     }
     quantize_block_q8k(v, out_q8 + blk * Q8K_BYTES, lane);
 }
@@ -283,7 +295,10 @@ extern "C" int ckb200_dev_swiglu_q8k(const float *gate_up, void *out_q8, int tok
     if (dim % QK_K) return ckb_fail(CKB_ERR_SHAPE, "swiglu_q8k: dim %d is not a multiple of 256", dim);
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     const long long nblocks = (long long)tokens * (dim / QK_K);
-    return launch_pdl("swiglu_q8k", swiglu_q8k_kernel, dim3((unsigned)((nblocks + 3) / 4)), dim3(128), 0, ckb_stream(stream), gate_up,
+    if (((uintptr_t)gate_up & 15) == 0)
+        return launch_pdl("swiglu_q8k", swiglu_q8k_kernel<true>, dim3((unsigned)((nblocks + 3) / 4)), dim3(128), 0, ckb_stream(stream), gate_up,
+                          (uint8_t *)out_q8, tokens, dim);
+    return launch_pdl("swiglu_q8k", swiglu_q8k_kernel<false>, dim3((unsigned)((nblocks + 3) / 4)), dim3(128), 0, ckb_stream(stream), gate_up,
                       (uint8_t *)out_q8, tokens, dim);
 }
 

@@ -808,3 +808,32 @@ def test_registered_weights_in_unaligned_formats_get_a_planar_copy(ck, orc, fmt,
     finally:
         assert ck.ckb200_unregister_weights(cases.vptr(w)) == 0
     assert_fp32_close(cases.gemv(ck, "", fmt, w, xq, m, k), want, fmt + " after unregister")
+
+
+@pytest.mark.parametrize("tokens,dim", [(1, 256), (3, 1024), (17, 4864)])
+def test_swiglu_q8k_aligned_and_unaligned_inputs(ck, orc, tokens, dim):
+    """swiglu_q8k (swiglu_forward + quantize_row_q8_k in one kernel) reads a 16-byte-aligned input with vector loads and any
+    other with 4-byte loads: both give the same bytes, and the blocks decode to the oracle's swiglu within the Q8_K step."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(tokens * 1000 + dim)
+    gu = (2.0 * rng.standard_normal((tokens, 2 * dim))).astype(np.float32)
+    want = cases.swiglu(orc, "oracle_", gu, dim)
+    nb = dim // 256
+    outs = []
+    for off in (0, 1):
+        buf = torch.zeros(tokens * 2 * dim + 4, dtype=torch.float32, device=dev)
+        buf[off:off + tokens * 2 * dim] = torch.from_numpy(gu.reshape(-1)).to(dev)
+        q = torch.zeros(tokens * nb * 292, dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+        assert ck.ckb200_dev_swiglu_q8k(C.c_void_p(buf.data_ptr() + 4 * off), C.c_void_p(q.data_ptr()), tokens, dim, None) == 0
+        assert ck.ckb200_synchronize() == 0
+        outs.append(q.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    blocks = outs[0].reshape(tokens, nb, 292)
+    d = blocks[:, :, :4].copy().view(np.float32).reshape(tokens, nb, 1)
+    qs = blocks[:, :, 4:260].view(np.int8).astype(np.float32)
+    got = (d * qs).reshape(tokens, dim)
+    step = np.abs(np.repeat(d.reshape(tokens, nb), 256, axis=1))            # Q8_K's d carries the sign of the block's largest element
+    assert np.all(np.abs(got - want) <= 0.51 * step + 1e-4 * np.abs(want) + 1e-6)

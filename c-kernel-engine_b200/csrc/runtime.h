@@ -9,7 +9,7 @@
 extern "C" {
 #endif
 
-enum { CKB_SLOT_W = 0, CKB_SLOT_X = 1, CKB_SLOT_Y = 2, CKB_SLOT_A = 3, CKB_SLOT_B = 4, CKB_SLOT_C = 5, CKB_SLOT_T = 6, CKB_SLOT_G = 7, CKB_SLOT_P = 8, CKB_NSLOTS = 9 };
+enum { CKB_SLOT_W = 0, CKB_SLOT_X = 1, CKB_SLOT_Y = 2, CKB_SLOT_A = 3, CKB_SLOT_B = 4, CKB_SLOT_C = 5, CKB_SLOT_T = 6, CKB_SLOT_G = 7, CKB_SLOT_P = 8, CKB_SLOT_S = 9, CKB_NSLOTS = 10 };
 
 int ckb_ensure_init(void);                 /* 0 or CKB_ERR_NO_DEVICE; initialises on first use */
 int ckb_sm_count(void);

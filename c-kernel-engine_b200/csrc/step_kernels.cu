@@ -254,6 +254,8 @@ extern "C" int ckb200_dev_add_rmsnorm_q8k(float *x, const float *delta, const fl
     if (((uintptr_t)x | (uintptr_t)delta) & 15) return ckb_fail(CKB_ERR_ALIGN, "add_rmsnorm_q8k: x and delta must be 16-byte aligned");
     int threads = (aligned_embed_dim / 4 + 31) & ~31;          // one 16-byte piece per thread while that fits a CTA
     if (threads > 1024) threads = 1024;
+    // many rows (a prompt): four pieces per thread, so that several rows share an SM instead of one 1024-thread CTA at a time
+    if (tokens >= 64 && ckb_tune_get("add_rmsnorm_rows_narrow", 1)) { threads = ((aligned_embed_dim / 4 + ARQ_MAX_V4 - 1) / ARQ_MAX_V4 + 31) & ~31; if (threads < 128) threads = 128; }
     const size_t smem = (size_t)aligned_embed_dim * sizeof(float);
     if (smem > 48 * 1024) {
         static size_t set = 0;

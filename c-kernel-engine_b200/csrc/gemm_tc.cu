@@ -587,7 +587,11 @@ static int launch_tc(const void *A_q8, const void *B, const float *bias, float *
         attr_set = 1;
     }
     const int mtiles = (M + NT - 1) / NT, ntiles = (N + TC_ROWS - 1) / TC_ROWS;
-    int Z = M <= 128 && ckb_tune_get("gemm_tc_splitk", 1) ? tc_pick_slices(ntiles * mtiles, nb, ckb_sm_count() * Cfg::CTAS_PER_SM) : 1;
+    // K is split for a handful of tokens, and for any product whose tiles leave more than half of the SMs without a CTA (the k and
+    // v projections of a prompt: 8 x 4 tiles)
+    const int slots = ckb_sm_count() * Cfg::CTAS_PER_SM;
+    const int splitk = ckb_tune_get("gemm_tc_splitk", 1);
+    int Z = splitk && (M <= 128 || (splitk != 2 && 2 * ntiles * mtiles <= slots)) ? tc_pick_slices(ntiles * mtiles, nb, slots) : 1;
     const int forced = ckb_tune_get("gemm_tc_slices", 0);
     if (forced > 0 && forced <= nb) Z = forced;
     const int nbz = (nb + Z - 1) / Z;

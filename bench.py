@@ -88,23 +88,35 @@ class ClockSampler:
 
     def __init__(self, gpu: int):
         self.proc = None
+        self.lines = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
-            pass
+            return
+        import threading
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def count(self) -> int:
+        return len(self.lines)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if not self.proc:
             return out
-        time.sleep(0.15)
         self.proc.terminate()
         try:
-            text, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-            return out
+        self.thread.join(timeout=2)
+        text = "".join(self.lines)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in text.strip().splitlines():
@@ -412,19 +424,28 @@ def run_cuda(args, rank: int, world: int, local_rank: int):
         with torch.cuda.graph(graph, stream=stream):
             step(nstreams=args.streams)
         lib.ckb200_tune_set(b"gemv_occ_cap", 0)
+        sampler = ClockSampler(local_rank) if name == "q4_k" else None
         for _ in range(args.warmup):
             graph.replay()
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
-        sampler = ClockSampler(local_rank) if name == "q4_k" else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
             graph.replay()
         e1.record(stream)
         torch.cuda.synchronize()
-        clocks = sampler.stop() if sampler else None
+        clocks = None
+        if sampler:
+            # the timed region is a few milliseconds, the sampler's period 100 ms (and nvidia-smi needs a moment to start): the same
+            # step keeps running, untimed, until the sampler has seen it three times
+            t_load = time.time()
+            while sampler.proc and sampler.count() < 3 and time.time() - t_load < 4.0:
+                for _ in range(20):
+                    graph.replay()
+                torch.cuda.synchronize()
+            clocks = sampler.stop()
         ms = e0.elapsed_time(e1)
         if dist:
             t = torch.tensor([ms], device=dev)

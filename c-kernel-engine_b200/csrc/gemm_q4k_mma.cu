@@ -574,12 +574,19 @@ static int qm4_pick(const void *A_q8, const void *B, const float *bias, float *C
 using namespace ckb;
 
 // Returns -1 when this kernel does not take the call (token count, alignment, switched off): the caller falls through to its other paths.
+// Whether the launcher below takes this product (a caller that wants to run several products side by side asks first: this
+// kernel needs no workspace, the tcgen05 kernel shares one).
+extern "C" int ckb_gemm_q4k_mma_takes(const void *A_q8, const void *B, int M, int N, int K)
+{
+    if (!A_q8 || !B || N <= 0 || K <= 0 || K % QK_K) return 0;
+    // from 2 tokens up one pass of this kernel beats a GEMV per token (measured: up to 8 tokens cost about 1.2 GEMVs on the 57344 x 8192 shape)
+    if (M < ckb_tune_get("gemm_q4k_mma_min", 2) || M > ckb_tune_get("gemm_q4k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q4k_mma", 1)) return 0;
+    return !(((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3));
+}
+
 extern "C" int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream)
 {
-    if (!A_q8 || !B || !C || N <= 0 || K <= 0 || K % QK_K) return -1;
-    // from 2 tokens up one pass of this kernel beats a GEMV per token (measured: up to 8 tokens cost about 1.2 GEMVs on the 57344 x 8192 shape)
-    if (M < ckb_tune_get("gemm_q4k_mma_min", 2) || M > ckb_tune_get("gemm_q4k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q4k_mma", 1)) return -1;
-    if (((uintptr_t)B & 15) || ((uintptr_t)A_q8 & 3)) return -1;
+    if (!C || !ckb_gemm_q4k_mma_takes(A_q8, B, M, N, K)) return -1;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);
     const int nb = K / QK_K;

@@ -394,11 +394,17 @@ static int qm6_pick(const void *A_q8, const void *B, const float *bias, float *C
 using namespace ckb;
 
 // B_planar: ckb200_q6_k_planar_bytes(N, K) of row-planar Q6_K weights.  Returns -1 when this kernel does not take the call.
+// Whether the launcher below takes this product (for a caller that runs several products side by side: no workspace here).
+extern "C" int ckb_gemm_q6k_mma_takes(const void *A_q8, const void *B_planar, int M, int N, int K)
+{
+    if (!A_q8 || !B_planar || N <= 0 || K <= 0 || K % 1024) return 0;
+    if (M < ckb_tune_get("gemm_q6k_mma_min", 2) || M > ckb_tune_get("gemm_q6k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q6k_mma", 1)) return 0;
+    return !(((uintptr_t)B_planar & 15) || ((uintptr_t)A_q8 & 15));
+}
+
 extern "C" int ckb_launch_gemm_q6k_mma(const void *A_q8, const void *B_planar, const float *bias, float *C, int ldc, int M, int N, int K, void *stream)
 {
-    if (!A_q8 || !B_planar || !C || N <= 0 || K <= 0 || K % 1024) return -1;
-    if (M < ckb_tune_get("gemm_q6k_mma_min", 2) || M > ckb_tune_get("gemm_q6k_mma_max", 64) || M > 64 || !ckb_tune_get("gemm_q6k_mma", 1)) return -1;
-    if (((uintptr_t)B_planar & 15) || ((uintptr_t)A_q8 & 15)) return -1;
+    if (!C || !ckb_gemm_q6k_mma_takes(A_q8, B_planar, M, N, K)) return -1;
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     cudaStream_t st = ckb_stream(stream);
     const int nb = K / QK_K;

@@ -45,6 +45,8 @@ size_t ckb_gemm_tc_workspace_bytes(int M, int N, int K);
 /* integer-MMA kernel of gemm_q4k_mma.cu for up to 64 tokens (Q4_K rows, no workspace); -1 when it does not take the call */
 int ckb_launch_gemm_q4k_mma(const void *A_q8, const void *B, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);
 int ckb_launch_gemm_q6k_mma(const void *A_q8, const void *B_planar, const float *bias, float *C, int ldc, int M, int N, int K, void *stream);   /* gemm_q6k_mma.cu */
+int ckb_gemm_q4k_mma_takes(const void *A_q8, const void *B, int M, int N, int K);
+int ckb_gemm_q6k_mma_takes(const void *A_q8, const void *B_planar, int M, int N, int K);
 
 /* From this many sequences a projection runs as one batched product instead of a GEMV per sequence.  The tcgen05 kernel's time
  * hardly depends on the token count below 32 (it is bound by expanding the weights), so for the Q6_K matrices it wins from about
@@ -491,6 +493,17 @@ static int gemv_q(int fmt, float *y, const Tensor *w, const void *xq, void *st)
 }
 
 
+/* A product of matvec() that uses no shared workspace: a per-sequence GEMV, or a batch on the integer-MMA kernels.  Such products
+ * may run side by side on the side streams. */
+static int matvec_standalone(const CKB200Model *m, const Tensor *w, const uint8_t *xq)
+{
+    const int B = m->c.batch;
+    if (B < MODEL_GEMM_MIN_BATCH) return 1;
+    if (w->fmt == FMT_Q4K) return ckb_gemm_q4k_mma_takes(xq, w->w, B, w->rows, w->cols);
+    if (w->fmt == FMT_Q6K && w->planar) return ckb_gemm_q6k_mma_takes(xq, w->planar, B, w->rows, w->cols);
+    return 0;
+}
+
 /* y[b] = W . xq[b] for every sequence b; xq rows are `cols`-wide quantised vectors */
 static int matvec(CKB200Model *m, const Tensor *w, const uint8_t *xq, float *y, int y_stride, void *st)
 {
@@ -809,7 +822,9 @@ static int issue_step(CKB200Model *m, void *st)
         if ((rc = reduce_norm_quant(m, delta, &t[CKB_T_LN1], &t[CKB_T_WQ], st))) return rc;
         if (fmt_block32(t[CKB_T_WK].fmt) != fmt_block32(t[CKB_T_WQ].fmt) || fmt_block32(t[CKB_T_WV].fmt) != fmt_block32(t[CKB_T_WQ].fmt))
             return ckb_fail(CKB_ERR_STATE, "model step: q/k/v must share the activation format (all K-quant or all Q8_0)");
-        if (ckb_tune_get("model_qkv_streams", 1) && B < MODEL_GEMM_MIN_BATCH) {     /* the batched GEMMs share one workspace: keep them in order */
+        /* q, k and v side by side, unless one of them is a batched product on the tcgen05 kernel: those share one workspace */
+        if (ckb_tune_get("model_qkv_streams", 1) && matvec_standalone(m, &t[CKB_T_WQ], m->hq) && matvec_standalone(m, &t[CKB_T_WK], m->hq) &&
+            matvec_standalone(m, &t[CKB_T_WV], m->hq)) {
             cudaStream_t main_st = (cudaStream_t)st;
             if (ckb_check_cuda((int)cudaEventRecord(m->ev_fork, main_st), "fork")) return CKB_ERR_CUDA;
             if ((rc = matvec(m, &t[CKB_T_WQ], m->hq, m->q, m->Al, st))) return rc;

@@ -615,7 +615,23 @@ static int launch_tc(const void *A_q8, const void *B, const float *bias, float *
     if (forced > 0 && forced <= nb) Z = forced;
     const int nbz = (nb + Z - 1) / Z;
     Z = (nb + nbz - 1) / nbz;                          // no empty slice
-    const size_t xt_bytes = ((size_t)mtiles * nb * Cfg::XBLOB + 255) & ~(size_t)255, part_bytes = Z > 1 ? (size_t)Z * M * N * sizeof(float) : 0;
+    // A grid of whole waves plus a few CTAs pays a full wave for those few (28672 x 4096 at 512 tokens: 896 tiles = 6 waves of 148
+    // and 8 tiles).  The row tiles behind that remainder then go to a second launch with K split, which fills the SMs for a
+    // fraction of a wave; its partial sums are added as for any split.  Library workspace only (a caller's workspace is sized
+    // for one launch).
+    int tail_nt = 0, Zt = 1;
+    if (Z == 1 && !ws && ckb_tune_get("gemm_tc_tail", 1)) {
+        const int tiles = ntiles * mtiles, rem = tiles % slots;
+        if (tiles > slots && rem > 0 && 4 * rem <= slots && rem % mtiles == 0 && rem / mtiles < ntiles && N % TC_ROWS == 0) {
+            Zt = tc_pick_slices(rem, nb, slots);
+            if (Zt > 1) tail_nt = rem / mtiles;
+        }
+    }
+    const int nbzt = (nb + Zt - 1) / Zt;
+    if (tail_nt) Zt = (nb + nbzt - 1) / nbzt;
+    const int Nt = tail_nt * TC_ROWS;                  // rows (output columns) of the tail launch
+    const size_t xt_bytes = ((size_t)mtiles * nb * Cfg::XBLOB + 255) & ~(size_t)255;
+    const size_t part_bytes = Z > 1 ? (size_t)Z * M * N * sizeof(float) : (tail_nt ? (size_t)Zt * M * Nt * sizeof(float) : 0);
     // A caller that records the launch in a CUDA graph brings its own workspace: the library's pool may be freed and
     // regrown by any later call that needs more, which would leave a captured pointer dangling.
     if (ws && xt_bytes + part_bytes > ws_bytes)
@@ -633,10 +649,22 @@ static int launch_tc(const void *A_q8, const void *B, const float *bias, float *
         if (int rc = ckb_check_launch("gemm_x_tiles")) return rc;
         g_tc_tiles.a = A_q8; g_tc_tiles.M = M; g_tc_tiles.nb = nb; g_tc_tiles.nt = NT; g_tc_tiles.xt = xt; g_tc_tiles.st = st;
     }
-    const dim3 grid(ntiles, mtiles, Z);
+    const dim3 grid(ntiles - tail_nt, mtiles, Z);
     if (Z == 1) {
-        kernel<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B, bias, C, ldc, (size_t)0, M, N, nb, nbz, ckb_device_error_word());
-        return ckb_check_launch("gemm_kq_tc");
+        kernel<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B, bias, C, ldc, (size_t)0, M, N - Nt, nb, nbz, ckb_device_error_word());
+        if (int rc = ckb_check_launch("gemm_kq_tc")) return rc;
+        if (!tail_nt) return 0;
+        const int n0 = N - Nt;
+        const size_t rb = WF == TC_W_Q4K ? (size_t)nb * Q4K_BYTES : (((size_t)nb * Q6K_BYTES + 15) & ~(size_t)15);
+        kernel<<<dim3(tail_nt, mtiles, Zt), Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B + (size_t)n0 * rb, nullptr, part, Nt, (size_t)M * Nt, M, Nt, nb, nbzt,
+                                                                         ckb_device_error_word());
+        if (int rc = ckb_check_launch("gemm_kq_tc tail")) return rc;
+        const size_t mnt = (size_t)M * Nt;
+        const unsigned tb = (unsigned)((mnt + 1023) / 1024 < 1184 ? (mnt + 1023) / 1024 : 1184);
+        const float *bt = bias ? bias + n0 : nullptr;
+        if (ldc % 4 == 0 && (((uintptr_t)(C + n0) | (uintptr_t)bt) & 15) == 0) gemm_splitk_sum_kernel<true><<<tb, 256, 0, st>>>(part, Zt, bt, C + n0, ldc, M, Nt);
+        else gemm_splitk_sum_kernel<false><<<tb, 256, 0, st>>>(part, Zt, bt, C + n0, ldc, M, Nt);
+        return ckb_check_launch("gemm_splitk_sum");
     }
     kernel<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(xt, (const uint8_t *)B, nullptr, part, N, (size_t)M * N, M, N, nb, nbz, ckb_device_error_word());
     if (int rc = ckb_check_launch("gemm_kq_tc")) return rc;

@@ -302,6 +302,37 @@ def test_gemm_tensor_core_split_k(ck, orc, fmt, m, small_max, slices):
     assert np.array_equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
+def test_gemm_nt_tensor_core_tail_launch(ck, orc, fmt):
+    """A tile grid of whole waves plus a few tiles (150 tiles on 148 SMs) sends the last row tile to a second launch with K split:
+    same results within fp32 rounding, two launches more than with the switch off, two runs bit-identical."""
+    m, n, k = 130, 9600, 2048
+    w = synth.make_weights(fmt, n, k, seed=5)
+    a = synth.make_x(k, seed=6, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", fmt, a, rows=m)
+    bias = np.random.default_rng(7).standard_normal(n).astype(np.float32)
+    want = cases.gemm_nt(orc, "oracle_", fmt, aq, w, bias, m, n, k)
+    ck.ckb200_launch_count.restype = C.c_longlong
+    n0 = ck.ckb200_launch_count()
+    got = cases.gemm_nt(ck, "", fmt, aq, w, bias, m, n, k)
+    with_tail = ck.ckb200_launch_count() - n0
+    again = cases.gemm_nt(ck, "", fmt, aq, w, bias, m, n, k)
+    try:
+        ck.ckb200_tune_set(b"gemm_tc_tail", 0)
+        n0 = ck.ckb200_launch_count()
+        plain = cases.gemm_nt(ck, "", fmt, aq, w, bias, m, n, k)
+        without = ck.ckb200_launch_count() - n0
+    finally:
+        ck.ckb200_tune_set(b"gemm_tc_tail", 1)
+    assert_fp32_close(got, want, f"{fmt} tail launch")
+    assert_fp32_close(plain, want, f"{fmt} single launch")
+    assert np.array_equal(got, again)
+    import torch
+
+    if torch.cuda.get_device_properties(0).multi_processor_count == 148:
+        assert with_tail == without + 2, (with_tail, without)
+
+
 @pytest.mark.parametrize("m", [64, 128])
 def test_gemm_nt_q4_k_tensor_core_extreme_values(ck, orc, m):
     """Largest scales, nibbles and activations: the integer sums reach the top of the fp32-exact range (both tile widths)."""

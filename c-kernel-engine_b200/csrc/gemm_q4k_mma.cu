@@ -563,6 +563,41 @@ static int qm4_pick(const void *A_q8, const void *B, const float *bias, float *C
         shape = qm4_auto_shape(16 * rw, N, nb, narrow && rw == 1 ? 2 * want : want);       // small CTAs: two per SM wanted (8192 x 8192, 8 tokens: 9.8 us against 16.1)
         if (shape == 1 && narrow && rw == 1 && nb >= 32) shape = 2;
     }
+    // From 17 tokens up a CTA fills its SM, so a grid of whole waves plus a part of one pays a whole wave for the part (57344 rows
+    // in CTAs of 256 on 148 SMs: 148 + 76).  The rows behind the whole waves then go to a second launch in smaller CTAs (one tile
+    // per warp), which spreads them over all SMs.
+    if constexpr (NT >= 4) {
+        const int sms = ckb_sm_count();
+        const bool tail_on = ckb_tune_get("gemm_q4k_mma_tail", 1) != 0;
+        if (tail_on && ckb_tune_get("gemm_q4k_mma_shape", 0) == 0) {
+            // time of a shape ~ rows per CTA x (whole waves + the last, partial one; a small remainder costs little once it is a tail
+            // launch), with 8 % per halving of the CTA for the activation traffic and pipeline starts that grow with the CTA count
+            // (57344 x 8192, 32 tokens: 224 CTAs of 256 rows 114 us, 448 of 128 with a 4-CTA tail 109 us)
+            double best_cost = 0.0;
+            int best_shape = shape;
+            for (int cand = shape, halvings = 0; cand <= 4 && nb >= 2 * cand; cand *= 2, ++halvings) {
+                const int rows_c = 16 * rw * 8 / cand, ctas_c = (N + rows_c - 1) / rows_c, rem_c = ctas_c % sms;
+                if (cand == shape && ctas_c <= sms) break;                 // one wave: nothing to gain
+                const double last = rem_c == 0 ? 0.0 : (4 * rem_c <= sms && N % rows_c == 0 ? 0.3 : 1.0);
+                const double cost = (double)rows_c * ((double)(ctas_c / sms) + last) * (1.0 + 0.08 * halvings);
+                if (best_cost == 0.0 || cost < best_cost) { best_cost = cost; best_shape = cand; }
+            }
+            shape = best_shape;
+        }
+        const int rows = 16 * rw * 8 / shape, ctas = (N + rows - 1) / rows, rem = ctas % sms;
+        if (tail_on && ctas > sms && N % rows == 0 && rem > 0 && 4 * rem <= sms) {
+            const int n_main = (ctas - rem) * rows, n_tail = N - n_main;
+            int rc;
+            if constexpr (NT < 8) {
+                rc = rw == 2 ? qm4_shape<NT, 2>(shape, A_q8, B, bias, C, ldc, M, n_main, nb, st) : qm4_shape<NT, 1>(shape, A_q8, B, bias, C, ldc, M, n_main, nb, st);
+            } else {
+                rc = qm4_shape<NT, 1>(shape, A_q8, B, bias, C, ldc, M, n_main, nb, st);
+            }
+            if (rc) return rc;
+            const int shape_t = qm4_auto_shape(16, n_tail, nb, want);
+            return qm4_shape<NT, 1>(shape_t, A_q8, (const uint8_t *)B + (size_t)n_main * nb * Q4K_BYTES, bias ? bias + n_main : nullptr, C + n_main, ldc, M, n_tail, nb, st);
+        }
+    }
     if constexpr (NT < 8) {
         if (rw == 2) return qm4_shape<NT, 2>(shape, A_q8, B, bias, C, ldc, M, N, nb, st);
     }

@@ -302,6 +302,40 @@ def test_gemm_tensor_core_split_k(ck, orc, fmt, m, small_max, slices):
     assert np.array_equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("m", [17, 40])
+def test_gemm_nt_q4_k_integer_mma_tail_launch(ck, orc, m):
+    """From 17 tokens up the rows behind whole waves of CTAs go to a second launch in smaller CTAs: 150 CTAs of 32 rows on 148 SMs
+    leave 64 rows for it.  Same results within fp32 rounding as one launch; bit-identical between runs."""
+    import torch
+
+    n, k = 4800, 1024
+    w = synth.make_weights("q4_k", n, k, seed=m)
+    a = synth.make_x(k, seed=m + 1, rows=m)
+    aq = cases.quantize_act(orc, "oracle_", "q4_k", a, rows=m)
+    bias = np.random.default_rng(m).standard_normal(n).astype(np.float32)
+    want = cases.gemm_nt(orc, "oracle_", "q4_k", aq, w, bias, m, n, k)
+    ck.ckb200_launch_count.restype = C.c_longlong
+    try:
+        ck.ckb200_tune_set(b"gemm_q4k_mma_shape", 4)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_rw", 1)
+        n0 = ck.ckb200_launch_count()
+        got = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+        launches = ck.ckb200_launch_count() - n0
+        again = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_tail", 0)
+        single = cases.gemm_nt(ck, "", "q4_k", aq, w, bias, m, n, k)
+    finally:
+        ck.ckb200_tune_set(b"gemm_q4k_mma_shape", 0)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_rw", 0)
+        ck.ckb200_tune_set(b"gemm_q4k_mma_tail", 1)
+    assert_fp32_close(got, want, "q4_k integer-MMA tail launch")
+    assert_fp32_close(single, want, "q4_k integer-MMA single launch")
+    assert np.array_equal(got, again)
+    if torch.cuda.get_device_properties(0).multi_processor_count == 148:
+        assert launches == 2, launches
+        assert np.array_equal(got[:, :4736], single[:, :4736])      # the rows of the whole waves come from the same CTAs either way
+
+
 @pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
 def test_gemm_nt_tensor_core_tail_launch(ck, orc, fmt):
     """A tile grid of whole waves plus a few tiles (150 tiles on 148 SMs) sends the last row tile to a second launch with K split:

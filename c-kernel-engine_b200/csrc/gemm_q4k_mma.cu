@@ -565,7 +565,8 @@ static int qm4_pick(const void *A_q8, const void *B, const float *bias, float *C
     }
     // From 17 tokens up a CTA fills its SM, so a grid of whole waves plus a part of one pays a whole wave for the part (57344 rows
     // in CTAs of 256 on 148 SMs: 148 + 76).  The rows behind the whole waves then go to a second launch in smaller CTAs (one tile
-    // per warp), which spreads them over all SMs.
+    // per warp), which spreads them over all SMs.  (Up to 16 tokens several CTAs share an SM and start as others end: there the
+    // same tail launch measured slower, 58 against 55 us at 8 tokens on the same matrix.)
     if constexpr (NT >= 4) {
         const int sms = ckb_sm_count();
         const bool tail_on = ckb_tune_get("gemm_q4k_mma_tail", 1) != 0;

@@ -48,6 +48,47 @@ __global__ void __launch_bounds__(256) prefill_rope_scatter_kernel(const float *
     }
 }
 
+// The same with four rotation pairs per thread (16-byte accesses): d a multiple of 8, all pointers 16-byte aligned.
+__global__ void __launch_bounds__(256) prefill_rope_scatter_v4_kernel(const float *__restrict__ q_tm, const float *__restrict__ k_tm, const float *__restrict__ v_tm,
+                                                                      float *__restrict__ q_hm, float *__restrict__ kc, float *__restrict__ vc,
+                                                                      const float *__restrict__ cos_cache, const float *__restrict__ sin_cache, int T, int H,
+                                                                      int Hkv, int d, int max_seq, int pos0)
+{
+    const int half = d / 2, q4 = half / 4;
+    const long long per_tok = (long long)(H + 2 * Hkv) * q4, n = (long long)T * per_tok;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / per_tok), r = (int)(i - (long long)t * per_tok);
+        const int h = r / q4, j = 4 * (r - h * q4), pos = pos0 + t;
+        if (pos >= max_seq) continue;
+        const float *src;
+        float *dst;
+        if (h < H) {
+            src = q_tm + ((size_t)t * H + h) * d;
+            dst = q_hm + ((size_t)h * T + t) * d;
+        } else if (h < H + Hkv) {
+            src = k_tm + ((size_t)t * Hkv + (h - H)) * d;
+            dst = kc + ((size_t)(h - H) * max_seq + pos) * d;
+        } else {
+            src = v_tm + ((size_t)t * Hkv + (h - H - Hkv)) * d;
+            dst = vc + ((size_t)(h - H - Hkv) * max_seq + pos) * d;
+        }
+        const float4 a = *reinterpret_cast<const float4 *>(src + j), b = *reinterpret_cast<const float4 *>(src + j + half);
+        if (h >= H + Hkv) {
+            *reinterpret_cast<float4 *>(dst + j) = a;
+            *reinterpret_cast<float4 *>(dst + j + half) = b;
+            continue;
+        }
+        const float4 c = *reinterpret_cast<const float4 *>(cos_cache + (size_t)pos * half + j), sn = *reinterpret_cast<const float4 *>(sin_cache + (size_t)pos * half + j);
+        float4 lo, hi;
+        lo.x = __fsub_rn(__fmul_rn(a.x, c.x), __fmul_rn(b.x, sn.x)); hi.x = __fadd_rn(__fmul_rn(a.x, sn.x), __fmul_rn(b.x, c.x));
+        lo.y = __fsub_rn(__fmul_rn(a.y, c.y), __fmul_rn(b.y, sn.y)); hi.y = __fadd_rn(__fmul_rn(a.y, sn.y), __fmul_rn(b.y, c.y));
+        lo.z = __fsub_rn(__fmul_rn(a.z, c.z), __fmul_rn(b.z, sn.z)); hi.z = __fadd_rn(__fmul_rn(a.z, sn.z), __fmul_rn(b.z, c.z));
+        lo.w = __fsub_rn(__fmul_rn(a.w, c.w), __fmul_rn(b.w, sn.w)); hi.w = __fadd_rn(__fmul_rn(a.w, sn.w), __fmul_rn(b.w, c.w));
+        *reinterpret_cast<float4 *>(dst + j) = lo;
+        *reinterpret_cast<float4 *>(dst + j + half) = hi;
+    }
+}
+
 // one warp per (token, 256-element block): lane l takes elements 8l .. 8l+7 of the block (d is a multiple of 8, so they lie in one head)
 __global__ void __launch_bounds__(256) prefill_gather_q8k_kernel(const float *__restrict__ out_hm, uint8_t *__restrict__ aq, int T, int H, int d, int cols)
 {
@@ -80,6 +121,15 @@ extern "C" int ckb200_dev_prefill_rope_scatter(const float *q_tm, const float *k
     if (head_dim % 2 || pos0 < 0) return ckb_fail(CKB_ERR_SHAPE, "prefill_rope_scatter: head_dim %d, pos0 %d", head_dim, pos0);
     if (ckb_ensure_init()) return CKB_ERR_NO_DEVICE;
     const long long n = (long long)tokens * (num_heads + 2 * num_kv_heads) * (head_dim / 2);
+    const uintptr_t all = (uintptr_t)q_tm | (uintptr_t)k_tm | (uintptr_t)v_tm | (uintptr_t)q_hm | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_cache |
+                          (uintptr_t)sin_cache;
+    if (head_dim % 8 == 0 && (all & 15) == 0) {
+        const long long n4 = n / 4;
+        const unsigned g4 = (unsigned)((n4 + 255) / 256 < 4736 ? (n4 + 255) / 256 : 4736);
+        prefill_rope_scatter_v4_kernel<<<g4, 256, 0, ckb_stream(stream)>>>(q_tm, k_tm, v_tm, q_hm, k_cache, v_cache, cos_cache, sin_cache, tokens, num_heads,
+                                                                           num_kv_heads, head_dim, max_seq_len, pos0);
+        return ckb_check_launch("prefill_rope_scatter");
+    }
     const unsigned grid = (unsigned)((n + 255) / 256 < 4736 ? (n + 255) / 256 : 4736);
     prefill_rope_scatter_kernel<<<grid, 256, 0, ckb_stream(stream)>>>(q_tm, k_tm, v_tm, q_hm, k_cache, v_cache, cos_cache, sin_cache, tokens, num_heads, num_kv_heads,
                                                                       head_dim, max_seq_len, pos0);

@@ -902,3 +902,47 @@ def test_swiglu_q8k_aligned_and_unaligned_inputs(ck, orc, tokens, dim):
     got = (d * qs).reshape(tokens, dim)
     step = np.abs(np.repeat(d.reshape(tokens, nb), 256, axis=1))            # Q8_K's d carries the sign of the block's largest element
     assert np.all(np.abs(got - want) <= 0.51 * step + 1e-4 * np.abs(want) + 1e-6)
+
+
+@pytest.mark.parametrize("heads,kvh,d,tokens,cap,pos0", [(8, 2, 128, 37, 64, 0), (14, 2, 64, 20, 32, 5), (4, 4, 72, 9, 16, 0)])
+def test_prefill_rope_scatter_vector_and_scalar_forms(ck, heads, kvh, d, tokens, cap, pos0):
+    """prefill_rope_scatter (rotate-half RoPE of q and k, head-major q, k and v rows into the caches) takes 16-byte accesses when
+    every pointer is aligned and the head size a multiple of 8, 4-byte accesses otherwise: both forms give the same bits and match
+    the rotation computed here."""
+    import torch
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu").manual_seed(heads * 100 + d)
+    q = torch.randn(tokens, heads, d, generator=g)
+    k = torch.randn(tokens, kvh, d, generator=g)
+    v = torch.randn(tokens, kvh, d, generator=g)
+    half = d // 2
+    ang = torch.rand(cap, half, generator=g) * 6.0
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    outs = []
+    for off in (0, 1):                                          # off = 1: q_tm is only 4-byte aligned -> the scalar form
+        qb = torch.zeros(q.numel() + 4, device=dev)
+        qb[off:off + q.numel()] = q.reshape(-1).to(dev)
+        kd, vd, cd, sd = k.to(dev).contiguous(), v.to(dev).contiguous(), cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        qh = torch.zeros(heads, tokens, d, device=dev)
+        kc = torch.zeros(kvh, cap, d, device=dev)
+        vc = torch.zeros(kvh, cap, d, device=dev)
+        torch.cuda.synchronize()
+        assert ck.ckb200_dev_prefill_rope_scatter(C.c_void_p(qb.data_ptr() + 4 * off), C.c_void_p(kd.data_ptr()), C.c_void_p(vd.data_ptr()), C.c_void_p(qh.data_ptr()),
+                                                  C.c_void_p(kc.data_ptr()), C.c_void_p(vc.data_ptr()), C.c_void_p(cd.data_ptr()), C.c_void_p(sd.data_ptr()),
+                                                  tokens, heads, kvh, d, cap, pos0, None) == 0
+        assert ck.ckb200_synchronize() == 0
+        outs.append((qh.cpu(), kc.cpu(), vc.cpu()))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    c, s = cos[pos0:pos0 + tokens, None, :], sin[pos0:pos0 + tokens, None, :]
+
+    def rot(x):
+        a, b = x[..., :half], x[..., half:]
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+
+    qh, kc, vc = outs[0]
+    assert torch.allclose(qh, rot(q).permute(1, 0, 2), rtol=0, atol=2e-6)
+    assert torch.allclose(kc[:, pos0:pos0 + tokens], rot(k).permute(1, 0, 2), rtol=0, atol=2e-6)
+    assert torch.equal(vc[:, pos0:pos0 + tokens], v.permute(1, 0, 2))
+    assert float(kc[:, pos0 + tokens:].abs().max()) == 0.0 if pos0 + tokens < cap else True
